@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload (metric: Q4_K GEMV HBM GB/s): the decode GEMV of BASELINE.json's first
+config — Q4_K weight [4096, 4096] x f32 activation row — run over a ring of 64 distinct
+weights (604 MB, larger than the 126 MB L2) so every launch streams from HBM.  One step =
+one pass over the ring = 64 GEMV launches replayed from a CUDA graph.  Weights are resident
+in HBM before the timed region (the engine uploads weights once at load).
+
+`value` is device-timed with CUDA events on the launching stream; `e2e` is the same pass
+through the C ABI with HOST activations and results (pinned host -> device copy of the 64
+activation rows, 64 GEMVs, device -> host copy of the 64 result rows, every step).
+
+With --impl reference the reference's own CPU path (the oracle restatement of matvec_kq,
+all host threads) is timed on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_ROWS = K_COLS = 4096
+RING = 64
+Q4K_BYTES = N_ROWS * K_COLS // 256 * 144                      # GGUF bytes of one weight
+ALGO_BYTES_PER_LAUNCH = Q4K_BYTES + 4 * K_COLS + 4 * N_ROWS      # weight + x + y (f32)
+METRIC = "Q4_K GEMV HBM GB/s"
+WORKLOAD = "q4k_gemv_n4096_k4096_m1_ring64"
+
+
+def measured_peaks() -> tuple[float, float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            p = json.load(fh)
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs (read-only queries)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ inputs
+def ring_weights(count: int, seed: int) -> list[np.ndarray]:
+    """`count` distinct Q4_K [4096, 4096] weights: N(0, 0.02) quantized with the library's
+    test-input encoder (the first from `seed`), the rest row-rotations of a few bases
+    so set-up stays short; HBM streaming only needs distinct bytes at distinct addresses."""
+    import ojas_engine_b200 as ob
+    bases = []
+    for b in range(4):
+        rng = np.random.default_rng(seed + b)
+        w = rng.standard_normal((N_ROWS, K_COLS), dtype=np.float32) * np.float32(0.02)
+        bases.append(ob.encode(ob.Q4_K, w).reshape(N_ROWS, -1))
+    out = []
+    for i in range(count):
+        out.append(np.ascontiguousarray(np.roll(bases[i % 4], 97 * (i // 4), axis=0)).reshape(-1))
+    return out
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_reference_pass(weights: list[np.ndarray], x: np.ndarray, seconds: float, threads: int, native: bool):
+    """Times the oracle's matvec_kq over a bounded sample; returns (GB/s, matvecs, elapsed)."""
+    import oracle
+    import ojas_engine_b200 as ob
+    oracle.matvec_kq(weights[0], ob.Q4_K, N_ROWS, K_COLS, x[0], threads, native)  # warm-up
+    done, t0 = 0, time.perf_counter()
+    while True:
+        i = done % len(weights)
+        oracle.matvec_kq(weights[i], ob.Q4_K, N_ROWS, K_COLS, x[i % x.shape[0]], threads, native)
+        done += 1
+        el = time.perf_counter() - t0
+        if el >= seconds:
+            break
+    return done * ALGO_BYTES_PER_LAUNCH / el / 1e9, done, el
+
+
+def oracle_native_ok() -> bool:
+    try:
+        import oracle
+        oracle.lib(native=True)
+        return True
+    except Exception:
+        return False
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    native = oracle_native_ok()
+    weights = ring_weights(4, 0)
+    x = np.random.default_rng(1).standard_normal((4, K_COLS), dtype=np.float32)
+    per_step = max(1, 8)  # matvecs per step: a bounded sample of the 64-weight pass
+    import oracle
+    import ojas_engine_b200 as ob
+    for _ in range(max(args.warmup, 1)):
+        oracle.matvec_kq(weights[0], ob.Q4_K, N_ROWS, K_COLS, x[0], threads, native)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        for j in range(per_step):
+            oracle.matvec_kq(weights[j % 4], ob.Q4_K, N_ROWS, K_COLS, x[j % 4], threads, native)
+    el = time.perf_counter() - t0
+    gbs = args.steps * per_step * ALGO_BYTES_PER_LAUNCH / el / 1e9
+    sample = f"{per_step} of the {RING} ring GEMVs per step, oracle matvec_kq ({'-march=native' if native else 'portable'} build)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x u4 block dots, f32 combine", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "where": "host CPU"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def time_graph(gpu, graph, steps: int, warmup: int) -> float:
+    for _ in range(warmup):
+        gpu.graph_launch(graph)
+    gpu.sync()
+    e0, e1 = gpu.event(), gpu.event()
+    gpu.record(e0)
+    for _ in range(steps):
+        gpu.graph_launch(graph)
+    gpu.record(e1)
+    gpu.sync()
+    return gpu.elapsed_ms(e0, e1)
+
+
+def extra_gemv(gpu, ob, ggml_type: int, n: int, k: int, m: int, peak: float, tag: str) -> dict:
+    """One more GEMV shape, ring sized past L2, timed the same way (reported, not the headline)."""
+    import oracle
+    gguf = ob.raw_bytes(ggml_type, n, k)
+    ring = max(2, int(300e6 // gguf) + 1)
+    base = oracle.synth_blocks(ggml_type, n * k // (32 if ggml_type == ob.Q8_0 else 256)).reshape(n, -1)
+    ws = [gpu.load_weight(np.ascontiguousarray(np.roll(base, 13 * i, axis=0)), ggml_type, n, k) for i in range(ring)]
+    x = gpu.upload(np.random.default_rng(7).standard_normal((m, k), dtype=np.float32))
+    y = gpu.alloc(m * n)
+    gpu.gemv(ws[0], x, y, m)
+    gpu.sync()
+    gpu.graph_begin()
+    for w in ws:
+        gpu.gemv(w, x, y, m)
+    g = gpu.graph_end()
+    reps = max(3, int(2000 // ring))
+    ms = time_graph(gpu, g, reps, 3)
+    gpu.graph_destroy(g)
+    per_launch_us = ms * 1e3 / (reps * ring)
+    algo = gguf + 4 * m * (k + n)
+    gbs = algo / (per_launch_us * 1e-6) / 1e9
+    for w in ws:
+        gpu.free(w.buf)
+    gpu.free(x)
+    gpu.free(y)
+    return {"workload": f"{tag}_gemv_n{n}_k{k}_m{m}", "us_per_launch": round(per_launch_us, 3), "GB/s": round(gbs, 1),
+            "frac_of_peak": round(gbs / peak, 4), "ring": ring}
+
+
+def run_ours(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist  # plumbing only: barrier, max over ranks, the all-gather
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import ojas_engine_b200 as ob
+
+    hbm_peak, _, peak_kind = measured_peaks()
+    gpu = ob.B200Gpu(local)
+    raws = ring_weights(RING, seed=rank * 1000)
+    weights = [gpu.load_weight(r, ob.Q4_K, N_ROWS, K_COLS) for r in raws]
+    rng = np.random.default_rng(1 + rank)
+    x_host = gpu.host_alloc(RING * K_COLS * 4, np.float32)
+    x_host[:] = rng.standard_normal(RING * K_COLS, dtype=np.float32)
+    y_host = gpu.host_alloc(RING * N_ROWS * 4, np.float32)
+    xd = gpu.upload(x_host)
+    yd = gpu.alloc(RING * N_ROWS)
+
+    def launch_pass():
+        for i, w in enumerate(weights):
+            gpu.gemv(w, ob.Buf(xd.ptr + i * K_COLS * 4, K_COLS * 4), ob.Buf(yd.ptr + i * N_ROWS * 4, N_ROWS * 4), 1)
+
+    launch_pass()  # outside capture: one-time function attribute set-up
+    gpu.sync()
+    l0 = gpu.launch_count
+    gpu.graph_begin()
+    launch_pass()
+    graph = gpu.graph_end()
+    launches_per_step = gpu.launch_count - l0
+
+    # multi-GPU: each rank owns the row shard [rank*4096, (rank+1)*4096) of a [world*4096, 4096]
+    # projection per ring slot (column-parallel); the shards are joined by ONE all-gather of the
+    # step's outputs.  No other data-path collective.
+    gathered = y_view = ext_stream = None
+    if dist is not None:
+        import torch
+        y_view = _wrap_device_f32(yd.ptr, RING * N_ROWS, local)       # the library's output buffer, no copy
+        gathered = torch.empty(world * RING * N_ROWS, dtype=torch.float32, device=f"cuda:{local}")
+        ext_stream = torch.cuda.ExternalStream(gpu.stream, device=f"cuda:{local}")
+
+    def step():
+        gpu.graph_launch(graph)
+        if dist is not None:
+            import torch
+            with torch.cuda.stream(ext_stream):                        # ordered after the pass on the same stream
+                dist.all_gather_into_tensor(gathered, y_view)
+
+    for _ in range(args.warmup):
+        step()
+    gpu.sync()
+    if dist is not None:
+        import torch
+        torch.cuda.synchronize()
+        dist.barrier()
+    e0, e1 = gpu.event(), gpu.event()
+    with ClockSampler(local) as clocks:
+        gpu.record(e0)
+        for _ in range(args.steps):
+            step()
+        gpu.record(e1)
+        gpu.sync()
+        if dist is not None:
+            import torch
+            torch.cuda.synchronize()
+            dist.barrier()
+    ms = gpu.elapsed_ms(e0, e1)
+    if dist is not None:
+        import torch
+        t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    bytes_per_step_all = world * RING * ALGO_BYTES_PER_LAUNCH
+    value = bytes_per_step_all / (ms_per_step * 1e-3) / 1e9
+    us_per_launch = ms_per_step * 1e3 / RING
+    achieved = ALGO_BYTES_PER_LAUNCH / (us_per_launch * 1e-6) / 1e9
+
+    # parity spot check of the timed buffers against the oracle (not timed)
+    parity = None
+    if rank == 0:
+        import oracle
+        got = gpu.read(yd, np.float32, N_ROWS)
+        want = oracle.matvec_kq(raws[0], ob.Q4_K, N_ROWS, K_COLS, np.asarray(x_host[:K_COLS]))
+        parity = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+
+    # end to end through the C ABI with host buffers: H2D of the step's activations, the pass,
+    # D2H of the step's results, one synchronisation per step.
+    e2e = None
+    if rank == 0 or dist is not None:
+        gpu.graph_begin()
+        gpu._ck(gpu._l.ojas_b200_upload(gpu.ctx, xd.ptr, x_host.ctypes.data, x_host.nbytes))
+        launch_pass()
+        gpu._ck(gpu._l.ojas_b200_download(gpu.ctx, y_host.ctypes.data, yd.ptr, y_host.nbytes))
+        g2 = gpu.graph_end()
+        for _ in range(max(3, args.warmup)):
+            gpu.graph_launch(g2)
+            gpu.sync()
+        if dist is not None:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            gpu.graph_launch(g2)
+            gpu.sync()
+        el = time.perf_counter() - t0
+        if dist is not None:
+            import torch
+            t = torch.tensor([el], dtype=torch.float64, device=f"cuda:{local}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            el = float(t.item())
+        e2e = {"value": bytes_per_step_all * args.steps / el / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": int(x_host.nbytes) * world, "d2h_bytes_per_step": int(y_host.nbytes) * world,
+               "ms_per_step": el / args.steps * 1e3}
+        gpu.graph_destroy(g2)
+
+    if rank == 0:
+        cpu = None
+        extras = []
+        if world == 1:
+            threads = os.cpu_count() or 1
+            native = oracle_native_ok()
+            gbs, n_mv, el = cpu_reference_pass(raws[:8], np.asarray(x_host).reshape(RING, K_COLS), 10.0, threads, native)
+            cpu = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                   "sample": f"{n_mv} matvec_kq calls over 8 of the ring weights in {el:.1f} s ({'-march=native' if native else 'portable'} oracle build)"}
+            if not args.no_extras:
+                for (t, n, k, m, tag) in [(ob.Q4_K, 28672, 8192, 1, "q4k"), (ob.Q4_K, 14336, 4096, 1, "q4k"),
+                                          (ob.Q6_K, 14336, 4096, 1, "q6k"), (ob.Q6_K, 4096, 14336, 1, "q6k"),
+                                          (ob.Q8_0, 14336, 4096, 1, "q80"), (ob.Q8_0, 4096, 14336, 1, "q80"),
+                                          (ob.Q4_K, 4096, 4096, 8, "q4k"), (ob.Q6_K, 14336, 4096, 8, "q6k"),
+                                          (ob.Q8_0, 14336, 4096, 8, "q80")]:
+                    try:
+                        extras.append(extra_gemv(gpu, ob, t, n, k, m, hbm_peak, tag))
+                    except Exception as exc:  # an extra must not take the headline down
+                        extras.append({"workload": f"{tag}_gemv_n{n}_k{k}_m{m}", "error": str(exc)})
+        traffic = profile_traffic()
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 x u4 block dots (exact int32), f32 combine", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "ring_bytes": RING * Q4K_BYTES, "l2": "inputs larger than L2 (ring of 64 weights, 604 MB)",
+                       "launch": "CUDA graph of 64 kernel launches per step",
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel row shards x{world}, one NCCL all-gather per step"},
+            "pct_of_8TBps": value / world / 8000.0,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                         "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "gemv_q4k_kernel<1,false,false>",
+                         "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH, "us_per_launch": us_per_launch},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary, "parity_rel_l2_vs_oracle": parity, "extras": extras,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    gpu.close()
+
+
+def _wrap_device_f32(ptr: int, count: int, device: int):
+    """A torch view of a device buffer owned by the library (for the NCCL collective)."""
+    import torch
+
+    class _Holder:
+        pass
+
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (ptr, False), "version": 3, "strides": None}
+    return torch.as_tensor(h, device=f"cuda:{device}")
+
+
+def profile_traffic():
+    """DRAM bytes per launch of the GEMV kernel from the committed ncu summary, if present."""
+    path = os.path.join(ROOT, "profiles", "gemv_q4k_4096x4096.json")
+    try:
+        with open(path) as fh:
+            return json.load(fh).get("dram_bytes_per_launch")
+    except Exception:
+        return None
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the additional GEMV shapes")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

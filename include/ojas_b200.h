@@ -1,0 +1,151 @@
+/*
+ * ojas_b200.h — C ABI of the B200 (sm_100a) quantized-matmul backend.
+ *
+ * Every entry point takes plain pointers and sizes.  Device pointers are raw CUDA
+ * device addresses (what the engine's CuBuf holds, crates/ojas-cuda/src/device.rs:20-23);
+ * nothing here allocates unless its comment says so, and every launch is
+ * asynchronous on the context's stream (errors surface at ojas_b200_sync, like the
+ * engine's submit(), crates/ojas-cuda/src/device.rs:534-536).
+ *
+ * All functions return 0 on success or a negative ojas_b200_status; the message of
+ * the most recent failure on a context is kept by ojas_b200_last_error().
+ *
+ * Data contract (crates/ojas-cuda/src/kernels/gemm_q.rs:1-4): x is [M,K] f32
+ * row-major, W is [N,K] with one output per row (y = x * W^T), y is [M,N] f32.
+ * K must be a multiple of 256 (crates/ojas-cpu/src/cpu_math.rs:1148).
+ */
+#ifndef OJAS_B200_H
+#define OJAS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define OJAS_B200_API __attribute__((visibility("default")))
+#else
+#define OJAS_B200_API
+#endif
+
+typedef struct ojas_b200_ctx ojas_b200_ctx;
+
+/* GGUF tensor type codes on this path (crates/ojas-formats/src/synth.rs:12-21). */
+enum { OJAS_B200_Q8_0 = 8, OJAS_B200_Q4_K = 12, OJAS_B200_Q6_K = 14 };
+
+/* Store forms of the native GEMV family: y = acc, y += acc, y = acc + bias
+ * (crates/ojas-cuda/src/kernels/nat.rs:69-91). */
+enum { OJAS_B200_PLAIN = 0, OJAS_B200_ACCUM = 1, OJAS_B200_BIAS = 2 };
+
+typedef enum {
+    OJAS_B200_OK = 0,
+    OJAS_B200_E_ARG = -1,      /* bad shape, null pointer, unsupported type */
+    OJAS_B200_E_CUDA = -2,     /* a CUDA call failed; message holds the CUDA error */
+    OJAS_B200_E_UNSUPPORTED = -3,
+    OJAS_B200_E_NAME = -4,     /* ojas_b200_dispatch: unknown kernel name */
+    OJAS_B200_E_DEVICE = -5,   /* a kernel reported a bounded wait that ran out */
+    OJAS_B200_E_LIMIT = -6     /* size beyond a fixed capacity */
+} ojas_b200_status;
+
+/* ---- context: replaces CudaGpu (crates/ojas-cuda/src/device.rs:87-146): one device, one
+ * stream.  `stream` is a cudaStream_t to adopt, or NULL to create a private non-blocking
+ * stream.  Allocates only host memory. */
+OJAS_B200_API int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out);
+OJAS_B200_API void ojas_b200_destroy(ojas_b200_ctx *ctx);
+OJAS_B200_API int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream);
+OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
+OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
+OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
+/* Launches issued by this context since creation (the benchmark's launch counter). */
+OJAS_B200_API uint64_t ojas_b200_launch_count(ojas_b200_ctx *ctx);
+OJAS_B200_API const char *ojas_b200_version(void);
+
+/* ---- Device trait helpers (crates/ojas-core/src/lib.rs:26-40: alloc / upload / read) and
+ * submit (crates/ojas-core/src/kernel.rs:82).  For callers that have no CUDA runtime of
+ * their own; a caller that already owns device memory passes its pointers directly. */
+OJAS_B200_API int ojas_b200_alloc(ojas_b200_ctx *ctx, size_t bytes, void **dptr);
+OJAS_B200_API int ojas_b200_free(ojas_b200_ctx *ctx, void *dptr);
+OJAS_B200_API int ojas_b200_upload(ojas_b200_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+OJAS_B200_API int ojas_b200_download(ojas_b200_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+OJAS_B200_API int ojas_b200_memset(ojas_b200_ctx *ctx, void *dst_dev, int value, size_t bytes);
+OJAS_B200_API int ojas_b200_sync(ojas_b200_ctx *ctx);
+
+/* ---- timing and graphs: the event profiler and capture/replay of the CUDA device
+ * (crates/ojas-cuda/src/device.rs:275-318 KernelProfile, :541-554 begin_capture / end_capture /
+ * replay).  Every kernel of this library is capture-safe: no allocation, no host
+ * synchronisation, no host state that changes launch arguments between replays. */
+OJAS_B200_API int ojas_b200_event_create(ojas_b200_ctx *ctx, void **event);
+OJAS_B200_API int ojas_b200_event_destroy(ojas_b200_ctx *ctx, void *event);
+OJAS_B200_API int ojas_b200_event_record(ojas_b200_ctx *ctx, void *event);
+OJAS_B200_API int ojas_b200_event_elapsed_ms(ojas_b200_ctx *ctx, void *start, void *stop, float *ms);
+OJAS_B200_API int ojas_b200_graph_begin(ojas_b200_ctx *ctx);
+OJAS_B200_API int ojas_b200_graph_end(ojas_b200_ctx *ctx, void **graph_exec);
+OJAS_B200_API int ojas_b200_graph_launch(ojas_b200_ctx *ctx, void *graph_exec);
+OJAS_B200_API int ojas_b200_graph_destroy(ojas_b200_ctx *ctx, void *graph_exec);
+/* Pinned host staging memory (the expert cache stages through pinned memory,
+ * crates/ojas-cuda/src/expert_cache.rs:93-150). */
+OJAS_B200_API int ojas_b200_host_alloc(ojas_b200_ctx *ctx, size_t bytes, void **hptr);
+OJAS_B200_API int ojas_b200_host_free(ojas_b200_ctx *ctx, void *hptr);
+
+/* ---- upload layout: replaces Repr / Lin::load_as (crates/ojas-cuda/src/qwen35.rs:146-226)
+ * and relayout_q4k_q4l (crates/ojas-formats/src/quant.rs:192-222).  GGUF blocks are re-laid
+ * once at load into 16-byte-aligned planes (lossless: every GGUF bit is kept, no f16
+ * rounding of products).  raw_bytes = N * K/256 * {144, 210, 272}. */
+OJAS_B200_API size_t ojas_b200_raw_bytes(uint32_t ggml_type, size_t N, size_t K);
+OJAS_B200_API size_t ojas_b200_repacked_bytes(uint32_t ggml_type, size_t N, size_t K);
+/* raw_dev: GGUF blocks in device memory, rows contiguous.  out_dev: repacked_bytes bytes,
+ * 256-byte aligned.  Runs on the stream. */
+OJAS_B200_API int ojas_b200_repack(ojas_b200_ctx *ctx, uint32_t ggml_type, const void *raw_dev, size_t N, size_t K,
+                     void *out_dev);
+/* Host restatement of the same layout (for a loader that repacks before upload, and for
+ * checking the device kernel). */
+OJAS_B200_API int ojas_b200_repack_host(uint32_t ggml_type, const void *raw_host, size_t N, size_t K, void *out_host);
+
+/* ---- activations: device form of quant_q8k (crates/ojas-cpu/src/cpu_math.rs:545-563).
+ * x [M,K] f32 -> q [M,K] i8, scales [M,K/256] f32, bsums [M,K/32] i32; bit-identical to the
+ * CPU routine (round half away from zero, scale = amax/127 or 1). */
+OJAS_B200_API int ojas_b200_quant_q8k(ojas_b200_ctx *ctx, const float *x, size_t M, size_t K, int8_t *q, float *scales,
+                        int32_t *bsums);
+
+/* ---- decode GEMV: replaces gemv_nat_{q4k,q6k,q80}{,_accum,_bias,_m}
+ * (crates/ojas-cuda/src/kernels/nat.rs:69-91; bodies crates/ojas-core/src/quant_src.rs:779-867,
+ * 1028-1057, 1154-1180) with the arithmetic of matvec_kq (crates/ojas-cpu/src/cpu_math.rs:
+ * 1145-1189): Q4_K / Q6_K rows meet int8 Q8_K activations in exact integer block dots, Q8_0
+ * rows meet f32 activations.  w is the repacked weight.  M <= OJAS_B200_GEMV_MAX_M. */
+#define OJAS_B200_GEMV_MAX_M 8
+OJAS_B200_API int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *x, const void *w, float *y,
+                   const float *bias, size_t K, size_t N, size_t M);
+/* Same, with activations already quantized by ojas_b200_quant_q8k (Q4_K / Q6_K only):
+ * one quantization can feed several projections (gate and up read the same row). */
+OJAS_B200_API int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const int8_t *q, const float *scales,
+                       const int32_t *bsums, const void *w, float *y, const float *bias, size_t K, size_t N,
+                       size_t M);
+/* Checking aid: the integer sub-block dots of row-0 activations against every weight row,
+ * exactly as dot_q4k / dot_q6k form them (crates/ojas-cpu/src/cpu_math.rs:619-632, 703-719):
+ * Q4_K -> idots [N, K/32], Q6_K -> idots [N, K/16] (int32). */
+OJAS_B200_API int ojas_b200_gemv_idots(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, int32_t *idots,
+                         size_t K, size_t N);
+
+/* ---- name-based dispatch: the C form of KernelRuntime::dispatch / has_kernel
+ * (crates/ojas-core/src/kernel.rs:68-83; argument marshalling crates/ojas-cuda/src/device.rs:
+ * 391-415): buffers are (device pointer, byte offset) pairs in the kernel's positional order,
+ * then the u32 constants.  grid and block are accepted for signature compatibility and
+ * ignored.  Names served: gemv_nat_{q4k,q6k,q80}{,_accum,_bias,_m}
+ * (crates/ojas-cuda/src/kernels/nat.rs:56-64) and the entries listed by ojas_b200_kernel_name. */
+OJAS_B200_API int ojas_b200_has_kernel(const char *name);
+OJAS_B200_API int ojas_b200_kernel_count(void);
+OJAS_B200_API const char *ojas_b200_kernel_name(int index);
+OJAS_B200_API int ojas_b200_dispatch(ojas_b200_ctx *ctx, const char *name, void *const *bufs, const uint64_t *offsets, int nbufs,
+                       const uint32_t *consts, int nconsts, const uint32_t grid[3], const uint32_t block[3]);
+
+/* ---- test-input encoders (host): f32 [N,K] -> GGUF blocks.  The reference has no encoder
+ * for these formats (its GEMM tests use random blocks, crates/ojas-formats/src/synth.rs:29);
+ * these simple min/max encoders exist so seeded N(0, sigma) matrices can become legal blocks. */
+OJAS_B200_API int ojas_b200_encode_host(uint32_t ggml_type, const float *w, size_t N, size_t K, void *raw_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OJAS_B200_H */

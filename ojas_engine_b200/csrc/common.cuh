@@ -1,0 +1,126 @@
+// Shared declarations of the B200 quantized-matmul library: the context object behind the
+// C ABI, status plumbing, the repacked-weight layouts, and small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/ojas_b200.h"
+
+// ---------------------------------------------------------------------------- context
+struct ojas_b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
+    uint64_t launches = 0;
+    unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
+    unsigned int *dev_status = nullptr;  // the same word as the device sees it
+    char err[512] = {0};
+};
+
+int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
+
+#define OJAS_CUDA(ctx, call)                                                                     \
+    do {                                                                                         \
+        cudaError_t e__ = (call);                                                                \
+        if (e__ != cudaSuccess)                                                                  \
+            return ojas_fail((ctx), OJAS_B200_E_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define OJAS_LAUNCH_CHECK(ctx, what)                                                                  \
+    do {                                                                                              \
+        cudaError_t e__ = cudaGetLastError();                                                         \
+        if (e__ != cudaSuccess)                                                                       \
+            return ojas_fail((ctx), OJAS_B200_E_CUDA, "launch %s: %s", what, cudaGetErrorString(e__)); \
+        (ctx)->launches++;                                                                            \
+    } while (0)
+
+// ---------------------------------------------------------------------------- layouts
+// Repacked weights are a set of planes in one buffer; every plane starts on a 256-byte
+// boundary and every row of every plane is a whole number of 16-byte units.
+//
+// Q4_K  (GGUF: 144 B per 256 weights: f16 d, f16 dmin, u8 sc[12], u8 qs[128])
+//   plane qs : [N][K/256][128]  nibbles; within a super-block byte h*64 + c*16 + i holds
+//              GGUF qs[c*32 + h*16 + i] (c = 64-weight chunk 0..3, h = 16-byte half), so the
+//              four lanes that share a super-block read 64 contiguous bytes per load.
+//   plane hdr: [N][K/256][16]   the GGUF header bytes 0..15 unchanged (d, dmin, sc[12]).
+// Q6_K  (GGUF: 210 B per 256: u8 ql[128], u8 qh[64], i8 sc[16], f16 d)
+//   plane lo : [N][K/256][128]  low nibbles; byte h*64 + c*16 + i: low nibble = weight
+//              64c + 16h + i, high nibble = weight 64c + 32 + 16h + i.
+//   plane hi : [N][K/256][64]   top two bits; byte c*16 + k*4 + i: bit field t (bits 2t, 2t+1)
+//              = weight 64c + 16t + 4k + i.
+//   plane sc : [N][K/256][16]   int8 sub-scales, GGUF order.
+//   plane d  : [N][K/256]       f16 super-block scale.
+// Q8_0  (GGUF: 34 B per 32: f16 d, i8 q[32])
+//   plane q  : [N][K]           int8, natural order.
+//   plane d  : [N][K/32]        f16.
+struct WeightPlanes {
+    const uint8_t *p0, *p1, *p2, *p3;
+};
+
+static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static inline int plane_offsets(uint32_t type, size_t N, size_t K, size_t off[5]) {
+    size_t nsb = K / 256;
+    off[0] = 0;
+    switch (type) {
+    case OJAS_B200_Q4_K:
+        off[1] = align256(N * nsb * 128);
+        off[2] = off[3] = off[4] = off[1] + align256(N * nsb * 16);
+        return 0;
+    case OJAS_B200_Q6_K:
+        off[1] = align256(N * nsb * 128);
+        off[2] = off[1] + align256(N * nsb * 64);
+        off[3] = off[2] + align256(N * nsb * 16);
+        off[4] = off[3] + align256(N * nsb * 2);
+        return 0;
+    case OJAS_B200_Q8_0:
+        off[1] = align256(N * K);
+        off[2] = off[3] = off[4] = off[1] + align256(N * (K / 32) * 2);
+        return 0;
+    default:
+        return -1;
+    }
+}
+
+static inline WeightPlanes weight_planes(uint32_t type, const void *w, size_t N, size_t K) {
+    size_t off[5];
+    plane_offsets(type, N, K, off);
+    const uint8_t *b = (const uint8_t *)w;
+    return WeightPlanes{b + off[0], b + off[1], b + off[2], b + off[3]};
+}
+
+// ---------------------------------------------------------------------------- device helpers
+#ifdef __CUDACC__
+__device__ __forceinline__ uint4 ldg_stream_u4(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+    return __half2float(__ushort_as_half((unsigned short)(h & 0xffffu)));
+}
+
+// round half away from zero, exactly (v - trunc(v) is exact in binary32), as Rust's
+// f32::round does (crates/ojas-cpu/src/cpu_math.rs:557).
+__device__ __forceinline__ float round_half_away(float v) {
+    float r = truncf(v);
+    float f = v - r;
+    if (fabsf(f) >= 0.5f) r += copysignf(1.0f, v);
+    return r;
+}
+#endif

@@ -1,0 +1,282 @@
+"""Host-side mirror of the engine's backend interface for the quantized-matmul path.
+
+``B200Gpu`` plays the part of ``CudaGpu`` (crates/ojas-cuda/src/device.rs:87-146, 418-537): it
+owns one device + one stream and offers the ``Device`` calls (alloc / upload / read,
+crates/ojas-core/src/lib.rs:26-40) and the ``KernelRuntime`` calls (has_kernel / begin /
+dispatch / submit, crates/ojas-core/src/kernel.rs:68-83) with the same names and argument
+meaning.  ``Lin`` is the loaded weight (crates/ojas-cuda/src/qwen35.rs:146-226) and ``mm`` the
+matmul operator (``CudaSsm::mm``, crates/ojas-cuda/src/qwen35.rs:644-702).  Everything
+computes through the C ABI; nothing here falls back to the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import lib as _lib
+
+Q8_0, Q4_K, Q6_K = 8, 12, 14
+PLAIN, ACCUM, BIAS = 0, 1, 2
+GEMV_MAX_M = 8
+_TAGS = {Q4_K: "q4k", Q6_K: "q6k", Q8_0: "q80"}
+
+
+class OjasB200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"ojas_b200 error {code}: {message}")
+        self.code = code
+
+
+@dataclass
+class Buf:
+    """A device allocation (the engine's CuBuf, crates/ojas-cuda/src/device.rs:20-23)."""
+    ptr: int
+    nbytes: int
+
+    def at(self, byte_offset: int) -> int:
+        return self.ptr + byte_offset
+
+
+@dataclass
+class Lin:
+    """A weight as it lives on the device: repacked planes + its GGUF type and shape
+    ([n, k]: one output per row).  Counterpart of ``Lin`` / ``Repr`` in
+    crates/ojas-cuda/src/qwen35.rs:146-226."""
+    buf: Buf
+    ggml_type: int
+    n: int
+    k: int
+
+    @property
+    def gguf_bytes(self) -> int:
+        return _lib.load().ojas_b200_raw_bytes(self.ggml_type, self.n, self.k)
+
+
+class Enc:
+    """A chain of dispatches on the context's stream (``KernelRuntime::begin``)."""
+
+    def __init__(self) -> None:
+        self.dispatches = 0
+
+
+class B200Gpu:
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._l = _lib.load()
+        ctx = C.c_void_p()
+        rc = self._l.ojas_b200_create(device, C.c_void_p(stream) if stream else None, C.byref(ctx))
+        if rc != 0:
+            why = {-1: "no such device", -2: "CUDA runtime error (no GPU?)", -3: "device is not sm_100 (B200)"}.get(rc, "")
+            raise OjasB200Error(rc, f"ojas_b200_create(device={device}) failed: {why}")
+        self._ctx = ctx
+        self.device = device
+
+    # ------------------------------------------------------------------ plumbing
+    def _ck(self, rc: int) -> None:
+        if rc != 0:
+            raise OjasB200Error(rc, self._l.ojas_b200_last_error(self._ctx).decode())
+
+    def close(self) -> None:
+        if getattr(self, "_ctx", None):
+            self._l.ojas_b200_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def ctx(self) -> C.c_void_p:
+        return self._ctx
+
+    @property
+    def sm_count(self) -> int:
+        return self._l.ojas_b200_sm_count(self._ctx)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._l.ojas_b200_launch_count(self._ctx))
+
+    @property
+    def stream(self) -> int:
+        return int(self._l.ojas_b200_stream(self._ctx) or 0)
+
+    # ------------------------------------------------------------------ Device
+    def alloc_bytes(self, nbytes: int) -> Buf:
+        p = C.c_void_p()
+        self._ck(self._l.ojas_b200_alloc(self._ctx, nbytes, C.byref(p)))
+        return Buf(int(p.value), nbytes)
+
+    def alloc(self, len_f32: int) -> Buf:
+        """``Device::alloc``: room for ``len_f32`` floats."""
+        return self.alloc_bytes(len_f32 * 4)
+
+    def free(self, buf: Buf) -> None:
+        self._ck(self._l.ojas_b200_free(self._ctx, C.c_void_p(buf.ptr)))
+
+    def write(self, buf: Buf, data: np.ndarray, byte_offset: int = 0) -> None:
+        data = np.ascontiguousarray(data)
+        assert byte_offset + data.nbytes <= buf.nbytes
+        self._ck(self._l.ojas_b200_upload(self._ctx, C.c_void_p(buf.ptr + byte_offset), data.ctypes.data_as(C.c_void_p), data.nbytes))
+        self.sync()  # the host array may be pageable and short-lived
+
+    def upload(self, data: np.ndarray) -> Buf:
+        """``Device::upload``: a new buffer holding ``data``."""
+        data = np.ascontiguousarray(data)
+        buf = self.alloc_bytes(max(data.nbytes, 1))
+        if data.nbytes:
+            self.write(buf, data)
+        return buf
+
+    def read(self, buf: Buf, dtype, count: int, byte_offset: int = 0) -> np.ndarray:
+        """``Device::read``: waits for the stream, then copies ``count`` items back."""
+        out = np.empty(count, dtype)
+        assert byte_offset + out.nbytes <= buf.nbytes
+        self._ck(self._l.ojas_b200_download(self._ctx, out.ctypes.data_as(C.c_void_p), C.c_void_p(buf.ptr + byte_offset), out.nbytes))
+        self.sync()
+        return out
+
+    def memset(self, buf: Buf, value: int = 0) -> None:
+        self._ck(self._l.ojas_b200_memset(self._ctx, C.c_void_p(buf.ptr), value, buf.nbytes))
+
+    def sync(self) -> None:
+        self._ck(self._l.ojas_b200_sync(self._ctx))
+
+    # ------------------------------------------------------------------ upload layout
+    def load_weight(self, raw: np.ndarray, ggml_type: int, n: int, k: int) -> Lin:
+        """``Lin::load_as``: GGUF blocks (host bytes) -> repacked planes on the device."""
+        raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+        want = self._l.ojas_b200_raw_bytes(ggml_type, n, k)
+        if want == 0 or raw.size != want:
+            raise OjasB200Error(-1, f"load_weight: type {ggml_type} [{n},{k}] needs {want} bytes, got {raw.size}")
+        tmp = self.upload(raw)
+        out = self.alloc_bytes(self._l.ojas_b200_repacked_bytes(ggml_type, n, k))
+        try:
+            self._ck(self._l.ojas_b200_repack(self._ctx, ggml_type, C.c_void_p(tmp.ptr), n, k, C.c_void_p(out.ptr)))
+            self.sync()
+        finally:
+            self.free(tmp)
+        return Lin(out, ggml_type, n, k)
+
+    # ------------------------------------------------------------------ typed entry points
+    def quant_q8k(self, x: Buf, m: int, k: int, q: Buf, scales: Buf, bsums: Buf) -> None:
+        self._ck(self._l.ojas_b200_quant_q8k(self._ctx, C.c_void_p(x.ptr), m, k, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr)))
+
+    def gemv(self, w: Lin, x: Buf, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
+        self._ck(self._l.ojas_b200_gemv(self._ctx, w.ggml_type, form, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
+                                        C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
+
+    def gemv_q8k(self, w: Lin, q: Buf, scales: Buf, bsums: Buf, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
+        self._ck(self._l.ojas_b200_gemv_q8k(self._ctx, w.ggml_type, form, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr),
+                                            C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
+
+    def gemv_idots(self, w: Lin, x: Buf, idots: Buf) -> None:
+        self._ck(self._l.ojas_b200_gemv_idots(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(idots.ptr), w.k, w.n))
+
+    # ------------------------------------------------------------------ KernelRuntime
+    def has_kernel(self, name: str) -> bool:
+        return bool(self._l.ojas_b200_has_kernel(name.encode()))
+
+    def kernel_names(self) -> list[str]:
+        return [self._l.ojas_b200_kernel_name(i).decode() for i in range(self._l.ojas_b200_kernel_count())]
+
+    def begin(self) -> Enc:
+        return Enc()
+
+    def dispatch(self, enc: Enc, name: str, bufs, consts, grid=(1, 1, 1), block=(1, 1, 1)) -> None:
+        """``KernelRuntime::dispatch``: ``bufs`` = [(Buf, byte_offset), ...] positional, then u32 ``consts``."""
+        n = len(bufs)
+        ptrs = (C.c_void_p * max(n, 1))(*[C.c_void_p(b.ptr) for b, _ in bufs])
+        offs = (C.c_uint64 * max(n, 1))(*[int(o) for _, o in bufs])
+        cs = (C.c_uint32 * max(len(consts), 1))(*[int(c) for c in consts])
+        g = (C.c_uint32 * 3)(*grid)
+        bl = (C.c_uint32 * 3)(*block)
+        self._ck(self._l.ojas_b200_dispatch(self._ctx, name.encode(), ptrs, offs, n, cs, len(consts), g, bl))
+        enc.dispatches += 1
+
+    def submit(self, enc: Enc) -> None:
+        """``KernelRuntime::submit``: wait for the chain; device errors surface here."""
+        self.sync()
+
+    # ------------------------------------------------------------------ the matmul operator
+    def mm(self, x: Buf, w: Lin, y: Buf, m: int, accum: bool = False) -> None:
+        """``CudaSsm::mm(st, x, w, y, m, accum)`` (crates/ojas-cuda/src/qwen35.rs:644-702): picks the
+        kernel from the weight representation and the row count."""
+        form = ACCUM if accum else PLAIN
+        if m <= GEMV_MAX_M:
+            self.gemv(w, x, y, m, form)
+            return
+        if hasattr(self, "gemm"):
+            self.gemm(w, x, y, m, accum)  # tensor-core prefill path
+            return
+        for m0 in range(0, m, GEMV_MAX_M):
+            mb = min(GEMV_MAX_M, m - m0)
+            self.gemv(w, Buf(x.ptr + m0 * w.k * 4, mb * w.k * 4), Buf(y.ptr + m0 * w.n * 4, mb * w.n * 4), mb, form)
+
+    # ------------------------------------------------------------------ timing / graphs
+    def event(self) -> int:
+        p = C.c_void_p()
+        self._ck(self._l.ojas_b200_event_create(self._ctx, C.byref(p)))
+        return int(p.value)
+
+    def record(self, ev: int) -> None:
+        self._ck(self._l.ojas_b200_event_record(self._ctx, C.c_void_p(ev)))
+
+    def elapsed_ms(self, start: int, stop: int) -> float:
+        ms = C.c_float()
+        self._ck(self._l.ojas_b200_event_elapsed_ms(self._ctx, C.c_void_p(start), C.c_void_p(stop), C.byref(ms)))
+        return float(ms.value)
+
+    def graph_begin(self) -> None:
+        self._ck(self._l.ojas_b200_graph_begin(self._ctx))
+
+    def graph_end(self) -> int:
+        p = C.c_void_p()
+        self._ck(self._l.ojas_b200_graph_end(self._ctx, C.byref(p)))
+        return int(p.value)
+
+    def graph_launch(self, g: int) -> None:
+        self._ck(self._l.ojas_b200_graph_launch(self._ctx, C.c_void_p(g)))
+
+    def graph_destroy(self, g: int) -> None:
+        self._ck(self._l.ojas_b200_graph_destroy(self._ctx, C.c_void_p(g)))
+
+    def host_alloc(self, nbytes: int, dtype=np.uint8) -> np.ndarray:
+        """Pinned host array (kept alive by the returned array's base object)."""
+        p = C.c_void_p()
+        self._ck(self._l.ojas_b200_host_alloc(self._ctx, nbytes, C.byref(p)))
+        raw = (C.c_uint8 * nbytes).from_address(p.value)
+        arr = np.frombuffer(raw, dtype=np.uint8).view(dtype)
+        return arr
+
+
+# ---------------------------------------------------------------------- host utilities (no GPU)
+def raw_bytes(ggml_type: int, n: int, k: int) -> int:
+    return int(_lib.load().ojas_b200_raw_bytes(ggml_type, n, k))
+
+
+def repacked_bytes(ggml_type: int, n: int, k: int) -> int:
+    return int(_lib.load().ojas_b200_repacked_bytes(ggml_type, n, k))
+
+
+def encode(ggml_type: int, w: np.ndarray) -> np.ndarray:
+    """f32 [n, k] -> GGUF blocks with this library's simple test-input encoder."""
+    w = np.ascontiguousarray(w, np.float32)
+    n, k = w.shape
+    out = np.empty(raw_bytes(ggml_type, n, k), np.uint8)
+    rc = _lib.load().ojas_b200_encode_host(ggml_type, w.ctypes.data_as(C.c_void_p), n, k, out.ctypes.data_as(C.c_void_p))
+    if rc != 0:
+        raise OjasB200Error(rc, f"encode: type {ggml_type} [{n},{k}]")
+    return out
+
+
+def repack_host(ggml_type: int, raw: np.ndarray, n: int, k: int) -> np.ndarray:
+    raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+    out = np.empty(repacked_bytes(ggml_type, n, k), np.uint8)
+    rc = _lib.load().ojas_b200_repack_host(ggml_type, raw.ctypes.data_as(C.c_void_p), n, k, out.ctypes.data_as(C.c_void_p))
+    if rc != 0:
+        raise OjasB200Error(rc, f"repack_host: type {ggml_type} [{n},{k}]")
+    return out

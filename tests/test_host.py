@@ -1,0 +1,85 @@
+"""Host-side logic of the product library: exports, layouts, encoders (no GPU, no compute calls)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle
+import ojas_engine_b200 as ob
+from ojas_engine_b200 import lib as oblib
+
+from helpers import TYPES, gauss_weights, model_dequant, synth_weights
+
+
+def test_library_exports_every_declared_symbol():
+    l = oblib.load()
+    declared = oblib.header_symbols()
+    assert len(declared) >= 30
+    assert set(declared) == set(oblib.SIGNATURES)
+    for name in declared:
+        assert hasattr(l, name), name
+    assert b"sm_100a" in l.ojas_b200_version()
+
+
+def test_kernel_name_table():
+    l = oblib.load()
+    names = [l.ojas_b200_kernel_name(i).decode() for i in range(l.ojas_b200_kernel_count())]
+    assert len(names) == len(set(names))
+    # every native GEMV format carries its four forms (crates/ojas-cuda/tests/conformance.rs:85-202)
+    for tag in ("q4k", "q6k", "q80"):
+        for suffix in ("", "_accum", "_bias", "_m"):
+            assert f"gemv_nat_{tag}{suffix}" in names
+            assert l.ojas_b200_has_kernel(f"gemv_nat_{tag}{suffix}".encode())
+    assert not l.ojas_b200_has_kernel(b"gemv_nat_q2k")
+
+
+@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
+def test_sizes(tag):
+    t = TYPES[tag]
+    per256 = {"q4k": 144, "q6k": 210, "q80": 272}[tag]
+    assert ob.raw_bytes(t, 4096, 4096) == 4096 * 16 * per256
+    assert ob.raw_bytes(t, 3, 256) == oracle.row_bytes(t, 256) * 3
+    rp = ob.repacked_bytes(t, 4096, 4096)
+    assert ob.raw_bytes(t, 4096, 4096) <= rp <= ob.raw_bytes(t, 4096, 4096) + 4 * 256  # lossless, padding only
+    assert ob.repacked_bytes(t, 8, 100) == 0  # K must be a multiple of 256
+    assert ob.repacked_bytes(5, 8, 256) == 0  # unsupported type
+
+
+@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
+@pytest.mark.parametrize("source", ["synth", "gauss"])
+def test_repack_is_lossless(tag, source):
+    """Decoding the repacked planes the way the kernels' lanes do gives exactly the values the
+    reference decoder gives for the GGUF blocks."""
+    t = TYPES[tag]
+    n, k = 5, 768
+    raw = synth_weights(t, n, k) if source == "synth" else gauss_weights(t, n, k, seed=4)
+    packed = ob.repack_host(t, raw, n, k)
+    got = model_dequant(t, packed, n, k)
+    want = oracle.dequant_f32(raw, t, n * k).reshape(n, k)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("tag,tol", [("q4k", 0.12), ("q6k", 0.03), ("q80", 0.01)])
+def test_encoders_round_trip(tag, tol):
+    t = TYPES[tag]
+    n, k = 16, 1024
+    w = (np.random.default_rng(0).standard_normal((n, k)) * 0.02).astype(np.float32)
+    raw = ob.encode(t, w)
+    assert raw.size == ob.raw_bytes(t, n, k)
+    back = oracle.dequant_f32(raw, t, n * k).reshape(n, k)
+    err = np.linalg.norm(back - w) / np.linalg.norm(w)
+    assert err < tol, err
+    assert np.isfinite(back).all()
+
+
+def test_encoder_handles_zeros():
+    for t in TYPES.values():
+        raw = ob.encode(t, np.zeros((2, 256), np.float32))
+        assert not oracle.dequant_f32(raw, t, 512).any()
+
+
+def test_no_gpu_fails_loudly():
+    l = oblib.load()
+    ctx = C.c_void_p()
+    rc = l.ojas_b200_create(9999, None, C.byref(ctx))
+    assert rc != 0 and not ctx.value

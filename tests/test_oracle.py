@@ -1,0 +1,134 @@
+"""The CPU oracle against the reference's own golden values (no GPU)."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import Q4_K, Q6_K, Q8_0
+
+from conftest import rel_l2
+
+
+# crates/ojas-formats/tests/quant_formats.rs:33-50: (type, value count, FNV-1a digest)
+@pytest.mark.parametrize("t,n,want", [(Q4_K, 10240, 0x6536b83e8b2292b4), (Q6_K, 10240, 0x38ecabe858257db6)])
+def test_synth_block_digests(t, n, want):
+    raw = oracle.synth_blocks(t, 40)
+    vals = oracle.dequant_f16(raw, t, n)
+    assert vals.size == n
+    assert oracle.digest_f16(vals) == want
+
+
+def test_q80_rows_fixture():
+    # crates/ojas-formats/tests/rows.rs:13-17,57-66: block r has d = 0.25*(r+1), q[j] = j-16+r
+    raw = bytearray()
+    for r in range(3):
+        raw += np.float16(0.25 * (r + 1)).tobytes()
+        raw += bytes(((j - 16 + r) & 0xFF) for j in range(32))
+    raw = np.frombuffer(bytes(raw), np.uint8)
+    got = oracle.dequant_f32(raw, Q8_0, 96).reshape(3, 32)
+    for r in range(3):
+        want = 0.25 * (r + 1) * (np.arange(32) - 16 + r)
+        assert np.array_equal(got[r], want.astype(np.float32))
+
+
+def test_f16_conversion_matches_numpy():
+    bits = np.arange(0, 65536, dtype=np.uint16)
+    ours = np.array([oracle.lib().orc_f16_to_f32(int(b)) for b in bits[::7]], np.float32)
+    ref = bits[::7].view(np.float16).astype(np.float32)
+    ok = (ours == ref) | (np.isnan(ours) & np.isnan(ref))
+    assert ok.all()
+    rng = np.random.default_rng(3)
+    xs = np.concatenate([rng.standard_normal(4000).astype(np.float32) * s for s in (1e-8, 1e-5, 1e-3, 1.0, 300.0, 7e4)])
+    xs = np.concatenate([xs, np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 2.0 ** -24, 2.0 ** -25, 3 * 2.0 ** -26], np.float32)])
+    ours = np.array([oracle.lib().orc_f32_to_f16(float(v)) for v in xs], np.uint16)
+    with np.errstate(over="ignore"):
+        ref = xs.astype(np.float16).view(np.uint16)
+    assert np.array_equal(ours, ref)
+
+
+def test_quant_q8k_rules():
+    # crates/ojas-cpu/src/cpu_math.rs:545-563: scale = amax/127 (1 when all zero), half away from zero
+    x = np.zeros(512, np.float32)
+    x[:256] = np.linspace(-3, 3, 256, dtype=np.float32)
+    scales, q, bsums = oracle.quant_q8k(x)
+    assert scales[1] == 1.0 and not q[256:].any() and not bsums[8:].any()
+    assert scales[0] == np.float32(3.0) / np.float32(127.0)
+    assert q[0] == -127 and q[255] == 127
+    assert np.array_equal(bsums[:8], q[:256].astype(np.int32).reshape(8, 32).sum(1))
+    # ties: amax = 127 -> scale 1, inv 1: 0.5 -> 1, -0.5 -> -1, 2.5 -> 3 (half away, not half even)
+    y = np.zeros(256, np.float32)
+    y[0], y[1], y[2], y[3], y[4] = 127.0, 0.5, -0.5, 2.5, -2.5
+    _, q2, _ = oracle.quant_q8k(y)
+    assert list(q2[:5]) == [127, 1, -1, 3, -3]
+
+
+@pytest.mark.parametrize("t", [Q4_K, Q6_K])
+def test_kquant_dot_identity(t):
+    """dot(row, q8k(x)) equals sum dequant(row)[i] * (sx*q[i]) up to f32 rounding, and the dumped
+    integer sub-block dots equal a direct integer recomputation."""
+    k, n = 1024, 6
+    bb, bw = oracle.block_shape(t)
+    raw = oracle.synth_blocks(t, n * k // bw).reshape(n, -1)
+    x = np.random.default_rng(5).standard_normal(k).astype(np.float32)
+    act = oracle.quant_q8k(x)
+    scales, q, _ = act
+    xhat = (np.repeat(scales, 256) * q.astype(np.float32)).astype(np.float64)
+    for r in range(n):
+        w = oracle.dequant_f32(raw[r], t, k).astype(np.float64)
+        want = float(w @ xhat)
+        if t == Q4_K:
+            got, idots = oracle.dot_q4k(raw[r], act, want_idots=True)
+            blk = raw[r].reshape(-1, 144)[:, 16:].reshape(-1, 4, 32)
+            wq = np.stack([blk & 0xF, blk >> 4], axis=2).reshape(-1, 8, 32).astype(np.int64)
+            direct = (wq * q.reshape(-1, 8, 32).astype(np.int64)).sum(-1).reshape(-1)
+            assert np.array_equal(idots, direct.astype(np.int32))
+        else:
+            got, idots = oracle.dot_q6k(raw[r], act, want_idots=True)
+            assert idots.size == k // 16
+        assert abs(got - want) <= 2e-5 * max(1.0, np.abs(w).dot(np.abs(xhat)))
+
+
+def test_q80_dot_and_matvec():
+    k, n = 512, 40
+    raw = oracle.synth_blocks(Q8_0, n * k // 32).reshape(n, -1)
+    x = oracle.tvec(k, 9)
+    w = oracle.dequant_f32(raw.reshape(-1), Q8_0, n * k).reshape(n, k).astype(np.float64)
+    y1 = oracle.matvec_kq(raw, Q8_0, n, k, x, threads=1)
+    y8 = oracle.matvec_kq(raw, Q8_0, n, k, x, threads=8)
+    assert np.array_equal(y1, y8)  # row results do not depend on the thread count
+    assert rel_l2(y1, w @ x.astype(np.float64)) < 1e-6
+    assert y1[3] == np.float32(oracle.dot_q80(raw[3], x))
+
+
+def test_matvec_threads_and_batch():
+    k, n, m = 768, 37, 3
+    raw = oracle.synth_blocks(Q4_K, n * k // 256)
+    x = np.random.default_rng(1).standard_normal((m, k)).astype(np.float32)
+    ys = oracle.matmul_kq(raw, Q4_K, n, k, x, threads=5)
+    for t in range(m):
+        assert np.array_equal(ys[t], oracle.matvec_kq(raw, Q4_K, n, k, x[t], threads=1))
+
+
+def test_moe_topk_semantics():
+    # crates/ojas-cuda/src/kernels/moe.rs:45-70: ties go to the lowest index; weights renormalised
+    lg = np.array([[0.5, 2.0, 2.0, -1.0]], np.float32)
+    idx, wgt = oracle.moe_topk(lg, 2)
+    assert list(idx[0]) == [1, 2]
+    assert np.allclose(wgt[0], [0.5, 0.5])
+    lg = np.random.default_rng(2).standard_normal((16, 8)).astype(np.float32)
+    idx, wgt = oracle.moe_topk(lg, 2)
+    order = np.argsort(-lg, axis=1, kind="stable")[:, :2]
+    assert np.array_equal(idx, order.astype(np.uint32))
+    e = np.exp(np.take_along_axis(lg, order, 1).astype(np.float64))
+    assert np.allclose(wgt, e / e.sum(1, keepdims=True), atol=1e-6)
+    assert np.allclose(wgt.sum(1), 1.0, atol=1e-6)
+
+
+def test_tvec_generator():
+    # crates/ojas-cuda/tests/conformance.rs:223-231
+    v = oracle.tvec(4, 7)
+    s = (7 * 2654435761 + 1) & 0xFFFFFFFF
+    want = []
+    for _ in range(4):
+        s = (s * 1664525 + 1013904223) & 0xFFFFFFFF
+        want.append(np.float32(s >> 9) / np.float32(1 << 23) - np.float32(1.0))
+    assert np.array_equal(v, np.array(want, np.float32))
