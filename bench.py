@@ -231,6 +231,8 @@ def run_ours(args) -> None:
 
     hbm_peak, _, peak_kind = measured_peaks()
     gpu = ob.B200Gpu(local)
+    if args.pdl:
+        gpu.set_option("pdl", 1)
     raws = ring_weights(RING, seed=rank * 1000)
     weights = [gpu.load_weight(r, ob.Q4_K, N_ROWS, K_COLS) for r in raws]
     rng = np.random.default_rng(1 + rank)
@@ -376,6 +378,56 @@ def run_ours(args) -> None:
     gpu.close()
 
 
+def run_case(args) -> None:
+    """One GEMV shape on one GPU: `--case q4k:4096:4096:1 [--ring R] [--no-graph]`.  The mode the
+    ncu captures and the shape sweeps use; prints one JSON line."""
+    import ojas_engine_b200 as ob
+    import oracle
+    tag, n, k, m = args.case.split(":")
+    n, k, m = int(n), int(k), int(m)
+    t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
+    hbm_peak, _, peak_kind = measured_peaks()
+    gpu = ob.B200Gpu(0)
+    if args.pdl:
+        gpu.set_option("pdl", 1)
+    if args.depth:
+        gpu.set_option("gemv_depth", args.depth)
+    gguf = ob.raw_bytes(t, n, k)
+    ring = args.ring or max(2, int(300e6 // gguf) + 1)
+    base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
+    ws = [gpu.load_weight(np.ascontiguousarray(np.roll(base, 13 * i, axis=0)), t, n, k) for i in range(ring)]
+    x = gpu.upload(np.random.default_rng(7).standard_normal((m, k), dtype=np.float32))
+    y = gpu.alloc(m * n)
+
+    def one_pass():
+        for w in ws:
+            gpu.gemv(w, x, y, m)
+
+    one_pass()
+    gpu.sync()
+    graph = None
+    if not args.no_graph:
+        gpu.graph_begin()
+        one_pass()
+        graph = gpu.graph_end()
+    run = (lambda: gpu.graph_launch(graph)) if graph else one_pass
+    for _ in range(args.warmup):
+        run()
+    gpu.sync()
+    e0, e1 = gpu.event(), gpu.event()
+    gpu.record(e0)
+    for _ in range(args.steps):
+        run()
+    gpu.record(e1)
+    gpu.sync()
+    us = gpu.elapsed_ms(e0, e1) * 1e3 / (args.steps * ring)
+    algo = gguf + 4 * m * (k + n)
+    gbs = algo / (us * 1e-6) / 1e9
+    print(json.dumps({"case": args.case, "ring": ring, "graph": graph is not None, "pdl": bool(args.pdl), "depth": args.depth or 4, "us_per_launch": us, "GB/s": gbs,
+                      "frac": gbs / hbm_peak, "peak_kind": peak_kind, "algorithmic_bytes": algo}))
+    gpu.close()
+
+
 def _wrap_device_f32(ptr: int, count: int, device: int):
     """A torch view of a device buffer owned by the library (for the NCCL collective)."""
     import torch
@@ -405,9 +457,16 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the additional GEMV shapes")
+    ap.add_argument("--case", default=None, help="time one GEMV shape instead: tag:N:K:M, e.g. q4k:4096:4096:1")
+    ap.add_argument("--ring", type=int, default=0, help="--case: number of distinct weights (default: enough to pass L2)")
+    ap.add_argument("--no-graph", action="store_true", help="--case: plain launches instead of a CUDA graph")
+    ap.add_argument("--depth", type=int, default=0, help="--case: stages of the GEMV cp.async ring (2..4)")
+    ap.add_argument("--pdl", action="store_true", help="launch GEMVs with programmatic dependent launch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

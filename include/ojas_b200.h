@@ -56,6 +56,11 @@ OJAS_B200_API int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out
 OJAS_B200_API void ojas_b200_destroy(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream);
 OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
+/* Options, also read once from the environment at creation the way the engine reads its OJAS_*
+ * switches (crates/ojas-core/src/config.rs:1-22): "pdl" (OJAS_B200_PDL=1) launches the GEMVs with
+ * programmatic dependent launch so that a kernel's weight prefetch overlaps the tail of the
+ * kernel before it in the stream. */
+OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
 /* Launches issued by this context since creation (the benchmark's launch counter). */

@@ -27,8 +27,9 @@ __device__ __forceinline__ Q8kLane quant_q8k_warp(const float *seg /* 256 floats
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         float r = round_half_away(__fmul_rn(v[i], inv));
+        const bool nan = r != r;   // a NaN quotient quantizes to 0 (Rust's `as i8`)
         r = fminf(fmaxf(r, -127.0f), 127.0f);
-        qi[i] = (r != r) ? 0 : (int)r;
+        qi[i] = nan ? 0 : (int)r;
         s += qi[i];
     }
     Q8kLane out;
@@ -37,6 +38,54 @@ __device__ __forceinline__ Q8kLane quant_q8k_warp(const float *seg /* 256 floats
     out.packed.y = (uint32_t)(qi[4] & 0xff) | ((uint32_t)(qi[5] & 0xff) << 8) | ((uint32_t)(qi[6] & 0xff) << 16) |
                    ((uint32_t)(qi[7] & 0xff) << 24);
     out.sum8 = s;
+    out.scale = scale;
+    return out;
+}
+
+// Half-warp form: lanes 0-15 quantize one super-block, lanes 16-31 another; lane l owns values
+// 16*(l & 15) .. +15 of its super-block.  Fewer, fuller instructions per super-block than the
+// one-warp form; same results bit for bit.
+struct Q8kHalfLane {
+    uint4 packed;   // the lane's sixteen int8 values in value order (one 16-byte unit)
+    int sum16;      // their sum
+    float scale;
+};
+
+__device__ __forceinline__ Q8kHalfLane quant_q8k_halfwarp(const float *seg /* 256 floats of this half-warp's block */, int lane) {
+    const int hl = lane & 15;
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(seg) + hl * 4 + j);
+        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+    }
+    float m = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) m = fmaxf(m, fabsf(v[i]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float scale = (m > 0.0f) ? __fdiv_rn(m, 127.0f) : 1.0f;
+    const float inv = __fdiv_rn(1.0f, scale);
+    uint32_t w[4];
+    int s = 0;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float t = __fmul_rn(v[4 * j + i], inv);
+            float r = round_half_away(t);
+            const bool nan = r != r;
+            r = fminf(fmaxf(r, -127.0f), 127.0f);
+            const int qi = nan ? 0 : (int)r;
+            s += qi;
+            word |= (uint32_t)(qi & 0xff) << (8 * i);
+        }
+        w[j] = word;
+    }
+    Q8kHalfLane out;
+    out.packed = make_uint4(w[0], w[1], w[2], w[3]);
+    out.sum16 = s;
     out.scale = scale;
     return out;
 }

@@ -53,6 +53,8 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
         return OJAS_B200_E_CUDA;
     }
     memset(ctx->host_status, 0, 64);
+    const char *pdl = getenv("OJAS_B200_PDL");   // read once at context creation, like the engine's OJAS_* switches
+    ctx->pdl = pdl && pdl[0] == '1';
     *out = ctx;
     return 0;
 }
@@ -73,6 +75,17 @@ extern "C" int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream) {
     }
     ctx->stream = (cudaStream_t)stream;
     return 0;
+}
+
+extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value) {
+    if (!ctx || !key) return OJAS_B200_E_ARG;
+    if (!strcmp(key, "pdl")) { ctx->pdl = value != 0; return 0; }
+    if (!strcmp(key, "gemv_depth")) {
+        if (value < 2 || value > 4) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_depth must be 2..4");
+        ctx->gemv_depth = value;
+        return 0;
+    }
+    return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: unknown key '%s'", key);
 }
 
 extern "C" void *ojas_b200_stream(ojas_b200_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }

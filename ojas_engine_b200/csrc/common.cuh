@@ -18,6 +18,8 @@ struct ojas_b200_ctx {
     int sm_count = 0;
     int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
     uint64_t launches = 0;
+    int gemv_depth = 4;          // stages in each warp's cp.async ring (2..4)
+    int pdl = 0;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
     unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
     unsigned int *dev_status = nullptr;  // the same word as the device sees it
     char err[512] = {0};
@@ -48,7 +50,9 @@ int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
 //   plane qs : [N][K/256][128]  nibbles; within a super-block byte h*64 + c*16 + i holds
 //              GGUF qs[c*32 + h*16 + i] (c = 64-weight chunk 0..3, h = 16-byte half), so the
 //              four lanes that share a super-block read 64 contiguous bytes per load.
-//   plane hdr: [N][K/256][16]   the GGUF header bytes 0..15 unchanged (d, dmin, sc[12]).
+//   plane hdr: [N][K/256][16]   f16 d, f16 dmin, then the sixteen 6-bit scales / mins regrouped
+//              per chunk: bytes 4 + 3c .. 6 + 3c hold the little-endian 24-bit group
+//              s(2c) | s(2c+1) << 6 | m(2c) << 12 | m(2c+1) << 18  (same 96 bits as GGUF's sc[12]).
 // Q6_K  (GGUF: 210 B per 256: u8 ql[128], u8 qh[64], i8 sc[16], f16 d)
 //   plane lo : [N][K/256][128]  low nibbles; byte h*64 + c*16 + i: low nibble = weight
 //              64c + 16h + i, high nibble = weight 64c + 32 + 16h + i.
@@ -104,6 +108,11 @@ __device__ __forceinline__ uint4 ldg_stream_u4(const void *p) {
                  : "l"(p));
     return v;
 }
+
+// Programmatic dependent launch: wait for the kernel before this one in the stream (a no-op
+// when the launch did not ask for overlap), and let the kernel after this one start early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

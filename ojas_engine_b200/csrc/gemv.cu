@@ -29,7 +29,21 @@ struct GemvArgs {
     const float *bias;       // [N] or null
     int32_t *idots;          // dump of the integer sub-block dots (DUMP kernels)
     int K, N, M, form;
+    int S;                   // segments per row (work split); chosen by the host
+    int depth;               // stages in each warp's cp.async ring (2..4); chosen by the host
+    int rows_base, rows_rem; // CTA b owns rows_base (+1 if b < rows_rem) rows: N = grid*rows_base + rows_rem
 };
+
+// First row and row count of this CTA (no 64-bit division on the device).
+__device__ __forceinline__ void cta_rows(const GemvArgs &a, int &r_begin, int &R) {
+    const int b = (int)blockIdx.x;
+    r_begin = b * a.rows_base + (b < a.rows_rem ? b : a.rows_rem);
+    R = a.rows_base + (b < a.rows_rem ? 1 : 0);
+}
+
+// Floats reserved for the per-super-block activation scales: a multiple of four, so the block
+// sums that follow stay 16-byte aligned for any super-block count.
+__host__ __device__ __forceinline__ int sx_floats(int mt, int nsb) { return (mt * nsb + 3) & ~3; }
 
 __device__ __forceinline__ void store_form(float *yp, float v, int form, const float *bias, int n) {
     if (form == OJAS_B200_ACCUM) v += *yp;
@@ -37,14 +51,66 @@ __device__ __forceinline__ void store_form(float *yp, float v, int form, const f
     *yp = v;
 }
 
-// Fixed-order sum of the item partials of every row of this CTA, then the store.
+// ---------------------------------------------------------------------------- work split
+// CTA b owns rows [N*b/G, N*(b+1)/G).  A row is cut into S segments of whole groups (a group
+// = eight super-blocks = 2048 weights; S = 1 unless the CTA has fewer rows than warps);
+// (row, segment) units go round-robin to the warps.  A warp walks the groups of its unit with
+// the next group's loads already in flight, reduces once per unit, and the S partial sums of
+// a row are added in a fixed order, so results do not depend on timing.
+struct WarpCursor {
+    int u;          // unit index inside the CTA
+    int row;        // global weight row
+    int g, g_end;   // current group and end of the unit's group range
+};
+
+__device__ __forceinline__ void cursor_set(WarpCursor &cu, int u, int n_units, int S, int G8, int r_begin) {
+    cu.u = u;
+    cu.row = 0; cu.g = 0; cu.g_end = 0;
+    if (u < n_units) {
+        const int rr = u / S, seg = u - rr * S;
+        cu.row = r_begin + rr;
+        cu.g = seg * G8 / S;
+        cu.g_end = (seg + 1) * G8 / S;
+    }
+}
+
+__device__ __forceinline__ void cursor_advance(WarpCursor &cu, int n_units, int S, int G8, int r_begin) {
+    if (++cu.g >= cu.g_end) cursor_set(cu, cu.u + GEMV_WARPS, n_units, S, G8, r_begin);
+}
+
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, uint32_t b, int c) {   // unsigned bytes x signed bytes
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// End of a unit: warp-reduce the accumulators; S == 1 stores y directly, otherwise the partial
+// goes to shared memory for finish_rows.
 template <int MT>
-__device__ __forceinline__ void finish_rows(const float *part, int R, int G8, int r_begin, const GemvArgs &a) {
+__device__ __forceinline__ void unit_done(float (&acc)[MT], const WarpCursor &cu, int S, float *part, const GemvArgs &a, int lane) {
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        const float s = warp_sum(acc[m]);
+        acc[m] = 0.0f;
+        if (lane == 0) {
+            if (S == 1) {
+                if (m < a.M) store_form(a.y + (size_t)m * a.N + cu.row, s, a.form, a.bias, cu.row);
+            } else {
+                part[cu.u * MT + m] = s;
+            }
+        }
+    }
+}
+
+template <int MT>
+__device__ __forceinline__ void finish_rows(const float *part, int R, int S, int r_begin, const GemvArgs &a) {
+    if (S == 1) return;
+    __syncthreads();
     for (int idx = threadIdx.x; idx < R * MT; idx += blockDim.x) {
         const int r = idx / MT, m = idx - r * MT;
         if (m >= a.M) continue;
         float s = 0.0f;
-        for (int g = 0; g < G8; g++) s += part[(r * G8 + g) * MT + m];
+        for (int g = 0; g < S; g++) s += part[(r * S + g) * MT + m];
         const int n = r_begin + r;
         store_form(a.y + (size_t)m * a.N + n, s, a.form, a.bias, n);
     }
@@ -57,25 +123,28 @@ __device__ __forceinline__ void stage_q8k(const GemvArgs &a, unsigned char *xq, 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int NB = BS16 ? 16 : 8;
     if (!PREQ) {
-        for (int u = warp; u < MT * nsb; u += GEMV_WARPS) {
-            const int m = u / nsb, sb = u - m * nsb;
-            uint2 packed = make_uint2(0u, 0u);
-            int s = 0;
-            float scale = 0.0f;
-            if (m < a.M) {
-                Q8kLane ql = quant_q8k_warp(a.x + (size_t)m * a.K + (size_t)sb * 256, lane);
-                packed = ql.packed; s = ql.sum8; scale = ql.scale;
+        // half-warps: task t = (row m, super-block sb); lane l owns the 16-byte unit (l & 15)
+        const int half = lane >> 4, un = lane & 15;
+        for (int t0 = warp * 2; t0 < MT * nsb; t0 += GEMV_WARPS * 2) {
+            const int t = t0 + half;
+            const bool live = t < MT * nsb;
+            const int tt = live ? t : t0;                 // idle half-warps shadow a live task and store nothing
+            const int m = tt / nsb, sb = tt - m * nsb;
+            // Both half-warps always run the quantizer (it shuffles with a full mask, so no lane may
+            // skip it); a padding row m >= M reads row M-1 and its result is replaced by zeros.
+            const int ml = m < a.M ? m : a.M - 1;
+            Q8kHalfLane ql = quant_q8k_halfwarp(a.x + (size_t)ml * a.K + (size_t)sb * 256, lane);
+            const bool pad = m >= a.M;
+            const uint4 packed = pad ? make_uint4(0u, 0u, 0u, 0u) : ql.packed;
+            const int s = pad ? 0 : ql.sum16;
+            const float scale = pad ? 0.0f : ql.scale;
+            const int s32 = s + __shfl_xor_sync(0xffffffffu, s, 1);
+            if (live) {
+                reinterpret_cast<uint4 *>(xq + (size_t)m * Kpad)[xq_unit(sb, un >> 2, un & 3)] = packed;
+                if (BS16) bs[(m * nsb + sb) * 16 + un] = s;
+                else if ((un & 1) == 0) bs[(m * nsb + sb) * 8 + (un >> 1)] = s32;
+                if (un == 0) sx[m * nsb + sb] = scale;
             }
-            const int un = lane >> 1;
-            *reinterpret_cast<uint2 *>(xq + (size_t)m * Kpad + xq_unit(sb, un >> 2, un & 3) * 16 + (lane & 1) * 8) = packed;
-            s += __shfl_xor_sync(0xffffffffu, s, 1);
-            if (BS16) {
-                if ((lane & 1) == 0) bs[(m * nsb + sb) * 16 + (lane >> 1)] = s;
-            } else {
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                if ((lane & 3) == 0) bs[(m * nsb + sb) * 8 + (lane >> 2)] = s;
-            }
-            if (lane == 0) sx[m * nsb + sb] = scale;
         }
     } else {
         const int units = nsb * 16;
@@ -106,104 +175,188 @@ __device__ __forceinline__ void stage_q8k(const GemvArgs &a, unsigned char *xq, 
     }
 }
 
-// ---------------------------------------------------------------------------- Q4_K
-struct Q4kRegs { uint4 A, B, H; };
-
-// The two 6-bit sub-block scales and mins of chunk c, packed as bytes (lo = sub-block 2c,
-// hi = 2c + 1).  Same bit rules as scale_min_k4 (crates/ojas-cpu/src/cpu_math.rs:566-574).
-__device__ __forceinline__ void q4k_scales(const uint4 &H, int c, int &s1, int &s2, int &m1, int &m2) {
-    const int sh = (c & 1) * 16;
-    const uint32_t a = (H.y >> sh) & 0xffffu, b = (H.z >> sh) & 0xffffu, e = (H.w >> sh) & 0xffffu;
-    const uint32_t S_lo = a & 0x3f3fu, M_lo = b & 0x3f3fu;
-    const uint32_t S_hi = (e & 0x0f0fu) | ((a >> 2) & 0x3030u);
-    const uint32_t M_hi = ((e >> 4) & 0x0f0fu) | ((b >> 2) & 0x3030u);
-    const uint32_t S = (c < 2) ? S_lo : S_hi, Mn = (c < 2) ? M_lo : M_hi;
-    s1 = (int)(S & 0xffu); s2 = (int)(S >> 8);
-    m1 = (int)(Mn & 0xffu); m2 = (int)(Mn >> 8);
+// ---------------------------------------------------------------------------- async staging
+// Weights travel global -> shared memory with cp.async (16 bytes per lane, no registers held
+// while in flight).  Each warp owns a ring of `depth` stages; a stage holds one step of the
+// warp (one row x eight super-blocks).  depth - 1 steps are always in flight, which is what
+// keeps enough bytes outstanding per SM to cover HBM latency.
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
+// Same, executed only when `pred` is non-zero (a predicated instruction, not a branch).
+__device__ __forceinline__ void cp_async16_if(void *smem_dst, const void *gmem_src, int pred) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}"
+                 ::"r"(d), "l"(gmem_src), "r"(pred) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// wait until at most `pending` of this thread's groups are outstanding (pending = depth - 1, 1..3)
+__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
+    if (pending >= 3) cp_async_wait<3>();
+    else if (pending == 2) cp_async_wait<2>();
+    else cp_async_wait<1>();
+}
+
+// ---------------------------------------------------------------------------- Q4_K
+// A Q4_K step is one row x sixteen super-blocks (4096 weights, 2304 bytes): every lane owns
+// chunk c of super-blocks sbi and sbi + 8.  Each warp has two stages in shared memory: the
+// copies of step t + 1 are in flight while step t is computed.
+constexpr int Q4K_STAGE_BYTES = 2304;   // A0 512, B0 512, A1 512, B1 512, sixteen headers 256
+
+// Walks the (row, segment) units of one warp, step by step, without divisions.
+struct StepIter {
+    int row, seg, gi;      // current unit's row and segment, step inside the unit
+    int left;              // steps left for this warp (0 = done)
+};
 
 template <int MT, bool PREQ, bool DUMP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int nsb = a.K >> 8, G8 = (nsb + 7) >> 3;
+    const int nsb = a.K >> 8, S = a.S;
+    const int G = (nsb + 15) >> 4, GP = G / S;                // steps per row, per unit (host makes S divide G)
     const int Kpad = ((nsb + 1) >> 1) * 512;
-    unsigned char *xq = smem;
-    float *sx = reinterpret_cast<float *>(smem + (size_t)MT * Kpad);
-    int *bs = reinterpret_cast<int *>(sx + MT * nsb);
-    float *part = reinterpret_cast<float *>(bs + MT * nsb * 8);
-
-    const int r_begin = (int)((long long)a.N * blockIdx.x / gridDim.x);
-    const int r_end = (int)((long long)a.N * (blockIdx.x + 1) / gridDim.x);
-    const int R = r_end - r_begin, n_items = R * G8;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sbi = lane >> 2, c = lane & 3;
-    const uint4 *qs = reinterpret_cast<const uint4 *>(a.w.p0);
-    const uint4 *hdr = reinterpret_cast<const uint4 *>(a.w.p1);
+    unsigned char *ring = smem + (size_t)warp * 2 * Q4K_STAGE_BYTES;          // this warp's two stages
+    unsigned char *xq = smem + (size_t)GEMV_WARPS * 2 * Q4K_STAGE_BYTES;
+    float *sx = reinterpret_cast<float *>(xq + (size_t)MT * Kpad);
+    int *bs = reinterpret_cast<int *>(sx + sx_floats(MT, nsb));
+    float *part = reinterpret_cast<float *>(bs + MT * nsb * 8);
 
-    auto load = [&](int item, Q4kRegs &r) {
-        const int rr = item / G8, sb = (item - rr * G8) * 8 + sbi;
-        r.A = r.B = r.H = make_uint4(0u, 0u, 0u, 0u);
-        if (item < n_items && sb < nsb) {
-            const size_t blk = (size_t)(r_begin + rr) * nsb + sb;
-            r.A = ldg_stream_u4(qs + blk * 8 + c);
-            r.B = ldg_stream_u4(qs + blk * 8 + 4 + c);
-            r.H = __ldg(hdr + blk);
+    int r_begin, R;
+    cta_rows(a, r_begin, R);
+    const int n_units = R * S;
+    const uint4 *qs = reinterpret_cast<const uint4 *>(a.w.p0) + c;
+    const uint4 *hdr = reinterpret_cast<const uint4 *>(a.w.p1);
+    const int sc_shift = (c * 24) & 31;                       // where this lane's 24-bit scale group starts
+    // lane-constant parts of the shared-memory addresses (step g adds a multiple of a fixed stride)
+    const uint4 *x_lane = reinterpret_cast<const uint4 *>(xq) + ((sbi >> 1) * 32 + (sbi & 1) * 4 + c);
+    const int *bs_lane = bs + sbi * 8 + 2 * c;
+    const float *sx_lane = sx + sbi;
+    unsigned char *st_lane = ring + lane * 16;
+    const int dq = GEMV_WARPS / S, dr = GEMV_WARPS - dq * S;  // unit index + 32 in (row, segment) terms
+
+    auto iter_init = [&](StepIter &it) {
+        const int my_units = warp < n_units ? (n_units - warp + GEMV_WARPS - 1) / GEMV_WARPS : 0;
+        it.left = my_units * GP;
+        const int rr = warp / S;
+        it.row = r_begin + rr;
+        it.seg = warp - rr * S;
+        it.gi = 0;
+    };
+    auto iter_next = [&](StepIter &it) {
+        it.left--;
+        if (++it.gi == GP) {
+            it.gi = 0;
+            it.seg += dr;
+            it.row += dq;
+            if (it.seg >= S) { it.seg -= S; it.row++; }
         }
     };
 
-    Q4kRegs cur;
-    load(warp, cur);                      // weights are in flight while x is quantized
-    stage_q8k<MT, PREQ, false>(a, xq, sx, bs, nsb, Kpad);
-    __syncthreads();
+    // issue the copies of one step into a stage (nothing is issued for lanes past the end of K)
+    auto issue = [&](const StepIter &it, int stage) {
+        const int sb0 = (it.seg * GP + it.gi) * 16 + sbi;
+        const unsigned blk = (unsigned)it.row * (unsigned)nsb + (unsigned)sb0;
+        unsigned char *st = st_lane + stage * Q4K_STAGE_BYTES;
+        const uint4 *src = qs + (size_t)blk * 8;
+        const int ok0 = it.left > 0 && sb0 < nsb, ok1 = it.left > 0 && sb0 + 8 < nsb;
+        cp_async16_if(st, src, ok0);
+        cp_async16_if(st + 512, src + 4, ok0);
+        cp_async16_if(st + 1024, src + 64, ok1);
+        cp_async16_if(st + 1536, src + 68, ok1);
+        // headers: lanes with c == 0 fetch the one of super-block sbi, lanes with c == 1 that of sbi + 8
+        cp_async16_if(ring + stage * Q4K_STAGE_BYTES + 2048 + (c * 8 + sbi) * 16, hdr + blk + c * 8, c == 0 ? ok0 : (c == 1 ? ok1 : 0));
+        cp_async_commit();
+    };
 
-    for (int item = warp; item < n_items; item += GEMV_WARPS) {
-        Q4kRegs nxt;
-        load(item + GEMV_WARPS, nxt);
-        const int rr = item / G8, sb = (item - rr * G8) * 8 + sbi;
-        float acc[MT];
+    float acc[MT];
 #pragma unroll
-        for (int m = 0; m < MT; m++) acc[m] = 0.0f;
-        if (sb < nsb) {
-            int s1, s2, m1, m2;
-            q4k_scales(cur.H, c, s1, s2, m1, m2);
-            const float d = f16_bits_to_f32(cur.H.x), dmin = f16_bits_to_f32(cur.H.x >> 16);
-            const uint32_t a_lo[4] = {cur.A.x & 0x0f0f0f0fu, cur.A.y & 0x0f0f0f0fu, cur.A.z & 0x0f0f0f0fu, cur.A.w & 0x0f0f0f0fu};
-            const uint32_t a_hi[4] = {(cur.A.x >> 4) & 0x0f0f0f0fu, (cur.A.y >> 4) & 0x0f0f0f0fu, (cur.A.z >> 4) & 0x0f0f0f0fu, (cur.A.w >> 4) & 0x0f0f0f0fu};
-            const uint32_t b_lo[4] = {cur.B.x & 0x0f0f0f0fu, cur.B.y & 0x0f0f0f0fu, cur.B.z & 0x0f0f0f0fu, cur.B.w & 0x0f0f0f0fu};
-            const uint32_t b_hi[4] = {(cur.B.x >> 4) & 0x0f0f0f0fu, (cur.B.y >> 4) & 0x0f0f0f0fu, (cur.B.z >> 4) & 0x0f0f0f0fu, (cur.B.w >> 4) & 0x0f0f0f0fu};
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                const uint4 *xm = reinterpret_cast<const uint4 *>(xq + (size_t)m * Kpad);
-                const uint4 X0 = xm[xq_unit(sb, c, 0)], X1 = xm[xq_unit(sb, c, 1)];
-                const uint4 X2 = xm[xq_unit(sb, c, 2)], X3 = xm[xq_unit(sb, c, 3)];
-                int pA = 0, pB = 0;   // exact int32 dots of sub-blocks 2c and 2c+1
-                pA = __dp4a((int)a_lo[0], (int)X0.x, pA); pA = __dp4a((int)a_lo[1], (int)X0.y, pA);
-                pA = __dp4a((int)a_lo[2], (int)X0.z, pA); pA = __dp4a((int)a_lo[3], (int)X0.w, pA);
-                pA = __dp4a((int)b_lo[0], (int)X1.x, pA); pA = __dp4a((int)b_lo[1], (int)X1.y, pA);
-                pA = __dp4a((int)b_lo[2], (int)X1.z, pA); pA = __dp4a((int)b_lo[3], (int)X1.w, pA);
-                pB = __dp4a((int)a_hi[0], (int)X2.x, pB); pB = __dp4a((int)a_hi[1], (int)X2.y, pB);
-                pB = __dp4a((int)a_hi[2], (int)X2.z, pB); pB = __dp4a((int)a_hi[3], (int)X2.w, pB);
-                pB = __dp4a((int)b_hi[0], (int)X3.x, pB); pB = __dp4a((int)b_hi[1], (int)X3.y, pB);
-                pB = __dp4a((int)b_hi[2], (int)X3.z, pB); pB = __dp4a((int)b_hi[3], (int)X3.w, pB);
-                if (DUMP && m == 0) {
-                    int32_t *o = a.idots + (size_t)(r_begin + rr) * (nsb * 8) + sb * 8 + 2 * c;
-                    o[0] = pA; o[1] = pB;
-                }
-                const int2 b2 = *reinterpret_cast<const int2 *>(bs + (m * nsb + sb) * 8 + 2 * c);
-                const int isum = s1 * pA + s2 * pB;            // sum_j s_j * idot_j  (exact)
-                const int msum = m1 * b2.x + m2 * b2.y;        // sum_j m_j * bsum_j  (exact)
-                acc[m] = sx[m * nsb + sb] * (d * (float)isum - dmin * (float)msum);
-            }
-        }
+    for (int m = 0; m < MT; m++) acc[m] = 0.0f;
+
+    // one super-block of the step: A, B = the lane's two 16-byte pieces, H = the header
+    auto block_dot = [&](const uint4 &A, const uint4 &B, const uint4 &H, int sb, int row) {
+        // 24-bit group: s(2c) | s(2c+1) << 6 | m(2c) << 12 | m(2c+1) << 18
+        const uint32_t lo_w = (c < 2) ? H.y : (c == 2 ? H.z : H.w);
+        const uint32_t hi_w = (c < 2) ? H.z : H.w;
+        const uint32_t sg = __funnelshift_r(lo_w, hi_w, sc_shift);
+        const int s1 = (int)(sg & 63u), s2 = (int)((sg >> 6) & 63u);
+        const int m1 = (int)((sg >> 12) & 63u), m2 = (int)((sg >> 18) & 63u);
+        const float d = f16_bits_to_f32(H.x), dmin = f16_bits_to_f32(H.x >> 16);
+        const uint32_t a_lo[4] = {A.x & 0x0f0f0f0fu, A.y & 0x0f0f0f0fu, A.z & 0x0f0f0f0fu, A.w & 0x0f0f0f0fu};
+        const uint32_t a_hi[4] = {A.x & 0xf0f0f0f0u, A.y & 0xf0f0f0f0u, A.z & 0xf0f0f0f0u, A.w & 0xf0f0f0f0u};
+        const uint32_t b_lo[4] = {B.x & 0x0f0f0f0fu, B.y & 0x0f0f0f0fu, B.z & 0x0f0f0f0fu, B.w & 0x0f0f0f0fu};
+        const uint32_t b_hi[4] = {B.x & 0xf0f0f0f0u, B.y & 0xf0f0f0f0u, B.z & 0xf0f0f0f0u, B.w & 0xf0f0f0f0u};
+        const int sbg = sb - sbi;                              // first super-block of the 8-group (multiple of 8)
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            const float s = warp_sum(acc[m]);
-            if (lane == 0) part[item * MT + m] = s;
+            const uint4 *xm = x_lane + m * (Kpad / 16) + sbg * 16;
+            const uint4 X0 = xm[0], X1 = xm[8], X2 = xm[16], X3 = xm[24];
+            int pA = 0, pB = 0;   // exact int32 dots of sub-blocks 2c and 2c+1 (pB carries a factor 16)
+            pA = dp4a_u8s8(a_lo[0], X0.x, pA); pA = dp4a_u8s8(a_lo[1], X0.y, pA);
+            pA = dp4a_u8s8(a_lo[2], X0.z, pA); pA = dp4a_u8s8(a_lo[3], X0.w, pA);
+            pA = dp4a_u8s8(b_lo[0], X1.x, pA); pA = dp4a_u8s8(b_lo[1], X1.y, pA);
+            pA = dp4a_u8s8(b_lo[2], X1.z, pA); pA = dp4a_u8s8(b_lo[3], X1.w, pA);
+            pB = dp4a_u8s8(a_hi[0], X2.x, pB); pB = dp4a_u8s8(a_hi[1], X2.y, pB);
+            pB = dp4a_u8s8(a_hi[2], X2.z, pB); pB = dp4a_u8s8(a_hi[3], X2.w, pB);
+            pB = dp4a_u8s8(b_hi[0], X3.x, pB); pB = dp4a_u8s8(b_hi[1], X3.y, pB);
+            pB = dp4a_u8s8(b_hi[2], X3.z, pB); pB = dp4a_u8s8(b_hi[3], X3.w, pB);
+            pB >>= 4;             // the high nibbles were left in place: every product carried x16
+            if (DUMP && m == 0) {
+                int32_t *o = a.idots + (size_t)row * (nsb * 8) + sb * 8 + 2 * c;
+                o[0] = pA; o[1] = pB;
+            }
+            const int2 b2 = *reinterpret_cast<const int2 *>(bs_lane + m * nsb * 8 + sbg * 8);
+            const int isum = s1 * pA + s2 * pB;            // sum_j s_j * idot_j  (exact)
+            const int msum = m1 * b2.x + m2 * b2.y;        // sum_j m_j * bsum_j  (exact)
+            acc[m] += sx_lane[m * nsb + sbg] * (d * (float)isum - dmin * (float)msum);
         }
-        cur = nxt;
-    }
+    };
+
+    StepIter ii, ic;                         // issue runs one step ahead of compute
+    iter_init(ii);
+    ic = ii;
+    issue(ii, 0);                            // weights are in flight while x is staged
+    iter_next(ii);
+    grid_dependency_wait();                  // x (and y for the accumulate form) come from the kernel before
+    stage_q8k<MT, PREQ, false>(a, xq, sx, bs, nsb, Kpad);
     __syncthreads();
-    if (!DUMP) finish_rows<MT>(part, R, G8, r_begin, a);
+    grid_launch_dependents();
+
+    int stage = 0;
+    while (ic.left > 0) {
+        issue(ii, stage ^ 1);                // the stage consumed one iteration ago
+        iter_next(ii);
+        cp_async_wait<1>();                  // this thread's copies for `stage` have landed
+        __syncwarp();                        // ... and so have the headers copied by other lanes
+        const unsigned char *st = st_lane + stage * Q4K_STAGE_BYTES;
+        const unsigned char *sh = ring + stage * Q4K_STAGE_BYTES + 2048 + sbi * 16;
+        const int sb0 = (ic.seg * GP + ic.gi) * 16 + sbi;
+        if (sb0 < nsb)
+            block_dot(*reinterpret_cast<const uint4 *>(st), *reinterpret_cast<const uint4 *>(st + 512),
+                      *reinterpret_cast<const uint4 *>(sh), sb0, ic.row);
+        if (sb0 + 8 < nsb)
+            block_dot(*reinterpret_cast<const uint4 *>(st + 1024), *reinterpret_cast<const uint4 *>(st + 1536),
+                      *reinterpret_cast<const uint4 *>(sh + 128), sb0 + 8, ic.row);
+        __syncwarp();                        // every lane has read this stage's headers before it is refilled
+        if (!DUMP && ic.gi + 1 == GP) {
+            WarpCursor cu;
+            cu.row = ic.row;
+            cu.u = (ic.row - r_begin) * S + ic.seg;
+            unit_done<MT>(acc, cu, S, part, a, lane);
+        }
+        iter_next(ic);
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+    if (!DUMP) finish_rows<MT>(part, R, S, r_begin, a);
 }
 
 // ---------------------------------------------------------------------------- Q6_K
@@ -212,54 +365,60 @@ struct Q6kRegs { uint4 A, B, H; uint32_t sc; uint32_t d; };
 template <int MT, bool PREQ, bool DUMP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int nsb = a.K >> 8, G8 = (nsb + 7) >> 3;
+    const int nsb = a.K >> 8, G8 = (nsb + 7) >> 3, S = a.S;
     const int Kpad = ((nsb + 1) >> 1) * 512;
     unsigned char *xq = smem;
     float *sx = reinterpret_cast<float *>(smem + (size_t)MT * Kpad);
-    int *bs = reinterpret_cast<int *>(sx + MT * nsb);          // per-16 activation sums
+    int *bs = reinterpret_cast<int *>(sx + sx_floats(MT, nsb)); // per-16 activation sums
     float *part = reinterpret_cast<float *>(bs + MT * nsb * 16);
 
-    const int r_begin = (int)((long long)a.N * blockIdx.x / gridDim.x);
-    const int r_end = (int)((long long)a.N * (blockIdx.x + 1) / gridDim.x);
-    const int R = r_end - r_begin, n_items = R * G8;
+    int r_begin, R;
+    cta_rows(a, r_begin, R);
+    const int n_units = R * S;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sbi = lane >> 2, c = lane & 3;
-    const uint4 *lo = reinterpret_cast<const uint4 *>(a.w.p0);
-    const uint4 *hi = reinterpret_cast<const uint4 *>(a.w.p1);
-    const uint32_t *scp = reinterpret_cast<const uint32_t *>(a.w.p2);
+    const uint4 *lo = reinterpret_cast<const uint4 *>(a.w.p0) + c;
+    const uint4 *hi = reinterpret_cast<const uint4 *>(a.w.p1) + c;
+    const uint32_t *scp = reinterpret_cast<const uint32_t *>(a.w.p2) + c;
     const unsigned short *dp = reinterpret_cast<const unsigned short *>(a.w.p3);
 
-    auto load = [&](int item, Q6kRegs &r) {
-        const int rr = item / G8, sb = (item - rr * G8) * 8 + sbi;
+    auto load = [&](const WarpCursor &cu, Q6kRegs &r) {
+        const int sb = cu.g * 8 + sbi;
         r.A = r.B = r.H = make_uint4(0u, 0u, 0u, 0u);
         r.sc = 0u; r.d = 0u;
-        if (item < n_items && sb < nsb) {
-            const size_t blk = (size_t)(r_begin + rr) * nsb + sb;
-            r.A = ldg_stream_u4(lo + blk * 8 + c);
-            r.B = ldg_stream_u4(lo + blk * 8 + 4 + c);
-            r.H = ldg_stream_u4(hi + blk * 4 + c);
-            r.sc = __ldg(scp + blk * 4 + c);
+        if (cu.u < n_units && sb < nsb) {
+            const size_t blk = (size_t)cu.row * nsb + sb;
+            r.A = ldg_stream_u4(lo + blk * 8);
+            r.B = ldg_stream_u4(lo + blk * 8 + 4);
+            r.H = ldg_stream_u4(hi + blk * 4);
+            r.sc = __ldg(scp + blk * 4);
             r.d = __ldg(dp + blk);
         }
     };
 
-    Q6kRegs cur;
-    load(warp, cur);
+    WarpCursor nx;
+    cursor_set(nx, warp, n_units, S, G8, r_begin);
+    Q6kRegs rn;
+    load(nx, rn);
+    grid_dependency_wait();
     stage_q8k<MT, PREQ, true>(a, xq, sx, bs, nsb, Kpad);
     __syncthreads();
+    grid_launch_dependents();
 
-    for (int item = warp; item < n_items; item += GEMV_WARPS) {
-        Q6kRegs nxt;
-        load(item + GEMV_WARPS, nxt);
-        const int rr = item / G8, sb = (item - rr * G8) * 8 + sbi;
-        float acc[MT];
+    float acc[MT];
 #pragma unroll
-        for (int m = 0; m < MT; m++) acc[m] = 0.0f;
+    for (int m = 0; m < MT; m++) acc[m] = 0.0f;
+    while (nx.u < n_units) {
+        const WarpCursor cu = nx;
+        const Q6kRegs rc = rn;
+        cursor_advance(nx, n_units, S, G8, r_begin);
+        load(nx, rn);
+        const int sb = cu.g * 8 + sbi;
         if (sb < nsb) {
-            const float d = f16_bits_to_f32(cur.d);
-            const uint32_t Aw[4] = {cur.A.x, cur.A.y, cur.A.z, cur.A.w};
-            const uint32_t Bw[4] = {cur.B.x, cur.B.y, cur.B.z, cur.B.w};
-            const uint32_t Hw[4] = {cur.H.x, cur.H.y, cur.H.z, cur.H.w};
+            const float d = f16_bits_to_f32(rc.d);
+            const uint32_t Aw[4] = {rc.A.x, rc.A.y, rc.A.z, rc.A.w};
+            const uint32_t Bw[4] = {rc.B.x, rc.B.y, rc.B.z, rc.B.w};
+            const uint32_t Hw[4] = {rc.H.x, rc.H.y, rc.H.z, rc.H.w};
             // six-bit values 0..63 of the four 16-weight groups t = 0..3 of this chunk
             uint32_t w6[4][4];
 #pragma unroll
@@ -269,39 +428,36 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_kernel(const GemvArg
                 w6[2][k] = ((Aw[k] >> 4) & 0x0f0f0f0fu) | (Hw[k] & 0x30303030u);
                 w6[3][k] = ((Bw[k] >> 4) & 0x0f0f0f0fu) | ((Hw[k] >> 2) & 0x30303030u);
             }
+            const int s0 = (int)(signed char)(rc.sc & 0xffu), s1 = (int)(signed char)((rc.sc >> 8) & 0xffu);
+            const int s2 = (int)(signed char)((rc.sc >> 16) & 0xffu), s3 = (int)(signed char)(rc.sc >> 24);
+            const int st[4] = {s0, s1, s2, s3};
+            const int u0 = xq_unit(sb, c, 0);
 #pragma unroll
             for (int m = 0; m < MT; m++) {
-                const uint4 *xm = reinterpret_cast<const uint4 *>(xq + (size_t)m * Kpad);
+                const uint4 *xm = reinterpret_cast<const uint4 *>(xq + (size_t)m * Kpad) + u0;
                 const int4 b4 = *reinterpret_cast<const int4 *>(bs + (m * nsb + sb) * 16 + 4 * c);
                 const int bsum[4] = {b4.x, b4.y, b4.z, b4.w};
                 int isum = 0;
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                    const uint4 X = xm[xq_unit(sb, c, t)];
-                    int it = __dp4a((int)w6[t][0], (int)X.x, 0);   // exact int32 dot of 16 weights
-                    it = __dp4a((int)w6[t][1], (int)X.y, it);
-                    it = __dp4a((int)w6[t][2], (int)X.z, it);
-                    it = __dp4a((int)w6[t][3], (int)X.w, it);
-                    if (DUMP && m == 0) a.idots[(size_t)(r_begin + rr) * (nsb * 16) + sb * 16 + 4 * c + t] = it;
-                    const int st = (int)(signed char)((cur.sc >> (8 * t)) & 0xffu);
-                    isum += st * (it - 32 * bsum[t]);              // s*(i) - 32*s*(x sum), exact
+                    const uint4 X = xm[t * 8];
+                    int it = dp4a_u8s8(w6[t][0], X.x, 0);   // exact int32 dot of 16 weights
+                    it = dp4a_u8s8(w6[t][1], X.y, it);
+                    it = dp4a_u8s8(w6[t][2], X.z, it);
+                    it = dp4a_u8s8(w6[t][3], X.w, it);
+                    if (DUMP && m == 0) a.idots[(size_t)cu.row * (nsb * 16) + sb * 16 + 4 * c + t] = it;
+                    isum += st[t] * (it - 32 * bsum[t]);    // s*(i) - 32*s*(x sum), exact
                 }
-                acc[m] = (sx[m * nsb + sb] * d) * (float)isum;
+                acc[m] += (sx[m * nsb + sb] * d) * (float)isum;
             }
         }
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-            const float s = warp_sum(acc[m]);
-            if (lane == 0) part[item * MT + m] = s;
-        }
-        cur = nxt;
+        if (!DUMP && cu.g + 1 == cu.g_end) unit_done<MT>(acc, cu, S, part, a, lane);
     }
-    __syncthreads();
-    if (!DUMP) finish_rows<MT>(part, R, G8, r_begin, a);
+    if (!DUMP) finish_rows<MT>(part, R, S, r_begin, a);
 }
 
 // ---------------------------------------------------------------------------- Q8_0
-// f32 activations in shared memory.  An item is one row x 2048 weights: lane l owns the four
+// f32 activations in shared memory.  A group is 2048 weights of one row: lane l owns the four
 // 16-weight pieces j*512 + 16l (j = 0..3), so every weight load instruction of the warp
 // reads 512 contiguous bytes.  x is stored so that, for a fixed piece and float4 index, the
 // 32 lanes read 512 contiguous bytes.
@@ -316,35 +472,37 @@ __device__ __forceinline__ float s8_to_f32(uint32_t w_flipped, int i) {
 template <int MT>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q80_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int K = a.K, G8 = (K + 2047) >> 11;
+    const int K = a.K, G8 = (K + 2047) >> 11, S = a.S;
     const int Kpad = G8 * 2048;
     float4 *xs = reinterpret_cast<float4 *>(smem);                         // [MT][Kpad/4]
     float *part = reinterpret_cast<float *>(smem + (size_t)MT * Kpad * 4);
 
-    const int r_begin = (int)((long long)a.N * blockIdx.x / gridDim.x);
-    const int r_end = (int)((long long)a.N * (blockIdx.x + 1) / gridDim.x);
-    const int R = r_end - r_begin, n_items = R * G8;
+    int r_begin, R;
+    cta_rows(a, r_begin, R);
+    const int n_units = R * S;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint4 *qp = reinterpret_cast<const uint4 *>(a.w.p0);
     const unsigned short *dp = reinterpret_cast<const unsigned short *>(a.w.p1);
 
-    auto load = [&](int item, Q80Regs &r) {
-        const int rr = item / G8, g = item - rr * G8;
+    auto load = [&](const WarpCursor &cu, Q80Regs &r) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const int k0 = g * 2048 + j * 512 + lane * 16;
+            const int k0 = cu.g * 2048 + j * 512 + lane * 16;
             r.W[j] = make_uint4(0u, 0u, 0u, 0u);
             r.d[j] = 0u;
-            if (item < n_items && k0 < K) {
-                const size_t row = (size_t)(r_begin + rr);
+            if (cu.u < n_units && k0 < K) {
+                const size_t row = (size_t)cu.row;
                 r.W[j] = ldg_stream_u4(qp + (row * K + k0) / 16);
                 r.d[j] = __ldg(dp + row * (K / 32) + (k0 >> 5));
             }
         }
     };
 
-    Q80Regs cur;
-    load(warp, cur);
+    WarpCursor nx;
+    cursor_set(nx, warp, n_units, S, G8, r_begin);
+    Q80Regs rn;
+    load(nx, rn);
+    grid_dependency_wait();
     // stage x: float4 (piece-block pb, lane l, idx p) -> xs[m][pb*128 + p*32 + l]
     for (int idx = threadIdx.x; idx < MT * (Kpad / 4); idx += blockDim.x) {
         const int m = idx / (Kpad / 4), f4 = idx - m * (Kpad / 4);
@@ -354,18 +512,20 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q80_kernel(const GemvArg
         xs[(size_t)m * (Kpad / 4) + pb * 128 + p * 32 + l] = v;
     }
     __syncthreads();
+    grid_launch_dependents();
 
-    for (int item = warp; item < n_items; item += GEMV_WARPS) {
-        Q80Regs nxt;
-        load(item + GEMV_WARPS, nxt);
-        const int rr = item / G8, g = item - rr * G8;
-        float acc[MT];
+    float acc[MT];
 #pragma unroll
-        for (int m = 0; m < MT; m++) acc[m] = 0.0f;
+    for (int m = 0; m < MT; m++) acc[m] = 0.0f;
+    while (nx.u < n_units) {
+        const WarpCursor cu = nx;
+        const Q80Regs rc = rn;
+        cursor_advance(nx, n_units, S, G8, r_begin);
+        load(nx, rn);
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float d = f16_bits_to_f32(cur.d[j]);
-            const uint32_t wv[4] = {cur.W[j].x ^ 0x80808080u, cur.W[j].y ^ 0x80808080u, cur.W[j].z ^ 0x80808080u, cur.W[j].w ^ 0x80808080u};
+            const float d = f16_bits_to_f32(rc.d[j]);
+            const uint32_t wv[4] = {rc.W[j].x ^ 0x80808080u, rc.W[j].y ^ 0x80808080u, rc.W[j].z ^ 0x80808080u, rc.W[j].w ^ 0x80808080u};
             float wf[16];
 #pragma unroll
             for (int p = 0; p < 4; p++)
@@ -373,7 +533,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q80_kernel(const GemvArg
                 for (int i = 0; i < 4; i++) wf[p * 4 + i] = s8_to_f32(wv[p], i);
 #pragma unroll
             for (int m = 0; m < MT; m++) {
-                const float4 *xm = xs + (size_t)m * (Kpad / 4) + (g * 4 + j) * 128 + lane;
+                const float4 *xm = xs + (size_t)m * (Kpad / 4) + (cu.g * 4 + j) * 128 + lane;
                 float s = 0.0f;
 #pragma unroll
                 for (int p = 0; p < 4; p++) {
@@ -386,15 +546,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q80_kernel(const GemvArg
                 acc[m] = fmaf(d, s, acc[m]);
             }
         }
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-            const float s = warp_sum(acc[m]);
-            if (lane == 0) part[item * MT + m] = s;
-        }
-        cur = nxt;
+        if (cu.g + 1 == cu.g_end) unit_done<MT>(acc, cu, S, part, a, lane);
     }
-    __syncthreads();
-    finish_rows<MT>(part, R, G8, r_begin, a);
+    finish_rows<MT>(part, R, S, r_begin, a);
 }
 
 // ---------------------------------------------------------------------------- quant_q8k
@@ -413,13 +567,46 @@ __global__ void __launch_bounds__(256) quant_q8k_kernel(const float *x, int8_t *
 }
 
 // ---------------------------------------------------------------------------- host side
-static size_t gemv_smem_bytes(uint32_t type, int MT, size_t K, size_t rows_max) {
+// Segments per row: 1 when a CTA has at least ~3/4 as many rows as warps, otherwise enough
+// segments to give every warp a unit (never more than the row has groups).
+static int gemv_segments(size_t rows_max, size_t G8) {
+    if (rows_max >= 24) return 1;
+    size_t s = (GEMV_WARPS + rows_max - 1) / rows_max;
+    if (s > G8) s = G8;
+    return s < 1 ? 1 : (int)s;
+}
+
+// Q4_K: steps are sixteen super-blocks and the segment count must divide the steps per row.
+static int gemv_segments_q4k(size_t rows_max, size_t nsb) {
+    const size_t G = (nsb + 15) / 16;
+    if (rows_max >= 24) return 1;
+    const size_t want = (GEMV_WARPS + rows_max - 1) / rows_max;
+    size_t best = 1;
+    for (size_t s = 1; s <= G && s <= want; s++)
+        if (G % s == 0) best = s;
+    return (int)best;
+}
+
+static size_t gemv_ring_bytes(uint32_t type, int depth) {
+    (void)depth;
+    return type == OJAS_B200_Q4_K ? (size_t)GEMV_WARPS * 2 * Q4K_STAGE_BYTES : 0;
+}
+
+static size_t gemv_smem_bytes(uint32_t type, int MT, size_t K, size_t rows_max, int S, int depth) {
     const size_t nsb = K / 256, G8 = (nsb + 7) / 8;
-    const size_t part = rows_max * G8 * MT * 4;
+    const size_t part = (S > 1 ? rows_max * S * MT * 4 : 0) + 16;
     if (type == OJAS_B200_Q8_0) return (size_t)MT * G8 * 2048 * 4 + part;
     const size_t Kpad = ((nsb + 1) / 2) * 512;
     const size_t nb = (type == OJAS_B200_Q6_K) ? 16 : 8;
-    return (size_t)MT * Kpad + (size_t)MT * nsb * 4 + (size_t)MT * nsb * nb * 4 + part;
+    return gemv_ring_bytes(type, depth) + (size_t)MT * Kpad + (size_t)sx_floats(MT, (int)nsb) * 4 + (size_t)MT * nsb * nb * 4 + part;
+}
+
+// Deepest ring (4, 3 or 2 stages) that leaves room for `mt` rows of activations; 0 if even 2 does not fit.
+static int gemv_depth(ojas_b200_ctx *ctx, uint32_t type, int mt, size_t K, size_t rows_max, int S) {
+    int want = ctx->gemv_depth >= 2 && ctx->gemv_depth <= 4 ? ctx->gemv_depth : 4;
+    for (int d = want; d >= 2; d--)
+        if (gemv_smem_bytes(type, mt, K, rows_max, S, d) <= (size_t)ctx->smem_optin) return d;
+    return 0;
 }
 
 template <typename KernelT>
@@ -428,8 +615,21 @@ static int launch_gemv(ojas_b200_ctx *ctx, KernelT kernel, const GemvArgs &args,
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "%s: shared memory %zu: %s", name, smem, cudaGetErrorString(e));
     }
-    kernel<<<grid, GEMV_THREADS, smem, ctx->stream>>>(args);
-    OJAS_LAUNCH_CHECK(ctx, name);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (ctx->pdl) {   // let this kernel's weight prefetch overlap the tail of the kernel before it
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
+    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch %s: %s", name, cudaGetErrorString(e));
+    ctx->launches++;
     return 0;
 }
 
@@ -440,8 +640,13 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     const int grid = ctx->sm_count < args.N ? ctx->sm_count : args.N;
     const size_t rows_max = ((size_t)args.N + grid - 1) / grid;
     const int MT = pick_mt((size_t)args.M);
-    const size_t smem = gemv_smem_bytes(type, MT, (size_t)args.K, rows_max);
-    if (smem > (size_t)ctx->smem_optin)
+    const size_t G8 = ((size_t)args.K / 256 + 7) / 8;
+    args.S = dump ? 1 : (type == OJAS_B200_Q4_K ? gemv_segments_q4k(rows_max, (size_t)args.K / 256) : gemv_segments(rows_max, G8));
+    args.rows_base = args.N / grid;
+    args.rows_rem = args.N % grid;
+    args.depth = gemv_depth(ctx, type, MT, (size_t)args.K, rows_max, args.S);
+    const size_t smem = gemv_smem_bytes(type, MT, (size_t)args.K, rows_max, args.S, args.depth ? args.depth : 2);
+    if (args.depth == 0 || smem > (size_t)ctx->smem_optin)
         return ojas_fail(ctx, OJAS_B200_E_LIMIT, "gemv: %zu bytes of shared memory needed, %d available", smem, ctx->smem_optin);
 #define GEMV_CASE(KERNEL, NAME)                                                 \
     switch (MT) {                                                               \
@@ -479,8 +684,9 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
 static int gemv_max_mt(ojas_b200_ctx *ctx, uint32_t type, size_t K, size_t N) {
     const int grid = ctx->sm_count < (int)N ? ctx->sm_count : (int)N;
     const size_t rows_max = (N + grid - 1) / grid;
+    const int S = type == OJAS_B200_Q4_K ? gemv_segments_q4k(rows_max, K / 256) : gemv_segments(rows_max, (K / 256 + 7) / 8);
     for (int mt = 8; mt >= 1; mt >>= 1)
-        if (gemv_smem_bytes(type, mt, K, rows_max) <= (size_t)ctx->smem_optin) return mt;
+        if (gemv_depth(ctx, type, mt, K, rows_max, S) != 0) return mt;
     return 0;
 }
 

@@ -11,7 +11,20 @@ struct PlanePtrs { uint8_t *p0, *p1, *p2, *p3; };
 __host__ __device__ static inline void repack_q4k_block(const uint8_t *raw, size_t blk, PlanePtrs o) {
     const uint8_t *src = raw + blk * 144;
     uint8_t *qs = o.p0 + blk * 128, *hdr = o.p1 + blk * 16;
-    for (int i = 0; i < 16; i++) hdr[i] = src[i];
+    for (int i = 0; i < 4; i++) hdr[i] = src[i];
+    const uint8_t *sc = src + 4;
+    for (int c = 0; c < 4; c++) {
+        unsigned v[4];   // s(2c), s(2c+1), m(2c), m(2c+1) by the GGUF rule (crates/ojas-formats/src/gguf.rs:1132-1140)
+        for (int h = 0; h < 2; h++) {
+            const int j = 2 * c + h;
+            if (j < 4) { v[h] = sc[j] & 63u; v[2 + h] = sc[j + 4] & 63u; }
+            else { v[h] = (sc[j + 4] & 0xFu) | ((unsigned)(sc[j - 4] >> 6) << 4); v[2 + h] = (unsigned)(sc[j + 4] >> 4) | ((unsigned)(sc[j] >> 6) << 4); }
+        }
+        const unsigned g = v[0] | (v[1] << 6) | (v[2] << 12) | (v[3] << 18);
+        hdr[4 + 3 * c] = (uint8_t)(g & 0xff);
+        hdr[5 + 3 * c] = (uint8_t)((g >> 8) & 0xff);
+        hdr[6 + 3 * c] = (uint8_t)((g >> 16) & 0xff);
+    }
     for (int c = 0; c < 4; c++)
         for (int h = 0; h < 2; h++)
             for (int i = 0; i < 16; i++) qs[h * 64 + c * 16 + i] = src[16 + c * 32 + h * 16 + i];

@@ -20,6 +20,7 @@ SIGNATURES = {
     "ojas_b200_destroy": (None, [_vp]),
     "ojas_b200_set_stream": (_i, [_vp, _vp]),
     "ojas_b200_stream": (_vp, [_vp]),
+    "ojas_b200_set_option": (_i, [_vp, C.c_char_p, _i]),
     "ojas_b200_last_error": (C.c_char_p, [_vp]),
     "ojas_b200_sm_count": (_i, [_vp]),
     "ojas_b200_launch_count": (_u64, [_vp]),

@@ -104,6 +104,9 @@ class B200Gpu:
     def stream(self) -> int:
         return int(self._l.ojas_b200_stream(self._ctx) or 0)
 
+    def set_option(self, key: str, value: int) -> None:
+        self._ck(self._l.ojas_b200_set_option(self._ctx, key.encode(), int(value)))
+
     # ------------------------------------------------------------------ Device
     def alloc_bytes(self, nbytes: int) -> Buf:
         p = C.c_void_p()

@@ -60,13 +60,10 @@ def model_dequant(ggml_type: int, packed: np.ndarray, n: int, k: int) -> np.ndar
         sc = hdr[:, 4:16].astype(np.uint32)
         s = np.empty((nb, 8), np.float32)
         mn = np.empty((nb, 8), np.float32)
-        for j in range(8):
-            if j < 4:
-                s[:, j] = sc[:, j] & 63
-                mn[:, j] = sc[:, j + 4] & 63
-            else:
-                s[:, j] = (sc[:, j + 4] & 0xF) | ((sc[:, j - 4] >> 6) << 4)
-                mn[:, j] = (sc[:, j + 4] >> 4) | ((sc[:, j] >> 6) << 4)
+        for c in range(4):  # 24-bit group per chunk: s(2c) | s(2c+1)<<6 | m(2c)<<12 | m(2c+1)<<18
+            g = sc[:, 3 * c] | (sc[:, 3 * c + 1] << 8) | (sc[:, 3 * c + 2] << 16)
+            s[:, 2 * c], s[:, 2 * c + 1] = g & 63, (g >> 6) & 63
+            mn[:, 2 * c], mn[:, 2 * c + 1] = (g >> 12) & 63, (g >> 18) & 63
         out = np.empty((nb, 256), np.float32)
         for c in range(4):
             for h in range(2):
