@@ -383,6 +383,8 @@ def run_case(args) -> None:
     ncu captures and the shape sweeps use; prints one JSON line."""
     import ojas_engine_b200 as ob
     import oracle
+    if args.case.startswith("gemm:"):
+        return run_gemm_case(args)
     tag, n, k, m = args.case.split(":")
     n, k, m = int(n), int(k), int(m)
     t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
@@ -428,6 +430,50 @@ def run_case(args) -> None:
     gpu.close()
 
 
+def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int, tc_peak: float, ksplit: int = 0) -> dict:
+    """Times the tensor-core prefill GEMM (activation preparation + MMA kernel per call)."""
+    import oracle
+    t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
+    base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
+    ring = max(2, int(200e6 // ob.raw_bytes(t, n, k)) + 1)          # distinct weights: more than L2 in total
+    ws = [gpu.load_weight(np.ascontiguousarray(np.roll(base, 13 * i, axis=0)), t, n, k) for i in range(ring)]
+    x = gpu.upload(np.random.default_rng(7).standard_normal((m, k), dtype=np.float32))
+    y = gpu.alloc(m * n)
+    work = gpu.alloc_bytes(gpu.gemm_workspace_bytes(m, k))
+    if ksplit:
+        gpu.set_option("gemm_ksplit", ksplit)
+    for i in range(warmup):
+        gpu.gemm(ws[i % ring], x, y, m, workspace=work)
+    gpu.sync()
+    e0, e1 = gpu.event(), gpu.event()
+    gpu.record(e0)
+    for i in range(steps):
+        gpu.gemm(ws[i % ring], x, y, m, workspace=work)
+    gpu.record(e1)
+    gpu.sync()
+    us = gpu.elapsed_ms(e0, e1) * 1e3 / steps
+    gpu.set_option("gemm_ksplit", 0)
+    for w in ws:
+        gpu.free(w.buf)
+    for b in (x, y, work):
+        gpu.free(b)
+    tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
+    return {"workload": f"{tag}_gemm_m{m}_n{n}_k{k}", "us_per_call": round(us, 2), "TFLOP/s": round(tf, 1),
+            "frac_of_peak": round(tf / tc_peak, 4), "ksplit": ksplit or "auto"}
+
+
+def run_gemm_case(args) -> None:
+    """`--case gemm:q4k:M:N:K [--ksplit S]`: one prefill GEMM shape on one GPU."""
+    import ojas_engine_b200 as ob
+    _, tag, m, n, k = args.case.split(":")
+    _, tc_peak, peak_kind = measured_peaks()
+    gpu = ob.B200Gpu(0)
+    out = gemm_case(gpu, ob, tag, int(m), int(n), int(k), args.steps, args.warmup, tc_peak, args.ksplit)
+    out["peak_kind"] = peak_kind
+    print(json.dumps(out))
+    gpu.close()
+
+
 def _wrap_device_f32(ptr: int, count: int, device: int):
     """A torch view of a device buffer owned by the library (for the NCCL collective)."""
     import torch
@@ -460,6 +506,7 @@ def main() -> None:
     ap.add_argument("--case", default=None, help="time one GEMV shape instead: tag:N:K:M, e.g. q4k:4096:4096:1")
     ap.add_argument("--ring", type=int, default=0, help="--case: number of distinct weights (default: enough to pass L2)")
     ap.add_argument("--no-graph", action="store_true", help="--case: plain launches instead of a CUDA graph")
+    ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: force the K split (0 = automatic)")
     ap.add_argument("--depth", type=int, default=0, help="--case: stages of the GEMV cp.async ring (2..4)")
     ap.add_argument("--pdl", action="store_true", help="launch GEMVs with programmatic dependent launch")
     args = ap.parse_args()

@@ -59,7 +59,8 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
 /* Options, also read once from the environment at creation the way the engine reads its OJAS_*
  * switches (crates/ojas-core/src/config.rs:1-22): "pdl" (OJAS_B200_PDL=1) launches the GEMVs with
  * programmatic dependent launch so that a kernel's weight prefetch overlaps the tail of the
- * kernel before it in the stream. */
+ * kernel before it in the stream; "gemm_ksplit" (0 = automatic) forces the K split of the GEMM;
+ * "gemv_depth" is kept for compatibility and ignored by the two-stage GEMV ring. */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
@@ -132,6 +133,17 @@ OJAS_B200_API int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t ggml_type, int
  * Q4_K -> idots [N, K/32], Q6_K -> idots [N, K/16] (int32). */
 OJAS_B200_API int ojas_b200_gemv_idots(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, int32_t *idots,
                          size_t K, size_t N);
+
+/* ---- prefill GEMM on the tensor cores (tcgen05 + TMEM): replaces gemm_mm_{q4l,q6k,q8_0} and
+ * their split-K forms (crates/ojas-cuda/src/kernels/gemm_q.rs:499-590; call site CudaSsm::mm,
+ * crates/ojas-cuda/src/qwen35.rs:644-702).  y [M,N] = x [M,K] * W^T (accum != 0: y += ...).  Q4_K and
+ * Q6_K activations are quantized to Q8_K first, as the CPU path does, and enter the MMA as
+ * f16(sx * q); Q8_0 activations enter as f16(x); accumulation is fp32.  `workspace` is
+ * caller-owned scratch of at least ojas_b200_gemm_workspace_bytes(M, K) bytes, 256-byte
+ * aligned (the f16 activation tiles); nothing is allocated here. */
+OJAS_B200_API size_t ojas_b200_gemm_workspace_bytes(size_t M, size_t K);
+OJAS_B200_API int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, float *y, size_t K,
+                                 size_t N, size_t M, int accum, void *workspace, size_t workspace_bytes);
 
 /* ---- name-based dispatch: the C form of KernelRuntime::dispatch / has_kernel
  * (crates/ojas-core/src/kernel.rs:68-83; argument marshalling crates/ojas-cuda/src/device.rs:

@@ -55,6 +55,18 @@ static int d_quant_q8k(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
     return ojas_b200_quant_q8k(ctx, (const float *)b[0], c[1], c[0], (int8_t *)b[1], (float *)b[2], (int32_t *)b[3]);
 }
 
+// gemm_mm_<q4k|q6k|q8_0>: (x, w, y, workspace) (K, N, accum, M, workspace_bytes) — the prefill entries
+// of crates/ojas-cuda/src/kernels/gemm_q.rs:499-531 ((x, w, y, K, N, accum, M)) plus the scratch
+// buffer this implementation needs for its f16 activation tiles.
+#define GEMM_ENTRY(tag, type)                                                                                     \
+    static int gemm_##tag(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {                                \
+        return ojas_b200_gemm(ctx, type, (const float *)b[0], b[1], (float *)b[2], c[0], c[1], c[3], (int)c[2],   \
+                              b[3], (size_t)c[4]);                                                                \
+    }
+GEMM_ENTRY(q4k, OJAS_B200_Q4_K)
+GEMM_ENTRY(q6k, OJAS_B200_Q6_K)
+GEMM_ENTRY(q8_0, OJAS_B200_Q8_0)
+
 #define GEMV_TABLE(tag)                                      \
     {"gemv_nat_" #tag, 3, 2, gemv_##tag##_plain},            \
     {"gemv_nat_" #tag "_accum", 3, 2, gemv_##tag##_accum},   \
@@ -64,6 +76,7 @@ static int d_quant_q8k(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
 static const NameEntry kTable[] = {
     GEMV_TABLE(q4k), GEMV_TABLE(q6k), GEMV_TABLE(q80),
     {"quant_q8k", 4, 2, d_quant_q8k},
+    {"gemm_mm_q4k", 4, 5, gemm_q4k}, {"gemm_mm_q6k", 4, 5, gemm_q6k}, {"gemm_mm_q8_0", 4, 5, gemm_q8_0},
 };
 static const int kTableLen = (int)(sizeof kTable / sizeof kTable[0]);
 

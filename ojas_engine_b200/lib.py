@@ -49,6 +49,8 @@ SIGNATURES = {
     "ojas_b200_gemv": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_q8k": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_idots": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz]),
+    "ojas_b200_gemm_workspace_bytes": (_sz, [_sz, _sz]),
+    "ojas_b200_gemm": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i, _vp, _sz]),
     "ojas_b200_has_kernel": (_i, [C.c_char_p]),
     "ojas_b200_kernel_count": (_i, []),
     "ojas_b200_kernel_name": (C.c_char_p, [_i]),

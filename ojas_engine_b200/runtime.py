@@ -176,6 +176,24 @@ class B200Gpu:
         self._ck(self._l.ojas_b200_gemv_q8k(self._ctx, w.ggml_type, form, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr),
                                             C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
 
+    def gemm_workspace_bytes(self, m: int, k: int) -> int:
+        return int(self._l.ojas_b200_gemm_workspace_bytes(m, k))
+
+    def gemm(self, w: Lin, x: Buf, y: Buf, m: int, accum: bool = False, workspace: Buf | None = None) -> None:
+        """Tensor-core prefill GEMM.  Without a caller workspace a grow-only scratch buffer owned by
+        this object is used (allocated outside the call path of the C ABI, which never allocates)."""
+        need = self.gemm_workspace_bytes(m, w.k)
+        if workspace is None:
+            ws = getattr(self, "_gemm_ws", None)
+            if ws is None or ws.nbytes < need:
+                if ws is not None:
+                    self.sync()
+                    self.free(ws)
+                ws = self._gemm_ws = self.alloc_bytes(need)
+            workspace = ws
+        self._ck(self._l.ojas_b200_gemm(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
+                                        w.k, w.n, m, 1 if accum else 0, C.c_void_p(workspace.ptr), workspace.nbytes))
+
     def gemv_idots(self, w: Lin, x: Buf, idots: Buf) -> None:
         self._ck(self._l.ojas_b200_gemv_idots(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(idots.ptr), w.k, w.n))
 
@@ -212,12 +230,7 @@ class B200Gpu:
         if m <= GEMV_MAX_M:
             self.gemv(w, x, y, m, form)
             return
-        if hasattr(self, "gemm"):
-            self.gemm(w, x, y, m, accum)  # tensor-core prefill path
-            return
-        for m0 in range(0, m, GEMV_MAX_M):
-            mb = min(GEMV_MAX_M, m - m0)
-            self.gemv(w, Buf(x.ptr + m0 * w.k * 4, mb * w.k * 4), Buf(y.ptr + m0 * w.n * 4, mb * w.n * 4), mb, form)
+        self.gemm(w, x, y, m, accum)  # tensor-core prefill path
 
     # ------------------------------------------------------------------ timing / graphs
     def event(self) -> int:

@@ -1,0 +1,119 @@
+"""Parity of the tensor-core prefill GEMM with the CPU oracle, through the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+
+import oracle
+import ojas_engine_b200 as ob
+from ojas_engine_b200 import Q4_K, Q6_K, Q8_0
+
+from conftest import rel_l2
+from helpers import TYPES, activations, gauss_weights, synth_weights
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3       # relative L2 against the reference CPU path (loop of matvec_kq)
+SENT = 12345.5   # guard value past row M, as crates/ojas-cuda/tests/prefill_gemm_q.rs:308-319 does
+
+
+def _gemm_case(gpu, tag, m, n, k, source="gauss", accum=False, ksplit=0, seed=0, want=None, raw=None):
+    t = TYPES[tag]
+    if raw is None:
+        raw = synth_weights(t, n, k) if source == "synth" else gauss_weights(t, n, k, seed)
+    x = activations(m, k, seed=seed + 100)
+    if want is None:
+        want = oracle.matmul_kq(raw, t, n, k, x)
+    w = gpu.load_weight(raw, t, n, k)
+    xb = gpu.upload(x)
+    y0 = activations(m, n, seed=seed + 200) if accum else np.zeros((m, n), np.float32)
+    yinit = np.concatenate([y0, np.full((1, n), SENT, np.float32)])
+    yb = gpu.upload(yinit)
+    gpu.set_option("gemm_ksplit", ksplit)
+    try:
+        gpu.gemm(w, xb, yb, m, accum)
+        got = gpu.read(yb, np.float32, (m + 1) * n).reshape(m + 1, n)
+    finally:
+        gpu.set_option("gemm_ksplit", 0)
+        for b in (w.buf, xb, yb):
+            gpu.free(b)
+    assert np.all(got[m] == SENT), "wrote past row M"
+    err = rel_l2(got[:m], want + y0 if accum else want)
+    assert err < TOL, f"{tag} m={m} n={n} k={k} accum={accum} ksplit={ksplit}: rel L2 {err:.3e}"
+    return err
+
+
+@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
+def test_single_tile(gpu, tag):
+    _gemm_case(gpu, tag, 32, 128, 256)
+    _gemm_case(gpu, tag, 128, 128, 1024, source="synth")
+
+
+@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
+def test_ragged_shapes(gpu, tag):
+    for m, n, k in [(9, 130, 256), (17, 1000, 768), (100, 257, 2304), (300, 515, 512), (513, 384, 1280)]:
+        _gemm_case(gpu, tag, m, n, k, seed=m)
+
+
+@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
+def test_accumulate_and_split_k(gpu, tag):
+    _gemm_case(gpu, tag, 64, 256, 2048, accum=True)
+    for ks in (2, 3, 8):
+        _gemm_case(gpu, tag, 200, 300, 2048, ksplit=ks)
+    _gemm_case(gpu, tag, 40, 256, 4096, accum=True, ksplit=4)
+
+
+@pytest.mark.parametrize("n,k", [(4096, 4096), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("m", [128, 512])
+def test_config3_q4k_prefill(gpu, m, n, k):
+    """Q4_K prefill GEMM, the tensor-core configuration: M tokens x K=4096 / 14336, N in {4096, 14336}."""
+    _gemm_case(gpu, "q4k", m, n, k, seed=3)
+
+
+def test_config3_q4k_prefill_m2048(gpu):
+    _gemm_case(gpu, "q4k", 2048, 4096, 4096, seed=4)
+
+
+def test_gemm_agrees_with_exact_integer_path(gpu):
+    """The f16 tensor-core result against the GEMV kernel's exact integer block dots on the same
+    inputs (reduced shape): the only differences are the f16 roundings of the two operands."""
+    n, k, m = 512, 2048, 8
+    for t in (Q4_K, Q6_K):
+        raw = gauss_weights(t, n, k, seed=7)
+        x = activations(m, k, seed=8)
+        w = gpu.load_weight(raw, t, n, k)
+        xb, y1, y2 = gpu.upload(x), gpu.alloc(m * n), gpu.alloc(m * n)
+        gpu.gemv(w, xb, y1, m)
+        gpu.gemm(w, xb, y2, m)
+        a, b = gpu.read(y1, np.float32, m * n), gpu.read(y2, np.float32, m * n)
+        assert rel_l2(b, a) < 1e-3
+        for buf in (w.buf, xb, y1, y2):
+            gpu.free(buf)
+
+
+def test_mm_operator_picks_by_row_count(gpu):
+    """CudaSsm::mm (crates/ojas-cuda/src/qwen35.rs:644-702): few rows -> GEMV, many -> tensor-core GEMM."""
+    n, k = 384, 1024
+    raw = gauss_weights(Q4_K, n, k, seed=1)
+    w = gpu.load_weight(raw, Q4_K, n, k)
+    for m in (1, 8, 9, 70):
+        x = activations(m, k, seed=m)
+        xb, y = gpu.upload(x), gpu.upload(np.ones((m, n), np.float32))
+        gpu.mm(xb, w, y, m, accum=True)
+        got = gpu.read(y, np.float32, m * n).reshape(m, n)
+        assert rel_l2(got, oracle.matmul_kq(raw, Q4_K, n, k, x) + 1.0) < TOL
+        gpu.free(xb)
+        gpu.free(y)
+    gpu.free(w.buf)
+
+
+def test_gemm_argument_errors(gpu):
+    w = gpu.load_weight(synth_weights(Q4_K, 4, 256), Q4_K, 4, 256)
+    x, y = gpu.upload(np.zeros((16, 256), np.float32)), gpu.alloc(16 * 4)
+    small = gpu.alloc_bytes(256)
+    with pytest.raises(ob.OjasB200Error, match="workspace"):
+        gpu.gemm(w, x, y, 16, workspace=small)
+    with pytest.raises(ob.OjasB200Error, match="multiple of 256"):
+        gpu.gemm(ob.Lin(w.buf, Q4_K, 4, 100), x, y, 16)
+    gpu.gemm(w, x, y, 16)
+    gpu.sync()
+    for b in (w.buf, x, y, small):
+        gpu.free(b)
