@@ -13,8 +13,9 @@
 //   accumulator D[128 x BN] fp32 in TMEM; TMEM lane = weight row, column = token, so the
 //   epilogue's 32 lanes store 32 consecutive outputs of one token: coalesced without a
 //   shared-memory transpose.
-// Warps 0-3 dequantize (one thread per weight row, one 64-weight chunk per stage) and later
-// drain TMEM; warp 4 issues the TMA loads; warp 5 owns TMEM and issues tcgen05.mma.
+// The kernel is persistent (one CTA per SM walks a list of tiles) with two TMEM accumulators, so
+// the drain of one tile overlaps the main loop of the next; the warp roles are listed above the
+// kernel.
 // Every wait on an mbarrier is bounded: a wait that runs out sets the context's status word,
 // raises the CTA's abort flag, and every role falls through to the common teardown (TMEM is
 // always released).
@@ -28,7 +29,9 @@ constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
 constexpr int GEMM_STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 480;   // 4 epilogue + 8 dequantizing warps, TMA (activations), MMA, TMA (raw weights)
+constexpr int WQ_BUFS = 2;          // raw Q4_K nibble tiles (one super-block x 128 rows = 16 KB) in flight
+constexpr int WQ_BYTES = BM * 128;
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
 struct GemmArgs {
@@ -51,21 +54,21 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {   // non-blocking probe
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
 
 // Bounded wait.  Returns false if the CTA is aborting (this wait or another one ran out).
 __device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; i++)
-            if (mbar_try(bar, parity)) return true;
+        for (int i = 0; i < 256; i++)
+            if (mbar_test(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_CYCLES) {
             *abort_flag = 1;
@@ -74,6 +77,23 @@ __device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile 
             return false;
         }
     }
+}
+
+// Single-thread roles (MMA issue, TMA): a tight inline poll first, so the common case costs a
+// handful of instructions; the bounded slow path only when the barrier is late.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
+#pragma unroll 1
+    for (int i = 0; i < 2048; i++)
+        if (mbar_test(bar, parity)) return true;
+    return mbar_wait(bar, parity, abort_flag, status, code);
+}
+
+// Warp form: lane 0 waits, the result is broadcast, __syncwarp orders the other lanes behind it.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_spin(bar, parity, abort_flag, status, code) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint64_t *bar) {
@@ -121,11 +141,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---------------------------------------------------------------- dequantizers (one row, 64 weights)
-// All three write eight 16-byte chunks (8 halves each) of one 128-byte smem row; chunk j goes to
-// position j ^ (row & 7) (the 128-byte swizzle).  For the K-quants the k order inside every group
-// of four is (0, 2, 1, 3): that is the order the nibble pairs fall out of a 32-bit word, and the
-// activation tile is written in the same order (see gemm_prep_kernel), so the dot is unchanged.
+// ---------------------------------------------------------------- dequantizers (one row, 32 weights)
+// A stage row is 64 weights = 128 bytes of f16 = eight 16-byte chunks; chunk j goes to position
+// j ^ (row & 7) (the 128-byte swizzle).  Two threads share a row: `half` 0 writes chunks 0-3
+// (weights 0..31 of the 64-chunk), half 1 writes chunks 4-7.  For the K-quants the k order inside
+// every group of four is (0, 2, 1, 3): that is the order the nibble pairs fall out of a 32-bit
+// word, and the activation tile is written in the same order (see gemm_prep_kernel), so the dot
+// is unchanged.
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
@@ -133,127 +155,146 @@ __device__ __forceinline__ void store_chunk(unsigned char *row_base, int row, in
     *reinterpret_cast<uint4 *>(row_base + ((j ^ (row & 7)) << 4)) = make_uint4(a, b, c, d);
 }
 
-struct RowRegs { uint4 A, B, H; uint32_t e0, e1; };
-
-// Q4_K: A, B = the chunk's two 16-byte nibble pieces, H = header (d, dmin, 24-bit scale groups).
-__device__ __forceinline__ void dequant_q4k(const RowRegs &r, int c, unsigned char *row_base, int row) {
+// Q4_K: A, B = the chunk's two 16-byte nibble pieces (low nibbles = weights 0..31, high = 32..63),
+// H = header (d, dmin, 24-bit scale groups), c = chunk index inside the super-block.
+__device__ __forceinline__ void dequant_q4k_half(const uint4 &A, const uint4 &B, const uint4 &H, int c, int half,
+                                                 unsigned char *row_base, int row) {
     const int sh = (c * 24) & 31;
-    const uint32_t lo_w = (c < 2) ? r.H.y : (c == 2 ? r.H.z : r.H.w);
-    const uint32_t hi_w = (c < 2) ? r.H.z : r.H.w;
-    const uint32_t sg = __funnelshift_r(lo_w, hi_w, sh);
-    const float d = f16_bits_to_f32(r.H.x), dmin = f16_bits_to_f32(r.H.x >> 16);
-    const __half2 ds1 = __float2half2_rn(d * (float)(sg & 63u)), ds2 = __float2half2_rn(d * (float)((sg >> 6) & 63u));
-    const __half2 nm1 = __float2half2_rn(-(dmin * (float)((sg >> 12) & 63u))), nm2 = __float2half2_rn(-(dmin * (float)((sg >> 18) & 63u)));
+    const uint32_t lo_w = (c < 2) ? H.y : (c == 2 ? H.z : H.w);
+    const uint32_t hi_w = (c < 2) ? H.z : H.w;
+    const uint32_t sg = __funnelshift_r(lo_w, hi_w, sh) >> (6 * half);     // s at bits 0..5, m at bits 12..17
+    const float d = f16_bits_to_f32(H.x), dmin = f16_bits_to_f32(H.x >> 16);
+    const __half2 ds = __float2half2_rn(d * (float)(sg & 63u));
+    const __half2 nm = __float2half2_rn(-(dmin * (float)((sg >> 12) & 63u)));
     const __half2 k1024 = u32_as_h2(0x64006400u);
-    const uint32_t w[8] = {r.A.x, r.A.y, r.A.z, r.A.w, r.B.x, r.B.y, r.B.z, r.B.w};
-    uint32_t lo[16], hi[16];
+    const int nsh = 4 * half;
+    const uint32_t w[8] = {A.x >> nsh, A.y >> nsh, A.z >> nsh, A.w >> nsh, B.x >> nsh, B.y >> nsh, B.z >> nsh, B.w >> nsh};
+    uint32_t o[16];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const __half2 t0 = u32_as_h2((w[i] & 0x000f000fu) | 0x64006400u);          // weights (4i, 4i+2) of the low half
-        const __half2 t1 = u32_as_h2(((w[i] >> 8) & 0x000f000fu) | 0x64006400u);   // (4i+1, 4i+3)
-        const __half2 t2 = u32_as_h2(((w[i] >> 4) & 0x000f000fu) | 0x64006400u);   // high half: (4i, 4i+2)
-        const __half2 t3 = u32_as_h2(((w[i] >> 12) & 0x000f000fu) | 0x64006400u);  // (4i+1, 4i+3)
-        lo[2 * i] = h2_as_u32(__hfma2(__hsub2(t0, k1024), ds1, nm1));
-        lo[2 * i + 1] = h2_as_u32(__hfma2(__hsub2(t1, k1024), ds1, nm1));
-        hi[2 * i] = h2_as_u32(__hfma2(__hsub2(t2, k1024), ds2, nm2));
-        hi[2 * i + 1] = h2_as_u32(__hfma2(__hsub2(t3, k1024), ds2, nm2));
+        const __half2 t0 = u32_as_h2((w[i] & 0x000f000fu) | 0x64006400u);          // weights (4i, 4i+2)
+        const __half2 t1 = u32_as_h2(((w[i] >> 8) & 0x000f000fu) | 0x64006400u);   // weights (4i+1, 4i+3)
+        o[2 * i] = h2_as_u32(__hfma2(__hsub2(t0, k1024), ds, nm));
+        o[2 * i + 1] = h2_as_u32(__hfma2(__hsub2(t1, k1024), ds, nm));
     }
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        store_chunk(row_base, row, j, lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
-        store_chunk(row_base, row, 4 + j, hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
-    }
+    for (int j = 0; j < 4; j++) store_chunk(row_base, row, 4 * half + j, o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
 }
 
-// Q6_K: A, B = low nibbles (same arrangement as Q4_K), H = the chunk's 16 bytes of top bits,
-// e0 = four int8 sub-scales of the chunk, e1 = f16 d.  Value = d * sc * (q - 32).
-__device__ __forceinline__ void dequant_q6k(const RowRegs &r, unsigned char *row_base, int row) {
-    const float d = f16_bits_to_f32(r.e1);
-    __half2 dsc[4];
-#pragma unroll
-    for (int t = 0; t < 4; t++) dsc[t] = __float2half2_rn(d * (float)(int)(signed char)((r.e0 >> (8 * t)) & 0xffu));
+// Q6_K: A, B = low nibbles (same arrangement as Q4_K), Hh = the chunk's 16 bytes of top bits,
+// sc4 = the chunk's four int8 sub-scales, dbits = f16 d.  Value = d * sc * (q - 32).  half 0
+// handles the groups t = 0, 1 (low nibbles of A, B), half 1 the groups 2, 3 (high nibbles).
+__device__ __forceinline__ void dequant_q6k_half(const uint4 &A, const uint4 &B, const uint4 &Hh, uint32_t sc4, uint32_t dbits,
+                                                 int half, unsigned char *row_base, int row) {
+    const float d = f16_bits_to_f32(dbits);
+    const int t0i = 2 * half;
+    const __half2 dscA = __float2half2_rn(d * (float)(int)(signed char)((sc4 >> (8 * t0i)) & 0xffu));
+    const __half2 dscB = __float2half2_rn(d * (float)(int)(signed char)((sc4 >> (8 * t0i + 8)) & 0xffu));
     const __half2 k1056 = u32_as_h2(0x64206420u);   // 1024 + 32
-    const uint32_t Aw[4] = {r.A.x, r.A.y, r.A.z, r.A.w}, Bw[4] = {r.B.x, r.B.y, r.B.z, r.B.w};
-    const uint32_t Hw[4] = {r.H.x, r.H.y, r.H.z, r.H.w};
-    uint32_t g[4][8];   // g[t] = the 16 weights of group t as eight half2 words
+    const int nsh = 4 * half;
+    const uint32_t Aw[4] = {A.x >> nsh, A.y >> nsh, A.z >> nsh, A.w >> nsh};
+    const uint32_t Bw[4] = {B.x >> nsh, B.y >> nsh, B.z >> nsh, B.w >> nsh};
+    // top-bit fields: group t uses bits (2t, 2t+1) of every byte; bring them to bits 4, 5 of each 16-bit lane
+    const uint32_t Hw[4] = {Hh.x >> nsh, Hh.y >> nsh, Hh.z >> nsh, Hh.w >> nsh};   // half 1: fields 2, 3 move to 0, 1
+    uint32_t ga[8], gb[8];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         const uint32_t h = Hw[k];
-        // group 0: A low nibbles, top bits field 0; group 1: B low, field 1; group 2: A high, field 2; group 3: B high, field 3
-        const uint32_t n00 = (Aw[k] & 0x000f000fu) | ((h << 4) & 0x00300030u), n01 = ((Aw[k] >> 8) & 0x000f000fu) | ((h >> 4) & 0x00300030u);
-        const uint32_t n10 = (Bw[k] & 0x000f000fu) | ((h << 2) & 0x00300030u), n11 = ((Bw[k] >> 8) & 0x000f000fu) | ((h >> 6) & 0x00300030u);
-        const uint32_t n20 = ((Aw[k] >> 4) & 0x000f000fu) | (h & 0x00300030u), n21 = ((Aw[k] >> 12) & 0x000f000fu) | ((h >> 8) & 0x00300030u);
-        const uint32_t n30 = ((Bw[k] >> 4) & 0x000f000fu) | ((h >> 2) & 0x00300030u), n31 = ((Bw[k] >> 12) & 0x000f000fu) | ((h >> 10) & 0x00300030u);
-        g[0][2 * k] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n00 | 0x64006400u), k1056), dsc[0]));
-        g[0][2 * k + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n01 | 0x64006400u), k1056), dsc[0]));
-        g[1][2 * k] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n10 | 0x64006400u), k1056), dsc[1]));
-        g[1][2 * k + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n11 | 0x64006400u), k1056), dsc[1]));
-        g[2][2 * k] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n20 | 0x64006400u), k1056), dsc[2]));
-        g[2][2 * k + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n21 | 0x64006400u), k1056), dsc[2]));
-        g[3][2 * k] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n30 | 0x64006400u), k1056), dsc[3]));
-        g[3][2 * k + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(n31 | 0x64006400u), k1056), dsc[3]));
+        const uint32_t a0 = (Aw[k] & 0x000f000fu) | ((h << 4) & 0x00300030u), a1 = ((Aw[k] >> 8) & 0x000f000fu) | ((h >> 4) & 0x00300030u);
+        const uint32_t b0 = (Bw[k] & 0x000f000fu) | ((h << 2) & 0x00300030u), b1 = ((Bw[k] >> 8) & 0x000f000fu) | ((h >> 6) & 0x00300030u);
+        ga[2 * k] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(a0 | 0x64006400u), k1056), dscA));
+        ga[2 * k + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(a1 | 0x64006400u), k1056), dscA));
+        gb[2 * k] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(b0 | 0x64006400u), k1056), dscB));
+        gb[2 * k + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(b1 | 0x64006400u), k1056), dscB));
     }
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        store_chunk(row_base, row, 2 * t, g[t][0], g[t][1], g[t][2], g[t][3]);
-        store_chunk(row_base, row, 2 * t + 1, g[t][4], g[t][5], g[t][6], g[t][7]);
-    }
+    store_chunk(row_base, row, 4 * half, ga[0], ga[1], ga[2], ga[3]);
+    store_chunk(row_base, row, 4 * half + 1, ga[4], ga[5], ga[6], ga[7]);
+    store_chunk(row_base, row, 4 * half + 2, gb[0], gb[1], gb[2], gb[3]);
+    store_chunk(row_base, row, 4 * half + 3, gb[4], gb[5], gb[6], gb[7]);
 }
 
-// Q8_0: 64 int8 weights (four 16-byte pieces in A, B, H and the e-registers are not used: the
-// caller passes the pieces in q[]), two f16 block scales.  Natural k order.
-__device__ __forceinline__ void dequant_q80(const uint4 (&q)[4], uint32_t dpair, unsigned char *row_base, int row) {
+// Q8_0: one 32-weight block (two 16-byte pieces of int8, one f16 scale).  Natural k order.
+__device__ __forceinline__ void dequant_q80_half(const uint4 &q0, const uint4 &q1, uint32_t dbits, int half, unsigned char *row_base, int row) {
     const __half2 k1152 = u32_as_h2(0x64806480u);   // 1024 + 128
-    const __half2 d0 = __half2half2(__ushort_as_half((unsigned short)(dpair & 0xffffu)));
-    const __half2 d1 = __half2half2(__ushort_as_half((unsigned short)(dpair >> 16)));
+    const __half2 dd = __half2half2(__ushort_as_half((unsigned short)(dbits & 0xffffu)));
 #pragma unroll
-    for (int p = 0; p < 4; p++) {
-        const __half2 dd = p < 2 ? d0 : d1;
-        const uint32_t w[4] = {q[p].x ^ 0x80808080u, q[p].y ^ 0x80808080u, q[p].z ^ 0x80808080u, q[p].w ^ 0x80808080u};
+    for (int p = 0; p < 2; p++) {
+        const uint4 q = p == 0 ? q0 : q1;
+        const uint32_t w[4] = {q.x ^ 0x80808080u, q.y ^ 0x80808080u, q.z ^ 0x80808080u, q.w ^ 0x80808080u};
         uint32_t o[8];
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             o[2 * i] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w[i], 0x64646464u, 0x4140)), k1152), dd));
             o[2 * i + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w[i], 0x64646464u, 0x4342)), k1152), dd));
         }
-        store_chunk(row_base, row, 2 * p, o[0], o[1], o[2], o[3]);
-        store_chunk(row_base, row, 2 * p + 1, o[4], o[5], o[6], o[7]);
+        store_chunk(row_base, row, 4 * half + 2 * p, o[0], o[1], o[2], o[3]);
+        store_chunk(row_base, row, 4 * half + 2 * p + 1, o[4], o[5], o[6], o[7]);
     }
 }
 
 // ---------------------------------------------------------------- the GEMM kernel
+// Persistent: CTA b works through the tiles b, b + grid, b + 2 grid, ...  A tile is 128 weight
+// rows x BN tokens x one K range.  Roles (warp index):
+//   0-3   epilogue: drain one of the two TMEM accumulators to y while the next tile is computed
+//   4-11  dequantize: thread (row, half) turns 32 weights of one weight row into f16 per stage
+//   12    TMA of the f16 activation tiles          13  tcgen05.mma issue (owns TMEM)
+//   14    TMA of the raw Q4_K nibble tiles (one super-block x 128 rows per load)
+struct TileCoord { int n0, m0, sb_begin, sb_end; };
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tiles_n, int n_tiles_m, int ksplit, int nsb) {
+    const int nx = tile % n_tiles_n;
+    const int r = tile / n_tiles_n;
+    const int my = r % n_tiles_m, kz = r / n_tiles_m;
+    TileCoord t;
+    t.n0 = nx * BM;
+    t.m0 = my;      // multiplied by BN by the caller
+    t.sb_begin = (int)((long long)nsb * kz / ksplit);
+    t.sb_end = (int)((long long)nsb * (kz + 1) / ksplit);
+    return t;
+}
+
 template <int BN, int TYPE>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                   const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
     extern __shared__ unsigned char gemm_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)gemm_smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_STAGE_BYTES = BN * BK * 2;
+    constexpr bool STAGED_W = (TYPE == OJAS_B200_Q4_K);   // raw nibble tiles arrive by TMA, one super-block at a time
+    constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulators
     unsigned char *smem_a = smem;
     unsigned char *smem_b = smem + GEMM_STAGES * A_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_b + GEMM_STAGES * B_STAGE_BYTES);
-    uint64_t *full_a = bars, *full_b = bars + GEMM_STAGES, *empty = bars + 2 * GEMM_STAGES, *accum_bar = bars + 3 * GEMM_STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * GEMM_STAGES + 1);
+    unsigned char *smem_wq = smem_b + GEMM_STAGES * B_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_wq + (STAGED_W ? WQ_BUFS * WQ_BYTES : 0));
+    uint64_t *full_a = bars, *full_b = bars + GEMM_STAGES, *empty = bars + 2 * GEMM_STAGES;
+    uint64_t *wq_full = bars + 3 * GEMM_STAGES, *wq_empty = wq_full + WQ_BUFS;
+    uint64_t *tmem_full = wq_empty + WQ_BUFS, *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN;
     const int nsb = a.K >> 8;
-    const int kb_total = a.K / BK;
-    const int kb_begin = (int)((long long)kb_total * blockIdx.z / a.ksplit);
-    const int kb_end = (int)((long long)kb_total * (blockIdx.z + 1) / a.ksplit);
-    const int n_kb = kb_end - kb_begin;
+    const int n_tiles_n = (a.N + BM - 1) / BM, n_tiles_m = (a.M + BN - 1) / BN;
+    const int n_tiles = n_tiles_n * n_tiles_m * a.ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
-            mbar_init(&full_a[s], BM);
+            mbar_init(&full_a[s], 8);          // one arrival per dequantizing warp
             mbar_init(&full_b[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < WQ_BUFS; b++) {
+            mbar_init(&wq_full[b], 1);
+            mbar_init(&wq_empty[b], 8);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 4);      // one arrival per epilogue warp
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {   // TMEM allocation: BN columns (a power of two >= 32)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    if (warp == 13) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -262,121 +303,201 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        // ---------------- producers: thread t dequantizes weight row n0 + t, one 64-weight chunk per stage
-        const int t = threadIdx.x;
-        const int row = n0 + t;
-        const bool live = row < a.N;
-        const size_t rowblk = (size_t)(live ? row : 0) * nsb;
-        RowRegs cur, nxt;
-        uint4 q8[4], q8n[4];
-        auto fetch = [&](int kb, RowRegs &r, uint4 (&q)[4]) {
-            if (TYPE == OJAS_B200_Q8_0) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + ((size_t)(live ? row : 0) * a.K + (size_t)kb * BK) / 16;
-                q[0] = __ldg(src); q[1] = __ldg(src + 1); q[2] = __ldg(src + 2); q[3] = __ldg(src + 3);
-                r.e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p1) + ((size_t)(live ? row : 0) * (a.K / 32) + (size_t)kb * 2) / 2);
-            } else {
-                const int sb = kb >> 2, c = kb & 3;
-                const size_t blk = rowblk + sb;
-                r.A = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + c);
-                r.B = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + 4 + c);
-                if (TYPE == OJAS_B200_Q4_K) {
-                    r.H = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk);
-                } else {
-                    r.H = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk * 4 + c);
-                    r.e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + blk * 4 + c);
-                    r.e1 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + blk);
-                }
-            }
-        };
-        if (n_kb > 0) fetch(kb_begin, cur, q8);
-        for (int i = 0; i < n_kb; i++) {
-            const int kb = kb_begin + i, s = i % GEMM_STAGES;
-            const uint32_t ph = (uint32_t)(i / GEMM_STAGES) & 1u;
-            if (i + 1 < n_kb) fetch(kb + 1, nxt, q8n);
-            if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, a.status, 0x100u)) break;
-            unsigned char *row_base = smem_a + s * A_STAGE_BYTES + t * 128;
-            if (!live) {
-#pragma unroll
-                for (int j = 0; j < 8; j++) store_chunk(row_base, t, j, 0u, 0u, 0u, 0u);
-            } else if (TYPE == OJAS_B200_Q4_K) {
-                dequant_q4k(cur, kb & 3, row_base, t);
-            } else if (TYPE == OJAS_B200_Q6_K) {
-                dequant_q6k(cur, row_base, t);
-            } else {
-                dequant_q80(q8, cur.e0, row_base, t);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
-            mbar_arrive(&full_a[s]);
-            cur = nxt;
-#pragma unroll
-            for (int j = 0; j < 4; j++) q8[j] = q8n[j];
-        }
-        // ---------------- epilogue: warp w drains TMEM lanes 32w .. 32w+31 (weight rows n0 + 32w + lane)
-        if (n_kb > 0 && mbar_wait(accum_bar, 0u, abort_flag, a.status, 0x400u)) {
+        // ---------------- epilogue: warp e drains TMEM lanes 32e .. 32e+31 (weight rows n0 + 32e + lane)
+        int it = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
+            const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
+            const int m0 = tc.m0 * BN, acc = it & 1;
+            if (tc.sb_end <= tc.sb_begin) continue;                     // empty K range: nothing was accumulated
+            if (!mbar_wait_warp(&tmem_full[acc], (uint32_t)(it >> 1) & 1u, abort_flag, a.status, 0x400u)) break;
             tc_fence_after();
-            const int n = n0 + warp * 32 + lane;
+            const int n = tc.n0 + warp * 32 + lane;
+            float *ycol = a.y + n;
 #pragma unroll 1
             for (int col = 0; col < BN; col += 32) {
-                if (m0 + col >= a.M) break;            // uniform: the whole CTA shares m0
+                if (m0 + col >= a.M) break;                              // uniform: the whole CTA shares m0
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col, v);
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN + col), v);
                 if (n < a.N) {
+                    const int rows = a.M - (m0 + col) < 32 ? a.M - (m0 + col) : 32;
+                    float *yp = ycol + (size_t)(m0 + col) * a.N;
+                    if (a.ksplit > 1) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int m = m0 + col + j;
-                        if (m < a.M) {
-                            float *yp = a.y + (size_t)m * a.N + n;
-                            const float val = __uint_as_float(v[j]);
-                            if (a.ksplit > 1) atomicAdd(yp, val);
-                            else *yp = a.accum ? *yp + val : val;
-                        }
+                        for (int j = 0; j < 32; j++)
+                            if (j < rows) atomicAdd(yp + (size_t)j * a.N, __uint_as_float(v[j]));
+                    } else if (a.accum) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < rows) yp[(size_t)j * a.N] += __uint_as_float(v[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (j < rows) yp[(size_t)j * a.N] = __uint_as_float(v[j]);
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);                // this warp's quarter of the accumulator is free
         }
-    } else if (warp == 4) {
+    } else if (warp < 12) {
+        // ---------------- dequantizers: thread (row, half) writes 32 weights of weight row n0 + row per stage
+        const int t = threadIdx.x - 128;
+        const int row = t & 127, half = t >> 7;
+        uint32_t sc = 0;      // running stage counter (ring position and phase)
+        uint32_t wc = 0;      // running raw-tile counter
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+            const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
+            const int grow = tc.n0 + row;
+            const bool live = grow < a.N;
+            const size_t rowblk = (size_t)(live ? grow : 0) * nsb;
+            const int n_sb = tc.sb_end - tc.sb_begin;
+            if (STAGED_W) {
+                uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
+                if (n_sb > 0) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + tc.sb_begin);
+                for (int j = 0; ok && j < n_sb; j++, wc++) {
+                    const int wb = wc % WQ_BUFS;
+                    const uint4 H = hdr_next;
+                    if (j + 1 < n_sb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + tc.sb_begin + j + 1);
+                    if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
+                    const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++, sc++) {
+                        const int s = sc % GEMM_STAGES;
+                        const uint4 A = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));
+                        const uint4 B = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
+                        if (!mbar_wait_warp(&empty[s], ((sc / GEMM_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
+                        unsigned char *row_base = smem_a + s * A_STAGE_BYTES + row * 128;
+                        if (!live) {
+#pragma unroll
+                            for (int q = 0; q < 4; q++) store_chunk(row_base, row, 4 * half + q, 0u, 0u, 0u, 0u);
+                        } else {
+                            dequant_q4k_half(A, B, H, c, half, row_base, row);
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&full_a[s]);
+                    }
+                    __syncwarp();
+                    if (ok && lane == 0) mbar_arrive(&wq_empty[wb]);     // this warp is done with the raw tile
+                }
+            } else {
+                // weights straight from global memory, the next stage's loads in flight while this one is converted
+                uint4 cA, cB, cH, nA, nB, nH;
+                uint32_t ce0 = 0, ce1 = 0, ne0 = 0, ne1 = 0;
+                const size_t lrow = (size_t)(live ? grow : 0);
+                auto fetch = [&](int kb, uint4 &A, uint4 &B, uint4 &H, uint32_t &e0, uint32_t &e1) {
+                    if (TYPE == OJAS_B200_Q8_0) {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + (lrow * a.K + (size_t)kb * BK + (size_t)half * 32) / 16;
+                        A = __ldg(src); B = __ldg(src + 1);
+                        e0 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p1) + lrow * (a.K / 32) + (size_t)kb * 2 + half);
+                    } else {
+                        const int sb = kb >> 2, c = kb & 3;
+                        const size_t blk = rowblk + sb;
+                        A = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + c);
+                        B = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + 4 + c);
+                        H = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk * 4 + c);
+                        e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + blk * 4 + c);
+                        e1 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + blk);
+                    }
+                };
+                const int kb0 = tc.sb_begin * 4, n_kb = n_sb * 4;
+                if (n_kb > 0) fetch(kb0, cA, cB, cH, ce0, ce1);
+                for (int i = 0; ok && i < n_kb; i++, sc++) {
+                    const int s = sc % GEMM_STAGES;
+                    if (i + 1 < n_kb) fetch(kb0 + i + 1, nA, nB, nH, ne0, ne1);
+                    if (!mbar_wait_warp(&empty[s], ((sc / GEMM_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
+                    unsigned char *row_base = smem_a + s * A_STAGE_BYTES + row * 128;
+                    if (!live) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) store_chunk(row_base, row, 4 * half + q, 0u, 0u, 0u, 0u);
+                    } else if (TYPE == OJAS_B200_Q6_K) {
+                        dequant_q6k_half(cA, cB, cH, ce0, ce1, half, row_base, row);
+                    } else {
+                        dequant_q80_half(cA, cB, ce0, half, row_base, row);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full_a[s]);
+                    cA = nA; cB = nB; cH = nH; ce0 = ne0; ce1 = ne1;
+                }
+            }
+        }
+    } else if (warp == 12) {
         // ---------------- TMA: activation tile [BN tokens x 64 k] per stage
         if (lane == 0) {
-            for (int i = 0; i < n_kb; i++) {
-                const int s = i % GEMM_STAGES;
-                const uint32_t ph = (uint32_t)(i / GEMM_STAGES) & 1u;
-                if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag, a.status, 0x200u)) break;
-                mbar_arrive_expect_tx(&full_b[s], (uint32_t)B_STAGE_BYTES);
-                tma_load_2d(smem_b + s * B_STAGE_BYTES, &tmap_x, (kb_begin + i) * BK, m0, &full_b[s]);
+            uint32_t sc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
+                const int m0 = tc.m0 * BN;
+                for (int kb = tc.sb_begin * 4; kb < tc.sb_end * 4; kb++, sc++) {
+                    const int s = sc % GEMM_STAGES;
+                    if (!mbar_wait_spin(&empty[s], ((sc / GEMM_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full_b[s], (uint32_t)B_STAGE_BYTES);
+                    tma_load_2d(smem_b + s * B_STAGE_BYTES, &tmap_x, kb * BK, m0, &full_b[s]);
+                }
+            }
+        }
+    } else if (warp == 13) {
+        // ---------------- MMA issue: one thread; the loop body is kept as short as possible
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BN);
+            const uint64_t adesc0 = umma_desc(smem_u32(smem_a)), bdesc0 = umma_desc(smem_u32(smem_b));
+            uint32_t sc = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, it++) {
+                const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
+                const int n_kb = (tc.sb_end - tc.sb_begin) * 4, acc = it & 1;
+                if (n_kb <= 0) continue;
+                if (!mbar_wait_spin(&tmem_empty[acc], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag, a.status, 0x8000u)) break;
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+                for (int i = 0; i < n_kb; i++, sc++) {
+                    const uint32_t s = sc % GEMM_STAGES, ph = (sc / GEMM_STAGES) & 1u;
+                    if (!mbar_wait_spin(&full_a[s], ph, abort_flag, a.status, 0x800u)) { ok = false; break; }
+                    if (!mbar_wait_spin(&full_b[s], ph, abort_flag, a.status, 0x1000u)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = adesc0 + (uint64_t)(s * (A_STAGE_BYTES >> 4));
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(s * (B_STAGE_BYTES >> 4));
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)       // 32 bytes further along K per MMA (descriptor units of 16 bytes)
+                        umma_f16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);                 // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(&tmem_full[acc]);       // the accumulator is complete when all MMAs above are
             }
         }
     } else {
-        // ---------------- MMA issue: one thread
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(BN);
-            for (int i = 0; i < n_kb; i++) {
-                const int s = i % GEMM_STAGES;
-                const uint32_t ph = (uint32_t)(i / GEMM_STAGES) & 1u;
-                if (!mbar_wait(&full_a[s], ph, abort_flag, a.status, 0x800u)) break;
-                if (!mbar_wait(&full_b[s], ph, abort_flag, a.status, 0x1000u)) break;
-                tc_fence_after();
-                const uint64_t adesc = umma_desc(smem_u32(smem_a + s * A_STAGE_BYTES));
-                const uint64_t bdesc = umma_desc(smem_u32(smem_b + s * B_STAGE_BYTES));
-#pragma unroll
-                for (int k = 0; k < BK / 16; k++)       // 32 bytes further along K per MMA (descriptor units of 16 bytes)
-                    umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);                 // frees the stage once these MMAs have read it
-                if (i == n_kb - 1) umma_commit(accum_bar);
+        // ---------------- TMA: raw Q4_K nibble tile [128 rows x 128 bytes] per super-block
+        if (STAGED_W && lane == 0) {
+            uint32_t wc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
+                for (int sb = tc.sb_begin; sb < tc.sb_end; sb++, wc++) {
+                    const int wb = wc % WQ_BUFS;
+                    if (!mbar_wait_spin(&wq_empty[wb], ((wc / WQ_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000u)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
+                    tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, tc.n0, &wq_full[wb]);
+                }
             }
         }
     }
 
     // ---------------- teardown (every role arrives here, also after an abort)
-    if (*abort_flag && warp == 4 && lane == 0) {
+    if (*abort_flag && warp == 12 && lane == 0) {
         // give copies that are still in flight a bounded time to land before the CTA releases shared memory
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) { }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 13) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -429,26 +550,28 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-size_t gemm_smem_bytes(int bn) { return 1024 + (size_t)GEMM_STAGES * (A_STAGE_BYTES + bn * BK * 2) + 256; }
+size_t gemm_smem_bytes(int bn, bool staged_w) {
+    return 1024 + (size_t)GEMM_STAGES * (A_STAGE_BYTES + bn * BK * 2) + (staged_w ? WQ_BUFS * WQ_BYTES : 0) + 256;
+}
 
 template <int BN, int TYPE>
-int launch_gemm_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const GemmArgs &args, dim3 grid) {
+int launch_gemm_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const GemmArgs &args, dim3 grid) {
     auto kernel = gemm_tc_kernel<BN, TYPE>;
-    const size_t smem = gemm_smem_bytes(BN);
+    const size_t smem = gemm_smem_bytes(BN, TYPE == OJAS_B200_Q4_K);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    kernel<<<grid, GEMM_THREADS, smem, ctx->stream>>>(tmap, args);
+    kernel<<<grid, GEMM_THREADS, smem, ctx->stream>>>(tmap, tmap_w, args);
     OJAS_LAUNCH_CHECK(ctx, "gemm_tc");
     return 0;
 }
 
 template <int TYPE>
-int launch_gemm_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const GemmArgs &args, dim3 grid) {
+int launch_gemm_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const GemmArgs &args, dim3 grid) {
     switch (bn) {
-    case 32: return launch_gemm_bn<32, TYPE>(ctx, tmap, args, grid);
-    case 64: return launch_gemm_bn<64, TYPE>(ctx, tmap, args, grid);
-    case 128: return launch_gemm_bn<128, TYPE>(ctx, tmap, args, grid);
-    default: return launch_gemm_bn<256, TYPE>(ctx, tmap, args, grid);
+    case 32: return launch_gemm_bn<32, TYPE>(ctx, tmap, tmap_w, args, grid);
+    case 64: return launch_gemm_bn<64, TYPE>(ctx, tmap, tmap_w, args, grid);
+    case 128: return launch_gemm_bn<128, TYPE>(ctx, tmap, tmap_w, args, grid);
+    default: return launch_gemm_bn<256, TYPE>(ctx, tmap, tmap_w, args, grid);
     }
 }
 
@@ -467,7 +590,7 @@ static void gemm_plan(ojas_b200_ctx *ctx, size_t M, size_t N, size_t K, int &bn,
     } else {
         while (tiles * ksplit * 2 <= (size_t)ctx->sm_count && (K / BK) / (ksplit * 2) >= 8) ksplit *= 2;
     }
-    if ((size_t)ksplit > K / BK) ksplit = (int)(K / BK);
+    if ((size_t)ksplit > K / 256) ksplit = (int)(K / 256);   // K ranges are whole super-blocks
     if (ksplit < 1) ksplit = 1;
 }
 
@@ -507,6 +630,17 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
+    // raw nibble plane as bytes [N rows][K/2 bytes], box = one super-block (128 bytes) x 128 rows
+    CUtensorMap tmap_w = tmap;
+    if (type == OJAS_B200_Q4_K) {
+        const cuuint64_t wdims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)(K / 2)};
+        const cuuint32_t wbox[2] = {128, (cuuint32_t)BM};
+        cr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (weights) failed (%d)", (int)cr);
+    }
+
     GemmArgs args{};
     args.w = weight_planes(type, w, N, K);
     args.y = y;
@@ -517,8 +651,9 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     if (ksplit > 1 && !accum) {   // split-K adds into y: start from zero unless the caller accumulates
         OJAS_CUDA(ctx, cudaMemsetAsync(y, 0, M * N * sizeof(float), ctx->stream));
     }
-    const dim3 grid((unsigned)((N + BM - 1) / BM), (unsigned)((M + bn - 1) / bn), (unsigned)ksplit);
-    if (type == OJAS_B200_Q4_K) return launch_gemm_type<OJAS_B200_Q4_K>(ctx, bn, tmap, args, grid);
-    if (type == OJAS_B200_Q6_K) return launch_gemm_type<OJAS_B200_Q6_K>(ctx, bn, tmap, args, grid);
-    return launch_gemm_type<OJAS_B200_Q8_0>(ctx, bn, tmap, args, grid);
+    const size_t n_tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn) * (size_t)ksplit;
+    const dim3 grid((unsigned)(n_tiles < (size_t)ctx->sm_count ? n_tiles : (size_t)ctx->sm_count));
+    if (type == OJAS_B200_Q4_K) return launch_gemm_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, args, grid);
+    if (type == OJAS_B200_Q6_K) return launch_gemm_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, args, grid);
+    return launch_gemm_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, args, grid);
 }
