@@ -145,6 +145,36 @@ OJAS_B200_API size_t ojas_b200_gemm_workspace_bytes(size_t M, size_t K);
 OJAS_B200_API int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, float *y, size_t K,
                                  size_t N, size_t M, int accum, void *workspace, size_t workspace_bytes);
 
+/* ---- mixture of experts.
+ * Router: moe_topk (crates/ojas-cuda/src/kernels/moe.rs:45-70) and its batched form moe_topk_m
+ * (crates/ojas-metal/src/kernels/moe.rs:173-199): logits [M,E] -> idx u32 [M,KSEL], wgt f32 [M,KSEL];
+ * softmax, KSEL arg-max passes (ties -> lowest index), weights renormalised over the picks. */
+OJAS_B200_API int ojas_b200_moe_topk(ojas_b200_ctx *ctx, const float *logits, uint32_t *idx, float *wgt, size_t M, size_t E,
+                                     size_t KSEL);
+/* Expert FFN: replaces moe_gu_<fmt> / moe_down_<fmt> (crates/ojas-cuda/src/kernels/moe.rs:75-125; the
+ * Q4_K / Q6_K forms exist upstream only for Metal, crates/ojas-metal/src/kernels/moe.rs:513-529, 769-815)
+ * with the arithmetic of the CPU expert block (crates/ojas-cpu/src/cpu_glm.rs:551-582).
+ * h [M,d] f32; wg, wu: repacked stacked experts [E*ffn, d]; wd: [E*d, ffn]; idx, wgt as produced by
+ * ojas_b200_moe_topk; out [M,d] f32 = sum_j wgt_j * down_e(silu(gate_e h) * up_e h)  (accum != 0: +=).
+ * Assignments are grouped by expert so each expert's weights are read once.  `workspace`: caller-owned
+ * scratch of ojas_b200_moe_workspace_bytes(...) bytes, 256-byte aligned.  Expert types: Q4_K, Q6_K. */
+OJAS_B200_API size_t ojas_b200_moe_workspace_bytes(size_t M, size_t E, size_t KSEL, size_t d, size_t ffn);
+OJAS_B200_API int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t type_d, const float *h, const void *wg,
+                                    const void *wu, const void *wd, const uint32_t *idx, const float *wgt, size_t M, size_t E,
+                                    size_t KSEL, size_t d, size_t ffn, float *out, int accum, void *workspace,
+                                    size_t workspace_bytes);
+
+/* ---- tensor-parallel shard planning (host).  No counterpart in the reference, which is single-GPU
+ * (its only distributed code is a TCP pipeline for another backend, crates/ojas-swarm/src/lib.rs:12-40);
+ * the shard shapes follow the weight contract of crates/ojas-cuda/src/kernels/gemm_q.rs:1-4.
+ * Column-parallel: rank r owns weight rows [row0, row0+rows) and its outputs are all-gathered.
+ * Row-parallel: rank r owns K range [k0, k0+klen), whole 256-weight super-blocks, and the partial
+ * results are all-reduced.  The collectives themselves run in the caller (NCCL). */
+OJAS_B200_API int ojas_b200_tp_shard_rows(size_t N, int world, int rank, size_t *row0, size_t *rows);
+OJAS_B200_API int ojas_b200_tp_shard_k(size_t K, int world, int rank, size_t *k0, size_t *klen);
+OJAS_B200_API int ojas_b200_tp_slice_k_host(uint32_t ggml_type, const void *raw, size_t N, size_t K, size_t k0, size_t klen,
+                                            void *out);
+
 /* ---- name-based dispatch: the C form of KernelRuntime::dispatch / has_kernel
  * (crates/ojas-core/src/kernel.rs:68-83; argument marshalling crates/ojas-cuda/src/device.rs:
  * 391-415): buffers are (device pointer, byte offset) pairs in the kernel's positional order,

@@ -11,10 +11,17 @@ struct Q8kLane {
     float scale;    // the super-block scale (same in every lane)
 };
 
+__device__ __forceinline__ Q8kLane quant_q8k_values(const float (&v)[8]);
+
 __device__ __forceinline__ Q8kLane quant_q8k_warp(const float *seg /* 256 floats, 32-byte aligned */, int lane) {
     const float4 a = __ldg(reinterpret_cast<const float4 *>(seg) + lane * 2);
     const float4 b = __ldg(reinterpret_cast<const float4 *>(seg) + lane * 2 + 1);
-    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    return quant_q8k_values(v);
+}
+
+// The same for values already in registers (lane l holds values 8l .. 8l+7 of the super-block).
+__device__ __forceinline__ Q8kLane quant_q8k_values(const float (&v)[8]) {
     float m = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) m = fmaxf(m, fabsf(v[i]));

@@ -100,6 +100,23 @@ static inline WeightPlanes weight_planes(uint32_t type, const void *w, size_t N,
     return WeightPlanes{b + off[0], b + off[1], b + off[2], b + off[3]};
 }
 
+// Planes of rows [row0, ...) of a stacked tensor (experts stacked along N, as the engine keeps them:
+// crates/ojas-cuda/src/kernels/moe.rs:75-125 index `idx[j] * N + row`).
+static inline WeightPlanes weight_planes_at(uint32_t type, const void *w, size_t n_total, size_t K, size_t row0) {
+    WeightPlanes p = weight_planes(type, w, n_total, K);
+    const size_t nsb = K / 256;
+    switch (type) {
+    case OJAS_B200_Q4_K: p.p0 += row0 * nsb * 128; p.p1 += row0 * nsb * 16; break;
+    case OJAS_B200_Q6_K: p.p0 += row0 * nsb * 128; p.p1 += row0 * nsb * 64; p.p2 += row0 * nsb * 16; p.p3 += row0 * nsb * 2; break;
+    default: p.p0 += row0 * K; p.p1 += row0 * (K / 32) * 2; break;
+    }
+    return p;
+}
+
+int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &planes, const int8_t *q, const float *scales,
+                      const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
+                      size_t K, size_t N);
+
 // ---------------------------------------------------------------------------- device helpers
 #ifdef __CUDACC__
 __device__ __forceinline__ uint4 ldg_stream_u4(const void *p) {

@@ -67,6 +67,14 @@ GEMM_ENTRY(q4k, OJAS_B200_Q4_K)
 GEMM_ENTRY(q6k, OJAS_B200_Q6_K)
 GEMM_ENTRY(q8_0, OJAS_B200_Q8_0)
 
+// moe_topk: (lg, idx, wgt) (E, KSEL) — crates/ojas-cuda/src/kernels/moe.rs:45; moe_topk_m adds M.
+static int d_moe_topk(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
+    return ojas_b200_moe_topk(ctx, (const float *)b[0], (uint32_t *)b[1], (float *)b[2], 1, c[0], c[1]);
+}
+static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
+    return ojas_b200_moe_topk(ctx, (const float *)b[0], (uint32_t *)b[1], (float *)b[2], c[2], c[0], c[1]);
+}
+
 #define GEMV_TABLE(tag)                                      \
     {"gemv_nat_" #tag, 3, 2, gemv_##tag##_plain},            \
     {"gemv_nat_" #tag "_accum", 3, 2, gemv_##tag##_accum},   \
@@ -76,6 +84,7 @@ GEMM_ENTRY(q8_0, OJAS_B200_Q8_0)
 static const NameEntry kTable[] = {
     GEMV_TABLE(q4k), GEMV_TABLE(q6k), GEMV_TABLE(q80),
     {"quant_q8k", 4, 2, d_quant_q8k},
+    {"moe_topk", 3, 2, d_moe_topk}, {"moe_topk_m", 3, 3, d_moe_topk_m},
     {"gemm_mm_q4k", 4, 5, gemm_q4k}, {"gemm_mm_q6k", 4, 5, gemm_q6k}, {"gemm_mm_q8_0", 4, 5, gemm_q8_0},
 };
 static const int kTableLen = (int)(sizeof kTable / sizeof kTable[0]);

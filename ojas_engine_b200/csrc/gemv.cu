@@ -28,6 +28,11 @@ struct GemvArgs {
     float *y;                // [M, N]
     const float *bias;       // [N] or null
     int32_t *idots;          // dump of the integer sub-block dots (DUMP kernels)
+    // grouped (per-expert) launches: activation row m of the batch is source row row_index[m]
+    // (null: row m); the group's row count and first position come from device memory
+    const int *row_index;
+    const int *grp_count;
+    const int *grp_offset;
     int K, N, M, form;
     int S;                   // segments per row (work split); chosen by the host
     int depth;               // stages in each warp's cp.async ring (2..4); chosen by the host
@@ -116,6 +121,8 @@ __device__ __forceinline__ void finish_rows(const float *part, int R, int S, int
     }
 }
 
+__device__ __forceinline__ int src_row(const GemvArgs &a, int m) { return a.row_index ? __ldg(a.row_index + m) : m; }
+
 // Quantize (or copy pre-quantized) activations into shared memory.  BS16: keep per-16 sums
 // (Q6_K) instead of per-32 sums (Q4_K).
 template <int MT, bool PREQ, bool BS16>
@@ -152,7 +159,7 @@ __device__ __forceinline__ void stage_q8k(const GemvArgs &a, unsigned char *xq, 
             const int m = idx / units, rem = idx - m * units;
             const int sb = rem >> 4, un = rem & 15;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (m < a.M) v = __ldg(reinterpret_cast<const uint4 *>(a.q + (size_t)m * a.K) + rem);
+            if (m < a.M) v = __ldg(reinterpret_cast<const uint4 *>(a.q + (size_t)src_row(a, m) * a.K) + rem);
             reinterpret_cast<uint4 *>(xq + (size_t)m * Kpad)[xq_unit(sb, un >> 2, un & 3)] = v;
             if (BS16) {
                 int s = __dp4a((int)v.x, 0x01010101, 0);
@@ -164,12 +171,12 @@ __device__ __forceinline__ void stage_q8k(const GemvArgs &a, unsigned char *xq, 
         }
         for (int idx = threadIdx.x; idx < MT * nsb; idx += blockDim.x) {
             const int m = idx / nsb;
-            sx[idx] = (m < a.M) ? __ldg(a.scales + (size_t)m * nsb + (idx - m * nsb)) : 0.0f;
+            sx[idx] = (m < a.M) ? __ldg(a.scales + (size_t)src_row(a, m) * nsb + (idx - m * nsb)) : 0.0f;
         }
         if (!BS16) {
             for (int idx = threadIdx.x; idx < MT * nsb * NB; idx += blockDim.x) {
                 const int m = idx / (nsb * NB);
-                bs[idx] = (m < a.M) ? __ldg(a.bsums + (size_t)m * nsb * NB + (idx - m * nsb * NB)) : 0;
+                bs[idx] = (m < a.M) ? __ldg(a.bsums + (size_t)src_row(a, m) * nsb * NB + (idx - m * nsb * NB)) : 0;
             }
         }
     }
@@ -217,7 +224,7 @@ struct StepIter {
 };
 
 template <int MT, bool PREQ, bool DUMP>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_kernel(const GemvArgs a) {
+__device__ __forceinline__ void gemv_q4k_body(const GemvArgs &a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nsb = a.K >> 8, S = a.S;
     const int G = (nsb + 15) >> 4, GP = G / S;                // steps per row, per unit (host makes S divide G)
@@ -359,11 +366,30 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_kernel(const GemvArg
     if (!DUMP) finish_rows<MT>(part, R, S, r_begin, a);
 }
 
+template <int MT, bool PREQ, bool DUMP>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_kernel(const GemvArgs a) { gemv_q4k_body<MT, PREQ, DUMP>(a); }
+
+// Grouped form: the group's rows (count and first position read from device memory, so the launch
+// is capture-safe whatever the routing) are processed eight at a time; passes after the first
+// find the group's weights in L2.
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_grouped_kernel(const GemvArgs a) {
+    const int count = __ldg(a.grp_count), off = __ldg(a.grp_offset);
+    for (int mb = 0; mb < count; mb += 8) {
+        GemvArgs b = a;
+        b.M = count - mb < 8 ? count - mb : 8;
+        if (a.row_index) b.row_index = a.row_index + off + mb;
+        else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
+        b.y = a.y + (size_t)(off + mb) * a.N;
+        gemv_q4k_body<8, true, false>(b);
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------------------- Q6_K
 struct Q6kRegs { uint4 A, B, H; uint32_t sc; uint32_t d; };
 
 template <int MT, bool PREQ, bool DUMP>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_kernel(const GemvArgs a) {
+__device__ __forceinline__ void gemv_q6k_body(const GemvArgs &a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nsb = a.K >> 8, G8 = (nsb + 7) >> 3, S = a.S;
     const int Kpad = ((nsb + 1) >> 1) * 512;
@@ -454,6 +480,25 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_kernel(const GemvArg
         if (!DUMP && cu.g + 1 == cu.g_end) unit_done<MT>(acc, cu, S, part, a, lane);
     }
     if (!DUMP) finish_rows<MT>(part, R, S, r_begin, a);
+}
+
+template <int MT, bool PREQ, bool DUMP>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_kernel(const GemvArgs a) { gemv_q6k_body<MT, PREQ, DUMP>(a); }
+
+// Grouped form: the group's rows (count and first position read from device memory, so the launch
+// is capture-safe whatever the routing) are processed eight at a time; passes after the first
+// find the group's weights in L2.
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_grouped_kernel(const GemvArgs a) {
+    const int count = __ldg(a.grp_count), off = __ldg(a.grp_offset);
+    for (int mb = 0; mb < count; mb += 8) {
+        GemvArgs b = a;
+        b.M = count - mb < 8 ? count - mb : 8;
+        if (a.row_index) b.row_index = a.row_index + off + mb;
+        else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
+        b.y = a.y + (size_t)(off + mb) * a.N;
+        gemv_q6k_body<8, true, false>(b);
+        __syncthreads();
+    }
 }
 
 // ---------------------------------------------------------------------------- Q8_0
@@ -719,6 +764,30 @@ static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args,
         if (rc) return rc;
     }
     return 0;
+}
+
+// One grouped launch (see gemv_*_grouped_kernel): weights `planes` [N, K], activations pre-quantized.
+int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &planes, const int8_t *q, const float *scales,
+                      const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
+                      size_t K, size_t N) {
+    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q6_K)
+        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "grouped gemv: only Q4_K and Q6_K experts are supported");
+    GemvArgs a{};
+    a.q = q; a.scales = scales; a.bsums = bsums; a.w = planes; a.y = y;
+    a.row_index = row_index; a.grp_count = grp_count; a.grp_offset = grp_offset;
+    a.K = (int)K; a.N = (int)N; a.M = 8; a.form = OJAS_B200_PLAIN;
+    const int grid = ctx->sm_count < a.N ? ctx->sm_count : a.N;
+    const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
+    const size_t G8 = (K / 256 + 7) / 8;
+    a.S = type == OJAS_B200_Q4_K ? gemv_segments_q4k(rows_max, K / 256) : gemv_segments(rows_max, G8);
+    a.rows_base = a.N / grid;
+    a.rows_rem = a.N % grid;
+    a.depth = gemv_depth(ctx, type, 8, K, rows_max, a.S);
+    const size_t smem = gemv_smem_bytes(type, 8, K, rows_max, a.S, a.depth ? a.depth : 2);
+    if (a.depth == 0 || smem > (size_t)ctx->smem_optin)
+        return ojas_fail(ctx, OJAS_B200_E_LIMIT, "grouped gemv: K=%zu needs %zu bytes of shared memory, %d available", K, smem, ctx->smem_optin);
+    if (type == OJAS_B200_Q4_K) return launch_gemv(ctx, gemv_q4k_grouped_kernel, a, grid, smem, "gemv_q4k_grouped");
+    return launch_gemv(ctx, gemv_q6k_grouped_kernel, a, grid, smem, "gemv_q6k_grouped");
 }
 
 extern "C" int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t type, int form, const float *x, const void *w, float *y,

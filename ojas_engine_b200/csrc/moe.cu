@@ -1,0 +1,220 @@
+// Mixture-of-experts path: router top-k and the expert FFN, grouped by expert.
+//
+// Semantics follow the engine:
+//   router   moe_topk (crates/ojas-cuda/src/kernels/moe.rs:45-70; batched form moe_topk_m,
+//            crates/ojas-metal/src/kernels/moe.rs:173-199): softmax over E logits, KSEL arg-max
+//            passes (ties -> lowest index), weights renormalised over the picks;
+//   experts  act = silu(Wg_e h) * (Wu_e h), out += wgt * (Wd_e act), experts stacked [E*N, K]
+//            (moe_gu_* / moe_down_*, crates/ojas-cuda/src/kernels/moe.rs:75-125), with the
+//            arithmetic of the CPU path (crates/ojas-cpu/src/cpu_glm.rs:551-582): three matvec_kq
+//            per (token, pick), so h AND the SwiGLU output are quantized to Q8_K and every block
+//            dot is an exact integer dot.
+// Where the engine launches one GEMV per (token, pick) and re-reads an expert once per token routed
+// to it, this implementation sorts the assignments by expert and runs one grouped launch per
+// expert and projection: each expert's weights stream from HBM once.  Row counts live in device
+// memory, so the launch sequence does not depend on the routing (capture-safe).
+#include "act_quant.cuh"
+
+// ---------------------------------------------------------------- router
+// One warp per token.  E <= 1024.
+__global__ void __launch_bounds__(32) moe_topk_kernel(const float *lg, uint32_t *idx, float *wgt, int E, int ksel) {
+    __shared__ float pr[1024];
+    __shared__ float tw[32];
+    const int lane = threadIdx.x;
+    const float *l = lg + (size_t)blockIdx.x * E;
+    uint32_t *oi = idx + (size_t)blockIdx.x * ksel;
+    float *ow = wgt + (size_t)blockIdx.x * ksel;
+    float mx = -1e30f;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, l[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+    for (int e = lane; e < E; e += 32) { const float v = expf(l[e] - mx); pr[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    __syncwarp();
+    float wsum = 0.0f;
+    for (int j = 0; j < ksel; j++) {
+        float bv = -1.0f;
+        uint32_t bi = 0u;
+        for (int e = lane; e < E; e += 32) if (pr[e] > bv) { bv = pr[e]; bi = (uint32_t)e; }
+        float m2 = bv;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, o));
+        uint32_t cand = (bv == m2) ? bi : 0xffffffffu;     // ties resolve to the lowest index
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+        if (lane == 0) { oi[j] = cand; tw[j] = m2 / sum; pr[cand] = -1.0f; }
+        wsum += m2 / sum;
+        __syncwarp();
+    }
+    for (int j = lane; j < ksel; j += 32) ow[j] = tw[j] / wsum;
+}
+
+// ---------------------------------------------------------------- grouping
+// Sorts the A = M * KSEL assignments by expert (stable: by assignment id inside an expert).
+//   counts[e], offsets[e] : rows of expert e and where they start in the sorted order
+//   tok[p]                : token row of sorted position p (the gather index of the gate/up GEMVs)
+//   pos[a]                : sorted position of assignment a = t * KSEL + j (for the combine)
+// One CTA; warp w handles the experts w, w + 32, ...
+__global__ void __launch_bounds__(1024) moe_group_kernel(const uint32_t *idx, int A, int E, int ksel, int *counts, int *offsets,
+                                                          int *tok, int *pos) {
+    __shared__ int s_off[1025];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int e = warp; e < E; e += 32) {
+        int c = 0;
+        for (int a0 = 0; a0 < A; a0 += 32) {
+            const int a = a0 + lane;
+            const bool hit = a < A && (int)idx[a] == e;
+            c += __popc(__ballot_sync(0xffffffffu, hit));
+        }
+        if (lane == 0) counts[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; e++) { s_off[e] = run; offsets[e] = run; run += counts[e]; }
+        s_off[E] = run;
+    }
+    __syncthreads();
+    for (int e = warp; e < E; e += 32) {
+        int base = s_off[e];
+        for (int a0 = 0; a0 < A; a0 += 32) {
+            const int a = a0 + lane;
+            const bool hit = a < A && (int)idx[a] == e;
+            const unsigned mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int p = base + __popc(mask & ((1u << lane) - 1u));
+                tok[p] = a / ksel;
+                pos[a] = p;
+            }
+            base += __popc(mask);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- SwiGLU + requantization
+// act = silu(g) * u, then quant_q8k(act): one warp per (row, super-block).  silu(x) = x / (1 + exp(-x))
+// (crates/ojas-cpu/src/cpu_math.rs:486).
+__global__ void __launch_bounds__(256) moe_silu_quant_kernel(const float *g, const float *u, int8_t *q, float *scales, int32_t *bsums,
+                                                              long long n_sb) {
+    const int lane = threadIdx.x & 31;
+    const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (sb >= n_sb) return;
+    const float4 g0 = __ldg(reinterpret_cast<const float4 *>(g + sb * 256) + lane * 2), g1 = __ldg(reinterpret_cast<const float4 *>(g + sb * 256) + lane * 2 + 1);
+    const float4 u0 = __ldg(reinterpret_cast<const float4 *>(u + sb * 256) + lane * 2), u1 = __ldg(reinterpret_cast<const float4 *>(u + sb * 256) + lane * 2 + 1);
+    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __fmul_rn(__fdiv_rn(gv[i], 1.0f + expf(-gv[i])), uv[i]);
+    const Q8kLane ql = quant_q8k_values(v);
+    reinterpret_cast<uint2 *>(q + sb * 256)[lane] = ql.packed;
+    int s = ql.sum8;
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    if ((lane & 3) == 0) bsums[sb * 8 + (lane >> 2)] = s;
+    if (lane == 0) scales[sb] = ql.scale;
+}
+
+// ---------------------------------------------------------------- combine
+// out[t, :] (=, +=) sum_j wgt[t, j] * yd[pos[t*KSEL + j], :], picks added in order j = 0, 1, ... as the
+// CPU path does (crates/ojas-cpu/src/cpu_glm.rs:581).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float *yd, const int *pos, const float *wgt, float *out, int ksel, int d,
+                                                           int accum) {
+    const int t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= d) return;
+    float s = 0.0f;
+    for (int j = 0; j < ksel; j++) s = __fadd_rn(s, __fmul_rn(wgt[t * ksel + j], yd[(size_t)pos[t * ksel + j] * d + i]));
+    float *o = out + (size_t)t * d + i;
+    *o = accum ? *o + s : s;
+}
+
+// ---------------------------------------------------------------- host side
+extern "C" int ojas_b200_moe_topk(ojas_b200_ctx *ctx, const float *logits, uint32_t *idx, float *wgt, size_t M, size_t E, size_t KSEL) {
+    if (!ctx) return OJAS_B200_E_ARG;
+    if (!logits || !idx || !wgt) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_topk: null pointer");
+    if (E == 0 || E > 1024 || KSEL == 0 || KSEL > 32 || KSEL > E)
+        return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_topk: E=%zu (1..1024), KSEL=%zu (1..32, <= E)", E, KSEL);
+    if (M == 0) return 0;
+    if (M > 0x7fffffffu) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_topk: too many rows");
+    moe_topk_kernel<<<(unsigned)M, 32, 0, ctx->stream>>>(logits, idx, wgt, (int)E, (int)KSEL);
+    OJAS_LAUNCH_CHECK(ctx, "moe_topk");
+    return 0;
+}
+
+namespace {
+struct MoeWorkspace {
+    int8_t *xq; float *xs; int32_t *xb;          // quantized h            [M, d]
+    int *counts, *offsets, *tok, *pos;           // grouping
+    float *g, *u;                                // gate / up outputs      [A, ffn]
+    int8_t *aq; float *as; int32_t *ab;          // quantized SwiGLU       [A, ffn]
+    float *yd;                                   // down outputs           [A, d]
+    size_t bytes;
+};
+
+MoeWorkspace moe_carve(void *base, size_t M, size_t E, size_t KSEL, size_t d, size_t ffn) {
+    const size_t A = M * KSEL;
+    uint8_t *p = (uint8_t *)base;
+    size_t off = 0;
+    auto take = [&](size_t n) { uint8_t *r = p ? p + off : nullptr; off += align256(n); return r; };
+    MoeWorkspace w;
+    w.xq = (int8_t *)take(M * d); w.xs = (float *)take(M * (d / 256) * 4); w.xb = (int32_t *)take(M * (d / 32) * 4);
+    w.counts = (int *)take(E * 4); w.offsets = (int *)take(E * 4); w.tok = (int *)take(A * 4); w.pos = (int *)take(A * 4);
+    w.g = (float *)take(A * ffn * 4); w.u = (float *)take(A * ffn * 4);
+    w.aq = (int8_t *)take(A * ffn); w.as = (float *)take(A * (ffn / 256) * 4); w.ab = (int32_t *)take(A * (ffn / 32) * 4);
+    w.yd = (float *)take(A * d * 4);
+    w.bytes = off;
+    return w;
+}
+}  // namespace
+
+extern "C" size_t ojas_b200_moe_workspace_bytes(size_t M, size_t E, size_t KSEL, size_t d, size_t ffn) {
+    return moe_carve(nullptr, M, E, KSEL, d, ffn).bytes;
+}
+
+extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t type_d, const float *h, const void *wg, const void *wu,
+                                 const void *wd, const uint32_t *idx, const float *wgt, size_t M, size_t E, size_t KSEL, size_t d,
+                                 size_t ffn, float *out, int accum, void *workspace, size_t workspace_bytes) {
+    if (!ctx) return OJAS_B200_E_ARG;
+    if (!h || !wg || !wu || !wd || !idx || !wgt || !out || !workspace) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: null pointer");
+    if (d == 0 || ffn == 0 || d % 256 != 0 || ffn % 256 != 0)
+        return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: d=%zu and ffn=%zu must be positive multiples of 256", d, ffn);
+    if (E == 0 || E > 1024 || KSEL == 0 || KSEL > 32 || KSEL > E) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: E=%zu KSEL=%zu out of range", E, KSEL);
+    if (M == 0) return 0;
+    if (M * KSEL > 0x3fffffffu) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: too many assignments");
+    if ((type_gu != OJAS_B200_Q4_K && type_gu != OJAS_B200_Q6_K) || (type_d != OJAS_B200_Q4_K && type_d != OJAS_B200_Q6_K))
+        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "moe_ffn: expert weights must be Q4_K or Q6_K (got %u / %u)", type_gu, type_d);
+    if (workspace_bytes < ojas_b200_moe_workspace_bytes(M, E, KSEL, d, ffn))
+        return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: workspace of %zu bytes, %zu needed", workspace_bytes,
+                         ojas_b200_moe_workspace_bytes(M, E, KSEL, d, ffn));
+    if (((uintptr_t)workspace & 255) || ((uintptr_t)wg & 255) || ((uintptr_t)wu & 255) || ((uintptr_t)wd & 255) || ((uintptr_t)h & 15))
+        return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: misaligned pointer");
+    const size_t A = M * KSEL;
+    const MoeWorkspace w = moe_carve(workspace, M, E, KSEL, d, ffn);
+
+    int rc = ojas_b200_quant_q8k(ctx, h, M, d, w.xq, w.xs, w.xb);
+    if (rc) return rc;
+    moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
+    OJAS_LAUNCH_CHECK(ctx, "moe_group");
+    for (size_t e = 0; e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
+        rc = ojas_gemv_grouped(ctx, type_gu, weight_planes_at(type_gu, wg, E * ffn, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+                               w.counts + e, w.offsets + e, w.g, d, ffn);
+        if (rc) return rc;
+        rc = ojas_gemv_grouped(ctx, type_gu, weight_planes_at(type_gu, wu, E * ffn, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+                               w.counts + e, w.offsets + e, w.u, d, ffn);
+        if (rc) return rc;
+    }
+    const long long n_sb = (long long)A * (long long)(ffn / 256);
+    moe_silu_quant_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(w.g, w.u, w.aq, w.as, w.ab, n_sb);
+    OJAS_LAUNCH_CHECK(ctx, "moe_silu_quant");
+    for (size_t e = 0; e < E; e++) {   // down of expert e over its (contiguous, sorted) rows
+        rc = ojas_gemv_grouped(ctx, type_d, weight_planes_at(type_d, wd, E * d, ffn, e * d), w.aq, w.as, w.ab, nullptr,
+                               w.counts + e, w.offsets + e, w.yd, ffn, d);
+        if (rc) return rc;
+    }
+    const dim3 grid((unsigned)((d + 255) / 256), (unsigned)M);
+    moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0);
+    OJAS_LAUNCH_CHECK(ctx, "moe_combine");
+    return 0;
+}

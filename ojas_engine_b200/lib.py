@@ -51,6 +51,12 @@ SIGNATURES = {
     "ojas_b200_gemv_idots": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz]),
     "ojas_b200_gemm_workspace_bytes": (_sz, [_sz, _sz]),
     "ojas_b200_gemm": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i, _vp, _sz]),
+    "ojas_b200_moe_topk": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "ojas_b200_moe_workspace_bytes": (_sz, [_sz, _sz, _sz, _sz, _sz]),
+    "ojas_b200_moe_ffn": (_i, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
+    "ojas_b200_tp_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
+    "ojas_b200_tp_shard_k": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
+    "ojas_b200_tp_slice_k_host": (_i, [_u32, _vp, _sz, _sz, _sz, _sz, _vp]),
     "ojas_b200_has_kernel": (_i, [C.c_char_p]),
     "ojas_b200_kernel_count": (_i, []),
     "ojas_b200_kernel_name": (C.c_char_p, [_i]),

@@ -194,6 +194,31 @@ class B200Gpu:
         self._ck(self._l.ojas_b200_gemm(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
                                         w.k, w.n, m, 1 if accum else 0, C.c_void_p(workspace.ptr), workspace.nbytes))
 
+    def moe_topk(self, logits: Buf, idx: Buf, wgt: Buf, m: int, e: int, ksel: int) -> None:
+        self._ck(self._l.ojas_b200_moe_topk(self._ctx, C.c_void_p(logits.ptr), C.c_void_p(idx.ptr), C.c_void_p(wgt.ptr), m, e, ksel))
+
+    def moe_workspace_bytes(self, m: int, e: int, ksel: int, d: int, ffn: int) -> int:
+        return int(self._l.ojas_b200_moe_workspace_bytes(m, e, ksel, d, ffn))
+
+    def moe_ffn(self, wg: Lin, wu: Lin, wd: Lin, h: Buf, idx: Buf, wgt: Buf, out: Buf, m: int, e: int, ksel: int,
+                accum: bool = False, workspace: Buf | None = None) -> None:
+        """Expert FFN over stacked experts: wg, wu are [e*ffn, d], wd is [e*d, ffn]."""
+        ffn, d = wg.n // e, wg.k
+        assert wu.n == wg.n and wu.k == d and wd.n == e * d and wd.k == ffn
+        need = self.moe_workspace_bytes(m, e, ksel, d, ffn)
+        if workspace is None:
+            ws = getattr(self, "_moe_ws", None)
+            if ws is None or ws.nbytes < need:
+                if ws is not None:
+                    self.sync()
+                    self.free(ws)
+                ws = self._moe_ws = self.alloc_bytes(need)
+            workspace = ws
+        self._ck(self._l.ojas_b200_moe_ffn(self._ctx, wg.ggml_type, wd.ggml_type, C.c_void_p(h.ptr), C.c_void_p(wg.buf.ptr),
+                                           C.c_void_p(wu.buf.ptr), C.c_void_p(wd.buf.ptr), C.c_void_p(idx.ptr), C.c_void_p(wgt.ptr),
+                                           m, e, ksel, d, ffn, C.c_void_p(out.ptr), 1 if accum else 0, C.c_void_p(workspace.ptr),
+                                           workspace.nbytes))
+
     def gemv_idots(self, w: Lin, x: Buf, idots: Buf) -> None:
         self._ck(self._l.ojas_b200_gemv_idots(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(idots.ptr), w.k, w.n))
 

@@ -1,0 +1,112 @@
+"""MoE router and grouped expert FFN against the CPU oracle, through the C ABI (needs a B200)."""
+import numpy as np
+import pytest
+
+import oracle
+import ojas_engine_b200 as ob
+from ojas_engine_b200 import Q4_K, Q6_K
+
+from conftest import rel_l2
+from helpers import activations, gauss_weights
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3
+
+
+def _topk(gpu, logits, ksel):
+    m, e = logits.shape
+    lb = gpu.upload(logits)
+    ib, wb = gpu.alloc_bytes(m * ksel * 4), gpu.alloc(m * ksel)
+    gpu.moe_topk(lb, ib, wb, m, e, ksel)
+    idx = gpu.read(ib, np.uint32, m * ksel).reshape(m, ksel)
+    wgt = gpu.read(wb, np.float32, m * ksel).reshape(m, ksel)
+    for b in (lb, ib, wb):
+        gpu.free(b)
+    return idx, wgt
+
+
+def test_router_matches_reference_semantics(gpu):
+    rng = np.random.default_rng(0)
+    for m, e, ksel in [(64, 8, 2), (5, 64, 6), (3, 160, 8), (1, 8, 2), (7, 3, 3)]:
+        lg = rng.standard_normal((m, e), dtype=np.float32)
+        idx, wgt = _topk(gpu, lg, ksel)
+        widx, wwgt = oracle.moe_topk(lg, ksel)
+        assert np.array_equal(idx, widx)
+        assert np.allclose(wgt, wwgt, rtol=1e-5, atol=1e-7)
+        assert np.allclose(wgt.sum(1), 1.0, atol=1e-5)
+    ties = np.array([[0.5, 2.0, 2.0, -1.0, 2.0]], np.float32)  # ties resolve to the lowest index
+    idx, wgt = _topk(gpu, ties, 2)
+    assert list(idx[0]) == [1, 2] and np.allclose(wgt[0], [0.5, 0.5])
+
+
+def _moe_case(gpu, m, e, ksel, d, ffn, t_gu, t_d, idx=None, accum=False, seed=0, experts=None):
+    rng = np.random.default_rng(seed)
+    if experts is None:
+        wg = np.concatenate([gauss_weights(t_gu, ffn, d, seed + 10 * i) for i in range(e)])
+        wu = np.concatenate([gauss_weights(t_gu, ffn, d, seed + 10 * i + 1) for i in range(e)])
+        wd = np.concatenate([gauss_weights(t_d, d, ffn, seed + 10 * i + 2) for i in range(e)])
+    else:
+        wg, wu, wd = experts
+    h = activations(m, d, seed=seed + 5)
+    if idx is None:
+        lg = rng.standard_normal((m, e), dtype=np.float32)
+        idx, wgt = oracle.moe_topk(lg, ksel)
+    else:
+        idx = np.asarray(idx, np.uint32).reshape(m, ksel)
+        wgt = rng.random((m, ksel), dtype=np.float32)
+        wgt /= wgt.sum(1, keepdims=True)
+    want = oracle.moe_ffn(wg, wu, wd, t_gu, t_d, h, idx, wgt, d, ffn)
+    lg_, lu_, ld_ = gpu.load_weight(wg, t_gu, e * ffn, d), gpu.load_weight(wu, t_gu, e * ffn, d), gpu.load_weight(wd, t_d, e * d, ffn)
+    hb, ib, wb = gpu.upload(h), gpu.upload(idx), gpu.upload(wgt)
+    o0 = activations(m, d, seed=seed + 6) if accum else np.zeros((m, d), np.float32)
+    ob_ = gpu.upload(o0)
+    gpu.moe_ffn(lg_, lu_, ld_, hb, ib, wb, ob_, m, e, ksel, accum)
+    got = gpu.read(ob_, np.float32, m * d).reshape(m, d)
+    for b in (lg_.buf, lu_.buf, ld_.buf, hb, ib, wb, ob_):
+        gpu.free(b)
+    err = rel_l2(got, want + o0)
+    assert err < TOL, f"moe m={m} e={e} ksel={ksel} d={d} ffn={ffn}: rel L2 {err:.3e}"
+    return err
+
+
+@pytest.mark.parametrize("t_gu,t_d", [(Q4_K, Q4_K), (Q4_K, Q6_K), (Q6_K, Q6_K)])
+def test_expert_ffn_small(gpu, t_gu, t_d):
+    _moe_case(gpu, 9, 4, 2, 512, 768, t_gu, t_d)
+    _moe_case(gpu, 3, 5, 3, 256, 512, t_gu, t_d, accum=True, seed=3)
+
+
+def test_uneven_routing(gpu):
+    """All tokens on one expert (more rows than one eight-row pass), experts with no tokens at all."""
+    m, e, ksel = 21, 6, 2
+    idx = np.zeros((m, ksel), np.uint32)
+    idx[:, 0], idx[:, 1] = 4, 1                       # experts 0, 2, 3, 5 receive nothing
+    idx[::5, 1] = 5
+    _moe_case(gpu, m, e, ksel, 512, 512, Q4_K, Q4_K, idx=idx)
+    _moe_case(gpu, 1, 8, 2, 256, 256, Q4_K, Q4_K, idx=np.array([[7, 0]]))
+
+
+def test_config4_mixtral_shapes(gpu):
+    """8 experts, gate/up 14336 x 4096 and down 4096 x 14336 in Q4_K, 64 tokens, top-2 routing from N(0,1)
+    logits, softmax weights over the chosen two.  One expert's N(0, 0.02) weights are generated and
+    row-rotated for the other seven to keep set-up short."""
+    e, d, ffn, m, ksel = 8, 4096, 14336, 64, 2
+    g0 = gauss_weights(Q4_K, ffn, d, 1).reshape(ffn, -1)
+    u0 = gauss_weights(Q4_K, ffn, d, 2).reshape(ffn, -1)
+    d0 = gauss_weights(Q4_K, d, ffn, 3).reshape(d, -1)
+    wg = np.concatenate([np.roll(g0, 31 * i, axis=0).reshape(-1) for i in range(e)])
+    wu = np.concatenate([np.roll(u0, 17 * i, axis=0).reshape(-1) for i in range(e)])
+    wd = np.concatenate([np.roll(d0, 13 * i, axis=0).reshape(-1) for i in range(e)])
+    _moe_case(gpu, m, e, ksel, d, ffn, Q4_K, Q4_K, experts=(wg, wu, wd), seed=0)
+
+
+def test_moe_argument_errors(gpu):
+    w = gpu.load_weight(gauss_weights(ob.Q8_0, 2 * 256, 256), ob.Q8_0, 2 * 256, 256)
+    h, idx, wgt, out = gpu.upload(np.zeros((1, 256), np.float32)), gpu.upload(np.zeros(2, np.uint32)), gpu.upload(np.ones(2, np.float32)), gpu.alloc(256)
+    with pytest.raises(ob.OjasB200Error, match="Q4_K or Q6_K"):
+        gpu.moe_ffn(w, w, w, h, idx, wgt, out, 1, 2, 2)
+    lg = gpu.upload(np.zeros((1, 4), np.float32))
+    with pytest.raises(ob.OjasB200Error, match="KSEL"):
+        gpu.moe_topk(lg, idx, wgt, 1, 4, 5)
+    for b in (w.buf, h, idx, wgt, out, lg):
+        gpu.free(b)
