@@ -385,6 +385,13 @@ def run_case(args) -> None:
     import oracle
     if args.case.startswith("gemm:"):
         return run_gemm_case(args)
+    if args.case == "moe":
+        import ojas_engine_b200 as ob
+        hbm_peak, tc_peak, _ = measured_peaks()
+        gpu = ob.B200Gpu(0)
+        print(json.dumps(moe_case(gpu, ob, args.steps, args.warmup, hbm_peak, tc_peak)))
+        gpu.close()
+        return
     tag, n, k, m = args.case.split(":")
     n, k, m = int(n), int(k), int(m)
     t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
@@ -460,6 +467,42 @@ def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int
     tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
     return {"workload": f"{tag}_gemm_m{m}_n{n}_k{k}", "us_per_call": round(us, 2), "TFLOP/s": round(tf, 1),
             "frac_of_peak": round(tf / tc_peak, 4), "ksplit": ksplit or "auto"}
+
+
+def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float) -> dict:
+    """Mixtral-like expert FFN: 8 experts (gate/up 14336 x 4096, down 4096 x 14336, Q4_K), 64 tokens, top-2."""
+    import oracle
+    e, d, ffn, m, ksel = 8, 4096, 14336, 64, 2
+    rng = np.random.default_rng(0)
+    mk = lambda n, k: oracle.synth_blocks(ob.Q4_K, e * n * k // 256)
+    wg, wu, wd = (gpu.load_weight(mk(ffn, d), ob.Q4_K, e * ffn, d), gpu.load_weight(mk(ffn, d), ob.Q4_K, e * ffn, d),
+                  gpu.load_weight(mk(d, ffn), ob.Q4_K, e * d, ffn))
+    h = gpu.upload(rng.standard_normal((m, d), dtype=np.float32) * np.float32(1e-3))
+    lg = gpu.upload(rng.standard_normal((m, e), dtype=np.float32))
+    idx, wgt, out = gpu.alloc_bytes(m * ksel * 4), gpu.alloc(m * ksel), gpu.alloc(m * d)
+    work = gpu.alloc_bytes(gpu.moe_workspace_bytes(m, e, ksel, d, ffn))
+
+    def step():
+        gpu.moe_topk(lg, idx, wgt, m, e, ksel)
+        gpu.moe_ffn(wg, wu, wd, h, idx, wgt, out, m, e, ksel, workspace=work)
+
+    for _ in range(warmup):
+        step()
+    gpu.sync()
+    e0, e1 = gpu.event(), gpu.event()
+    gpu.record(e0)
+    for _ in range(steps):
+        step()
+    gpu.record(e1)
+    gpu.sync()
+    us = gpu.elapsed_ms(e0, e1) * 1e3 / steps
+    gguf = 3 * ob.raw_bytes(ob.Q4_K, e * ffn, d)
+    flops = 2.0 * m * ksel * 3 * ffn * d
+    for b in (wg.buf, wu.buf, wd.buf, h, lg, idx, wgt, out, work):
+        gpu.free(b)
+    return {"workload": "moe_q4k_e8_top2_m64_d4096_ffn14336", "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
+            "frac_of_hbm_peak": round(gguf / us / 1e3 / hbm_peak, 4), "TFLOP/s": round(flops / us / 1e6, 2),
+            "frac_of_tensor_peak": round(flops / us / 1e6 / tc_peak, 5), "expert_bytes": gguf}
 
 
 def run_gemm_case(args) -> None:

@@ -370,17 +370,18 @@ template <int MT, bool PREQ, bool DUMP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_kernel(const GemvArgs a) { gemv_q4k_body<MT, PREQ, DUMP>(a); }
 
 // Grouped form: the group's rows (count and first position read from device memory, so the launch
-// is capture-safe whatever the routing) are processed eight at a time; passes after the first
+// is capture-safe whatever the routing) are processed MT at a time (eight, or fewer when K is long and shared memory is short); passes after the first
 // find the group's weights in L2.
+template <int MT>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q4k_grouped_kernel(const GemvArgs a) {
     const int count = __ldg(a.grp_count), off = __ldg(a.grp_offset);
-    for (int mb = 0; mb < count; mb += 8) {
+    for (int mb = 0; mb < count; mb += MT) {
         GemvArgs b = a;
-        b.M = count - mb < 8 ? count - mb : 8;
+        b.M = count - mb < MT ? count - mb : MT;
         if (a.row_index) b.row_index = a.row_index + off + mb;
         else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
         b.y = a.y + (size_t)(off + mb) * a.N;
-        gemv_q4k_body<8, true, false>(b);
+        gemv_q4k_body<MT, true, false>(b);
         __syncthreads();
     }
 }
@@ -486,17 +487,18 @@ template <int MT, bool PREQ, bool DUMP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_kernel(const GemvArgs a) { gemv_q6k_body<MT, PREQ, DUMP>(a); }
 
 // Grouped form: the group's rows (count and first position read from device memory, so the launch
-// is capture-safe whatever the routing) are processed eight at a time; passes after the first
+// is capture-safe whatever the routing) are processed MT at a time (eight, or fewer when K is long and shared memory is short); passes after the first
 // find the group's weights in L2.
+template <int MT>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q6k_grouped_kernel(const GemvArgs a) {
     const int count = __ldg(a.grp_count), off = __ldg(a.grp_offset);
-    for (int mb = 0; mb < count; mb += 8) {
+    for (int mb = 0; mb < count; mb += MT) {
         GemvArgs b = a;
-        b.M = count - mb < 8 ? count - mb : 8;
+        b.M = count - mb < MT ? count - mb : MT;
         if (a.row_index) b.row_index = a.row_index + off + mb;
         else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
         b.y = a.y + (size_t)(off + mb) * a.N;
-        gemv_q6k_body<8, true, false>(b);
+        gemv_q6k_body<MT, true, false>(b);
         __syncthreads();
     }
 }
@@ -766,6 +768,8 @@ static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args,
     return 0;
 }
 
+static int gemv_max_mt(ojas_b200_ctx *ctx, uint32_t type, size_t K, size_t N);
+
 // One grouped launch (see gemv_*_grouped_kernel): weights `planes` [N, K], activations pre-quantized.
 int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &planes, const int8_t *q, const float *scales,
                       const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
@@ -775,19 +779,26 @@ int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &pla
     GemvArgs a{};
     a.q = q; a.scales = scales; a.bsums = bsums; a.w = planes; a.y = y;
     a.row_index = row_index; a.grp_count = grp_count; a.grp_offset = grp_offset;
-    a.K = (int)K; a.N = (int)N; a.M = 8; a.form = OJAS_B200_PLAIN;
+    a.K = (int)K; a.N = (int)N; a.form = OJAS_B200_PLAIN;
     const int grid = ctx->sm_count < a.N ? ctx->sm_count : a.N;
     const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
     const size_t G8 = (K / 256 + 7) / 8;
     a.S = type == OJAS_B200_Q4_K ? gemv_segments_q4k(rows_max, K / 256) : gemv_segments(rows_max, G8);
     a.rows_base = a.N / grid;
     a.rows_rem = a.N % grid;
-    a.depth = gemv_depth(ctx, type, 8, K, rows_max, a.S);
-    const size_t smem = gemv_smem_bytes(type, 8, K, rows_max, a.S, a.depth ? a.depth : 2);
-    if (a.depth == 0 || smem > (size_t)ctx->smem_optin)
-        return ojas_fail(ctx, OJAS_B200_E_LIMIT, "grouped gemv: K=%zu needs %zu bytes of shared memory, %d available", K, smem, ctx->smem_optin);
-    if (type == OJAS_B200_Q4_K) return launch_gemv(ctx, gemv_q4k_grouped_kernel, a, grid, smem, "gemv_q4k_grouped");
-    return launch_gemv(ctx, gemv_q6k_grouped_kernel, a, grid, smem, "gemv_q6k_grouped");
+    const int mt = gemv_max_mt(ctx, type, K, N);      // rows per pass: as many as fit beside the weight ring
+    if (mt < 2) return ojas_fail(ctx, OJAS_B200_E_LIMIT, "grouped gemv: K=%zu does not fit in shared memory", K);
+    a.M = mt;
+    a.depth = gemv_depth(ctx, type, mt, K, rows_max, a.S);
+    const size_t smem = gemv_smem_bytes(type, mt, K, rows_max, a.S, a.depth);
+    if (type == OJAS_B200_Q4_K) {
+        if (mt == 8) return launch_gemv(ctx, gemv_q4k_grouped_kernel<8>, a, grid, smem, "gemv_q4k_grouped");
+        if (mt == 4) return launch_gemv(ctx, gemv_q4k_grouped_kernel<4>, a, grid, smem, "gemv_q4k_grouped");
+        return launch_gemv(ctx, gemv_q4k_grouped_kernel<2>, a, grid, smem, "gemv_q4k_grouped");
+    }
+    if (mt == 8) return launch_gemv(ctx, gemv_q6k_grouped_kernel<8>, a, grid, smem, "gemv_q6k_grouped");
+    if (mt == 4) return launch_gemv(ctx, gemv_q6k_grouped_kernel<4>, a, grid, smem, "gemv_q6k_grouped");
+    return launch_gemv(ctx, gemv_q6k_grouped_kernel<2>, a, grid, smem, "gemv_q6k_grouped");
 }
 
 extern "C" int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t type, int form, const float *x, const void *w, float *y,
