@@ -145,6 +145,20 @@ OJAS_B200_API size_t ojas_b200_gemm_workspace_bytes(size_t M, size_t K);
 OJAS_B200_API int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, float *y, size_t K,
                                  size_t N, size_t M, int accum, void *workspace, size_t workspace_bytes);
 
+/* ---- prefill GEMM for callers that cannot provide scratch memory.  No counterpart in the reference.
+ * Meant for hosts that may not allocate device memory around the call: a plugin inside an engine
+ * whose allocator it cannot reach, or a serving loop that has frozen its memory map.  Same result as
+ * ojas_b200_gemm, but the f16 activation tiles go to an 8 MiB array built into the library (each GPU
+ * that loads the library holds it until the process exits), so M * K <= 4 194 304
+ * (ojas_b200_gemm_static_capacity() bytes / 2); larger shapes are refused with OJAS_B200_E_LIMIT.
+ * Calls nothing that allocates.  The first call on a device looks up the array's device address; make
+ * that call before any stream capture.  The array is shared by every call and keeps the last call's
+ * contents (each call overwrites the part it uses); two calls whose kernels overlap on the GPU (other
+ * streams, other contexts on the same device) race on it. */
+OJAS_B200_API size_t ojas_b200_gemm_static_capacity(void);
+OJAS_B200_API int ojas_b200_gemm_static(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, float *y, size_t K,
+                                        size_t N, size_t M, int accum);
+
 /* ---- mixture of experts.
  * Router: moe_topk (crates/ojas-cuda/src/kernels/moe.rs:45-70) and its batched form moe_topk_m
  * (crates/ojas-metal/src/kernels/moe.rs:173-199): logits [M,E] -> idx u32 [M,KSEL], wgt f32 [M,KSEL];

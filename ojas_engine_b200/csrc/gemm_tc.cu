@@ -657,3 +657,49 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     if (type == OJAS_B200_Q6_K) return launch_gemm_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, args, grid);
     return launch_gemm_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, args, grid);
 }
+
+// ---------------------------------------------------------------- GEMM without a caller workspace
+// Some hosts of this library cannot hand over scratch memory: a plugin loaded into an engine whose
+// allocator is closed to it, or a caller inside a region where cudaMalloc is not allowed (a
+// latency-critical serving loop that has frozen its memory map).  For them the f16 activation tiles
+// of the GEMM live in a fixed array inside the library image.  Every device that loads the library
+// carries the array until the process exits, so it is kept modest: 8 MiB, i.e. M * K <= 4 194 304.
+#define OJAS_B200_GEMM_STATIC_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_gemm_static_scratch[OJAS_B200_GEMM_STATIC_BYTES];
+
+// In host code the array's name is only a handle; the device address comes from the runtime, once per
+// device, with that device current.
+static void *gemm_static_scratch_ptr(ojas_b200_ctx *ctx, int *rc_out) {
+    static void *ptrs[64] = {nullptr};
+    *rc_out = 0;
+    if (ctx->device < 0 || ctx->device >= 64) { *rc_out = ojas_fail(ctx, OJAS_B200_E_LIMIT, "gemm_static: device index %d out of range", ctx->device); return nullptr; }
+    if (!ptrs[ctx->device]) {
+        int cur = -1;
+        cudaError_t e = cudaGetDevice(&cur);
+        if (e == cudaSuccess && cur != ctx->device) e = cudaSetDevice(ctx->device);
+        void *p = nullptr;
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&p, g_gemm_static_scratch);
+        if (e == cudaSuccess && cur >= 0 && cur != ctx->device) e = cudaSetDevice(cur);
+        if (e != cudaSuccess || !p) {
+            *rc_out = ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        ptrs[ctx->device] = p;
+    }
+    return ptrs[ctx->device];
+}
+
+extern "C" size_t ojas_b200_gemm_static_capacity(void) { return OJAS_B200_GEMM_STATIC_BYTES; }
+
+extern "C" int ojas_b200_gemm_static(ojas_b200_ctx *ctx, uint32_t type, const float *x, const void *w, float *y, size_t K, size_t N,
+                                     size_t M, int accum) {
+    if (!ctx) return OJAS_B200_E_ARG;
+    const size_t need = ojas_b200_gemm_workspace_bytes(M, K);
+    if (M == 0 || K == 0 || need > OJAS_B200_GEMM_STATIC_BYTES || need / 2 < M * K)
+        return ojas_fail(ctx, OJAS_B200_E_LIMIT, "gemm_static: M=%zu x K=%zu needs %zu bytes of scratch, the built-in array holds %u (M*K <= %u)",
+                         M, K, need, OJAS_B200_GEMM_STATIC_BYTES, OJAS_B200_GEMM_STATIC_BYTES / 2);
+    int rc = 0;
+    void *scratch = gemm_static_scratch_ptr(ctx, &rc);
+    if (!scratch) return rc;
+    return ojas_b200_gemm(ctx, type, x, w, y, K, N, M, accum, scratch, OJAS_B200_GEMM_STATIC_BYTES);
+}

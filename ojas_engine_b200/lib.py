@@ -51,6 +51,8 @@ SIGNATURES = {
     "ojas_b200_gemv_idots": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz]),
     "ojas_b200_gemm_workspace_bytes": (_sz, [_sz, _sz]),
     "ojas_b200_gemm": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i, _vp, _sz]),
+    "ojas_b200_gemm_static_capacity": (_sz, []),
+    "ojas_b200_gemm_static": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "ojas_b200_moe_topk": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_moe_workspace_bytes": (_sz, [_sz, _sz, _sz, _sz, _sz]),
     "ojas_b200_moe_ffn": (_i, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _i, _vp, _sz]),

@@ -219,6 +219,12 @@ class B200Gpu:
                                            m, e, ksel, d, ffn, C.c_void_p(out.ptr), 1 if accum else 0, C.c_void_p(workspace.ptr),
                                            workspace.nbytes))
 
+    def gemm_static(self, w: Lin, x: Buf, y: Buf, m: int, accum: bool = False) -> None:
+        """The GEMM for callers that cannot supply scratch: uses the library's built-in 8 MiB array
+        (m * k <= 4 194 304), allocates nothing."""
+        self._ck(self._l.ojas_b200_gemm_static(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
+                                               w.k, w.n, m, 1 if accum else 0))
+
     def gemv_idots(self, w: Lin, x: Buf, idots: Buf) -> None:
         self._ck(self._l.ojas_b200_gemv_idots(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(idots.ptr), w.k, w.n))
 
