@@ -357,6 +357,17 @@ def run_ours(args) -> None:
                         extras.append(extra_gemv(gpu, ob, t, n, k, m, hbm_peak, tag))
                     except Exception as exc:  # an extra must not take the headline down
                         extras.append({"workload": f"{tag}_gemv_n{n}_k{k}_m{m}", "error": str(exc)})
+            if not args.no_extras:
+                _, tc_peak, _ = measured_peaks()
+                for (m, n, k) in [(512, 4096, 4096), (512, 14336, 4096), (512, 4096, 14336), (2048, 14336, 4096), (128, 4096, 4096)]:
+                    try:
+                        extras.append(gemm_case(gpu, ob, "q4k", m, n, k, 10, 3, tc_peak))
+                    except Exception as exc:
+                        extras.append({"workload": f"q4k_gemm_m{m}_n{n}_k{k}", "error": str(exc)})
+                try:
+                    extras.append(moe_case(gpu, ob, 5, 2, hbm_peak, tc_peak))
+                except Exception as exc:
+                    extras.append({"workload": "moe", "error": str(exc)})
         traffic = profile_traffic()
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
