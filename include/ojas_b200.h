@@ -57,9 +57,10 @@ OJAS_B200_API void ojas_b200_destroy(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream);
 OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
 /* Options, also read once from the environment at creation the way the engine reads its OJAS_*
- * switches (crates/ojas-core/src/config.rs:1-22): "pdl" (OJAS_B200_PDL=1) launches the GEMVs with
- * programmatic dependent launch so that a kernel's weight prefetch overlaps the tail of the
- * kernel before it in the stream; "gemm_ksplit" (0 = automatic) forces the K split of the GEMM;
+ * switches (crates/ojas-core/src/config.rs:1-22): "pdl" (on by default; OJAS_B200_PDL=0 or
+ * set_option("pdl", 0) turns it off) launches the GEMVs with programmatic dependent launch so that a
+ * kernel's weight prefetch overlaps the tail of the GEMV before it in the stream (activations and y are
+ * only touched after the wait on the previous kernel; only GEMVs release their successor early); "gemm_ksplit" (0 = automatic) forces the K split of the GEMM;
  * "gemv_depth" is kept for compatibility and ignored by the two-stage GEMV ring. */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);

@@ -54,7 +54,7 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
     }
     memset(ctx->host_status, 0, 64);
     const char *pdl = getenv("OJAS_B200_PDL");   // read once at context creation, like the engine's OJAS_* switches
-    ctx->pdl = pdl && pdl[0] == '1';
+    ctx->pdl = !(pdl && pdl[0] == '0');          // on unless OJAS_B200_PDL=0
     *out = ctx;
     return 0;
 }

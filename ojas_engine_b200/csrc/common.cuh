@@ -20,7 +20,7 @@ struct ojas_b200_ctx {
     uint64_t launches = 0;
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
     int gemv_depth = 4;          // stages in each warp's cp.async ring (2..4)
-    int pdl = 0;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
+    int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
     unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
     unsigned int *dev_status = nullptr;  // the same word as the device sees it
     char err[512] = {0};

@@ -29,10 +29,22 @@ constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
 constexpr int GEMM_STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;
-constexpr int GEMM_THREADS = 480;   // 4 epilogue + 8 dequantizing warps, TMA (activations), MMA, TMA (raw weights)
+constexpr int DEQ_WARPS_PER_GROUP = 8;                 // two groups of eight dequantizing warps
+constexpr int WARP_TMA_X = 4 + 2 * DEQ_WARPS_PER_GROUP; // warp 20: TMA of the activation tiles
+constexpr int WARP_MMA0 = WARP_TMA_X + 1;              // warps 21-24: one MMA-issuing thread per ring slot
+constexpr int WARP_TMA_W = WARP_MMA0 + 4;              // warp 25: TMA of raw Q4_K tiles; owns the TMEM allocation
+constexpr int GEMM_THREADS = (WARP_TMA_W + 1) * 32;    // 832
 constexpr int WQ_BUFS = 2;          // raw Q4_K nibble tiles (one super-block x 128 rows = 16 KB) in flight
 constexpr int WQ_BYTES = BM * 128;
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
+
+#ifdef OJAS_GEMM_TRACE
+// Development aid (never compiled into the product library): clock64 stamps of CTA 0's roles.
+__device__ long long g_gemm_trace[12][1024];
+#define GEMM_TRACE(role, idx) do { if (blockIdx.x == 0 && (idx) < 1024) g_gemm_trace[role][idx] = clock64(); } while (0)
+#else
+#define GEMM_TRACE(role, idx) do { } while (0)
+#endif
 
 struct GemmArgs {
     WeightPlanes w;
@@ -79,12 +91,22 @@ __device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile 
     }
 }
 
-// Single-thread roles (MMA issue, TMA): a tight inline poll first, so the common case costs a
-// handful of instructions; the bounded slow path only when the barrier is late.
+// Up to 64 hardware-suspended waits (mbarrier.try_wait returns as soon as the phase completes, or after
+// a time limit of its own), entirely inside one asm block: the common case costs a few instructions.
+__device__ __forceinline__ bool mbar_try_loop(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .u32 n;\n\tmov.u32 n, 0;\n"
+                 "WAIT_LOOP:\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t@p bra WAIT_DONE;\n\t"
+                 "add.u32 n, n, 1;\n\tsetp.lt.u32 p, n, 64;\n\t@p bra WAIT_LOOP;\n"
+                 "WAIT_DONE:\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Single-thread roles (MMA issue, TMA) and warp leaders: the fast loop first, the clock-bounded slow
+// path only when the barrier is very late.
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
-#pragma unroll 1
-    for (int i = 0; i < 2048; i++)
-        if (mbar_test(bar, parity)) return true;
+    if (mbar_try_loop(bar, parity)) return true;
     return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
@@ -128,6 +150,15 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Zero 32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_zero32(uint32_t taddr) {
+    const uint32_t z = 0u;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, "
+                 "%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                 ::"r"(taddr), "r"(z) : "memory");
+}
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -234,11 +265,15 @@ __device__ __forceinline__ void dequant_q80_half(const uint4 &q0, const uint4 &q
 
 // ---------------------------------------------------------------- the GEMM kernel
 // Persistent: CTA b works through the tiles b, b + grid, b + 2 grid, ...  A tile is 128 weight
-// rows x BN tokens x one K range.  Roles (warp index):
-//   0-3   epilogue: drain one of the two TMEM accumulators to y while the next tile is computed
-//   4-11  dequantize: thread (row, half) turns 32 weights of one weight row into f16 per stage
-//   12    TMA of the f16 activation tiles          13  tcgen05.mma issue (owns TMEM)
-//   14    TMA of the raw Q4_K nibble tiles (one super-block x 128 rows per load)
+// rows x BN tokens x one K range.  A pipeline stage is one 64-weight chunk c of a super-block and
+// always lives in ring slot c; every stage barrier's phase is the parity of the super-block count.
+// Roles (warp index):
+//   0-3    epilogue: drain one of the two TMEM accumulators to y (and zero it) while the next tile runs
+//   4-19   dequantize: group 0 (warps 4-11) fills slots 0 and 2, group 1 (12-19) slots 1 and 3; thread
+//          (row, half) turns 32 weights of one weight row into f16 per stage
+//   20     TMA of the f16 activation tiles
+//   21-24  tcgen05.mma issue, one thread per ring slot
+//   25     TMA of the raw Q4_K nibble tiles (one super-block x 128 rows per load); owns TMEM
 struct TileCoord { int n0, m0, sb_begin, sb_end; };
 
 __device__ __forceinline__ TileCoord tile_coord(int tile, int n_tiles_n, int n_tiles_m, int ksplit, int nsb) {
@@ -265,8 +300,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     unsigned char *smem_b = smem + GEMM_STAGES * A_STAGE_BYTES;
     unsigned char *smem_wq = smem_b + GEMM_STAGES * B_STAGE_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_wq + (STAGED_W ? WQ_BUFS * WQ_BYTES : 0));
-    uint64_t *full_a = bars, *full_b = bars + GEMM_STAGES, *empty = bars + 2 * GEMM_STAGES;
-    uint64_t *wq_full = bars + 3 * GEMM_STAGES, *wq_empty = wq_full + WQ_BUFS;
+    uint64_t *full = bars, *empty = bars + GEMM_STAGES;
+    uint64_t *wq_full = bars + 2 * GEMM_STAGES, *wq_empty = wq_full + WQ_BUFS;
     uint64_t *tmem_full = wq_empty + WQ_BUFS, *tmem_empty = tmem_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -278,22 +313,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
-            mbar_init(&full_a[s], 8);          // one arrival per dequantizing warp
-            mbar_init(&full_b[s], 1);
+            mbar_init(&full[s], DEQ_WARPS_PER_GROUP + 1);   // the stage's dequantizing warps + the TMA thread (with its byte count)
             mbar_init(&empty[s], 1);
         }
         for (int b = 0; b < WQ_BUFS; b++) {
             mbar_init(&wq_full[b], 1);
-            mbar_init(&wq_empty[b], 8);
+            mbar_init(&wq_empty[b], 2 * DEQ_WARPS_PER_GROUP);
         }
         for (int b = 0; b < 2; b++) {
-            mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 4);      // one arrival per epilogue warp
+            mbar_init(&tmem_full[b], GEMM_STAGES);           // one commit per MMA-issuing thread
+            mbar_init(&tmem_empty[b], 4);                    // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 13) {
+    if (warp == WARP_TMA_W) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -301,6 +335,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Several threads issue MMAs into one accumulator, so no MMA can be "the first" (overwrite): every MMA
+    // accumulates and the accumulators start from zero (here, and again after each drain).
+    if (warp < 4) {
+        for (int col = 0; col < TMEM_COLS; col += 32) tmem_zero32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
 
     if (warp < 4) {
         // ---------------- epilogue: warp e drains TMEM lanes 32e .. 32e+31 (weight rows n0 + 32e + lane)
@@ -315,159 +358,169 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
             float *ycol = a.y + n;
 #pragma unroll 1
             for (int col = 0; col < BN; col += 32) {
-                if (m0 + col >= a.M) break;                              // uniform: the whole CTA shares m0
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN + col), v);
-                if (n < a.N) {
-                    const int rows = a.M - (m0 + col) < 32 ? a.M - (m0 + col) : 32;
-                    float *yp = ycol + (size_t)(m0 + col) * a.N;
-                    if (a.ksplit > 1) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * BN + col);
+                if (m0 + col < a.M) {                                    // uniform: the whole CTA shares m0
+                    uint32_t v[32];
+                    tmem_ld32(taddr, v);
+                    if (n < a.N) {
+                        const int rows = a.M - (m0 + col) < 32 ? a.M - (m0 + col) : 32;
+                        float *yp = ycol + (size_t)(m0 + col) * a.N;
+                        if (a.ksplit > 1) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (j < rows) atomicAdd(yp + (size_t)j * a.N, __uint_as_float(v[j]));
-                    } else if (a.accum) {
+                            for (int j = 0; j < 32; j++)
+                                if (j < rows) atomicAdd(yp + (size_t)j * a.N, __uint_as_float(v[j]));
+                        } else if (a.accum) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (j < rows) yp[(size_t)j * a.N] += __uint_as_float(v[j]);
-                    } else {
+                            for (int j = 0; j < 32; j++)
+                                if (j < rows) yp[(size_t)j * a.N] += __uint_as_float(v[j]);
+                        } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (j < rows) yp[(size_t)j * a.N] = __uint_as_float(v[j]);
+                            for (int j = 0; j < 32; j++)
+                                if (j < rows) yp[(size_t)j * a.N] = __uint_as_float(v[j]);
+                        }
                     }
                 }
+                tmem_zero32(taddr);                                      // ready for the next tile's accumulation
             }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);                // this warp's quarter of the accumulator is free
         }
-    } else if (warp < 12) {
-        // ---------------- dequantizers: thread (row, half) writes 32 weights of weight row n0 + row per stage
-        const int t = threadIdx.x - 128;
+    } else if (warp < WARP_TMA_X) {
+        // ---------------- dequantizers: two groups of eight warps; group g fills the stages c = g and g + 2 of every
+        // super-block, thread (row, half) of the group writes 32 weights of weight row n0 + row per stage
+        const int g = (warp - 4) / DEQ_WARPS_PER_GROUP;
+        const int t = threadIdx.x - 128 - g * (DEQ_WARPS_PER_GROUP * 32);
         const int row = t & 127, half = t >> 7;
-        uint32_t sc = 0;      // running stage counter (ring position and phase)
-        uint32_t wc = 0;      // running raw-tile counter
+        uint32_t wc = 0;      // running super-block counter: raw-tile ring position, and phase of every stage barrier
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
             const int grow = tc.n0 + row;
             const bool live = grow < a.N;
-            const size_t rowblk = (size_t)(live ? grow : 0) * nsb;
+            const size_t lrow = (size_t)(live ? grow : 0);
+            const size_t rowblk = lrow * nsb;
             const int n_sb = tc.sb_end - tc.sb_begin;
-            if (STAGED_W) {
-                uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
-                if (n_sb > 0) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + tc.sb_begin);
-                for (int j = 0; ok && j < n_sb; j++, wc++) {
-                    const int wb = wc % WQ_BUFS;
-                    const uint4 H = hdr_next;
+            uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
+            if (STAGED_W && n_sb > 0) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + tc.sb_begin);
+            // weights that come straight from global memory (Q6_K, Q8_0): the next stage's loads are in flight
+            // while this one is converted
+            uint4 cA = make_uint4(0u, 0u, 0u, 0u), cB = cA, cH = cA, nA = cA, nB = cA, nH = cA;
+            uint32_t ce0 = 0, ce1 = 0, ne0 = 0, ne1 = 0;
+            auto fetch = [&](int sb, int c, uint4 &A, uint4 &B, uint4 &H, uint32_t &e0, uint32_t &e1) {
+                if (TYPE == OJAS_B200_Q8_0) {
+                    const size_t k0 = (size_t)sb * 256 + (size_t)c * BK + (size_t)half * 32;
+                    const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + (lrow * a.K + k0) / 16;
+                    A = __ldg(src); B = __ldg(src + 1);
+                    e0 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p1) + lrow * (a.K / 32) + k0 / 32);
+                } else if (TYPE == OJAS_B200_Q6_K) {
+                    const size_t blk = rowblk + sb;
+                    A = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + c);
+                    B = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + 4 + c);
+                    H = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk * 4 + c);
+                    e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + blk * 4 + c);
+                    e1 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + blk);
+                }
+            };
+            if (!STAGED_W && n_sb > 0) fetch(tc.sb_begin, g, cA, cB, cH, ce0, ce1);
+            for (int j = 0; ok && j < n_sb; j++, wc++) {
+                const int wb = wc % WQ_BUFS;
+                const uint32_t ph = wc & 1u;
+                const uint4 H = hdr_next;
+                const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
+                if (STAGED_W) {
                     if (j + 1 < n_sb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + tc.sb_begin + j + 1);
                     if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
-                    const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
-#pragma unroll 1
-                    for (int c = 0; c < 4; c++, sc++) {
-                        const int s = sc % GEMM_STAGES;
-                        const uint4 A = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));
-                        const uint4 B = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
-                        if (!mbar_wait_warp(&empty[s], ((sc / GEMM_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
-                        unsigned char *row_base = smem_a + s * A_STAGE_BYTES + row * 128;
-                        if (!live) {
-#pragma unroll
-                            for (int q = 0; q < 4; q++) store_chunk(row_base, row, 4 * half + q, 0u, 0u, 0u, 0u);
-                        } else {
-                            dequant_q4k_half(A, B, H, c, half, row_base, row);
-                        }
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&full_a[s]);
-                    }
-                    __syncwarp();
-                    if (ok && lane == 0) mbar_arrive(&wq_empty[wb]);     // this warp is done with the raw tile
                 }
-            } else {
-                // weights straight from global memory, the next stage's loads in flight while this one is converted
-                uint4 cA, cB, cH, nA, nB, nH;
-                uint32_t ce0 = 0, ce1 = 0, ne0 = 0, ne1 = 0;
-                const size_t lrow = (size_t)(live ? grow : 0);
-                auto fetch = [&](int kb, uint4 &A, uint4 &B, uint4 &H, uint32_t &e0, uint32_t &e1) {
-                    if (TYPE == OJAS_B200_Q8_0) {
-                        const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + (lrow * a.K + (size_t)kb * BK + (size_t)half * 32) / 16;
-                        A = __ldg(src); B = __ldg(src + 1);
-                        e0 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p1) + lrow * (a.K / 32) + (size_t)kb * 2 + half);
-                    } else {
-                        const int sb = kb >> 2, c = kb & 3;
-                        const size_t blk = rowblk + sb;
-                        A = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + c);
-                        B = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + 4 + c);
-                        H = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk * 4 + c);
-                        e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + blk * 4 + c);
-                        e1 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + blk);
+#pragma unroll
+                for (int cc = 0; cc < 2; cc++) {
+                    const int c = g + 2 * cc;                            // this group's stage (ring slot = chunk index)
+                    if (STAGED_W) {
+                        cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));
+                        cB = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
+                    } else {                                             // prefetch this group's next stage
+                        const bool last = (cc == 1) && (j + 1 >= n_sb);
+                        if (!last) fetch(tc.sb_begin + j + (cc == 1 ? 1 : 0), cc == 1 ? g : g + 2, nA, nB, nH, ne0, ne1);
                     }
-                };
-                const int kb0 = tc.sb_begin * 4, n_kb = n_sb * 4;
-                if (n_kb > 0) fetch(kb0, cA, cB, cH, ce0, ce1);
-                for (int i = 0; ok && i < n_kb; i++, sc++) {
-                    const int s = sc % GEMM_STAGES;
-                    if (i + 1 < n_kb) fetch(kb0 + i + 1, nA, nB, nH, ne0, ne1);
-                    if (!mbar_wait_warp(&empty[s], ((sc / GEMM_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
-                    unsigned char *row_base = smem_a + s * A_STAGE_BYTES + row * 128;
+                    if (threadIdx.x == 128) GEMM_TRACE(7, wc * 4 + c);
+                    if (!mbar_wait_warp(&empty[c], ph ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
+                    if (threadIdx.x == 128) GEMM_TRACE(0, wc * 4 + c);
+                    unsigned char *row_base = smem_a + c * A_STAGE_BYTES + row * 128;
                     if (!live) {
 #pragma unroll
                         for (int q = 0; q < 4; q++) store_chunk(row_base, row, 4 * half + q, 0u, 0u, 0u, 0u);
+                    } else if (TYPE == OJAS_B200_Q4_K) {
+                        dequant_q4k_half(cA, cB, H, c, half, row_base, row);
                     } else if (TYPE == OJAS_B200_Q6_K) {
                         dequant_q6k_half(cA, cB, cH, ce0, ce1, half, row_base, row);
                     } else {
                         dequant_q80_half(cA, cB, ce0, half, row_base, row);
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    if (threadIdx.x == 128) GEMM_TRACE(1, wc * 4 + c);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&full_a[s]);
-                    cA = nA; cB = nB; cH = nH; ce0 = ne0; ce1 = ne1;
+                    if (lane == 0) mbar_arrive(&full[c]);
+                    if (threadIdx.x == 128) GEMM_TRACE(2, wc * 4 + c);
+                    if (!STAGED_W) { cA = nA; cB = nB; cH = nH; ce0 = ne0; ce1 = ne1; }
+                }
+                if (STAGED_W) {
+                    __syncwarp();
+                    if (ok && lane == 0) mbar_arrive(&wq_empty[wb]);     // this warp is done with the raw tile
                 }
             }
         }
-    } else if (warp == 12) {
+    } else if (warp == WARP_TMA_X) {
         // ---------------- TMA: activation tile [BN tokens x 64 k] per stage
         if (lane == 0) {
-            uint32_t sc = 0;
+            uint32_t wc = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
                 const int m0 = tc.m0 * BN;
-                for (int kb = tc.sb_begin * 4; kb < tc.sb_end * 4; kb++, sc++) {
-                    const int s = sc % GEMM_STAGES;
-                    if (!mbar_wait_spin(&empty[s], ((sc / GEMM_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&full_b[s], (uint32_t)B_STAGE_BYTES);
-                    tma_load_2d(smem_b + s * B_STAGE_BYTES, &tmap_x, kb * BK, m0, &full_b[s]);
+                for (int sb = tc.sb_begin; ok && sb < tc.sb_end; sb++, wc++) {
+                    const uint32_t ph = wc & 1u;
+#pragma unroll
+                    for (int c = 0; c < GEMM_STAGES; c++) {
+                        if (!mbar_wait_spin(&empty[c], ph ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
+                        GEMM_TRACE(3, wc * 4 + c);
+                        mbar_arrive_expect_tx(&full[c], (uint32_t)B_STAGE_BYTES);
+                        tma_load_2d(smem_b + c * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, m0, &full[c]);
+                    }
                 }
             }
         }
-    } else if (warp == 13) {
-        // ---------------- MMA issue: one thread; the loop body is kept as short as possible
+    } else if (warp < WARP_TMA_W) {
+        // ---------------- MMA issue: four threads, thread c owns ring slot c (chunk c of every super-block).  A
+        // single issuing thread spends about a thousand cycles per stage on its own barrier probes and issue
+        // latency; four of them keep the tensor pipe fed.  Every MMA accumulates (see the zeroing above).
         if (lane == 0) {
+            const int c = warp - WARP_MMA0;
             constexpr uint32_t idesc = umma_idesc(BN);
-            const uint64_t adesc0 = umma_desc(smem_u32(smem_a)), bdesc0 = umma_desc(smem_u32(smem_b));
-            uint32_t sc = 0;
+            const uint64_t adesc = umma_desc(smem_u32(smem_a + c * A_STAGE_BYTES));
+            const uint64_t bdesc = umma_desc(smem_u32(smem_b + c * B_STAGE_BYTES));
+            uint32_t wc = 0;
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, it++) {
                 const TileCoord tc = tile_coord(tile, n_tiles_n, n_tiles_m, a.ksplit, nsb);
-                const int n_kb = (tc.sb_end - tc.sb_begin) * 4, acc = it & 1;
-                if (n_kb <= 0) continue;
+                const int n_sb = tc.sb_end - tc.sb_begin, acc = it & 1;
+                if (n_sb <= 0) continue;
                 if (!mbar_wait_spin(&tmem_empty[acc], ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag, a.status, 0x8000u)) break;
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
-                for (int i = 0; i < n_kb; i++, sc++) {
-                    const uint32_t s = sc % GEMM_STAGES, ph = (sc / GEMM_STAGES) & 1u;
-                    if (!mbar_wait_spin(&full_a[s], ph, abort_flag, a.status, 0x800u)) { ok = false; break; }
-                    if (!mbar_wait_spin(&full_b[s], ph, abort_flag, a.status, 0x1000u)) { ok = false; break; }
+                for (int j = 0; j < n_sb; j++, wc++) {
+                    if (!mbar_wait_spin(&full[c], wc & 1u, abort_flag, a.status, 0x800u)) { ok = false; break; }
+                    if (c == 0) GEMM_TRACE(4, wc * 4);
                     tc_fence_after();
-                    const uint64_t adesc = adesc0 + (uint64_t)(s * (A_STAGE_BYTES >> 4));
-                    const uint64_t bdesc = bdesc0 + (uint64_t)(s * (B_STAGE_BYTES >> 4));
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++)       // 32 bytes further along K per MMA (descriptor units of 16 bytes)
-                        umma_f16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&empty[s]);                 // frees the stage once these MMAs have read it
+                        umma_f16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
+                    if (c == 0) GEMM_TRACE(9, wc * 4);
+                    umma_commit(&empty[c]);                 // frees the stage once these MMAs have read it
+                    if (c == 0) GEMM_TRACE(6, wc * 4);
                 }
-                if (ok) umma_commit(&tmem_full[acc]);       // the accumulator is complete when all MMAs above are
+                if (ok) umma_commit(&tmem_full[acc]);       // this thread's share of the accumulator is complete
             }
         }
     } else {
@@ -488,14 +541,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     }
 
     // ---------------- teardown (every role arrives here, also after an abort)
-    if (*abort_flag && warp == 12 && lane == 0) {
+    if (*abort_flag && warp == WARP_TMA_X && lane == 0) {
         // give copies that are still in flight a bounded time to land before the CTA releases shared memory
         const long long t0 = clock64();
         while (clock64() - t0 < 2000000LL) { }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == WARP_TMA_W) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
@@ -703,3 +756,9 @@ extern "C" int ojas_b200_gemm_static(ojas_b200_ctx *ctx, uint32_t type, const fl
     if (!scratch) return rc;
     return ojas_b200_gemm(ctx, type, x, w, y, K, N, M, accum, scratch, OJAS_B200_GEMM_STATIC_BYTES);
 }
+
+#ifdef OJAS_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_trace(long long *host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(long long) * 12 * 1024);
+}
+#endif

@@ -89,7 +89,7 @@ def load() -> C.CDLL:
             raise RuntimeError(
                 f"{_build.LIB} is missing and nvcc is not available to build it; "
                 "run `python -m ojas_engine_b200._build` on a machine with the CUDA toolkit")
-    lib = C.CDLL(_build.LIB)
+    lib = C.CDLL(os.environ.get("OJAS_B200_LIBRARY") or _build.LIB)   # the override is for development builds
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError here = header and library out of step
         fn.restype, fn.argtypes = res, args
