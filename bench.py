@@ -396,6 +396,8 @@ def run_case(args) -> None:
     import oracle
     if args.case.startswith("gemm:"):
         return run_gemm_case(args)
+    if args.case == "tp70b":
+        return run_tp70b(args)
     if args.case == "moe":
         import ojas_engine_b200 as ob
         hbm_peak, tc_peak, _ = measured_peaks()
@@ -514,6 +516,92 @@ def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float) 
     return {"workload": "moe_q4k_e8_top2_m64_d4096_ffn14336", "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
             "frac_of_hbm_peak": round(gguf / us / 1e3 / hbm_peak, 4), "TFLOP/s": round(flops / us / 1e6, 2),
             "frac_of_tensor_peak": round(flops / us / 1e6 / tc_peak, 5), "expert_bytes": gguf}
+
+
+def run_tp70b(args) -> None:
+    """`--case tp70b` under torchrun (or alone for 1 GPU): the Llama-70B-shaped projections row-sharded over
+    the ranks.  QKV 10240x8192, gate/up 28672x8192 (Q4_K) are column-parallel (all-gather of the output
+    shards); O 8192x8192 (Q4_K) and down 8192x28672 (Q6_K) are row-parallel (K split on super-block
+    boundaries, all-reduce of the partial outputs).  M = 1 (GEMV) and M = 512 (tensor-core GEMM).  Each call =
+    local matmul + its NCCL collective on the same stream; time = CUDA events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    import oracle
+    import ojas_engine_b200 as ob
+    from ojas_engine_b200 import tp
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    gpu = ob.B200Gpu(local)
+    stream = torch.cuda.ExternalStream(gpu.stream, device=f"cuda:{local}")
+    dev = f"cuda:{local}"
+    projections = [("qkv", ob.Q4_K, 10240, 8192, "col"), ("o", ob.Q4_K, 8192, 8192, "row"),
+                   ("gate_up", ob.Q4_K, 28672, 8192, "col"), ("down", ob.Q6_K, 8192, 28672, "row")]
+    rows_out = []
+    for name, t, n, k, mode in projections:
+        if mode == "col":
+            _, n_loc = tp.shard_rows(n, world, rank)
+            k_loc = k
+        else:
+            n_loc = n
+            _, k_loc = tp.shard_k(k, world, rank)
+        raw = oracle.synth_blocks(t, n_loc * k_loc // 256)
+        w = gpu.load_weight(raw, t, n_loc, k_loc)
+        for m in (1, 512):
+            x = (torch.randn(m, k_loc, device=dev, dtype=torch.float32) * 1e-2).contiguous()
+            y = torch.empty(m, n_loc, device=dev, dtype=torch.float32)
+            full = torch.empty(world * m, n_loc, device=dev, dtype=torch.float32) if (mode == "col" and world > 1) else None
+            xb, yb = ob.Buf(x.data_ptr(), x.numel() * 4), ob.Buf(y.data_ptr(), y.numel() * 4)
+            work = gpu.alloc_bytes(gpu.gemm_workspace_bytes(m, k_loc)) if m > ob.GEMV_MAX_M else None
+            torch.cuda.synchronize()
+
+            def call():
+                if m <= ob.GEMV_MAX_M:
+                    gpu.gemv(w, xb, yb, m)
+                else:
+                    gpu.gemm(w, xb, yb, m, workspace=work)
+                if world > 1:
+                    with torch.cuda.stream(stream):
+                        if mode == "col":
+                            dist.all_gather_into_tensor(full, y)
+                        else:
+                            dist.all_reduce(y, op=dist.ReduceOp.SUM)
+
+            def timed(fn, steps):
+                for _ in range(3):
+                    fn()
+                gpu.sync(); torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                e0, e1 = gpu.event(), gpu.event()
+                gpu.record(e0)
+                for _ in range(steps):
+                    fn()
+                gpu.record(e1)
+                gpu.sync(); torch.cuda.synchronize()
+                tt = torch.tensor([gpu.elapsed_ms(e0, e1) * 1e3 / steps], dtype=torch.float64, device=dev)
+                if world > 1:
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                return float(tt.item())
+
+            us = timed(call, args.steps)
+            gguf_total = ob.raw_bytes(t, n, k)
+            row = {"proj": name, "type": {ob.Q4_K: "q4k", ob.Q6_K: "q6k"}[t], "N": n, "K": k, "mode": mode, "M": m,
+                   "us_per_call": round(us, 2)}
+            if m == 1:
+                row["aggregate_GB/s"] = round(gguf_total / us / 1e3, 1)
+            else:
+                row["aggregate_TFLOP/s"] = round(2.0 * m * n * k / us / 1e6, 1)
+            rows_out.append(row)
+            if work is not None:
+                gpu.free(work)
+        gpu.free(w.buf)
+    if rank == 0:
+        print(json.dumps({"case": "tp70b", "n_gpus": world, "steps": args.steps, "rows": rows_out}))
+    if world > 1:
+        dist.destroy_process_group()
+    gpu.close()
 
 
 def run_gemm_case(args) -> None:

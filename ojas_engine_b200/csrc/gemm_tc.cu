@@ -38,14 +38,6 @@ constexpr int WQ_BUFS = 2;          // raw Q4_K nibble tiles (one super-block x 
 constexpr int WQ_BYTES = BM * 128;
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
-#ifdef OJAS_GEMM_TRACE
-// Development aid (never compiled into the product library): clock64 stamps of CTA 0's roles.
-__device__ long long g_gemm_trace[12][1024];
-#define GEMM_TRACE(role, idx) do { if (blockIdx.x == 0 && (idx) < 1024) g_gemm_trace[role][idx] = clock64(); } while (0)
-#else
-#define GEMM_TRACE(role, idx) do { } while (0)
-#endif
-
 struct GemmArgs {
     WeightPlanes w;
     float *y;
@@ -443,9 +435,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                         const bool last = (cc == 1) && (j + 1 >= n_sb);
                         if (!last) fetch(tc.sb_begin + j + (cc == 1 ? 1 : 0), cc == 1 ? g : g + 2, nA, nB, nH, ne0, ne1);
                     }
-                    if (threadIdx.x == 128) GEMM_TRACE(7, wc * 4 + c);
                     if (!mbar_wait_warp(&empty[c], ph ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
-                    if (threadIdx.x == 128) GEMM_TRACE(0, wc * 4 + c);
                     unsigned char *row_base = smem_a + c * A_STAGE_BYTES + row * 128;
                     if (!live) {
 #pragma unroll
@@ -457,11 +447,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                     } else {
                         dequant_q80_half(cA, cB, ce0, half, row_base, row);
                     }
-                    if (threadIdx.x == 128) GEMM_TRACE(1, wc * 4 + c);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the MMA
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&full[c]);
-                    if (threadIdx.x == 128) GEMM_TRACE(2, wc * 4 + c);
                     if (!STAGED_W) { cA = nA; cB = nB; cH = nH; ce0 = ne0; ce1 = ne1; }
                 }
                 if (STAGED_W) {
@@ -483,7 +471,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 #pragma unroll
                     for (int c = 0; c < GEMM_STAGES; c++) {
                         if (!mbar_wait_spin(&empty[c], ph ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
-                        GEMM_TRACE(3, wc * 4 + c);
                         mbar_arrive_expect_tx(&full[c], (uint32_t)B_STAGE_BYTES);
                         tma_load_2d(smem_b + c * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, m0, &full[c]);
                     }
@@ -511,14 +498,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
                 for (int j = 0; j < n_sb; j++, wc++) {
                     if (!mbar_wait_spin(&full[c], wc & 1u, abort_flag, a.status, 0x800u)) { ok = false; break; }
-                    if (c == 0) GEMM_TRACE(4, wc * 4);
                     tc_fence_after();
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++)       // 32 bytes further along K per MMA (descriptor units of 16 bytes)
                         umma_f16(tmem_acc, adesc + 2 * k, bdesc + 2 * k, idesc, 1u);
-                    if (c == 0) GEMM_TRACE(9, wc * 4);
                     umma_commit(&empty[c]);                 // frees the stage once these MMAs have read it
-                    if (c == 0) GEMM_TRACE(6, wc * 4);
                 }
                 if (ok) umma_commit(&tmem_full[acc]);       // this thread's share of the accumulator is complete
             }
@@ -757,8 +741,3 @@ extern "C" int ojas_b200_gemm_static(ojas_b200_ctx *ctx, uint32_t type, const fl
     return ojas_b200_gemm(ctx, type, x, w, y, K, N, M, accum, scratch, OJAS_B200_GEMM_STATIC_BYTES);
 }
 
-#ifdef OJAS_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_trace(long long *host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_gemm_trace, sizeof(long long) * 12 * 1024);
-}
-#endif
