@@ -80,6 +80,11 @@ extern "C" int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream) {
 extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value) {
     if (!ctx || !key) return OJAS_B200_E_ARG;
     if (!strcmp(key, "pdl")) { ctx->pdl = value != 0; return 0; }
+    if (!strcmp(key, "gemv_mma")) {
+        if (value < 0 || value > 2) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_mma must be 0, 1 or 2");
+        ctx->gemv_mma = value;
+        return 0;
+    }
     if (!strcmp(key, "gemm_ksplit")) {
         if (value < 0 || value > 64) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemm_ksplit must be 0..64");
         ctx->gemm_ksplit = value;

@@ -598,6 +598,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_q80_kernel(const GemvArg
     finish_rows<MT>(part, R, S, r_begin, a);
 }
 
+#include "gemv_mma.cuh"
+
 // ---------------------------------------------------------------------------- quant_q8k
 __global__ void __launch_bounds__(256) quant_q8k_kernel(const float *x, int8_t *q, float *scales, int32_t *bsums,
                                                          long long n_sb) {
@@ -680,6 +682,76 @@ static int launch_gemv(ojas_b200_ctx *ctx, KernelT kernel, const GemvArgs &args,
     return 0;
 }
 
+// ---- integer tensor-core path (Q4_K, M <= 8): configuration and launch
+static int mma_segments(size_t rows_max, size_t nsb, int warps) {
+    const size_t tiles = (rows_max + 15) / 16;
+    size_t best = 1;
+    for (size_t s = 1; s <= nsb; s++) {
+        if (nsb % s) continue;
+        best = s;
+        if (tiles * s >= (size_t)warps) break;
+    }
+    return (int)best;
+}
+
+static size_t mma_smem_bytes(int warps, size_t M, size_t K, size_t rows_max, int S) {
+    const size_t nsb = K / 256, tiles = (rows_max + 15) / 16;
+    return (size_t)warps * 2 * MMA_STAGE_BYTES + ((M * (K + MMA_XPAD) + 15) & ~(size_t)15) + (size_t)sx_floats((int)M, (int)nsb) * 4 +
+           M * nsb * 8 * 4 + (S > 1 ? tiles * S * 128 * 4 : 0) + 16;
+}
+
+// Fills S / row partition and picks 32 or 16 warps by shared-memory fit; returns 0 if neither fits.
+static int mma_plan(ojas_b200_ctx *ctx, GemvArgs &a, int &grid, size_t &smem) {
+    grid = ctx->sm_count < a.N ? ctx->sm_count : a.N;
+    const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
+    a.rows_base = a.N / grid;
+    a.rows_rem = a.N % grid;
+    for (int warps = 32; warps >= 16; warps >>= 1) {
+        a.S = mma_segments(rows_max, (size_t)a.K / 256, warps);
+        smem = mma_smem_bytes(warps, (size_t)a.M, (size_t)a.K, rows_max, a.S);
+        if (smem <= (size_t)ctx->smem_optin) return warps;
+    }
+    return 0;
+}
+
+template <typename KernelT>
+static int launch_gemv_threads(ojas_b200_ctx *ctx, KernelT kernel, const GemvArgs &args, int grid, int threads, size_t smem, const char *name) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "%s: shared memory %zu: %s", name, smem, cudaGetErrorString(e));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (ctx->pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
+    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch %s: %s", name, cudaGetErrorString(e));
+    ctx->launches++;
+    return 0;
+}
+
+// Returns 1 if the shape does not fit this path (the caller falls back to the dp4a kernels), else a status.
+static int gemv_mma_launch(ojas_b200_ctx *ctx, bool preq, GemvArgs a) {
+    int grid;
+    size_t smem;
+    const int warps = mma_plan(ctx, a, grid, smem);
+    if (warps == 0) return 1;
+    if (warps == 32) {
+        if (preq) return launch_gemv_threads(ctx, gemv_q4k_mma_kernel<32, true>, a, grid, 1024, smem, "gemv_q4k_mma_q8k");
+        return launch_gemv_threads(ctx, gemv_q4k_mma_kernel<32, false>, a, grid, 1024, smem, "gemv_q4k_mma");
+    }
+    if (preq) return launch_gemv_threads(ctx, gemv_q4k_mma_kernel<16, true>, a, grid, 512, smem, "gemv_q4k_mma_q8k");
+    return launch_gemv_threads(ctx, gemv_q4k_mma_kernel<16, false>, a, grid, 512, smem, "gemv_q4k_mma");
+}
+
 static int pick_mt(size_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
 
 // One launch over at most 8 activation rows.
@@ -753,6 +825,13 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
 }
 
 static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args, size_t M) {
+    // Q4_K batches of 2..8 rows (or every Q4_K call when the option says so) take the integer tensor-core path
+    if (type == OJAS_B200_Q4_K && ctx->gemv_mma != 0 && (M >= 2 || ctx->gemv_mma == 2)) {
+        GemvArgs b = args;
+        b.M = (int)M;
+        const int rc = gemv_mma_launch(ctx, preq, b);
+        if (rc != 1) return rc;
+    }
     const int cap = gemv_max_mt(ctx, type, (size_t)args.K, (size_t)args.N);
     if (cap == 0) return ojas_fail(ctx, OJAS_B200_E_LIMIT, "gemv: K=%d does not fit in shared memory", args.K);
     const size_t nsb = (size_t)args.K / 256;
@@ -786,6 +865,15 @@ int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &pla
     a.S = type == OJAS_B200_Q4_K ? gemv_segments_q4k(rows_max, K / 256) : gemv_segments(rows_max, G8);
     a.rows_base = a.N / grid;
     a.rows_rem = a.N % grid;
+    if (type == OJAS_B200_Q4_K && ctx->gemv_mma != 0) {
+        GemvArgs b = a;
+        b.M = 8;
+        int g2;
+        size_t smem2;
+        const int warps = mma_plan(ctx, b, g2, smem2);
+        if (warps == 32) return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<32>, b, g2, 1024, smem2, "gemv_q4k_mma_grouped");
+        if (warps == 16) return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<16>, b, g2, 512, smem2, "gemv_q4k_mma_grouped");
+    }
     const int mt = gemv_max_mt(ctx, type, K, N);      // rows per pass: as many as fit beside the weight ring
     if (mt < 2) return ojas_fail(ctx, OJAS_B200_E_LIMIT, "grouped gemv: K=%zu does not fit in shared memory", K);
     a.M = mt;

@@ -155,6 +155,22 @@ def test_prequantized_activations_match(gpu, tag):
         gpu.free(buf)
 
 
+@pytest.mark.parametrize("mode", [0, 2])
+def test_q4k_both_inner_loops(gpu, mode):
+    """Q4_K has two inner loops (dp4a per lane; integer tensor-core MMA for small batches).  Force each one
+    over every batch size and check it against the oracle and against the other one."""
+    gpu.set_option("gemv_mma", mode)
+    try:
+        for n, k, m in [(4096, 4096, 1), (300, 2304, 3), (1000, 4352, 8), (17, 256, 5), (14336, 4096, 8), (4096, 14336, 4)]:
+            for source in ("gauss", "synth"):
+                err = _gemv_case(gpu, "q4k", n, k, m, source, seed=m)
+                assert err < 1e-5
+        _gemv_case(gpu, "q4k", 777, 1024, 6, form=ACCUM)
+        _gemv_case(gpu, "q4k", 130, 512, 2, form=BIAS)
+    finally:
+        gpu.set_option("gemv_mma", 1)
+
+
 def test_results_are_deterministic(gpu):
     raw = _weights("q4k", 4096, 4096, "gauss")
     w = gpu.load_weight(raw, Q4_K, 4096, 4096)
