@@ -1,0 +1,403 @@
+// The prefill GEMM with the dequantized weight tiles in tensor memory (included by gemm_tc.cu).
+//
+// tcgen05.mma takes its A operand either from shared memory or from TMEM.  Here the dequantizing warps
+// write the f16 weight tile straight into TMEM (tcgen05.st: lane = weight row, one 32-bit column = two
+// consecutive k), so shared memory holds only the activation tiles and the raw Q4_K nibbles.  That buys
+// ring depth, which is what the pipeline needs: a stage passes through three hand-offs (MMA done ->
+// dequantizer, dequantizer -> MMA thread, MMA thread -> tensor pipe), each several hundred cycles, and a
+// four-deep ring of 512-cycle stages cannot cover them.
+//   TMEM columns   0..255  accumulator(s): one of 256 tokens, or two of <= 128 tokens
+//   TMEM columns 256..511  eight A stages of 128 rows x 64 k (32 columns each) = two super-blocks
+//   shared memory          6-8 activation stages (BN tokens x 64 k, by TMA) + two raw Q4_K tiles
+// Work is cut "stream-K" style: the (tile, super-block) pairs are numbered tile-major and CTA b takes the
+// b-th equal share of that list, so every SM gets the same number of super-blocks whatever the tile
+// count; a tile whose K range is split across CTAs is summed with fp32 atomics into y (zeroed first).
+#pragma once
+
+constexpr int TS_A_STAGES = 8;
+constexpr int TS_A_COL0 = 256;
+#ifndef TS_EPI_WARPS_N
+#define TS_EPI_WARPS_N 8
+#endif
+constexpr int TS_EPI_WARPS = TS_EPI_WARPS_N;                      // warps 0-7: epilogue (lane quarter = warp % 4)
+constexpr int TS_WARP_DEQ0 = TS_EPI_WARPS;                        // warps 8-23: four dequantizing groups
+constexpr int TS_WARP_TMA_X = TS_WARP_DEQ0 + 16;
+constexpr int TS_WARP_MMA0 = TS_WARP_TMA_X + 1;                   // warps 25-28: MMA issue, thread c owns chunk c
+constexpr int TS_WARP_TMA_W = TS_WARP_MMA0 + 4;                   // warp 29: raw-tile TMA, owns the TMEM allocation
+constexpr int TS_THREADS = (TS_WARP_TMA_W + 1) * 32;              // 960
+constexpr int TS_BAR_BYTES = 512;
+constexpr int TS_SMEM_BUDGET = 232448 - 1024 - TS_BAR_BYTES;      // 227 KB minus alignment slack and barriers
+
+__host__ __device__ constexpr int ts_b_stages(int bn, bool staged_w) {
+    const int s = (TS_SMEM_BUDGET - (staged_w ? WQ_BUFS * WQ_BYTES : 0)) / (bn * BK * 2);
+    return s > 8 ? 8 : s;
+}
+
+// ---------------------------------------------------------------- work list
+struct TsPiece { int n0, m0, sb0, sb1; bool partial; };
+
+struct TsSched {
+    long long g, g_end;        // balanced mode: next / one-past-last (tile, super-block) index of this CTA
+    int p, p_end, stride;      // forced-split mode: next piece index
+    int n_tiles_n, nsb, ksplit, bn, n_tiles;
+
+    __device__ TsSched(const GemmArgs &a, int bn_) {
+        bn = bn_;
+        nsb = a.K >> 8;
+        n_tiles_n = (a.N + BM - 1) / BM;
+        n_tiles = n_tiles_n * ((a.M + bn - 1) / bn);
+        ksplit = a.ksplit;
+        const long long total = (long long)n_tiles * nsb;
+        g = total * blockIdx.x / gridDim.x;
+        g_end = total * (blockIdx.x + 1) / gridDim.x;
+        p = blockIdx.x;
+        p_end = n_tiles * (ksplit > 0 ? ksplit : 1);
+        stride = gridDim.x;
+    }
+    __device__ bool next(TsPiece &pc) {
+        int tile;
+        if (ksplit == 0) {
+            if (g >= g_end) return false;
+            tile = (int)(g / nsb);
+            pc.sb0 = (int)(g - (long long)tile * nsb);
+            const long long left = g_end - g;
+            pc.sb1 = left < (long long)(nsb - pc.sb0) ? pc.sb0 + (int)left : nsb;
+            g += pc.sb1 - pc.sb0;
+            pc.partial = (pc.sb1 - pc.sb0) < nsb;
+        } else {
+            for (;;) {
+                if (p >= p_end) return false;
+                tile = p % n_tiles;
+                const int kz = p / n_tiles;
+                p += stride;
+                pc.sb0 = (int)((long long)nsb * kz / ksplit);
+                pc.sb1 = (int)((long long)nsb * (kz + 1) / ksplit);
+                if (pc.sb1 > pc.sb0) break;
+            }
+            pc.partial = ksplit > 1;
+        }
+        pc.n0 = (tile % n_tiles_n) * BM;
+        pc.m0 = (tile / n_tiles_n) * bn;
+        return true;
+    }
+};
+
+// ---------------------------------------------------------------- tcgen05 forms used only here
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 1, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc) : "memory");
+}
+
+// 16 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&o)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                 ::"r"(taddr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+                   "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+}
+
+#ifdef TS_TRACE
+__device__ unsigned long long g_ts_trace[9][4096];
+#define TS_TR_DECL int tr_n = 0
+#define TS_TR(role, code, kb)                                                                                     \
+    do {                                                                                                          \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 4096)                                            \
+            g_ts_trace[role][tr_n++] = ((unsigned long long)clock64() << 16) | ((unsigned long long)(code) << 12) | ((kb) & 0xfff); \
+    } while (0)
+#else
+#define TS_TR_DECL
+#define TS_TR(role, code, kb)
+#endif
+
+// ---------------------------------------------------------------- the kernel
+template <int BN, int TYPE>
+__global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                 const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
+    extern __shared__ unsigned char gemm_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)gemm_smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int B_STAGE_BYTES = BN * BK * 2;
+    constexpr bool STAGED_W = (TYPE == OJAS_B200_Q4_K);
+    constexpr int BS = ts_b_stages(BN, STAGED_W);
+    constexpr int NACC = BN <= 128 ? 2 : 1;
+    static_assert(BS >= 4 && BS <= 8, "activation ring depth");
+    unsigned char *smem_b = smem;
+    unsigned char *smem_wq = smem_b + BS * B_STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_wq + (STAGED_W ? WQ_BUFS * WQ_BYTES : 0));
+    uint64_t *a_full = bars, *a_empty = bars + 8, *b_full = bars + 16, *b_empty = bars + 24;
+    uint64_t *wq_full = bars + 32, *wq_empty = wq_full + WQ_BUFS;
+    uint64_t *tmem_full = wq_empty + WQ_BUFS, *tmem_empty = tmem_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nsb = a.K >> 8;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TS_A_STAGES; s++) {
+            mbar_init(&a_full[s], 4);                         // the four warps of the stage's group
+            mbar_init(&a_empty[s], 1);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&b_empty[s], 1);
+        }
+        for (int b = 0; b < WQ_BUFS; b++) {
+            mbar_init(&wq_full[b], 1);
+            mbar_init(&wq_empty[b], 16);                     // every dequantizing warp
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 4);                     // one commit per MMA-issuing thread
+            mbar_init(&tmem_empty[b], TS_EPI_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == TS_WARP_TMA_W) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // several threads issue MMAs into one accumulator, so every MMA accumulates and the accumulators start
+    // from zero (here, and again after each drain)
+    if (warp < 4) {
+        for (int col = 0; col < NACC * BN; col += 32) tmem_zero32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    TsSched sched(a, BN);
+    TsPiece pc;
+
+    if (warp < TS_EPI_WARPS) {
+        // ---------------- epilogue: warp e drains TMEM lanes 32 (e % 4) .. +31 (weight rows), column half e / 4
+        const int quarter = warp & 3, chalf = warp >> 2;
+        constexpr bool SPLIT = TS_EPI_WARPS == 8 && BN >= 64;     // two warps per lane quarter share the columns
+        constexpr int ECOLS = SPLIT ? BN / 2 : BN;
+        const int col_begin = SPLIT ? chalf * ECOLS : 0, col_end = (SPLIT || chalf == 0) ? col_begin + ECOLS : 0;
+        TS_TR_DECL;
+        for (int it = 0; sched.next(pc); it++) {
+            const int acc = it % NACC, use = it / NACC;
+            if (warp == 0) TS_TR(0, 1, it);
+            if (!mbar_wait_warp_long(&tmem_full[acc], (uint32_t)use & 1u, abort_flag, a.status, 0x400u)) break;
+            tc_fence_after();
+            if (warp == 0) TS_TR(0, 2, it);
+            const int n = pc.n0 + quarter * 32 + lane;
+            float *ycol = a.y + n;
+#pragma unroll 1
+            for (int col = col_begin; col < col_end; col += 32) {
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
+                if (pc.m0 + col < a.M) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr, v);
+                    if (n < a.N) {
+                        const int rows = a.M - (pc.m0 + col) < 32 ? a.M - (pc.m0 + col) : 32;
+                        float *yp = ycol + (size_t)(pc.m0 + col) * a.N;
+                        if (pc.partial) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (j < rows) atomicAdd(yp + (size_t)j * a.N, __uint_as_float(v[j]));
+                        } else if (a.accum) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (j < rows) yp[(size_t)j * a.N] += __uint_as_float(v[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (j < rows) yp[(size_t)j * a.N] = __uint_as_float(v[j]);
+                        }
+                    }
+                }
+                tmem_zero32(taddr);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+            if (warp == 0) TS_TR(0, 3, it);
+        }
+    } else if (warp < TS_WARP_TMA_X) {
+        // ---------------- dequantizers: four groups of four warps; group c owns chunk c of every super-block
+        // (A stage (sb & 1) * 4 + c, the stage MMA thread c consumes), thread = weight row: 64 weights -> 32 TMEM
+        // columns per stage.  Four stages are in work at once, which is what hides the latency of a stage's
+        // own chain (raw tile -> registers -> f16 -> TMEM -> barrier).
+        const int c = (warp - TS_WARP_DEQ0) >> 2;
+        const int row = ((warp & 3) << 5) + lane;
+        const uint32_t tmem_row = tmem_base + ((uint32_t)(row & ~31) << 16) + (uint32_t)TS_A_COL0;
+        uint32_t wc = 0;      // running super-block counter
+        bool ok = true;
+        TS_TR_DECL;
+        const bool tr_on = (warp & 3) == 0 && (c & 1) == 0;
+        while (ok && sched.next(pc)) {
+            const int grow = pc.n0 + row;
+            const bool live = grow < a.N;
+            const size_t lrow = (size_t)(live ? grow : 0);
+            const size_t rowblk = lrow * nsb;
+            const int n_sb = pc.sb1 - pc.sb0;
+            uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
+            if (STAGED_W) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + pc.sb0);
+            // weights that come straight from global memory (Q6_K, Q8_0): the next super-block's loads are in
+            // flight while this one is converted
+            uint4 cA = make_uint4(0u, 0u, 0u, 0u), cB = cA, cC = cA, cD = cA, nA = cA, nB = cA, nC = cA, nD = cA;
+            uint32_t ce0 = 0, ce1 = 0, ne0 = 0, ne1 = 0;
+            auto fetch = [&](int sb, uint4 &A, uint4 &B, uint4 &C, uint4 &D, uint32_t &e0, uint32_t &e1) {
+                if (TYPE == OJAS_B200_Q8_0) {          // 64 int8 + two f16 scales
+                    const size_t k0 = (size_t)sb * 256 + (size_t)c * BK;
+                    const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + (lrow * a.K + k0) / 16;
+                    A = __ldg(src); B = __ldg(src + 1); C = __ldg(src + 2); D = __ldg(src + 3);
+                    e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p1) + (lrow * (a.K / 32) + k0 / 32) / 2);
+                } else if (TYPE == OJAS_B200_Q6_K) {   // two 16-byte pieces of low nibbles, 16 bytes of top bits, 4 scales, d
+                    const size_t blk = rowblk + sb;
+                    A = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + c);
+                    B = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + 4 + c);
+                    C = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk * 4 + c);
+                    e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + blk * 4 + c);
+                    e1 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + blk);
+                }
+            };
+            if (!STAGED_W) fetch(pc.sb0, cA, cB, cC, cD, ce0, ce1);
+            for (int j = 0; ok && j < n_sb; j++, wc++) {
+                const int wb = wc % WQ_BUFS;
+                const int aslot = (int)(wc & 1u) * 4 + c;
+                const uint4 H = hdr_next;
+                if (tr_on) TS_TR(1 + (c >> 1), 1, wc * 4 + c);
+                if (STAGED_W) {
+                    if (j + 1 < n_sb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + pc.sb0 + j + 1);
+                    if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
+                    const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
+                    cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));
+                    cB = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
+                } else if (j + 1 < n_sb) {
+                    fetch(pc.sb0 + j + 1, nA, nB, nC, nD, ne0, ne1);
+                }
+                if (tr_on) TS_TR(1 + (c >> 1), 2, wc * 4 + c);
+                uint32_t o[16];
+                auto convert = [&](int half) {
+                    if (!live) {
+#pragma unroll
+                        for (int q = 0; q < 16; q++) o[q] = 0u;
+                    } else if (TYPE == OJAS_B200_Q4_K) {
+                        dequant_q4k_half(cA, cB, H, c, half, o);
+                    } else if (TYPE == OJAS_B200_Q6_K) {
+                        dequant_q6k_half(cA, cB, cC, ce0, ce1, half, o);
+                    } else if (half == 0) {
+                        dequant_q80_half(cA, cB, ce0, o);
+                    } else {
+                        dequant_q80_half(cC, cD, ce0 >> 16, o);
+                    }
+                };
+                convert(0);
+                if (STAGED_W) {                                          // the raw tile is in registers: hand the buffer back
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&wq_empty[wb]);
+                }
+                if (tr_on) TS_TR(1 + (c >> 1), 3, wc * 4 + c);
+                if (!mbar_wait_warp(&a_empty[aslot], ((wc >> 1) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
+                tc_fence_after();
+                if (tr_on) TS_TR(1 + (c >> 1), 4, wc * 4 + c);
+                tmem_st16(tmem_row + (uint32_t)(aslot * 32), o);
+                convert(1);
+                tmem_st16(tmem_row + (uint32_t)(aslot * 32 + 16), o);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[aslot]);
+                if (tr_on) TS_TR(1 + (c >> 1), 5, wc * 4 + c);
+                if (!STAGED_W) { cA = nA; cB = nB; cC = nC; cD = nD; ce0 = ne0; ce1 = ne1; }
+            }
+        }
+    } else if (warp == TS_WARP_TMA_X) {
+        // ---------------- TMA: activation tile [BN tokens x 64 k] per stage, BS stages in flight
+        if (lane == 0) {
+            int bslot = 0;
+            uint32_t bphase = 0;
+            bool ok = true;
+            TS_TR_DECL;
+            int tr_kb = 0;
+            while (ok && sched.next(pc)) {
+                for (int sb = pc.sb0; ok && sb < pc.sb1; sb++) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; c++) {
+                        TS_TR(3, 1, tr_kb);
+                        if (!mbar_wait_spin(&b_empty[bslot], bphase ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
+                        TS_TR(3, 2, tr_kb);
+                        tr_kb++;
+                        mbar_arrive_expect_tx(&b_full[bslot], (uint32_t)B_STAGE_BYTES);
+                        tma_load_2d(smem_b + bslot * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, pc.m0, &b_full[bslot]);
+                        if (++bslot == BS) { bslot = 0; bphase ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp < TS_WARP_TMA_W) {
+        // ---------------- MMA issue: thread c owns chunk c of every super-block (A stage (sb & 1) * 4 + c);
+        // every MMA accumulates (see the zeroing above)
+        if (lane == 0) {
+            const int c = warp - TS_WARP_MMA0;
+            constexpr uint32_t idesc = umma_idesc(BN);
+            uint32_t wc = 0, bphase = 0;
+            int bslot = c;
+            bool ok = true;
+            TS_TR_DECL;
+            for (int it = 0; ok && sched.next(pc); it++) {
+                const int acc = it % NACC, use = it / NACC;
+                if (!mbar_wait_spin(&tmem_empty[acc], ((uint32_t)use & 1u) ^ 1u, abort_flag, a.status, 0x8000u)) break;
+                tc_fence_after();
+                const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
+                for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
+                    const int aslot = (int)(wc & 1u) * 4 + c;
+                    TS_TR(4 + c, 1, wc * 4 + c);
+                    if (!mbar_wait_spin(&a_full[aslot], (wc >> 1) & 1u, abort_flag, a.status, 0x800u)) { ok = false; break; }
+                    TS_TR(4 + c, 2, wc * 4 + c);
+                    if (!mbar_wait_spin(&b_full[bslot], bphase, abort_flag, a.status, 0x1000u)) { ok = false; break; }
+                    tc_fence_after();
+                    TS_TR(4 + c, 3, wc * 4 + c);
+                    const uint32_t tmem_a = tmem_base + (uint32_t)(TS_A_COL0 + aslot * 32);
+                    const uint64_t bdesc = umma_desc(smem_u32(smem_b + bslot * B_STAGE_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)       // 16 k per MMA: 8 TMEM columns of A, 32 bytes of every B row
+                        umma_f16_ts(tmem_acc, tmem_a + 8 * k, bdesc + 2 * k, idesc);
+                    umma_commit(&a_empty[aslot]);
+                    umma_commit(&b_empty[bslot]);
+                    TS_TR(4 + c, 4, wc * 4 + c);
+                    bslot += 4;
+                    if (bslot >= BS) { bslot -= BS; bphase ^= 1u; }
+                }
+                if (ok) umma_commit(&tmem_full[acc]);
+            }
+        }
+    } else {
+        // ---------------- TMA: raw Q4_K nibble tile [128 rows x 128 bytes] per super-block
+        if (STAGED_W && lane == 0) {
+            uint32_t wc = 0;
+            bool ok = true;
+            TS_TR_DECL;
+            while (ok && sched.next(pc)) {
+                for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
+                    const int wb = wc % WQ_BUFS;
+                    TS_TR(8, 1, wc * 4);
+                    if (!mbar_wait_spin(&wq_empty[wb], ((wc / WQ_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000u)) { ok = false; break; }
+                    TS_TR(8, 2, wc * 4);
+                    mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
+                    tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, pc.n0, &wq_full[wb]);
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown (every role arrives here, also after an abort)
+    if (*abort_flag && warp == TS_WARP_TMA_X && lane == 0) {
+        // give copies that are still in flight a bounded time to land before the CTA releases shared memory
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) { }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == TS_WARP_TMA_W) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
