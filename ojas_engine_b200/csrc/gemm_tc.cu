@@ -53,6 +53,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {   // non-blocking probe
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {    // may suspend the thread until the phase completes or a hardware time limit passes
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
@@ -89,21 +95,23 @@ __device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile 
 #endif
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code,
                                                unsigned nap = OJAS_GEMM_NAP) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_test(bar, parity)) return true;
     return mbar_wait(bar, parity, abort_flag, status, code, nap);
 }
 
-// Warp form: lane 0 waits, the result is broadcast, __syncwarp orders the other lanes behind it.
+// Warp form.  The common case (the phase is already complete) is one probe by all lanes and a vote; otherwise
+// lane 0 waits and the result is broadcast.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
+    if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait_spin(bar, parity, abort_flag, status, code) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, code, OJAS_GEMM_NAP) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     return ok != 0;
 }
 // The same for waits that are known to be long (a whole tile): one probe, then sleep between probes.
 __device__ __forceinline__ bool mbar_wait_warp_long(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
     int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = (mbar_try(bar, parity) || mbar_wait(bar, parity, abort_flag, status, code, 256u)) ? 1 : 0;
+    if ((threadIdx.x & 31) == 0) ok = (mbar_test(bar, parity) || mbar_wait(bar, parity, abort_flag, status, code, 256u)) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
     return ok != 0;
 }
@@ -317,6 +325,12 @@ int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, con
 #ifdef TS_TRACE
 extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_trace(void *dst, size_t bytes) {
     return (int)cudaMemcpyFromSymbol(dst, g_ts_trace, bytes);
+}
+extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_prog(void *dst, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(dst, g_ts_prog, bytes);
+}
+extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_span(void *dst, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(dst, g_ts_span, bytes);
 }
 #endif
 

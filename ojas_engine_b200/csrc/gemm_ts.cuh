@@ -89,6 +89,11 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
                  ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc) : "memory");
 }
 
+// Atomic add without a return value: nothing comes back, so the epilogue does not wait a round trip to L2.
+__device__ __forceinline__ void red_add_f32(float *p, float v) {
+    asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
 // 16 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&o)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -98,6 +103,10 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&o)[16
 }
 
 #ifdef TS_TRACE
+__device__ unsigned long long g_ts_span[148][32][2];
+__device__ __forceinline__ unsigned long long ts_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ unsigned int g_ts_prog[148][32];
+#define TS_PROG(val) do { if ((threadIdx.x & 31) == 0) g_ts_prog[blockIdx.x][threadIdx.x >> 5] = (unsigned)(val); } while (0)
 __device__ unsigned long long g_ts_trace[9][4096];
 #define TS_TR_DECL int tr_n = 0
 #define TS_TR(role, code, kb)                                                                                     \
@@ -108,6 +117,7 @@ __device__ unsigned long long g_ts_trace[9][4096];
 #else
 #define TS_TR_DECL
 #define TS_TR(role, code, kb)
+#define TS_PROG(val)
 #endif
 
 // ---------------------------------------------------------------- the kernel
@@ -129,6 +139,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     uint64_t *tmem_full = wq_empty + WQ_BUFS, *tmem_empty = tmem_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile unsigned *b_seen = reinterpret_cast<volatile unsigned *>(tmem_slot + 2);   // [4], see the MMA threads
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = a.K >> 8;
@@ -149,6 +160,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             mbar_init(&tmem_empty[b], TS_EPI_WARPS);
         }
         *abort_flag = 0;
+        for (int i = 0; i < 4; i++) b_seen[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TS_WARP_TMA_W) {
@@ -162,7 +174,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     // several threads issue MMAs into one accumulator, so every MMA accumulates and the accumulators start
     // from zero (here, and again after each drain)
     if (warp < 4) {
-        for (int col = 0; col < NACC * BN; col += 32) tmem_zero32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
+#ifdef TS_X_NOST
+        for (int col = 0; col < 512; col += 32) tmem_zero32(
+#else
+        for (int col = 0; col < NACC * BN; col += 32) tmem_zero32(
+#endif
+tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -171,6 +188,9 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
 
     TsSched sched(a, BN);
     TsPiece pc;
+#ifdef TS_TRACE
+    if (lane == 0) g_ts_span[blockIdx.x][warp][0] = ts_gtime();
+#endif
 
     if (warp < TS_EPI_WARPS) {
         // ---------------- epilogue: warp e drains TMEM lanes 32 (e % 4) .. +31 (weight rows), column half e / 4
@@ -182,9 +202,11 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         for (int it = 0; sched.next(pc); it++) {
             const int acc = it % NACC, use = it / NACC;
             if (warp == 0) TS_TR(0, 1, it);
+            TS_PROG(it * 16 + 1);
             if (!mbar_wait_warp_long(&tmem_full[acc], (uint32_t)use & 1u, abort_flag, a.status, 0x400u)) break;
             tc_fence_after();
             if (warp == 0) TS_TR(0, 2, it);
+            TS_PROG(it * 16 + 2);
             const int n = pc.n0 + quarter * 32 + lane;
             float *ycol = a.y + n;
 #pragma unroll 1
@@ -199,7 +221,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         if (pc.partial) {
 #pragma unroll
                             for (int j = 0; j < 32; j++)
-                                if (j < rows) atomicAdd(yp + (size_t)j * a.N, __uint_as_float(v[j]));
+                                if (j < rows) red_add_f32(yp + (size_t)j * a.N, __uint_as_float(v[j]));
                         } else if (a.accum) {
 #pragma unroll
                             for (int j = 0; j < 32; j++)
@@ -218,6 +240,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
             if (warp == 0) TS_TR(0, 3, it);
+            TS_PROG(it * 16 + 3);
         }
     } else if (warp < TS_WARP_TMA_X) {
         // ---------------- dequantizers: four groups of four warps; group c owns chunk c of every super-block
@@ -264,6 +287,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 const int aslot = (int)(wc & 1u) * 4 + c;
                 const uint4 H = hdr_next;
                 if (tr_on) TS_TR(1 + (c >> 1), 1, wc * 4 + c);
+                TS_PROG(wc * 16 + 1);
                 if (STAGED_W) {
                     if (j + 1 < n_sb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + pc.sb0 + j + 1);
                     if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
@@ -274,6 +298,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     fetch(pc.sb0 + j + 1, nA, nB, nC, nD, ne0, ne1);
                 }
                 if (tr_on) TS_TR(1 + (c >> 1), 2, wc * 4 + c);
+                TS_PROG(wc * 16 + 2);
                 uint32_t o[16];
                 auto convert = [&](int half) {
                     if (!live) {
@@ -289,23 +314,40 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         dequant_q80_half(cC, cD, ce0 >> 16, o);
                     }
                 };
+#ifndef TS_X_NOCONV
                 convert(0);
+#else
+                for (int q = 0; q < 16; q++) o[q] = 0x3c003c00u + ((cA.x + cB.y) & 0x00ff00ffu);
+#endif
                 if (STAGED_W) {                                          // the raw tile is in registers: hand the buffer back
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&wq_empty[wb]);
                 }
                 if (tr_on) TS_TR(1 + (c >> 1), 3, wc * 4 + c);
+                TS_PROG(wc * 16 + 3);
                 if (!mbar_wait_warp(&a_empty[aslot], ((wc >> 1) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
                 tc_fence_after();
                 if (tr_on) TS_TR(1 + (c >> 1), 4, wc * 4 + c);
+                TS_PROG(wc * 16 + 4);
+#ifndef TS_X_NOST
                 tmem_st16(tmem_row + (uint32_t)(aslot * 32), o);
+#endif
+#ifndef TS_X_NOCONV
                 convert(1);
+#endif
+#ifndef TS_X_NOST
                 tmem_st16(tmem_row + (uint32_t)(aslot * 32 + 16), o);
+#else
+                asm volatile("" ::"r"(o[0] ^ o[1] ^ o[2] ^ o[3] ^ o[4] ^ o[5] ^ o[6] ^ o[7] ^ o[8] ^ o[9] ^ o[10] ^ o[11] ^ o[12] ^ o[13] ^ o[14] ^ o[15]));
+#endif
+                if (tr_on) TS_TR(1 + (c >> 1), 6, wc * 4 + c);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                if (tr_on) TS_TR(1 + (c >> 1), 7, wc * 4 + c);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[aslot]);
                 if (tr_on) TS_TR(1 + (c >> 1), 5, wc * 4 + c);
+                TS_PROG(wc * 16 + 5);
                 if (!STAGED_W) { cA = nA; cB = nB; cC = nC; cD = nD; ce0 = ne0; ce1 = ne1; }
             }
         }
@@ -322,8 +364,10 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
 #pragma unroll 1
                     for (int c = 0; c < 4; c++) {
                         TS_TR(3, 1, tr_kb);
+                        TS_PROG(tr_kb * 16 + 1);
                         if (!mbar_wait_spin(&b_empty[bslot], bphase ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
                         TS_TR(3, 2, tr_kb);
+                        TS_PROG(tr_kb * 16 + 2);
                         tr_kb++;
                         mbar_arrive_expect_tx(&b_full[bslot], (uint32_t)B_STAGE_BYTES);
                         tma_load_2d(smem_b + bslot * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, pc.m0, &b_full[bslot]);
@@ -344,17 +388,36 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             TS_TR_DECL;
             for (int it = 0; ok && sched.next(pc); it++) {
                 const int acc = it % NACC, use = it / NACC;
+                TS_PROG(wc * 16 + 9 + 256 * 65536 * (it & 15));
                 if (!mbar_wait_spin(&tmem_empty[acc], ((uint32_t)use & 1u) ^ 1u, abort_flag, a.status, 0x8000u)) break;
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
                     const int aslot = (int)(wc & 1u) * 4 + c;
                     TS_TR(4 + c, 1, wc * 4 + c);
+                    TS_PROG(wc * 16 + 1 + 256 * 65536 * (it & 15));
                     if (!mbar_wait_spin(&a_full[aslot], (wc >> 1) & 1u, abort_flag, a.status, 0x800u)) { ok = false; break; }
                     TS_TR(4 + c, 2, wc * 4 + c);
+                    TS_PROG(wc * 16 + 2 + 256 * 65536 * (it & 15));
+                    // A parity wait tells "this use is filled" from "the use before is not filled yet" only for a
+                    // waiter that saw the use before complete.  Use u - 1 of this activation slot (k-block kb - BS)
+                    // belongs to another MMA thread unless BS is a multiple of four, so wait until that thread has
+                    // seen it land (it publishes the k-blocks it has passed in b_seen).
+                    const uint32_t kb = wc * 4u + (uint32_t)c;
+                    if ((BS & 3) != 0 && kb >= (uint32_t)BS) {
+                        const uint32_t need = kb - (uint32_t)BS;
+                        const long long t0 = clock64();
+                        while (b_seen[need & 3u] <= need) {
+                            if (*abort_flag) { ok = false; break; }
+                            if (clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; atomicOr(a.status, 0x10000u); __threadfence_system(); ok = false; break; }
+                        }
+                        if (!ok) break;
+                    }
                     if (!mbar_wait_spin(&b_full[bslot], bphase, abort_flag, a.status, 0x1000u)) { ok = false; break; }
+                    b_seen[c] = kb + 1u;
                     tc_fence_after();
                     TS_TR(4 + c, 3, wc * 4 + c);
+                    TS_PROG(wc * 16 + 3 + 256 * 65536 * (it & 15));
                     const uint32_t tmem_a = tmem_base + (uint32_t)(TS_A_COL0 + aslot * 32);
                     const uint64_t bdesc = umma_desc(smem_u32(smem_b + bslot * B_STAGE_BYTES));
 #pragma unroll
@@ -363,6 +426,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     umma_commit(&a_empty[aslot]);
                     umma_commit(&b_empty[bslot]);
                     TS_TR(4 + c, 4, wc * 4 + c);
+                    TS_PROG(wc * 16 + 4 + 256 * 65536 * (it & 15));
                     bslot += 4;
                     if (bslot >= BS) { bslot -= BS; bphase ^= 1u; }
                 }
@@ -379,8 +443,10 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
                     const int wb = wc % WQ_BUFS;
                     TS_TR(8, 1, wc * 4);
+                    TS_PROG(wc * 16 + 1);
                     if (!mbar_wait_spin(&wq_empty[wb], ((wc / WQ_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000u)) { ok = false; break; }
                     TS_TR(8, 2, wc * 4);
+                    TS_PROG(wc * 16 + 2);
                     mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
                     tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, pc.n0, &wq_full[wb]);
                 }
@@ -388,6 +454,9 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         }
     }
 
+#ifdef TS_TRACE
+    if (lane == 0) g_ts_span[blockIdx.x][warp][1] = ts_gtime();
+#endif
     // ---------------- teardown (every role arrives here, also after an abort)
     if (*abort_flag && warp == TS_WARP_TMA_X && lane == 0) {
         // give copies that are still in flight a bounded time to land before the CTA releases shared memory
