@@ -27,7 +27,7 @@ namespace {
 constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
 #ifndef OJAS_GEMM_WQ_BUFS
-#define OJAS_GEMM_WQ_BUFS 4
+#define OJAS_GEMM_WQ_BUFS 3
 #endif
 constexpr int WQ_BUFS = OJAS_GEMM_WQ_BUFS;   // raw Q4_K nibble tiles (one super-block x 128 rows = 16 KB) in flight
 constexpr int WQ_BYTES = BM * 128;
@@ -39,6 +39,7 @@ struct GemmArgs {
     int M, N, K;
     int accum;           // 1: y += result
     int ksplit;          // 0: K ranges balanced across the CTAs; S > 0: every tile's K range cut into S pieces
+    int y_tma;           // 1: the epilogue writes y through bulk tensor stores (needs N % 4 == 0 and y on 16 bytes)
     unsigned *status;    // device-visible status word of the context
 };
 
@@ -296,27 +297,30 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 size_t gemm_ts_smem_bytes(int bn, bool staged_w) {
-    return 1024 + (size_t)ts_b_stages(bn, staged_w) * bn * BK * 2 + (staged_w ? WQ_BUFS * WQ_BYTES : 0) + TS_BAR_BYTES;
+    return 1024 + (size_t)ts_b_stages(bn, staged_w) * bn * BK * 2 + (staged_w ? WQ_BUFS * WQ_BYTES : 0) +
+           TS_EPI_WARPS * TS_EPI_TILE_BYTES + TS_BAR_BYTES;
 }
 
 template <int BN, int TYPE>
-int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_y,
+                      const GemmArgs &args, dim3 grid) {
     auto kernel = gemm_ts_kernel<BN, TYPE>;
     const size_t smem = gemm_ts_smem_bytes(BN, TYPE == OJAS_B200_Q4_K);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    kernel<<<grid, TS_THREADS, smem, ctx->stream>>>(tmap, tmap_w, args);
+    kernel<<<grid, TS_THREADS, smem, ctx->stream>>>(tmap, tmap_w, tmap_y, args);
     OJAS_LAUNCH_CHECK(ctx, "gemm_ts");
     return 0;
 }
 
 template <int TYPE>
-int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_y,
+                        const GemmArgs &args, dim3 grid) {
     switch (bn) {
-    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_w, args, grid);
-    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_w, args, grid);
-    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_w, args, grid);
-    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_w, args, grid);
+    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
     }
 }
 
@@ -391,7 +395,20 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
         if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (weights) failed (%d)", (int)cr);
     }
 
+    // y as a tensor [M rows][N floats], box = 32 floats x 16 rows (one epilogue warp's staging tile)
+    CUtensorMap tmap_y = tmap;
+    const bool y_tma = (N % 4 == 0) && (((uintptr_t)y & 15) == 0);
+    if (y_tma) {
+        const cuuint64_t ydims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)N * 4};
+        const cuuint32_t ybox[2] = {32, 16};
+        cr = encode(&tmap_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)y, ydims, ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (output) failed (%d)", (int)cr);
+    }
+
     GemmArgs args{};
+    args.y_tma = y_tma ? 1 : 0;
     args.w = weight_planes(type, w, N, K);
     args.y = y;
     args.M = (int)M; args.N = (int)N; args.K = (int)K;
@@ -407,9 +424,9 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
             for (size_t b = 1; b < ctas && !partial; b++) partial = ((tiles * nsb * b / ctas) % nsb) != 0;
         if (partial && !accum) OJAS_CUDA(ctx, cudaMemsetAsync(y, 0, M * N * sizeof(float), ctx->stream));
         const dim3 grid_ts((unsigned)ctas);
-        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, args, grid_ts);
-        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, args, grid_ts);
-        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, args, grid_ts);
+        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
     }
 }
 

@@ -26,7 +26,8 @@ constexpr int TS_WARP_MMA0 = TS_WARP_TMA_X + 1;                   // warps 25-28
 constexpr int TS_WARP_TMA_W = TS_WARP_MMA0 + 4;                   // warp 29: raw-tile TMA, owns the TMEM allocation
 constexpr int TS_THREADS = (TS_WARP_TMA_W + 1) * 32;              // 960
 constexpr int TS_BAR_BYTES = 512;
-constexpr int TS_SMEM_BUDGET = 232448 - 1024 - TS_BAR_BYTES;      // 227 KB minus alignment slack and barriers
+constexpr int TS_EPI_TILE_BYTES = 16 * 32 * 4;                    // per epilogue warp: 16 tokens x 32 weight rows, fp32
+constexpr int TS_SMEM_BUDGET = 232448 - 1024 - TS_BAR_BYTES - TS_EPI_WARPS * TS_EPI_TILE_BYTES;   // 227 KB minus slack, barriers, staging
 
 __host__ __device__ constexpr int ts_b_stages(int bn, bool staged_w) {
     const int s = (TS_SMEM_BUDGET - (staged_w ? WQ_BUFS * WQ_BYTES : 0)) / (bn * BK * 2);
@@ -94,6 +95,30 @@ __device__ __forceinline__ void red_add_f32(float *p, float v) {
     asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
 }
 
+// Tile [rows of 32 floats] from shared memory into the 2-D tensor behind `tmap` at (x, y): plain store, or add.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void *smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *tmap, const void *smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"((uint64_t)tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_zero16(uint32_t taddr) {
+    const uint32_t z = 0u;
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+                 ::"r"(taddr), "r"(z) : "memory");
+}
+
 // 16 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&o)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -123,7 +148,8 @@ __device__ unsigned long long g_ts_trace[9][4096];
 // ---------------------------------------------------------------- the kernel
 template <int BN, int TYPE>
 __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                                 const __grid_constant__ CUtensorMap tmap_w, const GemmArgs a) {
+                                                                 const __grid_constant__ CUtensorMap tmap_w,
+                                                                 const __grid_constant__ CUtensorMap tmap_y, const GemmArgs a) {
     extern __shared__ unsigned char gemm_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)gemm_smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_STAGE_BYTES = BN * BK * 2;
@@ -133,7 +159,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     static_assert(BS >= 4 && BS <= 8, "activation ring depth");
     unsigned char *smem_b = smem;
     unsigned char *smem_wq = smem_b + BS * B_STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_wq + (STAGED_W ? WQ_BUFS * WQ_BYTES : 0));
+    unsigned char *smem_epi = smem_wq + (STAGED_W ? WQ_BUFS * WQ_BYTES : 0);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + TS_EPI_WARPS * TS_EPI_TILE_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + 8, *b_full = bars + 16, *b_empty = bars + 24;
     uint64_t *wq_full = bars + 32, *wq_empty = wq_full + WQ_BUFS;
     uint64_t *tmem_full = wq_empty + WQ_BUFS, *tmem_empty = tmem_full + 2;
@@ -198,6 +225,7 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
         constexpr bool SPLIT = TS_EPI_WARPS == 8 && BN >= 64;     // two warps per lane quarter share the columns
         constexpr int ECOLS = SPLIT ? BN / 2 : BN;
         const int col_begin = SPLIT ? chalf * ECOLS : 0, col_end = (SPLIT || chalf == 0) ? col_begin + ECOLS : 0;
+        float *epi_tile = reinterpret_cast<float *>(smem_epi + warp * TS_EPI_TILE_BYTES);
         TS_TR_DECL;
         for (int it = 0; sched.next(pc); it++) {
             const int acc = it % NACC, use = it / NACC;
@@ -209,31 +237,62 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
             TS_PROG(it * 16 + 2);
             const int n = pc.n0 + quarter * 32 + lane;
             float *ycol = a.y + n;
+            if (a.y_tma) {
+                // 16 tokens at a time through this warp's 2 KB staging tile [16 tokens][32 rows] and one bulk
+                // tensor store (or reduce-add) per tile: the copy engine clips the tile at the edges of y and
+                // keeps many more bytes in flight than a warp's own stores can
+                const int xn = pc.n0 + quarter * 32;
+                const bool add = pc.partial || a.accum;
 #pragma unroll 1
-            for (int col = col_begin; col < col_end; col += 32) {
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
-                if (pc.m0 + col < a.M) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr, v);
-                    if (n < a.N) {
-                        const int rows = a.M - (pc.m0 + col) < 32 ? a.M - (pc.m0 + col) : 32;
-                        float *yp = ycol + (size_t)(pc.m0 + col) * a.N;
-                        if (pc.partial) {
+                for (int col = col_begin; col < col_end; col += 16) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
+                    if (pc.m0 + col < a.M && xn < a.N) {
+                        uint32_t v[16];
+                        tmem_ld16(taddr, v);
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile before has left
+                        __syncwarp();
 #pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (j < rows) red_add_f32(yp + (size_t)j * a.N, __uint_as_float(v[j]));
-                        } else if (a.accum) {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (j < rows) yp[(size_t)j * a.N] += __uint_as_float(v[j]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (j < rows) yp[(size_t)j * a.N] = __uint_as_float(v[j]);
+                        for (int j = 0; j < 16; j++) epi_tile[j * 32 + lane] = __uint_as_float(v[j]);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (add) tma_reduce_add_2d(&tmap_y, epi_tile, xn, pc.m0 + col);
+                            else tma_store_2d(&tmap_y, epi_tile, xn, pc.m0 + col);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
                     }
+                    tmem_zero16(taddr);
                 }
-                tmem_zero32(taddr);
+            } else {
+#pragma unroll 1
+                for (int col = col_begin; col < col_end; col += 32) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
+                    if (pc.m0 + col < a.M) {
+                        uint32_t v[32];
+                        if (warp == 0) TS_TR(0, 4, it);
+                        tmem_ld32(taddr, v);
+                        if (warp == 0) TS_TR(0, 5, it);
+                        if (n < a.N) {
+                            const int rows = a.M - (pc.m0 + col) < 32 ? a.M - (pc.m0 + col) : 32;
+                            float *yp = ycol + (size_t)(pc.m0 + col) * a.N;
+                            if (pc.partial) {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (j < rows) red_add_f32(yp + (size_t)j * a.N, __uint_as_float(v[j]));
+                            } else if (a.accum) {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (j < rows) yp[(size_t)j * a.N] += __uint_as_float(v[j]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; j++)
+                                    if (j < rows) yp[(size_t)j * a.N] = __uint_as_float(v[j]);
+                            }
+                        }
+                    }
+                    if (warp == 0) TS_TR(0, 6, it);
+                    tmem_zero32(taddr);
+                }
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
@@ -242,6 +301,7 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
             if (warp == 0) TS_TR(0, 3, it);
             TS_PROG(it * 16 + 3);
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA ends
     } else if (warp < TS_WARP_TMA_X) {
         // ---------------- dequantizers: four groups of four warps; group c owns chunk c of every super-block
         // (A stage (sb & 1) * 4 + c, the stage MMA thread c consumes), thread = weight row: 64 weights -> 32 TMEM
