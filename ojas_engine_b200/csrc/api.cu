@@ -53,6 +53,14 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
         return OJAS_B200_E_CUDA;
     }
     memset(ctx->host_status, 0, 64);
+    if (cudaMalloc((void **)&ctx->gemm_flags, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(ctx->gemm_flags, 0, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess) {
+        if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
+        cudaFreeHost(ctx->host_status);
+        if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return OJAS_B200_E_CUDA;
+    }
     const char *pdl = getenv("OJAS_B200_PDL");   // read once at context creation, like the engine's OJAS_* switches
     ctx->pdl = !(pdl && pdl[0] == '0');          // on unless OJAS_B200_PDL=0
     *out = ctx;
@@ -62,6 +70,7 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
 extern "C" void ojas_b200_destroy(ojas_b200_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;

@@ -22,10 +22,14 @@ struct ojas_b200_ctx {
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
     int gemv_depth = 4;          // stages in each warp's cp.async ring (2..4)
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
+    unsigned int *gemm_flags = nullptr;  // device words, one per GEMM output tile: "the tile has been stored" marks (see gemm_ts.cuh)
+    unsigned int gemm_serial = 0;        // value that means "stored" for the GEMM launch in flight; never 0
     unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
     unsigned int *dev_status = nullptr;  // the same word as the device sees it
     char err[512] = {0};
 };
+
+constexpr size_t OJAS_GEMM_FLAG_WORDS = 65536;
 
 int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
 

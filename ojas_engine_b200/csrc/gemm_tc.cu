@@ -39,6 +39,8 @@ struct GemmArgs {
     int M, N, K;
     int accum;           // 1: y += result
     int ksplit;          // 0: K ranges balanced across the CTAs; S > 0: every tile's K range cut into S pieces
+    unsigned *flags;     // per-tile "stored" marks (null: split tiles are added into a zeroed y instead)
+    unsigned serial;     // the value of a mark that belongs to this launch
     int y_tma;           // 1: the epilogue writes y through bulk tensor stores (needs N % 4 == 0 and y on 16 bytes)
     unsigned *status;    // device-visible status word of the context
 };
@@ -422,7 +424,18 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
         bool partial = args.ksplit > 1;
         if (!args.ksplit)
             for (size_t b = 1; b < ctas && !partial; b++) partial = ((tiles * nsb * b / ctas) % nsb) != 0;
-        if (partial && !accum) OJAS_CUDA(ctx, cudaMemsetAsync(y, 0, M * N * sizeof(float), ctx->stream));
+        if (partial && !accum) {
+            // A tile whose K range is split over CTAs: either the piece with the tile's last super-block stores
+            // and marks the tile and the others add after the mark (no zeroing of y), or y is zeroed and every
+            // piece adds.
+            if (y_tma && !args.ksplit && tiles <= OJAS_GEMM_FLAG_WORDS) {
+                if (++ctx->gemm_serial == 0) ctx->gemm_serial = 1;
+                args.flags = ctx->gemm_flags;
+                args.serial = ctx->gemm_serial;
+            } else {
+                OJAS_CUDA(ctx, cudaMemsetAsync(y, 0, M * N * sizeof(float), ctx->stream));
+            }
+        }
         const dim3 grid_ts((unsigned)ctas);
         if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
         if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);

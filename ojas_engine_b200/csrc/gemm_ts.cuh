@@ -35,7 +35,7 @@ __host__ __device__ constexpr int ts_b_stages(int bn, bool staged_w) {
 }
 
 // ---------------------------------------------------------------- work list
-struct TsPiece { int n0, m0, sb0, sb1; bool partial; };
+struct TsPiece { int tile, n0, m0, sb0, sb1; bool partial; };
 
 struct TsSched {
     long long g, g_end;        // balanced mode: next / one-past-last (tile, super-block) index of this CTA
@@ -77,6 +77,7 @@ struct TsSched {
             }
             pc.partial = ksplit > 1;
         }
+        pc.tile = tile;
         pc.n0 = (tile % n_tiles_n) * BM;
         pc.m0 = (tile / n_tiles_n) * bn;
         return true;
@@ -93,6 +94,25 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
 // Atomic add without a return value: nothing comes back, so the epilogue does not wait a round trip to L2.
 __device__ __forceinline__ void red_add_f32(float *p, float v) {
     asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+// Bounded wait for a tile's "stored" mark (written by another CTA that is resident at the same time: the grid
+// never exceeds one CTA per SM, and the marking piece is the first thing its CTA does).
+__device__ __noinline__ bool flag_wait(const unsigned *flag, unsigned serial, volatile int *abort_flag, unsigned *status) {
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v == serial) return true;
+        __nanosleep(100);
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) {
+            *abort_flag = 1;
+            atomicOr(status, 0x20000u);
+            __threadfence_system();
+            return false;
+        }
+    }
 }
 
 // Tile [rows of 32 floats] from shared memory into the 2-D tensor behind `tmap` at (x, y): plain store, or add.
@@ -242,11 +262,24 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
                 // tensor store (or reduce-add) per tile: the copy engine clips the tile at the edges of y and
                 // keeps many more bytes in flight than a warp's own stores can
                 const int xn = pc.n0 + quarter * 32;
-                const bool add = pc.partial || a.accum;
+                // split tile with marks: the piece that ends the tile's K range stores, the others add after its mark
+                const bool marks = pc.partial && a.flags != nullptr;
+                const bool storer = marks && pc.sb1 == nsb;
+                const bool add = (pc.partial && !storer) || a.accum;
+                if (marks && !storer) {
+                    int ok = 1;
+                    if (lane == 0) ok = flag_wait(a.flags + pc.tile, a.serial, abort_flag, a.status) ? 1 : 0;
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
 #pragma unroll 1
                 for (int col = col_begin; col < col_end; col += 16) {
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
+#ifdef TS_X_NOEPI
+                    if (false) {
+#else
                     if (pc.m0 + col < a.M && xn < a.N) {
+#endif
                         uint32_t v[16];
                         tmem_ld16(taddr, v);
                         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile before has left
@@ -262,6 +295,13 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
                         }
                     }
                     tmem_zero16(taddr);
+                }
+                if (storer) {
+                    // all eight warps' stores have landed -> mark the tile (every epilogue warp takes part in every piece)
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    __threadfence();
+                    asm volatile("bar.sync 1, %0;" ::"n"(TS_EPI_WARPS * 32) : "memory");
+                    if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + pc.tile), "r"(a.serial) : "memory");
                 }
             } else {
 #pragma unroll 1
