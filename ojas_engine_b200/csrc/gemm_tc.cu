@@ -257,6 +257,7 @@ template <bool QUANT>
 __global__ void __launch_bounds__(256) gemm_prep_kernel(const float *x, __half *xh, long long n_sb) {
     const int lane = threadIdx.x & 31;
     const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    grid_launch_dependents();   // the GEMM behind this kernel may begin its set-up; it waits for this grid before it reads xh
     if (sb >= n_sb) return;
     float v[8];
     if (QUANT) {
@@ -310,7 +311,20 @@ int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtenso
     const size_t smem = gemm_ts_smem_bytes(BN, TYPE == OJAS_B200_Q4_K);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    kernel<<<grid, TS_THREADS, smem, ctx->stream>>>(tmap, tmap_w, tmap_y, args);
+    // programmatic dependent launch: the kernel's set-up, weight loads and dequantization overlap the tail of the
+    // activation-preparation kernel; only the thread that loads the prepared activations waits for it
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(TS_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_w, tmap_y, args);
+    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemm_ts: %s", cudaGetErrorString(e));
     OJAS_LAUNCH_CHECK(ctx, "gemm_ts");
     return 0;
 }

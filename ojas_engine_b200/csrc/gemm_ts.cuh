@@ -459,6 +459,7 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
             bool ok = true;
             TS_TR_DECL;
             int tr_kb = 0;
+            grid_dependency_wait();     // the prepared activations come from the kernel before this one
             while (ok && sched.next(pc)) {
                 for (int sb = pc.sb0; ok && sb < pc.sb1; sb++) {
 #pragma unroll 1
