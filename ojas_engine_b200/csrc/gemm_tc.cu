@@ -39,6 +39,7 @@ struct GemmArgs {
     int M, N, K;
     int accum;           // 1: y += result
     int ksplit;          // 0: K ranges balanced across the CTAs; S > 0: every tile's K range cut into S pieces
+    int e2;              // balanced split: cost of a tile's end in half super-blocks (see ts_share_begin)
     unsigned *flags;     // per-tile "stored" marks (null: split tiles are added into a zeroed y instead)
     unsigned serial;     // the value of a mark that belongs to this launch
     int y_tma;           // 1: the epilogue writes y through bulk tensor stores (needs N % 4 == 0 and y on 16 bytes)
@@ -435,9 +436,14 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
         const size_t tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn), nsb = K / 256;
         const size_t units = args.ksplit ? tiles * (size_t)args.ksplit : tiles * nsb;
         const size_t ctas = units < (size_t)ctx->sm_count ? units : (size_t)ctx->sm_count;
+#ifndef OJAS_GEMM_E2
+#define OJAS_GEMM_E2 6
+#endif
+        args.e2 = bn > 128 ? OJAS_GEMM_E2 : 0;      // one accumulator: the drain is exposed; two: it overlaps the next tile
         bool partial = args.ksplit > 1;
         if (!args.ksplit)
-            for (size_t b = 1; b < ctas && !partial; b++) partial = ((tiles * nsb * b / ctas) % nsb) != 0;
+            for (size_t b = 1; b < ctas && !partial; b++)
+                partial = (ts_share_begin((long long)tiles, (int)nsb, args.e2, (long long)b, (long long)ctas) % (long long)nsb) != 0;
         if (partial && !accum) {
             // A tile whose K range is split over CTAs: either the piece with the tile's last super-block stores
             // and marks the tile and the others add after the mark (no zeroing of y), or y is zeroed and every

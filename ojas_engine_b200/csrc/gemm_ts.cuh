@@ -37,6 +37,17 @@ __host__ __device__ constexpr int ts_b_stages(int bn, bool staged_w) {
 // ---------------------------------------------------------------- work list
 struct TsPiece { int tile, n0, m0, sb0, sb1; bool partial; };
 
+// Balanced split.  Every piece of work ends with a drain of the accumulator that the main loop cannot hide when
+// there is a single accumulator, so the list is cut at equal *cost*: a super-block costs 2 units, the end of a
+// tile e2 units (the drain of a 128 x 256 tile takes about as long as 2.5 super-blocks).  Returns the first
+// (tile, super-block) index of share b out of `shares`.
+__host__ __device__ inline long long ts_share_begin(long long n_tiles, int nsb, int e2, long long b, long long shares) {
+    const long long per_tile = 2LL * nsb + e2;
+    const long long t = n_tiles * per_tile * b / shares;
+    const long long q = t / per_tile, r = t - q * per_tile;
+    return q * nsb + (r < 2LL * nsb ? r / 2 : nsb);
+}
+
 struct TsSched {
     long long g, g_end;        // balanced mode: next / one-past-last (tile, super-block) index of this CTA
     int p, p_end, stride;      // forced-split mode: next piece index
@@ -48,9 +59,8 @@ struct TsSched {
         n_tiles_n = (a.N + BM - 1) / BM;
         n_tiles = n_tiles_n * ((a.M + bn - 1) / bn);
         ksplit = a.ksplit;
-        const long long total = (long long)n_tiles * nsb;
-        g = total * blockIdx.x / gridDim.x;
-        g_end = total * (blockIdx.x + 1) / gridDim.x;
+        g = ts_share_begin(n_tiles, nsb, a.e2, blockIdx.x, gridDim.x);
+        g_end = ts_share_begin(n_tiles, nsb, a.e2, blockIdx.x + 1, gridDim.x);
         p = blockIdx.x;
         p_end = n_tiles * (ksplit > 0 ? ksplit : 1);
         stride = gridDim.x;
@@ -123,20 +133,6 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *tmap, const void
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *tmap, const void *smem_src, int x, int y) {
     asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"((uint64_t)tmap), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_zero16(uint32_t taddr) {
-    const uint32_t z = 0u;
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-                 ::"r"(taddr), "r"(z) : "memory");
 }
 
 // 16 columns of this thread's TMEM lane.
@@ -273,29 +269,36 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
 #pragma unroll 1
-                for (int col = col_begin; col < col_end; col += 16) {
+                for (int col = col_begin; col < col_end; col += 32) {
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
 #ifdef TS_X_NOEPI
                     if (false) {
 #else
                     if (pc.m0 + col < a.M && xn < a.N) {
 #endif
-                        uint32_t v[16];
-                        tmem_ld16(taddr, v);
-                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile before has left
-                        __syncwarp();
+                        uint32_t v[32];
+                        tmem_ld32(taddr, v);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) epi_tile[j * 32 + lane] = __uint_as_float(v[j]);
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (add) tma_reduce_add_2d(&tmap_y, epi_tile, xn, pc.m0 + col);
-                            else tma_store_2d(&tmap_y, epi_tile, xn, pc.m0 + col);
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        for (int h = 0; h < 2; h++) {            // two staging rounds of 16 tokens
+                            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile before has left
+                            __syncwarp();
+#pragma unroll
+                            for (int j = 0; j < 16; j++) epi_tile[j * 32 + lane] = __uint_as_float(v[16 * h + j]);
+                            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                            __syncwarp();
+                            if (lane == 0 && pc.m0 + col + 16 * h < a.M) {
+                                if (add) tma_reduce_add_2d(&tmap_y, epi_tile, xn, pc.m0 + col + 16 * h);
+                                else tma_store_2d(&tmap_y, epi_tile, xn, pc.m0 + col + 16 * h);
+                                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                            }
                         }
                     }
-                    tmem_zero16(taddr);
                 }
+                // the accumulator is read out: zero this warp's columns in one go
+#pragma unroll
+                for (int col = 0; col < ECOLS; col += 32)
+                    if (col_begin + col < col_end)
+                        tmem_zero32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_begin + col));
                 if (storer) {
                     // all eight warps' stores have landed -> mark the tile (every epilogue warp takes part in every piece)
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
