@@ -94,6 +94,11 @@ extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int val
         ctx->gemv_mma = value;
         return 0;
     }
+    if (!strcmp(key, "gemv_slim")) {
+        if (value < 0 || value > 2) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_slim must be 0, 1 or 2");
+        ctx->gemv_slim = value;
+        return 0;
+    }
     if (!strcmp(key, "gemm_ksplit")) {
         if (value < 0 || value > 64) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemm_ksplit must be 0..64");
         ctx->gemm_ksplit = value;

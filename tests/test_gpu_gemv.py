@@ -171,6 +171,33 @@ def test_q4k_both_inner_loops(gpu, mode):
         gpu.set_option("gemv_mma", 1)
 
 
+@pytest.mark.parametrize("mode", [0, 2])
+def test_q4k_single_row_kernel_sizes(gpu, mode):
+    """Single-row Q4_K calls have a full-size and a half-size kernel (two CTAs per SM); force each one over
+    small, ragged and large shapes, all store forms, and the pre-quantized entry."""
+    gpu.set_option("gemv_slim", mode)
+    try:
+        for n, k in [(4096, 4096), (300, 2304), (17, 256), (14336, 4096), (4096, 14336), (5000, 8192)]:
+            for source in ("gauss", "synth"):
+                assert _gemv_case(gpu, "q4k", n, k, 1, source, seed=n % 7) < 1e-5
+        _gemv_case(gpu, "q4k", 777, 1024, 1, form=ACCUM)
+        _gemv_case(gpu, "q4k", 130, 512, 1, form=BIAS)
+        # the pre-quantized entry takes the same kernel: bit-identical to the fused call
+        n, k = 4096, 4096
+        w = gpu.load_weight(_weights("q4k", n, k, "gauss"), Q4_K, n, k)
+        xb = gpu.upload(activations(1, k, seed=9))
+        q, sc, b = gpu.alloc_bytes(k), gpu.alloc(k // 256), gpu.alloc_bytes(k // 32 * 4)
+        y1, y2 = gpu.alloc(n), gpu.alloc(n)
+        gpu.quant_q8k(xb, 1, k, q, sc, b)
+        gpu.gemv_q8k(w, q, sc, b, y1, 1)
+        gpu.gemv(w, xb, y2, 1)
+        assert np.array_equal(gpu.read(y1, np.uint32, n), gpu.read(y2, np.uint32, n))
+        for buf in (w.buf, xb, q, sc, b, y1, y2):
+            gpu.free(buf)
+    finally:
+        gpu.set_option("gemv_slim", 1)
+
+
 def test_results_are_deterministic(gpu):
     raw = _weights("q4k", 4096, 4096, "gauss")
     w = gpu.load_weight(raw, Q4_K, 4096, 4096)
