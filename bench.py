@@ -231,8 +231,8 @@ def run_ours(args) -> None:
 
     hbm_peak, _, peak_kind = measured_peaks()
     gpu = ob.B200Gpu(local)
-    if args.pdl:
-        gpu.set_option("pdl", 1)
+    if args.no_pdl:
+        gpu.set_option("pdl", 0)
     raws = ring_weights(RING, seed=rank * 1000)
     weights = [gpu.load_weight(r, ob.Q4_K, N_ROWS, K_COLS) for r in raws]
     rng = np.random.default_rng(1 + rank)
@@ -410,10 +410,8 @@ def run_case(args) -> None:
     t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
     hbm_peak, _, peak_kind = measured_peaks()
     gpu = ob.B200Gpu(0)
-    if args.pdl:
-        gpu.set_option("pdl", 1)
-    if args.depth:
-        gpu.set_option("gemv_depth", args.depth)
+    if args.no_pdl:
+        gpu.set_option("pdl", 0)
     gguf = ob.raw_bytes(t, n, k)
     ring = args.ring or max(2, int(300e6 // gguf) + 1)
     base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
@@ -445,7 +443,7 @@ def run_case(args) -> None:
     us = gpu.elapsed_ms(e0, e1) * 1e3 / (args.steps * ring)
     algo = gguf + 4 * m * (k + n)
     gbs = algo / (us * 1e-6) / 1e9
-    print(json.dumps({"case": args.case, "ring": ring, "graph": graph is not None, "pdl": bool(args.pdl), "depth": args.depth or 4, "us_per_launch": us, "GB/s": gbs,
+    print(json.dumps({"case": args.case, "ring": ring, "graph": graph is not None, "pdl": not args.no_pdl, "us_per_launch": us, "GB/s": gbs,
                       "frac": gbs / hbm_peak, "peak_kind": peak_kind, "algorithmic_bytes": algo}))
     gpu.close()
 
@@ -649,8 +647,7 @@ def main() -> None:
     ap.add_argument("--ring", type=int, default=0, help="--case: number of distinct weights (default: enough to pass L2)")
     ap.add_argument("--no-graph", action="store_true", help="--case: plain launches instead of a CUDA graph")
     ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: force the K split (0 = automatic)")
-    ap.add_argument("--depth", type=int, default=0, help="--case: stages of the GEMV cp.async ring (2..4)")
-    ap.add_argument("--pdl", action="store_true", help="launch GEMVs with programmatic dependent launch")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (default: with)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.case:

@@ -56,12 +56,14 @@ OJAS_B200_API int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out
 OJAS_B200_API void ojas_b200_destroy(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream);
 OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
-/* Options, also read once from the environment at creation the way the engine reads its OJAS_*
- * switches (crates/ojas-core/src/config.rs:1-22): "pdl" (on by default; OJAS_B200_PDL=0 or
- * set_option("pdl", 0) turns it off) launches the GEMVs with programmatic dependent launch so that a
- * kernel's weight prefetch overlaps the tail of the GEMV before it in the stream (activations and y are
- * only touched after the wait on the previous kernel; only GEMVs release their successor early); "gemm_ksplit" (0 = automatic) forces the K split of the GEMM;
- * "gemv_depth" is kept for compatibility and ignored by the two-stage GEMV ring. */
+/* Options.  "pdl" (default 1; OJAS_B200_PDL=0 in the environment at creation turns it off, the way the
+ * engine reads its OJAS_* switches, crates/ojas-core/src/config.rs:1-22): GEMVs and the GEMM are launched
+ * with programmatic dependent launch, so a kernel's weight prefetch and set-up overlap the tail of the
+ * kernel before it in the stream (activations and y are only touched after the wait on that kernel).
+ * "gemv_mma" (0, 1 = default, 2): Q4_K batches on the integer tensor-core inner loop never / for 2..8
+ * rows / also for one row.  "gemv_slim" (0, 1 = default, 2): the half-size single-row Q4_K kernel
+ * never / for small matrices / always.  "gemm_ksplit": 0 = K ranges balanced across the SMs, S > 0 =
+ * every tile's K range cut into S pieces.  "gemv_depth" is kept for compatibility and ignored. */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);

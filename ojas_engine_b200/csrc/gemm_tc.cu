@@ -26,10 +26,7 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
-#ifndef OJAS_GEMM_WQ_BUFS
-#define OJAS_GEMM_WQ_BUFS 3
-#endif
-constexpr int WQ_BUFS = OJAS_GEMM_WQ_BUFS;   // raw Q4_K nibble tiles (one super-block x 128 rows = 16 KB) in flight
+constexpr int WQ_BUFS = 3;          // raw Q4_K nibble tiles (one super-block x 128 rows = 16 KB) in flight
 constexpr int WQ_BYTES = BM * 128;
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
@@ -94,9 +91,7 @@ __device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile 
 // Single-thread roles (MMA issue, TMA) and warp leaders: one probe, then probes `nap` nanoseconds apart.  A
 // thread that spins on a barrier takes issue slots from the dequantizing warps on its scheduler, and there are
 // half a dozen waiting threads at any time; the short sleeps cost less than that contention.
-#ifndef OJAS_GEMM_NAP
-#define OJAS_GEMM_NAP 32u
-#endif
+constexpr unsigned OJAS_GEMM_NAP = 32u;
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code,
                                                unsigned nap = OJAS_GEMM_NAP) {
     if (mbar_test(bar, parity)) return true;
@@ -436,10 +431,7 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
         const size_t tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn), nsb = K / 256;
         const size_t units = args.ksplit ? tiles * (size_t)args.ksplit : tiles * nsb;
         const size_t ctas = units < (size_t)ctx->sm_count ? units : (size_t)ctx->sm_count;
-#ifndef OJAS_GEMM_E2
-#define OJAS_GEMM_E2 6
-#endif
-        args.e2 = bn > 128 ? OJAS_GEMM_E2 : 0;      // one accumulator: the drain is exposed; two: it overlaps the next tile
+        args.e2 = bn > 128 ? 6 : 0;      // one accumulator: the drain is exposed; two: it overlaps the next tile
         bool partial = args.ksplit > 1;
         if (!args.ksplit)
             for (size_t b = 1; b < ctas && !partial; b++)

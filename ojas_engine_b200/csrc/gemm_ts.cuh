@@ -16,10 +16,7 @@
 
 constexpr int TS_A_STAGES = 8;
 constexpr int TS_A_COL0 = 256;
-#ifndef TS_EPI_WARPS_N
-#define TS_EPI_WARPS_N 8
-#endif
-constexpr int TS_EPI_WARPS = TS_EPI_WARPS_N;                      // warps 0-7: epilogue (lane quarter = warp % 4)
+constexpr int TS_EPI_WARPS = 8;                      // warps 0-7: epilogue (lane quarter = warp % 4)
 constexpr int TS_WARP_DEQ0 = TS_EPI_WARPS;                        // warps 8-23: four dequantizing groups
 constexpr int TS_WARP_TMA_X = TS_WARP_DEQ0 + 16;
 constexpr int TS_WARP_MMA0 = TS_WARP_TMA_X + 1;                   // warps 25-28: MMA issue, thread c owns chunk c
@@ -217,12 +214,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     // several threads issue MMAs into one accumulator, so every MMA accumulates and the accumulators start
     // from zero (here, and again after each drain)
     if (warp < 4) {
-#ifdef TS_X_NOST
-        for (int col = 0; col < 512; col += 32) tmem_zero32(
-#else
-        for (int col = 0; col < NACC * BN; col += 32) tmem_zero32(
-#endif
-tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
+        for (int col = 0; col < NACC * BN; col += 32) tmem_zero32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -271,11 +263,7 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
 #pragma unroll 1
                 for (int col = col_begin; col < col_end; col += 32) {
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
-#ifdef TS_X_NOEPI
-                    if (false) {
-#else
                     if (pc.m0 + col < a.M && xn < a.N) {
-#endif
                         uint32_t v[32];
                         tmem_ld32(taddr, v);
 #pragma unroll
@@ -402,26 +390,22 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
                 }
                 if (tr_on) TS_TR(1 + (c >> 1), 2, wc * 4 + c);
                 TS_PROG(wc * 16 + 2);
-                uint32_t o[16];
-                auto convert = [&](int half) {
+                uint32_t o[16], o1[16];
+                auto convert = [&](int half, uint32_t (&out)[16]) {
                     if (!live) {
 #pragma unroll
-                        for (int q = 0; q < 16; q++) o[q] = 0u;
+                        for (int q = 0; q < 16; q++) out[q] = 0u;
                     } else if (TYPE == OJAS_B200_Q4_K) {
-                        dequant_q4k_half(cA, cB, H, c, half, o);
+                        dequant_q4k_half(cA, cB, H, c, half, out);
                     } else if (TYPE == OJAS_B200_Q6_K) {
-                        dequant_q6k_half(cA, cB, cC, ce0, ce1, half, o);
+                        dequant_q6k_half(cA, cB, cC, ce0, ce1, half, out);
                     } else if (half == 0) {
-                        dequant_q80_half(cA, cB, ce0, o);
+                        dequant_q80_half(cA, cB, ce0, out);
                     } else {
-                        dequant_q80_half(cC, cD, ce0 >> 16, o);
+                        dequant_q80_half(cC, cD, ce0 >> 16, out);
                     }
                 };
-#ifndef TS_X_NOCONV
-                convert(0);
-#else
-                for (int q = 0; q < 16; q++) o[q] = 0x3c003c00u + ((cA.x + cB.y) & 0x00ff00ffu);
-#endif
+                convert(0, o);
                 if (STAGED_W) {                                          // the raw tile is in registers: hand the buffer back
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&wq_empty[wb]);
@@ -432,17 +416,9 @@ tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col);
                 tc_fence_after();
                 if (tr_on) TS_TR(1 + (c >> 1), 4, wc * 4 + c);
                 TS_PROG(wc * 16 + 4);
-#ifndef TS_X_NOST
-                tmem_st16(tmem_row + (uint32_t)(aslot * 32), o);
-#endif
-#ifndef TS_X_NOCONV
-                convert(1);
-#endif
-#ifndef TS_X_NOST
-                tmem_st16(tmem_row + (uint32_t)(aslot * 32 + 16), o);
-#else
-                asm volatile("" ::"r"(o[0] ^ o[1] ^ o[2] ^ o[3] ^ o[4] ^ o[5] ^ o[6] ^ o[7] ^ o[8] ^ o[9] ^ o[10] ^ o[11] ^ o[12] ^ o[13] ^ o[14] ^ o[15]));
-#endif
+                tmem_st16(tmem_row + (uint32_t)(aslot * 32), o);      // (one 32-column store of both halves measured slower)
+                convert(1, o1);
+                tmem_st16(tmem_row + (uint32_t)(aslot * 32 + 16), o1);
                 if (tr_on) TS_TR(1 + (c >> 1), 6, wc * 4 + c);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 if (tr_on) TS_TR(1 + (c >> 1), 7, wc * 4 + c);

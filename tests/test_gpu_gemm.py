@@ -72,6 +72,24 @@ def test_config3_q4k_prefill_m2048(gpu):
     _gemm_case(gpu, "q4k", 2048, 4096, 4096, seed=4)
 
 
+def test_repeated_calls_reuse_the_tile_marks(gpu):
+    """Tiles whose K range is shared by several CTAs are marked "stored" with a per-launch serial number in
+    memory the context owns; launches in a row (same and different shapes) must not see each other's marks."""
+    t, n, k = Q4_K, 1024, 4096            # 8 tiles x 16 super-blocks over 128 CTAs: every tile is shared
+    raw = gauss_weights(t, n, k, seed=5)
+    w = gpu.load_weight(raw, t, n, k)
+    for m in (300, 300, 64, 300):
+        x = activations(m, k, seed=m)
+        xb = gpu.upload(x)
+        yb = gpu.upload(np.full((m, n), 7.0, np.float32))      # stale contents must not leak into the result
+        gpu.gemm(w, xb, yb, m)
+        got = gpu.read(yb, np.float32, m * n).reshape(m, n)
+        assert rel_l2(got, oracle.matmul_kq(raw, t, n, k, x)) < TOL
+        gpu.free(xb)
+        gpu.free(yb)
+    gpu.free(w.buf)
+
+
 def test_gemm_agrees_with_exact_integer_path(gpu):
     """The f16 tensor-core result against the GEMV kernel's exact integer block dots on the same
     inputs (reduced shape): the only differences are the f16 roundings of the two operands."""
