@@ -378,7 +378,7 @@ def run_ours(args) -> None:
                        "parallelism": "single GPU" if world == 1 else f"column-parallel row shards x{world}, one NCCL all-gather per step"},
             "pct_of_8TBps": value / world / 8000.0,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "gemv_q4k_kernel<1,false,false>",
+                         "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "gemv_q4k_slim_kernel<false>",
                          "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH, "us_per_launch": us_per_launch},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary, "parity_rel_l2_vs_oracle": parity, "extras": extras,
