@@ -765,6 +765,84 @@ static int gemv_mma_launch(ojas_b200_ctx *ctx, bool preq, GemvArgs a) {
     return launch_gemv_threads(ctx, gemv_q4k_mma_kernel<16, false>, a, grid, 512, smem, "gemv_q4k_mma");
 }
 
+// ---- the same for Q6_K: 16 or 8 warps (a stage is 3840 bytes), per-16 activation sums
+static size_t mma6_smem_bytes(int warps, size_t M, size_t K, size_t rows_max, int S) {
+    const size_t nsb = K / 256, tiles = (rows_max + 15) / 16;
+    return (size_t)warps * 2 * MMA6_STAGE_BYTES + ((M * (K + MMA_XPAD) + 15) & ~(size_t)15) + (size_t)sx_floats((int)M, (int)nsb) * 4 +
+           M * nsb * 16 * 4 + (S > 1 ? tiles * S * 128 * 4 : 0) + 16;
+}
+
+static int mma6_plan(ojas_b200_ctx *ctx, GemvArgs &a, int &grid, size_t &smem) {
+    grid = ctx->sm_count < a.N ? ctx->sm_count : a.N;
+    const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
+    a.rows_base = a.N / grid;
+    a.rows_rem = a.N % grid;
+    for (int warps = 16; warps >= 8; warps >>= 1) {
+        a.S = mma_segments(rows_max, (size_t)a.K / 256, warps);
+        smem = mma6_smem_bytes(warps, (size_t)a.M, (size_t)a.K, rows_max, a.S);
+        if (smem <= (size_t)ctx->smem_optin) return warps;
+    }
+    return 0;
+}
+
+static int gemv_mma6_launch(ojas_b200_ctx *ctx, bool preq, GemvArgs a) {
+    int grid;
+    size_t smem;
+    const int warps = mma6_plan(ctx, a, grid, smem);
+    if (warps == 0) return 1;
+    if (warps == 16) {
+        if (preq) return launch_gemv_threads(ctx, gemv_q6k_mma_kernel<16, true>, a, grid, 512, smem, "gemv_q6k_mma_q8k");
+        return launch_gemv_threads(ctx, gemv_q6k_mma_kernel<16, false>, a, grid, 512, smem, "gemv_q6k_mma");
+    }
+    if (preq) return launch_gemv_threads(ctx, gemv_q6k_mma_kernel<8, true>, a, grid, 256, smem, "gemv_q6k_mma_q8k");
+    return launch_gemv_threads(ctx, gemv_q6k_mma_kernel<8, false>, a, grid, 256, smem, "gemv_q6k_mma");
+}
+
+// ---- Q8_0 batches on the f16 tensor-core path: activations as two f16 terms (4 bytes per value, like fp32)
+static size_t mma8_smem_bytes(int warps, size_t M, size_t K, size_t rows_max, int S) {
+    const size_t nsb = K / 256, tiles = (rows_max + 15) / 16;
+    return (size_t)warps * 2 * MMA8_STAGE_BYTES + 2 * M * (K + MMA8_XPAD) * 2 + (size_t)sx_floats((int)M, (int)nsb) * 4 +
+           (S > 1 ? tiles * S * 128 * 4 : 0) + 16;
+}
+
+static int mma8_plan(ojas_b200_ctx *ctx, GemvArgs &a, int &grid, size_t &smem) {
+    grid = ctx->sm_count < a.N ? ctx->sm_count : a.N;
+    const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
+    a.rows_base = a.N / grid;
+    a.rows_rem = a.N % grid;
+    for (int warps = 16; warps >= 8; warps >>= 1) {
+        a.S = mma_segments(rows_max, (size_t)a.K / 256, warps);
+        smem = mma8_smem_bytes(warps, (size_t)a.M, (size_t)a.K, rows_max, a.S);
+        if (smem <= (size_t)ctx->smem_optin) return warps;
+    }
+    return 0;
+}
+
+// Batches of up to eight rows; a batch whose activations do not fit in shared memory is cut into smaller
+// ones.  Returns 1 if not even one row fits (the caller falls back to the per-lane kernel).
+static int gemv_mma8_run(ojas_b200_ctx *ctx, GemvArgs args, size_t M) {
+    int cap = 0, grid = 0;
+    size_t smem = 0;
+    for (int m = 8; m >= 1 && !cap; m >>= 1) {
+        GemvArgs t = args;
+        t.M = m;
+        if (mma8_plan(ctx, t, grid, smem)) cap = m;
+    }
+    if (!cap) return 1;
+    for (size_t m0 = 0; m0 < M; m0 += (size_t)cap) {
+        GemvArgs b = args;
+        b.M = (int)((M - m0) < (size_t)cap ? (M - m0) : (size_t)cap);
+        b.x = args.x + m0 * args.K;
+        b.y = args.y + m0 * args.N;
+        const int warps = mma8_plan(ctx, b, grid, smem);
+        int rc;
+        if (warps == 16) rc = launch_gemv_threads(ctx, gemv_q80_mma_kernel<16>, b, grid, 512, smem, "gemv_q80_mma");
+        else rc = launch_gemv_threads(ctx, gemv_q80_mma_kernel<8>, b, grid, 256, smem, "gemv_q80_mma");
+        if (rc) return rc;
+    }
+    return 0;
+}
+
 static int pick_mt(size_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
 
 // One launch over at most 8 activation rows.
@@ -861,6 +939,16 @@ static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args,
         const int rc = gemv_mma_launch(ctx, preq, b);
         if (rc != 1) return rc;
     }
+    if (type == OJAS_B200_Q8_0 && !preq && ctx->gemv_mma != 0 && (M >= 2 || ctx->gemv_mma == 2)) {
+        const int rc = gemv_mma8_run(ctx, args, M);
+        if (rc != 1) return rc;
+    }
+    if (type == OJAS_B200_Q6_K && ctx->gemv_mma != 0 && (M >= 2 || ctx->gemv_mma == 2)) {
+        GemvArgs b = args;
+        b.M = (int)M;
+        const int rc = gemv_mma6_launch(ctx, preq, b);
+        if (rc != 1) return rc;
+    }
     const int cap = gemv_max_mt(ctx, type, (size_t)args.K, (size_t)args.N);
     if (cap == 0) return ojas_fail(ctx, OJAS_B200_E_LIMIT, "gemv: K=%d does not fit in shared memory", args.K);
     const size_t nsb = (size_t)args.K / 256;
@@ -902,6 +990,15 @@ int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &pla
         const int warps = mma_plan(ctx, b, g2, smem2);
         if (warps == 32) return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<32>, b, g2, 1024, smem2, "gemv_q4k_mma_grouped");
         if (warps == 16) return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<16>, b, g2, 512, smem2, "gemv_q4k_mma_grouped");
+    }
+    if (type == OJAS_B200_Q6_K && ctx->gemv_mma != 0) {
+        GemvArgs b = a;
+        b.M = 8;
+        int g2;
+        size_t smem2;
+        const int warps = mma6_plan(ctx, b, g2, smem2);
+        if (warps == 16) return launch_gemv_threads(ctx, gemv_q6k_mma_grouped_kernel<16>, b, g2, 512, smem2, "gemv_q6k_mma_grouped");
+        if (warps == 8) return launch_gemv_threads(ctx, gemv_q6k_mma_grouped_kernel<8>, b, g2, 256, smem2, "gemv_q6k_mma_grouped");
     }
     const int mt = gemv_max_mt(ctx, type, K, N);      // rows per pass: as many as fit beside the weight ring
     if (mt < 2) return ojas_fail(ctx, OJAS_B200_E_LIMIT, "grouped gemv: K=%zu does not fit in shared memory", K);

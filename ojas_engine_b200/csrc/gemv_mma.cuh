@@ -214,3 +214,417 @@ __global__ void __launch_bounds__(WARPS * 32, 1) gemv_q4k_mma_grouped_kernel(con
         __syncthreads();
     }
 }
+
+// ============================================================================ Q6_K
+// The same scheme for Q6_K (dot_q6k, crates/ojas-cpu/src/cpu_math.rs:674-722): a sub-block is 16 weights with
+// its own int8 scale, so the MMA is m16n8k16 (u8 x s8): A = the 6-bit values 0..63 of 16 rows x one sub-block,
+// B = 16 int8 activations of up to 8 tokens.  The accumulator is the exact sum q*x; the -32 offset of the
+// format is applied as -32 * (sum of the 16 activations), an integer too.  Per super-block and (row, token):
+// isum = sum_j sc_j * (dot_j - 32 * xsum_j), exactly the integer the dp4a kernel forms.
+//
+// Stage = 16 rows x one super-block: low nibbles 16 x 128 B (row stride 144), top bits 16 x 64 B (row stride
+// 80), sub-scales 16 x 16 B: 3840 bytes, copied by cp.async; the sixteen f16 super-block scales travel in a
+// register of lanes 0..15, loaded one step ahead.
+constexpr int MMA6_LO_STRIDE = 144, MMA6_HI_STRIDE = 80;
+constexpr int MMA6_HI_OFF = 16 * MMA6_LO_STRIDE;                 // 2304
+constexpr int MMA6_SC_OFF = MMA6_HI_OFF + 16 * MMA6_HI_STRIDE;   // 3584
+constexpr int MMA6_STAGE_BYTES = MMA6_SC_OFF + 256;              // 3840
+
+__device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %8, %9, %10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+// Activations in natural order with per-16 sums: xq [M][K + 16] int8, sx [M][nsb] f32, bs [M][nsb * 16] i32.
+template <int WARPS, bool PREQ>
+__device__ __forceinline__ void stage_q8k_rows16(const GemvArgs &a, unsigned char *xq, float *sx, int *bs, int nsb, int xstride) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (!PREQ) {
+        for (int u = warp; u < a.M * nsb; u += WARPS) {
+            const int m = u / nsb, sb = u - m * nsb;
+            const Q8kLane ql = quant_q8k_warp(a.x + (size_t)m * a.K + (size_t)sb * 256, lane);
+            *reinterpret_cast<uint2 *>(xq + (size_t)m * xstride + sb * 256 + lane * 8) = ql.packed;
+            const int s = ql.sum8 + __shfl_xor_sync(0xffffffffu, ql.sum8, 1);
+            if ((lane & 1) == 0) bs[(m * nsb + sb) * 16 + (lane >> 1)] = s;
+            if (lane == 0) sx[m * nsb + sb] = ql.scale;
+        }
+    } else {
+        const int units = nsb * 16;
+        for (int idx = threadIdx.x; idx < a.M * units; idx += blockDim.x) {
+            const int m = idx / units, rem = idx - m * units;
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(a.q + (size_t)src_row(a, m) * a.K) + rem);
+            *reinterpret_cast<uint4 *>(xq + (size_t)m * xstride + rem * 16) = v;
+            int s = __dp4a((int)v.x, 0x01010101, 0);
+            s = __dp4a((int)v.y, 0x01010101, s);
+            s = __dp4a((int)v.z, 0x01010101, s);
+            s = __dp4a((int)v.w, 0x01010101, s);
+            bs[m * units + rem] = s;
+        }
+        for (int idx = threadIdx.x; idx < a.M * nsb; idx += blockDim.x) {
+            const int m = idx / nsb;
+            sx[idx] = __ldg(a.scales + (size_t)src_row(a, m) * nsb + (idx - m * nsb));
+        }
+    }
+}
+
+template <int WARPS, bool PREQ>
+__device__ __forceinline__ void gemv_q6k_mma_body(const GemvArgs &a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nsb = a.K >> 8, S = a.S, SP = nsb / S;
+    const int xstride = a.K + MMA_XPAD;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    unsigned char *ring = smem + (size_t)warp * 2 * MMA6_STAGE_BYTES;
+    unsigned char *xq = smem + (size_t)WARPS * 2 * MMA6_STAGE_BYTES;
+    float *sx = reinterpret_cast<float *>(xq + (((size_t)a.M * xstride + 15) & ~(size_t)15));
+    int *bs = reinterpret_cast<int *>(sx + sx_floats(a.M, nsb));
+    float *part = reinterpret_cast<float *>(bs + a.M * nsb * 16);
+
+    int r_begin, R;
+    cta_rows(a, r_begin, R);
+    const int n_tiles = (R + 15) >> 4, n_units = n_tiles * S;
+    const uint4 *lo = reinterpret_cast<const uint4 *>(a.w.p0);
+    const uint4 *hi = reinterpret_cast<const uint4 *>(a.w.p1);
+    const uint4 *scp = reinterpret_cast<const uint4 *>(a.w.p2);
+    const unsigned short *dp = reinterpret_cast<const unsigned short *>(a.w.p3);
+
+    struct It { int u, j; };
+    uint32_t d_next = 0u;                                     // lanes 0..15: f16 d of row (lane) of the step in flight
+    auto issue = [&](const It &it, int stage) {
+        d_next = 0u;
+        if (it.u < n_units) {
+            const int tile = it.u / S, seg = it.u - tile * S;
+            const int sb = seg * SP + it.j;
+            unsigned char *st = ring + stage * MMA6_STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {                     // 16 rows x 8 pieces of low nibbles
+                const int p = lane + 32 * i, row = p >> 3, piece = p & 7;
+                int gr = tile * 16 + row;
+                gr = gr < R ? gr : R - 1;                     // rows past the range repeat the last one (never stored)
+                cp_async16(st + row * MMA6_LO_STRIDE + piece * 16, lo + ((size_t)(r_begin + gr) * nsb + sb) * 8 + piece);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++) {                     // 16 rows x 4 pieces of top bits
+                const int p = lane + 32 * i, row = p >> 2, piece = p & 3;
+                int gr = tile * 16 + row;
+                gr = gr < R ? gr : R - 1;
+                cp_async16(st + MMA6_HI_OFF + row * MMA6_HI_STRIDE + piece * 16, hi + ((size_t)(r_begin + gr) * nsb + sb) * 4 + piece);
+            }
+            if (lane < 16) {
+                int gr = tile * 16 + lane;
+                gr = gr < R ? gr : R - 1;
+                const size_t blk = (size_t)(r_begin + gr) * nsb + sb;
+                cp_async16(st + MMA6_SC_OFF + lane * 16, scp + blk);
+                d_next = __ldg(dp + blk);
+            }
+        }
+        cp_async_commit();
+    };
+    auto next = [&](It &it) {
+        if (++it.j == SP) { it.j = 0; it.u += WARPS; }
+    };
+
+    It ii{warp, 0}, ic{warp, 0};
+    issue(ii, 0);
+    next(ii);
+    grid_dependency_wait();
+    stage_q8k_rows16<WARPS, PREQ>(a, xq, sx, bs, nsb, xstride);
+    __syncthreads();
+    grid_launch_dependents();
+
+    const int t0 = 2 * q, t1 = 2 * q + 1;
+    const bool tok_b = g < a.M, tok0 = t0 < a.M, tok1 = t1 < a.M;
+    const unsigned char *xb = xq + (size_t)(tok_b ? g : 0) * xstride + 4 * q;
+    const int *bs0 = bs + (tok0 ? t0 : 0) * nsb * 16, *bs1 = bs + (tok1 ? t1 : 0) * nsb * 16;
+    const float *sx0 = sx + (tok0 ? t0 : 0) * nsb, *sx1 = sx + (tok1 ? t1 : 0) * nsb;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int stage = 0;
+    while (ic.u < n_units) {
+        const uint32_t d_cur = d_next;                        // belongs to the step about to be consumed
+        issue(ii, stage ^ 1);
+        next(ii);
+        cp_async_wait<1>();
+        __syncwarp();
+        const int tile = ic.u / S, seg = ic.u - tile * S;
+        const int sb = seg * SP + ic.j;
+        const unsigned char *st = ring + stage * MMA6_STAGE_BYTES;
+        const unsigned char *la = st + g * MMA6_LO_STRIDE + 4 * q, *lb = la + 8 * MMA6_LO_STRIDE;
+        const unsigned char *ha = st + MMA6_HI_OFF + g * MMA6_HI_STRIDE + 4 * q, *hb = ha + 8 * MMA6_HI_STRIDE;
+        const uint4 Sa = *reinterpret_cast<const uint4 *>(st + MMA6_SC_OFF + g * 16);
+        const uint4 Sb = *reinterpret_cast<const uint4 *>(st + MMA6_SC_OFF + (g + 8) * 16);
+        const uint32_t sca[4] = {Sa.x, Sa.y, Sa.z, Sa.w}, scb[4] = {Sb.x, Sb.y, Sb.z, Sb.w};
+        int isum[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            // chunk c: low-nibble pieces h = 0 (weights 64c+0..15 | 64c+32..47) and h = 1 (64c+16..31 | 64c+48..63)
+            const uint32_t la0 = *reinterpret_cast<const uint32_t *>(la + c * 16), la1 = *reinterpret_cast<const uint32_t *>(la + 64 + c * 16);
+            const uint32_t lb0 = *reinterpret_cast<const uint32_t *>(lb + c * 16), lb1 = *reinterpret_cast<const uint32_t *>(lb + 64 + c * 16);
+            const uint32_t hwa = *reinterpret_cast<const uint32_t *>(ha + c * 16), hwb = *reinterpret_cast<const uint32_t *>(hb + c * 16);
+            int4 u0 = make_int4(0, 0, 0, 0), u1 = u0;         // per-16 activation sums of the chunk's four sub-blocks
+            if (tok0) u0 = *reinterpret_cast<const int4 *>(bs0 + sb * 16 + 4 * c);
+            if (tok1) u1 = *reinterpret_cast<const int4 *>(bs1 + sb * 16 + 4 * c);
+            const int x0[4] = {u0.x, u0.y, u0.z, u0.w}, x1[4] = {u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {                     // sub-block j = 4c + t: weights 64c + 16t .. + 15
+                const uint32_t na = (t & 1) ? la1 : la0, nb = (t & 1) ? lb1 : lb0;
+                const uint32_t a0 = ((na >> (4 * (t >> 1))) & 0x0f0f0f0fu) | (t < 2 ? ((hwa << (4 - 2 * t)) & 0x30303030u) : ((hwa >> (2 * t - 4)) & 0x30303030u));
+                const uint32_t a1 = ((nb >> (4 * (t >> 1))) & 0x0f0f0f0fu) | (t < 2 ? ((hwb << (4 - 2 * t)) & 0x30303030u) : ((hwb >> (2 * t - 4)) & 0x30303030u));
+                uint32_t b0 = 0u;
+                if (tok_b) b0 = *reinterpret_cast<const uint32_t *>(xb + sb * 256 + (4 * c + t) * 16);
+                int d[4];
+                mma_u8s8_k16(d, a0, a1, b0);                  // exact sums q*x: rows g, g+8 x tokens 2q, 2q+1
+                const int s_a = (int)(signed char)((sca[c] >> (8 * t)) & 0xffu), s_b = (int)(signed char)((scb[c] >> (8 * t)) & 0xffu);
+                isum[0] += s_a * (d[0] - 32 * x0[t]); isum[1] += s_a * (d[1] - 32 * x1[t]);
+                isum[2] += s_b * (d[2] - 32 * x0[t]); isum[3] += s_b * (d[3] - 32 * x1[t]);
+            }
+        }
+        const float da = f16_bits_to_f32(__shfl_sync(0xffffffffu, d_cur, g)), db = f16_bits_to_f32(__shfl_sync(0xffffffffu, d_cur, g + 8));
+        const float s0 = tok0 ? sx0[sb] : 0.f, s1 = tok1 ? sx1[sb] : 0.f;
+        acc[0] += (s0 * da) * (float)isum[0];
+        acc[1] += (s1 * da) * (float)isum[1];
+        acc[2] += (s0 * db) * (float)isum[2];
+        acc[3] += (s1 * db) * (float)isum[3];
+        __syncwarp();
+        if (ic.j + 1 == SP) {
+            const int row_a = tile * 16 + g, row_b = row_a + 8;
+            if (S == 1) {
+                if (tok0 && row_a < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_a, acc[0], a.form, a.bias, r_begin + row_a);
+                if (tok1 && row_a < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_a, acc[1], a.form, a.bias, r_begin + row_a);
+                if (tok0 && row_b < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_b, acc[2], a.form, a.bias, r_begin + row_b);
+                if (tok1 && row_b < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_b, acc[3], a.form, a.bias, r_begin + row_b);
+            } else {
+                float *pp = part + (size_t)ic.u * 128;
+                pp[g * 8 + t0] = acc[0]; pp[g * 8 + t1] = acc[1];
+                pp[(g + 8) * 8 + t0] = acc[2]; pp[(g + 8) * 8 + t1] = acc[3];
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        }
+        next(ic);
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+    if (S > 1) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n_tiles * 128; idx += blockDim.x) {
+            const int tile = idx >> 7, row = (idx >> 3) & 15, tok = idx & 7;
+            const int r = tile * 16 + row;
+            if (r >= R || tok >= a.M) continue;
+            float s = 0.f;
+            for (int seg = 0; seg < S; seg++) s += part[(size_t)(tile * S + seg) * 128 + row * 8 + tok];
+            store_form(a.y + (size_t)tok * a.N + r_begin + r, s, a.form, a.bias, r_begin + r);
+        }
+    }
+}
+
+template <int WARPS, bool PREQ>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_q6k_mma_kernel(const GemvArgs a) { gemv_q6k_mma_body<WARPS, PREQ>(a); }
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_q6k_mma_grouped_kernel(const GemvArgs a) {
+    const int count = __ldg(a.grp_count), off = __ldg(a.grp_offset);
+    for (int mb = 0; mb < count; mb += 8) {
+        GemvArgs b = a;
+        b.M = count - mb < 8 ? count - mb : 8;
+        if (a.row_index) b.row_index = a.row_index + off + mb;
+        else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
+        b.y = a.y + (size_t)(off + mb) * a.N;
+        gemv_q6k_mma_body<WARPS, true>(b);
+        __syncthreads();
+    }
+}
+
+// ============================================================================ Q8_0
+// Q8_0 keeps fp32 activations (dot_q80, crates/ojas-cpu/src/cpu_math.rs:971-981): per 32-weight block
+// acc = sum q_i * x_i in fp32, then sum += d * acc.  Here the block sum comes from the f16 tensor-core MMA
+// (m16n8k16, fp32 accumulate) without giving up fp32 accuracy: the int8 weights are exact in f16, and each
+// activation enters as two f16 terms x = hi + lo (hi = f16(x'), lo = f16(x' - hi), x' = x scaled by a power of
+// two per 256 values so that neither term overflows or underflows); every product is exact in fp32, so what
+// remains is fp32 summation order, as in the per-lane FMA kernel.  Two MMAs (hi, lo) per 16 weights.
+//
+// Stage = 16 rows x one super-block: 16 x 256 int8 (row stride 288 so that the 8-byte fragment reads of the
+// eight rows of a half-warp fall in different banks) + 16 x 8 f16 block scales: 4864 bytes.
+// k order inside a 32-block: lane q owns bytes 8q .. 8q+7; the first four are its share of the first MMA
+// (logical k 2q, 2q+1, 2q+8, 2q+9), the last four of the second; the activations use the same order.
+constexpr int MMA8_ROW_STRIDE = 288;
+constexpr int MMA8_D_OFF = 16 * MMA8_ROW_STRIDE;          // 4608
+constexpr int MMA8_STAGE_BYTES = MMA8_D_OFF + 256;        // 4864
+constexpr int MMA8_XPAD = 32;                             // activation rows are K + 32 halves apart (bank spread)
+
+__device__ __forceinline__ void mma_f16_k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// two int8 (byte pair `sel` of w ^ 0x80808080) -> half2, exactly: 0x6400 | (b + 128) is 1152 + b
+__device__ __forceinline__ uint32_t s8x2_to_h2(uint32_t w_biased, int sel) {
+    const uint32_t t = sel == 0 ? __byte_perm(w_biased, 0x64646464u, 0x4140) : __byte_perm(w_biased, 0x64646464u, 0x4342);
+    const uint32_t k1152 = 0x64806480u;
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2 *>(&t), *reinterpret_cast<const __half2 *>(&k1152));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+template <int WARPS>
+__device__ __forceinline__ void gemv_q80_mma_body(const GemvArgs &a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int nsb = a.K >> 8, S = a.S, SP = nsb / S;
+    const int xstride = a.K + MMA8_XPAD;                      // halves
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    unsigned char *ring = smem + (size_t)warp * 2 * MMA8_STAGE_BYTES;
+    __half *xh = reinterpret_cast<__half *>(smem + (size_t)WARPS * 2 * MMA8_STAGE_BYTES);   // [M][K + 32]
+    __half *xl = xh + (size_t)a.M * xstride;
+    float *fx = reinterpret_cast<float *>(xl + (size_t)a.M * xstride);                      // [M][nsb] power-of-two factors
+    float *part = fx + sx_floats(a.M, nsb);
+
+    int r_begin, R;
+    cta_rows(a, r_begin, R);
+    const int n_tiles = (R + 15) >> 4, n_units = n_tiles * S;
+    const uint4 *qp = reinterpret_cast<const uint4 *>(a.w.p0);
+    const uint4 *dp = reinterpret_cast<const uint4 *>(a.w.p1);                              // 8 f16 per (row, super-block)
+
+    struct It { int u, j; };
+    auto issue = [&](const It &it, int stage) {
+        if (it.u < n_units) {
+            const int tile = it.u / S, seg = it.u - tile * S;
+            const int sb = seg * SP + it.j;
+            unsigned char *st = ring + stage * MMA8_STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {                     // 16 rows x 16 pieces of 16 int8
+                const int p = lane + 32 * i, row = p >> 4, piece = p & 15;
+                int gr = tile * 16 + row;
+                gr = gr < R ? gr : R - 1;                     // rows past the range repeat the last one (never stored)
+                cp_async16(st + row * MMA8_ROW_STRIDE + piece * 16, qp + ((size_t)(r_begin + gr) * nsb + sb) * 16 + piece);
+            }
+            if (lane < 16) {
+                int gr = tile * 16 + lane;
+                gr = gr < R ? gr : R - 1;
+                cp_async16(st + MMA8_D_OFF + lane * 16, dp + (size_t)(r_begin + gr) * nsb + sb);
+            }
+        }
+        cp_async_commit();
+    };
+    auto next = [&](It &it) {
+        if (++it.j == SP) { it.j = 0; it.u += WARPS; }
+    };
+
+    It ii{warp, 0}, ic{warp, 0};
+    issue(ii, 0);
+    next(ii);
+    grid_dependency_wait();
+    // activations: one warp per (row, 256 values); lane l owns values 8l .. 8l+7
+    for (int u = warp; u < a.M * nsb; u += WARPS) {
+        const int m = u / nsb, sb = u - m * nsb;
+        const float4 p0 = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)m * a.K + (size_t)sb * 256) + lane * 2);
+        const float4 p1 = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)m * a.K + (size_t)sb * 256) + lane * 2 + 1);
+        const float v[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        float mx = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        // bring the largest magnitude into [2^13, 2^14): hi never overflows f16 and lo stays normal for all
+        // but terms 2^-24 below it; mx == 0, infinities and NaNs keep a factor of 1
+        int e = 0;
+        if (mx > 0.0f && mx < 3.0e38f) e = ilogbf(mx) - 13;
+        e = e < -100 ? -100 : e;                              // keep 2^-e finite for vanishing blocks
+        const float down = ldexpf(1.0f, -e), up = ldexpf(1.0f, e);
+        uint32_t hw[4], lw[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float s0 = v[2 * i] * down, s1 = v[2 * i + 1] * down;
+            const __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
+            const __half l0 = __float2half_rn(s0 - __half2float(h0)), l1 = __float2half_rn(s1 - __half2float(h1));
+            hw[i] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+            lw[i] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+        }
+        *reinterpret_cast<uint4 *>(xh + (size_t)m * xstride + sb * 256 + lane * 8) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        *reinterpret_cast<uint4 *>(xl + (size_t)m * xstride + sb * 256 + lane * 8) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        if (lane == 0) fx[m * nsb + sb] = up;
+    }
+    __syncthreads();
+    grid_launch_dependents();
+
+    const int t0 = 2 * q, t1 = 2 * q + 1;
+    const bool tok_b = g < a.M, tok0 = t0 < a.M, tok1 = t1 < a.M;
+    const __half *xhb = xh + (size_t)(tok_b ? g : 0) * xstride + 8 * q;
+    const __half *xlb = xl + (size_t)(tok_b ? g : 0) * xstride + 8 * q;
+    const float *f0 = fx + (tok0 ? t0 : 0) * nsb, *f1 = fx + (tok1 ? t1 : 0) * nsb;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int stage = 0;
+    while (ic.u < n_units) {
+        issue(ii, stage ^ 1);
+        next(ii);
+        cp_async_wait<1>();
+        __syncwarp();
+        const int tile = ic.u / S, seg = ic.u - tile * S;
+        const int sb = seg * SP + ic.j;
+        const unsigned char *st = ring + stage * MMA8_STAGE_BYTES;
+        const unsigned char *wa = st + g * MMA8_ROW_STRIDE + 8 * q, *wb = wa + 8 * MMA8_ROW_STRIDE;
+        const uint4 Da = *reinterpret_cast<const uint4 *>(st + MMA8_D_OFF + g * 16);
+        const uint4 Db = *reinterpret_cast<const uint4 *>(st + MMA8_D_OFF + (g + 8) * 16);
+        const uint32_t dwa[4] = {Da.x, Da.y, Da.z, Da.w}, dwb[4] = {Db.x, Db.y, Db.z, Db.w};
+        float sbsum[4] = {0.f, 0.f, 0.f, 0.f};                // sum over the super-block's blocks of d * acc
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const uint2 A2 = *reinterpret_cast<const uint2 *>(wa + b * 32), B2 = *reinterpret_cast<const uint2 *>(wb + b * 32);
+            uint4 XH = make_uint4(0u, 0u, 0u, 0u), XL = XH;
+            if (tok_b) {
+                XH = *reinterpret_cast<const uint4 *>(xhb + sb * 256 + b * 32);
+                XL = *reinterpret_cast<const uint4 *>(xlb + sb * 256 + b * 32);
+            }
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const uint32_t wa_ = A2.x ^ 0x80808080u, wb_ = B2.x ^ 0x80808080u;
+                const uint32_t a0 = s8x2_to_h2(wa_, 0), a2 = s8x2_to_h2(wa_, 1), a1 = s8x2_to_h2(wb_, 0), a3 = s8x2_to_h2(wb_, 1);
+                mma_f16_k16(c, a0, a1, a2, a3, XH.x, XH.y);
+                mma_f16_k16(c, a0, a1, a2, a3, XL.x, XL.y);
+            }
+            {
+                const uint32_t wa_ = A2.y ^ 0x80808080u, wb_ = B2.y ^ 0x80808080u;
+                const uint32_t a0 = s8x2_to_h2(wa_, 0), a2 = s8x2_to_h2(wa_, 1), a1 = s8x2_to_h2(wb_, 0), a3 = s8x2_to_h2(wb_, 1);
+                mma_f16_k16(c, a0, a1, a2, a3, XH.z, XH.w);
+                mma_f16_k16(c, a0, a1, a2, a3, XL.z, XL.w);
+            }
+            const float da = f16_bits_to_f32(dwa[b >> 1] >> (16 * (b & 1))), db = f16_bits_to_f32(dwb[b >> 1] >> (16 * (b & 1)));
+            sbsum[0] = fmaf(da, c[0], sbsum[0]); sbsum[1] = fmaf(da, c[1], sbsum[1]);
+            sbsum[2] = fmaf(db, c[2], sbsum[2]); sbsum[3] = fmaf(db, c[3], sbsum[3]);
+        }
+        const float s0 = tok0 ? f0[sb] : 0.f, s1 = tok1 ? f1[sb] : 0.f;
+        acc[0] = fmaf(s0, sbsum[0], acc[0]); acc[1] = fmaf(s1, sbsum[1], acc[1]);
+        acc[2] = fmaf(s0, sbsum[2], acc[2]); acc[3] = fmaf(s1, sbsum[3], acc[3]);
+        __syncwarp();
+        if (ic.j + 1 == SP) {
+            const int row_a = tile * 16 + g, row_b = row_a + 8;
+            if (S == 1) {
+                if (tok0 && row_a < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_a, acc[0], a.form, a.bias, r_begin + row_a);
+                if (tok1 && row_a < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_a, acc[1], a.form, a.bias, r_begin + row_a);
+                if (tok0 && row_b < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_b, acc[2], a.form, a.bias, r_begin + row_b);
+                if (tok1 && row_b < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_b, acc[3], a.form, a.bias, r_begin + row_b);
+            } else {
+                float *pp = part + (size_t)ic.u * 128;
+                pp[g * 8 + t0] = acc[0]; pp[g * 8 + t1] = acc[1];
+                pp[(g + 8) * 8 + t0] = acc[2]; pp[(g + 8) * 8 + t1] = acc[3];
+            }
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+        }
+        next(ic);
+        stage ^= 1;
+    }
+    cp_async_wait<0>();
+    if (S > 1) {
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n_tiles * 128; idx += blockDim.x) {
+            const int tile = idx >> 7, row = (idx >> 3) & 15, tok = idx & 7;
+            const int r = tile * 16 + row;
+            if (r >= R || tok >= a.M) continue;
+            float s = 0.f;
+            for (int seg = 0; seg < S; seg++) s += part[(size_t)(tile * S + seg) * 128 + row * 8 + tok];
+            store_form(a.y + (size_t)tok * a.N + r_begin + r, s, a.form, a.bias, r_begin + r);
+        }
+    }
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_q80_mma_kernel(const GemvArgs a) { gemv_q80_mma_body<WARPS>(a); }

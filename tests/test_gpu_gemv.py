@@ -155,18 +155,19 @@ def test_prequantized_activations_match(gpu, tag):
         gpu.free(buf)
 
 
+@pytest.mark.parametrize("tag", ["q4k", "q6k"])
 @pytest.mark.parametrize("mode", [0, 2])
-def test_q4k_both_inner_loops(gpu, mode):
-    """Q4_K has two inner loops (dp4a per lane; integer tensor-core MMA for small batches).  Force each one
-    over every batch size and check it against the oracle and against the other one."""
+def test_kquant_both_inner_loops(gpu, tag, mode):
+    """The K-quants have two inner loops (dp4a per lane; integer tensor-core MMA for small batches).  Force
+    each one over every batch size and check it against the oracle."""
     gpu.set_option("gemv_mma", mode)
     try:
         for n, k, m in [(4096, 4096, 1), (300, 2304, 3), (1000, 4352, 8), (17, 256, 5), (14336, 4096, 8), (4096, 14336, 4)]:
             for source in ("gauss", "synth"):
-                err = _gemv_case(gpu, "q4k", n, k, m, source, seed=m)
+                err = _gemv_case(gpu, tag, n, k, m, source, seed=m)
                 assert err < 1e-5
-        _gemv_case(gpu, "q4k", 777, 1024, 6, form=ACCUM)
-        _gemv_case(gpu, "q4k", 130, 512, 2, form=BIAS)
+        _gemv_case(gpu, tag, 777, 1024, 6, form=ACCUM)
+        _gemv_case(gpu, tag, 130, 512, 2, form=BIAS)
     finally:
         gpu.set_option("gemv_mma", 1)
 
