@@ -54,7 +54,8 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
     }
     memset(ctx->host_status, 0, 64);
     if (cudaMalloc((void **)&ctx->gemm_flags, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(ctx->gemm_flags, 0, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess) {
+        cudaMemset(ctx->gemm_flags, 0, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMalloc(&ctx->act_scratch, OJAS_ACT_SCRATCH_BYTES) != cudaSuccess) {
         if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
         cudaFreeHost(ctx->host_status);
         if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -70,6 +71,7 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
 extern "C" void ojas_b200_destroy(ojas_b200_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    if (ctx->act_scratch) cudaFree(ctx->act_scratch);
     if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);

@@ -23,6 +23,7 @@ struct ojas_b200_ctx {
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
     int gemv_depth = 4;          // stages in each warp's cp.async ring (2..4)
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
+    void *act_scratch = nullptr;         // device scratch for a batch's Q8_K activations (values, scales, block sums)
     unsigned int *gemm_flags = nullptr;  // device words, one per GEMM output tile: "the tile has been stored" marks (see gemm_ts.cuh)
     unsigned int gemm_serial = 0;        // value that means "stored" for the GEMM launch in flight; never 0
     unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
@@ -31,6 +32,10 @@ struct ojas_b200_ctx {
 };
 
 constexpr size_t OJAS_GEMM_FLAG_WORDS = 65536;
+// Activation scratch of a context: up to this many int8 values (8 rows of K = 32768), then one f32 scale per 256
+// and one i32 sum per 32 of them.
+constexpr size_t OJAS_ACT_SCRATCH_VALUES = 262144;
+constexpr size_t OJAS_ACT_SCRATCH_BYTES = OJAS_ACT_SCRATCH_VALUES + OJAS_ACT_SCRATCH_VALUES / 256 * 4 + OJAS_ACT_SCRATCH_VALUES / 32 * 4;
 
 int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
 

@@ -931,7 +931,29 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
     return 0;
 }
 
+// A batch of K-quant rows from fp32 activations: every CTA of the GEMV would quantize the whole batch for
+// itself (M * K / 256 warp tasks each).  From a few dozen tasks per warp on that prologue outweighs the
+// matrix, so the batch is quantized once into the context's scratch and the GEMV copies the result.
+static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs &args, size_t M) {
+    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch) return false;
+    const size_t values = M * (size_t)args.K;
+    if (values > OJAS_ACT_SCRATCH_VALUES || values < 32768) return false;
+    int8_t *q = (int8_t *)ctx->act_scratch;
+    float *scales = (float *)(q + OJAS_ACT_SCRATCH_VALUES);
+    int32_t *bsums = (int32_t *)(scales + OJAS_ACT_SCRATCH_VALUES / 256);
+    const long long n_sb = (long long)(values / 256);
+    quant_q8k_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(args.x, q, scales, bsums, n_sb);
+    if (cudaGetLastError() != cudaSuccess) return false;
+    ctx->launches++;
+    args.x = nullptr;
+    args.q = q;
+    args.scales = scales;
+    args.bsums = bsums;
+    return true;
+}
+
 static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args, size_t M) {
+    if (ctx->gemv_mma != 0 && gemv_prequantize(ctx, type, preq, args, M)) preq = true;
     // Q4_K batches of 2..8 rows (or every Q4_K call when the option says so) take the integer tensor-core path
     if (type == OJAS_B200_Q4_K && ctx->gemv_mma != 0 && (M >= 2 || ctx->gemv_mma == 2)) {
         GemvArgs b = args;

@@ -155,11 +155,12 @@ def test_prequantized_activations_match(gpu, tag):
         gpu.free(buf)
 
 
-@pytest.mark.parametrize("tag", ["q4k", "q6k"])
+@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
 @pytest.mark.parametrize("mode", [0, 2])
-def test_kquant_both_inner_loops(gpu, tag, mode):
-    """The K-quants have two inner loops (dp4a per lane; integer tensor-core MMA for small batches).  Force
-    each one over every batch size and check it against the oracle."""
+def test_both_inner_loops(gpu, tag, mode):
+    """Every format has two inner loops: per-lane (dp4a / fp32 FMA) and tensor-core MMA for small batches
+    (integer MMA for the K-quants, f16 MMA with two-term activations for Q8_0).  Force each one over every
+    batch size and check it against the oracle."""
     gpu.set_option("gemv_mma", mode)
     try:
         for n, k, m in [(4096, 4096, 1), (300, 2304, 3), (1000, 4352, 8), (17, 256, 5), (14336, 4096, 8), (4096, 14336, 4)]:
