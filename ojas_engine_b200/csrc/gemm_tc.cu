@@ -26,8 +26,12 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
-constexpr int WQ_BUFS = 3;          // raw Q4_K nibble tiles (one super-block x 128 rows = 16 KB) in flight
-constexpr int WQ_BYTES = BM * 128;
+constexpr int WQ_BUFS = 3;          // raw weight tiles (one super-block x 128 rows) in flight
+constexpr int WQ_LO_BYTES = BM * 128;   // Q4_K nibbles / Q6_K low nibbles: 128 bytes per row
+constexpr int WQ_HI_BYTES = BM * 64;    // Q6_K top bits: 64 bytes per row
+__host__ __device__ constexpr int wq_bytes(int type) {   // bytes of one staged raw tile (0: the type is not staged)
+    return type == OJAS_B200_Q4_K ? WQ_LO_BYTES : type == OJAS_B200_Q6_K ? WQ_LO_BYTES + WQ_HI_BYTES : 0;
+}
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
 struct GemmArgs {
@@ -137,11 +141,6 @@ __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
     return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -295,16 +294,16 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-size_t gemm_ts_smem_bytes(int bn, bool staged_w) {
-    return 1024 + (size_t)ts_b_stages(bn, staged_w) * bn * BK * 2 + (staged_w ? WQ_BUFS * WQ_BYTES : 0) +
+size_t gemm_ts_smem_bytes(int bn, int type) {
+    return 1024 + (size_t)ts_b_stages(bn, type) * bn * BK * 2 + (size_t)WQ_BUFS * wq_bytes(type) +
            TS_EPI_WARPS * TS_EPI_TILE_BYTES + TS_BAR_BYTES;
 }
 
 template <int BN, int TYPE>
-int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_y,
-                      const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_h,
+                      const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
     auto kernel = gemm_ts_kernel<BN, TYPE>;
-    const size_t smem = gemm_ts_smem_bytes(BN, TYPE == OJAS_B200_Q4_K);
+    const size_t smem = gemm_ts_smem_bytes(BN, TYPE);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: shared memory %zu: %s", smem, cudaGetErrorString(e));
     // programmatic dependent launch: the kernel's set-up, weight loads and dequantization overlap the tail of the
@@ -319,20 +318,20 @@ int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtenso
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_w, tmap_y, args);
+    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_w, tmap_h, tmap_y, args);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemm_ts: %s", cudaGetErrorString(e));
     OJAS_LAUNCH_CHECK(ctx, "gemm_ts");
     return 0;
 }
 
 template <int TYPE>
-int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_y,
-                        const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_h,
+                        const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
     switch (bn) {
-    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
-    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
-    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
-    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
+    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
+    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
+    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
     }
 }
 
@@ -396,15 +395,25 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
-    // raw nibble plane as bytes [N rows][K/2 bytes], box = one super-block (128 bytes) x 128 rows
-    CUtensorMap tmap_w = tmap;
-    if (type == OJAS_B200_Q4_K) {
+    // raw nibble plane (Q4_K nibbles, Q6_K low nibbles: the first plane of both layouts) as bytes
+    // [N rows][K/2 bytes], box = one super-block (128 bytes) x 128 rows
+    CUtensorMap tmap_w = tmap, tmap_h = tmap;
+    if (type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) {
         const cuuint64_t wdims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
         const cuuint64_t wstrides[1] = {(cuuint64_t)(K / 2)};
         const cuuint32_t wbox[2] = {128, (cuuint32_t)BM};
         cr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (weights) failed (%d)", (int)cr);
+    }
+    if (type == OJAS_B200_Q6_K) {   // top-bit plane [N rows][K/4 bytes], box = 64 bytes x 128 rows, 64-byte swizzle
+        const cuuint64_t hdims[2] = {(cuuint64_t)(K / 4), (cuuint64_t)N};
+        const cuuint64_t hstrides[1] = {(cuuint64_t)(K / 4)};
+        const cuuint32_t hbox[2] = {64, (cuuint32_t)BM};
+        cr = encode(&tmap_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)weight_planes(type, w, N, K).p1, hdims, hstrides, hbox, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (top bits) failed (%d)", (int)cr);
     }
 
     // y as a tensor [M rows][N floats], box = 32 floats x 16 rows (one epilogue warp's staging tile)
@@ -449,9 +458,9 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
             }
         }
         const dim3 grid_ts((unsigned)ctas);
-        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
-        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
-        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
+        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
     }
 }
 

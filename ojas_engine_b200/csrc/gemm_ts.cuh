@@ -8,7 +8,7 @@
 // four-deep ring of 512-cycle stages cannot cover them.
 //   TMEM columns   0..255  accumulator(s): one of 256 tokens, or two of <= 128 tokens
 //   TMEM columns 256..511  eight A stages of 128 rows x 64 k (32 columns each) = two super-blocks
-//   shared memory          6-8 activation stages (BN tokens x 64 k, by TMA) + two raw Q4_K tiles
+//   shared memory          4-8 activation stages (BN tokens x 64 k, by TMA) + three raw Q4_K / Q6_K tiles + staging
 // Work is cut "stream-K" style: the (tile, super-block) pairs are numbered tile-major and CTA b takes the
 // b-th equal share of that list, so every SM gets the same number of super-blocks whatever the tile
 // count; a tile whose K range is split across CTAs is summed with fp32 atomics into y (zeroed first).
@@ -26,8 +26,8 @@ constexpr int TS_BAR_BYTES = 512;
 constexpr int TS_EPI_TILE_BYTES = 16 * 32 * 4;                    // per epilogue warp: 16 tokens x 32 weight rows, fp32
 constexpr int TS_SMEM_BUDGET = 232448 - 1024 - TS_BAR_BYTES - TS_EPI_WARPS * TS_EPI_TILE_BYTES;   // 227 KB minus slack, barriers, staging
 
-__host__ __device__ constexpr int ts_b_stages(int bn, bool staged_w) {
-    const int s = (TS_SMEM_BUDGET - (staged_w ? WQ_BUFS * WQ_BYTES : 0)) / (bn * BK * 2);
+__host__ __device__ constexpr int ts_b_stages(int bn, int type) {
+    const int s = (TS_SMEM_BUDGET - WQ_BUFS * wq_bytes(type)) / (bn * BK * 2);
     return s > 8 ? 8 : s;
 }
 
@@ -162,17 +162,19 @@ __device__ unsigned long long g_ts_trace[9][4096];
 template <int BN, int TYPE>
 __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                  const __grid_constant__ CUtensorMap tmap_w,
+                                                                 const __grid_constant__ CUtensorMap tmap_h,
                                                                  const __grid_constant__ CUtensorMap tmap_y, const GemmArgs a) {
     extern __shared__ unsigned char gemm_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)gemm_smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_STAGE_BYTES = BN * BK * 2;
-    constexpr bool STAGED_W = (TYPE == OJAS_B200_Q4_K);
-    constexpr int BS = ts_b_stages(BN, STAGED_W);
+    constexpr int WQ_BYTES = wq_bytes(TYPE);                  // raw tiles arrive by TMA, one super-block at a time
+    constexpr bool STAGED_W = WQ_BYTES != 0;
+    constexpr int BS = ts_b_stages(BN, TYPE);
     constexpr int NACC = BN <= 128 ? 2 : 1;
     static_assert(BS >= 4 && BS <= 8, "activation ring depth");
     unsigned char *smem_b = smem;
     unsigned char *smem_wq = smem_b + BS * B_STAGE_BYTES;
-    unsigned char *smem_epi = smem_wq + (STAGED_W ? WQ_BUFS * WQ_BYTES : 0);
+    unsigned char *smem_epi = smem_wq + WQ_BUFS * WQ_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + TS_EPI_WARPS * TS_EPI_TILE_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + 8, *b_full = bars + 16, *b_empty = bars + 24;
     uint64_t *wq_full = bars + 32, *wq_empty = wq_full + WQ_BUFS;
@@ -351,9 +353,19 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             const size_t lrow = (size_t)(live ? grow : 0);
             const size_t rowblk = lrow * nsb;
             const int n_sb = pc.sb1 - pc.sb0;
+            // small per-row items come straight from global memory, one super-block ahead: the Q4_K header
+            // (d, dmin, scales); the Q6_K chunk's four sub-scales and d
             uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
-            if (STAGED_W) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + pc.sb0);
-            // weights that come straight from global memory (Q6_K, Q8_0): the next super-block's loads are in
+            auto small_items = [&](int sb) {
+                if (TYPE == OJAS_B200_Q4_K) {
+                    hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + sb);
+                } else if (TYPE == OJAS_B200_Q6_K) {
+                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + (rowblk + sb) * 4 + c);
+                    hdr_next.y = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + rowblk + sb);
+                }
+            };
+            if (STAGED_W) small_items(pc.sb0);
+            // weights that come straight from global memory (Q8_0): the next super-block's loads are in
             // flight while this one is converted
             uint4 cA = make_uint4(0u, 0u, 0u, 0u), cB = cA, cC = cA, cD = cA, nA = cA, nB = cA, nC = cA, nD = cA;
             uint32_t ce0 = 0, ce1 = 0, ne0 = 0, ne1 = 0;
@@ -363,13 +375,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + (lrow * a.K + k0) / 16;
                     A = __ldg(src); B = __ldg(src + 1); C = __ldg(src + 2); D = __ldg(src + 3);
                     e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p1) + (lrow * (a.K / 32) + k0 / 32) / 2);
-                } else if (TYPE == OJAS_B200_Q6_K) {   // two 16-byte pieces of low nibbles, 16 bytes of top bits, 4 scales, d
-                    const size_t blk = rowblk + sb;
-                    A = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + c);
-                    B = __ldg(reinterpret_cast<const uint4 *>(a.w.p0) + blk * 8 + 4 + c);
-                    C = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + blk * 4 + c);
-                    e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + blk * 4 + c);
-                    e1 = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + blk);
                 }
             };
             if (!STAGED_W) fetch(pc.sb0, cA, cB, cC, cD, ce0, ce1);
@@ -380,11 +385,16 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 if (tr_on) TS_TR(1 + (c >> 1), 1, wc * 4 + c);
                 TS_PROG(wc * 16 + 1);
                 if (STAGED_W) {
-                    if (j + 1 < n_sb) hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + pc.sb0 + j + 1);
+                    if (j + 1 < n_sb) small_items(pc.sb0 + j + 1);
                     if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
                     const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
-                    cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));
+                    cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));             // 128-byte swizzle
                     cB = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
+                    if (TYPE == OJAS_B200_Q6_K) {                                                        // 64-byte swizzle
+                        cC = *reinterpret_cast<const uint4 *>(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
+                        ce0 = H.x;
+                        ce1 = H.y;
+                    }
                 } else if (j + 1 < n_sb) {
                     fetch(pc.sb0 + j + 1, nA, nB, nC, nD, ne0, ne1);
                 }
@@ -514,7 +524,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             }
         }
     } else {
-        // ---------------- TMA: raw Q4_K nibble tile [128 rows x 128 bytes] per super-block
+        // ---------------- TMA: raw tile per super-block: Q4_K / Q6_K nibbles [128 rows x 128 bytes], Q6_K top bits
+        // [128 rows x 64 bytes]
         if (STAGED_W && lane == 0) {
             uint32_t wc = 0;
             bool ok = true;
@@ -529,6 +540,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     TS_PROG(wc * 16 + 2);
                     mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
                     tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, pc.n0, &wq_full[wb]);
+                    if (TYPE == OJAS_B200_Q6_K) tma_load_2d(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES, &tmap_h, sb * 64, pc.n0, &wq_full[wb]);
                 }
             }
         }
