@@ -26,12 +26,15 @@ namespace {
 
 constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
-constexpr int WQ_BUFS = 3;          // raw weight tiles (one super-block x 128 rows) in flight
-constexpr int WQ_LO_BYTES = BM * 128;   // Q4_K nibbles / Q6_K low nibbles: 128 bytes per row
+constexpr int WQ_BUFS_MAX = 3;
+constexpr int WQ_LO_BYTES = BM * 128;   // Q4_K nibbles / Q6_K low nibbles / half a Q8_0 super-block: 128 bytes per row
 constexpr int WQ_HI_BYTES = BM * 64;    // Q6_K top bits: 64 bytes per row
-__host__ __device__ constexpr int wq_bytes(int type) {   // bytes of one staged raw tile (0: the type is not staged)
-    return type == OJAS_B200_Q4_K ? WQ_LO_BYTES : type == OJAS_B200_Q6_K ? WQ_LO_BYTES + WQ_HI_BYTES : 0;
+// One staged raw tile = one super-block x 128 rows: Q4_K 16 KB, Q6_K 24 KB, Q8_0 32 KB (two 128-byte halves).
+__host__ __device__ constexpr int wq_bytes(int type) {
+    return type == OJAS_B200_Q4_K ? WQ_LO_BYTES : type == OJAS_B200_Q6_K ? WQ_LO_BYTES + WQ_HI_BYTES : 2 * WQ_LO_BYTES;
 }
+// raw tiles in flight: three, or two of the large Q8_0 tiles (so that four activation stages still fit)
+__host__ __device__ constexpr int wq_bufs(int type) { return type == OJAS_B200_Q8_0 ? 2 : 3; }
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
 struct GemmArgs {
@@ -295,7 +298,7 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 size_t gemm_ts_smem_bytes(int bn, int type) {
-    return 1024 + (size_t)ts_b_stages(bn, type) * bn * BK * 2 + (size_t)WQ_BUFS * wq_bytes(type) +
+    return 1024 + (size_t)ts_b_stages(bn, type) * bn * BK * 2 + (size_t)wq_bufs(type) * wq_bytes(type) +
            TS_EPI_WARPS * TS_EPI_TILE_BYTES + TS_BAR_BYTES;
 }
 
@@ -398,9 +401,10 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     // raw nibble plane (Q4_K nibbles, Q6_K low nibbles: the first plane of both layouts) as bytes
     // [N rows][K/2 bytes], box = one super-block (128 bytes) x 128 rows
     CUtensorMap tmap_w = tmap, tmap_h = tmap;
-    if (type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) {
-        const cuuint64_t wdims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)N};
-        const cuuint64_t wstrides[1] = {(cuuint64_t)(K / 2)};
+    {   // (Q8_0: the int8 plane [N rows][K bytes]; a super-block is two such boxes)
+        const size_t row_bytes = type == OJAS_B200_Q8_0 ? K : K / 2;
+        const cuuint64_t wdims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
+        const cuuint64_t wstrides[1] = {(cuuint64_t)row_bytes};
         const cuuint32_t wbox[2] = {128, (cuuint32_t)BM};
         cr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -27,7 +27,7 @@ constexpr int TS_EPI_TILE_BYTES = 16 * 32 * 4;                    // per epilogu
 constexpr int TS_SMEM_BUDGET = 232448 - 1024 - TS_BAR_BYTES - TS_EPI_WARPS * TS_EPI_TILE_BYTES;   // 227 KB minus slack, barriers, staging
 
 __host__ __device__ constexpr int ts_b_stages(int bn, int type) {
-    const int s = (TS_SMEM_BUDGET - WQ_BUFS * wq_bytes(type)) / (bn * BK * 2);
+    const int s = (TS_SMEM_BUDGET - wq_bufs(type) * wq_bytes(type)) / (bn * BK * 2);
     return s > 8 ? 8 : s;
 }
 
@@ -167,8 +167,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     extern __shared__ unsigned char gemm_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)gemm_smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_STAGE_BYTES = BN * BK * 2;
-    constexpr int WQ_BYTES = wq_bytes(TYPE);                  // raw tiles arrive by TMA, one super-block at a time
-    constexpr bool STAGED_W = WQ_BYTES != 0;
+    constexpr int WQ_BYTES = wq_bytes(TYPE), WQ_BUFS = wq_bufs(TYPE);   // raw tiles arrive by TMA, one super-block at a time
+    constexpr bool STAGED_W = true;
     constexpr int BS = ts_b_stages(BN, TYPE);
     constexpr int NACC = BN <= 128 ? 2 : 1;
     static_assert(BS >= 4 && BS <= 8, "activation ring depth");
@@ -177,8 +177,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     unsigned char *smem_epi = smem_wq + WQ_BUFS * WQ_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem_epi + TS_EPI_WARPS * TS_EPI_TILE_BYTES);
     uint64_t *a_full = bars, *a_empty = bars + 8, *b_full = bars + 16, *b_empty = bars + 24;
-    uint64_t *wq_full = bars + 32, *wq_empty = wq_full + WQ_BUFS;
-    uint64_t *tmem_full = wq_empty + WQ_BUFS, *tmem_empty = tmem_full + 2;
+    uint64_t *wq_full = bars + 32, *wq_empty = wq_full + WQ_BUFS_MAX;
+    uint64_t *tmem_full = wq_empty + WQ_BUFS_MAX, *tmem_empty = tmem_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile unsigned *b_seen = reinterpret_cast<volatile unsigned *>(tmem_slot + 2);   // [4], see the MMA threads
@@ -354,7 +354,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             const size_t rowblk = lrow * nsb;
             const int n_sb = pc.sb1 - pc.sb0;
             // small per-row items come straight from global memory, one super-block ahead: the Q4_K header
-            // (d, dmin, scales); the Q6_K chunk's four sub-scales and d
+            // (d, dmin, scales); the Q6_K chunk's four sub-scales and d; the Q8_0 chunk's two block scales
             uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
             auto small_items = [&](int sb) {
                 if (TYPE == OJAS_B200_Q4_K) {
@@ -362,22 +362,13 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 } else if (TYPE == OJAS_B200_Q6_K) {
                     hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + (rowblk + sb) * 4 + c);
                     hdr_next.y = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + rowblk + sb);
+                } else {                                  // the chunk's two f16 block scales
+                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(a.w.p1) + (rowblk + sb) * 4 + c);
                 }
             };
             if (STAGED_W) small_items(pc.sb0);
-            // weights that come straight from global memory (Q8_0): the next super-block's loads are in
-            // flight while this one is converted
-            uint4 cA = make_uint4(0u, 0u, 0u, 0u), cB = cA, cC = cA, cD = cA, nA = cA, nB = cA, nC = cA, nD = cA;
-            uint32_t ce0 = 0, ce1 = 0, ne0 = 0, ne1 = 0;
-            auto fetch = [&](int sb, uint4 &A, uint4 &B, uint4 &C, uint4 &D, uint32_t &e0, uint32_t &e1) {
-                if (TYPE == OJAS_B200_Q8_0) {          // 64 int8 + two f16 scales
-                    const size_t k0 = (size_t)sb * 256 + (size_t)c * BK;
-                    const uint4 *src = reinterpret_cast<const uint4 *>(a.w.p0) + (lrow * a.K + k0) / 16;
-                    A = __ldg(src); B = __ldg(src + 1); C = __ldg(src + 2); D = __ldg(src + 3);
-                    e0 = __ldg(reinterpret_cast<const uint32_t *>(a.w.p1) + (lrow * (a.K / 32) + k0 / 32) / 2);
-                }
-            };
-            if (!STAGED_W) fetch(pc.sb0, cA, cB, cC, cD, ce0, ce1);
+            uint4 cA = make_uint4(0u, 0u, 0u, 0u), cB = cA, cC = cA, cD = cA;
+            uint32_t ce0 = 0, ce1 = 0;
             for (int j = 0; ok && j < n_sb; j++, wc++) {
                 const int wb = wc % WQ_BUFS;
                 const int aslot = (int)(wc & 1u) * 4 + c;
@@ -388,15 +379,24 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     if (j + 1 < n_sb) small_items(pc.sb0 + j + 1);
                     if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
                     const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
-                    cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));             // 128-byte swizzle
-                    cB = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
+                    if (TYPE == OJAS_B200_Q8_0) {
+                        // chunk c = 64 int8: four 16-byte pieces of the 128-byte half (c >> 1) of the row
+                        const unsigned char *hrow = wrow + (c >> 1) * WQ_LO_BYTES;
+                        const int p0 = (c & 1) * 4, sw = row & 7;                                       // 128-byte swizzle
+                        cA = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 0) ^ sw) << 4));
+                        cB = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 1) ^ sw) << 4));
+                        cC = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 2) ^ sw) << 4));
+                        cD = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 3) ^ sw) << 4));
+                        ce0 = H.x;
+                    } else {
+                        cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));         // 128-byte swizzle
+                        cB = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
+                    }
                     if (TYPE == OJAS_B200_Q6_K) {                                                        // 64-byte swizzle
                         cC = *reinterpret_cast<const uint4 *>(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
                         ce0 = H.x;
                         ce1 = H.y;
                     }
-                } else if (j + 1 < n_sb) {
-                    fetch(pc.sb0 + j + 1, nA, nB, nC, nD, ne0, ne1);
                 }
                 if (tr_on) TS_TR(1 + (c >> 1), 2, wc * 4 + c);
                 TS_PROG(wc * 16 + 2);
@@ -437,7 +437,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 if (lane == 0) mbar_arrive(&a_full[aslot]);
                 if (tr_on) TS_TR(1 + (c >> 1), 5, wc * 4 + c);
                 TS_PROG(wc * 16 + 5);
-                if (!STAGED_W) { cA = nA; cB = nB; cC = nC; cD = nD; ce0 = ne0; ce1 = ne1; }
             }
         }
     } else if (warp == TS_WARP_TMA_X) {
@@ -525,7 +524,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         }
     } else {
         // ---------------- TMA: raw tile per super-block: Q4_K / Q6_K nibbles [128 rows x 128 bytes], Q6_K top bits
-        // [128 rows x 64 bytes]
+        // [128 rows x 64 bytes], Q8_0 two halves of [128 rows x 128 bytes]
         if (STAGED_W && lane == 0) {
             uint32_t wc = 0;
             bool ok = true;
@@ -539,7 +538,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     TS_TR(8, 2, wc * 4);
                     TS_PROG(wc * 16 + 2);
                     mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
-                    tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, pc.n0, &wq_full[wb]);
+                    if (TYPE == OJAS_B200_Q8_0) {
+                        tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 256, pc.n0, &wq_full[wb]);
+                        tma_load_2d(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES, &tmap_w, sb * 256 + 128, pc.n0, &wq_full[wb]);
+                    } else {
+                        tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, pc.n0, &wq_full[wb]);
+                    }
                     if (TYPE == OJAS_B200_Q6_K) tma_load_2d(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES, &tmap_h, sb * 64, pc.n0, &wq_full[wb]);
                 }
             }
