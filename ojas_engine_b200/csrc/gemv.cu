@@ -708,7 +708,7 @@ static int mma_segments(size_t rows_max, size_t nsb, int warps) {
 static size_t mma_smem_bytes(int warps, size_t M, size_t K, size_t rows_max, int S) {
     const size_t nsb = K / 256, tiles = (rows_max + 15) / 16;
     return (size_t)warps * 2 * MMA_STAGE_BYTES + ((M * (K + MMA_XPAD) + 15) & ~(size_t)15) + (size_t)sx_floats((int)M, (int)nsb) * 4 +
-           M * nsb * 8 * 4 + (S > 1 ? tiles * S * 128 * 4 : 0) + 16;
+           M * nsb * 8 * 4 + (S > 1 ? tiles * S * 128 * ((M + 7) / 8) * 4 : 0) + 16;
 }
 
 // Fills S / row partition and picks 32 or 16 warps by shared-memory fit; returns 0 if neither fits.
@@ -1006,9 +1006,16 @@ int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &pla
     a.rows_rem = a.N % grid;
     if (type == OJAS_B200_Q4_K && ctx->gemv_mma != 0) {
         GemvArgs b = a;
-        b.M = 8;
         int g2;
         size_t smem2;
+        b.M = 16;                                     // sixteen rows per pass (16 warps) when their activations fit beside the ring
+        mma_plan(ctx, b, g2, smem2);                  // sets the grid and the row split
+        b.S = mma_segments(rows_max, K / 256, 16);
+        smem2 = mma_smem_bytes(16, 16, K, rows_max, b.S);
+        if (smem2 <= (size_t)ctx->smem_optin)
+            return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<16, 2>, b, g2, 512, smem2, "gemv_q4k_mma_grouped16");
+        b = a;
+        b.M = 8;
         const int warps = mma_plan(ctx, b, g2, smem2);
         if (warps == 32) return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<32>, b, g2, 1024, smem2, "gemv_q4k_mma_grouped");
         if (warps == 16) return launch_gemv_threads(ctx, gemv_q4k_mma_grouped_kernel<16>, b, g2, 512, smem2, "gemv_q4k_mma_grouped");

@@ -57,8 +57,9 @@ __device__ __forceinline__ void stage_q8k_rows(const GemvArgs &a, unsigned char 
     }
 }
 
-// a.S = segments per tile (divides the super-block count); a.M <= 8.
-template <int WARPS, bool PREQ>
+// a.S = segments per tile (divides the super-block count); a.M <= 8 * NT.  NT = 2 runs two MMAs per unpacked
+// weight fragment (tokens 0..7 and 8..15): the unpacking and the scale extraction are shared by 16 tokens.
+template <int WARPS, bool PREQ, int NT = 1>
 __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nsb = a.K >> 8, S = a.S, SP = nsb / S;          // super-blocks per unit
@@ -111,13 +112,21 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
     __syncthreads();
     grid_launch_dependents();
 
-    // this lane's accumulators: rows g, g + 8 of the tile x tokens 2q, 2q + 1
-    const int t0 = 2 * q, t1 = 2 * q + 1;
-    const bool tok_b = g < a.M, tok0 = t0 < a.M, tok1 = t1 < a.M;
-    const unsigned char *xb = xq + (size_t)(tok_b ? g : 0) * xstride + 4 * q;
-    const int *bs0 = bs + (tok0 ? t0 : 0) * nsb * 8, *bs1 = bs + (tok1 ? t1 : 0) * nsb * 8;
-    const float *sx0 = sx + (tok0 ? t0 : 0) * nsb, *sx1 = sx + (tok1 ? t1 : 0) * nsb;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // this lane's accumulators: rows g, g + 8 of the tile x tokens 8h + 2q, 8h + 2q + 1 (h = token half)
+    bool tok_b[NT], tok0[NT], tok1[NT];
+    const unsigned char *xb[NT];
+    const int *bs0[NT], *bs1[NT];
+    const float *sx0[NT], *sx1[NT];
+    float acc[NT][4];
+#pragma unroll
+    for (int h = 0; h < NT; h++) {
+        const int tb = 8 * h + g, t0 = 8 * h + 2 * q, t1 = t0 + 1;
+        tok_b[h] = tb < a.M; tok0[h] = t0 < a.M; tok1[h] = t1 < a.M;
+        xb[h] = xq + (size_t)(tok_b[h] ? tb : 0) * xstride + 4 * q;
+        bs0[h] = bs + (tok0[h] ? t0 : 0) * nsb * 8; bs1[h] = bs + (tok1[h] ? t1 : 0) * nsb * 8;
+        sx0[h] = sx + (tok0[h] ? t0 : 0) * nsb; sx1[h] = sx + (tok1[h] ? t1 : 0) * nsb;
+        acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+    }
     int stage = 0;
     while (ic.u < n_units) {
         issue(ii, stage ^ 1);
@@ -130,7 +139,11 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
         const unsigned char *ra = st + g * MMA_ROW_STRIDE + 4 * q, *rb = ra + 8 * MMA_ROW_STRIDE;
         const uint4 Ha = *reinterpret_cast<const uint4 *>(st + 16 * MMA_ROW_STRIDE + g * 16);
         const uint4 Hb = *reinterpret_cast<const uint4 *>(st + 16 * MMA_ROW_STRIDE + (g + 8) * 16);
-        int isum[4] = {0, 0, 0, 0}, msum[4] = {0, 0, 0, 0};
+        int isum[NT][4], msum[NT][4];
+#pragma unroll
+        for (int h = 0; h < NT; h++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) isum[h][i] = msum[h][i] = 0;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             // chunk c: piece h = 0 at byte c*16 (weights 64c + 0..15 low nibble, 64c + 32.. high), h = 1 at 64 + c*16
@@ -140,45 +153,55 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
             const uint32_t ga = c == 0 ? Ha.y : c == 1 ? __funnelshift_r(Ha.y, Ha.z, 24) : c == 2 ? __funnelshift_r(Ha.z, Ha.w, 16) : (Ha.w >> 8);
             const uint32_t gb = c == 0 ? Hb.y : c == 1 ? __funnelshift_r(Hb.y, Hb.z, 24) : c == 2 ? __funnelshift_r(Hb.z, Hb.w, 16) : (Hb.w >> 8);
 #pragma unroll
-            for (int h = 0; h < 2; h++) {                      // sub-block j = 2c + h: low (h = 0) or high nibbles
-                const int j = 2 * c + h;
-                const uint32_t a0 = (wa0 >> (4 * h)) & 0x0f0f0f0fu, a1 = (wb0 >> (4 * h)) & 0x0f0f0f0fu;
-                const uint32_t a2 = (wa1 >> (4 * h)) & 0x0f0f0f0fu, a3 = (wb1 >> (4 * h)) & 0x0f0f0f0fu;
-                uint32_t b0 = 0u, b1 = 0u;
-                if (tok_b) {
-                    b0 = *reinterpret_cast<const uint32_t *>(xb + sb * 256 + j * 32);
-                    b1 = *reinterpret_cast<const uint32_t *>(xb + sb * 256 + j * 32 + 16);
+            for (int nh = 0; nh < 2; nh++) {                   // sub-block j = 2c + nh: low (0) or high (1) nibbles
+                const int j = 2 * c + nh;
+                const uint32_t a0 = (wa0 >> (4 * nh)) & 0x0f0f0f0fu, a1 = (wb0 >> (4 * nh)) & 0x0f0f0f0fu;
+                const uint32_t a2 = (wa1 >> (4 * nh)) & 0x0f0f0f0fu, a3 = (wb1 >> (4 * nh)) & 0x0f0f0f0fu;
+                const int sa = (int)((ga >> (6 * nh)) & 63u), sb_ = (int)((gb >> (6 * nh)) & 63u);
+                const int ma = (int)((ga >> (12 + 6 * nh)) & 63u), mb = (int)((gb >> (12 + 6 * nh)) & 63u);
+#pragma unroll
+                for (int h = 0; h < NT; h++) {                 // token half
+                    uint32_t b0 = 0u, b1 = 0u;
+                    if (tok_b[h]) {
+                        b0 = *reinterpret_cast<const uint32_t *>(xb[h] + sb * 256 + j * 32);
+                        b1 = *reinterpret_cast<const uint32_t *>(xb[h] + sb * 256 + j * 32 + 16);
+                    }
+                    int d[4];
+                    mma_u8s8(d, a0, a1, a2, a3, b0, b1);       // exact int32 sub-block dots: rows g, g+8 x two tokens
+                    const int u0 = tok0[h] ? bs0[h][sb * 8 + j] : 0, u1 = tok1[h] ? bs1[h][sb * 8 + j] : 0;
+                    isum[h][0] += sa * d[0]; isum[h][1] += sa * d[1]; isum[h][2] += sb_ * d[2]; isum[h][3] += sb_ * d[3];
+                    msum[h][0] += ma * u0;   msum[h][1] += ma * u1;   msum[h][2] += mb * u0;    msum[h][3] += mb * u1;
                 }
-                int d[4];
-                mma_u8s8(d, a0, a1, a2, a3, b0, b1);           // exact int32 sub-block dots: rows g, g+8 x tokens 2q, 2q+1
-                const int sa = (int)((ga >> (6 * h)) & 63u), sb_ = (int)((gb >> (6 * h)) & 63u);
-                const int ma = (int)((ga >> (12 + 6 * h)) & 63u), mb = (int)((gb >> (12 + 6 * h)) & 63u);
-                const int u0 = tok0 ? bs0[sb * 8 + j] : 0, u1 = tok1 ? bs1[sb * 8 + j] : 0;
-                isum[0] += sa * d[0]; isum[1] += sa * d[1]; isum[2] += sb_ * d[2]; isum[3] += sb_ * d[3];
-                msum[0] += ma * u0;   msum[1] += ma * u1;   msum[2] += mb * u0;    msum[3] += mb * u1;
             }
         }
         const float da = f16_bits_to_f32(Ha.x), na = f16_bits_to_f32(Ha.x >> 16);
         const float db = f16_bits_to_f32(Hb.x), nb = f16_bits_to_f32(Hb.x >> 16);
-        const float s0 = tok0 ? sx0[sb] : 0.f, s1 = tok1 ? sx1[sb] : 0.f;
-        acc[0] += s0 * (da * (float)isum[0] - na * (float)msum[0]);
-        acc[1] += s1 * (da * (float)isum[1] - na * (float)msum[1]);
-        acc[2] += s0 * (db * (float)isum[2] - nb * (float)msum[2]);
-        acc[3] += s1 * (db * (float)isum[3] - nb * (float)msum[3]);
+#pragma unroll
+        for (int h = 0; h < NT; h++) {
+            const float s0 = tok0[h] ? sx0[h][sb] : 0.f, s1 = tok1[h] ? sx1[h][sb] : 0.f;
+            acc[h][0] += s0 * (da * (float)isum[h][0] - na * (float)msum[h][0]);
+            acc[h][1] += s1 * (da * (float)isum[h][1] - na * (float)msum[h][1]);
+            acc[h][2] += s0 * (db * (float)isum[h][2] - nb * (float)msum[h][2]);
+            acc[h][3] += s1 * (db * (float)isum[h][3] - nb * (float)msum[h][3]);
+        }
         __syncwarp();                                          // the stage is free for the next copy
-        if (ic.j + 1 == SP) {                                  // end of the unit: rows g, g+8 x tokens t0, t1
+        if (ic.j + 1 == SP) {                                  // end of the unit
             const int row_a = tile * 16 + g, row_b = row_a + 8;
-            if (S == 1) {
-                if (tok0 && row_a < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_a, acc[0], a.form, a.bias, r_begin + row_a);
-                if (tok1 && row_a < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_a, acc[1], a.form, a.bias, r_begin + row_a);
-                if (tok0 && row_b < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_b, acc[2], a.form, a.bias, r_begin + row_b);
-                if (tok1 && row_b < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_b, acc[3], a.form, a.bias, r_begin + row_b);
-            } else {
-                float *pp = part + (size_t)ic.u * 128;         // [unit][row 16][token 8]
-                pp[g * 8 + t0] = acc[0]; pp[g * 8 + t1] = acc[1];
-                pp[(g + 8) * 8 + t0] = acc[2]; pp[(g + 8) * 8 + t1] = acc[3];
+#pragma unroll
+            for (int h = 0; h < NT; h++) {
+                const int t0 = 8 * h + 2 * q, t1 = t0 + 1;
+                if (S == 1) {
+                    if (tok0[h] && row_a < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_a, acc[h][0], a.form, a.bias, r_begin + row_a);
+                    if (tok1[h] && row_a < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_a, acc[h][1], a.form, a.bias, r_begin + row_a);
+                    if (tok0[h] && row_b < R) store_form(a.y + (size_t)t0 * a.N + r_begin + row_b, acc[h][2], a.form, a.bias, r_begin + row_b);
+                    if (tok1[h] && row_b < R) store_form(a.y + (size_t)t1 * a.N + r_begin + row_b, acc[h][3], a.form, a.bias, r_begin + row_b);
+                } else {
+                    float *pp = part + (size_t)ic.u * (128 * NT);  // [unit][row 16][token 8 NT]
+                    pp[g * (8 * NT) + t0] = acc[h][0]; pp[g * (8 * NT) + t1] = acc[h][1];
+                    pp[(g + 8) * (8 * NT) + t0] = acc[h][2]; pp[(g + 8) * (8 * NT) + t1] = acc[h][3];
+                }
+                acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
             }
-            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
         }
         next(ic);
         stage ^= 1;
@@ -186,12 +209,13 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
     cp_async_wait<0>();
     if (S > 1) {
         __syncthreads();
-        for (int idx = threadIdx.x; idx < n_tiles * 128; idx += blockDim.x) {
-            const int tile = idx >> 7, row = (idx >> 3) & 15, tok = idx & 7;
+        for (int idx = threadIdx.x; idx < n_tiles * 128 * NT; idx += blockDim.x) {
+            const int tile = idx / (128 * NT), rem = idx - tile * (128 * NT);
+            const int row = rem / (8 * NT), tok = rem - row * (8 * NT);
             const int r = tile * 16 + row;
             if (r >= R || tok >= a.M) continue;
             float s = 0.f;
-            for (int seg = 0; seg < S; seg++) s += part[(size_t)(tile * S + seg) * 128 + row * 8 + tok];
+            for (int seg = 0; seg < S; seg++) s += part[(size_t)(tile * S + seg) * (128 * NT) + row * (8 * NT) + tok];
             store_form(a.y + (size_t)tok * a.N + r_begin + r, s, a.form, a.bias, r_begin + r);
         }
     }
@@ -200,17 +224,17 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
 template <int WARPS, bool PREQ>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_q4k_mma_kernel(const GemvArgs a) { gemv_q4k_mma_body<WARPS, PREQ>(a); }
 
-// Grouped form (experts): rows of the group, eight per pass; see gemv_q4k_grouped_kernel.
-template <int WARPS>
+// Grouped form (experts): rows of the group, 8 * NT per pass; see gemv_q4k_grouped_kernel.
+template <int WARPS, int NT = 1>
 __global__ void __launch_bounds__(WARPS * 32, 1) gemv_q4k_mma_grouped_kernel(const GemvArgs a) {
     const int count = __ldg(a.grp_count), off = __ldg(a.grp_offset);
-    for (int mb = 0; mb < count; mb += 8) {
+    for (int mb = 0; mb < count; mb += 8 * NT) {
         GemvArgs b = a;
-        b.M = count - mb < 8 ? count - mb : 8;
+        b.M = count - mb < 8 * NT ? count - mb : 8 * NT;
         if (a.row_index) b.row_index = a.row_index + off + mb;
         else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
         b.y = a.y + (size_t)(off + mb) * a.N;
-        gemv_q4k_mma_body<WARPS, true>(b);
+        gemv_q4k_mma_body<WARPS, true, NT>(b);
         __syncthreads();
     }
 }
