@@ -414,6 +414,8 @@ def run_case(args) -> None:
         gpu.set_option("pdl", 0)
     if args.mma >= 0:
         gpu.set_option("gemv_mma", args.mma)
+    if args.slim >= 0:
+        gpu.set_option("gemv_slim", args.slim)
     gguf = ob.raw_bytes(t, n, k)
     ring = args.ring or max(2, int(300e6 // gguf) + 1)
     base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
@@ -650,6 +652,7 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true", help="--case: plain launches instead of a CUDA graph")
     ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: force the K split (0 = automatic)")
     ap.add_argument("--mma", type=int, default=-1, help="--case: the gemv_mma option (0 per-lane loops only, 1 default, 2 tensor-core loop also for one row)")
+    ap.add_argument("--slim", type=int, default=-1, help="--case: the gemv_slim option (0 full-size kernel only, 1 default, 2 half-size kernel always)")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (default: with)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -21,7 +21,7 @@ struct ojas_b200_ctx {
     int gemv_mma = 1;            // Q4_K GEMV on the integer tensor-core path: 0 never, 1 for 2..8 rows, 2 always
     int gemv_slim = 1;           // single-row Q4_K GEMV in the half-size kernel: 0 never, 1 for small matrices, 2 always
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
-    int gemv_depth = 4;          // stages in each warp's cp.async ring (2..4)
+    int gemv_depth = 4;          // accepted and ignored (the GEMV ring has two stages)
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
     void *act_scratch = nullptr;         // device scratch for a batch's Q8_K activations (values, scales, block sums)
     unsigned int *gemm_flags = nullptr;  // device words, one per GEMM output tile: "the tile has been stored" marks (see gemm_ts.cuh)

@@ -184,9 +184,8 @@ __device__ __forceinline__ void stage_q8k(const GemvArgs &a, unsigned char *xq, 
 
 // ---------------------------------------------------------------------------- async staging
 // Weights travel global -> shared memory with cp.async (16 bytes per lane, no registers held
-// while in flight).  Each warp owns a ring of `depth` stages; a stage holds one step of the
-// warp (one row x eight super-blocks).  depth - 1 steps are always in flight, which is what
-// keeps enough bytes outstanding per SM to cover HBM latency.
+// while in flight).  Each warp owns a ring of two stages; a stage holds one step of the warp, and one
+// step is always in flight while the other is computed.
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
@@ -197,19 +196,9 @@ __device__ __forceinline__ void cp_async16_if(void *smem_dst, const void *gmem_s
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}"
                  ::"r"(d), "l"(gmem_src), "r"(pred) : "memory");
 }
-__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gmem_src) {
-    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
-}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-// wait until at most `pending` of this thread's groups are outstanding (pending = depth - 1, 1..3)
-__device__ __forceinline__ void cp_async_wait_dyn(int pending) {
-    if (pending >= 3) cp_async_wait<3>();
-    else if (pending == 2) cp_async_wait<2>();
-    else cp_async_wait<1>();
-}
 
 // ---------------------------------------------------------------------------- Q4_K
 // A Q4_K step is one row x sixteen super-blocks (4096 weights, 2304 bytes): every lane owns
