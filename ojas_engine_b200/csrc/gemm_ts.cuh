@@ -205,6 +205,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         for (int i = 0; i < 4; i++) b_seen[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (warp == TS_WARP_TMA_X && lane == 0) {              // the descriptors' first use would otherwise pay their fetch
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_w) : "memory");
+        if (TYPE == OJAS_B200_Q6_K) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_h) : "memory");
+        if (a.y_tma) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_y) : "memory");
+    }
     if (warp == TS_WARP_TMA_W) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
