@@ -359,11 +359,13 @@ def run_ours(args) -> None:
                         extras.append({"workload": f"{tag}_gemv_n{n}_k{k}_m{m}", "error": str(exc)})
             if not args.no_extras:
                 _, tc_peak, _ = measured_peaks()
-                for (m, n, k) in [(512, 4096, 4096), (512, 14336, 4096), (512, 4096, 14336), (2048, 14336, 4096), (128, 4096, 4096)]:
+                for (tag, m, n, k) in [("q4k", 512, 4096, 4096), ("q4k", 512, 14336, 4096), ("q4k", 512, 4096, 14336),
+                                       ("q4k", 2048, 14336, 4096), ("q4k", 128, 4096, 4096), ("q4k", 512, 28672, 8192),
+                                       ("q6k", 512, 8192, 28672), ("q6k", 512, 14336, 4096), ("q80", 512, 14336, 4096)]:
                     try:
-                        extras.append(gemm_case(gpu, ob, "q4k", m, n, k, 10, 3, tc_peak))
+                        extras.append(gemm_case(gpu, ob, tag, m, n, k, 10, 3, tc_peak))
                     except Exception as exc:
-                        extras.append({"workload": f"q4k_gemm_m{m}_n{n}_k{k}", "error": str(exc)})
+                        extras.append({"workload": f"{tag}_gemm_m{m}_n{n}_k{k}", "error": str(exc)})
                 try:
                     extras.append(moe_case(gpu, ob, 5, 2, hbm_peak, tc_peak))
                 except Exception as exc:
