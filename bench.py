@@ -400,11 +400,13 @@ def run_case(args) -> None:
         return run_gemm_case(args)
     if args.case == "tp70b":
         return run_tp70b(args)
-    if args.case == "moe":
+    if args.case == "moe" or args.case.startswith("moe:"):
         import ojas_engine_b200 as ob
         hbm_peak, tc_peak, _ = measured_peaks()
         gpu = ob.B200Gpu(0)
-        print(json.dumps(moe_case(gpu, ob, args.steps, args.warmup, hbm_peak, tc_peak)))
+        parts = args.case.split(":")          # moe[:TOKENS[:GEMM_ROWS]]
+        print(json.dumps(moe_case(gpu, ob, args.steps, args.warmup, hbm_peak, tc_peak, int(parts[1]) if len(parts) > 1 else 64,
+                                  int(parts[2]) if len(parts) > 2 else 0)))
         gpu.close()
         return
     tag, n, k, m = args.case.split(":")
@@ -486,10 +488,12 @@ def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int
             "frac_of_peak": round(tf / tc_peak, 4), "ksplit": ksplit or "auto"}
 
 
-def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float) -> dict:
-    """Mixtral-like expert FFN: 8 experts (gate/up 14336 x 4096, down 4096 x 14336, Q4_K), 64 tokens, top-2."""
+def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, tokens: int = 64, gemm_rows: int = 0) -> dict:
+    """Mixtral-like expert FFN: 8 experts (gate/up 14336 x 4096, down 4096 x 14336, Q4_K), `tokens` tokens, top-2.
+    gemm_rows > 0 turns on the grouped tensor-core GEMM form from that many rows per expert (option moe_gemm_rows)."""
     import oracle
-    e, d, ffn, m, ksel = 8, 4096, 14336, 64, 2
+    e, d, ffn, m, ksel = 8, 4096, 14336, tokens, 2
+    gpu.set_option("moe_gemm_rows", gemm_rows)
     rng = np.random.default_rng(0)
     mk = lambda n, k: oracle.synth_blocks(ob.Q4_K, e * n * k // 256)
     wg, wu, wd = (gpu.load_weight(mk(ffn, d), ob.Q4_K, e * ffn, d), gpu.load_weight(mk(ffn, d), ob.Q4_K, e * ffn, d),
@@ -517,7 +521,8 @@ def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float) 
     flops = 2.0 * m * ksel * 3 * ffn * d
     for b in (wg.buf, wu.buf, wd.buf, h, lg, idx, wgt, out, work):
         gpu.free(b)
-    return {"workload": "moe_q4k_e8_top2_m64_d4096_ffn14336", "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
+    gpu.set_option("moe_gemm_rows", 0)
+    return {"workload": f"moe_q4k_e8_top2_m{m}_d4096_ffn14336" + ("_grouped_gemm" if gemm_rows else ""), "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
             "frac_of_hbm_peak": round(gguf / us / 1e3 / hbm_peak, 4), "TFLOP/s": round(flops / us / 1e6, 2),
             "frac_of_tensor_peak": round(flops / us / 1e6 / tc_peak, 5), "expert_bytes": gguf}
 

@@ -101,6 +101,11 @@ extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int val
         ctx->gemv_slim = value;
         return 0;
     }
+    if (!strcmp(key, "moe_gemm_rows")) {
+        if (value < 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: moe_gemm_rows must be >= 0");
+        ctx->moe_gemm_rows = value;
+        return 0;
+    }
     if (!strcmp(key, "gemm_ksplit")) {
         if (value < 0 || value > 64) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemm_ksplit must be 0..64");
         ctx->gemm_ksplit = value;

@@ -20,6 +20,7 @@ struct ojas_b200_ctx {
     uint64_t launches = 0;
     int gemv_mma = 1;            // Q4_K GEMV on the integer tensor-core path: 0 never, 1 for 2..8 rows, 2 always
     int gemv_slim = 1;           // single-row Q4_K GEMV in the half-size kernel: 0 never, 1 for small matrices, 2 always
+    int moe_gemm_rows = 0;       // expert FFN: grouped tensor-core GEMMs from this many rows per expert on average (0: never)
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
     int gemv_depth = 4;          // accepted and ignored (the GEMV ring has two stages)
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
@@ -127,6 +128,12 @@ static inline WeightPlanes weight_planes_at(uint32_t type, const void *w, size_t
 int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &planes, const int8_t *q, const float *scales,
                       const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
                       size_t K, size_t N);
+
+// Prefill-sized expert groups: f32 rows -> the GEMM's f16 activation format (Q8_K-quantized when `quant`), and the
+// tensor-core GEMM over the rows [*grp_offset, + *grp_count) of xh / y (counts read on the device; y pre-zeroed).
+int ojas_gemm_prep(ojas_b200_ctx *ctx, const float *x, void *xh, size_t rows, size_t K, bool quant);
+int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t x_rows, const WeightPlanes &wp, float *y, size_t K,
+                      size_t N, size_t rows_bound, const int *grp_count, const int *grp_offset);
 
 // ---------------------------------------------------------------------------- device helpers
 #ifdef __CUDACC__

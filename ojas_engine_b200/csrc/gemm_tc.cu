@@ -44,6 +44,8 @@ struct GemmArgs {
     int accum;           // 1: y += result
     int ksplit;          // 0: K ranges balanced across the CTAs; S > 0: every tile's K range cut into S pieces
     int e2;              // balanced split: cost of a tile's end in half super-blocks (see ts_share_begin)
+    const int *grp_count;    // grouped form (experts): the row count and the first row of the group are read on the
+    const int *grp_offset;   // device; M is then only an upper bound used to choose the tile width
     unsigned *flags;     // per-tile "stored" marks (null: split tiles are added into a zeroed y instead)
     unsigned serial;     // the value of a mark that belongs to this launch
     int y_tma;           // 1: the epilogue writes y through bulk tensor stores (needs N % 4 == 0 and y on 16 bytes)
@@ -362,6 +364,9 @@ static void gemm_plan(ojas_b200_ctx *ctx, size_t M, size_t K, int &bn, int &kspl
     if ((size_t)ksplit > K / 256) ksplit = (int)(K / 256);   // K ranges are whole super-blocks
 }
 
+static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const WeightPlanes &wp, float *y,
+                       size_t K, size_t N, size_t M, int accum, const int *grp_count, const int *grp_offset);
+
 extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x, const void *w, float *y, size_t K, size_t N,
                               size_t M, int accum, void *workspace, size_t workspace_bytes) {
     if (!ctx) return OJAS_B200_E_ARG;
@@ -386,11 +391,25 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     else gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb);
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
 
-    // 2. plan + tensor map over xh [M rows][K halves], box = 64 halves x bn rows, 128-byte swizzle
+    return gemm_launch(ctx, type, xh, M, weight_planes(type, w, N, K), y, K, N, M, accum, nullptr, nullptr);
+}
+
+// Tensor maps, plan and launch over prepared f16 activations xh [x_rows][K].  Grouped form (grp_count != null):
+// the rows of the group are xh[*grp_offset .. + *grp_count) and go to y[*grp_offset ..); M is an upper bound
+// of the count; y must be zero where tiles can be split (the caller clears it) and is written with per-lane
+// stores, which can stop at the group's last row.
+static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const WeightPlanes &wp, float *y,
+                       size_t K, size_t N, size_t M, int accum, const int *grp_count, const int *grp_offset) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
+    const bool grouped = grp_count != nullptr;
+    const void *w = wp.p0;
+    // plan + tensor map over xh [x_rows][K halves], box = 64 halves x bn rows, 128-byte swizzle
     int bn, ksplit;
     gemm_plan(ctx, M, K, bn, ksplit);
+    if (grouped) ksplit = 0;
     CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)x_rows};
     const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
     const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)bn};
     const cuuint32_t estr[2] = {1, 1};
@@ -414,7 +433,7 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
         const cuuint64_t hdims[2] = {(cuuint64_t)(K / 4), (cuuint64_t)N};
         const cuuint64_t hstrides[1] = {(cuuint64_t)(K / 4)};
         const cuuint32_t hbox[2] = {64, (cuuint32_t)BM};
-        cr = encode(&tmap_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)weight_planes(type, w, N, K).p1, hdims, hstrides, hbox, estr,
+        cr = encode(&tmap_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)wp.p1, hdims, hstrides, hbox, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (top bits) failed (%d)", (int)cr);
@@ -422,7 +441,7 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
 
     // y as a tensor [M rows][N floats], box = 32 floats x 16 rows (one epilogue warp's staging tile)
     CUtensorMap tmap_y = tmap;
-    const bool y_tma = (N % 4 == 0) && (((uintptr_t)y & 15) == 0);
+    const bool y_tma = !grouped && (N % 4 == 0) && (((uintptr_t)y & 15) == 0);
     if (y_tma) {
         const cuuint64_t ydims[2] = {(cuuint64_t)N, (cuuint64_t)M};
         const cuuint64_t ystrides[1] = {(cuuint64_t)N * 4};
@@ -434,7 +453,9 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
 
     GemmArgs args{};
     args.y_tma = y_tma ? 1 : 0;
-    args.w = weight_planes(type, w, N, K);
+    args.w = wp;
+    args.grp_count = grp_count;
+    args.grp_offset = grp_offset;
     args.y = y;
     args.M = (int)M; args.N = (int)N; args.K = (int)K;
     args.accum = accum ? 1 : 0;
@@ -443,13 +464,15 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     {
         const size_t tiles = ((N + BM - 1) / BM) * ((M + bn - 1) / bn), nsb = K / 256;
         const size_t units = args.ksplit ? tiles * (size_t)args.ksplit : tiles * nsb;
-        const size_t ctas = units < (size_t)ctx->sm_count ? units : (size_t)ctx->sm_count;
+        const size_t ctas = (units < (size_t)ctx->sm_count && !grouped) ? units : (size_t)ctx->sm_count;
         args.e2 = bn > 128 ? 6 : 0;      // one accumulator: the drain is exposed; two: it overlaps the next tile
         bool partial = args.ksplit > 1;
         if (!args.ksplit)
             for (size_t b = 1; b < ctas && !partial; b++)
                 partial = (ts_share_begin((long long)tiles, (int)nsb, args.e2, (long long)b, (long long)ctas) % (long long)nsb) != 0;
-        if (partial && !accum) {
+        if (grouped) {
+            // (the tile count is only known on the device: every SM gets a CTA)
+        } else if (partial && !accum) {
             // A tile whose K range is split over CTAs: either the piece with the tile's last super-block stores
             // and marks the tile and the others add after the mark (no zeroing of y), or y is zeroed and every
             // piece adds.
@@ -466,6 +489,23 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
         if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
         return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
     }
+}
+
+// ---------------------------------------------------------------- pieces the expert FFN uses
+int ojas_gemm_prep(ojas_b200_ctx *ctx, const float *x, void *xh, size_t rows, size_t K, bool quant) {
+    const long long n_sb = (long long)rows * (long long)(K / 256);
+    const long long blocks = (n_sb + 7) / 8;
+    if (blocks <= 0) return 0;
+    if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
+    if (quant) gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb);
+    else gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb);
+    OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
+    return 0;
+}
+
+int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t x_rows, const WeightPlanes &wp, float *y, size_t K,
+                      size_t N, size_t rows_bound, const int *grp_count, const int *grp_offset) {
+    return gemm_launch(ctx, type, (const __half *)xh, x_rows, wp, y, K, N, rows_bound, 0, grp_count, grp_offset);
 }
 
 // ---------------------------------------------------------------- GEMM without a caller workspace

@@ -163,7 +163,14 @@ template <int BN, int TYPE>
 __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                  const __grid_constant__ CUtensorMap tmap_w,
                                                                  const __grid_constant__ CUtensorMap tmap_h,
-                                                                 const __grid_constant__ CUtensorMap tmap_y, const GemmArgs a) {
+                                                                 const __grid_constant__ CUtensorMap tmap_y, const GemmArgs a_in) {
+    GemmArgs a = a_in;
+    int x_row0 = 0;                                          // first activation row (grouped form: the group's offset)
+    if (a_in.grp_count) {
+        a.M = __ldg(a_in.grp_count);
+        x_row0 = __ldg(a_in.grp_offset);
+        a.y = a_in.y + (size_t)x_row0 * a_in.N;
+    }
     extern __shared__ unsigned char gemm_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)gemm_smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int B_STAGE_BYTES = BN * BK * 2;
@@ -465,7 +472,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         TS_PROG(tr_kb * 16 + 2);
                         tr_kb++;
                         mbar_arrive_expect_tx(&b_full[bslot], (uint32_t)B_STAGE_BYTES);
-                        tma_load_2d(smem_b + bslot * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, pc.m0, &b_full[bslot]);
+                        tma_load_2d(smem_b + bslot * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, x_row0 + pc.m0, &b_full[bslot]);
                         if (++bslot == BS) { bslot = 0; bphase ^= 1u; }
                     }
                 }

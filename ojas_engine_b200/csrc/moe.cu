@@ -116,6 +116,28 @@ __global__ void __launch_bounds__(256) moe_silu_quant_kernel(const float *g, con
     if (lane == 0) scales[sb] = ql.scale;
 }
 
+// ---------------------------------------------------------------- prefill form helpers
+// dst[p, :] = src[tok[p], :] for rows of d f16 values (d is a multiple of 256): one block per sorted position.
+__global__ void __launch_bounds__(256) moe_gather_f16_kernel(const uint4 *src, const int *tok, uint4 *dst, int d8) {
+    const size_t p = blockIdx.x;
+    const uint4 *s = src + (size_t)__ldg(tok + p) * d8;
+    uint4 *o = dst + p * d8;
+    for (int i = threadIdx.x; i < d8; i += blockDim.x) o[i] = __ldg(s + i);
+}
+
+// g = silu(g) * u in place, the same expression as moe_silu_quant_kernel.
+__global__ void __launch_bounds__(256) moe_silu_mul_kernel(float4 *g, const float4 *u, long long n4) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    float4 a = g[i];
+    const float4 b = __ldg(u + i);
+    a.x = __fmul_rn(__fdiv_rn(a.x, 1.0f + expf(-a.x)), b.x);
+    a.y = __fmul_rn(__fdiv_rn(a.y, 1.0f + expf(-a.y)), b.y);
+    a.z = __fmul_rn(__fdiv_rn(a.z, 1.0f + expf(-a.z)), b.z);
+    a.w = __fmul_rn(__fdiv_rn(a.w, 1.0f + expf(-a.w)), b.w);
+    g[i] = a;
+}
+
 // ---------------------------------------------------------------- combine
 // out[t, :] (=, +=) sum_j wgt[t, j] * yd[pos[t*KSEL + j], :], picks added in order j = 0, 1, ... as the
 // CPU path does (crates/ojas-cpu/src/cpu_glm.rs:581).
@@ -150,6 +172,7 @@ struct MoeWorkspace {
     float *g, *u;                                // gate / up outputs      [A, ffn]
     int8_t *aq; float *as; int32_t *ab;          // quantized SwiGLU       [A, ffn]
     float *yd;                                   // down outputs           [A, d]
+    void *xh, *xhs;                              // prefill form: f16 activations of h [M, d] and of its sorted rows [A, d]
     size_t bytes;
 };
 
@@ -164,6 +187,7 @@ MoeWorkspace moe_carve(void *base, size_t M, size_t E, size_t KSEL, size_t d, si
     w.g = (float *)take(A * ffn * 4); w.u = (float *)take(A * ffn * 4);
     w.aq = (int8_t *)take(A * ffn); w.as = (float *)take(A * (ffn / 256) * 4); w.ab = (int32_t *)take(A * (ffn / 32) * 4);
     w.yd = (float *)take(A * d * 4);
+    w.xh = take(M * d * 2); w.xhs = take(A * d * 2);
     w.bytes = off;
     return w;
 }
@@ -192,6 +216,45 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: misaligned pointer");
     const size_t A = M * KSEL;
     const MoeWorkspace w = moe_carve(workspace, M, E, KSEL, d, ffn);
+
+    // Prefill-sized batches (many rows per expert): the expert matmuls run as grouped tensor-core GEMMs over the
+    // sorted rows, each reading its row count and offset on the device.  Arithmetic contract as ojas_b200_gemm:
+    // h and the SwiGLU output are quantized to Q8_K and enter the MMA as f16(scale * q).
+    if (ctx->moe_gemm_rows > 0 && A / E >= (size_t)ctx->moe_gemm_rows) {
+        const size_t hint = (A / E) * 3 / 2 + 8 < M ? (A / E) * 3 / 2 + 8 : M;   // tile width for a typical group
+        int rc = ojas_gemm_prep(ctx, h, w.xh, M, d, true);
+        if (rc) return rc;
+        moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
+        OJAS_LAUNCH_CHECK(ctx, "moe_group");
+        moe_gather_f16_kernel<<<(unsigned)A, 256, 0, ctx->stream>>>((const uint4 *)w.xh, w.tok, (uint4 *)w.xhs, (int)(d / 8));
+        OJAS_LAUNCH_CHECK(ctx, "moe_gather");
+        OJAS_CUDA(ctx, cudaMemsetAsync(w.g, 0, A * ffn * sizeof(float), ctx->stream));   // split tiles are added into zeros
+        OJAS_CUDA(ctx, cudaMemsetAsync(w.u, 0, A * ffn * sizeof(float), ctx->stream));
+        for (size_t e = 0; e < E; e++) {
+            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_planes_at(type_gu, wg, E * ffn, d, e * ffn), w.g, d, ffn, hint,
+                                   w.counts + e, w.offsets + e);
+            if (rc) return rc;
+            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_planes_at(type_gu, wu, E * ffn, d, e * ffn), w.u, d, ffn, hint,
+                                   w.counts + e, w.offsets + e);
+            if (rc) return rc;
+        }
+        const long long n4 = (long long)(A * ffn / 4);
+        moe_silu_mul_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((float4 *)w.g, (const float4 *)w.u, n4);
+        OJAS_LAUNCH_CHECK(ctx, "moe_silu_mul");
+        void *ah = (void *)w.u;                      // the up outputs are consumed: their space takes the f16 SwiGLU rows
+        rc = ojas_gemm_prep(ctx, w.g, ah, A, ffn, true);
+        if (rc) return rc;
+        OJAS_CUDA(ctx, cudaMemsetAsync(w.yd, 0, A * d * sizeof(float), ctx->stream));
+        for (size_t e = 0; e < E; e++) {
+            rc = ojas_gemm_grouped(ctx, type_d, ah, A, weight_planes_at(type_d, wd, E * d, ffn, e * d), w.yd, ffn, d, hint,
+                                   w.counts + e, w.offsets + e);
+            if (rc) return rc;
+        }
+        const dim3 grid2((unsigned)((d + 255) / 256), (unsigned)M);
+        moe_combine_kernel<<<grid2, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0);
+        OJAS_LAUNCH_CHECK(ctx, "moe_combine");
+        return 0;
+    }
 
     int rc = ojas_b200_quant_q8k(ctx, h, M, d, w.xq, w.xs, w.xb);
     if (rc) return rc;
