@@ -63,7 +63,10 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
  * "gemv_mma" (0, 1 = default, 2): Q4_K batches on the integer tensor-core inner loop never / for 2..8
  * rows / also for one row.  "gemv_slim" (0, 1 = default, 2): the half-size single-row Q4_K kernel
  * never / for small matrices / always.  "gemm_ksplit": 0 = K ranges balanced across the SMs, S > 0 =
- * every tile's K range cut into S pieces.  "gemv_depth" is kept for compatibility and ignored. */
+ * every tile's K range cut into S pieces.  "moe_gemm_rows" (default 0 = off): from this many rows per expert
+ * on average the expert FFN runs as grouped tensor-core GEMMs (faster at prefill sizes; the FFN output is
+ * then 4e-3..6e-3 from the CPU path instead of exact in its integer block dots).  "gemv_depth" is kept for
+ * compatibility and ignored. */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
