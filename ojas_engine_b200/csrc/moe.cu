@@ -221,7 +221,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     // sorted rows, each reading its row count and offset on the device.  Arithmetic contract as ojas_b200_gemm:
     // h and the SwiGLU output are quantized to Q8_K and enter the MMA as f16(scale * q).
     if (ctx->moe_gemm_rows > 0 && A / E >= (size_t)ctx->moe_gemm_rows) {
-        const size_t hint = (A / E) * 3 / 2 + 8 < M ? (A / E) * 3 / 2 + 8 : M;   // tile width for a typical group
+        const size_t hint = A / E;                   // the tile width is chosen for a group of average size
         int rc = ojas_gemm_prep(ctx, h, w.xh, M, d, true);
         if (rc) return rc;
         moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
