@@ -2,7 +2,7 @@
 //
 // tcgen05.mma takes its A operand either from shared memory or from TMEM.  Here the dequantizing warps
 // write the f16 weight tile straight into TMEM (tcgen05.st: lane = weight row, one 32-bit column = two
-// consecutive k), so shared memory holds only the activation tiles and the raw Q4_K nibbles.  That buys
+// consecutive k), so shared memory holds only the activation tiles and the raw weight tiles.  That buys
 // ring depth, which is what the pipeline needs: a stage passes through three hand-offs (MMA done ->
 // dequantizer, dequantizer -> MMA thread, MMA thread -> tensor pipe), each several hundred cycles, and a
 // four-deep ring of 512-cycle stages cannot cover them.
@@ -10,8 +10,11 @@
 //   TMEM columns 256..511  eight A stages of 128 rows x 64 k (32 columns each) = two super-blocks
 //   shared memory          4-8 activation stages (BN tokens x 64 k, by TMA) + three raw Q4_K / Q6_K tiles + staging
 // Work is cut "stream-K" style: the (tile, super-block) pairs are numbered tile-major and CTA b takes the
-// b-th equal share of that list, so every SM gets the same number of super-blocks whatever the tile
-// count; a tile whose K range is split across CTAs is summed with fp32 atomics into y (zeroed first).
+// b-th share of equal cost of that list, so every SM gets the same work whatever the tile count.  A tile
+// whose K range is split across CTAs is combined without zeroing y: the piece that ends the K range stores
+// and marks the tile, the other pieces wait for the mark and add (see the epilogue); without marks (forced
+// split, grouped form, y not addressable by TMA) the pieces add into a y the host has zeroed.
+// Grouped form (expert FFN): the row count and first row of the group are read from device memory.
 #pragma once
 
 constexpr int TS_A_STAGES = 8;
