@@ -366,10 +366,11 @@ def run_ours(args) -> None:
                         extras.append(gemm_case(gpu, ob, tag, m, n, k, 10, 3, tc_peak))
                     except Exception as exc:
                         extras.append({"workload": f"{tag}_gemm_m{m}_n{n}_k{k}", "error": str(exc)})
-                try:
-                    extras.append(moe_case(gpu, ob, 5, 2, hbm_peak, tc_peak))
-                except Exception as exc:
-                    extras.append({"workload": "moe", "error": str(exc)})
+                for tokens, rows in ((64, 0), (2048, 32)):      # config 3 as stated; a prefill-sized batch on grouped GEMMs
+                    try:
+                        extras.append(moe_case(gpu, ob, 5, 2, hbm_peak, tc_peak, tokens, rows))
+                    except Exception as exc:
+                        extras.append({"workload": f"moe_m{tokens}", "error": str(exc)})
         traffic = profile_traffic()
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
