@@ -72,6 +72,21 @@ def test_config3_q4k_prefill_m2048(gpu):
     _gemm_case(gpu, "q4k", 2048, 4096, 4096, seed=4)
 
 
+def test_random_shapes(gpu):
+    """Seeded sweep over ragged shapes, all three formats, accumulate and forced-split forms: the work list of the
+    GEMM (shares of (tile, super-block) pairs, split tiles, token-tile widths) takes a different form for almost
+    every one of them."""
+    rng = np.random.default_rng(2024)
+    for _ in range(48):
+        tag = ["q4k", "q6k", "q80"][rng.integers(3)]
+        k = int(rng.integers(1, 17)) * 256
+        n, m = int(rng.integers(1, 2500)), int(rng.integers(9, 600))
+        if n * k * m > 2e8:
+            m = max(9, int(2e8 // (n * k)))
+        _gemm_case(gpu, tag, m, n, k, source="synth" if rng.integers(2) else "gauss", accum=bool(rng.integers(2)),
+                   ksplit=int([0, 0, 0, 2, 5][rng.integers(5)]), seed=int(rng.integers(1000)))
+
+
 def test_repeated_calls_reuse_the_tile_marks(gpu):
     """Tiles whose K range is shared by several CTAs are marked "stored" with a per-launch serial number in
     memory the context owns; launches in a row (same and different shapes) must not see each other's marks."""
