@@ -60,8 +60,8 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
  * engine reads its OJAS_* switches, crates/ojas-core/src/config.rs:1-22): GEMVs and the GEMM are launched
  * with programmatic dependent launch, so a kernel's weight prefetch and set-up overlap the tail of the
  * kernel before it in the stream (activations and y are only touched after the wait on that kernel).
- * "gemv_mma" (0, 1 = default, 2): Q4_K batches on the integer tensor-core inner loop never / for 2..8
- * rows / also for one row.  "gemv_slim" (0, 1 = default, 2): the half-size single-row Q4_K kernel
+ * "gemv_mma" (0, 1 = default, 2): batches on the tensor-core inner loops never / from three rows (Q4_K,
+ * Q6_K) or two rows (Q8_0) / always, one row included.  "gemv_slim" (0, 1 = default, 2): the half-size single-row Q4_K kernel
  * never / for small matrices / always.  "gemm_ksplit": 0 = K ranges balanced across the SMs, S > 0 =
  * every tile's K range cut into S pieces.  "moe_gemm_rows" (default 0 = off): from this many rows per expert
  * on average the expert FFN runs as grouped tensor-core GEMMs (faster at prefill sizes; the FFN output is

@@ -18,7 +18,7 @@ struct ojas_b200_ctx {
     int sm_count = 0;
     int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
     uint64_t launches = 0;
-    int gemv_mma = 1;            // Q4_K GEMV on the integer tensor-core path: 0 never, 1 for 2..8 rows, 2 always
+    int gemv_mma = 1;            // batch GEMVs on the tensor-core loops: 0 never, 1 from 3 rows (K-quants) / 2 rows (Q8_0), 2 always
     int gemv_slim = 1;           // single-row Q4_K GEMV in the half-size kernel: 0 never, 1 for small matrices, 2 always
     int moe_gemm_rows = 0;       // expert FFN: grouped tensor-core GEMMs from this many rows per expert on average (0: never)
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it

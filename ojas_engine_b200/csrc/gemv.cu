@@ -924,7 +924,7 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
 // itself (M * K / 256 warp tasks each).  From a few dozen tasks per warp on that prologue outweighs the
 // matrix, so the batch is quantized once into the context's scratch and the GEMV copies the result.
 static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs &args, size_t M) {
-    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch) return false;
+    if (preq || type == OJAS_B200_Q8_0 || M < 3 || !ctx->act_scratch) return false;
     const size_t values = M * (size_t)args.K;
     if (values > OJAS_ACT_SCRATCH_VALUES || values < 32768) return false;
     int8_t *q = (int8_t *)ctx->act_scratch;
@@ -943,8 +943,8 @@ static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvA
 
 static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args, size_t M) {
     if (ctx->gemv_mma != 0 && gemv_prequantize(ctx, type, preq, args, M)) preq = true;
-    // Q4_K batches of 2..8 rows (or every Q4_K call when the option says so) take the integer tensor-core path
-    if (type == OJAS_B200_Q4_K && ctx->gemv_mma != 0 && (M >= 2 || ctx->gemv_mma == 2)) {
+    // K-quant batches of 3..8 rows and Q8_0 batches of 2..8 rows (or every call when the option says so) take the tensor-core paths
+    if (type == OJAS_B200_Q4_K && ctx->gemv_mma != 0 && (M >= 3 || ctx->gemv_mma == 2)) {   // at two rows the per-lane loop is still faster
         GemvArgs b = args;
         b.M = (int)M;
         const int rc = gemv_mma_launch(ctx, preq, b);
@@ -954,7 +954,7 @@ static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args,
         const int rc = gemv_mma8_run(ctx, args, M);
         if (rc != 1) return rc;
     }
-    if (type == OJAS_B200_Q6_K && ctx->gemv_mma != 0 && (M >= 2 || ctx->gemv_mma == 2)) {
+    if (type == OJAS_B200_Q6_K && ctx->gemv_mma != 0 && (M >= 3 || ctx->gemv_mma == 2)) {
         GemvArgs b = args;
         b.M = (int)M;
         const int rc = gemv_mma6_launch(ctx, preq, b);
