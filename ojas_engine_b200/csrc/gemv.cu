@@ -818,15 +818,33 @@ static int gemv_mma8_run(ojas_b200_ctx *ctx, GemvArgs args, size_t M) {
         if (mma8_plan(ctx, t, grid, smem)) cap = m;
     }
     if (!cap) return 1;
+    // a batch is split into its two f16 terms once per call (context scratch: 4 bytes per value + factors) instead
+    // of once per CTA
+    const size_t values = M * (size_t)args.K;
+    const bool pre = M >= 2 && ctx->act_scratch && values >= 16384 && values * 4 + values / 256 * 4 <= OJAS_ACT_SCRATCH_BYTES;
+    __half *shi = (__half *)ctx->act_scratch, *slo = shi + values;
+    float *sfx = (float *)(slo + values);
+    if (pre) {
+        const long long n_sb = (long long)(values / 256);
+        q80_split_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(args.x, (uint4 *)shi, (uint4 *)slo, sfx, n_sb);
+        OJAS_LAUNCH_CHECK(ctx, "q80_split");
+    }
     for (size_t m0 = 0; m0 < M; m0 += (size_t)cap) {
         GemvArgs b = args;
         b.M = (int)((M - m0) < (size_t)cap ? (M - m0) : (size_t)cap);
         b.x = args.x + m0 * args.K;
         b.y = args.y + m0 * args.N;
+        if (pre) {
+            b.q = (const int8_t *)(shi + m0 * args.K);
+            b.bsums = (const int32_t *)(slo + m0 * args.K);
+            b.scales = sfx + m0 * ((size_t)args.K / 256);
+        }
         const int warps = mma8_plan(ctx, b, grid, smem);
         int rc;
-        if (warps == 16) rc = launch_gemv_threads(ctx, gemv_q80_mma_kernel<16>, b, grid, 512, smem, "gemv_q80_mma");
-        else rc = launch_gemv_threads(ctx, gemv_q80_mma_kernel<8>, b, grid, 256, smem, "gemv_q80_mma");
+        if (warps == 16) rc = pre ? launch_gemv_threads(ctx, gemv_q80_mma_kernel<16, true>, b, grid, 512, smem, "gemv_q80_mma")
+                                  : launch_gemv_threads(ctx, gemv_q80_mma_kernel<16, false>, b, grid, 512, smem, "gemv_q80_mma");
+        else rc = pre ? launch_gemv_threads(ctx, gemv_q80_mma_kernel<8, true>, b, grid, 256, smem, "gemv_q80_mma")
+                      : launch_gemv_threads(ctx, gemv_q80_mma_kernel<8, false>, b, grid, 256, smem, "gemv_q80_mma");
         if (rc) return rc;
     }
     return 0;

@@ -489,7 +489,50 @@ __device__ __forceinline__ uint32_t s8x2_to_h2(uint32_t w_biased, int sel) {
     return *reinterpret_cast<const uint32_t *>(&r);
 }
 
-template <int WARPS>
+// One block of 256 activations -> the two f16 terms and the power-of-two factor that scales their sum back.
+__device__ __forceinline__ void q80_split_block(const float *seg, int lane, uint4 &hi, uint4 &lo, float &up) {
+    const float4 p0 = __ldg(reinterpret_cast<const float4 *>(seg) + lane * 2);
+    const float4 p1 = __ldg(reinterpret_cast<const float4 *>(seg) + lane * 2 + 1);
+    const float v[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    // bring the largest magnitude into [2^13, 2^14): hi never overflows f16 and lo stays normal for all
+    // but terms 2^-24 below it; mx == 0, infinities and NaNs keep a factor of 1
+    int e = 0;
+    if (mx > 0.0f && mx < 3.0e38f) e = ilogbf(mx) - 13;
+    e = e < -100 ? -100 : e;                                  // keep 2^-e finite for vanishing blocks
+    const float down = ldexpf(1.0f, -e);
+    up = ldexpf(1.0f, e);
+    uint32_t hw[4], lw[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float s0 = v[2 * i] * down, s1 = v[2 * i + 1] * down;
+        const __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
+        const __half l0 = __float2half_rn(s0 - __half2float(h0)), l1 = __float2half_rn(s1 - __half2float(h1));
+        hw[i] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        lw[i] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+    }
+    hi = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+    lo = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+}
+
+// The split of a whole batch, once per call: hi, lo [rows][K] f16 in natural order, fx [rows][K / 256].
+__global__ void __launch_bounds__(256) q80_split_kernel(const float *x, uint4 *hi, uint4 *lo, float *fx, long long n_sb) {
+    const int lane = threadIdx.x & 31;
+    const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (sb >= n_sb) return;
+    uint4 h, l;
+    float up;
+    q80_split_block(x + sb * 256, lane, h, l, up);
+    hi[sb * 32 + lane] = h;
+    lo[sb * 32 + lane] = l;
+    if (lane == 0) fx[sb] = up;
+}
+
+template <int WARPS, bool PRE>
 __device__ __forceinline__ void gemv_q80_mma_body(const GemvArgs &a) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int nsb = a.K >> 8, S = a.S, SP = nsb / S;
@@ -537,35 +580,27 @@ __device__ __forceinline__ void gemv_q80_mma_body(const GemvArgs &a) {
     issue(ii, 0);
     next(ii);
     grid_dependency_wait();
-    // activations: one warp per (row, 256 values); lane l owns values 8l .. 8l+7
-    for (int u = warp; u < a.M * nsb; u += WARPS) {
-        const int m = u / nsb, sb = u - m * nsb;
-        const float4 p0 = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)m * a.K + (size_t)sb * 256) + lane * 2);
-        const float4 p1 = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)m * a.K + (size_t)sb * 256) + lane * 2 + 1);
-        const float v[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-        float mx = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        // bring the largest magnitude into [2^13, 2^14): hi never overflows f16 and lo stays normal for all
-        // but terms 2^-24 below it; mx == 0, infinities and NaNs keep a factor of 1
-        int e = 0;
-        if (mx > 0.0f && mx < 3.0e38f) e = ilogbf(mx) - 13;
-        e = e < -100 ? -100 : e;                              // keep 2^-e finite for vanishing blocks
-        const float down = ldexpf(1.0f, -e), up = ldexpf(1.0f, e);
-        uint32_t hw[4], lw[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float s0 = v[2 * i] * down, s1 = v[2 * i + 1] * down;
-            const __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
-            const __half l0 = __float2half_rn(s0 - __half2float(h0)), l1 = __float2half_rn(s1 - __half2float(h1));
-            hw[i] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
-            lw[i] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+    if (!PRE) {
+        // activations: one warp per (row, 256 values); lane l owns values 8l .. 8l+7
+        for (int u = warp; u < a.M * nsb; u += WARPS) {
+            const int m = u / nsb, sb = u - m * nsb;
+            uint4 hi, lo;
+            float up;
+            q80_split_block(a.x + (size_t)m * a.K + (size_t)sb * 256, lane, hi, lo, up);
+            *reinterpret_cast<uint4 *>(xh + (size_t)m * xstride + sb * 256 + lane * 8) = hi;
+            *reinterpret_cast<uint4 *>(xl + (size_t)m * xstride + sb * 256 + lane * 8) = lo;
+            if (lane == 0) fx[m * nsb + sb] = up;
         }
-        *reinterpret_cast<uint4 *>(xh + (size_t)m * xstride + sb * 256 + lane * 8) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-        *reinterpret_cast<uint4 *>(xl + (size_t)m * xstride + sb * 256 + lane * 8) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-        if (lane == 0) fx[m * nsb + sb] = up;
+    } else {
+        // split once per call by q80_split_kernel: a.q = hi terms, a.bsums = lo terms (both [M][K] f16), a.scales = factors
+        const int units = a.K >> 3;
+        const uint4 *shi = reinterpret_cast<const uint4 *>(a.q), *slo = reinterpret_cast<const uint4 *>(a.bsums);
+        for (int idx = threadIdx.x; idx < a.M * units; idx += blockDim.x) {
+            const int m = idx / units, un = idx - m * units;
+            *reinterpret_cast<uint4 *>(xh + (size_t)m * xstride + un * 8) = __ldg(shi + idx);
+            *reinterpret_cast<uint4 *>(xl + (size_t)m * xstride + un * 8) = __ldg(slo + idx);
+        }
+        for (int idx = threadIdx.x; idx < a.M * nsb; idx += blockDim.x) fx[idx] = __ldg(a.scales + idx);
     }
     __syncthreads();
     grid_launch_dependents();
@@ -650,5 +685,5 @@ __device__ __forceinline__ void gemv_q80_mma_body(const GemvArgs &a) {
     }
 }
 
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 1) gemv_q80_mma_kernel(const GemvArgs a) { gemv_q80_mma_body<WARPS>(a); }
+template <int WARPS, bool PRE>
+__global__ void __launch_bounds__(WARPS * 32, 1) gemv_q80_mma_kernel(const GemvArgs a) { gemv_q80_mma_body<WARPS, PRE>(a); }
