@@ -24,7 +24,9 @@ __device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, 
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
-// Activations into shared memory in natural order: xq [M][K + 16] int8, sx [M][nsb] f32, bs [M][nsb * 8] i32.
+// Activations into shared memory in natural order: xq [M][K + 16] int8, sx [M][nsb] f32, and the per-32 sums of
+// every super-block as two bytes each, sum = 64 * hi + lo with lo in 0..63 and hi in -64..63 (both fit the s8
+// operand of the MMA that forms the mins term): bs bytes [M][nsb][32] = lo[8], hi[8], 16 unused.
 template <int WARPS, bool PREQ>
 __device__ __forceinline__ void stage_q8k_rows(const GemvArgs &a, unsigned char *xq, float *sx, int *bs, int nsb, int xstride) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -36,7 +38,11 @@ __device__ __forceinline__ void stage_q8k_rows(const GemvArgs &a, unsigned char 
             int s = ql.sum8;
             s += __shfl_xor_sync(0xffffffffu, s, 1);
             s += __shfl_xor_sync(0xffffffffu, s, 2);
-            if ((lane & 3) == 0) bs[(m * nsb + sb) * 8 + (lane >> 2)] = s;
+            if ((lane & 3) == 0) {
+                unsigned char *bb = reinterpret_cast<unsigned char *>(bs) + (size_t)(m * nsb + sb) * 32 + (lane >> 2);
+                bb[0] = (unsigned char)(s & 63);
+                bb[8] = (unsigned char)((s >> 6) & 0xff);
+            }
             if (lane == 0) sx[m * nsb + sb] = ql.scale;
         }
     } else {
@@ -51,8 +57,11 @@ __device__ __forceinline__ void stage_q8k_rows(const GemvArgs &a, unsigned char 
             sx[idx] = __ldg(a.scales + (size_t)src_row(a, m) * nsb + (idx - m * nsb));
         }
         for (int idx = threadIdx.x; idx < a.M * nsb * 8; idx += blockDim.x) {
-            const int m = idx / (nsb * 8);
-            bs[idx] = __ldg(a.bsums + (size_t)src_row(a, m) * nsb * 8 + (idx - m * nsb * 8));
+            const int m = idx / (nsb * 8), rem = idx - m * nsb * 8;
+            const int s = __ldg(a.bsums + (size_t)src_row(a, m) * nsb * 8 + rem);
+            unsigned char *bb = reinterpret_cast<unsigned char *>(bs) + (size_t)(m * nsb + (rem >> 3)) * 32 + (rem & 7);
+            bb[0] = (unsigned char)(s & 63);
+            bb[8] = (unsigned char)((s >> 6) & 0xff);
         }
     }
 }
@@ -115,7 +124,7 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
     // this lane's accumulators: rows g, g + 8 of the tile x tokens 8h + 2q, 8h + 2q + 1 (h = token half)
     bool tok_b[NT], tok0[NT], tok1[NT];
     const unsigned char *xb[NT];
-    const int *bs0[NT], *bs1[NT];
+    const unsigned char *bsb[NT];                            // this lane's bytes of the mins-term B operand (token 8h + g)
     const float *sx0[NT], *sx1[NT];
     float acc[NT][4];
 #pragma unroll
@@ -123,7 +132,7 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
         const int tb = 8 * h + g, t0 = 8 * h + 2 * q, t1 = t0 + 1;
         tok_b[h] = tb < a.M; tok0[h] = t0 < a.M; tok1[h] = t1 < a.M;
         xb[h] = xq + (size_t)(tok_b[h] ? tb : 0) * xstride + 4 * q;
-        bs0[h] = bs + (tok0[h] ? t0 : 0) * nsb * 8; bs1[h] = bs + (tok1[h] ? t1 : 0) * nsb * 8;
+        bsb[h] = reinterpret_cast<const unsigned char *>(bs) + (size_t)(tok_b[h] ? tb : 0) * nsb * 32 + 4 * q;
         sx0[h] = sx + (tok0[h] ? t0 : 0) * nsb; sx1[h] = sx + (tok1[h] ? t1 : 0) * nsb;
         acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
     }
@@ -143,7 +152,29 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
 #pragma unroll
         for (int h = 0; h < NT; h++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) isum[h][i] = msum[h][i] = 0;
+            for (int i = 0; i < 4; i++) isum[h][i] = 0;
+        {
+            // mins term sum_j m_j * bsum_j for 16 rows x 8 tokens with two MMAs: A = the rows' eight 6-bit mins as
+            // bytes (k 0..7), B = the low / high bytes of the tokens' eight sub-block sums; sum = lo + 64 * hi
+            const uint32_t ga0 = Ha.y, ga1 = __funnelshift_r(Ha.y, Ha.z, 24), ga2 = __funnelshift_r(Ha.z, Ha.w, 16), ga3 = Ha.w >> 8;
+            const uint32_t gb0 = Hb.y, gb1 = __funnelshift_r(Hb.y, Hb.z, 24), gb2 = __funnelshift_r(Hb.z, Hb.w, 16), gb3 = Hb.w >> 8;
+            auto two_mins = [](uint32_t grp) { return ((grp >> 12) & 0x3fu) | ((grp >> 10) & 0x3f00u); };   // m(2c), m(2c+1) as bytes
+            const uint32_t ma = q == 0 ? (two_mins(ga0) | (two_mins(ga1) << 16)) : q == 1 ? (two_mins(ga2) | (two_mins(ga3) << 16)) : 0u;
+            const uint32_t mb = q == 0 ? (two_mins(gb0) | (two_mins(gb1) << 16)) : q == 1 ? (two_mins(gb2) | (two_mins(gb3) << 16)) : 0u;
+#pragma unroll
+            for (int h = 0; h < NT; h++) {
+                uint32_t bl = 0u, bh = 0u;
+                if (tok_b[h] && q < 2) {
+                    bl = *reinterpret_cast<const uint32_t *>(bsb[h] + sb * 32);
+                    bh = *reinterpret_cast<const uint32_t *>(bsb[h] + sb * 32 + 8);
+                }
+                int dl[4], dh[4];
+                mma_u8s8(dl, ma, mb, 0u, 0u, bl, 0u);
+                mma_u8s8(dh, ma, mb, 0u, 0u, bh, 0u);
+#pragma unroll
+                for (int i = 0; i < 4; i++) msum[h][i] = dl[i] + 64 * dh[i];
+            }
+        }
 #pragma unroll
         for (int c = 0; c < 4; c++) {
             // chunk c: piece h = 0 at byte c*16 (weights 64c + 0..15 low nibble, 64c + 32.. high), h = 1 at 64 + c*16
@@ -158,7 +189,6 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
                 const uint32_t a0 = (wa0 >> (4 * nh)) & 0x0f0f0f0fu, a1 = (wb0 >> (4 * nh)) & 0x0f0f0f0fu;
                 const uint32_t a2 = (wa1 >> (4 * nh)) & 0x0f0f0f0fu, a3 = (wb1 >> (4 * nh)) & 0x0f0f0f0fu;
                 const int sa = (int)((ga >> (6 * nh)) & 63u), sb_ = (int)((gb >> (6 * nh)) & 63u);
-                const int ma = (int)((ga >> (12 + 6 * nh)) & 63u), mb = (int)((gb >> (12 + 6 * nh)) & 63u);
 #pragma unroll
                 for (int h = 0; h < NT; h++) {                 // token half
                     uint32_t b0 = 0u, b1 = 0u;
@@ -168,9 +198,7 @@ __device__ __forceinline__ void gemv_q4k_mma_body(const GemvArgs &a) {
                     }
                     int d[4];
                     mma_u8s8(d, a0, a1, a2, a3, b0, b1);       // exact int32 sub-block dots: rows g, g+8 x two tokens
-                    const int u0 = tok0[h] ? bs0[h][sb * 8 + j] : 0, u1 = tok1[h] ? bs1[h][sb * 8 + j] : 0;
                     isum[h][0] += sa * d[0]; isum[h][1] += sa * d[1]; isum[h][2] += sb_ * d[2]; isum[h][3] += sb_ * d[3];
-                    msum[h][0] += ma * u0;   msum[h][1] += ma * u1;   msum[h][2] += mb * u0;    msum[h][3] += mb * u1;
                 }
             }
         }
