@@ -288,7 +288,15 @@ __device__ __forceinline__ void mma_u8s8_k16(int (&c)[4], uint32_t a0, uint32_t 
                  : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
 }
 
-// Activations in natural order with per-16 sums: xq [M][K + 16] int8, sx [M][nsb] f32, bs [M][nsb * 16] i32.
+__device__ __forceinline__ void mma_s8s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %8, %9, %10};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+// Activations in natural order with per-16 sums: xq [M][K + 16] int8, sx [M][nsb] f32, and the sixteen per-16 sums
+// of every super-block as two bytes each (sum = 64 * hi + lo, lo in 0..63, hi in -32..31): bs bytes [M][nsb][64] =
+// lo[16], hi[16], 32 unused.
 template <int WARPS, bool PREQ>
 __device__ __forceinline__ void stage_q8k_rows16(const GemvArgs &a, unsigned char *xq, float *sx, int *bs, int nsb, int xstride) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -298,7 +306,11 @@ __device__ __forceinline__ void stage_q8k_rows16(const GemvArgs &a, unsigned cha
             const Q8kLane ql = quant_q8k_warp(a.x + (size_t)m * a.K + (size_t)sb * 256, lane);
             *reinterpret_cast<uint2 *>(xq + (size_t)m * xstride + sb * 256 + lane * 8) = ql.packed;
             const int s = ql.sum8 + __shfl_xor_sync(0xffffffffu, ql.sum8, 1);
-            if ((lane & 1) == 0) bs[(m * nsb + sb) * 16 + (lane >> 1)] = s;
+            if ((lane & 1) == 0) {
+                unsigned char *bb = reinterpret_cast<unsigned char *>(bs) + (size_t)(m * nsb + sb) * 64 + (lane >> 1);
+                bb[0] = (unsigned char)(s & 63);
+                bb[16] = (unsigned char)((s >> 6) & 0xff);
+            }
             if (lane == 0) sx[m * nsb + sb] = ql.scale;
         }
     } else {
@@ -311,7 +323,9 @@ __device__ __forceinline__ void stage_q8k_rows16(const GemvArgs &a, unsigned cha
             s = __dp4a((int)v.y, 0x01010101, s);
             s = __dp4a((int)v.z, 0x01010101, s);
             s = __dp4a((int)v.w, 0x01010101, s);
-            bs[m * units + rem] = s;
+            unsigned char *bb = reinterpret_cast<unsigned char *>(bs) + (size_t)(m * nsb + (rem >> 4)) * 64 + (rem & 15);
+            bb[0] = (unsigned char)(s & 63);
+            bb[16] = (unsigned char)((s >> 6) & 0xff);
         }
         for (int idx = threadIdx.x; idx < a.M * nsb; idx += blockDim.x) {
             const int m = idx / nsb;
@@ -388,7 +402,7 @@ __device__ __forceinline__ void gemv_q6k_mma_body(const GemvArgs &a) {
     const int t0 = 2 * q, t1 = 2 * q + 1;
     const bool tok_b = g < a.M, tok0 = t0 < a.M, tok1 = t1 < a.M;
     const unsigned char *xb = xq + (size_t)(tok_b ? g : 0) * xstride + 4 * q;
-    const int *bs0 = bs + (tok0 ? t0 : 0) * nsb * 16, *bs1 = bs + (tok1 ? t1 : 0) * nsb * 16;
+    const unsigned char *bsb = reinterpret_cast<const unsigned char *>(bs) + (size_t)(tok_b ? g : 0) * nsb * 64 + 4 * q;
     const float *sx0 = sx + (tok0 ? t0 : 0) * nsb, *sx1 = sx + (tok1 ? t1 : 0) * nsb;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     int stage = 0;
@@ -413,10 +427,6 @@ __device__ __forceinline__ void gemv_q6k_mma_body(const GemvArgs &a) {
             const uint32_t la0 = *reinterpret_cast<const uint32_t *>(la + c * 16), la1 = *reinterpret_cast<const uint32_t *>(la + 64 + c * 16);
             const uint32_t lb0 = *reinterpret_cast<const uint32_t *>(lb + c * 16), lb1 = *reinterpret_cast<const uint32_t *>(lb + 64 + c * 16);
             const uint32_t hwa = *reinterpret_cast<const uint32_t *>(ha + c * 16), hwb = *reinterpret_cast<const uint32_t *>(hb + c * 16);
-            int4 u0 = make_int4(0, 0, 0, 0), u1 = u0;         // per-16 activation sums of the chunk's four sub-blocks
-            if (tok0) u0 = *reinterpret_cast<const int4 *>(bs0 + sb * 16 + 4 * c);
-            if (tok1) u1 = *reinterpret_cast<const int4 *>(bs1 + sb * 16 + 4 * c);
-            const int x0[4] = {u0.x, u0.y, u0.z, u0.w}, x1[4] = {u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
             for (int t = 0; t < 4; t++) {                     // sub-block j = 4c + t: weights 64c + 16t .. + 15
                 const uint32_t na = (t & 1) ? la1 : la0, nb = (t & 1) ? lb1 : lb0;
@@ -427,9 +437,25 @@ __device__ __forceinline__ void gemv_q6k_mma_body(const GemvArgs &a) {
                 int d[4];
                 mma_u8s8_k16(d, a0, a1, b0);                  // exact sums q*x: rows g, g+8 x tokens 2q, 2q+1
                 const int s_a = (int)(signed char)((sca[c] >> (8 * t)) & 0xffu), s_b = (int)(signed char)((scb[c] >> (8 * t)) & 0xffu);
-                isum[0] += s_a * (d[0] - 32 * x0[t]); isum[1] += s_a * (d[1] - 32 * x1[t]);
-                isum[2] += s_b * (d[2] - 32 * x0[t]); isum[3] += s_b * (d[3] - 32 * x1[t]);
+                isum[0] += s_a * d[0]; isum[1] += s_a * d[1];
+                isum[2] += s_b * d[2]; isum[3] += s_b * d[3];
             }
+        }
+        {
+            // the format's -32: isum -= 32 * sum_j sc_j * xsum_j, the sum over the sixteen sub-blocks by two MMAs
+            // (A = the rows' sixteen int8 sub-scales, B = low / high bytes of the tokens' per-16 activation sums)
+            uint32_t bl = 0u, bh = 0u;
+            if (tok_b) {
+                bl = *reinterpret_cast<const uint32_t *>(bsb + sb * 64);
+                bh = *reinterpret_cast<const uint32_t *>(bsb + sb * 64 + 16);
+            }
+            int cl[4], ch[4];
+            const uint32_t wa = q == 0 ? Sa.x : q == 1 ? Sa.y : q == 2 ? Sa.z : Sa.w;
+            const uint32_t wb = q == 0 ? Sb.x : q == 1 ? Sb.y : q == 2 ? Sb.z : Sb.w;
+            mma_s8s8_k16(cl, wa, wb, bl);
+            mma_s8s8_k16(ch, wa, wb, bh);
+#pragma unroll
+            for (int i = 0; i < 4; i++) isum[i] -= 32 * (cl[i] + 64 * ch[i]);
         }
         const float da = f16_bits_to_f32(__shfl_sync(0xffffffffu, d_cur, g)), db = f16_bits_to_f32(__shfl_sync(0xffffffffu, d_cur, g + 8));
         const float s0 = tok0 ? sx0[sb] : 0.f, s1 = tok1 ? sx1[sb] : 0.f;
