@@ -700,18 +700,43 @@ static size_t mma_smem_bytes(int warps, size_t M, size_t K, size_t rows_max, int
            M * nsb * 8 * 4 + (S > 1 ? tiles * S * 128 * ((M + 7) / 8) * 4 : 0) + 16;
 }
 
-// Fills S / row partition and picks 32 or 16 warps by shared-memory fit; returns 0 if neither fits.
+// Warps per CTA (hi or lo) and segments per tile (a divisor of the super-blocks per row) for the tensor-core GEMVs:
+// among the pairs that fit in shared memory, the one whose busiest warp has the fewest super-block steps; ties go to
+// more warps, then to more of them busy, then to fewer segments.  Returns the warps, 0 if nothing fits; sets S, smem.
+template <typename SmemFn>
+static int mma_pick(size_t limit, size_t rows_max, size_t nsb, int warps_hi, int warps_lo, SmemFn smem_of, int &S, size_t &smem) {
+    const size_t tiles = (rows_max + 15) / 16;
+    int best_warps = 0;
+    size_t best_steps = ~(size_t)0, best_busy = 0;
+    for (int warps = warps_hi; warps >= warps_lo; warps >>= 1) {
+        for (size_t s = 1; s <= nsb; s++) {
+            if (nsb % s) continue;
+            const size_t bytes = smem_of(warps, (int)s);
+            if (bytes > limit) continue;
+            const size_t units = tiles * s;
+            const size_t steps = ((units + (size_t)warps - 1) / (size_t)warps) * (nsb / s);
+            const size_t busy = units < (size_t)warps ? units : (size_t)warps;
+            if (steps < best_steps || (steps == best_steps && warps == best_warps && busy > best_busy)) {
+                best_steps = steps;
+                best_busy = busy;
+                best_warps = warps;
+                S = (int)s;
+                smem = bytes;
+            }
+        }
+    }
+    return best_warps;
+}
+
+// Fills S / row partition and picks 32 or 16 warps; returns 0 if neither fits.
 static int mma_plan(ojas_b200_ctx *ctx, GemvArgs &a, int &grid, size_t &smem) {
     grid = ctx->sm_count < a.N ? ctx->sm_count : a.N;
     const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
     a.rows_base = a.N / grid;
     a.rows_rem = a.N % grid;
-    for (int warps = 32; warps >= 16; warps >>= 1) {
-        a.S = mma_segments(rows_max, (size_t)a.K / 256, warps);
-        smem = mma_smem_bytes(warps, (size_t)a.M, (size_t)a.K, rows_max, a.S);
-        if (smem <= (size_t)ctx->smem_optin) return warps;
-    }
-    return 0;
+    const size_t M = (size_t)a.M, K = (size_t)a.K;
+    return mma_pick((size_t)ctx->smem_optin, rows_max, K / 256, 32, 16,
+                    [&](int warps, int S) { return mma_smem_bytes(warps, M, K, rows_max, S); }, a.S, smem);
 }
 
 template <typename KernelT>
@@ -766,12 +791,9 @@ static int mma6_plan(ojas_b200_ctx *ctx, GemvArgs &a, int &grid, size_t &smem) {
     const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
     a.rows_base = a.N / grid;
     a.rows_rem = a.N % grid;
-    for (int warps = 16; warps >= 8; warps >>= 1) {
-        a.S = mma_segments(rows_max, (size_t)a.K / 256, warps);
-        smem = mma6_smem_bytes(warps, (size_t)a.M, (size_t)a.K, rows_max, a.S);
-        if (smem <= (size_t)ctx->smem_optin) return warps;
-    }
-    return 0;
+    const size_t M = (size_t)a.M, K = (size_t)a.K;
+    return mma_pick((size_t)ctx->smem_optin, rows_max, K / 256, 16, 8,
+                    [&](int warps, int S) { return mma6_smem_bytes(warps, M, K, rows_max, S); }, a.S, smem);
 }
 
 static int gemv_mma6_launch(ojas_b200_ctx *ctx, bool preq, GemvArgs a) {
@@ -799,12 +821,9 @@ static int mma8_plan(ojas_b200_ctx *ctx, GemvArgs &a, int &grid, size_t &smem) {
     const size_t rows_max = ((size_t)a.N + grid - 1) / grid;
     a.rows_base = a.N / grid;
     a.rows_rem = a.N % grid;
-    for (int warps = 16; warps >= 8; warps >>= 1) {
-        a.S = mma_segments(rows_max, (size_t)a.K / 256, warps);
-        smem = mma8_smem_bytes(warps, (size_t)a.M, (size_t)a.K, rows_max, a.S);
-        if (smem <= (size_t)ctx->smem_optin) return warps;
-    }
-    return 0;
+    const size_t M = (size_t)a.M, K = (size_t)a.K;
+    return mma_pick((size_t)ctx->smem_optin, rows_max, K / 256, 16, 8,
+                    [&](int warps, int S) { return mma8_smem_bytes(warps, M, K, rows_max, S); }, a.S, smem);
 }
 
 // Batches of up to eight rows; a batch whose activations do not fit in shared memory is cut into smaller
