@@ -381,7 +381,7 @@ def run_ours(args) -> None:
                        "parallelism": "single GPU" if world == 1 else f"column-parallel row shards x{world}, one NCCL all-gather per step"},
             "pct_of_8TBps": value / world / 8000.0,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "gemv_q4k_slim_kernel<false>",
+                         "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "gemv_kernel<Q4_K, 1 row, f32 activations>",
                          "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH, "us_per_launch": us_per_launch},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary, "parity_rel_l2_vs_oracle": parity, "extras": extras,
@@ -417,10 +417,10 @@ def run_case(args) -> None:
     gpu = ob.B200Gpu(0)
     if args.no_pdl:
         gpu.set_option("pdl", 0)
-    if args.mma >= 0:
-        gpu.set_option("gemv_mma", args.mma)
-    if args.slim >= 0:
-        gpu.set_option("gemv_slim", args.slim)
+    if args.warps:
+        gpu.set_option("gemv_warps", args.warps)
+    if args.stages:
+        gpu.set_option("gemv_stages", args.stages)
     gguf = ob.raw_bytes(t, n, k)
     ring = args.ring or max(2, int(300e6 // gguf) + 1)
     base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
@@ -659,8 +659,8 @@ def main() -> None:
     ap.add_argument("--ring", type=int, default=0, help="--case: number of distinct weights (default: enough to pass L2)")
     ap.add_argument("--no-graph", action="store_true", help="--case: plain launches instead of a CUDA graph")
     ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: force the K split (0 = automatic)")
-    ap.add_argument("--mma", type=int, default=-1, help="--case: the gemv_mma option (0 per-lane loops only, 1 default, 2 tensor-core loop also for one row)")
-    ap.add_argument("--slim", type=int, default=-1, help="--case: the gemv_slim option (0 full-size kernel only, 1 default, 2 half-size kernel always)")
+    ap.add_argument("--warps", type=int, default=0, help="--case: the gemv_warps option (warps per CTA; 0 = chosen per shape)")
+    ap.add_argument("--stages", type=int, default=0, help="--case: the gemv_stages option (ring stages per warp; 0 = chosen per shape)")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (default: with)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -53,8 +53,8 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
         return OJAS_B200_E_CUDA;
     }
     memset(ctx->host_status, 0, 64);
-    if (cudaMalloc((void **)&ctx->gemm_flags, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(ctx->gemm_flags, 0, OJAS_GEMM_FLAG_WORDS * sizeof(unsigned int)) != cudaSuccess ||
+    if (cudaMalloc((void **)&ctx->gemm_flags, (OJAS_GEMM_FLAG_WORDS + 1) * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(ctx->gemm_flags, 0, (OJAS_GEMM_FLAG_WORDS + 1) * sizeof(unsigned int)) != cudaSuccess ||
         cudaMalloc(&ctx->act_scratch, OJAS_ACT_SCRATCH_BYTES) != cudaSuccess) {
         if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
         cudaFreeHost(ctx->host_status);
@@ -81,6 +81,7 @@ extern "C" void ojas_b200_destroy(ojas_b200_ctx *ctx) {
 extern "C" int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream) {
     if (!ctx) return OJAS_B200_E_ARG;
     if (ctx->owns_stream) {
+        OJAS_CUDA(ctx, cudaStreamSynchronize(ctx->stream));   // work queued on the private stream ends before the stream goes
         cudaStreamDestroy(ctx->stream);
         ctx->owns_stream = false;
     }
@@ -91,14 +92,14 @@ extern "C" int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream) {
 extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value) {
     if (!ctx || !key) return OJAS_B200_E_ARG;
     if (!strcmp(key, "pdl")) { ctx->pdl = value != 0; return 0; }
-    if (!strcmp(key, "gemv_mma")) {
-        if (value < 0 || value > 2) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_mma must be 0, 1 or 2");
-        ctx->gemv_mma = value;
+    if (!strcmp(key, "gemv_warps")) {
+        if (value < 0 || value > 16 || (value & (value - 1)) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_warps must be 0 (automatic), 1, 2, 4, 8 or 16");
+        ctx->gemv_warps = value;
         return 0;
     }
-    if (!strcmp(key, "gemv_slim")) {
-        if (value < 0 || value > 2) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_slim must be 0, 1 or 2");
-        ctx->gemv_slim = value;
+    if (!strcmp(key, "gemv_stages")) {
+        if (value < 0 || value > 4) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_stages must be 0 (automatic) or 1..4");
+        ctx->gemv_stages = value;
         return 0;
     }
     if (!strcmp(key, "moe_gemm_rows")) {
@@ -109,11 +110,6 @@ extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int val
     if (!strcmp(key, "gemm_ksplit")) {
         if (value < 0 || value > 64) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemm_ksplit must be 0..64");
         ctx->gemm_ksplit = value;
-        return 0;
-    }
-    if (!strcmp(key, "gemv_depth")) {
-        if (value < 2 || value > 4) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_depth must be 2..4");
-        ctx->gemv_depth = value;
         return 0;
     }
     return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: unknown key '%s'", key);

@@ -18,15 +18,14 @@ struct ojas_b200_ctx {
     int sm_count = 0;
     int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
     uint64_t launches = 0;
-    int gemv_mma = 1;            // batch GEMVs on the tensor-core loops: 0 never, 1 from 3 rows (K-quants) / 2 rows (Q8_0), 2 always
-    int gemv_slim = 1;           // single-row Q4_K GEMV in the half-size kernel: 0 never, 1 for small matrices, 2 always
+    int gemv_warps = 0;          // GEMV: warps per CTA (0: chosen per shape; otherwise 1..16)
+    int gemv_stages = 0;         // GEMV: ring stages per warp (0: chosen per shape; otherwise 1..4)
     int moe_gemm_rows = 0;       // expert FFN: grouped tensor-core GEMMs from this many rows per expert on average (0: never)
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
-    int gemv_depth = 4;          // accepted and ignored (the GEMV ring has two stages)
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
     void *act_scratch = nullptr;         // device scratch for a batch's Q8_K activations (values, scales, block sums)
-    unsigned int *gemm_flags = nullptr;  // device words, one per GEMM output tile: "the tile has been stored" marks (see gemm_ts.cuh)
-    unsigned int gemm_serial = 0;        // value that means "stored" for the GEMM launch in flight; never 0
+    unsigned int *gemm_flags = nullptr;  // device words, one per GEMM output tile: "the tile has been stored" marks (see gemm_ts.cuh),
+                                         // then one word: the value that means "stored" for the GEMM launch in flight (never 0)
     unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
     unsigned int *dev_status = nullptr;  // the same word as the device sees it
     char err[512] = {0};
@@ -56,83 +55,54 @@ int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
     } while (0)
 
 // ---------------------------------------------------------------------------- layouts
-// Repacked weights are a set of planes in one buffer; every plane starts on a 256-byte
-// boundary and every row of every plane is a whole number of 16-byte units.
+// A repacked weight is a grid of TILES: tile (u, s) holds rows 8u .. 8u+7 of super-block s (256 weights) and tiles are
+// stored unit-major, [ceil(N/8)][K/256][tile]: everything one 8-row unit needs along K is one contiguous run, and four
+// units (32 rows) of one super-block are four runs a row of tiles apart.  Inside a tile the data are 16-byte pieces,
+// piece-major and row-minor: piece p of row r sits at byte (p * 8 + r) * 16, so eight lanes that own eight
+// consecutive rows read 128 contiguous bytes per piece (coalesced from global memory, conflict-free from shared
+// memory, and one bulk copy moves whole tiles).  Rows past N are zero blocks.  Every GGUF bit is kept.
 //
-// Q4_K  (GGUF: 144 B per 256 weights: f16 d, f16 dmin, u8 sc[12], u8 qs[128])
-//   plane qs : [N][K/256][128]  nibbles; within a super-block byte h*64 + c*16 + i holds
-//              GGUF qs[c*32 + h*16 + i] (c = 64-weight chunk 0..3, h = 16-byte half), so the
-//              four lanes that share a super-block read 64 contiguous bytes per load.
-//   plane hdr: [N][K/256][16]   f16 d, f16 dmin, then the sixteen 6-bit scales / mins regrouped
-//              per chunk: bytes 4 + 3c .. 6 + 3c hold the little-endian 24-bit group
-//              s(2c) | s(2c+1) << 6 | m(2c) << 12 | m(2c+1) << 18  (same 96 bits as GGUF's sc[12]).
-// Q6_K  (GGUF: 210 B per 256: u8 ql[128], u8 qh[64], i8 sc[16], f16 d)
-//   plane lo : [N][K/256][128]  low nibbles; byte h*64 + c*16 + i: low nibble = weight
-//              64c + 16h + i, high nibble = weight 64c + 32 + 16h + i.
-//   plane hi : [N][K/256][64]   top two bits; byte c*16 + k*4 + i: bit field t (bits 2t, 2t+1)
-//              = weight 64c + 16t + 4k + i.
-//   plane sc : [N][K/256][16]   int8 sub-scales, GGUF order.
-//   plane d  : [N][K/256]       f16 super-block scale.
-// Q8_0  (GGUF: 34 B per 32: f16 d, i8 q[32])
-//   plane q  : [N][K]           int8, natural order.
-//   plane d  : [N][K/32]        f16.
-struct WeightPlanes {
-    const uint8_t *p0, *p1, *p2, *p3;
-};
+// Q4_K  (GGUF: 144 B per 256 weights: f16 d, f16 dmin, u8 sc[12], u8 qs[128])          tile = 1152 B
+//   pieces 0..7 : qs[16p .. 16p+15] in GGUF order: low nibbles = weights 64(p/2) + 16(p%2) + i, high nibbles the
+//                 same + 32 (crates/ojas-formats/src/gguf.rs:1049-1056)
+//   piece  8    : the block's first 16 bytes as they are: d, dmin, sc[12]
+// Q6_K  (GGUF: 210 B per 256: u8 ql[128], u8 qh[64], i8 sc[16], f16 d)                 tile = 1680 B
+//   pieces 0..7 : low nibbles, piece h*4 + c, byte i: low nibble = weight 64c + 16h + i, high nibble = weight
+//                 64c + 32 + 16h + i   (c = 64-weight chunk, h = 0, 1)
+//   pieces 8..11: top two bits, piece 8 + c, byte b: bit field t (bits 2t, 2t+1) = weight 64c + 16t + b
+//   piece  12   : the sixteen int8 sub-block scales, GGUF order
+//   then 8 x f16 d, one per row, at byte 13 * 128 + 2r
+// Q8_0  (GGUF: 34 B per 32: f16 d, i8 q[32]; eight blocks per 256 weights)             tile = 2176 B
+//   pieces 0..15: q[16p .. 16p+15] of the 256 weights, natural order
+//   piece  16   : the eight f16 block scales
+constexpr int OJAS_TILE_ROWS = 8;
+__host__ __device__ constexpr int tile_bytes(uint32_t type) {
+    return type == OJAS_B200_Q4_K ? 1152 : type == OJAS_B200_Q6_K ? 1680 : 2176;
+}
+// Bytes of the leading pieces that hold quants only (what the GEMM stages per tile; scales come after them).
+__host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
+    return type == OJAS_B200_Q4_K ? 1024 : type == OJAS_B200_Q6_K ? 1536 : 2048;
+}
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+static inline bool type_supported(uint32_t type) { return type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K || type == OJAS_B200_Q8_0; }
+static inline size_t tile_units(size_t N) { return (N + OJAS_TILE_ROWS - 1) / OJAS_TILE_ROWS; }
+static inline size_t repacked_size(uint32_t type, size_t N, size_t K) { return align256(tile_units(N) * (K / 256) * (size_t)tile_bytes(type)); }
 
-static inline int plane_offsets(uint32_t type, size_t N, size_t K, size_t off[5]) {
-    size_t nsb = K / 256;
-    off[0] = 0;
-    switch (type) {
-    case OJAS_B200_Q4_K:
-        off[1] = align256(N * nsb * 128);
-        off[2] = off[3] = off[4] = off[1] + align256(N * nsb * 16);
-        return 0;
-    case OJAS_B200_Q6_K:
-        off[1] = align256(N * nsb * 128);
-        off[2] = off[1] + align256(N * nsb * 64);
-        off[3] = off[2] + align256(N * nsb * 16);
-        off[4] = off[3] + align256(N * nsb * 2);
-        return 0;
-    case OJAS_B200_Q8_0:
-        off[1] = align256(N * K);
-        off[2] = off[3] = off[4] = off[1] + align256(N * (K / 32) * 2);
-        return 0;
-    default:
-        return -1;
-    }
+// First tile of rows [row0, ...) of a stacked tensor (experts stacked along N, as the engine keeps them:
+// crates/ojas-cuda/src/kernels/moe.rs:75-125 index `idx[j] * N + row`).  row0 must be a multiple of 8.
+static inline const uint8_t *weight_rows_at(uint32_t type, const void *w, size_t K, size_t row0) {
+    return (const uint8_t *)w + (row0 / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type);
 }
 
-static inline WeightPlanes weight_planes(uint32_t type, const void *w, size_t N, size_t K) {
-    size_t off[5];
-    plane_offsets(type, N, K, off);
-    const uint8_t *b = (const uint8_t *)w;
-    return WeightPlanes{b + off[0], b + off[1], b + off[2], b + off[3]};
-}
-
-// Planes of rows [row0, ...) of a stacked tensor (experts stacked along N, as the engine keeps them:
-// crates/ojas-cuda/src/kernels/moe.rs:75-125 index `idx[j] * N + row`).
-static inline WeightPlanes weight_planes_at(uint32_t type, const void *w, size_t n_total, size_t K, size_t row0) {
-    WeightPlanes p = weight_planes(type, w, n_total, K);
-    const size_t nsb = K / 256;
-    switch (type) {
-    case OJAS_B200_Q4_K: p.p0 += row0 * nsb * 128; p.p1 += row0 * nsb * 16; break;
-    case OJAS_B200_Q6_K: p.p0 += row0 * nsb * 128; p.p1 += row0 * nsb * 64; p.p2 += row0 * nsb * 16; p.p3 += row0 * nsb * 2; break;
-    default: p.p0 += row0 * K; p.p1 += row0 * (K / 32) * 2; break;
-    }
-    return p;
-}
-
-int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const WeightPlanes &planes, const int8_t *q, const float *scales,
+int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w, const int8_t *q, const float *scales,
                       const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
                       size_t K, size_t N);
 
 // Prefill-sized expert groups: f32 rows -> the GEMM's f16 activation format (Q8_K-quantized when `quant`), and the
 // tensor-core GEMM over the rows [*grp_offset, + *grp_count) of xh / y (counts read on the device; y pre-zeroed).
 int ojas_gemm_prep(ojas_b200_ctx *ctx, const float *x, void *xh, size_t rows, size_t K, bool quant);
-int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t x_rows, const WeightPlanes &wp, float *y, size_t K,
+int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t x_rows, const uint8_t *w, float *y, size_t K,
                       size_t N, size_t rows_bound, const int *grp_count, const int *grp_offset);
 
 // ---------------------------------------------------------------------------- device helpers

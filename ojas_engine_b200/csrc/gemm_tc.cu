@@ -27,18 +27,16 @@ namespace {
 constexpr int BM = 128;            // weight rows per CTA
 constexpr int BK = 64;             // k per stage = one 64-weight chunk = 128 bytes of f16
 constexpr int WQ_BUFS_MAX = 3;
-constexpr int WQ_LO_BYTES = BM * 128;   // Q4_K nibbles / Q6_K low nibbles / half a Q8_0 super-block: 128 bytes per row
-constexpr int WQ_HI_BYTES = BM * 64;    // Q6_K top bits: 64 bytes per row
-// One staged raw tile = one super-block x 128 rows: Q4_K 16 KB, Q6_K 24 KB, Q8_0 32 KB (two 128-byte halves).
-__host__ __device__ constexpr int wq_bytes(int type) {
-    return type == OJAS_B200_Q4_K ? WQ_LO_BYTES : type == OJAS_B200_Q6_K ? WQ_LO_BYTES + WQ_HI_BYTES : 2 * WQ_LO_BYTES;
-}
+// One staged raw tile = one super-block x 128 rows = the quant pieces of sixteen 8-row tiles of the weight layout
+// (common.cuh): Q4_K 16 KB, Q6_K 24 KB, Q8_0 32 KB.  Row r of 8-row tile t keeps its 16-byte piece p at
+// t * tile_quant_bytes + (p * 8 + r) * 16, so a warp's 32 consecutive rows read a piece without bank conflicts.
+__host__ __device__ constexpr int wq_bytes(int type) { return (BM / OJAS_TILE_ROWS) * tile_quant_bytes((uint32_t)type); }
 // raw tiles in flight: three, or two of the large Q8_0 tiles (so that four activation stages still fit)
 __host__ __device__ constexpr int wq_bufs(int type) { return type == OJAS_B200_Q8_0 ? 2 : 3; }
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
 struct GemmArgs {
-    WeightPlanes w;
+    const uint8_t *w;    // first tile of the weight rows (layout: common.cuh)
     float *y;
     int M, N, K;
     int accum;           // 1: y += result
@@ -47,7 +45,7 @@ struct GemmArgs {
     const int *grp_count;    // grouped form (experts): the row count and the first row of the group are read on the
     const int *grp_offset;   // device; M is then only an upper bound used to choose the tile width
     unsigned *flags;     // per-tile "stored" marks (null: split tiles are added into a zeroed y instead)
-    unsigned serial;     // the value of a mark that belongs to this launch
+    const unsigned *serial_word;   // device word holding the value that marks a tile as stored in this launch
     int y_tma;           // 1: the epilogue writes y through bulk tensor stores (needs N % 4 == 0 and y on 16 bytes)
     unsigned *status;    // device-visible status word of the context
 };
@@ -183,15 +181,24 @@ __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_c
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
 // Q4_K: A, B = the chunk's two 16-byte nibble pieces (low nibbles = weights 0..31, high = 32..63),
-// H = header (d, dmin, 24-bit scale groups), c = chunk index inside the super-block.
+// H = the block's GGUF header (d, dmin, sc[12]), c = chunk index inside the super-block.  The integer -> f16
+// step (OR the value into the mantissa of 1024.0, subtract 1024, one fused multiply-add with the scale and the
+// min term) is the one the reference's loaders use (crates/ojas-cuda/src/kernels/gemm_q.rs:104-119).
 __device__ __forceinline__ void dequant_q4k_half(const uint4 &A, const uint4 &B, const uint4 &H, int c, int half, uint32_t (&o)[16]) {
-    const int sh = (c * 24) & 31;
-    const uint32_t lo_w = (c < 2) ? H.y : (c == 2 ? H.z : H.w);
-    const uint32_t hi_w = (c < 2) ? H.z : H.w;
-    const uint32_t sg = __funnelshift_r(lo_w, hi_w, sh) >> (6 * half);     // s at bits 0..5, m at bits 12..17
+    // 6-bit scale and min of sub-block j = 2c + half (get_scale_min_k4, crates/ojas-formats/src/gguf.rs:1132-1140)
+    const int j = 2 * c + half;
+    uint32_t sv, mv;
+    if (j < 4) {
+        sv = (H.y >> (8 * j)) & 63u;
+        mv = (H.z >> (8 * j)) & 63u;
+    } else {
+        const uint32_t t = H.w >> (8 * (j - 4));
+        sv = (t & 0xFu) | (((H.y >> (8 * (j - 4) + 6)) & 3u) << 4);
+        mv = ((t >> 4) & 0xFu) | (((H.z >> (8 * (j - 4) + 6)) & 3u) << 4);
+    }
     const float d = f16_bits_to_f32(H.x), dmin = f16_bits_to_f32(H.x >> 16);
-    const __half2 ds = __float2half2_rn(d * (float)(sg & 63u));
-    const __half2 nm = __float2half2_rn(-(dmin * (float)((sg >> 12) & 63u)));
+    const __half2 ds = __float2half2_rn(d * (float)sv);
+    const __half2 nm = __float2half2_rn(-(dmin * (float)mv));
     const __half2 k1024 = u32_as_h2(0x64006400u);
     const int nsh = 4 * half;
     const uint32_t w[8] = {A.x >> nsh, A.y >> nsh, A.z >> nsh, A.w >> nsh, B.x >> nsh, B.y >> nsh, B.z >> nsh, B.w >> nsh};
@@ -254,8 +261,12 @@ __device__ __forceinline__ void dequant_q80_half(const uint4 &q0, const uint4 &q
 // in the k order the K-quant dequantizers produce ((0, 2, 1, 3) inside every group of four).
 // Otherwise xh = f16(x) in natural order (Q8_0).  One warp per 256 values.
 template <bool QUANT>
-__global__ void __launch_bounds__(256) gemm_prep_kernel(const float *x, __half *xh, long long n_sb) {
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const float *x, __half *xh, long long n_sb, unsigned *serial_word) {
     const int lane = threadIdx.x & 31;
+    if (serial_word && blockIdx.x == 0 && threadIdx.x == 0) {     // a fresh tile-mark value for the GEMM behind this kernel, never 0
+        const unsigned v = *serial_word + 1u;
+        *serial_word = v ? v : 1u;
+    }
     const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     grid_launch_dependents();   // the GEMM behind this kernel may begin its set-up; it waits for this grid before it reads xh
     if (sb >= n_sb) return;
@@ -305,8 +316,7 @@ size_t gemm_ts_smem_bytes(int bn, int type) {
 }
 
 template <int BN, int TYPE>
-int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_h,
-                      const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
     auto kernel = gemm_ts_kernel<BN, TYPE>;
     const size_t smem = gemm_ts_smem_bytes(BN, TYPE);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -323,36 +333,23 @@ int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtenso
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_w, tmap_h, tmap_y, args);
+    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_y, args);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemm_ts: %s", cudaGetErrorString(e));
     OJAS_LAUNCH_CHECK(ctx, "gemm_ts");
     return 0;
 }
 
 template <int TYPE>
-int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_h,
-                        const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
     switch (bn) {
-    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
-    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
-    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
-    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_w, tmap_h, tmap_y, args, grid);
+    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_y, args, grid);
+    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_y, args, grid);
+    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_y, args, grid);
+    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_y, args, grid);
     }
 }
 
 }  // namespace
-
-#ifdef TS_TRACE
-extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_trace(void *dst, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(dst, g_ts_trace, bytes);
-}
-extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_prog(void *dst, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(dst, g_ts_prog, bytes);
-}
-extern "C" __attribute__((visibility("default"))) int ojas_b200_debug_span(void *dst, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(dst, g_ts_span, bytes);
-}
-#endif
 
 extern "C" size_t ojas_b200_gemm_workspace_bytes(size_t M, size_t K) { return align256(M * K * 2); }
 
@@ -364,7 +361,7 @@ static void gemm_plan(ojas_b200_ctx *ctx, size_t M, size_t K, int &bn, int &kspl
     if ((size_t)ksplit > K / 256) ksplit = (int)(K / 256);   // K ranges are whole super-blocks
 }
 
-static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const WeightPlanes &wp, float *y,
+static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const uint8_t *w, float *y,
                        size_t K, size_t N, size_t M, int accum, const int *grp_count, const int *grp_offset);
 
 extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x, const void *w, float *y, size_t K, size_t N,
@@ -387,23 +384,22 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     const long long n_sb = (long long)M * (long long)(K / 256);
     const long long blocks = (n_sb + 7) / 8;
     if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
-    if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb);
-    else gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb);
+    if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb, ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS);
+    else gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb, ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS);
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
 
-    return gemm_launch(ctx, type, xh, M, weight_planes(type, w, N, K), y, K, N, M, accum, nullptr, nullptr);
+    return gemm_launch(ctx, type, xh, M, (const uint8_t *)w, y, K, N, M, accum, nullptr, nullptr);
 }
 
 // Tensor maps, plan and launch over prepared f16 activations xh [x_rows][K].  Grouped form (grp_count != null):
 // the rows of the group are xh[*grp_offset .. + *grp_count) and go to y[*grp_offset ..); M is an upper bound
 // of the count; y must be zero where tiles can be split (the caller clears it) and is written with per-lane
 // stores, which can stop at the group's last row.
-static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const WeightPlanes &wp, float *y,
+static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const uint8_t *w, float *y,
                        size_t K, size_t N, size_t M, int accum, const int *grp_count, const int *grp_offset) {
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
     const bool grouped = grp_count != nullptr;
-    const void *w = wp.p0;
     // plan + tensor map over xh [x_rows][K halves], box = 64 halves x bn rows, 128-byte swizzle
     int bn, ksplit;
     gemm_plan(ctx, M, K, bn, ksplit);
@@ -416,28 +412,6 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
     CUresult cr = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)xh, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
-
-    // raw nibble plane (Q4_K nibbles, Q6_K low nibbles: the first plane of both layouts) as bytes
-    // [N rows][K/2 bytes], box = one super-block (128 bytes) x 128 rows
-    CUtensorMap tmap_w = tmap, tmap_h = tmap;
-    {   // (Q8_0: the int8 plane [N rows][K bytes]; a super-block is two such boxes)
-        const size_t row_bytes = type == OJAS_B200_Q8_0 ? K : K / 2;
-        const cuuint64_t wdims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)N};
-        const cuuint64_t wstrides[1] = {(cuuint64_t)row_bytes};
-        const cuuint32_t wbox[2] = {128, (cuuint32_t)BM};
-        cr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)w, wdims, wstrides, wbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (weights) failed (%d)", (int)cr);
-    }
-    if (type == OJAS_B200_Q6_K) {   // top-bit plane [N rows][K/4 bytes], box = 64 bytes x 128 rows, 64-byte swizzle
-        const cuuint64_t hdims[2] = {(cuuint64_t)(K / 4), (cuuint64_t)N};
-        const cuuint64_t hstrides[1] = {(cuuint64_t)(K / 4)};
-        const cuuint32_t hbox[2] = {64, (cuuint32_t)BM};
-        cr = encode(&tmap_h, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)wp.p1, hdims, hstrides, hbox, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (top bits) failed (%d)", (int)cr);
-    }
 
     // y as a tensor [M rows][N floats], box = 32 floats x 16 rows (one epilogue warp's staging tile)
     CUtensorMap tmap_y = tmap;
@@ -453,7 +427,7 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
 
     GemmArgs args{};
     args.y_tma = y_tma ? 1 : 0;
-    args.w = wp;
+    args.w = w;
     args.grp_count = grp_count;
     args.grp_offset = grp_offset;
     args.y = y;
@@ -477,17 +451,16 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
             // and marks the tile and the others add after the mark (no zeroing of y), or y is zeroed and every
             // piece adds.
             if (y_tma && !args.ksplit && tiles <= OJAS_GEMM_FLAG_WORDS) {
-                if (++ctx->gemm_serial == 0) ctx->gemm_serial = 1;
                 args.flags = ctx->gemm_flags;
-                args.serial = ctx->gemm_serial;
+                args.serial_word = ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS;   // advanced by the preparation kernel of this call
             } else {
                 OJAS_CUDA(ctx, cudaMemsetAsync(y, 0, M * N * sizeof(float), ctx->stream));
             }
         }
         const dim3 grid_ts((unsigned)ctas);
-        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
-        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
-        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_h, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_y, args, grid_ts);
+        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_y, args, grid_ts);
     }
 }
 
@@ -497,15 +470,15 @@ int ojas_gemm_prep(ojas_b200_ctx *ctx, const float *x, void *xh, size_t rows, si
     const long long blocks = (n_sb + 7) / 8;
     if (blocks <= 0) return 0;
     if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
-    if (quant) gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb);
-    else gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb);
+    if (quant) gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
+    else gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
     return 0;
 }
 
-int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t x_rows, const WeightPlanes &wp, float *y, size_t K,
+int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t x_rows, const uint8_t *w, float *y, size_t K,
                       size_t N, size_t rows_bound, const int *grp_count, const int *grp_offset) {
-    return gemm_launch(ctx, type, (const __half *)xh, x_rows, wp, y, K, N, rows_bound, 0, grp_count, grp_offset);
+    return gemm_launch(ctx, type, (const __half *)xh, x_rows, w, y, K, N, rows_bound, 0, grp_count, grp_offset);
 }
 
 // ---------------------------------------------------------------- GEMM without a caller workspace

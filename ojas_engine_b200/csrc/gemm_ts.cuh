@@ -94,6 +94,12 @@ struct TsSched {
     }
 };
 
+// Plain (untiled) bulk copy global -> shared memory, completion counted on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 forms used only here
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 1, 0;\n\t"
@@ -143,33 +149,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&o)[16
                    "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
 }
 
-#ifdef TS_TRACE
-__device__ unsigned long long g_ts_span[148][32][2];
-__device__ __forceinline__ unsigned long long ts_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ unsigned int g_ts_prog[148][32];
-#define TS_PROG(val) do { if ((threadIdx.x & 31) == 0) g_ts_prog[blockIdx.x][threadIdx.x >> 5] = (unsigned)(val); } while (0)
-__device__ unsigned long long g_ts_trace[9][4096];
-#define TS_TR_DECL int tr_n = 0
-#define TS_TR(role, code, kb)                                                                                     \
-    do {                                                                                                          \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 4096)                                            \
-            g_ts_trace[role][tr_n++] = ((unsigned long long)clock64() << 16) | ((unsigned long long)(code) << 12) | ((kb) & 0xfff); \
-    } while (0)
-#else
-#define TS_TR_DECL
-#define TS_TR(role, code, kb)
-#define TS_PROG(val)
-#endif
-
 // ---------------------------------------------------------------- the kernel
 template <int BN, int TYPE>
 __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                                 const __grid_constant__ CUtensorMap tmap_w,
-                                                                 const __grid_constant__ CUtensorMap tmap_h,
                                                                  const __grid_constant__ CUtensorMap tmap_y, const GemmArgs a_in) {
     GemmArgs a = a_in;
     int x_row0 = 0;                                          // first activation row (grouped form: the group's offset)
     if (a_in.grp_count) {
+        grid_dependency_wait();                              // the counts come from a kernel before this one
         a.M = __ldg(a_in.grp_count);
         x_row0 = __ldg(a_in.grp_offset);
         a.y = a_in.y + (size_t)x_row0 * a_in.N;
@@ -192,6 +179,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile unsigned *b_seen = reinterpret_cast<volatile unsigned *>(tmem_slot + 2);   // [4], see the MMA threads
+    unsigned *epi_done = reinterpret_cast<unsigned *>(tmem_slot + 6);                   // epilogue warps that finished a storing piece
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = a.K >> 8;
@@ -213,12 +201,11 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         }
         *abort_flag = 0;
         for (int i = 0; i < 4; i++) b_seen[i] = 0u;
+        *epi_done = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TS_WARP_TMA_X && lane == 0) {              // the descriptors' first use would otherwise pay their fetch
         asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_x) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_w) : "memory");
-        if (TYPE == OJAS_B200_Q6_K) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_h) : "memory");
         if (a.y_tma) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_y) : "memory");
     }
     if (warp == TS_WARP_TMA_W) {
@@ -241,9 +228,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
 
     TsSched sched(a, BN);
     TsPiece pc;
-#ifdef TS_TRACE
-    if (lane == 0) g_ts_span[blockIdx.x][warp][0] = ts_gtime();
-#endif
 
     if (warp < TS_EPI_WARPS) {
         // ---------------- epilogue: warp e drains TMEM lanes 32 (e % 4) .. +31 (weight rows), column half e / 4
@@ -252,15 +236,17 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         constexpr int ECOLS = SPLIT ? BN / 2 : BN;
         const int col_begin = SPLIT ? chalf * ECOLS : 0, col_end = (SPLIT || chalf == 0) ? col_begin + ECOLS : 0;
         float *epi_tile = reinterpret_cast<float *>(smem_epi + warp * TS_EPI_TILE_BYTES);
-        TS_TR_DECL;
+        // The value that marks a tile as stored in this launch: a device word that the activation-preparation kernel
+        // in front of this one advances on every launch (so a replayed CUDA graph gets a fresh value each time).
+        unsigned serial = 0u;
+        if (a.flags) {
+            grid_dependency_wait();
+            serial = *reinterpret_cast<volatile const unsigned *>(a.serial_word);
+        }
         for (int it = 0; sched.next(pc); it++) {
             const int acc = it % NACC, use = it / NACC;
-            if (warp == 0) TS_TR(0, 1, it);
-            TS_PROG(it * 16 + 1);
             if (!mbar_wait_warp_long(&tmem_full[acc], (uint32_t)use & 1u, abort_flag, a.status, 0x400u)) break;
             tc_fence_after();
-            if (warp == 0) TS_TR(0, 2, it);
-            TS_PROG(it * 16 + 2);
             const int n = pc.n0 + quarter * 32 + lane;
             float *ycol = a.y + n;
             if (a.y_tma) {
@@ -274,7 +260,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 const bool add = (pc.partial && !storer) || a.accum;
                 if (marks && !storer) {
                     int ok = 1;
-                    if (lane == 0) ok = flag_wait(a.flags + pc.tile, a.serial, abort_flag, a.status) ? 1 : 0;
+                    if (lane == 0) ok = flag_wait(a.flags + pc.tile, serial, abort_flag, a.status) ? 1 : 0;
                     if (!__shfl_sync(0xffffffffu, ok, 0)) break;
                     asm volatile("fence.proxy.async;" ::: "memory");
                 }
@@ -306,11 +292,16 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     if (col_begin + col < col_end)
                         tmem_zero32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col_begin + col));
                 if (storer) {
-                    // all eight warps' stores have landed -> mark the tile (every epilogue warp takes part in every piece)
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                    __threadfence();
-                    asm volatile("bar.sync 1, %0;" ::"n"(TS_EPI_WARPS * 32) : "memory");
-                    if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + pc.tile), "r"(a.serial) : "memory");
+                    // all eight warps' stores have landed -> mark the tile.  Every epilogue warp takes part in every
+                    // piece; the warp that finishes last publishes the mark (a count, not a barrier: a warp that left
+                    // the loop after an abort cannot leave the others waiting).
+                    if (lane == 0) {
+                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                        __threadfence();
+                        const unsigned old = atomicAdd(epi_done, 1u);
+                        if (old % TS_EPI_WARPS == TS_EPI_WARPS - 1)
+                            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.flags + pc.tile), "r"(serial) : "memory");
+                    }
                 }
             } else {
 #pragma unroll 1
@@ -318,9 +309,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN + col);
                     if (pc.m0 + col < a.M) {
                         uint32_t v[32];
-                        if (warp == 0) TS_TR(0, 4, it);
                         tmem_ld32(taddr, v);
-                        if (warp == 0) TS_TR(0, 5, it);
                         if (n < a.N) {
                             const int rows = a.M - (pc.m0 + col) < 32 ? a.M - (pc.m0 + col) : 32;
                             float *yp = ycol + (size_t)(pc.m0 + col) * a.N;
@@ -339,7 +328,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                             }
                         }
                     }
-                    if (warp == 0) TS_TR(0, 6, it);
                     tmem_zero32(taddr);
                 }
             }
@@ -347,8 +335,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-            if (warp == 0) TS_TR(0, 3, it);
-            TS_PROG(it * 16 + 3);
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every store has landed before the CTA ends
     } else if (warp < TS_WARP_TMA_X) {
@@ -361,25 +347,27 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         const uint32_t tmem_row = tmem_base + ((uint32_t)(row & ~31) << 16) + (uint32_t)TS_A_COL0;
         uint32_t wc = 0;      // running super-block counter
         bool ok = true;
-        TS_TR_DECL;
-        const bool tr_on = (warp & 3) == 0 && (c & 1) == 0;
         while (ok && sched.next(pc)) {
             const int grow = pc.n0 + row;
             const bool live = grow < a.N;
-            const size_t lrow = (size_t)(live ? grow : 0);
-            const size_t rowblk = lrow * nsb;
+            const int lrow = live ? grow : 0;
+            constexpr int TB = tile_bytes((uint32_t)TYPE), QB = tile_quant_bytes((uint32_t)TYPE);
+            // this row's tile of super-block 0 in global memory, and its place in a staged raw tile
+            const uint8_t *grow_tiles = a.w + (size_t)(lrow >> 3) * nsb * TB + (lrow & 7) * 16;
+            const int soff = (row >> 3) * QB + (row & 7) * 16;
             const int n_sb = pc.sb1 - pc.sb0;
             // small per-row items come straight from global memory, one super-block ahead: the Q4_K header
             // (d, dmin, scales); the Q6_K chunk's four sub-scales and d; the Q8_0 chunk's two block scales
             uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
             auto small_items = [&](int sb) {
+                const uint8_t *t = grow_tiles + (size_t)sb * TB;
                 if (TYPE == OJAS_B200_Q4_K) {
-                    hdr_next = __ldg(reinterpret_cast<const uint4 *>(a.w.p1) + rowblk + sb);
+                    hdr_next = __ldg(reinterpret_cast<const uint4 *>(t + 8 * 128));
                 } else if (TYPE == OJAS_B200_Q6_K) {
-                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(a.w.p2) + (rowblk + sb) * 4 + c);
-                    hdr_next.y = __ldg(reinterpret_cast<const unsigned short *>(a.w.p3) + rowblk + sb);
+                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(t + 12 * 128) + c);
+                    hdr_next.y = __ldg(reinterpret_cast<const unsigned short *>(t - (lrow & 7) * 16 + 13 * 128) + (lrow & 7));
                 } else {                                  // the chunk's two f16 block scales
-                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(a.w.p1) + (rowblk + sb) * 4 + c);
+                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(t + 16 * 128) + c);
                 }
             };
             if (STAGED_W) small_items(pc.sb0);
@@ -389,33 +377,28 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 const int wb = wc % WQ_BUFS;
                 const int aslot = (int)(wc & 1u) * 4 + c;
                 const uint4 H = hdr_next;
-                if (tr_on) TS_TR(1 + (c >> 1), 1, wc * 4 + c);
-                TS_PROG(wc * 16 + 1);
                 if (STAGED_W) {
                     if (j + 1 < n_sb) small_items(pc.sb0 + j + 1);
                     if (!mbar_wait_warp(&wq_full[wb], (wc / WQ_BUFS) & 1u, abort_flag, a.status, 0x2000u)) { ok = false; break; }
-                    const unsigned char *wrow = smem_wq + wb * WQ_BYTES + row * 128;
+                    const unsigned char *wrow = smem_wq + wb * WQ_BYTES + soff;      // piece p of this row: wrow + 128 p
                     if (TYPE == OJAS_B200_Q8_0) {
-                        // chunk c = 64 int8: four 16-byte pieces of the 128-byte half (c >> 1) of the row
-                        const unsigned char *hrow = wrow + (c >> 1) * WQ_LO_BYTES;
-                        const int p0 = (c & 1) * 4, sw = row & 7;                                       // 128-byte swizzle
-                        cA = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 0) ^ sw) << 4));
-                        cB = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 1) ^ sw) << 4));
-                        cC = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 2) ^ sw) << 4));
-                        cD = *reinterpret_cast<const uint4 *>(hrow + (((p0 + 3) ^ sw) << 4));
+                        // chunk c = 64 int8: pieces 4c .. 4c + 3
+                        cA = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 0) * 128);
+                        cB = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 1) * 128);
+                        cC = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 2) * 128);
+                        cD = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 3) * 128);
                         ce0 = H.x;
+                    } else if (TYPE == OJAS_B200_Q4_K) {
+                        cA = *reinterpret_cast<const uint4 *>(wrow + (2 * c) * 128);          // qs[32c .. 32c + 15]
+                        cB = *reinterpret_cast<const uint4 *>(wrow + (2 * c + 1) * 128);      // qs[32c + 16 .. 32c + 31]
                     } else {
-                        cA = *reinterpret_cast<const uint4 *>(wrow + ((c ^ (row & 7)) << 4));         // 128-byte swizzle
-                        cB = *reinterpret_cast<const uint4 *>(wrow + (((4 + c) ^ (row & 7)) << 4));
-                    }
-                    if (TYPE == OJAS_B200_Q6_K) {                                                        // 64-byte swizzle
-                        cC = *reinterpret_cast<const uint4 *>(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
+                        cA = *reinterpret_cast<const uint4 *>(wrow + c * 128);                // low nibbles, h = 0
+                        cB = *reinterpret_cast<const uint4 *>(wrow + (4 + c) * 128);          // low nibbles, h = 1
+                        cC = *reinterpret_cast<const uint4 *>(wrow + (8 + c) * 128);          // top bits
                         ce0 = H.x;
                         ce1 = H.y;
                     }
                 }
-                if (tr_on) TS_TR(1 + (c >> 1), 2, wc * 4 + c);
-                TS_PROG(wc * 16 + 2);
                 uint32_t o[16], o1[16];
                 auto convert = [&](int half, uint32_t (&out)[16]) {
                     if (!live) {
@@ -436,23 +419,15 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&wq_empty[wb]);
                 }
-                if (tr_on) TS_TR(1 + (c >> 1), 3, wc * 4 + c);
-                TS_PROG(wc * 16 + 3);
                 if (!mbar_wait_warp(&a_empty[aslot], ((wc >> 1) & 1u) ^ 1u, abort_flag, a.status, 0x100u)) { ok = false; break; }
                 tc_fence_after();
-                if (tr_on) TS_TR(1 + (c >> 1), 4, wc * 4 + c);
-                TS_PROG(wc * 16 + 4);
                 tmem_st16(tmem_row + (uint32_t)(aslot * 32), o);      // (one 32-column store of both halves measured slower)
                 convert(1, o1);
                 tmem_st16(tmem_row + (uint32_t)(aslot * 32 + 16), o1);
-                if (tr_on) TS_TR(1 + (c >> 1), 6, wc * 4 + c);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                if (tr_on) TS_TR(1 + (c >> 1), 7, wc * 4 + c);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[aslot]);
-                if (tr_on) TS_TR(1 + (c >> 1), 5, wc * 4 + c);
-                TS_PROG(wc * 16 + 5);
             }
         }
     } else if (warp == TS_WARP_TMA_X) {
@@ -461,19 +436,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             int bslot = 0;
             uint32_t bphase = 0;
             bool ok = true;
-            TS_TR_DECL;
-            int tr_kb = 0;
             grid_dependency_wait();     // the prepared activations come from the kernel before this one
             while (ok && sched.next(pc)) {
                 for (int sb = pc.sb0; ok && sb < pc.sb1; sb++) {
 #pragma unroll 1
                     for (int c = 0; c < 4; c++) {
-                        TS_TR(3, 1, tr_kb);
-                        TS_PROG(tr_kb * 16 + 1);
                         if (!mbar_wait_spin(&b_empty[bslot], bphase ^ 1u, abort_flag, a.status, 0x200u)) { ok = false; break; }
-                        TS_TR(3, 2, tr_kb);
-                        TS_PROG(tr_kb * 16 + 2);
-                        tr_kb++;
                         mbar_arrive_expect_tx(&b_full[bslot], (uint32_t)B_STAGE_BYTES);
                         tma_load_2d(smem_b + bslot * B_STAGE_BYTES, &tmap_x, (sb * 4 + c) * BK, x_row0 + pc.m0, &b_full[bslot]);
                         if (++bslot == BS) { bslot = 0; bphase ^= 1u; }
@@ -490,20 +458,14 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             uint32_t wc = 0, bphase = 0;
             int bslot = c;
             bool ok = true;
-            TS_TR_DECL;
             for (int it = 0; ok && sched.next(pc); it++) {
                 const int acc = it % NACC, use = it / NACC;
-                TS_PROG(wc * 16 + 9 + 256 * 65536 * (it & 15));
                 if (!mbar_wait_spin(&tmem_empty[acc], ((uint32_t)use & 1u) ^ 1u, abort_flag, a.status, 0x8000u)) break;
                 tc_fence_after();
                 const uint32_t tmem_acc = tmem_base + (uint32_t)(acc * BN);
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
                     const int aslot = (int)(wc & 1u) * 4 + c;
-                    TS_TR(4 + c, 1, wc * 4 + c);
-                    TS_PROG(wc * 16 + 1 + 256 * 65536 * (it & 15));
                     if (!mbar_wait_spin(&a_full[aslot], (wc >> 1) & 1u, abort_flag, a.status, 0x800u)) { ok = false; break; }
-                    TS_TR(4 + c, 2, wc * 4 + c);
-                    TS_PROG(wc * 16 + 2 + 256 * 65536 * (it & 15));
                     // A parity wait tells "this use is filled" from "the use before is not filled yet" only for a
                     // waiter that saw the use before complete.  Use u - 1 of this activation slot (k-block kb - BS)
                     // belongs to another MMA thread unless BS is a multiple of four, so wait until that thread has
@@ -521,8 +483,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                     if (!mbar_wait_spin(&b_full[bslot], bphase, abort_flag, a.status, 0x1000u)) { ok = false; break; }
                     b_seen[c] = kb + 1u;
                     tc_fence_after();
-                    TS_TR(4 + c, 3, wc * 4 + c);
-                    TS_PROG(wc * 16 + 3 + 256 * 65536 * (it & 15));
                     const uint32_t tmem_a = tmem_base + (uint32_t)(TS_A_COL0 + aslot * 32);
                     const uint64_t bdesc = umma_desc(smem_u32(smem_b + bslot * B_STAGE_BYTES));
 #pragma unroll
@@ -530,8 +490,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         umma_f16_ts(tmem_acc, tmem_a + 8 * k, bdesc + 2 * k, idesc);
                     umma_commit(&a_empty[aslot]);
                     umma_commit(&b_empty[bslot]);
-                    TS_TR(4 + c, 4, wc * 4 + c);
-                    TS_PROG(wc * 16 + 4 + 256 * 65536 * (it & 15));
                     bslot += 4;
                     if (bslot >= BS) { bslot -= BS; bphase ^= 1u; }
                 }
@@ -539,36 +497,28 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             }
         }
     } else {
-        // ---------------- TMA: raw tile per super-block: Q4_K / Q6_K nibbles [128 rows x 128 bytes], Q6_K top bits
-        // [128 rows x 64 bytes], Q8_0 two halves of [128 rows x 128 bytes]
+        // ---------------- raw tile per super-block: the quant pieces of the sixteen 8-row tiles under this CTA's 128
+        // rows, one bulk copy each (tiles past the last row are not copied; their rows dequantize to zeros)
         if (STAGED_W && lane == 0) {
+            constexpr int TB = tile_bytes((uint32_t)TYPE), QB = tile_quant_bytes((uint32_t)TYPE);
+            const int units_total = (a.N + OJAS_TILE_ROWS - 1) / OJAS_TILE_ROWS;
             uint32_t wc = 0;
             bool ok = true;
-            TS_TR_DECL;
             while (ok && sched.next(pc)) {
+                const int u0 = pc.n0 / OJAS_TILE_ROWS;
+                const int cnt = units_total - u0 < BM / OJAS_TILE_ROWS ? units_total - u0 : BM / OJAS_TILE_ROWS;
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
                     const int wb = wc % WQ_BUFS;
-                    TS_TR(8, 1, wc * 4);
-                    TS_PROG(wc * 16 + 1);
                     if (!mbar_wait_spin(&wq_empty[wb], ((wc / WQ_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000u)) { ok = false; break; }
-                    TS_TR(8, 2, wc * 4);
-                    TS_PROG(wc * 16 + 2);
-                    mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
-                    if (TYPE == OJAS_B200_Q8_0) {
-                        tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 256, pc.n0, &wq_full[wb]);
-                        tma_load_2d(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES, &tmap_w, sb * 256 + 128, pc.n0, &wq_full[wb]);
-                    } else {
-                        tma_load_2d(smem_wq + wb * WQ_BYTES, &tmap_w, sb * 128, pc.n0, &wq_full[wb]);
-                    }
-                    if (TYPE == OJAS_B200_Q6_K) tma_load_2d(smem_wq + wb * WQ_BYTES + WQ_LO_BYTES, &tmap_h, sb * 64, pc.n0, &wq_full[wb]);
+                    mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)(cnt * QB));
+                    const uint8_t *src = a.w + ((size_t)u0 * nsb + sb) * TB;
+                    for (int t = 0; t < cnt; t++)
+                        bulk_load_1d(smem_wq + wb * WQ_BYTES + t * QB, src + (size_t)t * nsb * TB, (uint32_t)QB, &wq_full[wb]);
                 }
             }
         }
     }
 
-#ifdef TS_TRACE
-    if (lane == 0) g_ts_span[blockIdx.x][warp][1] = ts_gtime();
-#endif
     // ---------------- teardown (every role arrives here, also after an abort)
     if (*abort_flag && warp == TS_WARP_TMA_X && lane == 0) {
         // give copies that are still in flight a bounded time to land before the CTA releases shared memory

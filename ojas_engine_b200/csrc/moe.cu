@@ -231,10 +231,10 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         OJAS_CUDA(ctx, cudaMemsetAsync(w.g, 0, A * ffn * sizeof(float), ctx->stream));   // split tiles are added into zeros
         OJAS_CUDA(ctx, cudaMemsetAsync(w.u, 0, A * ffn * sizeof(float), ctx->stream));
         for (size_t e = 0; e < E; e++) {
-            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_planes_at(type_gu, wg, E * ffn, d, e * ffn), w.g, d, ffn, hint,
+            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_rows_at(type_gu, wg, d, e * ffn), w.g, d, ffn, hint,
                                    w.counts + e, w.offsets + e);
             if (rc) return rc;
-            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_planes_at(type_gu, wu, E * ffn, d, e * ffn), w.u, d, ffn, hint,
+            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_rows_at(type_gu, wu, d, e * ffn), w.u, d, ffn, hint,
                                    w.counts + e, w.offsets + e);
             if (rc) return rc;
         }
@@ -246,7 +246,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         if (rc) return rc;
         OJAS_CUDA(ctx, cudaMemsetAsync(w.yd, 0, A * d * sizeof(float), ctx->stream));
         for (size_t e = 0; e < E; e++) {
-            rc = ojas_gemm_grouped(ctx, type_d, ah, A, weight_planes_at(type_d, wd, E * d, ffn, e * d), w.yd, ffn, d, hint,
+            rc = ojas_gemm_grouped(ctx, type_d, ah, A, weight_rows_at(type_d, wd, ffn, e * d), w.yd, ffn, d, hint,
                                    w.counts + e, w.offsets + e);
             if (rc) return rc;
         }
@@ -261,10 +261,10 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
     OJAS_LAUNCH_CHECK(ctx, "moe_group");
     for (size_t e = 0; e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
-        rc = ojas_gemv_grouped(ctx, type_gu, weight_planes_at(type_gu, wg, E * ffn, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+        rc = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wg, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
                                w.counts + e, w.offsets + e, w.g, d, ffn);
         if (rc) return rc;
-        rc = ojas_gemv_grouped(ctx, type_gu, weight_planes_at(type_gu, wu, E * ffn, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+        rc = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wu, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
                                w.counts + e, w.offsets + e, w.u, d, ffn);
         if (rc) return rc;
     }
@@ -272,7 +272,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     moe_silu_quant_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(w.g, w.u, w.aq, w.as, w.ab, n_sb);
     OJAS_LAUNCH_CHECK(ctx, "moe_silu_quant");
     for (size_t e = 0; e < E; e++) {   // down of expert e over its (contiguous, sorted) rows
-        rc = ojas_gemv_grouped(ctx, type_d, weight_planes_at(type_d, wd, E * d, ffn, e * d), w.aq, w.as, w.ab, nullptr,
+        rc = ojas_gemv_grouped(ctx, type_d, weight_rows_at(type_d, wd, ffn, e * d), w.aq, w.as, w.ab, nullptr,
                                w.counts + e, w.offsets + e, w.yd, ffn, d);
         if (rc) return rc;
     }

@@ -1,37 +1,21 @@
-// Load-time re-layout of GGUF blocks into the aligned planes the kernels read (layouts are
-// described beside WeightPlanes).  Replaces the upload decisions of Repr / Lin::load_as
+// Load-time re-layout of GGUF blocks into the row-interleaved tiles the kernels read (the layout is
+// described in common.cuh).  Replaces the upload decisions of Repr / Lin::load_as
 // (crates/ojas-cuda/src/qwen35.rs:146-226); unlike relayout_q4k_q4l
 // (crates/ojas-formats/src/quant.rs:192-222) nothing is rounded: every GGUF bit survives.
-// The same per-block routine runs on the device (one thread per block) and on the host.
+// The same per-block routine runs on the device (one thread per 256 weights of one row) and on the host.
 #include "common.cuh"
 
-struct PlanePtrs { uint8_t *p0, *p1, *p2, *p3; };
+// Destination of 16-byte piece p of row r inside a tile.
+__host__ __device__ static inline uint8_t *tile_piece(uint8_t *tile, int p, int r) { return tile + (p * OJAS_TILE_ROWS + r) * 16; }
 
-// Q4_K block `blk` (row-major block index): GGUF 144 bytes -> 128 nibble bytes + 16 header bytes.
-__host__ __device__ static inline void repack_q4k_block(const uint8_t *raw, size_t blk, PlanePtrs o) {
-    const uint8_t *src = raw + blk * 144;
-    uint8_t *qs = o.p0 + blk * 128, *hdr = o.p1 + blk * 16;
-    for (int i = 0; i < 4; i++) hdr[i] = src[i];
-    const uint8_t *sc = src + 4;
-    for (int c = 0; c < 4; c++) {
-        unsigned v[4];   // s(2c), s(2c+1), m(2c), m(2c+1) by the GGUF rule (crates/ojas-formats/src/gguf.rs:1132-1140)
-        for (int h = 0; h < 2; h++) {
-            const int j = 2 * c + h;
-            if (j < 4) { v[h] = sc[j] & 63u; v[2 + h] = sc[j + 4] & 63u; }
-            else { v[h] = (sc[j + 4] & 0xFu) | ((unsigned)(sc[j - 4] >> 6) << 4); v[2 + h] = (unsigned)(sc[j + 4] >> 4) | ((unsigned)(sc[j] >> 6) << 4); }
-        }
-        const unsigned g = v[0] | (v[1] << 6) | (v[2] << 12) | (v[3] << 18);
-        hdr[4 + 3 * c] = (uint8_t)(g & 0xff);
-        hdr[5 + 3 * c] = (uint8_t)((g >> 8) & 0xff);
-        hdr[6 + 3 * c] = (uint8_t)((g >> 16) & 0xff);
-    }
-    for (int c = 0; c < 4; c++)
-        for (int h = 0; h < 2; h++)
-            for (int i = 0; i < 16; i++) qs[h * 64 + c * 16 + i] = src[16 + c * 32 + h * 16 + i];
+// Q4_K: the 128 nibble bytes keep their GGUF order (eight pieces), the 16-byte block header is piece 8.
+__host__ __device__ static inline void repack_q4k_block(const uint8_t *src, uint8_t *tile, int r) {
+    for (int p = 0; p < 8; p++)
+        for (int i = 0; i < 16; i++) tile_piece(tile, p, r)[i] = src[16 + p * 16 + i];
+    for (int i = 0; i < 16; i++) tile_piece(tile, 8, r)[i] = src[i];
 }
 
-// Q6_K block: GGUF 210 bytes (ql[128], qh[64], sc[16], d) -> lo[128], hi[64], sc[16], d[2].
-// Six-bit value of weight w (0..255), as the reference decodes it
+// Six-bit value of weight w (0..255) of a Q6_K block, as the reference decodes it
 // (crates/ojas-formats/src/gguf.rs:1086-1108): half = w/128, quarter = (w%128)/32, l = w%32.
 __host__ __device__ static inline unsigned q6k_value(const uint8_t *src, int w) {
     const int hh = w >> 7, quarter = (w >> 5) & 3, l = w & 31;
@@ -42,67 +26,60 @@ __host__ __device__ static inline unsigned q6k_value(const uint8_t *src, int w) 
     return lo4 | (hi2 << 4);
 }
 
-__host__ __device__ static inline void repack_q6k_block(const uint8_t *raw, size_t blk, PlanePtrs o) {
-    const uint8_t *src = raw + blk * 210;
-    uint8_t *lo = o.p0 + blk * 128, *hi = o.p1 + blk * 64, *sc = o.p2 + blk * 16, *d = o.p3 + blk * 2;
+// Q6_K: low nibbles regrouped per 64-weight chunk c (piece h*4 + c), top bits per chunk (piece 8 + c, field t =
+// sub-block 4c + t), the sixteen int8 scales (piece 12), then d.
+__host__ __device__ static inline void repack_q6k_block(const uint8_t *src, uint8_t *tile, int r) {
     for (int c = 0; c < 4; c++) {
         for (int h = 0; h < 2; h++)
             for (int i = 0; i < 16; i++) {
                 const unsigned a = q6k_value(src, 64 * c + 16 * h + i) & 0xFu;
                 const unsigned b = q6k_value(src, 64 * c + 32 + 16 * h + i) & 0xFu;
-                lo[h * 64 + c * 16 + i] = (uint8_t)(a | (b << 4));
+                tile_piece(tile, h * 4 + c, r)[i] = (uint8_t)(a | (b << 4));
             }
-        for (int k = 0; k < 4; k++)
-            for (int i = 0; i < 4; i++) {
-                unsigned v = 0;
-                for (int t = 0; t < 4; t++) v |= (q6k_value(src, 64 * c + 16 * t + 4 * k + i) >> 4) << (2 * t);
-                hi[c * 16 + k * 4 + i] = (uint8_t)v;
-            }
+        for (int b = 0; b < 16; b++) {
+            unsigned v = 0;
+            for (int t = 0; t < 4; t++) v |= (q6k_value(src, 64 * c + 16 * t + b) >> 4) << (2 * t);
+            tile_piece(tile, 8 + c, r)[b] = (uint8_t)v;
+        }
     }
-    for (int i = 0; i < 16; i++) sc[i] = src[192 + i];
-    d[0] = src[208];
-    d[1] = src[209];
+    for (int i = 0; i < 16; i++) tile_piece(tile, 12, r)[i] = src[192 + i];
+    tile[13 * 128 + 2 * r] = src[208];
+    tile[13 * 128 + 2 * r + 1] = src[209];
 }
 
-// Q8_0 block of 32 weights: GGUF 34 bytes (d, q[32]) -> q[32], d[2].
-__host__ __device__ static inline void repack_q80_block(const uint8_t *raw, size_t blk, PlanePtrs o) {
-    const uint8_t *src = raw + blk * 34;
-    uint8_t *q = o.p0 + blk * 32, *d = o.p1 + blk * 2;
-    d[0] = src[0];
-    d[1] = src[1];
-    for (int i = 0; i < 32; i++) q[i] = src[2 + i];
+// Q8_0: eight GGUF blocks (34 bytes each) = 256 weights: int8 values in natural order, then the eight scales.
+__host__ __device__ static inline void repack_q80_block(const uint8_t *src, uint8_t *tile, int r) {
+    for (int b = 0; b < 8; b++) {
+        const uint8_t *blk = src + b * 34;
+        for (int i = 0; i < 32; i++) tile_piece(tile, 2 * b + (i >> 4), r)[i & 15] = blk[2 + i];
+        tile_piece(tile, 16, r)[2 * b] = blk[0];
+        tile_piece(tile, 16, r)[2 * b + 1] = blk[1];
+    }
 }
 
-__global__ void repack_kernel(uint32_t type, const uint8_t *raw, size_t nblocks, PlanePtrs o) {
+__host__ __device__ static inline size_t raw_sb_bytes(uint32_t type) { return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q6_K ? 210 : 272; }
+
+// Block `blk` = (row n, super-block s) in row-major order of the GGUF tensor.
+__host__ __device__ static inline void repack_one(uint32_t type, const uint8_t *raw, size_t blk, size_t nsb, uint8_t *out) {
+    const size_t n = blk / nsb, s = blk - n * nsb;
+    const uint8_t *src = raw + blk * raw_sb_bytes(type);
+    uint8_t *tile = out + ((n / OJAS_TILE_ROWS) * nsb + s) * (size_t)tile_bytes(type);
+    const int r = (int)(n % OJAS_TILE_ROWS);
+    if (type == OJAS_B200_Q4_K) repack_q4k_block(src, tile, r);
+    else if (type == OJAS_B200_Q6_K) repack_q6k_block(src, tile, r);
+    else repack_q80_block(src, tile, r);
+}
+
+__global__ void repack_kernel(uint32_t type, const uint8_t *raw, size_t nblocks, size_t nsb, uint8_t *out) {
     const size_t blk = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (blk >= nblocks) return;
-    if (type == OJAS_B200_Q4_K) repack_q4k_block(raw, blk, o);
-    else if (type == OJAS_B200_Q6_K) repack_q6k_block(raw, blk, o);
-    else repack_q80_block(raw, blk, o);
+    if (blk < nblocks) repack_one(type, raw, blk, nsb, out);
 }
 
-static size_t block_count(uint32_t type, size_t N, size_t K) { return type == OJAS_B200_Q8_0 ? N * (K / 32) : N * (K / 256); }
-
-extern "C" size_t ojas_b200_raw_bytes(uint32_t type, size_t N, size_t K) {
-    switch (type) {
-    case OJAS_B200_Q4_K: return N * (K / 256) * 144;
-    case OJAS_B200_Q6_K: return N * (K / 256) * 210;
-    case OJAS_B200_Q8_0: return N * (K / 256) * 272;
-    default: return 0;
-    }
-}
+extern "C" size_t ojas_b200_raw_bytes(uint32_t type, size_t N, size_t K) { return type_supported(type) ? N * (K / 256) * raw_sb_bytes(type) : 0; }
 
 extern "C" size_t ojas_b200_repacked_bytes(uint32_t type, size_t N, size_t K) {
-    size_t off[5];
-    if (K % 256 != 0 || plane_offsets(type, N, K, off)) return 0;
-    return off[4];
-}
-
-static PlanePtrs plane_ptrs(uint32_t type, void *out, size_t N, size_t K) {
-    size_t off[5];
-    plane_offsets(type, N, K, off);
-    uint8_t *b = (uint8_t *)out;
-    return PlanePtrs{b + off[0], b + off[1], b + off[2], b + off[3]};
+    if (K % 256 != 0 || !type_supported(type)) return 0;
+    return repacked_size(type, N, K);
 }
 
 extern "C" int ojas_b200_repack(ojas_b200_ctx *ctx, uint32_t type, const void *raw_dev, size_t N, size_t K, void *out_dev) {
@@ -111,10 +88,13 @@ extern "C" int ojas_b200_repack(ojas_b200_ctx *ctx, uint32_t type, const void *r
     if (K == 0 || K % 256 != 0 || N == 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "repack: N=%zu K=%zu (K must be a positive multiple of 256)", N, K);
     if (!ojas_b200_repacked_bytes(type, N, K)) return ojas_fail(ctx, OJAS_B200_E_ARG, "repack: unsupported GGUF type %u", type);
     if (((uintptr_t)out_dev & 255) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "repack: output must be 256-byte aligned");
-    const size_t nb = block_count(type, N, K);
+    const size_t nb = N * (K / 256);
     const size_t grid = (nb + 127) / 128;
     if (grid > 0x7fffffffu) return ojas_fail(ctx, OJAS_B200_E_ARG, "repack: tensor too large for one launch");
-    repack_kernel<<<(unsigned)grid, 128, 0, ctx->stream>>>(type, (const uint8_t *)raw_dev, nb, plane_ptrs(type, out_dev, N, K));
+    if (N % OJAS_TILE_ROWS != 0)   // the rows that pad the last unit must read as zero blocks
+        OJAS_CUDA(ctx, cudaMemsetAsync((uint8_t *)out_dev + (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type), 0,
+                                       (K / 256) * (size_t)tile_bytes(type), ctx->stream));
+    repack_kernel<<<(unsigned)grid, 128, 0, ctx->stream>>>(type, (const uint8_t *)raw_dev, nb, K / 256, (uint8_t *)out_dev);
     OJAS_LAUNCH_CHECK(ctx, "repack");
     return 0;
 }
@@ -122,13 +102,7 @@ extern "C" int ojas_b200_repack(ojas_b200_ctx *ctx, uint32_t type, const void *r
 extern "C" int ojas_b200_repack_host(uint32_t type, const void *raw_host, size_t N, size_t K, void *out_host) {
     if (!raw_host || !out_host || K == 0 || K % 256 != 0 || !ojas_b200_repacked_bytes(type, N, K)) return OJAS_B200_E_ARG;
     memset(out_host, 0, ojas_b200_repacked_bytes(type, N, K));
-    const size_t nb = block_count(type, N, K);
-    PlanePtrs o = plane_ptrs(type, out_host, N, K);
-    const uint8_t *raw = (const uint8_t *)raw_host;
-    for (size_t b = 0; b < nb; b++) {
-        if (type == OJAS_B200_Q4_K) repack_q4k_block(raw, b, o);
-        else if (type == OJAS_B200_Q6_K) repack_q6k_block(raw, b, o);
-        else repack_q80_block(raw, b, o);
-    }
+    const size_t nb = N * (K / 256);
+    for (size_t b = 0; b < nb; b++) repack_one(type, (const uint8_t *)raw_host, b, K / 256, (uint8_t *)out_host);
     return 0;
 }
