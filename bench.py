@@ -242,9 +242,29 @@ def run_ours(args) -> None:
     xd = gpu.upload(x_host)
     yd = gpu.alloc(RING * N_ROWS)
 
+    # multi-GPU: each rank owns the row shard [rank*4096, (rank+1)*4096) of a [world*4096, 4096] projection per ring
+    # slot (column-parallel).  The step's 64 outputs of a rank are joined by ONE all-gather kernel of this library:
+    # it stores them into every rank's receive window (peer stores over NVLink), raises a flag, waits with a limit
+    # for the other ranks and copies out y_all [world][64][4096].  No other data-path exchange, no NCCL call inside
+    # the timed region; the whole step is one CUDA graph.
+    group = y_all = None
+    if dist is not None:
+        from ojas_engine_b200 import tp as obtp
+
+        def exchange(blob):
+            out = [None] * world
+            dist.all_gather_object(out, blob)
+            return out
+
+        group = obtp.TpGroup(gpu, world, rank, RING * N_ROWS, exchange)
+        y_all = gpu.alloc(world * RING * N_ROWS)
+
     def launch_pass():
         for i, w in enumerate(weights):
-            gpu.gemv(w, ob.Buf(xd.ptr + i * K_COLS * 4, K_COLS * 4), ob.Buf(yd.ptr + i * N_ROWS * 4, N_ROWS * 4), 1)
+            xi = ob.Buf(xd.ptr + i * K_COLS * 4, K_COLS * 4)
+            gpu.gemv(w, xi, ob.Buf(yd.ptr + i * N_ROWS * 4, N_ROWS * 4), 1)
+        if group is not None:
+            group.allgather(yd, RING * N_ROWS, y_all)
 
     launch_pass()  # outside capture: one-time function attribute set-up
     gpu.sync()
@@ -254,22 +274,8 @@ def run_ours(args) -> None:
     graph = gpu.graph_end()
     launches_per_step = gpu.launch_count - l0
 
-    # multi-GPU: each rank owns the row shard [rank*4096, (rank+1)*4096) of a [world*4096, 4096]
-    # projection per ring slot (column-parallel); the shards are joined by ONE all-gather of the
-    # step's outputs.  No other data-path collective.
-    gathered = y_view = ext_stream = None
-    if dist is not None:
-        import torch
-        y_view = _wrap_device_f32(yd.ptr, RING * N_ROWS, local)       # the library's output buffer, no copy
-        gathered = torch.empty(world * RING * N_ROWS, dtype=torch.float32, device=f"cuda:{local}")
-        ext_stream = torch.cuda.ExternalStream(gpu.stream, device=f"cuda:{local}")
-
     def step():
         gpu.graph_launch(graph)
-        if dist is not None:
-            import torch
-            with torch.cuda.stream(ext_stream):                        # ordered after the pass on the same stream
-                dist.all_gather_into_tensor(gathered, y_view)
 
     for _ in range(args.warmup):
         step()
@@ -305,8 +311,18 @@ def run_ours(args) -> None:
     parity = None
     if rank == 0:
         import oracle
-        got = gpu.read(yd, np.float32, N_ROWS)
         want = oracle.matvec_kq(raws[0], ob.Q4_K, N_ROWS, K_COLS, np.asarray(x_host[:K_COLS]))
+        if group is None:
+            got = gpu.read(yd, np.float32, N_ROWS)
+        else:
+            # the JOINED result: this rank's own shard, and the shard the last rank pushed into this rank's window
+            got = gpu.read(y_all, np.float32, N_ROWS, byte_offset=rank * RING * N_ROWS * 4)
+            peer = world - 1
+            praw = ring_weights(1, seed=peer * 1000)[0]
+            px = np.random.default_rng(1 + peer).standard_normal(RING * K_COLS, dtype=np.float32)[:K_COLS]
+            pwant = oracle.matvec_kq(praw, ob.Q4_K, N_ROWS, K_COLS, px)
+            pgot = gpu.read(y_all, np.float32, N_ROWS, byte_offset=peer * RING * N_ROWS * 4)
+            want, got = np.concatenate([want, pwant]), np.concatenate([got, pgot])
         parity = float(np.linalg.norm(got - want) / np.linalg.norm(want))
 
     # end to end through the C ABI with host buffers: H2D of the step's activations, the pass,
@@ -338,9 +354,17 @@ def run_ours(args) -> None:
                "ms_per_step": el / args.steps * 1e3}
         gpu.graph_destroy(g2)
 
+    tp_rows = None
+    if dist is not None and not args.no_extras:
+        try:
+            tp_rows = tp70b_rows(gpu, dist, rank, world, local, 5)
+        except Exception as exc:      # every rank runs the same sequence; a failure is reported, not fatal to the headline
+            tp_rows = [{"case": "tp70b", "error": str(exc)}]
     if rank == 0:
         cpu = None
         extras = []
+        if tp_rows is not None:
+            extras.append({"workload": f"llama70b_projections_sharded_x{world}", "rows": tp_rows})
         if world == 1:
             threads = os.cpu_count() or 1
             native = oracle_native_ok()
@@ -378,7 +402,7 @@ def run_ours(args) -> None:
             "dtype": "int8 x u4 block dots (exact int32), f32 combine", "data": "synthetic",
             "config": {"workload": WORKLOAD, "ring_bytes": RING * Q4K_BYTES, "l2": "inputs larger than L2 (ring of 64 weights, 604 MB)",
                        "launch": "CUDA graph of 64 kernel launches per step",
-                       "parallelism": "single GPU" if world == 1 else f"column-parallel row shards x{world}, one NCCL all-gather per step"},
+                       "parallelism": "single GPU" if world == 1 else f"column-parallel row shards x{world}; one all-gather kernel per step (peer stores over NVLink + bounded-wait join, no NCCL in the timed region)"},
             "pct_of_8TBps": value / world / 8000.0,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "gemv_kernel<Q4_K, 1 row, f32 activations>",
@@ -528,87 +552,121 @@ def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, 
             "frac_of_tensor_peak": round(flops / us / 1e6 / tc_peak, 5), "expert_bytes": gguf}
 
 
-def run_tp70b(args) -> None:
-    """`--case tp70b` under torchrun (or alone for 1 GPU): the Llama-70B-shaped projections row-sharded over
-    the ranks.  QKV 10240x8192, gate/up 28672x8192 (Q4_K) are column-parallel (all-gather of the output
-    shards); O 8192x8192 (Q4_K) and down 8192x28672 (Q6_K) are row-parallel (K split on super-block
-    boundaries, all-reduce of the partial outputs).  M = 1 (GEMV) and M = 512 (tensor-core GEMM).  Each call =
-    local matmul + its NCCL collective on the same stream; time = CUDA events, max over ranks."""
+def tp70b_rows(gpu, dist, rank: int, world: int, local: int, steps: int) -> list[dict]:
+    """The Llama-70B-shaped projections row-sharded over the ranks.  QKV 10240x8192, gate/up 28672x8192 (Q4_K) are
+    column-parallel; O 8192x8192 (Q4_K) and down 8192x28672 (Q6_K) are row-parallel (K split on super-block
+    boundaries).  M = 1: the GEMV stores its shard / partial vector into every rank's window and a bounded-wait join
+    kernel forms the result (no library collective).  M = 512: tensor-core GEMM + NCCL all-gather / all-reduce on the
+    same stream.  Time = CUDA events, max over ranks; every row carries the rel-L2 of the JOINED result against the
+    CPU oracle (rank 0; M = 512: three sampled tokens)."""
     import torch
-    import torch.distributed as dist
     import oracle
     import ojas_engine_b200 as ob
     from ojas_engine_b200 import tp
-    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    gpu = ob.B200Gpu(local)
-    stream = torch.cuda.ExternalStream(gpu.stream, device=f"cuda:{local}")
     dev = f"cuda:{local}"
+    stream = torch.cuda.ExternalStream(gpu.stream, device=dev)
     projections = [("qkv", ob.Q4_K, 10240, 8192, "col"), ("o", ob.Q4_K, 8192, 8192, "row"),
                    ("gate_up", ob.Q4_K, 28672, 8192, "col"), ("down", ob.Q6_K, 8192, 28672, "row")]
+
+    def exchange(blob):
+        out = [None] * world
+        dist.all_gather_object(out, blob)
+        return out
+
+    group = tp.TpGroup(gpu, world, rank, 28672, exchange if world > 1 else (lambda blob: [blob]))
+    rng = np.random.default_rng(321)
     rows_out = []
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        gpu.sync(); torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = gpu.event(), gpu.event()
+        gpu.record(e0)
+        for _ in range(n):
+            fn()
+        gpu.record(e1)
+        gpu.sync(); torch.cuda.synchronize()
+        tt = torch.tensor([gpu.elapsed_ms(e0, e1) * 1e3 / n], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
     for name, t, n, k, mode in projections:
-        if mode == "col":
-            _, n_loc = tp.shard_rows(n, world, rank)
-            k_loc = k
-        else:
-            n_loc = n
-            _, k_loc = tp.shard_k(k, world, rank)
-        raw = oracle.synth_blocks(t, n_loc * k_loc // 256)
-        w = gpu.load_weight(raw, t, n_loc, k_loc)
-        for m in (1, 512):
-            x = (torch.randn(m, k_loc, device=dev, dtype=torch.float32) * 1e-2).contiguous()
-            y = torch.empty(m, n_loc, device=dev, dtype=torch.float32)
-            full = torch.empty(world * m, n_loc, device=dev, dtype=torch.float32) if (mode == "col" and world > 1) else None
-            xb, yb = ob.Buf(x.data_ptr(), x.numel() * 4), ob.Buf(y.data_ptr(), y.numel() * 4)
-            work = gpu.alloc_bytes(gpu.gemm_workspace_bytes(m, k_loc)) if m > ob.GEMV_MAX_M else None
-            torch.cuda.synchronize()
+        raw = oracle.synth_blocks(t, n * k // 256)
+        sh = tp.ShardedLinear(raw, t, n, k, mode, rank, world)
+        n_loc, k_loc = sh.local_shape
+        w = gpu.load_weight(sh.raw, t, n_loc, k_loc)
+        tag = {ob.Q4_K: "q4k", ob.Q6_K: "q6k"}[t]
+        # ---- M = 1
+        x1 = (rng.standard_normal((1, k)) * 0.1).astype(np.float32)
+        xb, y = gpu.upload(sh.local_x(x1)), gpu.alloc(n)
+        jm = group.COL if mode == "col" else group.ROW
+        reps = 16
+        gpu.graph_begin()
+        for _ in range(reps):
+            group.gemv(w, xb)
+            group.join(jm, y, n)
+        g = gpu.graph_end()
+        us = timed(lambda: gpu.graph_launch(g), max(steps, 3)) / reps
+        gpu.graph_destroy(g)
+        err = None
+        if rank == 0:
+            want = oracle.matvec_kq(raw, t, n, k, x1[0], os.cpu_count() or 1, oracle_native_ok())
+            got = gpu.read(y, np.float32, n)
+            err = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+        rows_out.append({"proj": name, "type": tag, "N": n, "K": k, "mode": mode, "M": 1, "us_per_call": round(us, 2),
+                         "aggregate_GB/s": round(ob.raw_bytes(t, n, k) / us / 1e3, 1), "join": "peer stores + bounded-wait join kernel",
+                         "rel_l2_joined_vs_oracle": err})
+        # ---- M = 512
+        m = 512
+        xm = (rng.standard_normal((m, k)) * 0.1).astype(np.float32)
+        xmb = gpu.upload(sh.local_x(xm))
+        yl = torch.empty(m, n_loc, device=dev, dtype=torch.float32)
+        ylb = ob.Buf(yl.data_ptr(), yl.numel() * 4)
+        work = gpu.alloc_bytes(gpu.gemm_workspace_bytes(m, k_loc))
+        out = {}
 
-            def call():
-                if m <= ob.GEMV_MAX_M:
-                    gpu.gemv(w, xb, yb, m)
-                else:
-                    gpu.gemm(w, xb, yb, m, workspace=work)
-                if world > 1:
-                    with torch.cuda.stream(stream):
-                        if mode == "col":
-                            dist.all_gather_into_tensor(full, y)
-                        else:
-                            dist.all_reduce(y, op=dist.ReduceOp.SUM)
-
-            def timed(fn, steps):
-                for _ in range(3):
-                    fn()
-                gpu.sync(); torch.cuda.synchronize()
-                if world > 1:
-                    dist.barrier()
-                e0, e1 = gpu.event(), gpu.event()
-                gpu.record(e0)
-                for _ in range(steps):
-                    fn()
-                gpu.record(e1)
-                gpu.sync(); torch.cuda.synchronize()
-                tt = torch.tensor([gpu.elapsed_ms(e0, e1) * 1e3 / steps], dtype=torch.float64, device=dev)
-                if world > 1:
-                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-                return float(tt.item())
-
-            us = timed(call, args.steps)
-            gguf_total = ob.raw_bytes(t, n, k)
-            row = {"proj": name, "type": {ob.Q4_K: "q4k", ob.Q6_K: "q6k"}[t], "N": n, "K": k, "mode": mode, "M": m,
-                   "us_per_call": round(us, 2)}
-            if m == 1:
-                row["aggregate_GB/s"] = round(gguf_total / us / 1e3, 1)
+        def call():
+            gpu.gemm(w, xmb, ylb, m, workspace=work)
+            if world > 1:
+                with torch.cuda.stream(stream):
+                    out["full"] = sh.join(yl, dist)
             else:
-                row["aggregate_TFLOP/s"] = round(2.0 * m * n * k / us / 1e6, 1)
-            rows_out.append(row)
-            if work is not None:
-                gpu.free(work)
-        gpu.free(w.buf)
+                out["full"] = yl
+
+        us = timed(call, max(steps, 3))
+        err = None
+        if rank == 0:
+            sample = [0, m // 3, m - 1]
+            want = oracle.matmul_kq(raw, t, n, k, xm[sample], os.cpu_count() or 1)
+            got = out["full"][sample].cpu().numpy()
+            err = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+        rows_out.append({"proj": name, "type": tag, "N": n, "K": k, "mode": mode, "M": m, "us_per_call": round(us, 2),
+                         "aggregate_TFLOP/s": round(2.0 * m * n * k / us / 1e6, 1), "join": "NCCL " + ("all-gather" if mode == "col" else "all-reduce"),
+                         "rel_l2_joined_vs_oracle": err})
+        for b in (w.buf, xb, y, xmb, work):
+            gpu.free(b)
+    group.close()
+    return rows_out
+
+
+def run_tp70b(args) -> None:
+    """`--case tp70b` under torchrun (or alone for 1 GPU): prints the rows of tp70b_rows as one JSON line."""
+    import torch
+    import ojas_engine_b200 as ob
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    gpu = ob.B200Gpu(local)
+    rows = tp70b_rows(gpu, dist, rank, world, local, args.steps)
     if rank == 0:
-        print(json.dumps({"case": "tp70b", "n_gpus": world, "steps": args.steps, "rows": rows_out}))
+        print(json.dumps({"case": "tp70b", "n_gpus": world, "steps": args.steps, "rows": rows}))
     if world > 1:
         dist.destroy_process_group()
     gpu.close()

@@ -121,6 +121,19 @@ OJAS_B200_API int ojas_b200_repack_host(uint32_t ggml_type, const void *raw_host
 OJAS_B200_API int ojas_b200_quant_q8k(ojas_b200_ctx *ctx, const float *x, size_t M, size_t K, int8_t *q, float *scales,
                         int32_t *bsums);
 
+/* ---- activation producers that end in Q8_K: counterparts of rmsnorm_q8 and silu_mul_q8
+ * (crates/ojas-cuda/src/kernels/ops.rs:27, 352), ending in the Q8_K form the K-quant GEMVs read (ojas_b200_gemv_q8k)
+ * instead of the reference's q8_1 blocks, so one quantization feeds every projection of the row (Q, K, V; gate, up)
+ * and the f32 row is never re-read.  rmsnorm (crates/ojas-cpu/src/cpu_math.rs:456-460): out = (x / sqrt(mean(x^2) +
+ * eps)) * w per row of x [M,K]; the mean is a tree sum (agrees with the CPU's in-order sum to fp32 rounding), the
+ * quantization of the normalized row is bit-identical to quant_q8k.  xn (may be null) receives the normalized f32 row.
+ * silu_mul: act = silu(g) * u (crates/ojas-cpu/src/cpu_math.rs:486), then quant_q8k(act), bit-identical to the CPU
+ * composition. */
+OJAS_B200_API int ojas_b200_rmsnorm_q8k(ojas_b200_ctx *ctx, const float *x, const float *w, float eps, size_t M, size_t K, float *xn,
+                                        int8_t *q, float *scales, int32_t *bsums);
+OJAS_B200_API int ojas_b200_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, const float *u, size_t M, size_t K, int8_t *q,
+                                         float *scales, int32_t *bsums);
+
 /* ---- decode GEMV: replaces gemv_nat_{q4k,q6k,q80}{,_accum,_bias,_m}
  * (crates/ojas-cuda/src/kernels/nat.rs:69-91; bodies crates/ojas-core/src/quant_src.rs:779-867,
  * 1028-1057, 1154-1180) with the arithmetic of matvec_kq (crates/ojas-cpu/src/cpu_math.rs:
@@ -194,6 +207,37 @@ OJAS_B200_API int ojas_b200_tp_shard_rows(size_t N, int world, int rank, size_t 
 OJAS_B200_API int ojas_b200_tp_shard_k(size_t K, int world, int rank, size_t *k0, size_t *klen);
 OJAS_B200_API int ojas_b200_tp_slice_k_host(uint32_t ggml_type, const void *raw, size_t N, size_t K, size_t k0, size_t klen,
                                             void *out);
+
+/* ---- decode join through peer memory.  No counterpart in the reference (single-GPU).  For one activation row a
+ * sharded projection is a few microseconds of GEMV and a library collective behind it costs several times that, so
+ * the GEMV's epilogue stores its results straight into every rank's receive window (device memory the other ranks
+ * map through CUDA IPC; plain peer stores, no tensor map covers peer memory).  Values travel stamped (8-byte pairs:
+ * the float's bits and the step's number, one store), so there is no flag and no fence: a join costs one NVLink
+ * crossing.  Each rank's join kernel polls the pairs it needs WITH A LIMIT (default about 2 s; on expiry the affected
+ * outputs are left alone, the step still closes, and ojas_b200_sync returns OJAS_B200_E_DEVICE) and forms the result
+ * from its own window.
+ * One process per GPU.  Set-up: every rank calls tp_create (allocates its window: 2 * world * slot_floats pairs),
+ * tp_export, hands the handle (ojas_b200_tp_handle_bytes() bytes) to the other ranks by any host channel, and
+ * tp_import for each peer.  A step: one or more tp_gemv, then tp_join; or local GEMVs, then tp_allgather.  Every rank
+ * must run the same sequence of steps.  All launches are capture-safe (the step counter lives in device memory).
+ * join modes: 1 column-parallel, y[n_total] = the ranks' shards in rank order (plan of ojas_b200_tp_shard_rows);
+ * 2 row-parallel, y[n_total] = sum of the ranks' partial vectors in rank order (the same order on every rank: all
+ * ranks end with identical bits). */
+typedef struct ojas_b200_tp ojas_b200_tp;
+OJAS_B200_API int ojas_b200_tp_create(ojas_b200_ctx *ctx, int world, int rank, size_t slot_floats, ojas_b200_tp **out);
+OJAS_B200_API void ojas_b200_tp_destroy(ojas_b200_tp *tp);
+OJAS_B200_API size_t ojas_b200_tp_handle_bytes(void);
+OJAS_B200_API int ojas_b200_tp_export(ojas_b200_tp *tp, void *handle_out);
+OJAS_B200_API int ojas_b200_tp_import(ojas_b200_tp *tp, int peer, const void *handle);
+OJAS_B200_API int ojas_b200_tp_set_wait_us(ojas_b200_tp *tp, unsigned micros);
+/* x [K] f32 through this rank's repacked shard w [N, K]; the N results go to float `offset` of this rank's slot in
+ * every rank's window. */
+OJAS_B200_API int ojas_b200_tp_gemv(ojas_b200_tp *tp, uint32_t ggml_type, const float *x, const void *w, size_t K, size_t N,
+                                    size_t offset);
+OJAS_B200_API int ojas_b200_tp_join(ojas_b200_tp *tp, int mode, float *y, size_t n_total);
+/* A whole step's exchange in one kernel: all-gather of `floats` values per rank (src -> every window, bounded wait,
+ * copy-out): y_all [world][floats]. */
+OJAS_B200_API int ojas_b200_tp_allgather(ojas_b200_tp *tp, const float *src, size_t floats, float *y_all);
 
 /* ---- name-based dispatch: the C form of KernelRuntime::dispatch / has_kernel
  * (crates/ojas-core/src/kernel.rs:68-83; argument marshalling crates/ojas-cuda/src/device.rs:

@@ -95,6 +95,20 @@ static inline const uint8_t *weight_rows_at(uint32_t type, const void *w, size_t
     return (const uint8_t *)w + (row0 / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type);
 }
 
+// ---------------------------------------------------------------------------- tensor-parallel epilogue
+// What a kernel needs to hand its results to the other ranks of a tensor-parallel group (tp.cu).  A receive window
+// holds STAMPED values: each float travels as an 8-byte pair (its bits, the number of the step it belongs to),
+// written with one 8-byte store, so a reader that sees the stamp of the step in flight has the value too: no flag,
+// no fence, no grid-wide rendezvous, one NVLink crossing.  step == null everywhere outside a group.
+constexpr int OJAS_TP_MAX_RANKS = 8;
+struct TpPush {
+    uint2 *dst[OJAS_TP_MAX_RANKS];         // this rank's place in every rank's window (the local one included), half 0
+    const unsigned *step;                  // local word: the number of the step in flight (the stamp); its low bit
+                                           // picks the half of the windows the step uses
+    size_t half_pairs;                     // distance of half 1 from half 0 in a window, in pairs
+    int n;                                 // destinations
+};
+
 int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w, const int8_t *q, const float *scales,
                       const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
                       size_t K, size_t N);

@@ -316,7 +316,7 @@ size_t gemm_ts_smem_bytes(int bn, int type) {
 }
 
 template <int BN, int TYPE>
-int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
     auto kernel = gemm_ts_kernel<BN, TYPE>;
     const size_t smem = gemm_ts_smem_bytes(BN, TYPE);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -333,19 +333,19 @@ int launch_gemm_ts_bn(ojas_b200_ctx *ctx, const CUtensorMap &tmap, const CUtenso
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_y, args);
+    e = cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_w, tmap_y, args);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemm_ts: %s", cudaGetErrorString(e));
     OJAS_LAUNCH_CHECK(ctx, "gemm_ts");
     return 0;
 }
 
 template <int TYPE>
-int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
+int launch_gemm_ts_type(ojas_b200_ctx *ctx, int bn, const CUtensorMap &tmap, const CUtensorMap &tmap_w, const CUtensorMap &tmap_y, const GemmArgs &args, dim3 grid) {
     switch (bn) {
-    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_y, args, grid);
-    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_y, args, grid);
-    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_y, args, grid);
-    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_y, args, grid);
+    case 32: return launch_gemm_ts_bn<32, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    case 64: return launch_gemm_ts_bn<64, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    case 128: return launch_gemm_ts_bn<128, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
+    default: return launch_gemm_ts_bn<256, TYPE>(ctx, tmap, tmap_w, tmap_y, args, grid);
     }
 }
 
@@ -413,6 +413,20 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
+    // the weight's quant pieces as a 4-D byte tensor: 128 bytes (one piece of the 8 rows of a tile) x pieces x
+    // super-blocks x 8-row units; box = every quant piece of one super-block of sixteen units = 128 rows
+    CUtensorMap tmap_w = tmap;
+    {
+        const size_t tb = (size_t)tile_bytes(type), pieces = (size_t)tile_quant_bytes(type) / 128;
+        const cuuint64_t wdims[4] = {128, (cuuint64_t)pieces, (cuuint64_t)(K / 256), (cuuint64_t)tile_units(N)};
+        const cuuint64_t wstrides[3] = {128, (cuuint64_t)tb, (cuuint64_t)((K / 256) * tb)};
+        const cuuint32_t wbox[4] = {128, (cuuint32_t)pieces, 1, (cuuint32_t)(BM / OJAS_TILE_ROWS)};
+        const cuuint32_t westr[4] = {1, 1, 1, 1};
+        cr = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)w, wdims, wstrides, wbox, westr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled (weights) failed (%d)", (int)cr);
+    }
+
     // y as a tensor [M rows][N floats], box = 32 floats x 16 rows (one epilogue warp's staging tile)
     CUtensorMap tmap_y = tmap;
     const bool y_tma = !grouped && (N % 4 == 0) && (((uintptr_t)y & 15) == 0);
@@ -458,9 +472,9 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
             }
         }
         const dim3 grid_ts((unsigned)ctas);
-        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_y, args, grid_ts);
-        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_y, args, grid_ts);
-        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
     }
 }
 

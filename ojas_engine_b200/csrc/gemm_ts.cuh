@@ -94,10 +94,9 @@ struct TsSched {
     }
 };
 
-// Plain (untiled) bulk copy global -> shared memory, completion counted on an mbarrier.
-__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gmem_src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *tmap, int c0, int c1, int c2, int c3, uint64_t *bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05 forms used only here
@@ -152,6 +151,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&o)[16
 // ---------------------------------------------------------------- the kernel
 template <int BN, int TYPE>
 __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                 const __grid_constant__ CUtensorMap tmap_w,
                                                                  const __grid_constant__ CUtensorMap tmap_y, const GemmArgs a_in) {
     GemmArgs a = a_in;
     int x_row0 = 0;                                          // first activation row (grouped form: the group's offset)
@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
     }
     if (warp == TS_WARP_TMA_X && lane == 0) {              // the descriptors' first use would otherwise pay their fetch
         asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_x) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_w) : "memory");
         if (a.y_tma) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_y) : "memory");
     }
     if (warp == TS_WARP_TMA_W) {
@@ -498,22 +499,17 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
         }
     } else {
         // ---------------- raw tile per super-block: the quant pieces of the sixteen 8-row tiles under this CTA's 128
-        // rows, one bulk copy each (tiles past the last row are not copied; their rows dequantize to zeros)
+        // rows in one tiled copy (the weight as a 4-D tensor: 128 bytes x pieces x super-blocks x 8-row units; units
+        // past the last row read as zeros)
         if (STAGED_W && lane == 0) {
-            constexpr int TB = tile_bytes((uint32_t)TYPE), QB = tile_quant_bytes((uint32_t)TYPE);
-            const int units_total = (a.N + OJAS_TILE_ROWS - 1) / OJAS_TILE_ROWS;
             uint32_t wc = 0;
             bool ok = true;
             while (ok && sched.next(pc)) {
-                const int u0 = pc.n0 / OJAS_TILE_ROWS;
-                const int cnt = units_total - u0 < BM / OJAS_TILE_ROWS ? units_total - u0 : BM / OJAS_TILE_ROWS;
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, wc++) {
                     const int wb = wc % WQ_BUFS;
                     if (!mbar_wait_spin(&wq_empty[wb], ((wc / WQ_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000u)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)(cnt * QB));
-                    const uint8_t *src = a.w + ((size_t)u0 * nsb + sb) * TB;
-                    for (int t = 0; t < cnt; t++)
-                        bulk_load_1d(smem_wq + wb * WQ_BYTES + t * QB, src + (size_t)t * nsb * TB, (uint32_t)QB, &wq_full[wb]);
+                    mbar_arrive_expect_tx(&wq_full[wb], (uint32_t)WQ_BYTES);
+                    tma_load_4d(smem_wq + wb * WQ_BYTES, &tmap_w, 0, 0, sb, pc.n0 / OJAS_TILE_ROWS, &wq_full[wb]);
                 }
             }
         }

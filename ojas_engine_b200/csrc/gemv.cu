@@ -42,10 +42,14 @@ struct GemvArgs {
     int K, N, M, form;
     int nsb;                 // super-blocks per row
     int units_base, units_rem;   // CTA b owns units_base (+1 if b < units_rem) 8-row units
-    int nst;                 // ring stages per warp
-    int S;                   // warps per team (a power of two that divides the warps of the CTA)
-    int P;                   // partial sums per row and group = min(S, nsb)
+    int nst_log;             // ring stages per warp = 1 << nst_log
+    int S_log;               // warps per team = 1 << S_log
+    int T_log;               // teams per CTA = 1 << T_log (warps per CTA = teams * warps per team)
+    int P;                   // partial sums per row and group = min(warps per team, nsb)
     int own_x;               // 1: warp w consumes exactly super-block w, so it quantizes that one for itself
+    // tensor-parallel epilogue (tp.cu): instead of y, every result goes, stamped with the step's number, to this
+    // rank's place in the receive window of every rank (plain 8-byte stores through peer-mapped pointers).
+    TpPush tp;
 };
 
 __device__ __forceinline__ void store_form(float *yp, float v, int form, const float *bias, int n) {
@@ -146,42 +150,38 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
             __syncwarp();
             return;
         }
-        for (int t = warp; t < a.M * nsb; t += warps) {
-            const int m = t / nsb, sb = t - m * nsb;
+        for (int m = 0; m < a.M; m++) {
             uint8_t *xq = act + m * rb, *bs = xq + nsb * 256;
             float *sx = reinterpret_cast<float *>(bs + nsb * L::BS_BYTES);
-            stage_quant_sb<TYPE>(a.x + (size_t)m * a.K, sb, lane, xq, bs, sx);
+            for (int sb = warp; sb < nsb; sb += warps) stage_quant_sb<TYPE>(a.x + (size_t)m * a.K, sb, lane, xq, bs, sx);
         }
     } else {
         const int units = nsb * 16;                               // 16-byte units per row
-        for (int idx = threadIdx.x; idx < a.M * units; idx += blockDim.x) {
-            const int m = idx / units, un = idx - m * units;
+        for (int m = 0; m < a.M; m++) {
             uint8_t *xq = act + m * rb, *bs = xq + nsb * 256;
-            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(a.q + (size_t)src_row(a, m) * a.K) + un);
-            reinterpret_cast<uint4 *>(xq)[un] = v;
-            if (TYPE == OJAS_B200_Q6_K) {                         // the sum of this unit's sixteen values
-                int s = __dp4a((int)v.x, 0x01010101, 0);
-                s = __dp4a((int)v.y, 0x01010101, s);
-                s = __dp4a((int)v.z, 0x01010101, s);
-                s = __dp4a((int)v.w, 0x01010101, s);
-                const int sb = un >> 4, j = un & 15;
-                bs[sb * 32 + j] = (uint8_t)(s & 63);
-                bs[sb * 32 + 16 + j] = (uint8_t)((s >> 6) & 0xff);
-            }
-        }
-        for (int idx = threadIdx.x; idx < a.M * nsb; idx += blockDim.x) {
-            const int m = idx / nsb, sb = idx - m * nsb;
-            uint8_t *bs = act + m * rb + nsb * 256;
             float *sx = reinterpret_cast<float *>(bs + nsb * L::BS_BYTES);
-            sx[sb] = __ldg(a.scales + (size_t)src_row(a, m) * nsb + sb);
-        }
-        if (TYPE == OJAS_B200_Q4_K) {
-            for (int idx = threadIdx.x; idx < a.M * nsb * 8; idx += blockDim.x) {
-                const int m = idx / (nsb * 8), rem = idx - m * (nsb * 8);
-                const int s = __ldg(a.bsums + (size_t)src_row(a, m) * nsb * 8 + rem);
-                uint8_t *bs = act + m * rb + nsb * 256;
-                bs[(rem >> 3) * 16 + (rem & 7)] = (uint8_t)(s & 63);
-                bs[(rem >> 3) * 16 + 8 + (rem & 7)] = (uint8_t)((s >> 6) & 0xff);
+            const int srow = src_row(a, m);
+            const uint4 *qsrc = reinterpret_cast<const uint4 *>(a.q + (size_t)srow * a.K);
+            for (int un = threadIdx.x; un < units; un += blockDim.x) {
+                const uint4 v = __ldg(qsrc + un);
+                reinterpret_cast<uint4 *>(xq)[un] = v;
+                if (TYPE == OJAS_B200_Q6_K) {                     // the sum of this unit's sixteen values
+                    int t = __dp4a((int)v.x, 0x01010101, 0);
+                    t = __dp4a((int)v.y, 0x01010101, t);
+                    t = __dp4a((int)v.z, 0x01010101, t);
+                    t = __dp4a((int)v.w, 0x01010101, t);
+                    const int sb = un >> 4, j = un & 15;
+                    bs[sb * 32 + j] = (uint8_t)(t & 63);
+                    bs[sb * 32 + 16 + j] = (uint8_t)((t >> 6) & 0xff);
+                }
+            }
+            for (int sb = threadIdx.x; sb < nsb; sb += blockDim.x) sx[sb] = __ldg(a.scales + (size_t)srow * nsb + sb);
+            if (TYPE == OJAS_B200_Q4_K) {
+                for (int i = threadIdx.x; i < nsb * 8; i += blockDim.x) {
+                    const int t = __ldg(a.bsums + (size_t)srow * nsb * 8 + i);
+                    bs[(i >> 3) * 16 + (i & 7)] = (uint8_t)(t & 63);
+                    bs[(i >> 3) * 16 + 8 + (i & 7)] = (uint8_t)((t >> 6) & 0xff);
+                }
             }
         }
     }
@@ -373,7 +373,8 @@ template <int TYPE, int MT, bool PREQ, bool DUMP>
 __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem, unsigned &ring_uses, bool first_pass) {
     constexpr int TB = tile_bytes(TYPE), STEP = 4 * TB;
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nsb = a.nsb, nst = a.nst, S = a.S, P = a.P, T = warps / S;
+    const int nsb = a.nsb, P = a.P;
+    const int nst = 1 << a.nst_log, S = 1 << a.S_log, T = 1 << a.T_log;   // powers of two: no divisions below
     uint8_t *ring = smem + (size_t)warp * nst * STEP;
     uint8_t *act = smem + (size_t)warps * nst * STEP;
     const size_t act_bytes = TYPE == OJAS_B200_Q8_0 ? (size_t)MT * a.K * 4 : (size_t)MT * ActLayout<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE>::row_bytes(nsb);
@@ -384,10 +385,10 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     const int ub = b * a.units_base + (b < a.units_rem ? b : a.units_rem);
     const int nu = a.units_base + (b < a.units_rem ? 1 : 0);
     const int ng = (nu + 3) >> 2;                                  // 32-row groups of this CTA
-    const int team = warp / S, wi = warp - team * S;
-    const int tg = team < ng ? (ng - team + T - 1) / T : 0;        // groups of this team: team, team + T, ...
+    const int team = warp >> a.S_log, wi = warp & (S - 1);
+    const int tg = team < ng ? (ng - team + T - 1) >> a.T_log : 0; // groups of this team: team, team + T, ...
     const int n = tg * nsb;                                        // steps of this team
-    const int nsteps = wi < n ? (n - wi + S - 1) / S : 0;          // this warp takes the team's steps wi, wi + S, ...
+    const int nsteps = wi < n ? (n - wi + S - 1) >> a.S_log : 0;   // this warp takes the team's steps wi, wi + S, ...
 
     if (first_pass) {
         if (lane == 0) {
@@ -397,13 +398,15 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         __syncwarp();
     }
     // issue cursor (used by lane 0): k-th group of the team and super-block inside it
-    int ik = wi / nsb, isb = wi - ik * nsb;
+    int ik = 0, isb = wi;
+    while (isb >= nsb) { isb -= nsb; ik++; }
+    const int k_first = ik, sb_first = isb;
     unsigned issued = ring_uses;
     auto issue = [&]() {
         const int g = team + ik * T;
         const int cnt = (nu - 4 * g) < 4 ? (nu - 4 * g) : 4;
         const uint8_t *src = a.w + ((size_t)(ub + 4 * g) * nsb + isb) * TB;
-        const unsigned stg = issued % (unsigned)nst;
+        const unsigned stg = issued & (unsigned)(nst - 1);
         gv_bar_expect(bar + stg, (unsigned)(cnt * TB));
         for (int t = 0; t < cnt; t++) gv_bulk_load(ring + stg * STEP + t * TB, src + (size_t)t * nsb * TB, TB, bar + stg);
         issued++;
@@ -418,18 +421,21 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     if (TYPE == OJAS_B200_Q8_0) stage_f32<MT>(a, reinterpret_cast<float *>(act));
     else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
+    // tensor-parallel launches: the step in flight is the stamp and picks the half of the windows
+    const unsigned tp_stamp = a.tp.step ? *reinterpret_cast<const volatile unsigned *>(a.tp.step) : 0u;
+    const size_t tp_half = (size_t)(tp_stamp & 1u) * a.tp.half_pairs;
 
     float acc[MT];
 #pragma unroll
     for (int m = 0; m < MT; m++) acc[m] = 0.0f;
-    int k = wi / nsb, sb = wi - k * nsb;
+    int k = k_first, sb = sb_first;
     const int unit = lane >> 3, r = lane & 7;
     const uint8_t *wl = ring + unit * TB + r * 16;
     for (int q = 0; q < nsteps; q++) {
         const unsigned use = ring_uses + (unsigned)q;
-        const unsigned stg = use % (unsigned)nst;
+        const unsigned stg = use & (unsigned)(nst - 1);
         const int g = team + k * T;
-        gv_bar_wait(bar + stg, (use / (unsigned)nst) & 1u, a.status);
+        gv_bar_wait(bar + stg, (use >> a.nst_log) & 1u, a.status);
         if (4 * g + unit < nu) {
             const int row = (ub + 4 * g + unit) * 8 + r;
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
@@ -441,7 +447,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue();
         }
-        const int slot = sb % S, k_now = k;
+        const int slot = sb & (S - 1), k_now = k;
         sb += S;
         bool flush = q + 1 == nsteps;
         while (sb >= nsb) { sb -= nsb; k++; flush = true; }
@@ -459,19 +465,29 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     // combine: four threads per (group, activation row, weight row), each adds every fourth partial sum
     for (int idx = threadIdx.x; idx < ng * MT * 32 * 4; idx += blockDim.x) {
         const int item = idx >> 2, pq = idx & 3;
-        const int g = item / (MT * 32), rem = item - g * (MT * 32);
+        const int g = item / (MT * 32), rem = item & (MT * 32 - 1);      // MT is a power of two
         const int m = rem >> 5, rr = rem & 31;
         float v = 0.0f;
         for (int p = pq; p < P; p += 4) v += part[((g * P + p) * MT + m) * 32 + rr];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
         const int row = (ub + 4 * g) * 8 + rr;
-        if (pq == 0 && m < a.M && 4 * g + (rr >> 3) < nu && row < a.N) store_form(a.y + (size_t)m * a.N + row, v, a.form, a.bias, row);
+        if (pq == 0 && m < a.M && 4 * g + (rr >> 3) < nu && row < a.N) {
+            if (a.tp.step) {
+                const uint2 pair = make_uint2(__float_as_uint(v), tp_stamp);
+                for (int i = 0; i < a.tp.n; i++) a.tp.dst[i][tp_half + (size_t)m * a.N + row] = pair;     // every rank's receive window
+            } else {
+                store_form(a.y + (size_t)m * a.N + row, v, a.form, a.bias, row);
+            }
+        }
     }
 }
 
-template <int TYPE, int MT, bool PREQ, bool DUMP>
-__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, MT == 1 ? 2 : 1) gemv_kernel(const GemvArgs a) {
+// MINB = 2: at most 64 registers per thread, so that two CTAs of 16 warps fit on an SM: the CTA of the next GEMV in
+// the stream becomes resident (and starts its weight copies) while this one still computes.  Used when the shape
+// needs less than half of an SM's shared memory; larger shapes take the 128-register form.
+template <int TYPE, int MT, bool PREQ, bool DUMP, int MINB>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, MINB) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char gemv_smem[];
     unsigned ring_uses = 0;
     gemv_body<TYPE, MT, PREQ, DUMP>(a, gemv_smem, ring_uses, true);
@@ -514,7 +530,7 @@ __global__ void __launch_bounds__(256) quant_q8k_kernel(const float *x, int8_t *
 
 // ---------------------------------------------------------------------------- host side
 struct GemvPlan {
-    int grid, warps, nst, S, P, own_x;
+    int grid, warps, nst_log, S_log, T_log, P, own_x;
     size_t smem;
 };
 
@@ -524,8 +540,11 @@ static size_t gemv_act_bytes(uint32_t type, int MT, size_t K) {
     return (size_t)MT * (type == OJAS_B200_Q4_K ? ActLayout<OJAS_B200_Q4_K>::row_bytes((int)nsb) : ActLayout<OJAS_B200_Q6_K>::row_bytes((int)nsb));
 }
 
-// Picks the grid, the warps per CTA, the ring depth and the team width for a shape.  Returns false if not even
-// the smallest configuration fits in shared memory.
+static int ilog2(size_t v) { int l = 0; while (((size_t)1 << (l + 1)) <= v) l++; return l; }
+
+// Picks the grid, the warps per CTA (a power of two), the ring depth (1, 2 or 4 stages) and the team width for a
+// shape: among the choices that fit in shared memory, the one that keeps the most weight bytes in flight.
+// Returns false if not even the smallest configuration fits.
 static bool gemv_plan(ojas_b200_ctx *ctx, uint32_t type, int MT, size_t K, size_t N, GemvPlan &p) {
     const size_t nsb = K / 256, units = tile_units(N), groups = (units + 3) / 4;
     const size_t step = 4 * (size_t)tile_bytes(type);
@@ -533,37 +552,39 @@ static bool gemv_plan(ojas_b200_ctx *ctx, uint32_t type, int MT, size_t K, size_
     p.grid = (int)(groups < (size_t)ctx->sm_count ? groups : (size_t)ctx->sm_count);
     const size_t units_max = (units + p.grid - 1) / p.grid, ng = (units_max + 3) / 4;
     const size_t steps = ng * nsb;                                 // steps of the busiest CTA
-    const size_t act = gemv_act_bytes(type, MT, K);
-    const size_t fixed = act + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
-    int best_w = 0, best_n = 0, best_S = 0;
-    size_t best_bytes = 0, best_smem = 0;
+    const size_t fixed = gemv_act_bytes(type, MT, K) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
     // the options are upper bounds: a forced choice that does not fit falls back to the next smaller one
-    const int w_hi = ctx->gemv_warps ? ctx->gemv_warps : GEMV_MAX_WARPS, w_lo = 1;
-    const int n_hi = ctx->gemv_stages ? ctx->gemv_stages : 2, n_lo = 1;
-    for (int w = w_hi; w >= w_lo; w--) {
-        if ((size_t)w > steps && w > 1 && !ctx->gemv_warps) continue;       // more warps than steps: idle warps
-        // team width: all warps share a group unless the partial sums would take too much room
-        int S = 1;
-        while (S * 2 <= w && w % (S * 2) == 0) S *= 2;             // largest power of two dividing w
-        if (S != w) continue;                                      // keep the warp count a power of two
-        size_t P = (size_t)S < nsb ? (size_t)S : nsb;
-        while (S > 1 && ng * P * MT * 128 > 32 * 1024) { S >>= 1; P = (size_t)S < nsb ? (size_t)S : nsb; }
+    const int w_hi = ctx->gemv_warps ? ctx->gemv_warps : GEMV_MAX_WARPS;
+    const int n_hi = ctx->gemv_stages ? ctx->gemv_stages : 2;
+    size_t best_bytes = 0;
+    bool found = false;
+    for (int w = w_hi; w >= 1; w >>= 1) {
+        if ((size_t)w > steps && w > 1) continue;                  // more warps than steps: idle warps
+        // Teams.  One row (the latency-bound case): all warps share a group, so a CTA's loads in flight are
+        // neighbours in memory.  Batches: as many teams as the CTA has groups (each team keeps its partial sums
+        // apart, so fewer warps per group means less shared memory for them).
+        size_t T = 1;
+        if (MT > 1) while (T * 2 <= (size_t)w && T * 2 <= ng) T *= 2;
+        size_t S = (size_t)w / T, P = S < nsb ? S : nsb;
+        while (S > 1 && ng * P * MT * 128 > 32 * 1024) { S >>= 1; T <<= 1; P = S < nsb ? S : nsb; }
         const size_t part = ng * P * MT * 128;
-        for (int n = n_hi; n >= n_lo; n--) {
-            const size_t per_warp = (steps + w - 1) / w;
-            const int nn = (size_t)n > per_warp ? (int)per_warp : n;
-            const size_t smem = (size_t)w * nn * step + fixed + part;
-            if (smem > limit || nn < 1) continue;
-            const size_t bytes = (size_t)w * nn * step;
-            if (bytes > best_bytes) { best_bytes = bytes; best_w = w; best_n = nn; best_S = S; best_smem = smem; }
+        const size_t per_warp = (((ng + T - 1) / T) * nsb + S - 1) / S;        // steps of the busiest warp
+        for (int n = n_hi; n >= 1; n--) {
+            if (n == 3) continue;                                  // depths are powers of two
+            const size_t nn = (size_t)n > per_warp ? ((size_t)1 << ilog2(per_warp)) : (size_t)n;
+            const size_t bytes = (size_t)w * nn * step, smem = bytes + fixed + part;
+            if (smem > limit) continue;
+            if (bytes > best_bytes) {
+                best_bytes = bytes;
+                found = true;
+                p.warps = w; p.nst_log = ilog2(nn); p.S_log = ilog2(S); p.T_log = ilog2(T);
+                p.P = (int)P;
+                p.own_x = (T == 1 && S == nsb) ? 1 : 0;
+                p.smem = smem;
+            }
         }
     }
-    if (!best_w) return false;
-    p.warps = best_w; p.nst = best_n; p.S = best_S;
-    p.P = (int)((size_t)best_S < nsb ? (size_t)best_S : nsb);
-    p.own_x = (best_S == best_w && (size_t)best_w == nsb) ? 1 : 0;
-    p.smem = best_smem;
-    return true;
+    return found;
 }
 
 template <typename KernelT>
@@ -597,7 +618,7 @@ static void gemv_fill(GemvArgs &a, ojas_b200_ctx *ctx, const GemvPlan &p) {
     a.nsb = a.K / 256;
     a.units_base = (int)(units / p.grid);
     a.units_rem = (int)(units % p.grid);
-    a.nst = p.nst; a.S = p.S; a.P = p.P; a.own_x = p.own_x;
+    a.nst_log = p.nst_log; a.S_log = p.S_log; a.T_log = p.T_log; a.P = p.P; a.own_x = p.own_x;
     a.status = ctx->dev_status;
 }
 
@@ -611,20 +632,22 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     if (!gemv_plan(ctx, type, MT, (size_t)args.K, (size_t)args.N, p)) return 1;
     gemv_fill(args, ctx, p);
     if (preq || dump) args.own_x = dump ? args.own_x : 0;
+    const bool two = p.smem <= (size_t)ctx->smem_optin / 2 - 1024;      // two CTAs per SM fit
 #define GEMV_CASE(T, PQ, NAME)                                                                 \
     switch (MT) {                                                                              \
-    case 1: return launch_gemv(ctx, gemv_kernel<T, 1, PQ, false>, args, p, NAME);              \
-    case 2: return launch_gemv(ctx, gemv_kernel<T, 2, PQ, false>, args, p, NAME);              \
-    case 4: return launch_gemv(ctx, gemv_kernel<T, 4, PQ, false>, args, p, NAME);              \
-    default: return launch_gemv(ctx, gemv_kernel<T, 8, PQ, false>, args, p, NAME);             \
+    case 1: return two ? launch_gemv(ctx, gemv_kernel<T, 1, PQ, false, 2>, args, p, NAME)      \
+                       : launch_gemv(ctx, gemv_kernel<T, 1, PQ, false, 1>, args, p, NAME);     \
+    case 2: return launch_gemv(ctx, gemv_kernel<T, 2, PQ, false, 1>, args, p, NAME);           \
+    case 4: return launch_gemv(ctx, gemv_kernel<T, 4, PQ, false, 1>, args, p, NAME);           \
+    default: return launch_gemv(ctx, gemv_kernel<T, 8, PQ, false, 1>, args, p, NAME);          \
     }
     if (type == OJAS_B200_Q4_K) {
-        if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q4_K, 1, false, true>, args, p, "gemv_q4k_idots");
+        if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q4_K, 1, false, true, 1>, args, p, "gemv_q4k_idots");
         if (preq) { GEMV_CASE(OJAS_B200_Q4_K, true, "gemv_q4k_q8k") }
         GEMV_CASE(OJAS_B200_Q4_K, false, "gemv_q4k")
     }
     if (type == OJAS_B200_Q6_K) {
-        if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q6_K, 1, false, true>, args, p, "gemv_q6k_idots");
+        if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q6_K, 1, false, true, 1>, args, p, "gemv_q6k_idots");
         if (preq) { GEMV_CASE(OJAS_B200_Q6_K, true, "gemv_q6k_q8k") }
         GEMV_CASE(OJAS_B200_Q6_K, false, "gemv_q6k")
     }
@@ -730,6 +753,20 @@ extern "C" int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t type, int form, const
     a.x = x; a.w = (const uint8_t *)w; a.y = y; a.bias = bias;
     a.K = (int)K; a.N = (int)N; a.M = (int)M; a.form = form;
     return gemv_run(ctx, type, false, a, M);
+}
+
+// The tensor-parallel form of a single-row GEMV (tp.cu): results also go to the peers' windows.
+int ojas_gemv_tp(ojas_b200_ctx *ctx, uint32_t type, const float *x, const void *w, size_t K, size_t N, const TpPush &push) {
+    float *y = reinterpret_cast<float *>(push.dst[0]);      // (not written: the results go to the windows)
+    int rc = gemv_check(ctx, type, OJAS_B200_PLAIN, w, y, nullptr, K, N, 1);
+    if (rc) return rc;
+    if (!x) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv: null activation pointer");
+    if (((uintptr_t)x & 15) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv: x must be 16-byte aligned");
+    GemvArgs a{};
+    a.x = x; a.w = (const uint8_t *)w; a.y = y;
+    a.K = (int)K; a.N = (int)N; a.M = 1; a.form = OJAS_B200_PLAIN;
+    a.tp = push;
+    return gemv_run(ctx, type, false, a, 1);
 }
 
 extern "C" int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t type, int form, const int8_t *q, const float *scales,

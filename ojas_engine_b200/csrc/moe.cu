@@ -16,38 +16,70 @@
 #include "act_quant.cuh"
 
 // ---------------------------------------------------------------- router
-// One warp per token.  E <= 1024.
-__global__ void __launch_bounds__(32) moe_topk_kernel(const float *lg, uint32_t *idx, float *wgt, int E, int ksel) {
-    __shared__ float pr[1024];
-    __shared__ float tw[32];
-    const int lane = threadIdx.x;
-    const float *l = lg + (size_t)blockIdx.x * E;
-    uint32_t *oi = idx + (size_t)blockIdx.x * ksel;
-    float *ow = wgt + (size_t)blockIdx.x * ksel;
+// One warp per token, MOE_ROUTER_WARPS tokens per CTA.  A pick is one warp-wide maximum over 64-bit keys
+// (probability bits << 32 | ~expert): probabilities are >= 0, so their bit patterns order like the values, and the
+// inverted index in the low half makes the lowest expert win a tie, as the engine's router does
+// (crates/ojas-cuda/src/kernels/moe.rs:62-64).  Up to 32 experts a lane keeps its expert's probability in a
+// register; beyond that the probabilities of a token sit in this warp's slice of shared memory and every lane
+// scans the experts lane, lane + 32, ...  A picked expert is retired by clearing its key.
+constexpr int MOE_ROUTER_WARPS = 4;
+
+__device__ __forceinline__ unsigned long long router_key(float p, int e) {
+    return ((unsigned long long)__float_as_uint(p) << 32) | (unsigned long long)(0xffffffffu - (unsigned)e);
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = t > v ? t : v;
+    }
+    return v;
+}
+
+template <bool SMALL>
+__global__ void __launch_bounds__(MOE_ROUTER_WARPS * 32) moe_router_kernel(const float *lg, uint32_t *idx, float *wgt, int M, int E, int ksel) {
+    extern __shared__ float router_probs[];                      // !SMALL: [MOE_ROUTER_WARPS][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * MOE_ROUTER_WARPS + warp;
+    if (tok >= M) return;
+    const float *l = lg + (size_t)tok * E;
+    float *probs = SMALL ? nullptr : router_probs + (size_t)warp * E;
+    // softmax numerators exp(l - max) and their sum
     float mx = -1e30f;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, l[e]);
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, __ldg(l + e));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.0f;
-    for (int e = lane; e < E; e += 32) { const float v = expf(l[e] - mx); pr[e] = v; sum += v; }
-    sum = warp_sum(sum);
-    __syncwarp();
-    float wsum = 0.0f;
-    for (int j = 0; j < ksel; j++) {
-        float bv = -1.0f;
-        uint32_t bi = 0u;
-        for (int e = lane; e < E; e += 32) if (pr[e] > bv) { bv = pr[e]; bi = (uint32_t)e; }
-        float m2 = bv;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, o));
-        uint32_t cand = (bv == m2) ? bi : 0xffffffffu;     // ties resolve to the lowest index
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
-        if (lane == 0) { oi[j] = cand; tw[j] = m2 / sum; pr[cand] = -1.0f; }
-        wsum += m2 / sum;
-        __syncwarp();
+    float mine = 0.0f, sum = 0.0f;                               // SMALL: this lane's expert
+    for (int e = lane; e < E; e += 32) {
+        const float v = expf(__ldg(l + e) - mx);
+        if (SMALL) mine = v; else probs[e] = v;
+        sum += v;
     }
-    for (int j = lane; j < ksel; j += 32) ow[j] = tw[j] / wsum;
+    sum = warp_sum(sum);
+    if (!SMALL) __syncwarp();
+    unsigned long long key = (SMALL && lane < E) ? router_key(mine, lane) : 0ull;
+    float picked_w = 0.0f, wsum = 0.0f;                          // lane j keeps pick j's weight
+    uint32_t picked_e = 0u;
+    for (int j = 0; j < ksel; j++) {
+        if (!SMALL) {
+            key = 0ull;
+            for (int e = lane; e < E; e += 32) {
+                const float v = probs[e];
+                if (v >= 0.0f) { const unsigned long long k2 = router_key(v, e); key = k2 > key ? k2 : key; }
+            }
+        }
+        const unsigned long long best = warp_max_u64(key);
+        const uint32_t e = 0xffffffffu - (uint32_t)(best & 0xffffffffull);
+        const float w = __uint_as_float((unsigned)(best >> 32)) / sum;
+        wsum += w;
+        if (lane == j) { picked_e = e; picked_w = w; }
+        if (SMALL) { if ((uint32_t)lane == e) key = 0ull; }
+        else { if (lane == 0) probs[e] = -1.0f; __syncwarp(); }
+    }
+    if (lane < ksel) {
+        idx[(size_t)tok * ksel + lane] = picked_e;
+        wgt[(size_t)tok * ksel + lane] = picked_w / wsum;
+    }
 }
 
 // ---------------------------------------------------------------- grouping
@@ -92,29 +124,8 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const uint32_t *idx, in
     }
 }
 
-// ---------------------------------------------------------------- SwiGLU + requantization
-// act = silu(g) * u, then quant_q8k(act): one warp per (row, super-block).  silu(x) = x / (1 + exp(-x))
-// (crates/ojas-cpu/src/cpu_math.rs:486).
-__global__ void __launch_bounds__(256) moe_silu_quant_kernel(const float *g, const float *u, int8_t *q, float *scales, int32_t *bsums,
-                                                              long long n_sb) {
-    const int lane = threadIdx.x & 31;
-    const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (sb >= n_sb) return;
-    const float4 g0 = __ldg(reinterpret_cast<const float4 *>(g + sb * 256) + lane * 2), g1 = __ldg(reinterpret_cast<const float4 *>(g + sb * 256) + lane * 2 + 1);
-    const float4 u0 = __ldg(reinterpret_cast<const float4 *>(u + sb * 256) + lane * 2), u1 = __ldg(reinterpret_cast<const float4 *>(u + sb * 256) + lane * 2 + 1);
-    const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-    const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = __fmul_rn(__fdiv_rn(gv[i], 1.0f + expf(-gv[i])), uv[i]);
-    const Q8kLane ql = quant_q8k_values(v);
-    reinterpret_cast<uint2 *>(q + sb * 256)[lane] = ql.packed;
-    int s = ql.sum8;
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    if ((lane & 3) == 0) bsums[sb * 8 + (lane >> 2)] = s;
-    if (lane == 0) scales[sb] = ql.scale;
-}
+// SwiGLU + requantization (act = silu(g) * u, then quant_q8k): producers.cu
+int ojas_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, const float *u, int8_t *q, float *scales, int32_t *bsums, size_t rows, size_t K);
 
 // ---------------------------------------------------------------- prefill form helpers
 // dst[p, :] = src[tok[p], :] for rows of d f16 values (d is a multiple of 256): one block per sorted position.
@@ -125,7 +136,7 @@ __global__ void __launch_bounds__(256) moe_gather_f16_kernel(const uint4 *src, c
     for (int i = threadIdx.x; i < d8; i += blockDim.x) o[i] = __ldg(s + i);
 }
 
-// g = silu(g) * u in place, the same expression as moe_silu_quant_kernel.
+// g = silu(g) * u in place, the same expression as silu_mul_q8k_kernel (producers.cu).
 __global__ void __launch_bounds__(256) moe_silu_mul_kernel(float4 *g, const float4 *u, long long n4) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n4) return;
@@ -160,7 +171,9 @@ extern "C" int ojas_b200_moe_topk(ojas_b200_ctx *ctx, const float *logits, uint3
         return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_topk: E=%zu (1..1024), KSEL=%zu (1..32, <= E)", E, KSEL);
     if (M == 0) return 0;
     if (M > 0x7fffffffu) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_topk: too many rows");
-    moe_topk_kernel<<<(unsigned)M, 32, 0, ctx->stream>>>(logits, idx, wgt, (int)E, (int)KSEL);
+    const unsigned blocks = (unsigned)((M + MOE_ROUTER_WARPS - 1) / MOE_ROUTER_WARPS);
+    if (E <= 32) moe_router_kernel<true><<<blocks, MOE_ROUTER_WARPS * 32, 0, ctx->stream>>>(logits, idx, wgt, (int)M, (int)E, (int)KSEL);
+    else moe_router_kernel<false><<<blocks, MOE_ROUTER_WARPS * 32, MOE_ROUTER_WARPS * E * sizeof(float), ctx->stream>>>(logits, idx, wgt, (int)M, (int)E, (int)KSEL);
     OJAS_LAUNCH_CHECK(ctx, "moe_topk");
     return 0;
 }
@@ -268,9 +281,8 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
                                w.counts + e, w.offsets + e, w.u, d, ffn);
         if (rc) return rc;
     }
-    const long long n_sb = (long long)A * (long long)(ffn / 256);
-    moe_silu_quant_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(w.g, w.u, w.aq, w.as, w.ab, n_sb);
-    OJAS_LAUNCH_CHECK(ctx, "moe_silu_quant");
+    rc = ojas_silu_mul_q8k(ctx, w.g, w.u, w.aq, w.as, w.ab, A, ffn);
+    if (rc) return rc;
     for (size_t e = 0; e < E; e++) {   // down of expert e over its (contiguous, sorted) rows
         rc = ojas_gemv_grouped(ctx, type_d, weight_rows_at(type_d, wd, ffn, e * d), w.aq, w.as, w.ab, nullptr,
                                w.counts + e, w.offsets + e, w.yd, ffn, d);

@@ -46,6 +46,8 @@ SIGNATURES = {
     "ojas_b200_repack": (_i, [_vp, _u32, _vp, _sz, _sz, _vp]),
     "ojas_b200_repack_host": (_i, [_u32, _vp, _sz, _sz, _vp]),
     "ojas_b200_quant_q8k": (_i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp]),
+    "ojas_b200_rmsnorm_q8k": (_i, [_vp, _vp, _vp, C.c_float, _sz, _sz, _vp, _vp, _vp, _vp]),
+    "ojas_b200_silu_mul_q8k": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp]),
     "ojas_b200_gemv": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_q8k": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_idots": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz]),
@@ -59,6 +61,15 @@ SIGNATURES = {
     "ojas_b200_tp_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "ojas_b200_tp_shard_k": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "ojas_b200_tp_slice_k_host": (_i, [_u32, _vp, _sz, _sz, _sz, _sz, _vp]),
+    "ojas_b200_tp_create": (_i, [_vp, _i, _i, _sz, C.POINTER(_vp)]),
+    "ojas_b200_tp_destroy": (None, [_vp]),
+    "ojas_b200_tp_handle_bytes": (_sz, []),
+    "ojas_b200_tp_export": (_i, [_vp, _vp]),
+    "ojas_b200_tp_import": (_i, [_vp, _i, _vp]),
+    "ojas_b200_tp_set_wait_us": (_i, [_vp, C.c_uint]),
+    "ojas_b200_tp_gemv": (_i, [_vp, _u32, _vp, _vp, _sz, _sz, _sz]),
+    "ojas_b200_tp_join": (_i, [_vp, _i, _vp, _sz]),
+    "ojas_b200_tp_allgather": (_i, [_vp, _vp, _sz, _vp]),
     "ojas_b200_has_kernel": (_i, [C.c_char_p]),
     "ojas_b200_kernel_count": (_i, []),
     "ojas_b200_kernel_name": (C.c_char_p, [_i]),

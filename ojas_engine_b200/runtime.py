@@ -168,6 +168,15 @@ class B200Gpu:
     def quant_q8k(self, x: Buf, m: int, k: int, q: Buf, scales: Buf, bsums: Buf) -> None:
         self._ck(self._l.ojas_b200_quant_q8k(self._ctx, C.c_void_p(x.ptr), m, k, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr)))
 
+    def rmsnorm_q8k(self, x: Buf, w: Buf, eps: float, m: int, k: int, q: Buf, scales: Buf, bsums: Buf, xn: Buf | None = None) -> None:
+        """RMSNorm of the rows of x [m,k] ending in Q8_K (the input of ``gemv_q8k``); ``xn`` also keeps the f32 rows."""
+        self._ck(self._l.ojas_b200_rmsnorm_q8k(self._ctx, C.c_void_p(x.ptr), C.c_void_p(w.ptr), C.c_float(eps), m, k,
+                                               C.c_void_p(xn.ptr) if xn else None, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr)))
+
+    def silu_mul_q8k(self, g: Buf, u: Buf, m: int, k: int, q: Buf, scales: Buf, bsums: Buf) -> None:
+        """act = silu(g) * u per element of [m,k], ending in Q8_K."""
+        self._ck(self._l.ojas_b200_silu_mul_q8k(self._ctx, C.c_void_p(g.ptr), C.c_void_p(u.ptr), m, k, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr)))
+
     def gemv(self, w: Lin, x: Buf, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
         self._ck(self._l.ojas_b200_gemv(self._ctx, w.ggml_type, form, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
                                         C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))

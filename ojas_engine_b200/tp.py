@@ -99,3 +99,46 @@ class ShardedLinear:
         parts = [torch.empty((m, s), dtype=y_local.dtype, device=y_local.device) for s in sizes]
         dist.all_gather(parts, y_local.contiguous())
         return torch.cat(parts, dim=1)
+
+
+class TpGroup:
+    """The decode join through peer memory (``ojas_b200_tp_*``): every rank's GEMV stores its results straight into
+    all ranks' receive windows (stamped values, no flags) and a join kernel with a bounded wait forms the result.  One process per GPU;
+    ``exchange(obj) -> list`` is any host all-gather of Python objects (``torch.distributed.all_gather_object``
+    wrapped by the caller): it carries the CUDA IPC handles once, at set-up, and nothing afterwards."""
+
+    COL, ROW = 1, 2
+
+    def __init__(self, gpu, world: int, rank: int, slot_floats: int, exchange):
+        self.gpu, self.world, self.rank, self.slot_floats = gpu, world, rank, slot_floats
+        self._l = _lib.load()
+        h = C.c_void_p()
+        gpu._ck(self._l.ojas_b200_tp_create(gpu.ctx, world, rank, slot_floats, C.byref(h)))
+        self._h = h
+        nbytes = self._l.ojas_b200_tp_handle_bytes()
+        mine = (C.c_uint8 * nbytes)()
+        gpu._ck(self._l.ojas_b200_tp_export(self._h, mine))
+        handles = exchange(bytes(mine))
+        for peer, blob in enumerate(handles):
+            if peer != rank:
+                buf = (C.c_uint8 * nbytes).from_buffer_copy(blob)
+                gpu._ck(self._l.ojas_b200_tp_import(self._h, peer, buf))
+
+    def set_wait_us(self, micros: int) -> None:
+        self.gpu._ck(self._l.ojas_b200_tp_set_wait_us(self._h, micros))
+
+    def gemv(self, w, x, offset: int = 0) -> None:
+        """One activation row through this rank's shard ``w`` (a ``Lin``); results pushed to every rank."""
+        self.gpu._ck(self._l.ojas_b200_tp_gemv(self._h, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), w.k, w.n, offset))
+
+    def join(self, mode: int, y=None, n_total: int = 0) -> None:
+        self.gpu._ck(self._l.ojas_b200_tp_join(self._h, mode, C.c_void_p(y.ptr) if y is not None else None, n_total))
+
+    def allgather(self, src, floats: int, y_all) -> None:
+        """One kernel: push ``floats`` values of ``src`` to every rank, wait (bounded), copy out ``y_all`` [world][floats]."""
+        self.gpu._ck(self._l.ojas_b200_tp_allgather(self._h, C.c_void_p(src.ptr), floats, C.c_void_p(y_all.ptr)))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._l.ojas_b200_tp_destroy(self._h)
+            self._h = None

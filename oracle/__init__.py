@@ -69,6 +69,8 @@ def _load(native: bool = False) -> C.CDLL:
         "orc_moe_ffn": (C.c_int, [u8p, u8p, u8p, C.c_uint32, C.c_uint32, f32p, u32p, f32p, C.c_size_t, C.c_int,
                                   C.c_size_t, C.c_size_t, C.c_int, f32p]),
         "orc_tvec": (None, [C.c_size_t, C.c_uint32, f32p]),
+        "orc_rmsnorm": (None, [f32p, f32p, C.c_size_t, C.c_float, f32p]),
+        "orc_silu_mul": (None, [f32p, f32p, C.c_size_t, f32p]),
     }
     for name_, (res, args) in sig.items():
         fn = getattr(lib, name_)
@@ -187,6 +189,22 @@ def matmul_kq(raw, t: int, n: int, k: int, x, threads: int = 0, native: bool = F
     rc = lib(native).orc_matmul_kq(_p(raw, C.c_uint8), t, n, k, _p(x, C.c_float), m, threads or (os.cpu_count() or 1),
                                    _p(out, C.c_float))
     assert rc == 0, rc
+    return out
+
+
+def rmsnorm(x, w, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32).reshape(-1)
+    w = np.ascontiguousarray(w, np.float32).reshape(-1)
+    out = np.empty_like(x)
+    lib().orc_rmsnorm(_p(x, C.c_float), _p(w, C.c_float), x.size, eps, _p(out, C.c_float))
+    return out
+
+
+def silu_mul(g, u) -> np.ndarray:
+    g = np.ascontiguousarray(g, np.float32).reshape(-1)
+    u = np.ascontiguousarray(u, np.float32).reshape(-1)
+    out = np.empty_like(g)
+    lib().orc_silu_mul(_p(g, C.c_float), _p(u, C.c_float), g.size, _p(out, C.c_float))
     return out
 
 

@@ -446,6 +446,21 @@ ORC_API void orc_moe_topk(const float *lg, int E, int ksel, uint32_t *idx, float
 
 static inline float silu(float x) { return x / (1.0f + expf(-x)); } /* cpu_math.rs:486 */
 
+/* rmsnorm (crates/ojas-cpu/src/cpu_math.rs:456-460): ss = (sum of v*v in index order) / n, inv = 1 / sqrt(ss + eps),
+ * out = (a * inv) * b. */
+ORC_API void orc_rmsnorm(const float *x, const float *w, size_t n, float eps, float *out) {
+    float ss = 0.0f;
+    for (size_t i = 0; i < n; i++) ss += x[i] * x[i];
+    ss = ss / (float)n;
+    const float inv = 1.0f / sqrtf(ss + eps);
+    for (size_t i = 0; i < n; i++) out[i] = x[i] * inv * w[i];
+}
+
+/* act = silu(g) * u, the SwiGLU step between the expert matmuls (crates/ojas-cpu/src/cpu_glm.rs:575). */
+ORC_API void orc_silu_mul(const float *g, const float *u, size_t n, float *out) {
+    for (size_t i = 0; i < n; i++) out[i] = silu(g[i]) * u[i];
+}
+
 /* Expert FFN for m tokens the way the CPU path runs it
  * (crates/ojas-cpu/src/cpu_glm.rs:551-582): per token, per pick j: three
  * matvec_kq (gate, up over h; down over act) and out += wgt * down.  Experts are

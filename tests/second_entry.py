@@ -1,0 +1,138 @@
+"""A second, independent entry of the reference's CPU quantized dot layer in numpy / Python scalars, written from the
+Rust source (crates/ojas-cpu/src/cpu_math.rs) and not from the C oracle.  The reference has no unit test or golden
+vector for quant_q8k / dot_q4k / dot_q6k / dot_q80, so the C oracle is checked against this transcription instead:
+two entries of the same text that agree bit for bit on random and on the reference's synthetic blocks.
+
+Every f32 operation is done in np.float32 in the order the Rust source performs it (Rust does not fuse
+multiply-adds).  Small inputs only: the loops are plain Python."""
+from __future__ import annotations
+
+import numpy as np
+
+F = np.float32
+
+
+def _round_half_away(v: np.float32) -> np.float32:
+    """f32::round: to nearest, ties away from zero (cpu_math.rs:557)."""
+    t = np.trunc(v)
+    return F(t + np.copysign(F(1.0), v)) if abs(F(v - t)) >= F(0.5) else F(t)
+
+
+def quant_q8k(x: np.ndarray):
+    """cpu_math.rs:545-563."""
+    x = np.asarray(x, F)
+    nsb = (x.size + 255) // 256
+    scales = np.empty(nsb, F)
+    q = np.zeros(nsb * 256, np.int8)
+    bsums = np.zeros(nsb * 8, np.int32)
+    for sb in range(nsb):
+        seg = x[sb * 256:min(sb * 256 + 256, x.size)]
+        m = F(0)
+        for v in seg:                                   # fold(0, |a, v| a.max(v.abs())): NaN is ignored by f32::max
+            a = F(abs(v))
+            if a > m:
+                m = a
+        scale = F(m / F(127.0)) if m > 0 else F(1.0)
+        inv = F(F(1.0) / scale)
+        scales[sb] = scale
+        for i, v in enumerate(seg):
+            r = _round_half_away(F(v * inv))
+            if np.isnan(r):
+                qi = 0                                  # `as i8` of NaN
+            else:
+                qi = int(min(max(r, F(-127.0)), F(127.0)))
+            q[sb * 256 + i] = qi
+            bsums[sb * 8 + i // 32] += qi
+    return scales, q, bsums
+
+
+def _f16(b: np.ndarray, off: int) -> np.float32:
+    return F(np.frombuffer(bytes(b[off:off + 2]), np.float16)[0])
+
+
+def _scale_min_k4(j: int, s: np.ndarray):
+    """cpu_math.rs:566-574."""
+    if j < 4:
+        return F(int(s[j]) & 63), F(int(s[j + 4]) & 63)
+    d = (int(s[j + 4]) & 0xF) | ((int(s[j - 4]) >> 6) << 4)
+    m = (int(s[j + 4]) >> 4) | ((int(s[j]) >> 6) << 4)
+    return F(d), F(m)
+
+
+def dot_q4k(row: np.ndarray, act):
+    """cpu_math.rs:609-635.  Returns (value, the eight integer sub-block dots per super-block)."""
+    scales, q, bsums = act
+    total = F(0)
+    idots = []
+    for sb in range(row.size // 144):
+        blk = row[sb * 144:(sb + 1) * 144]
+        d, dmin = _f16(blk, 0), _f16(blk, 2)
+        sc, qs = blk[4:16], blk[16:144]
+        sx = F(scales[sb])
+        xq = q[sb * 256:(sb + 1) * 256].astype(np.int32)
+        bs = bsums[sb * 8:(sb + 1) * 8]
+        sumd, summ = F(0), F(0)
+        for c in range(4):
+            qq = qs[c * 32:c * 32 + 32].astype(np.int32)
+            lo, hi = qq & 0xF, qq >> 4
+            s1, m1 = _scale_min_k4(c * 2, sc)
+            s2, m2 = _scale_min_k4(c * 2 + 1, sc)
+            i1 = int((lo * xq[c * 64:c * 64 + 32]).sum())
+            i2 = int((hi * xq[c * 64 + 32:c * 64 + 64]).sum())
+            idots += [i1, i2]
+            sumd = F(sumd + F(s1 * F(i1)))
+            sumd = F(sumd + F(s2 * F(i2)))
+            summ = F(summ + F(F(m1 * F(int(bs[c * 2]))) + F(m2 * F(int(bs[c * 2 + 1])))))
+        total = F(total + F(sx * F(F(d * sumd) - F(dmin * summ))))
+    return total, np.array(idots, np.int32)
+
+
+def dot_q6k(row: np.ndarray, act):
+    """cpu_math.rs:674-722.  Returns (value, the sixteen integer dots of 16 weights per super-block, in weight order)."""
+    scales, q, _ = act
+    total = F(0)
+    idots = []
+    for sb in range(row.size // 210):
+        blk = row[sb * 210:(sb + 1) * 210]
+        d = _f16(blk, 208)
+        sx = F(scales[sb])
+        xq = q[sb * 256:(sb + 1) * 256].astype(np.int32)
+        s_sum, s_sub = F(0), F(0)
+        for half in range(2):
+            ql = blk[half * 64:half * 64 + 64].astype(np.int32)
+            qh = blk[128 + half * 32:128 + half * 32 + 32].astype(np.int32)
+            sc = blk[192 + half * 8:192 + half * 8 + 8].view(np.int8)
+            xh = xq[half * 128:half * 128 + 128]
+            for quarter in range(4):
+                if quarter == 0:
+                    w = (ql[:32] & 0xF) | ((qh & 3) << 4)
+                elif quarter == 1:
+                    w = (ql[32:] & 0xF) | (((qh >> 2) & 3) << 4)
+                elif quarter == 2:
+                    w = (ql[:32] >> 4) | (((qh >> 4) & 3) << 4)
+                else:
+                    w = (ql[32:] >> 4) | (((qh >> 6) & 3) << 4)
+                x32 = xh[quarter * 32:quarter * 32 + 32]
+                s0, s1 = F(int(sc[quarter * 2])), F(int(sc[quarter * 2 + 1]))
+                i0, i1 = int((w[:16] * x32[:16]).sum()), int((w[16:] * x32[16:]).sum())
+                x0, x1 = int(x32[:16].sum()), int(x32[16:].sum())
+                idots += [i0, i1]
+                s_sum = F(s_sum + F(F(s0 * F(i0)) + F(s1 * F(i1))))
+                s_sub = F(s_sub + F(F(s0 * F(x0)) + F(s1 * F(x1))))
+        total = F(total + F(F(sx * d) * F(s_sum - F(F(32.0) * s_sub))))
+    return total, np.array(idots, np.int32)
+
+
+def dot_q80(row: np.ndarray, x: np.ndarray) -> np.float32:
+    """cpu_math.rs:971-981."""
+    x = np.asarray(x, F)
+    s = F(0)
+    for b in range(x.size // 32):
+        blk = row[b * 34:(b + 1) * 34]
+        d = _f16(blk, 0)
+        acc = F(0)
+        qv = blk[2:34].view(np.int8)
+        for j in range(32):
+            acc = F(acc + F(F(int(qv[j])) * x[b * 32 + j]))
+        s = F(s + F(d * acc))
+    return s

@@ -83,8 +83,70 @@ def test_kquant_dot_identity(t):
             assert np.array_equal(idots, direct.astype(np.int32))
         else:
             got, idots = oracle.dot_q6k(raw[r], act, want_idots=True)
-            assert idots.size == k // 16
+            # the 6-bit values 0..63 by the GGUF rule (crates/ojas-formats/src/gguf.rs:1086-1108), then per-16 dots
+            blk = raw[r].reshape(-1, 210)
+            ql, qh = blk[:, :128].reshape(-1, 2, 64).astype(np.int64), blk[:, 128:192].reshape(-1, 2, 32).astype(np.int64)
+            w6 = np.empty((blk.shape[0], 2, 4, 32), np.int64)
+            w6[:, :, 0] = (ql[:, :, :32] & 0xF) | ((qh & 3) << 4)
+            w6[:, :, 1] = (ql[:, :, 32:] & 0xF) | (((qh >> 2) & 3) << 4)
+            w6[:, :, 2] = (ql[:, :, :32] >> 4) | (((qh >> 4) & 3) << 4)
+            w6[:, :, 3] = (ql[:, :, 32:] >> 4) | (((qh >> 6) & 3) << 4)
+            direct = (w6.reshape(-1, 16, 16) * q.reshape(-1, 16, 16).astype(np.int64)).sum(-1).reshape(-1)
+            assert np.array_equal(idots, direct.astype(np.int32))
         assert abs(got - want) <= 2e-5 * max(1.0, np.abs(w).dot(np.abs(xhat)))
+
+
+# ---- the C oracle against an independent transcription of the Rust source (tests/second_entry.py)
+def _second_entry_inputs():
+    rng = np.random.default_rng(17)
+    xs = [rng.standard_normal(768).astype(np.float32), (rng.standard_normal(512) * 1e-3).astype(np.float32), oracle.tvec(512, 3),
+          np.zeros(256, np.float32)]
+    ties = np.zeros(256, np.float32)
+    ties[0] = 127.0
+    ties[1:253] = np.arange(-126, 126, dtype=np.float32) + np.float32(0.5)     # exact .5 after scaling by 1
+    xs.append(ties)
+    return xs
+
+
+def test_quant_q8k_second_entry():
+    import second_entry
+    for x in _second_entry_inputs():
+        a, b = oracle.quant_q8k(x), second_entry.quant_q8k(x)
+        assert np.array_equal(a[0].view(np.uint32), b[0].view(np.uint32))
+        assert np.array_equal(a[1], b[1]) and np.array_equal(a[2], b[2])
+
+
+@pytest.mark.parametrize("t", [Q4_K, Q6_K])
+@pytest.mark.parametrize("source", ["synth", "gauss"])
+def test_kquant_dots_second_entry(t, source):
+    import second_entry
+    import ojas_engine_b200 as ob
+    k, n = 768, 5
+    if source == "synth":
+        raw = oracle.synth_blocks(t, n * k // 256).reshape(n, -1)
+    else:
+        w = (np.random.default_rng(8).standard_normal((n, k)) * 0.02).astype(np.float32)
+        raw = ob.encode(t, w).reshape(n, -1)
+    x = np.random.default_rng(6).standard_normal(k).astype(np.float32)
+    act = oracle.quant_q8k(x)
+    for r in range(n):
+        if t == Q4_K:
+            got, idots = oracle.dot_q4k(raw[r], act, want_idots=True)
+            want, widots = second_entry.dot_q4k(raw[r], act)
+        else:
+            got, idots = oracle.dot_q6k(raw[r], act, want_idots=True)
+            want, widots = second_entry.dot_q6k(raw[r], act)
+        assert np.array_equal(idots, widots)
+        assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32), (got, want)
+
+
+def test_q80_dot_second_entry():
+    import second_entry
+    k, n = 512, 6
+    raw = oracle.synth_blocks(Q8_0, n * k // 32).reshape(n, -1)
+    x = np.random.default_rng(4).standard_normal(k).astype(np.float32)
+    for r in range(n):
+        assert np.float32(oracle.dot_q80(raw[r], x)).view(np.uint32) == second_entry.dot_q80(raw[r], x).view(np.uint32)
 
 
 def test_q80_dot_and_matvec():

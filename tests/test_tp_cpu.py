@@ -71,3 +71,20 @@ def test_two_gloo_ranks(mode, tmp_path):
             assert np.array_equal(got, full)
         else:
             assert rel_l2(got, full) < 1e-6
+
+
+@pytest.mark.parametrize("mode", ["col", "row"])
+def test_a_rank_that_never_arrives_is_an_error_not_a_hang(mode, tmp_path):
+    """Failure detection on the host: one rank leaves before the collective; the other rank's join raises after the
+    group's timeout (5 s here) instead of waiting for ever."""
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tp_rank_worker.py")
+    port = str(_free_port())
+    outs = [str(tmp_path / f"rank{r}.txt") for r in range(2)]
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "2", port, "absent-" + mode, outs[r]]) for r in range(2)]
+    for p in procs:
+        p.wait(timeout=120)
+    with open(outs[0]) as fh:
+        verdict = fh.read()
+    assert verdict.startswith("error"), verdict

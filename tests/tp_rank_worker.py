@@ -18,6 +18,30 @@ def main() -> None:
     from ojas_engine_b200 import Q4_K, tp
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=port)
+    if mode.startswith("absent-"):
+        # failure detection on the host: rank 1 joins the group and then leaves between steps without taking part in the
+        # collective; rank 0's join must end with an error after the group's timeout instead of hanging
+        import datetime
+        mode = mode[len("absent-"):]
+        dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+        if rank == 1:
+            with open(out, "w") as fh:
+                fh.write("left")
+            os._exit(0)
+        n, k, m = 50, 768, 2
+        raw = synth_weights(Q4_K, n, k)
+        x = np.random.default_rng(1).standard_normal((m, k)).astype(np.float32)
+        sh = tp.ShardedLinear(raw, Q4_K, n, k, mode, rank, world)
+        rows, klen = sh.local_shape
+        y_local = torch.from_numpy(oracle.matmul_kq(sh.raw, Q4_K, rows, klen, sh.local_x(x), threads=1))
+        try:
+            sh.join(y_local, dist)
+            verdict = "joined"
+        except Exception as exc:           # the collective reports the missing rank
+            verdict = "error: " + type(exc).__name__
+        with open(out, "w") as fh:
+            fh.write(verdict)
+        os._exit(0)                         # the group is broken: no orderly shutdown
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         n, k, m = 50, 768, 2      # 50 rows over 2 ranks: equal shards; 768 = 3 super-blocks: uneven K shards
