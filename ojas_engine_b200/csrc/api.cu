@@ -92,6 +92,11 @@ extern "C" int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream) {
 extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value) {
     if (!ctx || !key) return OJAS_B200_E_ARG;
     if (!strcmp(key, "pdl")) { ctx->pdl = value != 0; return 0; }
+    if (!strcmp(key, "gemv_mma")) {
+        if (value < 0 || value > 1) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_mma must be 0 or 1");
+        ctx->gemv_mma = value;
+        return 0;
+    }
     if (!strcmp(key, "gemv_warps")) {
         if (value < 0 || value > 16 || (value & (value - 1)) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_warps must be 0 (automatic), 1, 2, 4, 8 or 16");
         ctx->gemv_warps = value;

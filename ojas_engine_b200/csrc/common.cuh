@@ -18,6 +18,7 @@ struct ojas_b200_ctx {
     int sm_count = 0;
     int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
     uint64_t launches = 0;
+    int gemv_mma = 1;            // Q4_K batches of 3..8 rows and expert groups on the tensor-core batch kernel (0: per-lane kernels only)
     int gemv_warps = 0;          // GEMV: warps per CTA (0: chosen per shape; otherwise 1..16)
     int gemv_stages = 0;         // GEMV: ring stages per warp (0: chosen per shape; otherwise 1..4)
     int moe_gemm_rows = 0;       // expert FFN: grouped tensor-core GEMMs from this many rows per expert on average (0: never)
@@ -109,6 +110,9 @@ struct TpPush {
     int n;                                 // destinations
 };
 
+int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
+                          const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
+                          size_t rows_hint);
 int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w, const int8_t *q, const float *scales,
                       const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
                       size_t K, size_t N);

@@ -22,7 +22,7 @@
 
 constexpr int GEMV_MAX_WARPS = 16;
 constexpr int GEMV_MAX_STAGES = 4;
-constexpr unsigned GEMV_WAIT_PROBES = 1u << 22;     // bounded mbarrier wait: ~ seconds, then the status word is set
+constexpr unsigned GEMV_WAIT_PROBES = 1u << 18;     // bounded mbarrier wait: a fraction of a second at most, then the status word is set
 
 struct GemvArgs {
     const float *x;          // [M, K] f32 (null when activations come pre-quantized)
@@ -91,11 +91,17 @@ __device__ __forceinline__ bool gv_bar_try(uint64_t *bar, unsigned parity) {
 }
 // Bounded: after GEMV_WAIT_PROBES failed probes the status word is set and the warp goes on (its results are then
 // wrong, the kernel still ends, ojas_b200_sync reports OJAS_B200_E_DEVICE).
-__device__ __forceinline__ void gv_bar_wait(uint64_t *bar, unsigned parity, unsigned *status) {
-    for (unsigned i = 0; i < GEMV_WAIT_PROBES; i++)
+// `dead` stays set once a wait of this warp has run out: its later waits are single probes, so a kernel that has lost a
+// copy ends quickly however many steps it has left.
+__device__ __forceinline__ void gv_bar_wait(uint64_t *bar, unsigned parity, unsigned *status, bool &dead) {
+    const unsigned limit = dead ? 1u : GEMV_WAIT_PROBES;
+    for (unsigned i = 0; i < limit; i++)
         if (gv_bar_try(bar, parity)) return;
-    atomicOr(status, 0x40u);
-    __threadfence_system();
+    if (!dead) {
+        dead = true;
+        atomicOr(status, 0x40u);
+        __threadfence_system();
+    }
 }
 
 // ---------------------------------------------------------------------------- activations in shared memory
@@ -429,13 +435,14 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
 #pragma unroll
     for (int m = 0; m < MT; m++) acc[m] = 0.0f;
     int k = k_first, sb = sb_first;
+    bool dead = false;
     const int unit = lane >> 3, r = lane & 7;
     const uint8_t *wl = ring + unit * TB + r * 16;
     for (int q = 0; q < nsteps; q++) {
         const unsigned use = ring_uses + (unsigned)q;
         const unsigned stg = use & (unsigned)(nst - 1);
         const int g = team + k * T;
-        gv_bar_wait(bar + stg, (use >> a.nst_log) & 1u, a.status);
+        gv_bar_wait(bar + stg, (use >> a.nst_log) & 1u, a.status, dead);
         if (4 * g + unit < nu) {
             const int row = (ub + 4 * g + unit) * 8 + r;
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
@@ -512,6 +519,8 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_grouped_kernel(co
         __syncthreads();
     }
 }
+
+#include "gemv_mma.cuh"
 
 // ---------------------------------------------------------------------------- quant_q8k
 __global__ void __launch_bounds__(256) quant_q8k_kernel(const float *x, int8_t *q, float *scales, int32_t *bsums,
@@ -655,6 +664,128 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
 #undef GEMV_CASE
 }
 
+// ---- the tensor-core batch kernel (gemv_mma.cuh): plan and launch
+static bool batch_plan(ojas_b200_ctx *ctx, int NT, size_t K, size_t N, GemvPlan &p) {
+    const size_t nsb = K / 256, units = tile_units(N), groups = (units + 3) / 4;
+    const size_t step = 4 * (size_t)tile_bytes(OJAS_B200_Q4_K), limit = (size_t)ctx->smem_optin;
+    p.grid = (int)(groups < (size_t)ctx->sm_count ? groups : (size_t)ctx->sm_count);
+    const size_t units_max = (units + p.grid - 1) / p.grid, ng = (units_max + 3) / 4;
+    const size_t fixed = ((batch_act_bytes(NT, K) + 15) & ~(size_t)15) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
+    const int w_hi = ctx->gemv_warps ? ctx->gemv_warps : GEMV_MAX_WARPS, n_hi = ctx->gemv_stages ? ctx->gemv_stages : 2;
+    size_t best_bytes = 0;
+    bool found = false;
+    for (int w = w_hi; w >= 1; w >>= 1) {
+        if ((size_t)w > ng * nsb && w > 1) continue;
+        size_t T = 1;
+        while (T * 2 <= (size_t)w && T * 2 <= ng) T *= 2;          // as many teams as the CTA has groups
+        const size_t S = (size_t)w / T, P = S < nsb ? S : nsb;
+        const size_t part = ng * P * (size_t)(NT / 8) * 1024;
+        const size_t per_warp = (((ng + T - 1) / T) * nsb + S - 1) / S;
+        for (int n = n_hi; n >= 1; n--) {
+            if (n == 3) continue;
+            const size_t nn = (size_t)n > per_warp ? ((size_t)1 << ilog2(per_warp)) : (size_t)n;
+            const size_t bytes = (size_t)w * nn * step, smem = bytes + fixed + part;
+            if (smem > limit) continue;
+            if (bytes > best_bytes) {
+                best_bytes = bytes;
+                found = true;
+                p.warps = w; p.nst_log = ilog2(nn); p.S_log = ilog2(S); p.T_log = ilog2(T); p.P = (int)P; p.own_x = 0; p.smem = smem;
+            }
+        }
+    }
+    return found;
+}
+
+// Launches the batch kernel over `E` expert groups (E = 1, counts = null: a plain batch of M rows).  NT (8, 16 or 32)
+// is the largest pass that fits; returns 1 when nothing fits.
+static int batch_launch(ojas_b200_ctx *ctx, BatchArgs a, int nt_want) {
+    for (int NT = nt_want; NT >= 8; NT >>= 1) {
+        GemvPlan p;
+        if (!batch_plan(ctx, NT, (size_t)a.K, (size_t)a.N, p)) continue;
+        const size_t units = tile_units((size_t)a.N);
+        a.nsb = a.K / 256;
+        a.units_base = (int)(units / p.grid);
+        a.units_rem = (int)(units % p.grid);
+        a.nst_log = p.nst_log; a.S_log = p.S_log; a.T_log = p.T_log; a.P = p.P;
+        a.status = ctx->dev_status;
+        auto go = [&](auto kernel) -> int {
+            if (p.smem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
+                if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemv_q4k_batch: shared memory %zu: %s", p.smem, cudaGetErrorString(e));
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)p.grid);
+            cfg.blockDim = dim3((unsigned)p.warps * 32);
+            cfg.dynamicSmemBytes = p.smem;
+            cfg.stream = ctx->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = ctx->pdl ? 1 : 0;
+            cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
+            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemv_q4k_batch: %s", cudaGetErrorString(e));
+            ctx->launches++;
+            return 0;
+        };
+        if (NT == 32) return go(gemv_q4k_batch_kernel<4>);
+        if (NT == 16) return go(gemv_q4k_batch_kernel<2>);
+        return go(gemv_q4k_batch_kernel<1>);
+    }
+    return 1;
+}
+
+// The expert FFN's matmuls on the experts kernel (gemv_mma.cuh): `nw` weight tensors (gate and up share the
+// activations) of E stacked experts [E * N, K], rows grouped by expert (counts / offsets on the device).  Returns 1
+// when the shape does not fit (the caller falls back to one grouped launch per expert).
+int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
+                          const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
+                          size_t rows_hint) {
+    if (N % OJAS_TILE_ROWS != 0 || E > (size_t)EXPERT_MAX_E) return 1;       // experts must start on a tile boundary
+    ExpertArgs a{};
+    a.w[0] = w0; a.w[1] = w1; a.y[0] = y0; a.y[1] = y1; a.nw = w1 ? 2 : 1;
+    a.expert_bytes = (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(OJAS_B200_Q4_K);
+    a.q = q; a.scales = scales; a.bsums = bsums; a.row_index = row_index; a.counts = counts; a.offsets = offsets;
+    a.E = (int)E; a.K = (int)K; a.N = (int)N; a.nsb = (int)(K / 256);
+    a.status = ctx->dev_status;
+    // rows per pass: enough for an expert of average load plus half again (a second pass re-reads the weights)
+    const size_t want = rows_hint + rows_hint / 2;
+    const int ntile = want > 24 ? 4 : want > 16 ? 3 : want > 8 ? 2 : 1;
+    const int warps = ctx->gemv_warps ? ctx->gemv_warps : GEMV_MAX_WARPS;
+    const size_t step = 2 * (size_t)tile_bytes(OJAS_B200_Q4_K), limit = (size_t)ctx->smem_optin;
+    for (int nt = ntile; nt >= 1; nt--) {
+        const size_t fixed = ((expert_act_bytes(8 * nt, K) + 15) & ~(size_t)15) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
+        int nst = ctx->gemv_stages ? ctx->gemv_stages : GEMV_MAX_STAGES;
+        while (nst >= 2 && fixed + (size_t)warps * nst * step > limit) nst--;
+        if (nst < 2) continue;
+        a.nst = nst;
+        const size_t smem = fixed + (size_t)warps * nst * step;
+        auto go = [&](auto kernel) -> int {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "moe_q4k_experts: shared memory %zu: %s", smem, cudaGetErrorString(e));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)ctx->sm_count);
+            cfg.blockDim = dim3((unsigned)warps * 32);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = ctx->stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = ctx->pdl ? 1 : 0;
+            e = cudaLaunchKernelEx(&cfg, kernel, a);
+            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch moe_q4k_experts: %s", cudaGetErrorString(e));
+            ctx->launches++;
+            return 0;
+        };
+        if (nt == 4) return go(moe_q4k_experts_kernel<4>);
+        if (nt == 3) return go(moe_q4k_experts_kernel<3>);
+        if (nt == 2) return go(moe_q4k_experts_kernel<2>);
+        return go(moe_q4k_experts_kernel<1>);
+    }
+    return 1;
+}
+
 static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w, const float *y, const float *bias,
                       size_t K, size_t N, size_t M) {
     if (!ctx) return OJAS_B200_E_ARG;
@@ -676,7 +807,8 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
 static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs &args, size_t M) {
     if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch) return false;
     const size_t values = M * (size_t)args.K;
-    if (values > OJAS_ACT_SCRATCH_VALUES || values < 16384) return false;
+    if (values > OJAS_ACT_SCRATCH_VALUES) return false;
+    if (values < 16384 && !(type == OJAS_B200_Q4_K && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
     int8_t *q = (int8_t *)ctx->act_scratch;
     float *scales = (float *)(q + OJAS_ACT_SCRATCH_VALUES);
     int32_t *bsums = (int32_t *)(scales + OJAS_ACT_SCRATCH_VALUES / 256);
@@ -693,6 +825,15 @@ static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvA
 
 static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args, size_t M) {
     if (gemv_prequantize(ctx, type, preq, args, M)) preq = true;
+    if (type == OJAS_B200_Q4_K && preq && M >= 3 && ctx->gemv_mma != 0 && !args.tp.step) {   // tensor-core batch kernel
+        BatchArgs b{};
+        b.w[0] = args.w; b.y[0] = args.y; b.nw = 1;
+        b.q = args.q; b.scales = args.scales; b.bsums = args.bsums;
+        b.bias = args.bias; b.form = args.form;
+        b.E = 1; b.M = (int)M; b.K = args.K; b.N = args.N;
+        const int rc = batch_launch(ctx, b, 8);
+        if (rc != 1) return rc;
+    }
     const size_t nsb = (size_t)args.K / 256;
     // the whole batch in one launch when its activations fit beside the ring, else in halves
     for (size_t cap = M; cap >= 1; cap = cap / 2) {

@@ -1,0 +1,544 @@
+// Small batches of activation rows against Q4_K weights on the integer tensor-core path (included by gemv.cu):
+// 3..8 rows of a decode batch, and the expert groups of the mixture-of-experts FFN (up to 32 rows per pass, every
+// expert and both of gate / up in ONE launch).  Same tiles, same ring of bulk-copied stages and same work split as
+// the single-row kernel; what changes is the inside of a step.
+//
+// A step is 32 weight rows x one super-block, worked as two tiles of 16 rows with
+//   mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32     (A = 16 rows x 32 nibbles as bytes, B = 32 int8 x 8 tokens)
+// one MMA per sub-block and token tile, so every accumulator is the exact int32 sub-block dot of dot_q4k
+// (crates/ojas-cpu/src/cpu_math.rs:609-635) for 16 rows x 8 tokens at once.  The k order of an MMA is free as long as
+// A and B agree: lane (g, q) supplies the eight weights 8q .. 8q+7 of the sub-block, which are the low (or high)
+// nibbles of eight CONTIGUOUS bytes of row g's tile (one 8-byte load, no shuffling), against activations
+// 8q .. 8q+7 of token g (one 8-byte load from a token-major copy padded so that the loads do not conflict).
+// High nibbles stay in place (x16) and the accumulator is shifted down afterwards.  The mins term
+// sum_j m_j * bsum_j is two more MMAs per super-block (A = the eight 6-bit mins as bytes, B = the low / high bytes
+// of the tokens' block sums).  Scales and mins are decoded to bytes once per row and super-block with word-wide
+// operations.
+//
+// The launch walks JOBS: (expert, pass of up to NT of its rows, weight tensor).  Row counts and offsets are read on
+// the device (capture-safe whatever the routing), an expert without rows costs nothing, and the weight prefetch runs
+// across job boundaries while the CTA combines the finished job and stages the next activations.
+#pragma once
+
+struct BatchArgs {
+    const uint8_t *w[2];          // weight tensors (gate, up: they share the activations), experts stacked along N
+    float *y[2];                  // outputs [positions, N], one per weight tensor
+    int nw;
+    size_t expert_bytes;          // distance between consecutive experts in a weight tensor
+    const int8_t *q;              // quantized activation rows [rows, K] (ojas_b200_quant_q8k form)
+    const float *scales;          // [rows, K/256]
+    const int32_t *bsums;         // [rows, K/32]
+    const int *row_index;         // source row of sorted position p (null: p itself)
+    const int *counts, *offsets;  // per expert, on the device (null: one group of M rows at position 0)
+    const float *bias;
+    unsigned *status;
+    int form;
+    int E, M, K, N, nsb;
+    int units_base, units_rem;    // CTA b owns units_base (+1 if b < units_rem) 8-row units of every expert
+    int nst_log, S_log, T_log, P;
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct BatchJob {
+    int e, mb, wsel;              // expert, first row of the pass inside the expert's group, weight tensor
+    int count, off;               // rows of the expert and position of its first row
+};
+
+template <int NT>
+__device__ __forceinline__ bool batch_job_first(const BatchArgs &a, BatchJob &j) {
+    j.e = -1; j.mb = 0; j.wsel = 0; j.count = 0; j.off = 0;
+    for (int e = 0; e < a.E; e++) {
+        const int c = a.counts ? __ldg(a.counts + e) : a.M;
+        if (c > 0) { j.e = e; j.count = c; j.off = a.offsets ? __ldg(a.offsets + e) : 0; return true; }
+    }
+    return false;
+}
+template <int NT>
+__device__ __forceinline__ bool batch_job_next(const BatchArgs &a, BatchJob &j) {
+    if (j.wsel + 1 < a.nw) { j.wsel++; return true; }
+    j.wsel = 0;
+    if (j.mb + NT < j.count) { j.mb += NT; return true; }
+    j.mb = 0;
+    for (int e = j.e + 1; e < a.E; e++) {
+        const int c = a.counts ? __ldg(a.counts + e) : a.M;
+        if (c > 0) { j.e = e; j.count = c; j.off = a.offsets ? __ldg(a.offsets + e) : 0; return true; }
+    }
+    return false;
+}
+
+// Shared-memory bytes of the activations of one pass: NT rows of K + 32 int8 (the pad spreads the eight tokens of a
+// load over the banks), then per row and super-block 16 bytes of block sums (low bytes, high bytes) and the scale.
+__host__ __device__ inline size_t batch_act_bytes(int NT, size_t K) { return (size_t)NT * (K + 32) + (size_t)NT * (K / 256) * 20; }
+
+template <int NTILE>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_q4k_batch_kernel(const BatchArgs a) {
+    constexpr int NT = 8 * NTILE, TB = tile_bytes(OJAS_B200_Q4_K), STEP = 4 * TB;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g8 = lane >> 2, q4 = lane & 3;
+    const int nsb = a.nsb, P = a.P, K = a.K, Kpad = K + 32;
+    const int nst = 1 << a.nst_log, S = 1 << a.S_log, T = 1 << a.T_log;
+    uint8_t *ring = smem + (size_t)warp * nst * STEP;
+    uint8_t *xq = smem + (size_t)warps * nst * STEP;               // [NT][Kpad]
+    uint8_t *bsb = xq + (size_t)NT * Kpad;                         // [NT][nsb][16]
+    float *sx = reinterpret_cast<float *>(bsb + (size_t)NT * nsb * 16);   // [NT][nsb]
+    uint64_t *bar = reinterpret_cast<uint64_t *>(xq + ((batch_act_bytes(NT, (size_t)K) + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
+    float *part = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(xq + ((batch_act_bytes(NT, (size_t)K) + 15) & ~(size_t)15)) +
+                                            GEMV_MAX_WARPS * GEMV_MAX_STAGES);
+
+    const int b = blockIdx.x;
+    const int ub = b * a.units_base + (b < a.units_rem ? b : a.units_rem);
+    const int nu = a.units_base + (b < a.units_rem ? 1 : 0);
+    const int ng = (nu + 3) >> 2;
+    const int team = warp >> a.S_log, wi = warp & (S - 1);
+    const int tg = team < ng ? (ng - team + T - 1) >> a.T_log : 0;
+    const int n = tg * nsb;
+    const int nsteps = wi < n ? (n - wi + S - 1) >> a.S_log : 0;   // steps of this warp in every job
+    int k_first = 0, sb_first = wi;
+    while (sb_first >= nsb) { sb_first -= nsb; k_first++; }
+
+    if (lane == 0) {
+        for (int i = 0; i < nst; i++) gv_bar_init(bar + i);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    grid_dependency_wait();                                        // counts, offsets and activations come from kernels before this one
+
+    // issue cursor (lane 0 runs ahead of the computation by up to `nst` steps, across job boundaries)
+    BatchJob ji;
+    bool more_i = batch_job_first<NT>(a, ji) && nsteps > 0;
+    int ik = k_first, isb = sb_first, ileft = nsteps;
+    unsigned issued = 0;
+    auto issue = [&]() -> bool {
+        if (!more_i) return false;
+        const int g = team + ik * T;
+        const int cnt = (nu - 4 * g) < 4 ? (nu - 4 * g) : 4;
+        const uint8_t *src = a.w[ji.wsel] + (size_t)ji.e * a.expert_bytes + ((size_t)(ub + 4 * g) * nsb + isb) * TB;
+        const unsigned stg = issued & (unsigned)(nst - 1);
+        gv_bar_expect(bar + stg, (unsigned)(cnt * TB));
+        for (int t = 0; t < cnt; t++) gv_bulk_load(ring + stg * STEP + t * TB, src + (size_t)t * nsb * TB, TB, bar + stg);
+        issued++;
+        isb += S;
+        while (isb >= nsb) { isb -= nsb; ik++; }
+        if (--ileft == 0) {
+            more_i = batch_job_next<NT>(a, ji);
+            ik = k_first; isb = sb_first; ileft = nsteps;
+        }
+        return true;
+    };
+    if (lane == 0)
+        for (int i = 0; i < nst; i++) issue();
+    grid_launch_dependents();
+
+    BatchJob jc;
+    bool dead = false;
+    bool more = batch_job_first<NT>(a, jc);
+    int staged_e = -1, staged_mb = -1;
+    unsigned uses = 0;
+    while (more) {
+        const int m_here = jc.count - jc.mb < NT ? jc.count - jc.mb : NT;
+        if (staged_e != jc.e || staged_mb != jc.mb) {
+            // ---- the pass's activation rows: values token-major (padded), block sums as bytes, scales
+            __syncthreads();
+            const int units = K >> 4;
+            for (int m = 0; m < NT; m++) {
+                uint4 *dst = reinterpret_cast<uint4 *>(xq + (size_t)m * Kpad);
+                if (m < m_here) {
+                    const int pos = jc.off + jc.mb + m;
+                    const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
+                    const uint4 *qsrc = reinterpret_cast<const uint4 *>(a.q + (size_t)srow * K);
+                    for (int un = threadIdx.x; un < units; un += blockDim.x) dst[un] = __ldg(qsrc + un);
+                    for (int i = threadIdx.x; i < nsb * 8; i += blockDim.x) {
+                        const int t = __ldg(a.bsums + (size_t)srow * nsb * 8 + i);
+                        uint8_t *o = bsb + ((size_t)m * nsb + (i >> 3)) * 16;
+                        o[i & 7] = (uint8_t)(t & 63);
+                        o[8 + (i & 7)] = (uint8_t)((t >> 6) & 0xff);
+                    }
+                    for (int sb = threadIdx.x; sb < nsb; sb += blockDim.x) sx[m * nsb + sb] = __ldg(a.scales + (size_t)srow * nsb + sb);
+                } else {
+                    for (int un = threadIdx.x; un < units; un += blockDim.x) dst[un] = make_uint4(0u, 0u, 0u, 0u);
+                    for (int i = threadIdx.x; i < nsb * 4; i += blockDim.x) reinterpret_cast<uint32_t *>(bsb + (size_t)m * nsb * 16)[i] = 0u;
+                    for (int sb = threadIdx.x; sb < nsb; sb += blockDim.x) sx[m * nsb + sb] = 0.0f;
+                }
+            }
+            staged_e = jc.e; staged_mb = jc.mb;
+            __syncthreads();
+        }
+
+        // ---- this warp's steps of the job
+        float acc[2][NTILE][4];
+#pragma unroll
+        for (int rt = 0; rt < 2; rt++)
+#pragma unroll
+            for (int t = 0; t < NTILE; t++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[rt][t][i] = 0.0f;
+        int k = k_first, sb = sb_first;
+        for (int s = 0; s < nsteps; s++, uses++) {
+            const unsigned stg = uses & (unsigned)(nst - 1);
+            const int g = team + k * T;
+            gv_bar_wait(bar + stg, (uses >> a.nst_log) & 1u, a.status, dead);
+            const uint8_t *st = ring + stg * STEP;
+#pragma unroll
+            for (int rt = 0; rt < 2; rt++) {
+                if (4 * g + 2 * rt >= nu) continue;                 // no unit under this row tile (rows past the CTA's range)
+                const bool second = 4 * g + 2 * rt + 1 < nu;        // the tile's rows 8..15 exist
+                const uint8_t *t0 = st + (2 * rt) * TB + g8 * 16, *t1 = second ? t0 + TB : t0;
+                // scales and mins of the two rows as bytes (get_scale_min_k4, crates/ojas-formats/src/gguf.rs:1132-1140)
+                const uint4 H0 = *reinterpret_cast<const uint4 *>(t0 + 8 * 128), H1 = *reinterpret_cast<const uint4 *>(t1 + 8 * 128);
+                const uint32_t s0[2] = {H0.y & 0x3f3f3f3fu, (H0.w & 0x0f0f0f0fu) | ((H0.y >> 2) & 0x30303030u)};
+                const uint32_t s1[2] = {H1.y & 0x3f3f3f3fu, (H1.w & 0x0f0f0f0fu) | ((H1.y >> 2) & 0x30303030u)};
+                const uint32_t m0[2] = {H0.z & 0x3f3f3f3fu, ((H0.w >> 4) & 0x0f0f0f0fu) | ((H0.z >> 2) & 0x30303030u)};
+                const uint32_t m1[2] = {H1.z & 0x3f3f3f3fu, ((H1.w >> 4) & 0x0f0f0f0fu) | ((H1.z >> 2) & 0x30303030u)};
+                int isum[NTILE][4];
+#pragma unroll
+                for (int t = 0; t < NTILE; t++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) isum[t][i] = 0;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    // eight contiguous bytes of each row: low nibbles = weights 8q .. 8q+7 of sub-block 2c, high = of 2c+1
+                    const uint2 w0 = *reinterpret_cast<const uint2 *>(t0 + (2 * c + (q4 >> 1)) * 128 + (q4 & 1) * 8);
+                    uint2 w1 = *reinterpret_cast<const uint2 *>(t1 + (2 * c + (q4 >> 1)) * 128 + (q4 & 1) * 8);
+                    if (!second) w1 = make_uint2(0u, 0u);
+                    const uint32_t alo[4] = {w0.x & 0x0f0f0f0fu, w1.x & 0x0f0f0f0fu, w0.y & 0x0f0f0f0fu, w1.y & 0x0f0f0f0fu};
+                    const uint32_t ahi[4] = {w0.x & 0xf0f0f0f0u, w1.x & 0xf0f0f0f0u, w0.y & 0xf0f0f0f0u, w1.y & 0xf0f0f0f0u};
+                    const int sA0 = (int)__byte_perm(s0[c >> 1], 0, 0x4440 + 2 * (c & 1)), sB0 = (int)__byte_perm(s0[c >> 1], 0, 0x4441 + 2 * (c & 1));
+                    const int sA1 = (int)__byte_perm(s1[c >> 1], 0, 0x4440 + 2 * (c & 1)), sB1 = (int)__byte_perm(s1[c >> 1], 0, 0x4441 + 2 * (c & 1));
+#pragma unroll
+                    for (int t = 0; t < NTILE; t++) {
+                        const uint8_t *xr = xq + (size_t)(t * 8 + g8) * Kpad + sb * 256 + 64 * c + 8 * q4;
+                        const uint2 xa = *reinterpret_cast<const uint2 *>(xr), xb = *reinterpret_cast<const uint2 *>(xr + 32);
+                        int dlo[4] = {0, 0, 0, 0}, dhi[4] = {0, 0, 0, 0};
+                        mma_u8s8(dlo, alo, xa.x, xa.y);
+                        mma_u8s8(dhi, ahi, xb.x, xb.y);
+                        isum[t][0] += sA0 * dlo[0] + sB0 * (dhi[0] >> 4);
+                        isum[t][1] += sA0 * dlo[1] + sB0 * (dhi[1] >> 4);
+                        isum[t][2] += sA1 * dlo[2] + sB1 * (dhi[2] >> 4);
+                        isum[t][3] += sA1 * dlo[3] + sB1 * (dhi[3] >> 4);
+                    }
+                }
+                // mins: A = the eight mins of each row as bytes (lane q = 0 holds mins 0..3, q = 1 mins 4..7), B = the
+                // tokens' block sums, low bytes and high bytes
+                const uint32_t am[4] = {q4 < 2 ? m0[q4] : 0u, (q4 < 2 && second) ? m1[q4] : 0u, 0u, 0u};
+                const float d0 = f16_bits_to_f32(H0.x), dm0 = f16_bits_to_f32(H0.x >> 16);
+                const float d1 = second ? f16_bits_to_f32(H1.x) : 0.0f, dm1 = second ? f16_bits_to_f32(H1.x >> 16) : 0.0f;
+#pragma unroll
+                for (int t = 0; t < NTILE; t++) {
+                    const uint8_t *bp = bsb + ((size_t)(t * 8 + g8) * nsb + sb) * 16;
+                    const uint32_t blo = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 4 * q4) : 0u;
+                    const uint32_t bhi = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 8 + 4 * q4) : 0u;
+                    int ml[4] = {0, 0, 0, 0}, mh[4] = {0, 0, 0, 0};
+                    mma_u8s8(ml, am, blo, 0u);
+                    mma_u8s8(mh, am, bhi, 0u);
+                    const float sx0 = sx[(t * 8 + 2 * q4) * nsb + sb], sx1 = sx[(t * 8 + 2 * q4 + 1) * nsb + sb];
+                    acc[rt][t][0] += sx0 * (d0 * (float)isum[t][0] - dm0 * (float)(ml[0] + 64 * mh[0]));
+                    acc[rt][t][1] += sx1 * (d0 * (float)isum[t][1] - dm0 * (float)(ml[1] + 64 * mh[1]));
+                    acc[rt][t][2] += sx0 * (d1 * (float)isum[t][2] - dm1 * (float)(ml[2] + 64 * mh[2]));
+                    acc[rt][t][3] += sx1 * (d1 * (float)isum[t][3] - dm1 * (float)(ml[3] + 64 * mh[3]));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue();
+            }
+            const int slot = sb & (S - 1), k_now = k;
+            sb += S;
+            bool flush = s + 1 == nsteps;
+            while (sb >= nsb) { sb -= nsb; k++; flush = true; }
+            if (flush) {
+#pragma unroll
+                for (int rt = 0; rt < 2; rt++)
+#pragma unroll
+                    for (int t = 0; t < NTILE; t++) {
+                        float4 *o = reinterpret_cast<float4 *>(part) + ((((size_t)(team + k_now * T) * P + slot) * 2 + rt) * NTILE + t) * 32 + lane;
+                        *o = make_float4(acc[rt][t][0], acc[rt][t][1], acc[rt][t][2], acc[rt][t][3]);
+                        acc[rt][t][0] = acc[rt][t][1] = acc[rt][t][2] = acc[rt][t][3] = 0.0f;
+                    }
+            }
+        }
+        __syncthreads();
+        // ---- combine the warps' partial sums of the job and store: item = (group, row tile, token tile, lane)
+        float *yout = a.y[jc.wsel];
+        for (int item = threadIdx.x; item < ng * 2 * NTILE * 32; item += blockDim.x) {
+            const int ln = item & 31, t = (item >> 5) % NTILE, rt = ((item >> 5) / NTILE) & 1, gl = (item >> 5) / (2 * NTILE);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int p = 0; p < P; p++) {
+                const float4 u = reinterpret_cast<const float4 *>(part)[((((size_t)gl * P + p) * 2 + rt) * NTILE + t) * 32 + ln];
+                v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+            }
+            const int lg = ln >> 2, lq = ln & 3;
+            const float vals[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int unit = 4 * gl + 2 * rt + (i >> 1), tok = t * 8 + 2 * lq + (i & 1);
+                const int row = (ub + unit) * 8 + lg;
+                if (unit < nu && row < a.N && tok < m_here)
+                    store_form(yout + (size_t)(jc.off + jc.mb + tok) * a.N + row, vals[i], a.form, a.bias, row);
+            }
+        }
+        more = batch_job_next<NT>(a, jc);
+        if (more && staged_e == jc.e && staged_mb == jc.mb) __syncthreads();   // (a new pass syncs before it stages)
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// The expert FFN's matmuls in one launch.  Work is the list of 16-row tiles of every (expert with rows, weight
+// tensor) pair, expert-major; CTA b takes the b-th equal share of that list, so its tiles belong to one expert (two
+// at a boundary) and the expert's activation rows are staged once.  A WARP OWNS A TILE for the whole K range: its
+// sums stay in registers and go straight to y, so nothing is exchanged between warps and the only CTA-wide
+// barriers are those around the staging of activations.  Activations are staged per K segment of up to 4096 values
+// (all NT rows of the pass), so long rows (the down projection) fit beside a deep weight ring; a step is one
+// super-block of the tile (two 8-row tiles of the weight, 2304 bytes, two bulk copies) and the ring prefetch of a
+// warp runs ahead across segments, tiles and experts.
+constexpr int EXPERT_KSEG = 4096;
+constexpr int EXPERT_MAX_E = 64;
+
+struct ExpertArgs {
+    const uint8_t *w[2];
+    float *y[2];
+    int nw;
+    size_t expert_bytes;
+    const int8_t *q;
+    const float *scales;
+    const int32_t *bsums;
+    const int *row_index;
+    const int *counts, *offsets;
+    unsigned *status;
+    int E, K, N, nsb, nst;
+};
+
+__host__ __device__ inline size_t expert_act_bytes(int NT, size_t K) {
+    const size_t kseg = K < (size_t)EXPERT_KSEG ? K : (size_t)EXPERT_KSEG;
+    return (size_t)NT * (kseg + 32) + (size_t)NT * (kseg / 256) * 20;
+}
+
+// One 16-row tile x one super-block x up to NTILE token tiles.  t0 / t1: this lane's row (g8) in the tile's two
+// 8-row weight tiles; xq, bsb, sx: the staged activations of the segment, `sbl` the super-block inside the segment.
+template <int NTILE>
+__device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *t1, bool second, const uint8_t *xq, int xstride, const uint8_t *bsb,
+                                              const float *sx, int nsbseg, int sbl, int g8, int q4, int ntile, float (&acc)[NTILE][4]) {
+    const uint4 H0 = *reinterpret_cast<const uint4 *>(t0 + 8 * 128), H1 = *reinterpret_cast<const uint4 *>(t1 + 8 * 128);
+    const uint32_t s0[2] = {H0.y & 0x3f3f3f3fu, (H0.w & 0x0f0f0f0fu) | ((H0.y >> 2) & 0x30303030u)};
+    const uint32_t s1[2] = {H1.y & 0x3f3f3f3fu, (H1.w & 0x0f0f0f0fu) | ((H1.y >> 2) & 0x30303030u)};
+    const uint32_t m0[2] = {H0.z & 0x3f3f3f3fu, ((H0.w >> 4) & 0x0f0f0f0fu) | ((H0.z >> 2) & 0x30303030u)};
+    const uint32_t m1[2] = {H1.z & 0x3f3f3f3fu, ((H1.w >> 4) & 0x0f0f0f0fu) | ((H1.z >> 2) & 0x30303030u)};
+    int isum[NTILE][4];
+#pragma unroll
+    for (int t = 0; t < NTILE; t++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) isum[t][i] = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint2 w0 = *reinterpret_cast<const uint2 *>(t0 + (2 * c + (q4 >> 1)) * 128 + (q4 & 1) * 8);
+        uint2 w1 = *reinterpret_cast<const uint2 *>(t1 + (2 * c + (q4 >> 1)) * 128 + (q4 & 1) * 8);
+        if (!second) w1 = make_uint2(0u, 0u);
+        const uint32_t alo[4] = {w0.x & 0x0f0f0f0fu, w1.x & 0x0f0f0f0fu, w0.y & 0x0f0f0f0fu, w1.y & 0x0f0f0f0fu};
+        const uint32_t ahi[4] = {w0.x & 0xf0f0f0f0u, w1.x & 0xf0f0f0f0u, w0.y & 0xf0f0f0f0u, w1.y & 0xf0f0f0f0u};
+        const int sA0 = (int)__byte_perm(s0[c >> 1], 0, 0x4440 + 2 * (c & 1)), sB0 = (int)__byte_perm(s0[c >> 1], 0, 0x4441 + 2 * (c & 1));
+        const int sA1 = (int)__byte_perm(s1[c >> 1], 0, 0x4440 + 2 * (c & 1)), sB1 = (int)__byte_perm(s1[c >> 1], 0, 0x4441 + 2 * (c & 1));
+#pragma unroll
+        for (int t = 0; t < NTILE; t++) {
+            if (t < ntile) {
+                const uint8_t *xr = xq + (size_t)(t * 8 + g8) * xstride + sbl * 256 + 64 * c + 8 * q4;
+                const uint2 xa = *reinterpret_cast<const uint2 *>(xr), xb = *reinterpret_cast<const uint2 *>(xr + 32);
+                int dlo[4] = {0, 0, 0, 0}, dhi[4] = {0, 0, 0, 0};
+                mma_u8s8(dlo, alo, xa.x, xa.y);
+                mma_u8s8(dhi, ahi, xb.x, xb.y);
+                isum[t][0] += sA0 * dlo[0] + sB0 * (dhi[0] >> 4);
+                isum[t][1] += sA0 * dlo[1] + sB0 * (dhi[1] >> 4);
+                isum[t][2] += sA1 * dlo[2] + sB1 * (dhi[2] >> 4);
+                isum[t][3] += sA1 * dlo[3] + sB1 * (dhi[3] >> 4);
+            }
+        }
+    }
+    const uint32_t am[4] = {q4 < 2 ? m0[q4] : 0u, (q4 < 2 && second) ? m1[q4] : 0u, 0u, 0u};
+    const float d0 = f16_bits_to_f32(H0.x), dm0 = f16_bits_to_f32(H0.x >> 16);
+    const float d1 = second ? f16_bits_to_f32(H1.x) : 0.0f, dm1 = second ? f16_bits_to_f32(H1.x >> 16) : 0.0f;
+#pragma unroll
+    for (int t = 0; t < NTILE; t++) {
+        if (t < ntile) {
+            const uint8_t *bp = bsb + ((size_t)(t * 8 + g8) * nsbseg + sbl) * 16;
+            const uint32_t blo = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 4 * q4) : 0u;
+            const uint32_t bhi = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 8 + 4 * q4) : 0u;
+            int ml[4] = {0, 0, 0, 0}, mh[4] = {0, 0, 0, 0};
+            mma_u8s8(ml, am, blo, 0u);
+            mma_u8s8(mh, am, bhi, 0u);
+            const float sx0 = sx[(t * 8 + 2 * q4) * nsbseg + sbl], sx1 = sx[(t * 8 + 2 * q4 + 1) * nsbseg + sbl];
+            acc[t][0] += sx0 * (d0 * (float)isum[t][0] - dm0 * (float)(ml[0] + 64 * mh[0]));
+            acc[t][1] += sx1 * (d0 * (float)isum[t][1] - dm0 * (float)(ml[1] + 64 * mh[1]));
+            acc[t][2] += sx0 * (d1 * (float)isum[t][2] - dm1 * (float)(ml[2] + 64 * mh[2]));
+            acc[t][3] += sx1 * (d1 * (float)isum[t][3] - dm1 * (float)(ml[3] + 64 * mh[3]));
+        }
+    }
+}
+
+template <int NTILE>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_q4k_experts_kernel(const ExpertArgs a) {
+    constexpr int NT = 8 * NTILE, TB = tile_bytes(OJAS_B200_Q4_K), STEP = 2 * TB;
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int act_e[EXPERT_MAX_E], act_n;                    // experts that have rows, in order
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g8 = lane >> 2, q4 = lane & 3;
+    const int nsb = a.nsb, K = a.K, nst = a.nst;
+    const int kseg = K < EXPERT_KSEG ? K : EXPERT_KSEG, nsbseg = kseg >> 8, xstride = kseg + 32;
+    const int nseg = (K + kseg - 1) / kseg;
+    uint8_t *ring = smem + (size_t)warp * nst * STEP;
+    uint8_t *xq = smem + (size_t)warps * nst * STEP;
+    uint8_t *bsb = xq + (size_t)NT * xstride;
+    float *sx = reinterpret_cast<float *>(bsb + (size_t)NT * nsbseg * 16);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(xq + ((expert_act_bytes(NT, (size_t)K) + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
+
+    if (lane == 0) {
+        for (int i = 0; i < nst; i++) gv_bar_init(bar + i);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    grid_dependency_wait();                                        // counts, offsets and activations come from kernels before this one
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int e = 0; e < a.E; e++)
+            if (__ldg(a.counts + e) > 0) act_e[n++] = e;
+        act_n = n;
+    }
+    __syncthreads();
+    grid_launch_dependents();
+    const int tpe = (a.N + 15) >> 4;                               // 16-row tiles per (expert, tensor)
+    const unsigned total = (unsigned)act_n * (unsigned)a.nw * (unsigned)tpe;
+    const unsigned c0 = (unsigned)(((unsigned long long)total * blockIdx.x) / gridDim.x);
+    const unsigned c1 = (unsigned)(((unsigned long long)total * (blockIdx.x + 1)) / gridDim.x);
+    const int units_total = (a.N + 7) >> 3;
+
+    // ---- issue side (lane 0): the warp's steps in order: for every pair segment of the CTA's range, for every pass
+    // of the expert's rows, tiles lo + warp, lo + warp + warps, ..., super-blocks 0 .. nsb - 1
+    struct Cursor { unsigned seg_lo, seg_hi, tile; int pair, mb, count, sb; bool live; };
+    auto seg_open = [&](Cursor &c, unsigned from) {               // the pair segment that starts at global tile index `from`
+        c.live = from < c1;
+        if (!c.live) return;
+        c.pair = (int)(from / (unsigned)tpe);
+        const unsigned pair_end = (unsigned)(c.pair + 1) * (unsigned)tpe;
+        c.seg_lo = from; c.seg_hi = pair_end < c1 ? pair_end : c1;
+        c.count = __ldg(a.counts + act_e[c.pair / a.nw]);
+        c.mb = 0;
+        c.tile = c.seg_lo + (unsigned)warp;
+        c.sb = 0;
+    };
+    auto cur_fix = [&](Cursor &c) {                               // skip to the next (pass, segment) when this warp has no tile left in this one
+        while (c.live && c.tile >= c.seg_hi) {
+            if (c.mb + NT < c.count) { c.mb += NT; c.tile = c.seg_lo + (unsigned)warp; c.sb = 0; }
+            else seg_open(c, c.seg_hi);
+        }
+    };
+    Cursor ci;
+    seg_open(ci, c0);
+    cur_fix(ci);
+    int istg = 0;
+    auto issue = [&]() {
+        if (!ci.live) return;
+        const int e = act_e[ci.pair / a.nw], wsel = ci.pair % a.nw;
+        const int tl = (int)(ci.tile - (unsigned)ci.pair * (unsigned)tpe);          // tile inside the expert
+        const int cnt = units_total - 2 * tl < 2 ? units_total - 2 * tl : 2;
+        const uint8_t *src = a.w[wsel] + (size_t)e * a.expert_bytes + ((size_t)(2 * tl) * nsb + ci.sb) * TB;
+        gv_bar_expect(bar + istg, (unsigned)(cnt * TB));
+        for (int t = 0; t < cnt; t++) gv_bulk_load(ring + istg * STEP + t * TB, src + (size_t)t * nsb * TB, TB, bar + istg);
+        if (++istg == nst) istg = 0;
+        if (++ci.sb == nsb) { ci.sb = 0; ci.tile += (unsigned)warps; cur_fix(ci); }
+    };
+    if (lane == 0)
+        for (int i = 0; i < nst; i++) issue();
+
+    // ---- compute side: all warps walk the CTA's segments and passes together (the staging is CTA-wide)
+    int cstg = 0;
+    unsigned cphase = 0;
+    bool dead = false;
+    for (unsigned from = c0; from < c1;) {
+        const int pair = (int)(from / (unsigned)tpe);
+        const unsigned pair_end = (unsigned)(pair + 1) * (unsigned)tpe, seg_hi = pair_end < c1 ? pair_end : c1;
+        const int e = act_e[pair / a.nw], wsel = pair % a.nw;
+        const int count = __ldg(a.counts + e), off = __ldg(a.offsets + e);
+        const int rounds = (int)((seg_hi - from + (unsigned)warps - 1) / (unsigned)warps);
+        for (int mb = 0; mb < count; mb += NT) {
+            const int m_here = count - mb < NT ? count - mb : NT, ntile = (m_here + 7) >> 3;
+            for (int rd = 0; rd < rounds; rd++) {
+                const unsigned tile = from + (unsigned)(rd * warps + warp);
+                const bool mine = tile < seg_hi;
+                const int tl = (int)(tile - (unsigned)pair * (unsigned)tpe);
+                const bool second = 2 * tl + 1 < units_total;
+                float acc[NTILE][4];
+#pragma unroll
+                for (int t = 0; t < NTILE; t++) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+                for (int ks = 0; ks < nseg; ks++) {
+                    const int sb0 = ks * nsbseg, nsb_here = nsb - sb0 < nsbseg ? nsb - sb0 : nsbseg;
+                    // ---- stage the pass's rows, K segment ks (skipped when it is what is staged already: one segment, same rows)
+                    if (nseg > 1 || rd == 0) {
+                        __syncthreads();
+                        const int units = nsb_here * 16;
+                        for (int idx = threadIdx.x; idx < NT * units; idx += blockDim.x) {
+                            const int m = idx / units, un = idx - m * units;
+                            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                            if (m < m_here) {
+                                const int pos = off + mb + m;
+                                const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
+                                v = __ldg(reinterpret_cast<const uint4 *>(a.q + (size_t)srow * K + (size_t)sb0 * 256) + un);
+                            }
+                            reinterpret_cast<uint4 *>(xq + (size_t)m * xstride)[un] = v;
+                        }
+                        for (int idx = threadIdx.x; idx < NT * nsb_here * 8; idx += blockDim.x) {
+                            const int m = idx / (nsb_here * 8), i = idx - m * (nsb_here * 8);
+                            int t = 0;
+                            if (m < m_here) {
+                                const int pos = off + mb + m;
+                                const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
+                                t = __ldg(a.bsums + ((size_t)srow * nsb + sb0) * 8 + i);
+                            }
+                            uint8_t *o = bsb + ((size_t)m * nsbseg + (i >> 3)) * 16;
+                            o[i & 7] = (uint8_t)(t & 63);
+                            o[8 + (i & 7)] = (uint8_t)((t >> 6) & 0xff);
+                        }
+                        for (int idx = threadIdx.x; idx < NT * nsb_here; idx += blockDim.x) {
+                            const int m = idx / nsb_here, sbl = idx - m * nsb_here;
+                            float v = 0.0f;
+                            if (m < m_here) {
+                                const int pos = off + mb + m;
+                                const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
+                                v = __ldg(a.scales + (size_t)srow * nsb + sb0 + sbl);
+                            }
+                            sx[m * nsbseg + sbl] = v;
+                        }
+                        __syncthreads();
+                    }
+                    if (mine) {
+                        for (int sbl = 0; sbl < nsb_here; sbl++) {
+                            gv_bar_wait(bar + cstg, cphase, a.status, dead);
+                            const uint8_t *t0 = ring + cstg * STEP + g8 * 16, *t1 = second ? t0 + TB : t0;
+                            mma_tile_step<NTILE>(t0, t1, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
+                            __syncwarp();
+                            if (lane == 0) {
+                                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                                issue();
+                            }
+                            if (++cstg == nst) { cstg = 0; cphase ^= 1u; }
+                        }
+                    }
+                }
+                if (mine) {
+                    float *yout = a.y[wsel];
+#pragma unroll
+                    for (int t = 0; t < NTILE; t++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int tok = t * 8 + 2 * q4 + (i & 1), row = tl * 16 + (i >> 1) * 8 + g8;
+                            if (tok < m_here && row < a.N) yout[(size_t)(off + mb + tok) * a.N + row] = acc[t][i];
+                        }
+                }
+            }
+        }
+        from = seg_hi;
+    }
+}

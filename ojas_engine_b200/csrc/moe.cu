@@ -273,20 +273,32 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     if (rc) return rc;
     moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
     OJAS_LAUNCH_CHECK(ctx, "moe_group");
-    for (size_t e = 0; e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
-        rc = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wg, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
-                               w.counts + e, w.offsets + e, w.g, d, ffn);
-        if (rc) return rc;
-        rc = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wu, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+    // gate and up: one launch of the tensor-core batch kernel over every expert and both tensors (Q4_K); otherwise one
+    // grouped launch per expert and tensor
+    rc = 1;
+    if (type_gu == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
+        rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts, w.offsets, E, d, ffn,
+                                   (A + E - 1) / E);
+    if (rc < 0) return rc;
+    for (size_t e = 0; rc == 1 && e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
+        int r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wg, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+                                   w.counts + e, w.offsets + e, w.g, d, ffn);
+        if (r2) return r2;
+        r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wu, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
                                w.counts + e, w.offsets + e, w.u, d, ffn);
-        if (rc) return rc;
+        if (r2) return r2;
     }
     rc = ojas_silu_mul_q8k(ctx, w.g, w.u, w.aq, w.as, w.ab, A, ffn);
     if (rc) return rc;
-    for (size_t e = 0; e < E; e++) {   // down of expert e over its (contiguous, sorted) rows
-        rc = ojas_gemv_grouped(ctx, type_d, weight_rows_at(type_d, wd, ffn, e * d), w.aq, w.as, w.ab, nullptr,
-                               w.counts + e, w.offsets + e, w.yd, ffn, d);
-        if (rc) return rc;
+    rc = 1;
+    if (type_d == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
+        rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wd, nullptr, w.yd, nullptr, w.aq, w.as, w.ab, nullptr, w.counts, w.offsets, E, ffn, d,
+                                   (A + E - 1) / E);
+    if (rc < 0) return rc;
+    for (size_t e = 0; rc == 1 && e < E; e++) {   // down of expert e over its (contiguous, sorted) rows
+        const int r2 = ojas_gemv_grouped(ctx, type_d, weight_rows_at(type_d, wd, ffn, e * d), w.aq, w.as, w.ab, nullptr,
+                                         w.counts + e, w.offsets + e, w.yd, ffn, d);
+        if (r2) return r2;
     }
     const dim3 grid((unsigned)((d + 255) / 256), (unsigned)M);
     moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0);

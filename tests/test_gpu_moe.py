@@ -126,7 +126,14 @@ def test_prefill_sized_batches_on_grouped_gemms(gpu, t_gu, t_d):
 def test_both_expert_paths(gpu):
     """The same small batch through the grouped-GEMV form (default, exact integer block dots) and, forced, through
     the grouped-GEMM form."""
-    assert _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13) < 1e-5
+    # exact integer block dots: typically 1e-7; a 1e-7 difference in a gate / up output (fp32 summation order) can flip
+    # the Q8_K rounding of single SwiGLU values, which shows as 1e-4 on the output
+    assert _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13) < 3e-4
+    gpu.set_option("gemv_mma", 0)                     # the same through the per-lane grouped kernels
+    try:
+        assert _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13) < 3e-4
+    finally:
+        gpu.set_option("gemv_mma", 1)
     gpu.set_option("moe_gemm_rows", 1)
     try:
         _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13, tol=CHAIN_TOL)

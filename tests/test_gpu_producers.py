@@ -33,7 +33,7 @@ def test_rmsnorm_q8k(gpu, m, k):
     got_q, got_s, got_b = _read_q8k(gpu, q, s, b, m, k)
     for r in range(m):
         want_n = oracle.rmsnorm(x[r], w, eps)
-        assert rel_l2(got_n[r], want_n) < 1e-6            # tree sum vs in-order sum: fp32 rounding only
+        assert rel_l2(got_n[r], want_n) < 1e-5            # tree sum vs in-order sum: fp32 rounding only
         ws, wq, wb_ = oracle.quant_q8k(got_n[r])            # the quantization step itself: bit for bit
         assert np.array_equal(got_s[r].view(np.uint32), ws.view(np.uint32))
         assert np.array_equal(got_q[r], wq) and np.array_equal(got_b[r], wb_)
