@@ -164,14 +164,26 @@ OJAS_B200_API size_t ojas_b200_gemm_workspace_bytes(size_t M, size_t K);
 OJAS_B200_API int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t ggml_type, const float *x, const void *w, float *y, size_t K,
                                  size_t N, size_t M, int accum, void *workspace, size_t workspace_bytes);
 
+/* The same with f16 activations xh [M,K] (the engine's split-K prefill entries take them that way,
+ * crates/ojas-cuda/src/kernels/gemm_q.rs:537-556): widened exactly, then the arithmetic of ojas_b200_gemm. */
+OJAS_B200_API int ojas_b200_gemm_f16(ojas_b200_ctx *ctx, uint32_t ggml_type, const void *xh, const void *w, float *y, size_t K,
+                                     size_t N, size_t M, int accum, void *workspace, size_t workspace_bytes);
+/* Scratch owned by the context for the entry points that have no workspace argument (the name-based prefill entries
+ * gemm_mm_*, whose upstream argument lists carry none).  Grow-only; ALLOCATES: call it at set-up, never on the compute
+ * path.  Without it those entries use the array built into the library (up to ojas_b200_gemm_static_capacity() bytes)
+ * and refuse larger shapes. */
+OJAS_B200_API int ojas_b200_reserve(ojas_b200_ctx *ctx, size_t bytes);
+OJAS_B200_API size_t ojas_b200_reserved_bytes(ojas_b200_ctx *ctx);
+
 /* ---- prefill GEMM for callers that cannot provide scratch memory.  No counterpart in the reference.
  * Meant for hosts that may not allocate device memory around the call: a plugin inside an engine
  * whose allocator it cannot reach, or a serving loop that has frozen its memory map.  Same result as
  * ojas_b200_gemm, but the f16 activation tiles go to an 8 MiB array built into the library (each GPU
  * that loads the library holds it until the process exits), so M * K <= 4 194 304
  * (ojas_b200_gemm_static_capacity() bytes / 2); larger shapes are refused with OJAS_B200_E_LIMIT.
- * Calls nothing that allocates.  The first call on a device looks up the array's device address; make
- * that call before any stream capture.  The array is shared by every call and keeps the last call's
+ * Calls nothing that allocates.  The first call on a device looks up the array's device address and loads the code of
+ * every kernel the entry can launch (all tile widths, all three formats); make that call at set-up, from one thread,
+ * before any stream capture: after it no call on that device allocates, whatever its shape or type.  The array is shared by every call and keeps the last call's
  * contents (each call overwrites the part it uses); two calls whose kernels overlap on the GPU (other
  * streams, other contexts on the same device) race on it. */
 OJAS_B200_API size_t ojas_b200_gemm_static_capacity(void);
@@ -243,8 +255,12 @@ OJAS_B200_API int ojas_b200_tp_allgather(ojas_b200_tp *tp, const float *src, siz
  * (crates/ojas-core/src/kernel.rs:68-83; argument marshalling crates/ojas-cuda/src/device.rs:
  * 391-415): buffers are (device pointer, byte offset) pairs in the kernel's positional order,
  * then the u32 constants.  grid and block are accepted for signature compatibility and
- * ignored.  Names served: gemv_nat_{q4k,q6k,q80}{,_accum,_bias,_m}
- * (crates/ojas-cuda/src/kernels/nat.rs:56-64) and the entries listed by ojas_b200_kernel_name. */
+ * ignored, except grid[1] of the moe_gu_* entries (the number of picks, as upstream's blockIdx.y).  Names served, with
+ * the engine's own argument lists: gemv_nat_{q4k,q6k,q80}{,_accum,_bias,_m} (crates/ojas-cuda/src/kernels/nat.rs:56-64);
+ * gemm_mm_{q4l,q6k,q8_0}{,_sk} and gemm_mm_q4k{,_sk} (crates/ojas-cuda/src/kernels/gemm_q.rs:499-556; for q4l the weight
+ * buffer is this library's repacked Q4_K and qa / qb are ignored); moe_topk{,_m}; moe_gu_<fmt>, moe_down_<fmt> and their
+ * _slots forms for q80, q4k, q6k (crates/ojas-cuda/src/kernels/moe.rs:75-178); quant_q8k.  ojas_b200_kernel_name lists
+ * them. */
 OJAS_B200_API int ojas_b200_has_kernel(const char *name);
 OJAS_B200_API int ojas_b200_kernel_count(void);
 OJAS_B200_API const char *ojas_b200_kernel_name(int index);

@@ -72,6 +72,7 @@ extern "C" void ojas_b200_destroy(ojas_b200_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->act_scratch) cudaFree(ctx->act_scratch);
+    if (ctx->reserved) cudaFree(ctx->reserved);
     if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
     if (ctx->host_status) cudaFreeHost(ctx->host_status);
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
@@ -88,6 +89,26 @@ extern "C" int ojas_b200_set_stream(ojas_b200_ctx *ctx, void *stream) {
     ctx->stream = (cudaStream_t)stream;
     return 0;
 }
+
+// Grow-only scratch owned by the context, for the entry points that take no workspace argument (the name-based
+// prefill entries).  Allocates (and frees the smaller buffer after the stream has drained): call it at set-up, never
+// on the compute path.
+extern "C" int ojas_b200_reserve(ojas_b200_ctx *ctx, size_t bytes) {
+    if (!ctx) return OJAS_B200_E_ARG;
+    if (bytes <= ctx->reserved_bytes) return 0;
+    OJAS_CUDA(ctx, cudaSetDevice(ctx->device));
+    void *p = nullptr;
+    OJAS_CUDA(ctx, cudaMalloc(&p, bytes));
+    if (ctx->reserved) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->reserved);
+    }
+    ctx->reserved = p;
+    ctx->reserved_bytes = bytes;
+    return 0;
+}
+
+extern "C" size_t ojas_b200_reserved_bytes(ojas_b200_ctx *ctx) { return ctx ? ctx->reserved_bytes : 0; }
 
 extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value) {
     if (!ctx || !key) return OJAS_B200_E_ARG;

@@ -25,6 +25,8 @@ struct ojas_b200_ctx {
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
     void *act_scratch = nullptr;         // device scratch for a batch's Q8_K activations (values, scales, block sums)
+    void *reserved = nullptr;            // scratch the host reserved with ojas_b200_reserve (never grown inside a compute call)
+    size_t reserved_bytes = 0;
     unsigned int *gemm_flags = nullptr;  // device words, one per GEMM output tile: "the tile has been stored" marks (see gemm_ts.cuh),
                                          // then one word: the value that means "stored" for the GEMM launch in flight (never 0)
     unsigned int *host_status = nullptr; // pinned host word written by kernels whose bounded waits ran out
@@ -110,6 +112,12 @@ struct TpPush {
     int n;                                 // destinations
 };
 
+// Scratch for a call that needs `bytes`: the reserved buffer when it is large enough, else the array built into the
+// library when that is (gemm_tc.cu), else null with the error set.
+void *ojas_scratch_for(ojas_b200_ctx *ctx, size_t bytes, const char *who);
+int ojas_gemv_selected(ojas_b200_ctx *ctx, uint32_t type, int form, const float *x, const void *w, const uint32_t *sel, size_t sel_stride,
+                       const float *alpha, float *y, size_t K, size_t N);
+int ojas_silu_mul_inplace(ojas_b200_ctx *ctx, float *g, const float *u, size_t n);
 int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
                           const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
                           size_t rows_hint);

@@ -9,7 +9,7 @@
 struct NameEntry {
     const char *name;
     int nbufs, nconsts;
-    int (*fn)(ojas_b200_ctx *, void *const *b, const uint32_t *c);
+    int (*fn)(ojas_b200_ctx *, void *const *b, const uint32_t *c, const uint32_t *grid);
 };
 
 static uint32_t tag_type(const char *tag) {
@@ -21,19 +21,19 @@ static uint32_t tag_type(const char *tag) {
 // gemv_nat_<tag>{,_accum,_bias}: (x, w, y[, bs]) (K, N); _m: (x, w, y) (K, N, M, ACC)
 // (crates/ojas-cuda/src/kernels/nat.rs:69-74).
 #define GEMV_ENTRIES(tag)                                                                                           \
-    static int gemv_##tag##_plain(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {                          \
+    static int gemv_##tag##_plain(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {                          \
         return ojas_b200_gemv(ctx, tag_type(#tag), OJAS_B200_PLAIN, (const float *)b[0], b[1], (float *)b[2],       \
                               nullptr, c[0], c[1], 1);                                                              \
     }                                                                                                               \
-    static int gemv_##tag##_accum(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {                          \
+    static int gemv_##tag##_accum(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {                          \
         return ojas_b200_gemv(ctx, tag_type(#tag), OJAS_B200_ACCUM, (const float *)b[0], b[1], (float *)b[2],       \
                               nullptr, c[0], c[1], 1);                                                              \
     }                                                                                                               \
-    static int gemv_##tag##_bias(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {                           \
+    static int gemv_##tag##_bias(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {                           \
         return ojas_b200_gemv(ctx, tag_type(#tag), OJAS_B200_BIAS, (const float *)b[0], b[1], (float *)b[2],        \
                               (const float *)b[3], c[0], c[1], 1);                                                  \
     }                                                                                                               \
-    static int gemv_##tag##_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {                              \
+    static int gemv_##tag##_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {                              \
         const size_t M = c[2];                                                                                      \
         const int form = c[3] ? OJAS_B200_ACCUM : OJAS_B200_PLAIN;                                                  \
         for (size_t m0 = 0; m0 < M; m0 += OJAS_B200_GEMV_MAX_M) {                                                   \
@@ -51,27 +51,96 @@ GEMV_ENTRIES(q80)
 
 // quant_q8k: (x, q, scales, bsums) (K, M) — the activation step that precedes the K-quant
 // dots (crates/ojas-cpu/src/cpu_math.rs:545-563); no CUDA entry of this name exists upstream.
-static int d_quant_q8k(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
+static int d_quant_q8k(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {
     return ojas_b200_quant_q8k(ctx, (const float *)b[0], c[1], c[0], (int8_t *)b[1], (float *)b[2], (int32_t *)b[3]);
 }
 
-// gemm_mm_<q4k|q6k|q8_0>: (x, w, y, workspace) (K, N, accum, M, workspace_bytes) — the prefill entries
-// of crates/ojas-cuda/src/kernels/gemm_q.rs:499-531 ((x, w, y, K, N, accum, M)) plus the scratch
-// buffer this implementation needs for its f16 activation tiles.
-#define GEMM_ENTRY(tag, type)                                                                                     \
-    static int gemm_##tag(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {                                \
-        return ojas_b200_gemm(ctx, type, (const float *)b[0], b[1], (float *)b[2], c[0], c[1], c[3], (int)c[2],   \
-                              b[3], (size_t)c[4]);                                                                \
+// Prefill entries with the engine's own argument lists (crates/ojas-cuda/src/kernels/gemm_q.rs:499-556):
+//   gemm_mm_q6k, gemm_mm_q8_0 : (x, w, y) (K, N, accum, M)
+//   gemm_mm_q4l               : (x, w4, y, qa, qb) (K, N, accum, M) -- the engine's Q4L relayout of Q4_K is lossy and is
+//                               not reproduced here: w4 is this library's repacked Q4_K weight, qa / qb are ignored
+//   gemm_mm_q4k               : (x, w, y) (K, N, accum, M), the same without the two unused buffers
+//   *_sk                      : (xh, w, y[, qa, qb]) (K, N, M, nsplit): f16 activations, results ADDED into a y the
+//                               caller zeroed; nsplit is accepted and ignored (the K split is this library's business)
+// The f16 activation tiles go to the context's reserved scratch (ojas_b200_reserve) or, up to 8 MiB, to the array built
+// into the library; nothing is allocated here.
+static int gemm_named(ojas_b200_ctx *ctx, uint32_t type, const void *x, bool f16, const void *w, float *y, size_t K, size_t N, size_t M, int accum) {
+    const size_t need = ojas_b200_gemm_workspace_bytes(M, K);
+    void *ws = ojas_scratch_for(ctx, need, "gemm_mm");
+    if (!ws) return OJAS_B200_E_LIMIT;
+    if (f16) return ojas_b200_gemm_f16(ctx, type, x, w, y, K, N, M, accum, ws, need);
+    return ojas_b200_gemm(ctx, type, (const float *)x, w, y, K, N, M, accum, ws, need);
+}
+#define GEMM_ENTRY(tag, type)                                                                                       \
+    static int gemm_##tag(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {                \
+        return gemm_named(ctx, type, b[0], false, b[1], (float *)b[2], c[0], c[1], c[3], (int)c[2]);                \
+    }                                                                                                               \
+    static int gemm_##tag##_sk(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {           \
+        return gemm_named(ctx, type, b[0], true, b[1], (float *)b[2], c[0], c[1], c[2], 1);                         \
     }
 GEMM_ENTRY(q4k, OJAS_B200_Q4_K)
+GEMM_ENTRY(q4l, OJAS_B200_Q4_K)
 GEMM_ENTRY(q6k, OJAS_B200_Q6_K)
 GEMM_ENTRY(q8_0, OJAS_B200_Q8_0)
 
+// Decode-time expert FFN of one token (crates/ojas-cuda/src/kernels/moe.rs:75-178; upstream has the Q8_0 forms on
+// CUDA and the K-quant forms on Metal, crates/ojas-metal/src/kernels/moe.rs:513-529):
+//   moe_gu_<fmt>         (x, wg, wu, act, idx) (K, N), grid.y = picks: act[j, :] = silu(Wg_e x) * (Wu_e x), e = idx[j]
+//   moe_down_<fmt>       (act, wd, x, idx, wgt) (K, N, KSEL): x += sum_j wgt[j] * Wd_e act[j, :]
+//   moe_gu_<fmt>_slots   (x, arena_g, arena_u, act, off_g, off_u) (K, N): experts at byte offsets off_g[j], off_u[j]
+//   moe_down_<fmt>_slots (act, arena, x, off_d, wgt) (K, N, KSEL)
+// wg / wu / wd are this library's repacked stacked experts (expert e starts e * repacked_bytes(N, K) behind the base: N
+// must be a multiple of 8); offsets are byte offsets of repacked experts.  The pick is read on the device.  The up
+// outputs pass through the context's activation scratch.
+static size_t expert_stride(uint32_t type, size_t N, size_t K) { return (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type); }
+
+static int moe_gu_named(ojas_b200_ctx *ctx, uint32_t type, void *const *b, const uint32_t *c, const uint32_t *grid, bool slots) {
+    const size_t K = c[0], N = c[1], ksel = grid ? grid[1] : 0;
+    if (ksel == 0 || ksel > 32) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_gu: grid.y = %zu picks (1..32)", ksel);
+    if (N % OJAS_TILE_ROWS != 0 || N % 4 != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_gu: N=%zu must be a multiple of 8", N);
+    if (!ctx->act_scratch || ksel * N * sizeof(float) > OJAS_ACT_SCRATCH_BYTES)
+        return ojas_fail(ctx, OJAS_B200_E_LIMIT, "moe_gu: %zu picks x N=%zu exceed the context's activation scratch", ksel, N);
+    const float *x = (const float *)b[0];
+    float *act = (float *)b[3], *up = (float *)ctx->act_scratch;
+    const uint32_t *sg = (const uint32_t *)b[4], *su = slots ? (const uint32_t *)b[5] : (const uint32_t *)b[4];
+    const size_t stride = slots ? 0 : expert_stride(type, N, K);
+    for (size_t j = 0; j < ksel; j++) {
+        int rc = ojas_gemv_selected(ctx, type, OJAS_B200_PLAIN, x, b[1], sg + j, stride, nullptr, act + j * N, K, N);
+        if (rc) return rc;
+        rc = ojas_gemv_selected(ctx, type, OJAS_B200_PLAIN, x, b[2], su + j, stride, nullptr, up + j * N, K, N);
+        if (rc) return rc;
+    }
+    return ojas_silu_mul_inplace(ctx, act, up, ksel * N);
+}
+
+static int moe_down_named(ojas_b200_ctx *ctx, uint32_t type, void *const *b, const uint32_t *c, bool slots) {
+    const size_t K = c[0], N = c[1], ksel = c[2];
+    if (ksel == 0 || ksel > 32) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_down: KSEL = %zu (1..32)", ksel);
+    if (N % OJAS_TILE_ROWS != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_down: N=%zu must be a multiple of 8", N);
+    const float *act = (const float *)b[0], *wgt = (const float *)b[4];
+    const uint32_t *sel = (const uint32_t *)b[3];
+    const size_t stride = slots ? 0 : expert_stride(type, N, K);
+    for (size_t j = 0; j < ksel; j++) {
+        const int rc = ojas_gemv_selected(ctx, type, OJAS_B200_ACCUM, act + j * K, b[1], sel + j, stride, wgt + j, (float *)b[2], K, N);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+#define MOE_ENTRIES(tag)                                                                                                               \
+    static int moe_gu_##tag(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *g) { return moe_gu_named(ctx, tag_type(#tag), b, c, g, false); }       \
+    static int moe_gu_##tag##_slots(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *g) { return moe_gu_named(ctx, tag_type(#tag), b, c, g, true); } \
+    static int moe_down_##tag(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) { return moe_down_named(ctx, tag_type(#tag), b, c, false); }       \
+    static int moe_down_##tag##_slots(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) { return moe_down_named(ctx, tag_type(#tag), b, c, true); }
+MOE_ENTRIES(q4k)
+MOE_ENTRIES(q6k)
+MOE_ENTRIES(q80)
+
 // moe_topk: (lg, idx, wgt) (E, KSEL) — crates/ojas-cuda/src/kernels/moe.rs:45; moe_topk_m adds M.
-static int d_moe_topk(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
+static int d_moe_topk(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {
     return ojas_b200_moe_topk(ctx, (const float *)b[0], (uint32_t *)b[1], (float *)b[2], 1, c[0], c[1]);
 }
-static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
+static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {
     return ojas_b200_moe_topk(ctx, (const float *)b[0], (uint32_t *)b[1], (float *)b[2], c[2], c[0], c[1]);
 }
 
@@ -81,11 +150,18 @@ static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c) {
     {"gemv_nat_" #tag "_bias", 4, 2, gemv_##tag##_bias},     \
     {"gemv_nat_" #tag "_m", 3, 4, gemv_##tag##_m}
 
+#define MOE_TABLE(tag)                                                                             \
+    {"moe_gu_" #tag, 5, 2, moe_gu_##tag}, {"moe_down_" #tag, 5, 3, moe_down_##tag},                 \
+    {"moe_gu_" #tag "_slots", 6, 2, moe_gu_##tag##_slots}, {"moe_down_" #tag "_slots", 5, 3, moe_down_##tag##_slots}
+
 static const NameEntry kTable[] = {
     GEMV_TABLE(q4k), GEMV_TABLE(q6k), GEMV_TABLE(q80),
     {"quant_q8k", 4, 2, d_quant_q8k},
     {"moe_topk", 3, 2, d_moe_topk}, {"moe_topk_m", 3, 3, d_moe_topk_m},
-    {"gemm_mm_q4k", 4, 5, gemm_q4k}, {"gemm_mm_q6k", 4, 5, gemm_q6k}, {"gemm_mm_q8_0", 4, 5, gemm_q8_0},
+    {"gemm_mm_q4k", 3, 4, gemm_q4k}, {"gemm_mm_q6k", 3, 4, gemm_q6k}, {"gemm_mm_q8_0", 3, 4, gemm_q8_0}, {"gemm_mm_q4l", 5, 4, gemm_q4l},
+    {"gemm_mm_q4k_sk", 3, 4, gemm_q4k_sk}, {"gemm_mm_q6k_sk", 3, 4, gemm_q6k_sk}, {"gemm_mm_q8_0_sk", 3, 4, gemm_q8_0_sk},
+    {"gemm_mm_q4l_sk", 5, 4, gemm_q4l_sk},
+    MOE_TABLE(q4k), MOE_TABLE(q6k), MOE_TABLE(q80),
 };
 static const int kTableLen = (int)(sizeof kTable / sizeof kTable[0]);
 
@@ -103,7 +179,7 @@ extern "C" const char *ojas_b200_kernel_name(int i) { return (i >= 0 && i < kTab
 extern "C" int ojas_b200_dispatch(ojas_b200_ctx *ctx, const char *name, void *const *bufs, const uint64_t *offsets,
                                   int nbufs, const uint32_t *consts, int nconsts, const uint32_t grid[3],
                                   const uint32_t block[3]) {
-    (void)grid; (void)block;
+    (void)block;
     if (!ctx) return OJAS_B200_E_ARG;
     const NameEntry *e = find_entry(name);
     if (!e) return ojas_fail(ctx, OJAS_B200_E_NAME, "dispatch: no kernel named '%s'", name ? name : "(null)");
@@ -115,5 +191,5 @@ extern "C" int ojas_b200_dispatch(ojas_b200_ctx *ctx, const char *name, void *co
         if (!bufs || !bufs[i]) return ojas_fail(ctx, OJAS_B200_E_ARG, "dispatch %s: buffer %d is null", name, i);
         ptrs[i] = (uint8_t *)bufs[i] + (offsets ? offsets[i] : 0);
     }
-    return e->fn(ctx, ptrs, consts);
+    return e->fn(ctx, ptrs, consts, grid);
 }

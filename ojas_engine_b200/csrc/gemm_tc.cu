@@ -260,8 +260,10 @@ __device__ __forceinline__ void dequant_q80_half(const uint4 &q0, const uint4 &q
 // x f32 [M, K] -> xh f16 [M, K].  QUANT: xh = f16(sx * q) with (sx, q) = quant_q8k(x), written
 // in the k order the K-quant dequantizers produce ((0, 2, 1, 3) inside every group of four).
 // Otherwise xh = f16(x) in natural order (Q8_0).  One warp per 256 values.
-template <bool QUANT>
-__global__ void __launch_bounds__(256) gemm_prep_kernel(const float *x, __half *xh, long long n_sb, unsigned *serial_word) {
+// XIN = float or __half: the split-K entries of the engine hand over activations that are f16 already
+// (crates/ojas-cuda/src/kernels/gemm_q.rs:537-556).
+template <bool QUANT, typename XIN>
+__global__ void __launch_bounds__(256) gemm_prep_kernel(const XIN *x, __half *xh, long long n_sb, unsigned *serial_word) {
     const int lane = threadIdx.x & 31;
     if (serial_word && blockIdx.x == 0 && threadIdx.x == 0) {     // a fresh tile-mark value for the GEMM behind this kernel, never 0
         const unsigned v = *serial_word + 1u;
@@ -271,16 +273,29 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const float *x, __half *
     grid_launch_dependents();   // the GEMM behind this kernel may begin its set-up; it waits for this grid before it reads xh
     if (sb >= n_sb) return;
     float v[8];
-    if (QUANT) {
-        const Q8kLane ql = quant_q8k_warp(x + sb * 256, lane);
+    if (sizeof(XIN) == 2) {                 // f16 in: widen (exact), then the same steps as for f32
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(x + sb * 256) + lane);
+        const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; i++) { const float2 f = __half22float2(h2[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+        if (QUANT) {
+            const Q8kLane ql = quant_q8k_values(v);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t word = i < 4 ? ql.packed.x : ql.packed.y;
+                v[i] = __fmul_rn(ql.scale, (float)(int)(signed char)((word >> (8 * (i & 3))) & 0xffu));
+            }
+        }
+    } else if (QUANT) {
+        const Q8kLane ql = quant_q8k_warp(reinterpret_cast<const float *>(x) + sb * 256, lane);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const uint32_t word = i < 4 ? ql.packed.x : ql.packed.y;
             v[i] = __fmul_rn(ql.scale, (float)(int)(signed char)((word >> (8 * (i & 3))) & 0xffu));
         }
     } else {
-        const float4 p = __ldg(reinterpret_cast<const float4 *>(x + sb * 256) + lane * 2);
-        const float4 q = __ldg(reinterpret_cast<const float4 *>(x + sb * 256) + lane * 2 + 1);
+        const float4 p = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + sb * 256) + lane * 2);
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + sb * 256) + lane * 2 + 1);
         v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
     }
     uint4 out;
@@ -364,8 +379,23 @@ static void gemm_plan(ojas_b200_ctx *ctx, size_t M, size_t K, int &bn, int &kspl
 static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size_t x_rows, const uint8_t *w, float *y,
                        size_t K, size_t N, size_t M, int accum, const int *grp_count, const int *grp_offset);
 
+static int gemm_entry(ojas_b200_ctx *ctx, uint32_t type, const void *x, bool x_is_f16, const void *w, float *y, size_t K, size_t N, size_t M,
+                      int accum, void *workspace, size_t workspace_bytes);
+
 extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x, const void *w, float *y, size_t K, size_t N,
                               size_t M, int accum, void *workspace, size_t workspace_bytes) {
+    return gemm_entry(ctx, type, x, false, w, y, K, N, M, accum, workspace, workspace_bytes);
+}
+
+// The same with f16 activations [M, K] (the engine's split-K entries take them that way): widened exactly, then the
+// same arithmetic as ojas_b200_gemm.
+extern "C" int ojas_b200_gemm_f16(ojas_b200_ctx *ctx, uint32_t type, const void *xh, const void *w, float *y, size_t K, size_t N,
+                                  size_t M, int accum, void *workspace, size_t workspace_bytes) {
+    return gemm_entry(ctx, type, xh, true, w, y, K, N, M, accum, workspace, workspace_bytes);
+}
+
+static int gemm_entry(ojas_b200_ctx *ctx, uint32_t type, const void *x, bool x_is_f16, const void *w, float *y, size_t K, size_t N, size_t M,
+                      int accum, void *workspace, size_t workspace_bytes) {
     if (!ctx) return OJAS_B200_E_ARG;
     if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q6_K && type != OJAS_B200_Q8_0)
         return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: unsupported GGUF type %u", type);
@@ -374,8 +404,8 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     if (N == 0 || M == 0 || N > 0x7fffffffu || M > 0x7fffffffu) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: M=%zu N=%zu out of range", M, N);
     if (workspace_bytes < ojas_b200_gemm_workspace_bytes(M, K))
         return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: workspace of %zu bytes, %zu needed", workspace_bytes, ojas_b200_gemm_workspace_bytes(M, K));
-    if (((uintptr_t)w & 255) || ((uintptr_t)workspace & 255) || ((uintptr_t)x & 15))
-        return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: misaligned pointer (weights and workspace 256 bytes, x 16 bytes)");
+    if (((uintptr_t)w & 127) || ((uintptr_t)workspace & 255) || ((uintptr_t)x & 15))
+        return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: misaligned pointer (weights 128 bytes, workspace 256 bytes, x 16 bytes)");
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm: cuTensorMapEncodeTiled is not available from the driver");
 
@@ -384,8 +414,14 @@ extern "C" int ojas_b200_gemm(ojas_b200_ctx *ctx, uint32_t type, const float *x,
     const long long n_sb = (long long)M * (long long)(K / 256);
     const long long blocks = (n_sb + 7) / 8;
     if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
-    if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb, ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS);
-    else gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, xh, n_sb, ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS);
+    unsigned *serial = ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS;
+    if (x_is_f16) {
+        if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false, __half><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __half *)x, xh, n_sb, serial);
+        else gemm_prep_kernel<true, __half><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __half *)x, xh, n_sb, serial);
+    } else {
+        if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float *)x, xh, n_sb, serial);
+        else gemm_prep_kernel<true, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float *)x, xh, n_sb, serial);
+    }
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
 
     return gemm_launch(ctx, type, xh, M, (const uint8_t *)w, y, K, N, M, accum, nullptr, nullptr);
@@ -484,8 +520,8 @@ int ojas_gemm_prep(ojas_b200_ctx *ctx, const float *x, void *xh, size_t rows, si
     const long long blocks = (n_sb + 7) / 8;
     if (blocks <= 0) return 0;
     if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
-    if (quant) gemm_prep_kernel<true><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
-    else gemm_prep_kernel<false><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
+    if (quant) gemm_prep_kernel<true, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
+    else gemm_prep_kernel<false, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
     return 0;
 }
@@ -505,7 +541,8 @@ int ojas_gemm_grouped(ojas_b200_ctx *ctx, uint32_t type, const void *xh, size_t 
 static __device__ __align__(256) unsigned char g_gemm_static_scratch[OJAS_B200_GEMM_STATIC_BYTES];
 
 // In host code the array's name is only a handle; the device address comes from the runtime, once per
-// device, with that device current.
+// device, with that device current.  (The first call on a device is not thread-safe against another first call on
+// the same device: make it from one thread, at set-up.)
 static void *gemm_static_scratch_ptr(ojas_b200_ctx *ctx, int *rc_out) {
     static void *ptrs[64] = {nullptr};
     *rc_out = 0;
@@ -521,12 +558,35 @@ static void *gemm_static_scratch_ptr(ojas_b200_ctx *ctx, int *rc_out) {
             *rc_out = ojas_fail(ctx, OJAS_B200_E_CUDA, "gemm_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
             return nullptr;
         }
+        // Load every kernel this entry can launch now (the runtime loads a kernel's code at its first use, which may
+        // allocate device memory): after this first call on a device no later call allocates, whatever its shape or type.
+        cudaFuncAttributes fa;
+#define OJAS_TOUCH(K) cudaFuncGetAttributes(&fa, K)
+#define OJAS_TOUCH_TYPE(T) OJAS_TOUCH((gemm_ts_kernel<32, T>)); OJAS_TOUCH((gemm_ts_kernel<64, T>)); OJAS_TOUCH((gemm_ts_kernel<128, T>)); OJAS_TOUCH((gemm_ts_kernel<256, T>))
+        OJAS_TOUCH_TYPE(OJAS_B200_Q4_K); OJAS_TOUCH_TYPE(OJAS_B200_Q6_K); OJAS_TOUCH_TYPE(OJAS_B200_Q8_0);
+        OJAS_TOUCH((gemm_prep_kernel<true, float>)); OJAS_TOUCH((gemm_prep_kernel<false, float>));
+        OJAS_TOUCH((gemm_prep_kernel<true, __half>)); OJAS_TOUCH((gemm_prep_kernel<false, __half>));
+#undef OJAS_TOUCH_TYPE
+#undef OJAS_TOUCH
+        cudaGetLastError();
         ptrs[ctx->device] = p;
     }
     return ptrs[ctx->device];
 }
 
 extern "C" size_t ojas_b200_gemm_static_capacity(void) { return OJAS_B200_GEMM_STATIC_BYTES; }
+
+void *ojas_scratch_for(ojas_b200_ctx *ctx, size_t bytes, const char *who) {
+    if (ctx->reserved && ctx->reserved_bytes >= bytes) return ctx->reserved;
+    if (bytes <= OJAS_B200_GEMM_STATIC_BYTES) {
+        int rc = 0;
+        void *p = gemm_static_scratch_ptr(ctx, &rc);
+        if (p) return p;
+        return nullptr;
+    }
+    ojas_fail(ctx, OJAS_B200_E_LIMIT, "%s: %zu bytes of scratch needed, %zu reserved: call ojas_b200_reserve at set-up", who, bytes, ctx->reserved_bytes);
+    return nullptr;
+}
 
 extern "C" int ojas_b200_gemm_static(ojas_b200_ctx *ctx, uint32_t type, const float *x, const void *w, float *y, size_t K, size_t N,
                                      size_t M, int accum) {

@@ -47,6 +47,13 @@ struct GemvArgs {
     int T_log;               // teams per CTA = 1 << T_log (warps per CTA = teams * warps per team)
     int P;                   // partial sums per row and group = min(warps per team, nsb)
     int own_x;               // 1: warp w consumes exactly super-block w, so it quantizes that one for itself
+    // decode-time expert selection (the engine's moe_gu_* / moe_down_* and their _slots forms,
+    // crates/ojas-cuda/src/kernels/moe.rs:75-178): the weight rows start `*sel * sel_stride` bytes (sel_stride != 0)
+    // or `*sel` bytes (an offset table entry) behind w, read on the device; alpha (may be null): the result is
+    // multiplied by *alpha before it is stored (the router weight of the pick).
+    const uint32_t *sel;
+    size_t sel_stride;
+    const float *alpha;
     // tensor-parallel epilogue (tp.cu): instead of y, every result goes, stamped with the step's number, to this
     // rank's place in the receive window of every rank (plain 8-byte stores through peer-mapped pointers).
     TpPush tp;
@@ -403,6 +410,12 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         }
         __syncwarp();
     }
+    const uint8_t *wbase = a.w;
+    if (a.sel) {                                                  // the pick comes from the router kernel before this one
+        grid_dependency_wait();
+        const size_t s = (size_t)__ldg(a.sel);
+        wbase += a.sel_stride ? s * a.sel_stride : s;
+    }
     // issue cursor (used by lane 0): k-th group of the team and super-block inside it
     int ik = 0, isb = wi;
     while (isb >= nsb) { isb -= nsb; ik++; }
@@ -411,7 +424,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     auto issue = [&]() {
         const int g = team + ik * T;
         const int cnt = (nu - 4 * g) < 4 ? (nu - 4 * g) : 4;
-        const uint8_t *src = a.w + ((size_t)(ub + 4 * g) * nsb + isb) * TB;
+        const uint8_t *src = wbase + ((size_t)(ub + 4 * g) * nsb + isb) * TB;
         const unsigned stg = issued & (unsigned)(nst - 1);
         gv_bar_expect(bar + stg, (unsigned)(cnt * TB));
         for (int t = 0; t < cnt; t++) gv_bulk_load(ring + stg * STEP + t * TB, src + (size_t)t * nsb * TB, TB, bar + stg);
@@ -427,6 +440,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     if (TYPE == OJAS_B200_Q8_0) stage_f32<MT>(a, reinterpret_cast<float *>(act));
     else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
+    const float alpha = a.alpha ? __ldg(a.alpha) : 1.0f;
     // tensor-parallel launches: the step in flight is the stamp and picks the half of the windows
     const unsigned tp_stamp = a.tp.step ? *reinterpret_cast<const volatile unsigned *>(a.tp.step) : 0u;
     const size_t tp_half = (size_t)(tp_stamp & 1u) * a.tp.half_pairs;
@@ -478,6 +492,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         for (int p = pq; p < P; p += 4) v += part[((g * P + p) * MT + m) * 32 + rr];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v *= alpha;
         const int row = (ub + 4 * g) * 8 + rr;
         if (pq == 0 && m < a.M && 4 * g + (rr >> 3) < nu && row < a.N) {
             if (a.tp.step) {
@@ -894,6 +909,21 @@ extern "C" int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t type, int form, const
     a.x = x; a.w = (const uint8_t *)w; a.y = y; a.bias = bias;
     a.K = (int)K; a.N = (int)N; a.M = (int)M; a.form = form;
     return gemv_run(ctx, type, false, a, M);
+}
+
+// One activation row against the expert picked on the device: w + *sel * stride (stride != 0) or w + *sel (offset
+// table entry); y = (or +=) alpha * W x with alpha read on the device when given.
+int ojas_gemv_selected(ojas_b200_ctx *ctx, uint32_t type, int form, const float *x, const void *w, const uint32_t *sel, size_t sel_stride,
+                       const float *alpha, float *y, size_t K, size_t N) {
+    int rc = gemv_check(ctx, type, form, w, y, nullptr, K, N, 1);
+    if (rc) return rc;
+    if (!x || !sel) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv: null pointer");
+    if (((uintptr_t)x & 15) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv: x must be 16-byte aligned");
+    GemvArgs a{};
+    a.x = x; a.w = (const uint8_t *)w; a.y = y;
+    a.K = (int)K; a.N = (int)N; a.M = 1; a.form = form;
+    a.sel = sel; a.sel_stride = sel_stride; a.alpha = alpha;
+    return gemv_run(ctx, type, false, a, 1);
 }
 
 // The tensor-parallel form of a single-row GEMV (tp.cu): results also go to the peers' windows.

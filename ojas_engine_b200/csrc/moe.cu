@@ -149,6 +149,15 @@ __global__ void __launch_bounds__(256) moe_silu_mul_kernel(float4 *g, const floa
     g[i] = a;
 }
 
+int ojas_silu_mul_inplace(ojas_b200_ctx *ctx, float *g, const float *u, size_t n) {
+    if (n % 4 != 0 || ((uintptr_t)g & 15) || ((uintptr_t)u & 15)) return ojas_fail(ctx, OJAS_B200_E_ARG, "silu_mul: rows must be multiples of 4 floats on 16-byte boundaries");
+    const long long n4 = (long long)(n / 4);
+    if (n4 == 0) return 0;
+    moe_silu_mul_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((float4 *)g, (const float4 *)u, n4);
+    OJAS_LAUNCH_CHECK(ctx, "moe_silu_mul");
+    return 0;
+}
+
 // ---------------------------------------------------------------- combine
 // out[t, :] (=, +=) sum_j wgt[t, j] * yd[pos[t*KSEL + j], :], picks added in order j = 0, 1, ... as the
 // CPU path does (crates/ojas-cpu/src/cpu_glm.rs:581).

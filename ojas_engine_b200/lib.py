@@ -53,6 +53,9 @@ SIGNATURES = {
     "ojas_b200_gemv_idots": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz]),
     "ojas_b200_gemm_workspace_bytes": (_sz, [_sz, _sz]),
     "ojas_b200_gemm": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i, _vp, _sz]),
+    "ojas_b200_gemm_f16": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i, _vp, _sz]),
+    "ojas_b200_reserve": (_i, [_vp, _sz]),
+    "ojas_b200_reserved_bytes": (_sz, [_vp]),
     "ojas_b200_gemm_static_capacity": (_sz, []),
     "ojas_b200_gemm_static": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "ojas_b200_moe_topk": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),

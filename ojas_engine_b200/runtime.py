@@ -203,6 +203,10 @@ class B200Gpu:
         self._ck(self._l.ojas_b200_gemm(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
                                         w.k, w.n, m, 1 if accum else 0, C.c_void_p(workspace.ptr), workspace.nbytes))
 
+    def reserve(self, nbytes: int) -> None:
+        """Context-owned scratch for the name-based prefill entries (allocates: set-up only)."""
+        self._ck(self._l.ojas_b200_reserve(self._ctx, nbytes))
+
     def moe_topk(self, logits: Buf, idx: Buf, wgt: Buf, m: int, e: int, ksel: int) -> None:
         self._ck(self._l.ojas_b200_moe_topk(self._ctx, C.c_void_p(logits.ptr), C.c_void_p(idx.ptr), C.c_void_p(wgt.ptr), m, e, ksel))
 

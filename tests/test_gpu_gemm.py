@@ -5,6 +5,7 @@ import pytest
 import oracle
 import ojas_engine_b200 as ob
 from ojas_engine_b200 import Q4_K, Q6_K, Q8_0
+from ojas_engine_b200 import lib as oblib
 
 from conftest import rel_l2
 from helpers import TYPES, activations, gauss_weights, synth_weights
@@ -15,13 +16,15 @@ TOL = 2e-3       # relative L2 against the reference CPU path (loop of matvec_kq
 SENT = 12345.5   # guard value past row M, as crates/ojas-cuda/tests/prefill_gemm_q.rs:308-319 does
 
 
-def _gemm_case(gpu, tag, m, n, k, source="gauss", accum=False, ksplit=0, seed=0, want=None, raw=None):
+def _gemm_case(gpu, tag, m, n, k, source="gauss", accum=False, ksplit=0, seed=0, want=None, raw=None, sample=None):
+    """`sample`: compare only these token rows with the oracle (every row of a GEMM is computed the same way; the
+    oracle takes a matvec per token, which is what bounds the sizes it can check in full)."""
     t = TYPES[tag]
     if raw is None:
         raw = synth_weights(t, n, k) if source == "synth" else gauss_weights(t, n, k, seed)
     x = activations(m, k, seed=seed + 100)
     if want is None:
-        want = oracle.matmul_kq(raw, t, n, k, x)
+        want = oracle.matmul_kq(raw, t, n, k, x if sample is None else x[sample])
     w = gpu.load_weight(raw, t, n, k)
     xb = gpu.upload(x)
     y0 = activations(m, n, seed=seed + 200) if accum else np.zeros((m, n), np.float32)
@@ -36,6 +39,9 @@ def _gemm_case(gpu, tag, m, n, k, source="gauss", accum=False, ksplit=0, seed=0,
         for b in (w.buf, xb, yb):
             gpu.free(b)
     assert np.all(got[m] == SENT), "wrote past row M"
+    if sample is not None:
+        got, y0 = np.concatenate([got[sample], got[m:]]), y0[sample]
+        m = len(sample)
     err = rel_l2(got[:m], want + y0 if accum else want)
     assert err < TOL, f"{tag} m={m} n={n} k={k} accum={accum} ksplit={ksplit}: rel L2 {err:.3e}"
     return err
@@ -70,6 +76,106 @@ def test_config3_q4k_prefill(gpu, m, n, k):
 
 def test_config3_q4k_prefill_m2048(gpu):
     _gemm_case(gpu, "q4k", 2048, 4096, 4096, seed=4)
+
+
+@pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
+def test_config3_q4k_prefill_m2048_ffn_shapes(gpu, n, k):
+    """The two FFN shapes at M = 2048 (sampled token rows against the oracle; synthetic blocks)."""
+    _gemm_case(gpu, "q4k", 2048, n, k, source="synth", sample=[0, 1, 511, 1024, 1500, 2047])
+
+
+@pytest.mark.parametrize("name,tag,n,k", [("qkv", "q4k", 10240, 8192), ("o", "q4k", 8192, 8192), ("gate_up", "q4k", 28672, 8192),
+                                           ("down", "q6k", 8192, 28672)])
+def test_config5_70b_projections_unsharded(gpu, name, tag, n, k):
+    """The Llama-70B-shaped projections on one GPU: M = 1 through the GEMV (every output against the oracle) and
+    M = 512 through the tensor-core GEMM (sampled token rows)."""
+    t = TYPES[tag]
+    raw = synth_weights(t, n, k)
+    w = gpu.load_weight(raw, t, n, k)
+    x1 = activations(1, k, seed=7) * np.float32(0.1)
+    xb, y = gpu.upload(x1), gpu.alloc(n)
+    gpu.gemv(w, xb, y, 1)
+    assert rel_l2(gpu.read(y, np.float32, n), oracle.matvec_kq(raw, t, n, k, x1[0])) < 1e-5
+    for b in (w.buf, xb, y):
+        gpu.free(b)
+    _gemm_case(gpu, tag, 512, n, k, raw=raw, sample=[0, 200, 511])
+
+
+def test_captured_gemm_replays(gpu):
+    """A GEMM whose tiles are split across CTAs (16 tiles on 148 SMs), captured once and replayed: every replay must
+    give the same, correct result (the marks that order a split tile's pieces take a fresh value on every launch)."""
+    m, n, k = 512, 1024, 4096
+    raw = gauss_weights(Q4_K, n, k, 5)
+    x = activations(m, k, seed=105)
+    sample = [0, 100, 255, 256, 511]
+    want = oracle.matmul_kq(raw, Q4_K, n, k, x[sample])
+    w = gpu.load_weight(raw, Q4_K, n, k)
+    xb, yb = gpu.upload(x), gpu.alloc(m * n)
+    work = gpu.alloc_bytes(gpu.gemm_workspace_bytes(m, k))
+    gpu.gemm(w, xb, yb, m, workspace=work)             # first call outside capture
+    gpu.sync()
+    gpu.graph_begin()
+    gpu.gemm(w, xb, yb, m, workspace=work)
+    g = gpu.graph_end()
+    first = None
+    for _ in range(5):
+        gpu.memset(yb, 0xFF)                           # NaNs: a piece that adds before the storing piece would keep them
+        gpu.graph_launch(g)
+        got = gpu.read(yb, np.float32, m * n).reshape(m, n)
+        assert np.isfinite(got).all()
+        assert rel_l2(got[sample], want) < TOL
+        if first is None:
+            first = got
+        assert rel_l2(got, first) < 1e-5
+    gpu.graph_destroy(g)
+    for b in (w.buf, xb, yb, work):
+        gpu.free(b)
+
+
+@pytest.mark.parametrize("name,tag", [("gemm_mm_q4k", "q4k"), ("gemm_mm_q4l", "q4k"), ("gemm_mm_q6k", "q6k"), ("gemm_mm_q8_0", "q80")])
+def test_prefill_entries_by_name(gpu, name, tag):
+    """The engine's prefill entry names with the engine's own argument lists
+    (crates/ojas-cuda/src/kernels/gemm_q.rs:499-556): (x, w, y[, qa, qb]) (K, N, accum, M) and the split-K forms
+    (xh f16, w, y[, qa, qb]) (K, N, M, nsplit), which add into a zeroed y."""
+    t = TYPES[tag]
+    m, n, k = 70, 384, 1024
+    raw = gauss_weights(t, n, k, 9)
+    x = activations(m, k, seed=19)
+    want = oracle.matmul_kq(raw, t, n, k, x)
+    w = gpu.load_weight(raw, t, n, k)
+    xb, y = gpu.upload(x), gpu.upload(np.ones((m, n), np.float32))
+    dummy = gpu.alloc(4)
+    extra = [(dummy, 0), (dummy, 0)] if name.endswith("q4l") else []
+    enc = gpu.begin()
+    gpu.dispatch(enc, name, [(xb, 0), (w.buf, 0), (y, 0)] + extra, [k, n, 0, m])
+    assert rel_l2(gpu.read(y, np.float32, m * n).reshape(m, n), want) < TOL
+    gpu.dispatch(enc, name, [(xb, 0), (w.buf, 0), (y, 0)] + extra, [k, n, 1, m])             # accum
+    assert rel_l2(gpu.read(y, np.float32, m * n).reshape(m, n), 2 * want) < TOL
+    xh = gpu.upload(x.astype(np.float16))
+    want_h = oracle.matmul_kq(raw, t, n, k, x.astype(np.float16).astype(np.float32))
+    gpu.memset(y, 0)
+    gpu.dispatch(enc, name + "_sk", [(xh, 0), (w.buf, 0), (y, 0)] + extra, [k, n, m, 4])
+    assert rel_l2(gpu.read(y, np.float32, m * n).reshape(m, n), want_h) < TOL
+    for b in (w.buf, xb, y, dummy, xh):
+        gpu.free(b)
+
+
+def test_prefill_entries_need_reserved_scratch_beyond_the_builtin_array(gpu):
+    m, n, k = 1100, 128, 4096                          # m * k * 2 bytes > 8 MiB
+    raw = synth_weights(Q4_K, n, k)
+    w = gpu.load_weight(raw, Q4_K, n, k)
+    x = activations(m, k, seed=3)
+    xb, y = gpu.upload(x), gpu.alloc(m * n)
+    have = oblib.load().ojas_b200_reserved_bytes(gpu.ctx)
+    if have < gpu.gemm_workspace_bytes(m, k):
+        with pytest.raises(ob.OjasB200Error, match="ojas_b200_reserve"):
+            gpu.dispatch(gpu.begin(), "gemm_mm_q4k", [(xb, 0), (w.buf, 0), (y, 0)], [k, n, 0, m])
+    gpu.reserve(gpu.gemm_workspace_bytes(m, k))
+    gpu.dispatch(gpu.begin(), "gemm_mm_q4k", [(xb, 0), (w.buf, 0), (y, 0)], [k, n, 0, m])
+    sample = [0, 700, 1099]
+    assert rel_l2(gpu.read(y, np.float32, m * n).reshape(m, n)[sample], oracle.matmul_kq(raw, Q4_K, n, k, x[sample])) < TOL
+    for b in (w.buf, xb, y):
+        gpu.free(b)
 
 
 def test_random_shapes(gpu):

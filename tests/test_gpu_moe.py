@@ -141,6 +141,47 @@ def test_both_expert_paths(gpu):
         gpu.set_option("moe_gemm_rows", 0)
 
 
+@pytest.mark.parametrize("tag,t", [("q4k", Q4_K), ("q6k", Q6_K), ("q80", ob.Q8_0)])
+def test_decode_expert_entries_by_name(gpu, tag, t):
+    """One token through the engine's decode-time expert entries (crates/ojas-cuda/src/kernels/moe.rs:75-178):
+    moe_gu_<fmt> (grid.y = picks), moe_down_<fmt>, and their _slots forms with byte-offset tables."""
+    e, ksel, d, ffn = 6, 3, 512, 768
+    wg = np.concatenate([gauss_weights(t, ffn, d, 40 + i) for i in range(e)])
+    wu = np.concatenate([gauss_weights(t, ffn, d, 50 + i) for i in range(e)])
+    wd = np.concatenate([gauss_weights(t, d, ffn, 60 + i) for i in range(e)])
+    lg_, lu_, ld_ = gpu.load_weight(wg, t, e * ffn, d), gpu.load_weight(wu, t, e * ffn, d), gpu.load_weight(wd, t, e * d, ffn)
+    x = activations(1, d, seed=70)[0]
+    idx = np.array([4, 0, 5], np.uint32)
+    wgt = np.array([0.5, 0.3, 0.2], np.float32)
+    rb_gu, rb_d = oracle.row_bytes(t, d), oracle.row_bytes(t, ffn)
+    want_act = np.stack([oracle.silu_mul(oracle.matvec_kq(wg[ex * ffn * rb_gu:(ex + 1) * ffn * rb_gu], t, ffn, d, x),
+                                         oracle.matvec_kq(wu[ex * ffn * rb_gu:(ex + 1) * ffn * rb_gu], t, ffn, d, x)) for ex in idx])
+    x0 = activations(1, d, seed=71)[0]
+    want_x = x0.copy()
+    for j, ex in enumerate(idx):
+        want_x = want_x + wgt[j] * oracle.matvec_kq(wd[ex * d * rb_d:(ex + 1) * d * rb_d], t, d, ffn, want_act[j])
+    xb, ib, wb = gpu.upload(x), gpu.upload(idx), gpu.upload(wgt)
+    act, xo = gpu.alloc(ksel * ffn), gpu.upload(x0)
+    enc = gpu.begin()
+    gpu.dispatch(enc, f"moe_gu_{tag}", [(xb, 0), (lg_.buf, 0), (lu_.buf, 0), (act, 0), (ib, 0)], [d, ffn], grid=(ffn // 8, ksel, 1))
+    got_act = gpu.read(act, np.float32, ksel * ffn).reshape(ksel, ffn)
+    assert rel_l2(got_act, want_act) < 1e-5
+    gpu.dispatch(enc, f"moe_down_{tag}", [(act, 0), (ld_.buf, 0), (xo, 0), (ib, 0), (wb, 0)], [ffn, d, ksel])
+    assert rel_l2(gpu.read(xo, np.float32, d), want_x) < TOL
+    # the same with byte-offset tables (experts "cached" where they already are)
+    from helpers import TILE_BYTES
+    og = gpu.upload((idx.astype(np.uint64) * (ffn // 8 * (d // 256) * TILE_BYTES[t])).astype(np.uint32))
+    od = gpu.upload((idx.astype(np.uint64) * (d // 8 * (ffn // 256) * TILE_BYTES[t])).astype(np.uint32))
+    gpu.memset(act, 0)
+    gpu.write(xo, x0)
+    gpu.dispatch(enc, f"moe_gu_{tag}_slots", [(xb, 0), (lg_.buf, 0), (lu_.buf, 0), (act, 0), (og, 0), (og, 0)], [d, ffn], grid=(ffn // 8, ksel, 1))
+    assert np.array_equal(gpu.read(act, np.uint32, ksel * ffn), got_act.view(np.uint32).reshape(-1))
+    gpu.dispatch(enc, f"moe_down_{tag}_slots", [(act, 0), (ld_.buf, 0), (xo, 0), (od, 0), (wb, 0)], [ffn, d, ksel])
+    assert rel_l2(gpu.read(xo, np.float32, d), want_x) < TOL
+    for b in (lg_.buf, lu_.buf, ld_.buf, xb, ib, wb, act, xo, og, od):
+        gpu.free(b)
+
+
 def test_moe_argument_errors(gpu):
     w = gpu.load_weight(gauss_weights(ob.Q8_0, 2 * 256, 256), ob.Q8_0, 2 * 256, 256)
     h, idx, wgt, out = gpu.upload(np.zeros((1, 256), np.float32)), gpu.upload(np.zeros(2, np.uint32)), gpu.upload(np.ones(2, np.float32)), gpu.alloc(256)

@@ -34,6 +34,45 @@ def test_static_scratch_gemm_matches_workspace_gemm(gpu):
             gpu.free(buf)
 
 
+def _free_bytes():
+    import torch
+    return torch.cuda.mem_get_info(0)[0]
+
+
+def test_static_scratch_gemm_allocates_nothing_and_replays_from_a_graph(gpu):
+    """After the first call on the device, calls of other shapes and formats leave the device's free memory where it
+    was (cudaMemGetInfo), and a call captured into a CUDA graph after that first call replays correctly."""
+    cases = [(Q4_K, 64, 256, 1024, 3), (Q6_K, 300, 512, 2048, 4), (ob.Q8_0, 20, 128, 512, 5)]
+    bufs = []
+    for t, m, n, k, seed in cases:
+        raw = gauss_weights(t, n, k, seed)
+        x = activations(m, k, seed=seed + 60)
+        w = gpu.load_weight(raw, t, n, k)
+        bufs.append((w, gpu.upload(x), gpu.alloc(m * n), gpu.alloc(m * n), m, n))
+    w, xb, y_ref, y_new, m, n = bufs[0]
+    gpu.gemm_static(w, xb, y_new, m)                      # the first call on this device (set-up)
+    gpu.sync()
+    before = _free_bytes()
+    for w, xb, y_ref, y_new, m, n in bufs:                # other tile widths and formats: nothing may be allocated
+        gpu.gemm_static(w, xb, y_new, m)
+    gpu.sync()
+    assert _free_bytes() == before
+    w, xb, y_ref, y_new, m, n = bufs[1]
+    gpu.gemm(w, xb, y_ref, m)
+    want = gpu.read(y_ref, np.float32, m * n)
+    gpu.graph_begin()
+    gpu.gemm_static(w, xb, y_new, m)
+    g = gpu.graph_end()
+    for _ in range(3):
+        gpu.memset(y_new, 0)
+        gpu.graph_launch(g)
+        assert rel_l2(gpu.read(y_new, np.float32, m * n), want) < 1e-5
+    gpu.graph_destroy(g)
+    for w, xb, y_ref, y_new, m, n in bufs:
+        for buf in (w.buf, xb, y_ref, y_new):
+            gpu.free(buf)
+
+
 def test_static_scratch_limit_is_enforced(gpu):
     cap = oblib.load().ojas_b200_gemm_static_capacity()
     assert cap == 8 << 20
