@@ -209,6 +209,33 @@ OJAS_B200_API int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32
                                     size_t KSEL, size_t d, size_t ffn, float *out, int accum, void *workspace,
                                     size_t workspace_bytes);
 
+/* ---- expert residency: replaces ExpertCache (crates/ojas-cuda/src/expert_cache.rs:34-160).  A bounded arena of
+ * expert-sized slots in device memory with least-recently-used eviction; misses are streamed from the host through
+ * pinned staging memory and re-laid into tiles on the device.  gather() returns byte offsets into the arena: what the
+ * moe_gu_<fmt>_slots / moe_down_<fmt>_slots entries take (crates/ojas-cuda/src/kernels/moe.rs:127-178).
+ * create / destroy allocate and free; gather allocates nothing.  The expert_lru_* calls are the bookkeeping alone
+ * (pure host code): which slot serves which expert, hits, misses, evictions. */
+typedef struct ojas_b200_expert_lru ojas_b200_expert_lru;
+typedef struct ojas_b200_expert_cache ojas_b200_expert_cache;
+OJAS_B200_API int ojas_b200_expert_lru_create(size_t slots, ojas_b200_expert_lru **out);
+OJAS_B200_API void ojas_b200_expert_lru_destroy(ojas_b200_expert_lru *lru);
+OJAS_B200_API int ojas_b200_expert_lru_plan(ojas_b200_expert_lru *lru, const uint32_t *ids, size_t n, uint32_t *slot_out, uint8_t *miss_out);
+OJAS_B200_API void ojas_b200_expert_lru_stats(const ojas_b200_expert_lru *lru, size_t out[3]);
+/* One cache holds experts of one tensor: [N, K] of ggml_type each (N a multiple of 8).  budget_bytes / slot bytes
+ * slots, at least one. */
+OJAS_B200_API int ojas_b200_expert_cache_create(ojas_b200_ctx *ctx, uint32_t ggml_type, size_t N, size_t K, size_t budget_bytes,
+                                                ojas_b200_expert_cache **out);
+OJAS_B200_API void ojas_b200_expert_cache_destroy(ojas_b200_expert_cache *cache);
+OJAS_B200_API size_t ojas_b200_expert_cache_slots(const ojas_b200_expert_cache *cache);
+OJAS_B200_API size_t ojas_b200_expert_cache_slot_bytes(const ojas_b200_expert_cache *cache);
+OJAS_B200_API void *ojas_b200_expert_cache_arena(const ojas_b200_expert_cache *cache);
+OJAS_B200_API void ojas_b200_expert_cache_stats(const ojas_b200_expert_cache *cache, size_t out[4]);
+/* ids [n] -> offsets_out [n] (bytes into the arena).  load(user, id, dst, bytes) fills dst with expert id's GGUF blocks
+ * (bytes = ojas_b200_raw_bytes(ggml_type, N, K)) and returns 0.  More distinct ids than slots: OJAS_B200_E_LIMIT. */
+OJAS_B200_API int ojas_b200_expert_cache_gather(ojas_b200_expert_cache *cache, const uint32_t *ids, size_t n,
+                                                int (*load)(void *user, uint32_t id, void *dst, size_t bytes), void *user,
+                                                uint64_t *offsets_out);
+
 /* ---- tensor-parallel shard planning (host).  No counterpart in the reference, which is single-GPU
  * (its only distributed code is a TCP pipeline for another backend, crates/ojas-swarm/src/lib.rs:12-40);
  * the shard shapes follow the weight contract of crates/ojas-cuda/src/kernels/gemm_q.rs:1-4.

@@ -61,6 +61,17 @@ SIGNATURES = {
     "ojas_b200_moe_topk": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_moe_workspace_bytes": (_sz, [_sz, _sz, _sz, _sz, _sz]),
     "ojas_b200_moe_ffn": (_i, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
+    "ojas_b200_expert_lru_create": (_i, [_sz, C.POINTER(_vp)]),
+    "ojas_b200_expert_lru_destroy": (None, [_vp]),
+    "ojas_b200_expert_lru_plan": (_i, [_vp, C.POINTER(_u32), _sz, C.POINTER(_u32), C.POINTER(C.c_uint8)]),
+    "ojas_b200_expert_lru_stats": (None, [_vp, C.POINTER(_sz)]),
+    "ojas_b200_expert_cache_create": (_i, [_vp, _u32, _sz, _sz, _sz, C.POINTER(_vp)]),
+    "ojas_b200_expert_cache_destroy": (None, [_vp]),
+    "ojas_b200_expert_cache_slots": (_sz, [_vp]),
+    "ojas_b200_expert_cache_slot_bytes": (_sz, [_vp]),
+    "ojas_b200_expert_cache_arena": (_vp, [_vp]),
+    "ojas_b200_expert_cache_stats": (None, [_vp, C.POINTER(_sz)]),
+    "ojas_b200_expert_cache_gather": (_i, [_vp, C.POINTER(_u32), _sz, _vp, _vp, C.POINTER(_u64)]),
     "ojas_b200_tp_shard_rows": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "ojas_b200_tp_shard_k": (_i, [_sz, _i, _i, C.POINTER(_sz), C.POINTER(_sz)]),
     "ojas_b200_tp_slice_k_host": (_i, [_u32, _vp, _sz, _sz, _sz, _sz, _vp]),

@@ -313,6 +313,72 @@ class B200Gpu:
         return arr
 
 
+class ExpertCache:
+    """Bounded arena of expert slots with LRU eviction (``ExpertCache``, crates/ojas-cuda/src/expert_cache.rs:34-160).
+    ``gather(ids, load)`` makes the experts resident and returns their byte offsets into ``arena``; ``load(id)`` returns
+    the expert's GGUF blocks as a uint8 array (where a real caller reads from its model file)."""
+
+    def __init__(self, gpu: B200Gpu, ggml_type: int, n: int, k: int, budget_bytes: int):
+        self.gpu, self._l = gpu, gpu._l
+        h = C.c_void_p()
+        gpu._ck(self._l.ojas_b200_expert_cache_create(gpu.ctx, ggml_type, n, k, budget_bytes, C.byref(h)))
+        self._h = h
+        self.raw_bytes = raw_bytes(ggml_type, n, k)
+
+    @property
+    def slots(self) -> int:
+        return int(self._l.ojas_b200_expert_cache_slots(self._h))
+
+    @property
+    def slot_bytes(self) -> int:
+        return int(self._l.ojas_b200_expert_cache_slot_bytes(self._h))
+
+    @property
+    def resident_bytes(self) -> int:
+        return self.slots * self.slot_bytes
+
+    @property
+    def arena(self) -> Buf:
+        return Buf(int(self._l.ojas_b200_expert_cache_arena(self._h)), self.resident_bytes)
+
+    @property
+    def stats(self) -> dict:
+        out = (C.c_size_t * 4)()
+        self._l.ojas_b200_expert_cache_stats(self._h, out)
+        return {"hits": out[0], "misses": out[1], "evictions": out[2], "bytes_streamed": out[3]}
+
+    def hit_rate(self) -> float:
+        st = self.stats
+        total = st["hits"] + st["misses"]
+        return st["hits"] / total if total else 0.0
+
+    def gather(self, ids, load) -> np.ndarray:
+        ids = np.ascontiguousarray(ids, np.uint32)
+        offs = np.zeros(ids.size, np.uint64)
+        nbytes = self.raw_bytes
+
+        @C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t)
+        def cb(_user, expert, dst, n):
+            try:
+                data = np.ascontiguousarray(load(int(expert))).view(np.uint8).reshape(-1)
+                if data.size != n:
+                    return 1
+                C.memmove(dst, data.ctypes.data, n)
+                return 0
+            except Exception:
+                return 1
+
+        self.gpu._ck(self._l.ojas_b200_expert_cache_gather(self._h, ids.ctypes.data_as(C.POINTER(C.c_uint32)), ids.size, cb, None,
+                                                           offs.ctypes.data_as(C.POINTER(C.c_uint64))))
+        assert nbytes == self.raw_bytes
+        return offs
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._l.ojas_b200_expert_cache_destroy(self._h)
+            self._h = None
+
+
 # ---------------------------------------------------------------------- host utilities (no GPU)
 def raw_bytes(ggml_type: int, n: int, k: int) -> int:
     return int(_lib.load().ojas_b200_raw_bytes(ggml_type, n, k))

@@ -182,6 +182,40 @@ def test_decode_expert_entries_by_name(gpu, tag, t):
         gpu.free(b)
 
 
+def test_expert_cache_streams_and_serves_offsets(gpu):
+    """Experts live on the host; a cache of three slots serves a stream of tokens through the _slots entries.  Results
+    equal those of the fully resident tensors, and the cache reports its hits, misses and evictions."""
+    t, e, ksel, d, ffn = Q4_K, 6, 2, 512, 768
+    wg = [gauss_weights(t, ffn, d, 80 + i) for i in range(e)]
+    wu = [gauss_weights(t, ffn, d, 90 + i) for i in range(e)]
+    lg_, lu_ = gpu.load_weight(np.concatenate(wg), t, e * ffn, d), gpu.load_weight(np.concatenate(wu), t, e * ffn, d)
+    cg = ob.ExpertCache(gpu, t, ffn, d, 3 * ob.repacked_bytes(t, ffn, d))
+    cu = ob.ExpertCache(gpu, t, ffn, d, 3 * ob.repacked_bytes(t, ffn, d))
+    assert cg.slots == 3
+    x = activations(1, d, seed=75)[0]
+    xb = gpu.upload(x)
+    act, ref = gpu.alloc(ksel * ffn), gpu.alloc(ksel * ffn)
+    enc = gpu.begin()
+    for picks in ([0, 1], [1, 2], [0, 1], [3, 4], [4, 5], [0, 5]):
+        idx = np.array(picks, np.uint32)
+        ib = gpu.upload(idx)
+        gpu.dispatch(enc, "moe_gu_q4k", [(xb, 0), (lg_.buf, 0), (lu_.buf, 0), (ref, 0), (ib, 0)], [d, ffn], grid=(1, ksel, 1))
+        og = gpu.upload(cg.gather(idx, lambda i: wg[i]).astype(np.uint32))
+        ou = gpu.upload(cu.gather(idx, lambda i: wu[i]).astype(np.uint32))
+        gpu.dispatch(enc, "moe_gu_q4k_slots", [(xb, 0), (cg.arena, 0), (cu.arena, 0), (act, 0), (og, 0), (ou, 0)], [d, ffn], grid=(1, ksel, 1))
+        assert np.array_equal(gpu.read(act, np.uint32, ksel * ffn), gpu.read(ref, np.uint32, ksel * ffn))
+        for b in (ib, og, ou):
+            gpu.free(b)
+    st = cg.stats
+    assert st["hits"] == 5 and st["misses"] == 7 and st["evictions"] == 4 and st["bytes_streamed"] == 7 * ob.raw_bytes(t, ffn, d)
+    with pytest.raises(ob.OjasB200Error, match="more distinct experts"):
+        cg.gather(np.array([0, 1, 2, 3], np.uint32), lambda i: wg[i])
+    cg.close()
+    cu.close()
+    for b in (lg_.buf, lu_.buf, xb, act, ref):
+        gpu.free(b)
+
+
 def test_moe_argument_errors(gpu):
     w = gpu.load_weight(gauss_weights(ob.Q8_0, 2 * 256, 256), ob.Q8_0, 2 * 256, 256)
     h, idx, wgt, out = gpu.upload(np.zeros((1, 256), np.float32)), gpu.upload(np.zeros(2, np.uint32)), gpu.upload(np.ones(2, np.float32)), gpu.alloc(256)

@@ -83,3 +83,35 @@ def test_no_gpu_fails_loudly():
     ctx = C.c_void_p()
     rc = l.ojas_b200_create(9999, None, C.byref(ctx))
     assert rc != 0 and not ctx.value
+
+
+def test_expert_lru_bookkeeping():
+    """The expert cache's slot bookkeeping (host code): hits, misses, least-recently-used eviction, and the refusal of a
+    request that names more distinct experts than there are slots (crates/ojas-cuda/src/expert_cache.rs:96-150)."""
+    l = oblib.load()
+    h = C.c_void_p()
+    assert l.ojas_b200_expert_lru_create(3, C.byref(h)) == 0
+
+    def plan(ids):
+        ids = np.asarray(ids, np.uint32)
+        slot, miss = np.zeros(ids.size, np.uint32), np.zeros(ids.size, np.uint8)
+        rc = l.ojas_b200_expert_lru_plan(h, ids.ctypes.data_as(C.POINTER(C.c_uint32)), ids.size, slot.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                         miss.ctypes.data_as(C.POINTER(C.c_uint8)))
+        return rc, list(slot), list(miss)
+
+    def stats():
+        out = (C.c_size_t * 3)()
+        l.ojas_b200_expert_lru_stats(h, out)
+        return tuple(out)
+
+    assert plan([7, 9]) == (0, [0, 1], [1, 1])
+    assert plan([9, 7, 9]) == (0, [1, 0, 1], [0, 0, 0])           # hits: an address, not a copy
+    assert plan([4]) == (0, [2], [1])                              # the free slot
+    assert plan([5]) == (0, [0], [1])                              # evicts 7 (used before 9 and 4)
+    assert plan([9, 4]) == (0, [1, 2], [0, 0])
+    assert plan([7]) == (0, [0], [1])                              # evicts 5: the least recently used now
+    assert stats() == (5, 5, 2)
+    rc, _, _ = plan([1, 2, 3, 4])                                  # four distinct experts, three slots
+    assert rc == -6 and stats() == (5, 5, 2)                       # refused, nothing changed
+    assert plan([1, 1, 2, 2, 3]) == (0, [1, 1, 2, 2, 0], [1, 0, 1, 0, 1])
+    l.ojas_b200_expert_lru_destroy(h)
