@@ -209,6 +209,32 @@ OJAS_B200_API int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32
                                     size_t KSEL, size_t d, size_t ffn, float *out, int accum, void *workspace,
                                     size_t workspace_bytes);
 
+/* ---- loader side (host code): a GGUF tensor directory (crates/ojas-formats/src/gguf.rs:158-205, 298-455: versions 2
+ * and 3, one file) and a cache file of repacked weights keyed to the source file by size and modification time
+ * (crates/ojas-models/src/weights.rs:14-32).  err (may be null) receives a message on failure.
+ * GGUF stores a matrix as dims[0] = K (contiguous), dims[1] = N.  Rows of several matrices that share K (Q, K, V; gate,
+ * up) become ONE matrix by repacking each part into consecutive 8-row units of one buffer: parts whose row counts are
+ * multiples of 8 simply follow one another (crates/ojas-cuda/src/qwen35.rs:168-189 concatenates along N the same way). */
+typedef struct ojas_b200_gguf ojas_b200_gguf;
+typedef struct ojas_b200_weight_cache ojas_b200_weight_cache;
+OJAS_B200_API int ojas_b200_gguf_open(const char *path, ojas_b200_gguf **out, char *err, size_t errlen);
+OJAS_B200_API void ojas_b200_gguf_close(ojas_b200_gguf *g);
+OJAS_B200_API size_t ojas_b200_gguf_tensor_count(const ojas_b200_gguf *g);
+OJAS_B200_API int ojas_b200_gguf_tensor_info(const ojas_b200_gguf *g, size_t index, const char **name, uint32_t *ggml_type, uint32_t *ndims,
+                                             uint64_t dims[4], uint64_t *file_offset, uint64_t *bytes);
+OJAS_B200_API long long ojas_b200_gguf_find(const ojas_b200_gguf *g, const char *name);
+OJAS_B200_API int ojas_b200_gguf_read_raw(const ojas_b200_gguf *g, size_t index, void *dst, size_t bytes);
+/* build: every Q4_K / Q6_K / Q8_0 matrix of the GGUF re-laid on the host and written to cache_path (atomically).
+ * open: maps the file; with gguf_path given it must be the file the cache was built from, else OJAS_B200_E_UNSUPPORTED
+ * (rebuild).  entry: name, type, [N, K] and a pointer to the repacked bytes inside the mapping. */
+OJAS_B200_API int ojas_b200_weight_cache_build(const char *gguf_path, const char *cache_path, char *err, size_t errlen);
+OJAS_B200_API int ojas_b200_weight_cache_open(const char *cache_path, const char *gguf_path, ojas_b200_weight_cache **out, char *err,
+                                              size_t errlen);
+OJAS_B200_API void ojas_b200_weight_cache_close(ojas_b200_weight_cache *cache);
+OJAS_B200_API size_t ojas_b200_weight_cache_count(const ojas_b200_weight_cache *cache);
+OJAS_B200_API int ojas_b200_weight_cache_entry(const ojas_b200_weight_cache *cache, size_t index, const char **name, uint32_t *ggml_type,
+                                               uint64_t *N, uint64_t *K, const void **data, uint64_t *bytes);
+
 /* ---- expert residency: replaces ExpertCache (crates/ojas-cuda/src/expert_cache.rs:34-160).  A bounded arena of
  * expert-sized slots in device memory with least-recently-used eviction; misses are streamed from the host through
  * pinned staging memory and re-laid into tiles on the device.  gather() returns byte offsets into the arena: what the

@@ -61,6 +61,17 @@ SIGNATURES = {
     "ojas_b200_moe_topk": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_moe_workspace_bytes": (_sz, [_sz, _sz, _sz, _sz, _sz]),
     "ojas_b200_moe_ffn": (_i, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
+    "ojas_b200_gguf_open": (_i, [C.c_char_p, C.POINTER(_vp), C.c_char_p, _sz]),
+    "ojas_b200_gguf_close": (None, [_vp]),
+    "ojas_b200_gguf_tensor_count": (_sz, [_vp]),
+    "ojas_b200_gguf_tensor_info": (_i, [_vp, _sz, C.POINTER(C.c_char_p), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u64)]),
+    "ojas_b200_gguf_find": (C.c_longlong, [_vp, C.c_char_p]),
+    "ojas_b200_gguf_read_raw": (_i, [_vp, _sz, _vp, _sz]),
+    "ojas_b200_weight_cache_build": (_i, [C.c_char_p, C.c_char_p, C.c_char_p, _sz]),
+    "ojas_b200_weight_cache_open": (_i, [C.c_char_p, C.c_char_p, C.POINTER(_vp), C.c_char_p, _sz]),
+    "ojas_b200_weight_cache_close": (None, [_vp]),
+    "ojas_b200_weight_cache_count": (_sz, [_vp]),
+    "ojas_b200_weight_cache_entry": (_i, [_vp, _sz, C.POINTER(C.c_char_p), C.POINTER(_u32), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_vp), C.POINTER(_u64)]),
     "ojas_b200_expert_lru_create": (_i, [_sz, C.POINTER(_vp)]),
     "ojas_b200_expert_lru_destroy": (None, [_vp]),
     "ojas_b200_expert_lru_plan": (_i, [_vp, C.POINTER(_u32), _sz, C.POINTER(_u32), C.POINTER(C.c_uint8)]),

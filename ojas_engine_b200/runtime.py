@@ -164,6 +164,14 @@ class B200Gpu:
             self.free(tmp)
         return Lin(out, ggml_type, n, k)
 
+    def load_repacked(self, packed: np.ndarray, ggml_type: int, n: int, k: int) -> Lin:
+        """A weight that is already in the tile layout (an entry of the repacked-weight cache): one upload."""
+        packed = np.ascontiguousarray(packed).view(np.uint8).reshape(-1)
+        want = self._l.ojas_b200_repacked_bytes(ggml_type, n, k)
+        if want == 0 or packed.size != want:
+            raise OjasB200Error(-1, f"load_repacked: type {ggml_type} [{n},{k}] needs {want} bytes, got {packed.size}")
+        return Lin(self.upload(packed), ggml_type, n, k)
+
     # ------------------------------------------------------------------ typed entry points
     def quant_q8k(self, x: Buf, m: int, k: int, q: Buf, scales: Buf, bsums: Buf) -> None:
         self._ck(self._l.ojas_b200_quant_q8k(self._ctx, C.c_void_p(x.ptr), m, k, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr)))
