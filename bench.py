@@ -149,17 +149,19 @@ def run_reference(args) -> None:
         return
     threads = os.cpu_count() or 1
     native = oracle_native_ok()
-    weights = ring_weights(4, 0)
-    x = np.random.default_rng(1).standard_normal((4, K_COLS), dtype=np.float32)
-    per_step = max(1, 8)  # matvecs per step: a bounded sample of the 64-weight pass
     import oracle
-    import ojas_engine_b200 as ob
+    # This arm runs the CPU code only: its weights are the oracle's own block generator (the CPU time of a block dot
+    # does not depend on the values), so the CUDA library is never loaded here.
+    base = oracle.synth_blocks(oracle.Q4_K, N_ROWS * K_COLS // 256).reshape(N_ROWS, -1)
+    weights = [np.ascontiguousarray(np.roll(base, 97 * i, axis=0)).reshape(-1) for i in range(4)]
+    x = np.random.default_rng(1).standard_normal((4, K_COLS), dtype=np.float32)
+    per_step = 8  # matvecs per step: a bounded sample of the 64-weight pass
     for _ in range(max(args.warmup, 1)):
-        oracle.matvec_kq(weights[0], ob.Q4_K, N_ROWS, K_COLS, x[0], threads, native)
+        oracle.matvec_kq(weights[0], oracle.Q4_K, N_ROWS, K_COLS, x[0], threads, native)
     t0 = time.perf_counter()
     for s in range(args.steps):
         for j in range(per_step):
-            oracle.matvec_kq(weights[j % 4], ob.Q4_K, N_ROWS, K_COLS, x[j % 4], threads, native)
+            oracle.matvec_kq(weights[j % 4], oracle.Q4_K, N_ROWS, K_COLS, x[j % 4], threads, native)
     el = time.perf_counter() - t0
     gbs = args.steps * per_step * ALGO_BYTES_PER_LAUNCH / el / 1e9
     sample = f"{per_step} of the {RING} ring GEMVs per step, oracle matvec_kq ({'-march=native' if native else 'portable'} build)"
@@ -709,7 +711,7 @@ def profile_traffic():
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the additional GEMV shapes")

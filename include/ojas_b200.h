@@ -60,13 +60,13 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
  * engine reads its OJAS_* switches, crates/ojas-core/src/config.rs:1-22): GEMVs and the GEMM are launched
  * with programmatic dependent launch, so a kernel's weight prefetch and set-up overlap the tail of the
  * kernel before it in the stream (activations and y are only touched after the wait on that kernel).
- * "gemv_mma" (0, 1 = default, 2): batches on the tensor-core inner loops never / from three rows (Q4_K,
- * Q6_K) or two rows (Q8_0) / always, one row included.  "gemv_slim" (0, 1 = default, 2): the half-size single-row Q4_K kernel
- * never / for small matrices / always.  "gemm_ksplit": 0 = K ranges balanced across the SMs, S > 0 =
- * every tile's K range cut into S pieces.  "moe_gemm_rows" (default 0 = off): from this many rows per expert
+ * "gemv_mma" (0, 1 = default): pre-quantized Q4_K batches of three or more rows on the integer tensor-core kernel
+ * never / always.  "gemv_warps", "gemv_stages" (0 = chosen per shape): upper bounds on the warps per CTA (a power of
+ * two, at most 16) and on the depth of a warp's weight ring (1, 2 or 4) of the GEMV kernel; a bound the shape does
+ * not fit under falls back to the next smaller choice.  "gemm_ksplit": 0 = K ranges balanced across the SMs,
+ * S > 0 = every tile's K range cut into S pieces.  "moe_gemm_rows" (default 0 = off): from this many rows per expert
  * on average the expert FFN runs as grouped tensor-core GEMMs (faster at prefill sizes; the FFN output is
- * then 4e-3..6e-3 from the CPU path instead of exact in its integer block dots).  "gemv_depth" is kept for
- * compatibility and ignored. */
+ * then 4e-3..6e-3 from the CPU path instead of exact in its integer block dots). */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
