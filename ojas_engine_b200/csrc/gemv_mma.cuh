@@ -385,6 +385,7 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_q4k_experts_kernel
     constexpr int NT = 8 * NTILE, TB = tile_bytes(OJAS_B200_Q4_K), STEP = 2 * TB;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int act_e[EXPERT_MAX_E], act_n;                    // experts that have rows, in order
+    __shared__ unsigned share[2];                                 // this CTA's range of the tile list
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g8 = lane >> 2, q4 = lane & 3;
     const int nsb = a.nsb, K = a.K, nst = a.nst;
@@ -401,18 +402,47 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_q4k_experts_kernel
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     grid_dependency_wait();                                        // counts, offsets and activations come from kernels before this one
+    const int tpe = (a.N + 15) >> 4;                               // 16-row tiles per (expert, tensor)
     if (threadIdx.x == 0) {
+        // The CTA's share of the work list is a share of its COST, in units of ROUNDS.  A round is the tiles the CTA's
+        // warps take together (one each) from one (expert, tensor) pair: a share that ended inside a round would pay a
+        // whole round for a few tiles, and a tile of an expert with more rows does more token tiles per step (and more
+        // passes), so shares by tile count would leave the CTAs of quiet experts idle.
+        // Cost of a round = sum over the expert's passes of (2 + 3 * token tiles of the pass).
         int n = 0;
-        for (int e = 0; e < a.E; e++)
-            if (__ldg(a.counts + e) > 0) act_e[n++] = e;
+        unsigned long long total_cost = 0;
+        unsigned ecost[EXPERT_MAX_E];
+        const unsigned rpe = (unsigned)((tpe + warps - 1) / warps), rounds_e = (unsigned)a.nw * rpe;
+        for (int e = 0; e < a.E; e++) {
+            const int cnt = __ldg(a.counts + e);
+            if (cnt <= 0) continue;
+            const unsigned full = (unsigned)(cnt / NT), rest = (unsigned)(cnt % NT);
+            ecost[n] = full * (2u + 3u * NTILE) + (rest ? 2u + 3u * ((rest + 7u) >> 3) : 0u);
+            total_cost += (unsigned long long)ecost[n] * rounds_e;
+            act_e[n++] = e;
+        }
         act_n = n;
+        for (int side = 0; side < 2; side++) {
+            unsigned long long pos = total_cost * (blockIdx.x + side) / gridDim.x;
+            unsigned tile = 0;
+            int i = 0;
+            for (; i < n; i++) {
+                const unsigned long long span = (unsigned long long)ecost[i] * rounds_e;
+                if (pos < span) break;
+                pos -= span;
+                tile += (unsigned)(a.nw * tpe);
+            }
+            if (i < n) {
+                const unsigned rnd = (unsigned)(pos / ecost[i]), pl = rnd / rpe, r = rnd - pl * rpe;
+                const unsigned in_pair = r * (unsigned)warps < (unsigned)tpe ? r * (unsigned)warps : (unsigned)tpe;
+                tile += pl * (unsigned)tpe + in_pair;
+            }
+            share[side] = tile;
+        }
     }
     __syncthreads();
     grid_launch_dependents();
-    const int tpe = (a.N + 15) >> 4;                               // 16-row tiles per (expert, tensor)
-    const unsigned total = (unsigned)act_n * (unsigned)a.nw * (unsigned)tpe;
-    const unsigned c0 = (unsigned)(((unsigned long long)total * blockIdx.x) / gridDim.x);
-    const unsigned c1 = (unsigned)(((unsigned long long)total * (blockIdx.x + 1)) / gridDim.x);
+    const unsigned c0 = share[0], c1 = share[1];
     const int units_total = (a.N + 7) >> 3;
 
     // ---- issue side (lane 0): the warp's steps in order: for every pair segment of the CTA's range, for every pass
