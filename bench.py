@@ -431,6 +431,8 @@ def run_case(args) -> None:
         import ojas_engine_b200 as ob
         hbm_peak, tc_peak, _ = measured_peaks()
         gpu = ob.B200Gpu(0)
+        for kv in args.opt:
+            gpu.set_option(kv.split("=")[0], int(kv.split("=")[1]))
         parts = args.case.split(":")          # moe[:TOKENS[:GEMM_ROWS]]
         print(json.dumps(moe_case(gpu, ob, args.steps, args.warmup, hbm_peak, tc_peak, int(parts[1]) if len(parts) > 1 else 64,
                                   int(parts[2]) if len(parts) > 2 else 0)))
@@ -721,6 +723,7 @@ def main() -> None:
     ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: force the K split (0 = automatic)")
     ap.add_argument("--warps", type=int, default=0, help="--case: the gemv_warps option (warps per CTA; 0 = chosen per shape)")
     ap.add_argument("--stages", type=int, default=0, help="--case: the gemv_stages option (ring stages per warp; 0 = chosen per shape)")
+    ap.add_argument("--opt", action="append", default=[], help="--case moe: a library option as key=value (repeatable)")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (default: with)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

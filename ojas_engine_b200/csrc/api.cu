@@ -128,6 +128,7 @@ extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int val
         ctx->gemv_stages = value;
         return 0;
     }
+    if (!strcmp(key, "moe_i8")) { ctx->moe_i8 = value != 0; return 0; }
     if (!strcmp(key, "moe_gemm_rows")) {
         if (value < 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: moe_gemm_rows must be >= 0");
         ctx->moe_gemm_rows = value;

@@ -24,6 +24,7 @@ struct ojas_b200_ctx {
     int moe_gemm_rows = 0;       // expert FFN: grouped tensor-core GEMMs from this many rows per expert on average (0: never)
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
     int pdl = 1;                 // launch GEMVs with programmatic dependent launch (overlap with the kernel before)
+    int moe_i8 = 0;                      // 1: decode-sized Q4_K expert FFNs on the int8 tcgen05 kernel too (the prefill form always uses it)
     void *act_scratch = nullptr;         // device scratch for a batch's Q8_K activations (values, scales, block sums)
     void *reserved = nullptr;            // scratch the host reserved with ojas_b200_reserve (never grown inside a compute call)
     size_t reserved_bytes = 0;
@@ -118,6 +119,12 @@ void *ojas_scratch_for(ojas_b200_ctx *ctx, size_t bytes, const char *who);
 int ojas_gemv_selected(ojas_b200_ctx *ctx, uint32_t type, int form, const float *x, const void *w, const uint32_t *sel, size_t sel_stride,
                        const float *alpha, float *y, size_t K, size_t N);
 int ojas_silu_mul_inplace(ojas_b200_ctx *ctx, float *g, const float *u, size_t n);
+int ojas_gemm_prep_q8k(ojas_b200_ctx *ctx, const int8_t *q, const float *scales, void *xh, size_t rows, size_t K);
+size_t ojas_experts_i8_meta_bytes(size_t positions, size_t K);
+int ojas_experts_i8_pack(ojas_b200_ctx *ctx, const int8_t *q, const float *scales, const int32_t *bsums, const int *row_index, size_t positions,
+                         size_t K, int8_t *q_out, void *meta);
+int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const void *meta,
+                    size_t positions, const int *counts, const int *offsets, size_t E, size_t K, size_t N, int kparts, size_t part_stride);
 int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
                           const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
                           size_t rows_hint);

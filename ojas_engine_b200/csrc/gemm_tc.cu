@@ -21,6 +21,7 @@
 #include <cuda.h>
 
 #include "act_quant.cuh"
+#include "tc_util.cuh"
 
 namespace {
 
@@ -33,7 +34,6 @@ constexpr int WQ_BUFS_MAX = 3;
 __host__ __device__ constexpr int wq_bytes(int type) { return (BM / OJAS_TILE_ROWS) * tile_quant_bytes((uint32_t)type); }
 // raw tiles in flight: three, or two of the large Q8_0 tiles (so that four activation stages still fit)
 __host__ __device__ constexpr int wq_bufs(int type) { return type == OJAS_B200_Q8_0 ? 2 : 3; }
-constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
 
 struct GemmArgs {
     const uint8_t *w;    // first tile of the weight rows (layout: common.cuh)
@@ -50,105 +50,10 @@ struct GemmArgs {
     unsigned *status;    // device-visible status word of the context
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {   // non-blocking probe
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {    // may suspend the thread until the phase completes or a hardware time limit passes
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-
-// Bounded wait.  Returns false if the CTA is aborting (this wait or another one ran out).  `nap` > 0 puts the
-// thread to sleep for that many nanoseconds between probes: roles that wait for a whole tile must not compete
-// with the working warps for issue slots.
-__device__ __noinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code, unsigned nap) {
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 32; i++) {
-            if (mbar_try(bar, parity)) return true;
-            if (nap) __nanosleep(nap);
-        }
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
-            *abort_flag = 1;
-            atomicOr(status, code);
-            __threadfence_system();
-            return false;
-        }
-    }
-}
-
-// Single-thread roles (MMA issue, TMA) and warp leaders: one probe, then probes `nap` nanoseconds apart.  A
-// thread that spins on a barrier takes issue slots from the dequantizing warps on its scheduler, and there are
-// half a dozen waiting threads at any time; the short sleeps cost less than that contention.
-constexpr unsigned OJAS_GEMM_NAP = 32u;
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code,
-                                               unsigned nap = OJAS_GEMM_NAP) {
-    if (mbar_test(bar, parity)) return true;
-    return mbar_wait(bar, parity, abort_flag, status, code, nap);
-}
-
-// Warp form.  The common case (the phase is already complete) is one probe by all lanes and a vote; otherwise
-// lane 0 waits and the result is broadcast.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
-    if (__all_sync(0xffffffffu, mbar_test(bar, parity))) return true;
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, code, OJAS_GEMM_NAP) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    return ok != 0;
-}
-// The same for waits that are known to be long (a whole tile): one probe, then sleep between probes.
-__device__ __forceinline__ bool mbar_wait_warp_long(uint64_t *bar, uint32_t parity, volatile int *abort_flag, unsigned *status, unsigned code) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = (mbar_test(bar, parity) || mbar_wait(bar, parity, abort_flag, status, code, 256u)) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    return ok != 0;
-}
-
-__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *tmap, int x, int y, uint64_t *bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tmap), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, groups of eight rows 1024
-// bytes apart (stride byte offset), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);        // start address
-    d |= (uint64_t)1 << 16;                              // leading byte offset (unused with a swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset
-    d |= (uint64_t)1 << 46;                              // descriptor version
-    d |= (uint64_t)2 << 61;                              // 128-byte swizzle
-    return d;
-}
-
 // kind::f16, A and B f16 K-major, D f32, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t umma_idesc(int bn) {
     return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
-
-__device__ __forceinline__ void umma_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // Zero 32 columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_zero32(uint32_t taddr) {
@@ -309,22 +214,26 @@ __global__ void __launch_bounds__(256) gemm_prep_kernel(const XIN *x, __half *xh
     reinterpret_cast<uint4 *>(xh + sb * 256)[lane] = out;
 }
 
-// ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
+// The same tile source from activations that are Q8_K already (q int8 [rows, K], scales f32 per 256): f16(scale * q) in
+// the K-quant k order.  One warp per 256 values.
+__global__ void __launch_bounds__(256) gemm_prep_q8k_kernel(const int8_t *q, const float *scales, __half *xh, long long n_sb) {
+    const int lane = threadIdx.x & 31;
+    const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    grid_launch_dependents();
+    grid_dependency_wait();
+    if (sb >= n_sb) return;
+    const uint2 w = __ldg(reinterpret_cast<const uint2 *>(q + sb * 256) + lane);
+    const float sx = __ldg(scales + sb);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __fmul_rn(sx, (float)(int)(signed char)(((i < 4 ? w.x : w.y) >> (8 * (i & 3))) & 0xffu));
+    uint4 out;
+    out.x = h2_as_u32(__floats2half2_rn(v[0], v[2])); out.y = h2_as_u32(__floats2half2_rn(v[1], v[3]));
+    out.z = h2_as_u32(__floats2half2_rn(v[4], v[6])); out.w = h2_as_u32(__floats2half2_rn(v[5], v[7]));
+    reinterpret_cast<uint4 *>(xh + sb * 256)[lane] = out;
 }
 
+// ---------------------------------------------------------------- host side
 size_t gemm_ts_smem_bytes(int bn, int type) {
     return 1024 + (size_t)ts_b_stages(bn, type) * bn * BK * 2 + (size_t)wq_bufs(type) * wq_bytes(type) +
            TS_EPI_WARPS * TS_EPI_TILE_BYTES + TS_BAR_BYTES;
@@ -523,6 +432,16 @@ int ojas_gemm_prep(ojas_b200_ctx *ctx, const float *x, void *xh, size_t rows, si
     if (quant) gemm_prep_kernel<true, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
     else gemm_prep_kernel<false, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, (__half *)xh, n_sb, nullptr);
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
+    return 0;
+}
+
+int ojas_gemm_prep_q8k(ojas_b200_ctx *ctx, const int8_t *q, const float *scales, void *xh, size_t rows, size_t K) {
+    const long long n_sb = (long long)rows * (long long)(K / 256);
+    const long long blocks = (n_sb + 7) / 8;
+    if (blocks <= 0) return 0;
+    if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
+    gemm_prep_q8k_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(q, scales, (__half *)xh, n_sb);
+    OJAS_LAUNCH_CHECK(ctx, "gemm_prep_q8k");
     return 0;
 }
 

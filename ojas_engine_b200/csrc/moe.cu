@@ -127,15 +127,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const uint32_t *idx, in
 // SwiGLU + requantization (act = silu(g) * u, then quant_q8k): producers.cu
 int ojas_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, const float *u, int8_t *q, float *scales, int32_t *bsums, size_t rows, size_t K);
 
-// ---------------------------------------------------------------- prefill form helpers
-// dst[p, :] = src[tok[p], :] for rows of d f16 values (d is a multiple of 256): one block per sorted position.
-__global__ void __launch_bounds__(256) moe_gather_f16_kernel(const uint4 *src, const int *tok, uint4 *dst, int d8) {
-    const size_t p = blockIdx.x;
-    const uint4 *s = src + (size_t)__ldg(tok + p) * d8;
-    uint4 *o = dst + p * d8;
-    for (int i = threadIdx.x; i < d8; i += blockDim.x) o[i] = __ldg(s + i);
-}
-
+// ---------------------------------------------------------------- SwiGLU on f32 rows (the decode entries by name use it)
 // g = silu(g) * u in place, the same expression as silu_mul_q8k_kernel (producers.cu).
 __global__ void __launch_bounds__(256) moe_silu_mul_kernel(float4 *g, const float4 *u, long long n4) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -161,13 +153,20 @@ int ojas_silu_mul_inplace(ojas_b200_ctx *ctx, float *g, const float *u, size_t n
 // ---------------------------------------------------------------- combine
 // out[t, :] (=, +=) sum_j wgt[t, j] * yd[pos[t*KSEL + j], :], picks added in order j = 0, 1, ... as the
 // CPU path does (crates/ojas-cpu/src/cpu_glm.rs:581).
+// `parts` > 1: a down output is the sum, in order, of that many planes `part_stride` floats apart (the K parts of the
+// int8 tensor-core kernel).
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float *yd, const int *pos, const float *wgt, float *out, int ksel, int d,
-                                                           int accum) {
+                                                           int accum, int parts, size_t part_stride) {
     const int t = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= d) return;
     float s = 0.0f;
-    for (int j = 0; j < ksel; j++) s = __fadd_rn(s, __fmul_rn(wgt[t * ksel + j], yd[(size_t)pos[t * ksel + j] * d + i]));
+    for (int j = 0; j < ksel; j++) {
+        const float *src = yd + (size_t)pos[t * ksel + j] * d + i;
+        float v = src[0];
+        for (int p = 1; p < parts; p++) v = __fadd_rn(v, src[(size_t)p * part_stride]);
+        s = __fadd_rn(s, __fmul_rn(wgt[t * ksel + j], v));
+    }
     float *o = out + (size_t)t * d + i;
     *o = accum ? *o + s : s;
 }
@@ -188,13 +187,15 @@ extern "C" int ojas_b200_moe_topk(ojas_b200_ctx *ctx, const float *logits, uint3
 }
 
 namespace {
+constexpr size_t MOE_I8_SPLIT_ROWS = 512, MOE_I8_MAX_PARTS = 8;   // down outputs of up to 512 assignments may be cut into up to 8 K parts
 struct MoeWorkspace {
     int8_t *xq; float *xs; int32_t *xb;          // quantized h            [M, d]
     int *counts, *offsets, *tok, *pos;           // grouping
     float *g, *u;                                // gate / up outputs      [A, ffn]
     int8_t *aq; float *as; int32_t *ab;          // quantized SwiGLU       [A, ffn]
     float *yd;                                   // down outputs           [A, d]
-    void *xh, *xhs;                              // prefill form: f16 activations of h [M, d] and of its sorted rows [A, d]
+    int8_t *qg; void *meta_gu, *meta_d;          // int8 tensor-core form: h's integers in expert order, records of both stages
+    float *ydp;                                  // ... and the K-part planes of the down outputs [parts][A, d]
     size_t bytes;
 };
 
@@ -209,7 +210,8 @@ MoeWorkspace moe_carve(void *base, size_t M, size_t E, size_t KSEL, size_t d, si
     w.g = (float *)take(A * ffn * 4); w.u = (float *)take(A * ffn * 4);
     w.aq = (int8_t *)take(A * ffn); w.as = (float *)take(A * (ffn / 256) * 4); w.ab = (int32_t *)take(A * (ffn / 32) * 4);
     w.yd = (float *)take(A * d * 4);
-    w.xh = take(M * d * 2); w.xhs = take(A * d * 2);
+    w.qg = (int8_t *)take(A * d); w.meta_gu = take(ojas_experts_i8_meta_bytes(A, d)); w.meta_d = take(ojas_experts_i8_meta_bytes(A, ffn));
+    w.ydp = (float *)take(A <= MOE_I8_SPLIT_ROWS ? MOE_I8_MAX_PARTS * A * d * 4 : 0);
     w.bytes = off;
     return w;
 }
@@ -239,66 +241,81 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     const size_t A = M * KSEL;
     const MoeWorkspace w = moe_carve(workspace, M, E, KSEL, d, ffn);
 
-    // Prefill-sized batches (many rows per expert): the expert matmuls run as grouped tensor-core GEMMs over the
-    // sorted rows, each reading its row count and offset on the device.  Arithmetic contract as ojas_b200_gemm:
-    // h and the SwiGLU output are quantized to Q8_K and enter the MMA as f16(scale * q).
-    if (ctx->moe_gemm_rows > 0 && A / E >= (size_t)ctx->moe_gemm_rows) {
-        const size_t hint = A / E;                   // the tile width is chosen for a group of average size
-        int rc = ojas_gemm_prep(ctx, h, w.xh, M, d, true);
-        if (rc) return rc;
-        moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
-        OJAS_LAUNCH_CHECK(ctx, "moe_group");
-        moe_gather_f16_kernel<<<(unsigned)A, 256, 0, ctx->stream>>>((const uint4 *)w.xh, w.tok, (uint4 *)w.xhs, (int)(d / 8));
-        OJAS_LAUNCH_CHECK(ctx, "moe_gather");
-        OJAS_CUDA(ctx, cudaMemsetAsync(w.g, 0, A * ffn * sizeof(float), ctx->stream));   // split tiles are added into zeros
-        OJAS_CUDA(ctx, cudaMemsetAsync(w.u, 0, A * ffn * sizeof(float), ctx->stream));
-        for (size_t e = 0; e < E; e++) {
-            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_rows_at(type_gu, wg, d, e * ffn), w.g, d, ffn, hint,
-                                   w.counts + e, w.offsets + e);
-            if (rc) return rc;
-            rc = ojas_gemm_grouped(ctx, type_gu, w.xhs, A, weight_rows_at(type_gu, wu, d, e * ffn), w.u, d, ffn, hint,
-                                   w.counts + e, w.offsets + e);
-            if (rc) return rc;
-        }
-        const long long n4 = (long long)(A * ffn / 4);
-        moe_silu_mul_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, ctx->stream>>>((float4 *)w.g, (const float4 *)w.u, n4);
-        OJAS_LAUNCH_CHECK(ctx, "moe_silu_mul");
-        void *ah = (void *)w.u;                      // the up outputs are consumed: their space takes the f16 SwiGLU rows
-        rc = ojas_gemm_prep(ctx, w.g, ah, A, ffn, true);
-        if (rc) return rc;
-        OJAS_CUDA(ctx, cudaMemsetAsync(w.yd, 0, A * d * sizeof(float), ctx->stream));
-        for (size_t e = 0; e < E; e++) {
-            rc = ojas_gemm_grouped(ctx, type_d, ah, A, weight_rows_at(type_d, wd, ffn, e * d), w.yd, ffn, d, hint,
-                                   w.counts + e, w.offsets + e);
-            if (rc) return rc;
-        }
-        const dim3 grid2((unsigned)((d + 255) / 256), (unsigned)M);
-        moe_combine_kernel<<<grid2, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0);
-        OJAS_LAUNCH_CHECK(ctx, "moe_combine");
-        return 0;
-    }
-
+    // Every form quantizes h to Q8_K, sorts the assignments by expert and computes gate and up with EXACT integer block
+    // dots (the SwiGLU output is re-quantized, and an inexact gate / up value flips roundings there by whole steps).
+    //   decode-sized batches: down is exact too (the default).
+    //   prefill-sized batches (option moe_gemm_rows = R, from R rows per expert on average): gate and up on the int8
+    //     tcgen05 kernel, down as grouped f16 tensor-core GEMMs over the Q8_K SwiGLU rows (arithmetic of ojas_b200_gemm).
+    const bool prefill = ctx->moe_gemm_rows > 0 && A / E >= (size_t)ctx->moe_gemm_rows;
+    const bool i8_fits = type_gu == OJAS_B200_Q4_K && E <= 64;
     int rc = ojas_b200_quant_q8k(ctx, h, M, d, w.xq, w.xs, w.xb);
     if (rc) return rc;
     moe_group_kernel<<<1, 1024, 0, ctx->stream>>>(idx, (int)A, (int)E, (int)KSEL, w.counts, w.offsets, w.tok, w.pos);
     OJAS_LAUNCH_CHECK(ctx, "moe_group");
-    // gate and up: one launch of the tensor-core batch kernel over every expert and both tensors (Q4_K); otherwise one
-    // grouped launch per expert and tensor
-    rc = 1;
-    if (type_gu == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
-        rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts, w.offsets, E, d, ffn,
-                                   (A + E - 1) / E);
-    if (rc < 0) return rc;
-    for (size_t e = 0; rc == 1 && e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
-        int r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wg, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
-                                   w.counts + e, w.offsets + e, w.g, d, ffn);
-        if (r2) return r2;
-        r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wu, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
-                               w.counts + e, w.offsets + e, w.u, d, ffn);
-        if (r2) return r2;
+
+    // ---- gate and up
+    bool gu_i8 = false;
+    if (i8_fits && (prefill || (ctx->moe_i8 && type_d == OJAS_B200_Q4_K))) {
+        rc = ojas_experts_i8_pack(ctx, w.xq, w.xs, w.xb, w.tok, A, d, w.qg, w.meta_gu);
+        if (rc) return rc;
+        rc = ojas_experts_i8(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.qg, w.meta_gu, A, w.counts, w.offsets, E, d, ffn, 1, 0);
+        if (rc < 0) return rc;
+        gu_i8 = rc == 0;
+    }
+    if (!gu_i8) {
+        // one launch of the mma.sync experts kernel over every expert and both tensors (Q4_K); otherwise one grouped
+        // launch per expert and tensor
+        rc = 1;
+        if (type_gu == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
+            rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts, w.offsets, E, d, ffn,
+                                       (A + E - 1) / E);
+        if (rc < 0) return rc;
+        for (size_t e = 0; rc == 1 && e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
+            int r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wg, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+                                       w.counts + e, w.offsets + e, w.g, d, ffn);
+            if (r2) return r2;
+            r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wu, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
+                                   w.counts + e, w.offsets + e, w.u, d, ffn);
+            if (r2) return r2;
+        }
     }
     rc = ojas_silu_mul_q8k(ctx, w.g, w.u, w.aq, w.as, w.ab, A, ffn);
     if (rc) return rc;
+
+    // ---- down
+    const dim3 grid((unsigned)((d + 255) / 256), (unsigned)M);
+    if (prefill) {
+        void *ah = (void *)w.u;                      // the up outputs are consumed: their space takes the f16 SwiGLU rows
+        rc = ojas_gemm_prep_q8k(ctx, w.aq, w.as, ah, A, ffn);
+        if (rc) return rc;
+        OJAS_CUDA(ctx, cudaMemsetAsync(w.yd, 0, A * d * sizeof(float), ctx->stream));    // split tiles are added into zeros
+        for (size_t e = 0; e < E; e++) {
+            rc = ojas_gemm_grouped(ctx, type_d, ah, A, weight_rows_at(type_d, wd, ffn, e * d), w.yd, ffn, d, A / E, w.counts + e, w.offsets + e);
+            if (rc) return rc;
+        }
+        moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0, 1, 0);
+        OJAS_LAUNCH_CHECK(ctx, "moe_combine");
+        return 0;
+    }
+    if (gu_i8 && type_d == OJAS_B200_Q4_K) {
+        rc = ojas_experts_i8_pack(ctx, w.aq, w.as, w.ab, nullptr, A, ffn, nullptr, w.meta_d);
+        if (rc) return rc;
+        // K parts of the down projection: few 128-row tiles per expert, long rows -> cut K so that every SM gets
+        // about six items
+        const size_t tiles = (d + 127) / 128, items = (E < A ? E : A) * tiles;
+        size_t parts = 1;
+        if (A <= MOE_I8_SPLIT_ROWS) {
+            parts = (6 * (size_t)ctx->sm_count + items - 1) / items;
+            if (parts > MOE_I8_MAX_PARTS) parts = MOE_I8_MAX_PARTS;
+            if (parts > ffn / 1024) parts = ffn / 1024 ? ffn / 1024 : 1;
+        }
+        float *ydst = A <= MOE_I8_SPLIT_ROWS ? w.ydp : w.yd;
+        rc = ojas_experts_i8(ctx, (const uint8_t *)wd, nullptr, ydst, nullptr, w.aq, w.meta_d, A, w.counts, w.offsets, E, ffn, d, (int)parts, A * d);
+        if (rc) return rc < 0 ? rc : ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "moe_ffn: the down projection does not fit the int8 kernel");
+        moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(ydst, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0, (int)parts, A * d);
+        OJAS_LAUNCH_CHECK(ctx, "moe_combine");
+        return 0;
+    }
     rc = 1;
     if (type_d == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
         rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wd, nullptr, w.yd, nullptr, w.aq, w.as, w.ab, nullptr, w.counts, w.offsets, E, ffn, d,
@@ -309,8 +326,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
                                          w.counts + e, w.offsets + e, w.yd, ffn, d);
         if (r2) return r2;
     }
-    const dim3 grid((unsigned)((d + 255) / 256), (unsigned)M);
-    moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0);
+    moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(w.yd, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0, 1, 0);
     OJAS_LAUNCH_CHECK(ctx, "moe_combine");
     return 0;
 }

@@ -86,6 +86,19 @@ def test_uneven_routing(gpu):
     _moe_case(gpu, 1, 8, 2, 256, 256, Q4_K, Q4_K, idx=np.array([[7, 0]]))
 
 
+def test_int8_tensor_core_experts_passes_and_k_parts(gpu):
+    """The int8 tcgen05 form of the Q4_K expert FFN: experts with more rows than one 32-token pass (several passes over
+    the weights), a single row, long down rows cut into K parts, the accumulate form; within the bound of the exact
+    forms (typically 1e-7)."""
+    gpu.set_option("moe_i8", 1)
+    try:
+        assert _moe_case(gpu, 80, 2, 2, 512, 1024, Q4_K, Q4_K, seed=21) < 3e-4      # 80 rows per expert: three passes
+        assert _moe_case(gpu, 1, 4, 2, 256, 2048, Q4_K, Q4_K, seed=22) < 3e-4       # down K = 2048: two K parts
+        assert _moe_case(gpu, 33, 3, 1, 768, 4096, Q4_K, Q4_K, accum=True, seed=23) < 3e-4
+    finally:
+        gpu.set_option("moe_i8", 0)
+
+
 def test_config4_mixtral_shapes(gpu):
     """8 experts, gate/up 14336 x 4096 and down 4096 x 14336 in Q4_K, 64 tokens, top-2 routing from N(0,1)
     logits, softmax weights over the chosen two.  One expert's N(0, 0.02) weights are generated and
@@ -98,45 +111,50 @@ def test_config4_mixtral_shapes(gpu):
     wu = np.concatenate([np.roll(u0, 17 * i, axis=0).reshape(-1) for i in range(e)])
     wd = np.concatenate([np.roll(d0, 13 * i, axis=0).reshape(-1) for i in range(e)])
     _moe_case(gpu, m, e, ksel, d, ffn, Q4_K, Q4_K, experts=(wg, wu, wd), seed=0)
-
-
-# The grouped-GEMM form of the expert FFN is opt-in (option "moe_gemm_rows").  Each of its matmuls is within the
-# 2e-3 bar of the GEMM, but the chain is not: the oracle re-quantizes the SwiGLU output to Q8_K, and gate / up
-# outputs that are off by a few 1e-4 flip the rounding of a few per cent of those values by a whole step
-# (measured 4e-3 .. 6e-3 on the chain; the exact grouped-GEMV form stays below 1e-6).
-CHAIN_TOL = 1.5e-2
+    gpu.set_option("moe_i8", 1)                       # the same on the int8 tcgen05 kernel
+    try:
+        assert _moe_case(gpu, m, e, ksel, d, ffn, Q4_K, Q4_K, experts=(wg, wu, wd), seed=0) < 3e-4
+    finally:
+        gpu.set_option("moe_i8", 0)
 
 
 @pytest.mark.parametrize("t_gu,t_d", [(Q4_K, Q4_K), (Q4_K, Q6_K), (Q6_K, Q6_K)])
-def test_prefill_sized_batches_on_grouped_gemms(gpu, t_gu, t_d):
-    """Expert matmuls as grouped tensor-core GEMMs (row counts read on the device): uneven groups, an empty
-    expert, a group larger than one token tile, accumulate form."""
+def test_prefill_sized_batches_on_tensor_cores(gpu, t_gu, t_d):
+    """The prefill form (option "moe_gemm_rows"): gate and up with exact integers (Q4_K: on the int8 tcgen05 kernel, several
+    32-token passes per expert), the down projection as grouped f16 tcgen05 GEMMs over the Q8_K SwiGLU rows (row counts
+    read on the device).  Uneven groups, an empty expert, a group larger than one token tile, accumulate form: within
+    the stated 2e-3 of the oracle (what is left is the f16 rounding of the down GEMM's operands, typically 3e-4)."""
     gpu.set_option("moe_gemm_rows", 32)
     try:
-        _moe_case(gpu, 192, 4, 2, 512, 768, t_gu, t_d, seed=11, tol=CHAIN_TOL)
+        _moe_case(gpu, 192, 4, 2, 512, 768, t_gu, t_d, seed=11, tol=TOL)
         m, e, ksel = 300, 5, 2
         idx = np.zeros((m, ksel), np.uint32)
         idx[:, 0], idx[:, 1] = 3, 1                  # experts 0, 2, 4 get (almost) nothing; expert 3 gets 300 rows
         idx[::7, 1] = 4
-        _moe_case(gpu, m, e, ksel, 512, 512, t_gu, t_d, idx=idx, accum=True, seed=12, tol=CHAIN_TOL)
+        _moe_case(gpu, m, e, ksel, 512, 512, t_gu, t_d, idx=idx, accum=True, seed=12, tol=TOL)
     finally:
         gpu.set_option("moe_gemm_rows", 0)
 
 
-def test_both_expert_paths(gpu):
-    """The same small batch through the grouped-GEMV form (default, exact integer block dots) and, forced, through
-    the grouped-GEMM form."""
+def test_every_expert_path(gpu):
+    """The same small batch through the mma.sync experts kernel (default), the int8 tcgen05 kernel, the per-lane grouped
+    kernels and, forced, through the prefill form."""
     # exact integer block dots: typically 1e-7; a 1e-7 difference in a gate / up output (fp32 summation order) can flip
     # the Q8_K rounding of single SwiGLU values, which shows as 1e-4 on the output
     assert _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13) < 3e-4
-    gpu.set_option("gemv_mma", 0)                     # the same through the per-lane grouped kernels
+    gpu.set_option("moe_i8", 1)                       # both stages on the int8 tcgen05 kernel
+    try:
+        assert _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13) < 3e-4
+    finally:
+        gpu.set_option("moe_i8", 0)
+    gpu.set_option("gemv_mma", 0)                     # the per-lane grouped kernels
     try:
         assert _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13) < 3e-4
     finally:
         gpu.set_option("gemv_mma", 1)
     gpu.set_option("moe_gemm_rows", 1)
     try:
-        _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13, tol=CHAIN_TOL)
+        _moe_case(gpu, 40, 4, 2, 512, 768, Q4_K, Q4_K, seed=13, tol=TOL)
     finally:
         gpu.set_option("moe_gemm_rows", 0)
 
