@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -52,39 +53,67 @@ def measured_peaks() -> tuple[float, float, str]:
 
 # ------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """Samples nvidia-smi while the timed region runs (read-only queries)."""
+    """Samples nvidia-smi (read-only queries, every 50 ms) from before the warm-up on; `begin()` / `end()` mark the timed
+    region and the summary uses the samples that arrived inside it.  A region shorter than a few samples is followed by
+    the same load, untimed, until three samples are in (`keep_loaded`), and the summary says so."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
+        import threading
         self.index = index
-        self.proc = None
-
-    def __enter__(self):
+        self.rows = []            # (arrival time, fields)
+        self.t0 = self.t1 = None
+        self.extended = False
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
         except OSError:
             self.proc = None
-        return self
+            return
 
-    def __exit__(self, *exc):
-        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append((time.time(), line))
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def begin(self):
+        self.t0 = time.time()
+
+    def end(self):
+        self.t1 = time.time()
+
+    def inside(self):
+        t1 = self.t1 if self.t1 is not None else time.time()
+        return [line for t, line in self.rows if self.t0 is not None and self.t0 <= t <= t1 + 0.02]
+
+    def keep_loaded(self, run_step, sync, extra_steps: int):
+        """The timed region is over; if it was too short for a few samples, the caller keeps the same load running for
+        `extra_steps` more steps (the same number on every rank) and the window is extended over them."""
+        if extra_steps <= 0:
+            return
+        for _ in range(extra_steps):
+            run_step()
+        sync()
+        self.t1 = time.time()
+        self.extended = True
+
+    def close(self):
         if not self.proc:
             return
-        time.sleep(0.12)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out = ""
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.splitlines():
+        for line in self.inside():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 9:
                 continue
@@ -97,7 +126,8 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         if sm:
-            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            self.summary = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                            "window": "timed region, then the same load untimed until 3 samples" if self.extended else "timed region"}
 
 
 # ------------------------------------------------------------------------------ inputs
@@ -219,6 +249,57 @@ def extra_gemv(gpu, ob, ggml_type: int, n: int, k: int, m: int, peak: float, tag
             "frac_of_peak": round(gbs / peak, 4), "ring": ring}
 
 
+def decode_layer_case(gpu, ob, peak: float) -> dict:
+    """The matmul chain of one decode step of an 8B-shaped layer (d = 4096, ffn = 14336, 32 / 8 heads), with the fused
+    producers between the matmuls: RMSNorm -> Q8_K, fused Q|K|V GEMV (6144 rows), O projection, RMSNorm -> Q8_K, fused
+    gate|up GEMV (28672 rows), SiLU * up -> Q8_K, down (Q6_K).  Three layers of distinct weights (414 MB > L2) in one
+    CUDA graph; attention itself is not on this path (the O projection reads the first 4096 QKV outputs instead)."""
+    import oracle
+    d, ffn, nq = 4096, 14336, 6144
+    nsb_d, nsb_f = d // 256, ffn // 256
+
+    def weight(t, n, k, roll):
+        base = oracle.synth_blocks(t, n * k // 256).reshape(n, -1)
+        return gpu.load_weight(np.ascontiguousarray(np.roll(base, roll, axis=0)), t, n, k)
+
+    layers = [(weight(ob.Q4_K, nq, d, 7 * i), weight(ob.Q4_K, d, d, 11 * i), weight(ob.Q4_K, 2 * ffn, d, 13 * i), weight(ob.Q6_K, d, ffn, 17 * i))
+              for i in range(3)]
+    rng = np.random.default_rng(3)
+    x = gpu.upload(rng.standard_normal(d, dtype=np.float32))
+    nw = gpu.upload(np.ones(d, np.float32))
+    q_d, s_d, b_d = gpu.alloc_bytes(d), gpu.alloc(nsb_d), gpu.alloc_bytes(nsb_d * 8 * 4)
+    q_f, s_f, b_f = gpu.alloc_bytes(ffn), gpu.alloc(nsb_f), gpu.alloc_bytes(nsb_f * 8 * 4)
+    qkv, attn, gu, y = gpu.alloc(nq), gpu.alloc(d), gpu.alloc(2 * ffn), gpu.alloc(d)
+    g_view, u_view = ob.Buf(gu.ptr, ffn * 4), ob.Buf(gu.ptr + ffn * 4, ffn * 4)
+
+    def chain():
+        for wqkv, wo, wgu, wdn in layers:
+            gpu.rmsnorm_q8k(x, nw, 1e-5, 1, d, q_d, s_d, b_d)
+            gpu.gemv_q8k(wqkv, q_d, s_d, b_d, qkv)
+            gpu.gemv(wo, qkv, attn)
+            gpu.rmsnorm_q8k(attn, nw, 1e-5, 1, d, q_d, s_d, b_d)
+            gpu.gemv_q8k(wgu, q_d, s_d, b_d, gu)
+            gpu.silu_mul_q8k(g_view, u_view, 1, ffn, q_f, s_f, b_f)
+            gpu.gemv_q8k(wdn, q_f, s_f, b_f, y)
+
+    chain()
+    gpu.sync()
+    gpu.graph_begin()
+    chain()
+    g = gpu.graph_end()
+    ms = time_graph(gpu, g, 300, 5)
+    gpu.graph_destroy(g)
+    us_layer = ms * 1e3 / 300 / len(layers)
+    gguf = ob.raw_bytes(ob.Q4_K, nq, d) + ob.raw_bytes(ob.Q4_K, d, d) + ob.raw_bytes(ob.Q4_K, 2 * ffn, d) + ob.raw_bytes(ob.Q6_K, d, ffn)
+    for lay in layers:
+        for w in lay:
+            gpu.free(w.buf)
+    for b in (x, nw, q_d, s_d, b_d, q_f, s_f, b_f, qkv, attn, gu, y):
+        gpu.free(b)
+    return {"workload": "decode_layer_d4096_ffn14336_q4k_q6k_m1", "us_per_layer": round(us_layer, 2), "launches_per_layer": 7,
+            "GB/s": round(gguf / us_layer / 1e3, 1), "frac_of_peak": round(gguf / us_layer / 1e3 / peak, 4), "weight_bytes": gguf}
+
+
 def run_ours(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -279,6 +360,7 @@ def run_ours(args) -> None:
     def step():
         gpu.graph_launch(graph)
 
+    clocks = ClockSampler(local)
     for _ in range(args.warmup):
         step()
     gpu.sync()
@@ -287,22 +369,28 @@ def run_ours(args) -> None:
         torch.cuda.synchronize()
         dist.barrier()
     e0, e1 = gpu.event(), gpu.event()
-    with ClockSampler(local) as clocks:
-        gpu.record(e0)
-        for _ in range(args.steps):
-            step()
-        gpu.record(e1)
-        gpu.sync()
-        if dist is not None:
-            import torch
-            torch.cuda.synchronize()
-            dist.barrier()
+    clocks.begin()
+    gpu.record(e0)
+    for _ in range(args.steps):
+        step()
+    gpu.record(e1)
+    gpu.sync()
+    clocks.end()
+    if dist is not None:
+        import torch
+        torch.cuda.synchronize()
+        dist.barrier()
     ms = gpu.elapsed_ms(e0, e1)
     if dist is not None:
         import torch
         t = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    # a timed region shorter than 0.3 s gives nvidia-smi (50 ms period) too few samples: the same steps go on, untimed,
+    # until 0.3 s of load have passed (the count follows from the reduced time, so it is the same on every rank)
+    extra = int(math.ceil((300.0 - ms) / max(ms / args.steps, 1e-3))) if ms < 300.0 else 0
+    clocks.keep_loaded(step, gpu.sync, min(extra, 20000))
+    clocks.close()
     ms_per_step = ms / args.steps
     bytes_per_step_all = world * RING * ALGO_BYTES_PER_LAUNCH
     value = bytes_per_step_all / (ms_per_step * 1e-3) / 1e9
@@ -392,7 +480,11 @@ def run_ours(args) -> None:
                         extras.append(gemm_case(gpu, ob, tag, m, n, k, 10, 3, tc_peak))
                     except Exception as exc:
                         extras.append({"workload": f"{tag}_gemm_m{m}_n{n}_k{k}", "error": str(exc)})
-                for tokens, rows in ((64, 0), (2048, 32)):      # config 3 as stated; a prefill-sized batch on grouped GEMMs
+                try:
+                    extras.append(decode_layer_case(gpu, ob, hbm_peak))
+                except Exception as exc:
+                    extras.append({"workload": "decode_layer", "error": str(exc)})
+                for tokens, rows in ((64, 0), (2048, 32)):      # config 3 as stated; a prefill-sized batch in the prefill form
                     try:
                         extras.append(moe_case(gpu, ob, 5, 2, hbm_peak, tc_peak, tokens, rows))
                     except Exception as exc:
@@ -427,6 +519,12 @@ def run_case(args) -> None:
         return run_gemm_case(args)
     if args.case == "tp70b":
         return run_tp70b(args)
+    if args.case == "layer":
+        hbm_peak, _, _ = measured_peaks()
+        gpu = ob.B200Gpu(0)
+        print(json.dumps(decode_layer_case(gpu, ob, hbm_peak)))
+        gpu.close()
+        return
     if args.case == "moe" or args.case.startswith("moe:"):
         import ojas_engine_b200 as ob
         hbm_peak, tc_peak, _ = measured_peaks()
@@ -551,7 +649,7 @@ def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, 
     for b in (wg.buf, wu.buf, wd.buf, h, lg, idx, wgt, out, work):
         gpu.free(b)
     gpu.set_option("moe_gemm_rows", 0)
-    return {"workload": f"moe_q4k_e8_top2_m{m}_d4096_ffn14336" + ("_grouped_gemm" if gemm_rows else ""), "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
+    return {"workload": f"moe_q4k_e8_top2_m{m}_d4096_ffn14336" + ("_prefill_form" if gemm_rows else ""), "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
             "frac_of_hbm_peak": round(gguf / us / 1e3 / hbm_peak, 4), "TFLOP/s": round(flops / us / 1e6, 2),
             "frac_of_tensor_peak": round(flops / us / 1e6 / tc_peak, 5), "expert_bytes": gguf}
 
