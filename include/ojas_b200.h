@@ -65,8 +65,10 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
  * two, at most 16) and on the depth of a warp's weight ring (1, 2 or 4) of the GEMV kernel; a bound the shape does
  * not fit under falls back to the next smaller choice.  "gemm_ksplit": 0 = K ranges balanced across the SMs,
  * S > 0 = every tile's K range cut into S pieces.  "moe_gemm_rows" (default 0 = off): from this many rows per expert
- * on average the expert FFN runs as grouped tensor-core GEMMs (faster at prefill sizes; the FFN output is
- * then 4e-3..6e-3 from the CPU path instead of exact in its integer block dots). */
+ * on average the expert FFN takes its prefill form: gate and up on the int8 tensor-core kernel (exact integers), the
+ * down projection as grouped f16 tensor-core GEMMs; the FFN output stays within 2e-3 of the CPU path (typically 3e-4
+ * instead of 1e-7).  "moe_i8" (default 0): decode-sized Q4_K expert FFNs on the int8 tensor-core kernel too (same
+ * results as the default kernel; slower at 64 tokens). */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
