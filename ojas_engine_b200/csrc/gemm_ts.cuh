@@ -471,6 +471,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         const uint32_t need = kb - (uint32_t)BS;
                         const long long t0 = clock64();
                         while (b_seen[need & 3u] <= need) {
+                            __nanosleep(20);                 // (a spinning thread takes issue slots from the warps that work)
                             if (*abort_flag) { ok = false; break; }
                             if (clock64() - t0 > WAIT_CYCLES) { *abort_flag = 1; atomicOr(a.status, 0x10000u); __threadfence_system(); ok = false; break; }
                         }

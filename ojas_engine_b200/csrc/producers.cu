@@ -15,12 +15,27 @@ __global__ void __launch_bounds__(512) rmsnorm_q8k_kernel(const float *x, const 
     __shared__ float inv_s;
     const int row = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const float *xr = x + (size_t)row * K;
+    grid_launch_dependents();                    // the kernel behind this one may start its own set-up (it waits for this grid before it reads q)
     grid_dependency_wait();
+    // the row is read once: up to four float4 per thread stay in registers between the sum of squares and the scaling
+    constexpr int HOLD = 4;
+    float4 held[HOLD];
+    const bool fits = K <= (int)blockDim.x * 4 * HOLD;
     float s = 0.0f;
-    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + i));
-        s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+#pragma unroll
+    for (int h = 0; h < HOLD; h++) {
+        const int i = (h * (int)blockDim.x + (int)threadIdx.x) * 4;
+        held[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (fits && i < K) {
+            held[h] = __ldg(reinterpret_cast<const float4 *>(xr + i));
+            s = fmaf(held[h].x, held[h].x, s); s = fmaf(held[h].y, held[h].y, s); s = fmaf(held[h].z, held[h].z, s); s = fmaf(held[h].w, held[h].w, s);
+        }
     }
+    if (!fits)
+        for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + i));
+            s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+        }
     s = warp_sum(s);
     if (lane == 0) warp_part[warp] = s;
     __syncthreads();
@@ -31,17 +46,24 @@ __global__ void __launch_bounds__(512) rmsnorm_q8k_kernel(const float *x, const 
     }
     __syncthreads();
     const float inv = inv_s;
-    for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) {
-        const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + i));
+    auto emit = [&](int i, const float4 &v) {
         const float4 g = __ldg(reinterpret_cast<const float4 *>(w + i));
         float4 o;
         o.x = __fmul_rn(__fmul_rn(v.x, inv), g.x); o.y = __fmul_rn(__fmul_rn(v.y, inv), g.y);
         o.z = __fmul_rn(__fmul_rn(v.z, inv), g.z); o.w = __fmul_rn(__fmul_rn(v.w, inv), g.w);
         *reinterpret_cast<float4 *>(norm_row + i) = o;
         if (xn) *reinterpret_cast<float4 *>(xn + (size_t)row * K + i) = o;
+    };
+    if (fits) {
+#pragma unroll
+        for (int h = 0; h < HOLD; h++) {
+            const int i = (h * (int)blockDim.x + (int)threadIdx.x) * 4;
+            if (i < K) emit(i, held[h]);
+        }
+    } else {
+        for (int i = threadIdx.x * 4; i < K; i += blockDim.x * 4) emit(i, __ldg(reinterpret_cast<const float4 *>(xr + i)));
     }
     __syncthreads();
-    grid_launch_dependents();
     const int nsb = K >> 8;
     for (int sb = warp; sb < nsb; sb += warps) {
         float v[8];
@@ -64,6 +86,8 @@ __global__ void __launch_bounds__(256) silu_mul_q8k_kernel(const float *g, const
                                                             long long n_sb) {
     const int lane = threadIdx.x & 31;
     const long long sb = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    grid_launch_dependents();
+    grid_dependency_wait();                      // g and u come from the kernel before this one
     if (sb >= n_sb) return;
     const float4 g0 = __ldg(reinterpret_cast<const float4 *>(g + sb * 256) + lane * 2), g1 = __ldg(reinterpret_cast<const float4 *>(g + sb * 256) + lane * 2 + 1);
     const float4 u0 = __ldg(reinterpret_cast<const float4 *>(u + sb * 256) + lane * 2), u1 = __ldg(reinterpret_cast<const float4 *>(u + sb * 256) + lane * 2 + 1);
@@ -86,8 +110,18 @@ int ojas_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, const float *u, int8_t
     if (n_sb <= 0) return 0;
     const long long blocks = (n_sb + 7) / 8;
     if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "silu_mul_q8k: too many super-blocks");
-    silu_mul_q8k_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(g, u, q, scales, bsums, n_sb);
-    OJAS_LAUNCH_CHECK(ctx, "silu_mul_q8k");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, silu_mul_q8k_kernel, g, u, q, scales, bsums, n_sb);
+    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch silu_mul_q8k: %s", cudaGetErrorString(e));
+    ctx->launches++;
     return 0;
 }
 

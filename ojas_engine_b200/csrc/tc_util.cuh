@@ -9,6 +9,10 @@
 namespace {
 
 constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
+// A waiting thread that polls takes issue slots from the warps that work; the hint lets the hardware park it instead.
+#ifndef OJAS_TRY_WAIT_HINT_NS
+#define OJAS_TRY_WAIT_HINT_NS 20000u
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -27,10 +31,10 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {   //
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {    // may suspend the thread until the phase completes or a hardware time limit passes
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {    // suspends the thread until the phase completes or the hinted time passes
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(OJAS_TRY_WAIT_HINT_NS) : "memory");
     return ok != 0;
 }
 
