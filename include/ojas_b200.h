@@ -144,6 +144,12 @@ OJAS_B200_API int ojas_b200_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, con
 #define OJAS_B200_GEMV_MAX_M 8
 OJAS_B200_API int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *x, const void *w, float *y,
                    const float *bias, size_t K, size_t N, size_t M);
+/* Same with RMSNorm fused into the prologue: y = W ((x * inv) * norm_w), inv = 1 / sqrt(mean(x^2) + eps) per row of x
+ * (crates/ojas-cpu/src/cpu_math.rs:456-460; upstream runs rmsnorm_q8 and the GEMV as two launches,
+ * crates/ojas-cuda/src/kernels/ops.rs:27).  The sum of squares is a tree sum: equal to the separate producer to fp32
+ * rounding, not bit for bit. */
+OJAS_B200_API int ojas_b200_gemv_rmsnorm(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *x, const float *norm_w, float eps,
+                                         const void *w, float *y, const float *bias, size_t K, size_t N, size_t M);
 /* Same, with activations already quantized by ojas_b200_quant_q8k (Q4_K / Q6_K only):
  * one quantization can feed several projections (gate and up read the same row). */
 OJAS_B200_API int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const int8_t *q, const float *scales,

@@ -54,6 +54,10 @@ struct GemvArgs {
     const uint32_t *sel;
     size_t sel_stride;
     const float *alpha;
+    // fused RMSNorm (crates/ojas-cpu/src/cpu_math.rs:456-460): with norm_w given, row m of x enters as
+    // (x * inv_m) * norm_w with inv_m = 1 / sqrt(mean(x_m^2) + norm_eps), formed in the prologue
+    const float *norm_w;
+    float norm_eps;
     // tensor-parallel epilogue (tp.cu): instead of y, every result goes, stamped with the step's number, to this
     // rank's place in the receive window of every rank (plain 8-byte stores through peer-mapped pointers).
     TpPush tp;
@@ -125,8 +129,54 @@ template <int TYPE> struct ActLayout {
 // One warp quantizes super-block `sb` of one row into shared memory: bit-exact quant_q8k
 // (crates/ojas-cpu/src/cpu_math.rs:545-563).  lane l owns values 8l .. 8l+7.
 template <int TYPE>
+__device__ __forceinline__ void stage_quant_vals(const Q8kLane &ql, int sb, int lane, uint8_t *xq, uint8_t *bs, float *sx);
+
+template <int TYPE>
 __device__ __forceinline__ void stage_quant_sb(const float *xrow, int sb, int lane, uint8_t *xq, uint8_t *bs, float *sx) {
-    const Q8kLane ql = quant_q8k_warp(xrow + sb * 256, lane);
+    stage_quant_vals<TYPE>(quant_q8k_warp(xrow + sb * 256, lane), sb, lane, xq, bs, sx);
+}
+
+// The lane's eight values of super-block sb of a row, normalized: (x * inv) * w.
+__device__ __forceinline__ void load_normed(const float *xrow, const float *nw, float inv, int sb, int lane, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(xrow + sb * 256) + lane * 2), b = __ldg(reinterpret_cast<const float4 *>(xrow + sb * 256) + lane * 2 + 1);
+    const float4 g = __ldg(reinterpret_cast<const float4 *>(nw + sb * 256) + lane * 2), h = __ldg(reinterpret_cast<const float4 *>(nw + sb * 256) + lane * 2 + 1);
+    v[0] = __fmul_rn(__fmul_rn(a.x, inv), g.x); v[1] = __fmul_rn(__fmul_rn(a.y, inv), g.y);
+    v[2] = __fmul_rn(__fmul_rn(a.z, inv), g.z); v[3] = __fmul_rn(__fmul_rn(a.w, inv), g.w);
+    v[4] = __fmul_rn(__fmul_rn(b.x, inv), h.x); v[5] = __fmul_rn(__fmul_rn(b.y, inv), h.y);
+    v[6] = __fmul_rn(__fmul_rn(b.z, inv), h.z); v[7] = __fmul_rn(__fmul_rn(b.w, inv), h.w);
+}
+
+// 1 / sqrt(mean(x^2) + eps) of each of the M rows, the same value in every thread: per-thread sums over a strided
+// walk of the row, a butterfly per warp, then the warps' sums added in warp order (every thread adds them itself).
+template <int MT>
+__device__ __forceinline__ void row_inv_norms(const GemvArgs &a, int warps, float (&inv)[MT]) {
+    __shared__ float norm_part[MT * GEMV_MAX_WARPS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        float s = 0.0f;
+        if (m < a.M) {
+            const float *xr = a.x + (size_t)m * a.K;
+            for (int i = threadIdx.x * 4; i < a.K; i += blockDim.x * 4) {
+                const float4 v = __ldg(reinterpret_cast<const float4 *>(xr + i));
+                s = fmaf(v.x, v.x, s); s = fmaf(v.y, v.y, s); s = fmaf(v.z, v.z, s); s = fmaf(v.w, v.w, s);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (lane == 0) norm_part[m * GEMV_MAX_WARPS + warp] = s;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        float tot = 0.0f;
+        for (int j = 0; j < warps; j++) tot += norm_part[m * GEMV_MAX_WARPS + j];
+        inv[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)a.K), a.norm_eps)));
+    }
+}
+
+template <int TYPE>
+__device__ __forceinline__ void stage_quant_vals(const Q8kLane &ql, int sb, int lane, uint8_t *xq, uint8_t *bs, float *sx) {
     reinterpret_cast<uint2 *>(xq + sb * 256)[lane] = ql.packed;
     int s = ql.sum8;
     s += __shfl_xor_sync(0xffffffffu, s, 1);                       // sum of 16 values (lanes 2j, 2j+1)
@@ -147,27 +197,36 @@ __device__ __forceinline__ void stage_quant_sb(const float *xrow, int sb, int la
 
 // Activations of the K-quants.  MT rows (rows >= M are zeros).  !PREQ: quantize f32 rows; PREQ: copy rows that
 // ojas_b200_quant_q8k (or the expert FFN) quantized before, gathered through row_index when given.
-template <int TYPE, int MT, bool PREQ>
+template <int TYPE, int MT, bool PREQ, bool NORM>
 __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, int nsb, int warps) {
     using L = ActLayout<TYPE>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t rb = L::row_bytes(nsb);
     if (!PREQ) {
+        float inv[MT];
+        if (NORM) row_inv_norms<MT>(a, warps, inv);
+        auto quant_sb = [&](int m, int sb) {
+            uint8_t *xq = act + m * rb, *bs = xq + nsb * 256;
+            float *sx = reinterpret_cast<float *>(bs + nsb * L::BS_BYTES);
+            if (NORM) {
+                float v[8];
+                load_normed(a.x + (size_t)m * a.K, a.norm_w, inv[m], sb, lane, v);
+                stage_quant_vals<TYPE>(quant_q8k_values(v), sb, lane, xq, bs, sx);
+            } else {
+                stage_quant_sb<TYPE>(a.x + (size_t)m * a.K, sb, lane, xq, bs, sx);
+            }
+        };
         if (a.own_x) {
 #pragma unroll
-            for (int m = 0; m < MT; m++) {
-                uint8_t *xq = act + m * rb, *bs = xq + nsb * 256;
-                float *sx = reinterpret_cast<float *>(bs + nsb * L::BS_BYTES);
-                if (m < a.M) stage_quant_sb<TYPE>(a.x + (size_t)m * a.K, warp, lane, xq, bs, sx);
-            }
+            for (int m = 0; m < MT; m++)
+                if (m < a.M) quant_sb(m, warp);
             __syncwarp();
             return;
         }
-        for (int m = 0; m < a.M; m++) {
-            uint8_t *xq = act + m * rb, *bs = xq + nsb * 256;
-            float *sx = reinterpret_cast<float *>(bs + nsb * L::BS_BYTES);
-            for (int sb = warp; sb < nsb; sb += warps) stage_quant_sb<TYPE>(a.x + (size_t)m * a.K, sb, lane, xq, bs, sx);
-        }
+#pragma unroll
+        for (int m = 0; m < MT; m++)
+            if (m < a.M)
+                for (int sb = warp; sb < nsb; sb += warps) quant_sb(m, sb);
     } else {
         const int units = nsb * 16;                               // 16-byte units per row
         for (int m = 0; m < a.M; m++) {
@@ -205,13 +264,23 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
 }
 
 // Q8_0: f32 rows as they are.
-template <int MT>
-__device__ __forceinline__ void stage_f32(const GemvArgs &a, float *xs) {
+template <int MT, bool NORM>
+__device__ __forceinline__ void stage_f32(const GemvArgs &a, float *xs, int warps) {
     const int k4 = a.K >> 2;
+    float inv[MT];
+    if (NORM) row_inv_norms<MT>(a, warps, inv);
     for (int idx = threadIdx.x; idx < MT * k4; idx += blockDim.x) {
         const int m = idx / k4, f4 = idx - m * k4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (m < a.M) v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)src_row(a, m) * a.K) + f4);
+        if (NORM && m < a.M) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + f4);
+            float im = inv[0];
+#pragma unroll
+            for (int j = 1; j < MT; j++) im = m == j ? inv[j] : im;
+            v.x = __fmul_rn(__fmul_rn(v.x, im), g.x); v.y = __fmul_rn(__fmul_rn(v.y, im), g.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, im), g.z); v.w = __fmul_rn(__fmul_rn(v.w, im), g.w);
+        }
         reinterpret_cast<float4 *>(xs)[idx] = v;
     }
     __syncthreads();
@@ -382,7 +451,7 @@ __device__ __forceinline__ void step_q80(const uint8_t *wl, const float *xs, int
 // ---------------------------------------------------------------------------- the kernel body
 // `ring_uses` counts the steps this warp has put through its ring since the kernel began (the grouped kernel calls
 // the body once per pass and the barriers' phases carry over).
-template <int TYPE, int MT, bool PREQ, bool DUMP>
+template <int TYPE, int MT, bool PREQ, bool DUMP, bool NORM = false>
 __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem, unsigned &ring_uses, bool first_pass) {
     constexpr int TB = tile_bytes(TYPE), STEP = 4 * TB;
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -437,8 +506,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         for (int i = 0; i < nst && i < nsteps; i++) issue();
     }
     if (first_pass) grid_dependency_wait();                       // activations (and y for the accumulate form) come from the kernel before
-    if (TYPE == OJAS_B200_Q8_0) stage_f32<MT>(a, reinterpret_cast<float *>(act));
-    else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ>(a, act, nsb, warps);
+    if (TYPE == OJAS_B200_Q8_0) stage_f32<MT, NORM>(a, reinterpret_cast<float *>(act), warps);
+    else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ, NORM>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
     const float alpha = a.alpha ? __ldg(a.alpha) : 1.0f;
     // tensor-parallel launches: the step in flight is the stamp and picks the half of the windows
@@ -513,6 +582,14 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, MINB) gemv_kernel(const G
     extern __shared__ __align__(128) unsigned char gemv_smem[];
     unsigned ring_uses = 0;
     gemv_body<TYPE, MT, PREQ, DUMP>(a, gemv_smem, ring_uses, true);
+}
+
+// The same with the RMSNorm of the rows formed in the prologue (f32 activations only).
+template <int TYPE, int MT>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_norm_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char gemv_smem[];
+    unsigned ring_uses = 0;
+    gemv_body<TYPE, MT, false, false, true>(a, gemv_smem, ring_uses, true);
 }
 
 // Grouped form: the group's rows (count and first position read from device memory, so the launch is capture-safe
@@ -664,6 +741,19 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     case 2: return launch_gemv(ctx, gemv_kernel<T, 2, PQ, false, 1>, args, p, NAME);           \
     case 4: return launch_gemv(ctx, gemv_kernel<T, 4, PQ, false, 1>, args, p, NAME);           \
     default: return launch_gemv(ctx, gemv_kernel<T, 8, PQ, false, 1>, args, p, NAME);          \
+    }
+    if (args.norm_w) {
+#define GEMV_NORM_CASE(T, NAME)                                                        \
+    switch (MT) {                                                                      \
+    case 1: return launch_gemv(ctx, gemv_norm_kernel<T, 1>, args, p, NAME);            \
+    case 2: return launch_gemv(ctx, gemv_norm_kernel<T, 2>, args, p, NAME);            \
+    case 4: return launch_gemv(ctx, gemv_norm_kernel<T, 4>, args, p, NAME);            \
+    default: return launch_gemv(ctx, gemv_norm_kernel<T, 8>, args, p, NAME);           \
+    }
+        if (type == OJAS_B200_Q4_K) { GEMV_NORM_CASE(OJAS_B200_Q4_K, "gemv_q4k_rmsnorm") }
+        if (type == OJAS_B200_Q6_K) { GEMV_NORM_CASE(OJAS_B200_Q6_K, "gemv_q6k_rmsnorm") }
+        GEMV_NORM_CASE(OJAS_B200_Q8_0, "gemv_q80_rmsnorm")
+#undef GEMV_NORM_CASE
     }
     if (type == OJAS_B200_Q4_K) {
         if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q4_K, 1, false, true, 1>, args, p, "gemv_q4k_idots");
@@ -820,7 +910,7 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
 // itself (M * K / 256 warp tasks each).  From a few dozen tasks per warp on that prologue outweighs the
 // matrix, so the batch is quantized once into the context's scratch and the GEMV copies the result.
 static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs &args, size_t M) {
-    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch) return false;
+    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch || args.norm_w) return false;   // (a fused norm is formed in the kernel's prologue)
     const size_t values = M * (size_t)args.K;
     if (values > OJAS_ACT_SCRATCH_VALUES) return false;
     if (values < 16384 && !(type == OJAS_B200_Q4_K && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
@@ -908,6 +998,21 @@ extern "C" int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t type, int form, const
     GemvArgs a{};
     a.x = x; a.w = (const uint8_t *)w; a.y = y; a.bias = bias;
     a.K = (int)K; a.N = (int)N; a.M = (int)M; a.form = form;
+    return gemv_run(ctx, type, false, a, M);
+}
+
+// RMSNorm fused into the GEMV's prologue: y = W ((x * inv) * norm_w), inv = 1 / sqrt(mean(x^2) + eps) per row.  Replaces
+// a launch of the producer (ojas_b200_rmsnorm_q8k) in front of a GEMV: every CTA forms the norm of the row(s) itself.
+extern "C" int ojas_b200_gemv_rmsnorm(ojas_b200_ctx *ctx, uint32_t type, int form, const float *x, const float *norm_w, float eps, const void *w,
+                                      float *y, const float *bias, size_t K, size_t N, size_t M) {
+    int rc = gemv_check(ctx, type, form, w, y, bias, K, N, M);
+    if (rc) return rc;
+    if (!x || !norm_w) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_rmsnorm: null pointer");
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)norm_w & 15) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_rmsnorm: x and norm_w must be 16-byte aligned");
+    GemvArgs a{};
+    a.x = x; a.w = (const uint8_t *)w; a.y = y; a.bias = bias;
+    a.K = (int)K; a.N = (int)N; a.M = (int)M; a.form = form;
+    a.norm_w = norm_w; a.norm_eps = eps;
     return gemv_run(ctx, type, false, a, M);
 }
 

@@ -189,6 +189,11 @@ class B200Gpu:
         self._ck(self._l.ojas_b200_gemv(self._ctx, w.ggml_type, form, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
                                         C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
 
+    def gemv_rmsnorm(self, w: Lin, x: Buf, norm_w: Buf, eps: float, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
+        """``y = W rmsnorm(x)``: the norm is formed in the GEMV's prologue (one launch instead of producer + GEMV)."""
+        self._ck(self._l.ojas_b200_gemv_rmsnorm(self._ctx, w.ggml_type, form, C.c_void_p(x.ptr), C.c_void_p(norm_w.ptr), C.c_float(eps),
+                                                C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
+
     def gemv_q8k(self, w: Lin, q: Buf, scales: Buf, bsums: Buf, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
         self._ck(self._l.ojas_b200_gemv_q8k(self._ctx, w.ggml_type, form, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr),
                                             C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))

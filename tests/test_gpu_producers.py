@@ -93,3 +93,32 @@ def test_producer_argument_errors(gpu):
         gpu.silu_mul_q8k(x, x, 1, 100, q, s, b)
     for buf in (x, q, s, b):
         gpu.free(buf)
+
+
+@pytest.mark.parametrize("t,n,k,m", [(Q4_K, 1024, 4096, 1), (Q4_K, 520, 768, 3), (ob.Q6_K, 512, 2048, 2), (ob.Q8_0, 256, 1024, 1),
+                                     (Q4_K, 6144, 4096, 1)])
+def test_gemv_with_the_norm_in_its_prologue(gpu, t, n, k, m):
+    """ojas_b200_gemv_rmsnorm against the CPU composition (rmsnorm, then matvec_kq) and against the two-launch form
+    (producer, then gemv_q8k): the norm's sum of squares is a tree sum in both device forms, so they agree with each
+    other and with the CPU to fp32 rounding plus, rarely, a Q8_K rounding step of a value."""
+    raw = synth_weights(t, n, k)
+    wl = gpu.load_weight(raw, t, n, k)
+    x = activations(m, k, seed=41) * np.float32(2.5)
+    g = (1.0 + 0.1 * activations(1, k, seed=42)[0]).astype(np.float32)
+    eps = 1e-5
+    xb, gb = gpu.upload(x), gpu.upload(g)
+    y1, y2 = gpu.alloc(m * n), gpu.alloc(m * n)
+    gpu.gemv_rmsnorm(wl, xb, gb, eps, y1, m)
+    got = gpu.read(y1, np.float32, m * n).reshape(m, n)
+    want = np.stack([oracle.matvec_kq(raw, t, n, k, oracle.rmsnorm(x[r], g, eps)) for r in range(m)])
+    assert rel_l2(got, want) < 2e-4
+    if t != ob.Q8_0:
+        q, s, b = _q8k_bufs(gpu, m, k)
+        gpu.rmsnorm_q8k(xb, gb, eps, m, k, q, s, b)
+        gpu.gemv_q8k(wl, q, s, b, y2, m)
+        two = gpu.read(y2, np.float32, m * n).reshape(m, n)
+        assert rel_l2(got, two) < 2e-4
+        for buf in (q, s, b):
+            gpu.free(buf)
+    for buf in (wl.buf, xb, gb, y1, y2):
+        gpu.free(buf)
