@@ -252,7 +252,8 @@ def extra_gemv(gpu, ob, ggml_type: int, n: int, k: int, m: int, peak: float, tag
 def decode_layer_case(gpu, ob, peak: float) -> dict:
     """The matmul chain of one decode step of an 8B-shaped layer (d = 4096, ffn = 14336, 32 / 8 heads): fused Q|K|V GEMV
     (6144 rows) with the RMSNorm in its prologue, O projection, fused gate|up GEMV (28672 rows) with the RMSNorm in its
-    prologue, SiLU * up -> Q8_K, down (Q6_K); also timed with the two norms as separate RMSNorm -> Q8_K launches.  Three layers of distinct weights (414 MB > L2) in one
+    prologue, SiLU * up -> Q8_K, down (Q6_K); also timed with the norms as launches of their own (RMSNorm -> Q8_K) and
+    with SiLU * up in the down projection's prologue as well (slower: every CTA repeats the exponentials).  Three layers of distinct weights (414 MB > L2) in one
     CUDA graph; attention itself is not on this path (the O projection reads the first 4096 QKV outputs instead)."""
     import oracle
     d, ffn, nq = 4096, 14336, 6144
@@ -284,11 +285,14 @@ def decode_layer_case(gpu, ob, peak: float) -> dict:
                 gpu.gemv(wo, qkv, attn)
                 gpu.rmsnorm_q8k(attn, nw, 1e-5, 1, d, q_d, s_d, b_d)
                 gpu.gemv_q8k(wgu, q_d, s_d, b_d, gu)
-            gpu.silu_mul_q8k(g_view, u_view, 1, ffn, q_f, s_f, b_f)
-            gpu.gemv_q8k(wdn, q_f, s_f, b_f, y)
+            if fused_norm == 2:
+                gpu.gemv_silu_mul(wdn, g_view, u_view, y)
+            else:
+                gpu.silu_mul_q8k(g_view, u_view, 1, ffn, q_f, s_f, b_f)
+                gpu.gemv_q8k(wdn, q_f, s_f, b_f, y)
 
     us = {}
-    for fused_norm in (False, True):
+    for fused_norm in (0, 1, 2):        # producers as launches of their own; norms in the GEMV prologues; SwiGLU too
         chain()
         gpu.sync()
         gpu.graph_begin()
@@ -297,7 +301,7 @@ def decode_layer_case(gpu, ob, peak: float) -> dict:
         ms = time_graph(gpu, g, 300, 5)
         gpu.graph_destroy(g)
         us[fused_norm] = ms * 1e3 / 300 / len(layers)
-    us_layer = us[True]
+    us_layer = us[1]
     gguf = ob.raw_bytes(ob.Q4_K, nq, d) + ob.raw_bytes(ob.Q4_K, d, d) + ob.raw_bytes(ob.Q4_K, 2 * ffn, d) + ob.raw_bytes(ob.Q6_K, d, ffn)
     for lay in layers:
         for w in lay:
@@ -305,7 +309,7 @@ def decode_layer_case(gpu, ob, peak: float) -> dict:
     for b in (x, nw, q_d, s_d, b_d, q_f, s_f, b_f, qkv, attn, gu, y):
         gpu.free(b)
     return {"workload": "decode_layer_d4096_ffn14336_q4k_q6k_m1", "us_per_layer": round(us_layer, 2), "launches_per_layer": 5,
-            "us_per_layer_with_separate_norm_launches": round(us[False], 2),
+            "us_per_layer_with_separate_producer_launches": round(us[0], 2), "us_per_layer_with_swiglu_fused_too": round(us[2], 2),
             "GB/s": round(gguf / us_layer / 1e3, 1), "frac_of_peak": round(gguf / us_layer / 1e3 / peak, 4), "weight_bytes": gguf}
 
 

@@ -150,6 +150,11 @@ OJAS_B200_API int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t ggml_type, int for
  * rounding, not bit for bit. */
 OJAS_B200_API int ojas_b200_gemv_rmsnorm(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *x, const float *norm_w, float eps,
                                          const void *w, float *y, const float *bias, size_t K, size_t N, size_t M);
+/* Same with SwiGLU fused into the prologue: y = W (silu(g) * u) (crates/ojas-cpu/src/cpu_math.rs:486; upstream runs
+ * silu_mul_q8 and the GEMV as two launches, crates/ojas-cuda/src/kernels/ops.rs:352).  The same expression as
+ * ojas_b200_silu_mul_q8k: the two forms agree bit for bit. */
+OJAS_B200_API int ojas_b200_gemv_silu_mul(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *g, const float *u, const void *w,
+                                          float *y, const float *bias, size_t K, size_t N, size_t M);
 /* Same, with activations already quantized by ojas_b200_quant_q8k (Q4_K / Q6_K only):
  * one quantization can feed several projections (gate and up read the same row). */
 OJAS_B200_API int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const int8_t *q, const float *scales,

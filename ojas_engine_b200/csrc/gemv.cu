@@ -58,6 +58,8 @@ struct GemvArgs {
     // (x * inv_m) * norm_w with inv_m = 1 / sqrt(mean(x_m^2) + norm_eps), formed in the prologue
     const float *norm_w;
     float norm_eps;
+    // fused SwiGLU (crates/ojas-cpu/src/cpu_math.rs:486): with x2 given (and no norm_w), row m enters as silu(x) * x2
+    const float *x2;
     // tensor-parallel epilogue (tp.cu): instead of y, every result goes, stamped with the step's number, to this
     // rank's place in the receive window of every rank (plain 8-byte stores through peer-mapped pointers).
     TpPush tp;
@@ -146,6 +148,15 @@ __device__ __forceinline__ void load_normed(const float *xrow, const float *nw, 
     v[6] = __fmul_rn(__fmul_rn(b.z, inv), h.z); v[7] = __fmul_rn(__fmul_rn(b.w, inv), h.w);
 }
 
+// The lane's eight values of super-block sb of silu(g) * u, the expression of silu_mul_q8k_kernel (producers.cu).
+__device__ __forceinline__ void load_silu_mul(const float *grow, const float *urow, int sb, int lane, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(grow + sb * 256) + lane * 2), b = __ldg(reinterpret_cast<const float4 *>(grow + sb * 256) + lane * 2 + 1);
+    const float4 g = __ldg(reinterpret_cast<const float4 *>(urow + sb * 256) + lane * 2), h = __ldg(reinterpret_cast<const float4 *>(urow + sb * 256) + lane * 2 + 1);
+    const float gv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w}, uv[8] = {g.x, g.y, g.z, g.w, h.x, h.y, h.z, h.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __fmul_rn(__fdiv_rn(gv[i], 1.0f + expf(-gv[i])), uv[i]);
+}
+
 // 1 / sqrt(mean(x^2) + eps) of each of the M rows, the same value in every thread: per-thread sums over a strided
 // walk of the row, a butterfly per warp, then the warps' sums added in warp order (every thread adds them itself).
 template <int MT>
@@ -197,20 +208,24 @@ __device__ __forceinline__ void stage_quant_vals(const Q8kLane &ql, int sb, int 
 
 // Activations of the K-quants.  MT rows (rows >= M are zeros).  !PREQ: quantize f32 rows; PREQ: copy rows that
 // ojas_b200_quant_q8k (or the expert FFN) quantized before, gathered through row_index when given.
-template <int TYPE, int MT, bool PREQ, bool NORM>
+template <int TYPE, int MT, bool PREQ, int PRO>
 __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, int nsb, int warps) {
     using L = ActLayout<TYPE>;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t rb = L::row_bytes(nsb);
     if (!PREQ) {
         float inv[MT];
-        if (NORM) row_inv_norms<MT>(a, warps, inv);
+        if (PRO == 1) row_inv_norms<MT>(a, warps, inv);
         auto quant_sb = [&](int m, int sb) {
             uint8_t *xq = act + m * rb, *bs = xq + nsb * 256;
             float *sx = reinterpret_cast<float *>(bs + nsb * L::BS_BYTES);
-            if (NORM) {
+            if (PRO == 1) {
                 float v[8];
                 load_normed(a.x + (size_t)m * a.K, a.norm_w, inv[m], sb, lane, v);
+                stage_quant_vals<TYPE>(quant_q8k_values(v), sb, lane, xq, bs, sx);
+            } else if (PRO == 2) {
+                float v[8];
+                load_silu_mul(a.x + (size_t)m * a.K, a.x2 + (size_t)m * a.K, sb, lane, v);
                 stage_quant_vals<TYPE>(quant_q8k_values(v), sb, lane, xq, bs, sx);
             } else {
                 stage_quant_sb<TYPE>(a.x + (size_t)m * a.K, sb, lane, xq, bs, sx);
@@ -264,16 +279,21 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
 }
 
 // Q8_0: f32 rows as they are.
-template <int MT, bool NORM>
+template <int MT, int PRO>
 __device__ __forceinline__ void stage_f32(const GemvArgs &a, float *xs, int warps) {
     const int k4 = a.K >> 2;
     float inv[MT];
-    if (NORM) row_inv_norms<MT>(a, warps, inv);
+    if (PRO == 1) row_inv_norms<MT>(a, warps, inv);
     for (int idx = threadIdx.x; idx < MT * k4; idx += blockDim.x) {
         const int m = idx / k4, f4 = idx - m * k4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (m < a.M) v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)src_row(a, m) * a.K) + f4);
-        if (NORM && m < a.M) {
+        if (PRO == 2 && m < a.M) {
+            const float4 u = __ldg(reinterpret_cast<const float4 *>(a.x2 + (size_t)m * a.K) + f4);
+            v.x = __fmul_rn(__fdiv_rn(v.x, 1.0f + expf(-v.x)), u.x); v.y = __fmul_rn(__fdiv_rn(v.y, 1.0f + expf(-v.y)), u.y);
+            v.z = __fmul_rn(__fdiv_rn(v.z, 1.0f + expf(-v.z)), u.z); v.w = __fmul_rn(__fdiv_rn(v.w, 1.0f + expf(-v.w)), u.w);
+        }
+        if (PRO == 1 && m < a.M) {
             const float4 g = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + f4);
             float im = inv[0];
 #pragma unroll
@@ -451,7 +471,7 @@ __device__ __forceinline__ void step_q80(const uint8_t *wl, const float *xs, int
 // ---------------------------------------------------------------------------- the kernel body
 // `ring_uses` counts the steps this warp has put through its ring since the kernel began (the grouped kernel calls
 // the body once per pass and the barriers' phases carry over).
-template <int TYPE, int MT, bool PREQ, bool DUMP, bool NORM = false>
+template <int TYPE, int MT, bool PREQ, bool DUMP, int PRO = 0>
 __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem, unsigned &ring_uses, bool first_pass) {
     constexpr int TB = tile_bytes(TYPE), STEP = 4 * TB;
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -506,8 +526,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         for (int i = 0; i < nst && i < nsteps; i++) issue();
     }
     if (first_pass) grid_dependency_wait();                       // activations (and y for the accumulate form) come from the kernel before
-    if (TYPE == OJAS_B200_Q8_0) stage_f32<MT, NORM>(a, reinterpret_cast<float *>(act), warps);
-    else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ, NORM>(a, act, nsb, warps);
+    if (TYPE == OJAS_B200_Q8_0) stage_f32<MT, PRO>(a, reinterpret_cast<float *>(act), warps);
+    else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ, PRO>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
     const float alpha = a.alpha ? __ldg(a.alpha) : 1.0f;
     // tensor-parallel launches: the step in flight is the stamp and picks the half of the windows
@@ -584,12 +604,12 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, MINB) gemv_kernel(const G
     gemv_body<TYPE, MT, PREQ, DUMP>(a, gemv_smem, ring_uses, true);
 }
 
-// The same with the RMSNorm of the rows formed in the prologue (f32 activations only).
-template <int TYPE, int MT>
-__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_norm_kernel(const GemvArgs a) {
+// The same with a producer in the prologue (f32 activations only): PRO = 1 RMSNorm of the rows, 2 silu(x) * x2.
+template <int TYPE, int MT, int PRO>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_pro_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char gemv_smem[];
     unsigned ring_uses = 0;
-    gemv_body<TYPE, MT, false, false, true>(a, gemv_smem, ring_uses, true);
+    gemv_body<TYPE, MT, false, false, PRO>(a, gemv_smem, ring_uses, true);
 }
 
 // Grouped form: the group's rows (count and first position read from device memory, so the launch is capture-safe
@@ -742,18 +762,23 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     case 4: return launch_gemv(ctx, gemv_kernel<T, 4, PQ, false, 1>, args, p, NAME);           \
     default: return launch_gemv(ctx, gemv_kernel<T, 8, PQ, false, 1>, args, p, NAME);          \
     }
-    if (args.norm_w) {
-#define GEMV_NORM_CASE(T, NAME)                                                        \
+    if (args.norm_w || args.x2) {
+#define GEMV_PRO_CASE(T, PRO, NAME)                                                    \
     switch (MT) {                                                                      \
-    case 1: return launch_gemv(ctx, gemv_norm_kernel<T, 1>, args, p, NAME);            \
-    case 2: return launch_gemv(ctx, gemv_norm_kernel<T, 2>, args, p, NAME);            \
-    case 4: return launch_gemv(ctx, gemv_norm_kernel<T, 4>, args, p, NAME);            \
-    default: return launch_gemv(ctx, gemv_norm_kernel<T, 8>, args, p, NAME);           \
+    case 1: return launch_gemv(ctx, gemv_pro_kernel<T, 1, PRO>, args, p, NAME);        \
+    case 2: return launch_gemv(ctx, gemv_pro_kernel<T, 2, PRO>, args, p, NAME);        \
+    case 4: return launch_gemv(ctx, gemv_pro_kernel<T, 4, PRO>, args, p, NAME);        \
+    default: return launch_gemv(ctx, gemv_pro_kernel<T, 8, PRO>, args, p, NAME);       \
     }
-        if (type == OJAS_B200_Q4_K) { GEMV_NORM_CASE(OJAS_B200_Q4_K, "gemv_q4k_rmsnorm") }
-        if (type == OJAS_B200_Q6_K) { GEMV_NORM_CASE(OJAS_B200_Q6_K, "gemv_q6k_rmsnorm") }
-        GEMV_NORM_CASE(OJAS_B200_Q8_0, "gemv_q80_rmsnorm")
-#undef GEMV_NORM_CASE
+        if (args.norm_w) {
+            if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 1, "gemv_q4k_rmsnorm") }
+            if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 1, "gemv_q6k_rmsnorm") }
+            GEMV_PRO_CASE(OJAS_B200_Q8_0, 1, "gemv_q80_rmsnorm")
+        }
+        if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 2, "gemv_q4k_silu_mul") }
+        if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 2, "gemv_q6k_silu_mul") }
+        GEMV_PRO_CASE(OJAS_B200_Q8_0, 2, "gemv_q80_silu_mul")
+#undef GEMV_PRO_CASE
     }
     if (type == OJAS_B200_Q4_K) {
         if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q4_K, 1, false, true, 1>, args, p, "gemv_q4k_idots");
@@ -910,7 +935,7 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
 // itself (M * K / 256 warp tasks each).  From a few dozen tasks per warp on that prologue outweighs the
 // matrix, so the batch is quantized once into the context's scratch and the GEMV copies the result.
 static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs &args, size_t M) {
-    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch || args.norm_w) return false;   // (a fused norm is formed in the kernel's prologue)
+    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch || args.norm_w || args.x2) return false;   // (a fused producer runs in the kernel's prologue)
     const size_t values = M * (size_t)args.K;
     if (values > OJAS_ACT_SCRATCH_VALUES) return false;
     if (values < 16384 && !(type == OJAS_B200_Q4_K && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
@@ -1013,6 +1038,20 @@ extern "C" int ojas_b200_gemv_rmsnorm(ojas_b200_ctx *ctx, uint32_t type, int for
     a.x = x; a.w = (const uint8_t *)w; a.y = y; a.bias = bias;
     a.K = (int)K; a.N = (int)N; a.M = (int)M; a.form = form;
     a.norm_w = norm_w; a.norm_eps = eps;
+    return gemv_run(ctx, type, false, a, M);
+}
+
+// SwiGLU fused into the GEMV's prologue: y = W (silu(g) * u).  Replaces a launch of ojas_b200_silu_mul_q8k in front of the
+// down projection.
+extern "C" int ojas_b200_gemv_silu_mul(ojas_b200_ctx *ctx, uint32_t type, int form, const float *g, const float *u, const void *w, float *y,
+                                       const float *bias, size_t K, size_t N, size_t M) {
+    int rc = gemv_check(ctx, type, form, w, y, bias, K, N, M);
+    if (rc) return rc;
+    if (!g || !u) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_silu_mul: null pointer");
+    if (((uintptr_t)g & 15) != 0 || ((uintptr_t)u & 15) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_silu_mul: g and u must be 16-byte aligned");
+    GemvArgs a{};
+    a.x = g; a.x2 = u; a.w = (const uint8_t *)w; a.y = y; a.bias = bias;
+    a.K = (int)K; a.N = (int)N; a.M = (int)M; a.form = form;
     return gemv_run(ctx, type, false, a, M);
 }
 

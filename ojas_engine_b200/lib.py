@@ -50,6 +50,7 @@ SIGNATURES = {
     "ojas_b200_silu_mul_q8k": (_i, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp]),
     "ojas_b200_gemv": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_rmsnorm": (_i, [_vp, _u32, _i, _vp, _vp, C.c_float, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "ojas_b200_gemv_silu_mul": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_q8k": (_i, [_vp, _u32, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_gemv_idots": (_i, [_vp, _u32, _vp, _vp, _vp, _sz, _sz]),
     "ojas_b200_gemm_workspace_bytes": (_sz, [_sz, _sz]),

@@ -194,6 +194,11 @@ class B200Gpu:
         self._ck(self._l.ojas_b200_gemv_rmsnorm(self._ctx, w.ggml_type, form, C.c_void_p(x.ptr), C.c_void_p(norm_w.ptr), C.c_float(eps),
                                                 C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
 
+    def gemv_silu_mul(self, w: Lin, g: Buf, u: Buf, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
+        """``y = W (silu(g) * u)``: SwiGLU is formed in the GEMV's prologue (one launch instead of producer + GEMV)."""
+        self._ck(self._l.ojas_b200_gemv_silu_mul(self._ctx, w.ggml_type, form, C.c_void_p(g.ptr), C.c_void_p(u.ptr), C.c_void_p(w.buf.ptr),
+                                                 C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))
+
     def gemv_q8k(self, w: Lin, q: Buf, scales: Buf, bsums: Buf, y: Buf, m: int = 1, form: int = PLAIN, bias: Buf | None = None) -> None:
         self._ck(self._l.ojas_b200_gemv_q8k(self._ctx, w.ggml_type, form, C.c_void_p(q.ptr), C.c_void_p(scales.ptr), C.c_void_p(bsums.ptr),
                                             C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr), C.c_void_p(bias.ptr) if bias else None, w.k, w.n, m))

@@ -122,3 +122,27 @@ def test_gemv_with_the_norm_in_its_prologue(gpu, t, n, k, m):
             gpu.free(buf)
     for buf in (wl.buf, xb, gb, y1, y2):
         gpu.free(buf)
+
+
+@pytest.mark.parametrize("t,n,k,m", [(ob.Q6_K, 512, 14336, 1), (Q4_K, 520, 768, 3), (ob.Q8_0, 256, 1024, 2)])
+def test_gemv_with_swiglu_in_its_prologue(gpu, t, n, k, m):
+    """ojas_b200_gemv_silu_mul against the two-launch form (producer, then gemv_q8k) bit for bit (the same expression,
+    the same quantization), and against the CPU composition."""
+    raw = synth_weights(t, n, k)
+    wl = gpu.load_weight(raw, t, n, k)
+    g, u = activations(m, k, seed=51) * np.float32(2.0), activations(m, k, seed=52)
+    gb, ub = gpu.upload(g), gpu.upload(u)
+    y1, y2 = gpu.alloc(m * n), gpu.alloc(m * n)
+    gpu.gemv_silu_mul(wl, gb, ub, y1, m)
+    got = gpu.read(y1, np.float32, m * n).reshape(m, n)
+    want = np.stack([oracle.matvec_kq(raw, t, n, k, oracle.silu_mul(g[r], u[r])) for r in range(m)])
+    assert rel_l2(got, want) < 2e-4
+    if t != ob.Q8_0:
+        q, s, b = _q8k_bufs(gpu, m, k)
+        gpu.silu_mul_q8k(gb, ub, m, k, q, s, b)
+        gpu.gemv_q8k(wl, q, s, b, y2, m)
+        assert np.array_equal(gpu.read(y2, np.float32, m * n).view(np.uint32), got.reshape(-1).view(np.uint32))
+        for buf in (q, s, b):
+            gpu.free(buf)
+    for buf in (wl.buf, gb, ub, y1, y2):
+        gpu.free(buf)
