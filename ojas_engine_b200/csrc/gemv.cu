@@ -278,30 +278,63 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
     __syncthreads();
 }
 
-// Q8_0: f32 rows as they are.
+// Q8_0 keeps f32 activations on the CPU (dot_q80, crates/ojas-cpu/src/cpu_math.rs:971-981).  Here a value enters as
+// three int8 terms per block of 32: x = s * (q1 + q2 / 254 + q3 / 254^2) with s = max|x| / 127 of the block,
+// q1 = round(x / s), q2 = round(254 * remainder), q3 = round(254 * remainder of that): the representation error is
+// below s * 0.5 / 254^2, i.e. 6e-8 of the block's largest value -- fp32 level -- and the dot of a block becomes three
+// exact integer dots (dp4a) instead of 32 conversions and 32 fp32 multiply-adds.
+// Per activation row in shared memory: q1 [K], q2 [K], q3 [K] int8, then s [K / 32] f32.
+__host__ __device__ inline size_t q80_act_row_bytes(size_t K) { return 3 * K + K / 8; }
+
 template <int MT, int PRO>
-__device__ __forceinline__ void stage_f32(const GemvArgs &a, float *xs, int warps) {
-    const int k4 = a.K >> 2;
+__device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int nsb, int warps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t rb = q80_act_row_bytes((size_t)a.K);
     float inv[MT];
     if (PRO == 1) row_inv_norms<MT>(a, warps, inv);
-    for (int idx = threadIdx.x; idx < MT * k4; idx += blockDim.x) {
-        const int m = idx / k4, f4 = idx - m * k4;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (m < a.M) v = __ldg(reinterpret_cast<const float4 *>(a.x + (size_t)src_row(a, m) * a.K) + f4);
-        if (PRO == 2 && m < a.M) {
-            const float4 u = __ldg(reinterpret_cast<const float4 *>(a.x2 + (size_t)m * a.K) + f4);
-            v.x = __fmul_rn(__fdiv_rn(v.x, 1.0f + expf(-v.x)), u.x); v.y = __fmul_rn(__fdiv_rn(v.y, 1.0f + expf(-v.y)), u.y);
-            v.z = __fmul_rn(__fdiv_rn(v.z, 1.0f + expf(-v.z)), u.z); v.w = __fmul_rn(__fdiv_rn(v.w, 1.0f + expf(-v.w)), u.w);
-        }
-        if (PRO == 1 && m < a.M) {
-            const float4 g = __ldg(reinterpret_cast<const float4 *>(a.norm_w) + f4);
-            float im = inv[0];
 #pragma unroll
-            for (int j = 1; j < MT; j++) im = m == j ? inv[j] : im;
-            v.x = __fmul_rn(__fmul_rn(v.x, im), g.x); v.y = __fmul_rn(__fmul_rn(v.y, im), g.y);
-            v.z = __fmul_rn(__fmul_rn(v.z, im), g.z); v.w = __fmul_rn(__fmul_rn(v.w, im), g.w);
+    for (int m = 0; m < MT; m++) {
+        uint8_t *row = act + m * rb;
+        float *sc = reinterpret_cast<float *>(row + 3 * (size_t)a.K);
+        if (m < a.M) {
+            const float *xr = a.x + (size_t)src_row(a, m) * a.K;
+            for (int sb = warp; sb < nsb; sb += warps) {
+                float v[8];
+                if (PRO == 1) {
+                    load_normed(xr, a.norm_w, inv[m], sb, lane, v);
+                } else if (PRO == 2) {
+                    load_silu_mul(xr, a.x2 + (size_t)m * a.K, sb, lane, v);
+                } else {
+                    const float4 p = __ldg(reinterpret_cast<const float4 *>(xr + sb * 256) + lane * 2), q = __ldg(reinterpret_cast<const float4 *>(xr + sb * 256) + lane * 2 + 1);
+                    v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
+                }
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));      // a block of 32 = four lanes
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                const float s = __fdiv_rn(amax, 127.0f), is = amax > 0.0f ? __fdiv_rn(1.0f, s) : 0.0f;
+                uint32_t w1[2] = {0u, 0u}, w2[2] = {0u, 0u}, w3[2] = {0u, 0u};
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float t = __fmul_rn(v[i], is);
+                    const float q1 = fminf(fmaxf(rintf(t), -127.0f), 127.0f);
+                    const float t2 = __fmul_rn(__fsub_rn(t, q1), 254.0f);
+                    const float q2 = fminf(fmaxf(rintf(t2), -127.0f), 127.0f);
+                    const float q3 = fminf(fmaxf(rintf(__fmul_rn(__fsub_rn(t2, q2), 254.0f)), -127.0f), 127.0f);
+                    w1[i >> 2] |= ((uint32_t)(int)q1 & 0xffu) << (8 * (i & 3));
+                    w2[i >> 2] |= ((uint32_t)(int)q2 & 0xffu) << (8 * (i & 3));
+                    w3[i >> 2] |= ((uint32_t)(int)q3 & 0xffu) << (8 * (i & 3));
+                }
+                const size_t at = (size_t)sb * 256 + lane * 8;
+                *reinterpret_cast<uint2 *>(row + at) = make_uint2(w1[0], w1[1]);
+                *reinterpret_cast<uint2 *>(row + (size_t)a.K + at) = make_uint2(w2[0], w2[1]);
+                *reinterpret_cast<uint2 *>(row + 2 * (size_t)a.K + at) = make_uint2(w3[0], w3[1]);
+                if ((lane & 3) == 0) sc[sb * 8 + (lane >> 2)] = s;
+            }
+        } else {
+            for (size_t i = threadIdx.x; i < rb / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(row)[i] = 0u;
         }
-        reinterpret_cast<float4 *>(xs)[idx] = v;
     }
     __syncthreads();
 }
@@ -423,48 +456,35 @@ __device__ __forceinline__ void step_q6k(const uint8_t *wl, int r, const uint8_t
     }
 }
 
-// Q8_0 (dot_q80, crates/ojas-cpu/src/cpu_math.rs:971-981): f32 activations; per 32-weight block an f32 sum of
-// f32(q) * x, then d * that sum.
-__device__ __forceinline__ float s8_to_f32(uint32_t w_flipped, int i) {
-    // w_flipped = word ^ 0x80808080: byte + 128 in 0..255 goes into the mantissa of 2^23
-    const uint32_t bits = __byte_perm(w_flipped, 0x4b000000u, 0x7540 | i);
-    return __uint_as_float(bits) - 8388736.0f;
-}
-
+// Q8_0 (dot_q80, crates/ojas-cpu/src/cpu_math.rs:971-981): per block of 32 weights three exact integer dots against the
+// activation's three int8 terms, then d * s * (D1 + D2 / 254 + D3 / 254^2).
 template <int MT>
-__device__ __forceinline__ void step_q80(const uint8_t *wl, const float *xs, int K, int sb, float (&acc)[MT]) {
+__device__ __forceinline__ void step_q80(const uint8_t *wl, const uint8_t *act, int K, int sb, float (&acc)[MT]) {
     const uint4 D = *reinterpret_cast<const uint4 *>(wl + 16 * 128);
     const uint32_t dw[4] = {D.x, D.y, D.z, D.w};
+    const size_t rb = q80_act_row_bytes((size_t)K);
+    constexpr float C1 = 1.0f / 254.0f;
 #pragma unroll
     for (int b = 0; b < 8; b++) {
-        float s[MT];
-#pragma unroll
-        for (int m = 0; m < MT; m++) s[m] = 0.0f;
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const uint4 W = *reinterpret_cast<const uint4 *>(wl + (2 * b + h) * 128);
-            const uint32_t wv[4] = {W.x ^ 0x80808080u, W.y ^ 0x80808080u, W.z ^ 0x80808080u, W.w ^ 0x80808080u};
-            float wf[16];
-#pragma unroll
-            for (int p = 0; p < 4; p++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) wf[p * 4 + i] = s8_to_f32(wv[p], i);
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                const float4 *xm = reinterpret_cast<const float4 *>(xs + (size_t)m * K + sb * 256 + b * 32 + h * 16);
-#pragma unroll
-                for (int p = 0; p < 4; p++) {
-                    const float4 xv = xm[p];
-                    s[m] = fmaf(wf[p * 4 + 0], xv.x, s[m]);
-                    s[m] = fmaf(wf[p * 4 + 1], xv.y, s[m]);
-                    s[m] = fmaf(wf[p * 4 + 2], xv.z, s[m]);
-                    s[m] = fmaf(wf[p * 4 + 3], xv.w, s[m]);
-                }
-            }
-        }
+        const uint4 W0 = *reinterpret_cast<const uint4 *>(wl + (2 * b) * 128), W1 = *reinterpret_cast<const uint4 *>(wl + (2 * b + 1) * 128);
+        const int wv[8] = {(int)W0.x, (int)W0.y, (int)W0.z, (int)W0.w, (int)W1.x, (int)W1.y, (int)W1.z, (int)W1.w};
         const float d = f16_bits_to_f32(dw[b >> 1] >> (16 * (b & 1)));
 #pragma unroll
-        for (int m = 0; m < MT; m++) acc[m] = fmaf(d, s[m], acc[m]);
+        for (int m = 0; m < MT; m++) {
+            const uint8_t *row = act + m * rb + (size_t)sb * 256 + b * 32;
+            int dot[3];
+#pragma unroll
+            for (int t = 0; t < 3; t++) {
+                const uint4 x0 = *reinterpret_cast<const uint4 *>(row + (size_t)t * K), x1 = *reinterpret_cast<const uint4 *>(row + (size_t)t * K + 16);
+                int v = __dp4a(wv[0], (int)x0.x, 0);
+                v = __dp4a(wv[1], (int)x0.y, v); v = __dp4a(wv[2], (int)x0.z, v); v = __dp4a(wv[3], (int)x0.w, v);
+                v = __dp4a(wv[4], (int)x1.x, v); v = __dp4a(wv[5], (int)x1.y, v); v = __dp4a(wv[6], (int)x1.z, v); v = __dp4a(wv[7], (int)x1.w, v);
+                dot[t] = v;
+            }
+            const float s = reinterpret_cast<const float *>(act + m * rb + 3 * (size_t)K)[sb * 8 + b];
+            const float f = fmaf(fmaf((float)dot[2], C1, (float)dot[1]), C1, (float)dot[0]);
+            acc[m] = fmaf(__fmul_rn(d, s), f, acc[m]);
+        }
     }
 }
 
@@ -479,7 +499,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     const int nst = 1 << a.nst_log, S = 1 << a.S_log, T = 1 << a.T_log;   // powers of two: no divisions below
     uint8_t *ring = smem + (size_t)warp * nst * STEP;
     uint8_t *act = smem + (size_t)warps * nst * STEP;
-    const size_t act_bytes = TYPE == OJAS_B200_Q8_0 ? (size_t)MT * a.K * 4 : (size_t)MT * ActLayout<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE>::row_bytes(nsb);
+    const size_t act_bytes = TYPE == OJAS_B200_Q8_0 ? (size_t)MT * q80_act_row_bytes((size_t)a.K) : (size_t)MT * ActLayout<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE>::row_bytes(nsb);
     uint64_t *bar = reinterpret_cast<uint64_t *>(act + ((act_bytes + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
     float *part = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(act + ((act_bytes + 15) & ~(size_t)15)) + GEMV_MAX_WARPS * GEMV_MAX_STAGES);
 
@@ -526,7 +546,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         for (int i = 0; i < nst && i < nsteps; i++) issue();
     }
     if (first_pass) grid_dependency_wait();                       // activations (and y for the accumulate form) come from the kernel before
-    if (TYPE == OJAS_B200_Q8_0) stage_f32<MT, PRO>(a, reinterpret_cast<float *>(act), warps);
+    if (TYPE == OJAS_B200_Q8_0) stage_q80<MT, PRO>(a, act, nsb, warps);
     else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ, PRO>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
     const float alpha = a.alpha ? __ldg(a.alpha) : 1.0f;
@@ -550,7 +570,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
             const int row = (ub + 4 * g + unit) * 8 + r;
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q6_K) step_q6k<MT, DUMP>(wl + stg * STEP, r, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 16 : nullptr);
-            else step_q80<MT>(wl + stg * STEP, reinterpret_cast<const float *>(act), a.K, sb, acc);
+            else step_q80<MT>(wl + stg * STEP, act, a.K, sb, acc);
         }
         __syncwarp();                                             // every lane has read the stage
         if (q + nst < nsteps && lane == 0) {
@@ -657,7 +677,7 @@ struct GemvPlan {
 
 static size_t gemv_act_bytes(uint32_t type, int MT, size_t K) {
     const size_t nsb = K / 256;
-    if (type == OJAS_B200_Q8_0) return (size_t)MT * K * 4;
+    if (type == OJAS_B200_Q8_0) return (size_t)MT * q80_act_row_bytes(K);
     return (size_t)MT * (type == OJAS_B200_Q4_K ? ActLayout<OJAS_B200_Q4_K>::row_bytes((int)nsb) : ActLayout<OJAS_B200_Q6_K>::row_bytes((int)nsb));
 }
 
