@@ -284,7 +284,9 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
 // below s * 0.5 / 254^2, i.e. 6e-8 of the block's largest value -- fp32 level -- and the dot of a block becomes three
 // exact integer dots (dp4a) instead of 32 conversions and 32 fp32 multiply-adds.
 // Per activation row in shared memory: q1 [K], q2 [K], q3 [K] int8, then s [K / 32] f32.
-__host__ __device__ inline size_t q80_act_row_bytes(size_t K) { return 3 * K + K / 8; }
+// (16 bytes of padding: eight rows then start in eight different 16-byte bank groups, which the tensor-core form of
+// the batch reads at once)
+__host__ __device__ inline size_t q80_act_row_bytes(size_t K) { return 3 * K + K / 8 + 16; }
 
 template <int MT, int PRO>
 __device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int nsb, int warps) {
@@ -488,6 +490,51 @@ __device__ __forceinline__ void step_q80(const uint8_t *wl, const uint8_t *act, 
     }
 }
 
+// Q8_0, eight activation rows: the same three integer dots per block on the tensor cores.  One warp step = 32 weight
+// rows = two 16-row MMA tiles; per block of 32 weights A = 16 rows x 32 int8 (rows g, g + 8 = row g of two 8-row
+// units), B = 8 activation rows x 32 int8 of one term: mma.sync.m16n8k32.s8.s8, exact int32.  acc[4 t + i] belongs to
+// weight row 16 t + g + 8 (i / 2) of the step and activation row 2 q + (i % 2)  (g = lane / 4, q = lane % 4).
+__device__ __forceinline__ void mma_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void step_q80_mma(const uint8_t *stage, const uint8_t *act, int K, int sb, int lane, float (&acc)[8]) {
+    constexpr int TB = tile_bytes(OJAS_B200_Q8_0);
+    const int g8 = lane >> 2, q4 = lane & 3;
+    const size_t rb = q80_act_row_bytes((size_t)K);
+    constexpr float C1 = 1.0f / 254.0f;
+    const uint8_t *xb = act + g8 * rb + (size_t)sb * 256 + 4 * q4;                 // B fragments: activation row g8
+    const float *s0p = reinterpret_cast<const float *>(act + (2 * q4) * rb + 3 * (size_t)K) + sb * 8;
+    const float *s1p = reinterpret_cast<const float *>(act + (2 * q4 + 1) * rb + 3 * (size_t)K) + sb * 8;
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const uint8_t *ra = stage + (2 * t) * TB + g8 * 16, *rbw = ra + TB;          // row g8 of the tile's two units
+        const uint4 DA = *reinterpret_cast<const uint4 *>(ra + 16 * 128), DB = *reinterpret_cast<const uint4 *>(rbw + 16 * 128);
+        const uint32_t da[4] = {DA.x, DA.y, DA.z, DA.w}, db[4] = {DB.x, DB.y, DB.z, DB.w};
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const uint32_t a0 = *reinterpret_cast<const uint32_t *>(ra + (2 * b) * 128 + 4 * q4), a2 = *reinterpret_cast<const uint32_t *>(ra + (2 * b + 1) * 128 + 4 * q4);
+            const uint32_t a1 = *reinterpret_cast<const uint32_t *>(rbw + (2 * b) * 128 + 4 * q4), a3 = *reinterpret_cast<const uint32_t *>(rbw + (2 * b + 1) * 128 + 4 * q4);
+            float f[4];
+#pragma unroll
+            for (int term = 2; term >= 0; term--) {
+                const uint8_t *xp = xb + (size_t)term * K + b * 32;
+                int d[4] = {0, 0, 0, 0};
+                mma_s8s8(d, a0, a1, a2, a3, *reinterpret_cast<const uint32_t *>(xp), *reinterpret_cast<const uint32_t *>(xp + 16));
+#pragma unroll
+                for (int i = 0; i < 4; i++) f[i] = term == 2 ? (float)d[i] : fmaf(f[i], C1, (float)d[i]);
+            }
+            const float wa = f16_bits_to_f32(da[b >> 1] >> (16 * (b & 1))), wb = f16_bits_to_f32(db[b >> 1] >> (16 * (b & 1)));
+            const float s0 = s0p[b], s1 = s1p[b];
+            acc[4 * t + 0] = fmaf(__fmul_rn(wa, s0), f[0], acc[4 * t + 0]);
+            acc[4 * t + 1] = fmaf(__fmul_rn(wa, s1), f[1], acc[4 * t + 1]);
+            acc[4 * t + 2] = fmaf(__fmul_rn(wb, s0), f[2], acc[4 * t + 2]);
+            acc[4 * t + 3] = fmaf(__fmul_rn(wb, s1), f[3], acc[4 * t + 3]);
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------- the kernel body
 // `ring_uses` counts the steps this warp has put through its ring since the kernel began (the grouped kernel calls
 // the body once per pass and the barriers' phases carry over).
@@ -566,7 +613,11 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         const unsigned stg = use & (unsigned)(nst - 1);
         const int g = team + k * T;
         gv_bar_wait(bar + stg, (use >> a.nst_log) & 1u, a.status, dead);
-        if (4 * g + unit < nu) {
+        if (TYPE == OJAS_B200_Q8_0 && MT == 8) {
+            // the whole warp, whatever the number of live units: rows past the CTA's last unit read stale bytes of the
+            // ring and are never stored
+            step_q80_mma(ring + stg * STEP, act, a.K, sb, lane, reinterpret_cast<float (&)[8]>(acc));
+        } else if (4 * g + unit < nu) {
             const int row = (ub + 4 * g + unit) * 8 + r;
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q6_K) step_q6k<MT, DUMP>(wl + stg * STEP, r, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 16 : nullptr);
@@ -582,10 +633,19 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         bool flush = q + 1 == nsteps;
         while (sb >= nsb) { sb -= nsb; k++; flush = true; }
         if (flush && !DUMP) {
+            if (TYPE == OJAS_B200_Q8_0 && MT == 8) {              // tensor-core form: see step_q80_mma for who holds what
 #pragma unroll
-            for (int m = 0; m < MT; m++) {
-                part[(((team + k_now * T) * P + slot) * MT + m) * 32 + lane] = acc[m];
-                acc[m] = 0.0f;
+                for (int i = 0; i < 8; i++) {
+                    const int rr = 16 * (i >> 2) + (lane >> 2) + 8 * ((i >> 1) & 1), m = 2 * (lane & 3) + (i & 1);
+                    part[(((team + k_now * T) * P + slot) * MT + m) * 32 + rr] = acc[i];
+                    acc[i] = 0.0f;
+                }
+            } else {
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    part[(((team + k_now * T) * P + slot) * MT + m) * 32 + lane] = acc[m];
+                    acc[m] = 0.0f;
+                }
             }
         }
     }
@@ -764,11 +824,13 @@ static void gemv_fill(GemvArgs &a, ojas_b200_ctx *ctx, const GemvPlan &p) {
 }
 
 static int pick_mt(size_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
+// Q8_0 takes the tensor-core form (eight rows, the absent ones zero) from three rows on
+static int pick_mt_for(uint32_t type, size_t M) { return type == OJAS_B200_Q8_0 && M >= 3 ? 8 : pick_mt(M); }
 
 // One launch over at most 8 activation rows.  Returns 1 when the batch does not fit in shared memory at this
 // tile height (the caller then cuts the batch).
 static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool dump, GemvArgs args) {
-    const int MT = pick_mt((size_t)args.M);
+    const int MT = pick_mt_for(type, (size_t)args.M);
     GemvPlan p;
     if (!gemv_plan(ctx, type, MT, (size_t)args.K, (size_t)args.N, p)) return 1;
     gemv_fill(args, ctx, p);
@@ -988,7 +1050,7 @@ static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args,
     // the whole batch in one launch when its activations fit beside the ring, else in halves
     for (size_t cap = M; cap >= 1; cap = cap / 2) {
         GemvPlan p;
-        if (!gemv_plan(ctx, type, pick_mt(cap), (size_t)args.K, (size_t)args.N, p)) {
+        if (!gemv_plan(ctx, type, pick_mt_for(type, cap), (size_t)args.K, (size_t)args.N, p)) {
             if (cap == 1) break;
             continue;
         }
