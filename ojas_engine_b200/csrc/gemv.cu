@@ -835,7 +835,9 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     if (!gemv_plan(ctx, type, MT, (size_t)args.K, (size_t)args.N, p)) return 1;
     gemv_fill(args, ctx, p);
     if (preq || dump) args.own_x = dump ? args.own_x : 0;
-    const bool two = p.smem <= (size_t)ctx->smem_optin / 2 - 1024;      // two CTAs per SM fit
+    // two CTAs per SM fit.  (Not for Q8_0 and not for pre-quantized rows: their bodies do not fit in 64 registers, and a
+    // spilled value costs a cold round trip to memory in every launch: measured, 12 bytes of spills added 1 us.)
+    const bool two = p.smem <= (size_t)ctx->smem_optin / 2 - 1024 && type != OJAS_B200_Q8_0 && !(preq && type == OJAS_B200_Q4_K);
 #define GEMV_CASE(T, PQ, NAME)                                                                 \
     switch (MT) {                                                                              \
     case 1: return two ? launch_gemv(ctx, gemv_kernel<T, 1, PQ, false, 2>, args, p, NAME)      \
