@@ -136,3 +136,70 @@ def dot_q80(row: np.ndarray, x: np.ndarray) -> np.float32:
             acc = F(acc + F(F(int(qv[j])) * x[b * 32 + j]))
         s = F(s + F(d * acc))
     return s
+
+
+def matvec_kq(raw: np.ndarray, t: int, n: int, k: int, x: np.ndarray) -> np.ndarray:
+    """cpu_math.rs:1145-1189: activations quantized once (K-quants), one block dot per row."""
+    rb = {12: 144 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32)}[t]
+    rows = np.asarray(raw, np.uint8).reshape(n, rb)
+    out = np.empty(n, F)
+    if t == 8:
+        for r in range(n):
+            out[r] = dot_q80(rows[r], x)
+        return out
+    act = quant_q8k(x)
+    for r in range(n):
+        out[r] = (dot_q4k if t == 12 else dot_q6k)(rows[r], act)[0]
+    return out
+
+
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    """cpu_math.rs:456-460: the mean of squares summed in index order, inv = 1 / sqrt(mean + eps), (x * inv) * w."""
+    x, w = np.asarray(x, F), np.asarray(w, F)
+    ss = F(0)
+    for v in x:
+        ss = F(ss + F(v * v))
+    ss = F(ss / F(x.size))
+    inv = F(F(1) / np.sqrt(F(ss + F(eps)), dtype=F))
+    return (x * inv).astype(F) * w
+
+
+def silu_mul(g: np.ndarray, u: np.ndarray) -> np.ndarray:
+    """cpu_math.rs:486 and cpu_glm.rs:556: act = (g / (1 + exp(-g))) * u."""
+    g, u = np.asarray(g, F), np.asarray(u, F)
+    return ((g / (F(1) + np.exp(-g, dtype=F))).astype(F) * u).astype(F)
+
+
+def moe_topk(logits: np.ndarray, ksel: int):
+    """crates/ojas-cuda/src/kernels/moe.rs:45-70: softmax over the logits, KSEL passes each taking the largest remaining
+    probability (ties to the lowest index), the chosen weights renormalised to sum to 1."""
+    lg = np.asarray(logits, F)
+    p = np.exp(lg - lg.max(), dtype=F)
+    total = F(p.sum(dtype=np.float64))
+    idx, tw = [], []
+    for _ in range(ksel):
+        best = int(np.argmax(p))                      # numpy's argmax returns the first of equal maxima
+        idx.append(best)
+        tw.append(F(p[best] / total))
+        p[best] = F(-1)
+    wsum = F(0)
+    for v in tw:
+        wsum = F(wsum + v)
+    return np.asarray(idx, np.uint32), np.asarray([F(v / wsum) for v in tw], F)
+
+
+def moe_ffn(wg, wu, wd, t_gu: int, t_d: int, h: np.ndarray, idx: np.ndarray, wgt: np.ndarray, d: int, ffn: int) -> np.ndarray:
+    """cpu_glm.rs:551-582: per token, per pick in order: gate and up of the expert over the token's row, SwiGLU, the
+    expert's down projection, added with the pick's weight."""
+    h = np.asarray(h, F).reshape(-1, d)
+    rg, rd = {12: 144, 14: 210}[t_gu] * (d // 256) * ffn, {12: 144, 14: 210}[t_d] * (ffn // 256) * d
+    wg, wu, wd = np.asarray(wg, np.uint8).reshape(-1), np.asarray(wu, np.uint8).reshape(-1), np.asarray(wd, np.uint8).reshape(-1)
+    out = np.zeros((h.shape[0], d), F)
+    for t in range(h.shape[0]):
+        for j in range(idx.shape[1]):
+            e = int(idx[t, j])
+            gv = matvec_kq(wg[e * rg:(e + 1) * rg], t_gu, ffn, d, h[t])
+            uv = matvec_kq(wu[e * rg:(e + 1) * rg], t_gu, ffn, d, h[t])
+            dv = matvec_kq(wd[e * rd:(e + 1) * rd], t_d, d, ffn, silu_mul(gv, uv))
+            out[t] = (out[t] + (F(wgt[t, j]) * dv).astype(F)).astype(F)
+    return out

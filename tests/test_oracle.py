@@ -194,3 +194,46 @@ def test_tvec_generator():
         s = (s * 1664525 + 1013904223) & 0xFFFFFFFF
         want.append(np.float32(s >> 9) / np.float32(1 << 23) - np.float32(1.0))
     assert np.array_equal(v, np.array(want, np.float32))
+
+
+def test_matvec_second_entry():
+    import second_entry
+    rng = np.random.default_rng(11)
+    for t, n, k in ((Q4_K, 9, 512), (Q6_K, 7, 768), (Q8_0, 5, 256)):
+        raw = oracle.synth_blocks(t, n * k // (32 if t == Q8_0 else 256))
+        x = rng.standard_normal(k).astype(np.float32)
+        a, b = oracle.matvec_kq(raw, t, n, k, x, threads=1), second_entry.matvec_kq(raw, t, n, k, x)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_producers_second_entry():
+    """RMSNorm and SwiGLU of the oracle against the transcription of the Rust source: RMSNorm bit for bit (same order
+    of additions), SwiGLU to the last bit of the exponential (libm against numpy: at most one unit in the last place)."""
+    import second_entry
+    rng = np.random.default_rng(12)
+    x = (rng.standard_normal(768) * 3).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(768)).astype(np.float32)
+    a, b = oracle.rmsnorm(x, w, 1e-5), second_entry.rmsnorm(x, w, 1e-5)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    g, u = (rng.standard_normal(512) * 2).astype(np.float32), rng.standard_normal(512).astype(np.float32)
+    a, b = oracle.silu_mul(g, u), second_entry.silu_mul(g, u)
+    assert np.abs(a.view(np.int32).astype(np.int64) - b.view(np.int32).astype(np.int64)).max() <= 2
+
+
+def test_router_and_expert_ffn_second_entry():
+    import second_entry
+    rng = np.random.default_rng(13)
+    e, ksel, d, ffn, m = 4, 2, 256, 512, 3
+    lg = rng.standard_normal((m, e)).astype(np.float32)
+    lg[1, 2] = lg[1, 0]                                     # a tie: the lower index wins
+    idx, wgt = oracle.moe_topk(lg, ksel)
+    for t in range(m):
+        i2, w2 = second_entry.moe_topk(lg[t], ksel)
+        assert np.array_equal(idx[t], i2) and np.allclose(wgt[t], w2, rtol=2e-6, atol=0)
+    wg = oracle.synth_blocks(Q4_K, e * ffn * d // 256)
+    wu = oracle.synth_blocks(Q4_K, e * ffn * d // 256)[::-1].copy()
+    wd = oracle.synth_blocks(Q6_K, e * d * ffn // 256)
+    h = rng.standard_normal((m, d)).astype(np.float32)
+    a = oracle.moe_ffn(wg, wu, wd, Q4_K, Q6_K, h, idx, wgt, d, ffn, threads=1)
+    b = second_entry.moe_ffn(wg, wu, wd, Q4_K, Q6_K, h, idx, wgt, d, ffn)
+    assert rel_l2(a, b) < 1e-6                              # (the exponential's last bit may flip a Q8_K rounding)
