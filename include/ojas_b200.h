@@ -70,6 +70,16 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
  * instead of 1e-7).  "moe_i8" (default 0): decode-sized Q4_K expert FFNs on the int8 tensor-core kernel too (same
  * results as the default kernel; slower at 64 tokens). */
 OJAS_B200_API int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value);
+/* Every option can also be given in the environment, read once at ojas_b200_create: OJAS_B200_<OPTION>=<integer>
+ * (OJAS_B200_PDL=0, OJAS_B200_GEMM_KSPLIT=4, ...).
+ * "profile" (default 0; OJAS_B200_PROFILE=1): the per-launch event profiler, the counterpart of KernelProfile under
+ * OJAS_CUDA_PROFILE (crates/ojas-cuda/src/device.rs:275-318).  One event is recorded behind every launch; a launch is
+ * charged the time between the event before it and its own.  profile_report writes "kernel launches total_ms avg_us"
+ * lines (largest total first) and returns the length of the full text; it waits for the stream.  Launches made while
+ * the stream is being captured are not recorded.  With OJAS_B200_PROFILE set the report is also printed to stderr when
+ * the context is destroyed. */
+OJAS_B200_API size_t ojas_b200_profile_report(ojas_b200_ctx *ctx, char *buf, size_t len);
+OJAS_B200_API int ojas_b200_profile_reset(ojas_b200_ctx *ctx);
 OJAS_B200_API const char *ojas_b200_last_error(ojas_b200_ctx *ctx);
 OJAS_B200_API int ojas_b200_sm_count(ojas_b200_ctx *ctx);
 /* Launches issued by this context since creation (the benchmark's launch counter). */

@@ -2,7 +2,113 @@
 #include <stdarg.h>
 #include <stdlib.h>
 
+#include <ctype.h>
+
+#include <string>
+#include <vector>
+
 #include "common.cuh"
+
+// ---------------------------------------------------------------------------- per-launch profiler
+// The counterpart of KernelProfile (crates/ojas-cuda/src/device.rs:275-318: events around every launch when
+// OJAS_CUDA_PROFILE is set, per-kernel milliseconds printed at the end).  Here ONE event is recorded behind every
+// launch and a launch is charged the time between the event before it and its own: the stream is in order, so that is
+// the time the launch added to the stream (with programmatic dependent launch a kernel's prologue overlaps its
+// predecessor and is charged to the predecessor).  Nothing is recorded while the stream is being captured.
+struct OjasProfile {
+    struct Rec { const char *name; cudaEvent_t ev; };
+    struct Sum { std::string name; uint64_t launches; double ms; };
+    cudaEvent_t origin = nullptr;
+    std::vector<Rec> recs;
+    std::vector<cudaEvent_t> spare;
+    std::vector<Sum> sums;
+};
+
+static void profile_fold(ojas_b200_ctx *ctx) {                   // waits for the stream, turns the records into sums
+    OjasProfile *p = ctx->prof;
+    if (!p || p->recs.empty()) return;
+    cudaEventSynchronize(p->recs.back().ev);
+    cudaEvent_t prev = p->origin;
+    for (const OjasProfile::Rec &r : p->recs) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, prev, r.ev) != cudaSuccess) ms = 0.0f;
+        size_t i = 0;
+        while (i < p->sums.size() && p->sums[i].name != r.name) i++;
+        if (i == p->sums.size()) p->sums.push_back({r.name, 0, 0.0});
+        p->sums[i].launches++;
+        p->sums[i].ms += ms;
+        if (prev != p->origin) p->spare.push_back(prev);
+        prev = r.ev;
+    }
+    p->spare.push_back(p->origin);                               // the last event becomes the new origin
+    p->origin = prev;
+    p->recs.clear();
+    cudaGetLastError();
+}
+
+void ojas_count_launch(ojas_b200_ctx *ctx, const char *name) {
+    ctx->launches++;
+    OjasProfile *p = ctx->prof;
+    if (!p) return;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(ctx->stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return; }
+    if (p->recs.size() >= 16384) profile_fold(ctx);
+    cudaEvent_t ev = nullptr;
+    if (!p->spare.empty()) { ev = p->spare.back(); p->spare.pop_back(); }
+    else if (cudaEventCreate(&ev) != cudaSuccess) { cudaGetLastError(); return; }
+    cudaEventRecord(ev, ctx->stream);
+    p->recs.push_back({name, ev});
+}
+
+static int profile_set(ojas_b200_ctx *ctx, bool on) {
+    if (on == (ctx->prof != nullptr)) return 0;
+    if (on) {
+        OjasProfile *p = new OjasProfile();
+        if (cudaEventCreate(&p->origin) != cudaSuccess) { delete p; return ojas_fail(ctx, OJAS_B200_E_CUDA, "profile: cannot create an event"); }
+        cudaEventRecord(p->origin, ctx->stream);
+        ctx->prof = p;
+        return 0;
+    }
+    profile_fold(ctx);
+    OjasProfile *p = ctx->prof;
+    ctx->prof = nullptr;
+    for (cudaEvent_t e : p->spare) cudaEventDestroy(e);
+    if (p->origin) cudaEventDestroy(p->origin);
+    delete p;
+    return 0;
+}
+
+// "name launches total_ms avg_us" per line, largest total first; returns the length of the full text (which may exceed
+// `len`: call again with a larger buffer), 0 when the profiler is off.
+extern "C" size_t ojas_b200_profile_report(ojas_b200_ctx *ctx, char *buf, size_t len) {
+    if (!ctx || !ctx->prof) return 0;
+    profile_fold(ctx);
+    std::vector<OjasProfile::Sum> v = ctx->prof->sums;
+    for (size_t i = 0; i < v.size(); i++)
+        for (size_t j = i + 1; j < v.size(); j++)
+            if (v[j].ms > v[i].ms) std::swap(v[i], v[j]);
+    std::string text;
+    char line[256];
+    for (const OjasProfile::Sum &s : v) {
+        snprintf(line, sizeof line, "%-28s %10llu %12.3f %10.2f\n", s.name.c_str(), (unsigned long long)s.launches, s.ms,
+                 s.launches ? s.ms * 1e3 / (double)s.launches : 0.0);
+        text += line;
+    }
+    if (buf && len) {
+        const size_t n = text.size() < len - 1 ? text.size() : len - 1;
+        memcpy(buf, text.data(), n);
+        buf[n] = 0;
+    }
+    return text.size();
+}
+
+extern "C" int ojas_b200_profile_reset(ojas_b200_ctx *ctx) {
+    if (!ctx) return OJAS_B200_E_ARG;
+    if (!ctx->prof) return 0;
+    profile_fold(ctx);
+    ctx->prof->sums.clear();
+    return 0;
+}
 
 int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...) {
     if (ctx) {
@@ -62,8 +168,20 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
         delete ctx;
         return OJAS_B200_E_CUDA;
     }
-    const char *pdl = getenv("OJAS_B200_PDL");   // read once at context creation, like the engine's OJAS_* switches
-    ctx->pdl = !(pdl && pdl[0] == '0');          // on unless OJAS_B200_PDL=0
+    // The option set, read once at context creation the way the engine reads its OJAS_* switches
+    // (crates/ojas-core/src/config.rs:1-22, crates/ojas-cuda/src/device.rs:87-118): OJAS_B200_<OPTION>=<integer> for every
+    // key of ojas_b200_set_option, e.g. OJAS_B200_PDL=0, OJAS_B200_GEMM_KSPLIT=4, OJAS_B200_PROFILE=1.  A value that the
+    // option refuses is ignored.
+    static const char *const keys[] = {"pdl", "gemv_mma", "gemv_warps", "gemv_stages", "gemm_ksplit", "moe_gemm_rows", "moe_i8", "profile"};
+    for (const char *key : keys) {
+        char name[64] = "OJAS_B200_";
+        size_t n = strlen(name);
+        for (const char *c = key; *c && n + 1 < sizeof name; c++) name[n++] = (char)toupper((unsigned char)*c);
+        name[n] = 0;
+        const char *v = getenv(name);
+        if (v && *v) ojas_b200_set_option(ctx, key, atoi(v));
+    }
+    ctx->err[0] = 0;
     *out = ctx;
     return 0;
 }
@@ -71,6 +189,15 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
 extern "C" void ojas_b200_destroy(ojas_b200_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    if (ctx->prof) {
+        if (getenv("OJAS_B200_PROFILE")) {                        // switched on from the environment: the report goes to stderr
+            const size_t n = ojas_b200_profile_report(ctx, nullptr, 0);
+            std::string text(n + 1, '\0');
+            ojas_b200_profile_report(ctx, &text[0], n + 1);
+            fprintf(stderr, "ojas_b200 profile (kernel, launches, total ms, avg us)\n%s", text.c_str());
+        }
+        profile_set(ctx, false);
+    }
     if (ctx->act_scratch) cudaFree(ctx->act_scratch);
     if (ctx->reserved) cudaFree(ctx->reserved);
     if (ctx->gemm_flags) cudaFree(ctx->gemm_flags);
@@ -113,6 +240,7 @@ extern "C" size_t ojas_b200_reserved_bytes(ojas_b200_ctx *ctx) { return ctx ? ct
 extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int value) {
     if (!ctx || !key) return OJAS_B200_E_ARG;
     if (!strcmp(key, "pdl")) { ctx->pdl = value != 0; return 0; }
+    if (!strcmp(key, "profile")) return profile_set(ctx, value != 0);
     if (!strcmp(key, "gemv_mma")) {
         if (value < 0 || value > 1) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_mma must be 0 or 1");
         ctx->gemv_mma = value;

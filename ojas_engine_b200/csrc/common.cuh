@@ -18,6 +18,7 @@ struct ojas_b200_ctx {
     int sm_count = 0;
     int smem_optin = 0;          // max dynamic shared memory per block (opt-in)
     uint64_t launches = 0;
+    struct OjasProfile *prof = nullptr;  // per-launch event profiler (OJAS_B200_PROFILE=1 or option "profile"), null when off
     int gemv_mma = 1;            // Q4_K batches of 3..8 rows and expert groups on the tensor-core batch kernel (0: per-lane kernels only)
     int gemv_warps = 0;          // GEMV: warps per CTA (0: chosen per shape; otherwise 1..16)
     int gemv_stages = 0;         // GEMV: ring stages per warp (0: chosen per shape; otherwise 1..4)
@@ -50,12 +51,15 @@ int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
             return ojas_fail((ctx), OJAS_B200_E_CUDA, "%s: %s", #call, cudaGetErrorString(e__)); \
     } while (0)
 
+// Every launch of the library passes here: the launch counter and, when the profiler is on, an event behind the launch.
+void ojas_count_launch(ojas_b200_ctx *ctx, const char *name);
+
 #define OJAS_LAUNCH_CHECK(ctx, what)                                                                  \
     do {                                                                                              \
         cudaError_t e__ = cudaGetLastError();                                                         \
         if (e__ != cudaSuccess)                                                                       \
             return ojas_fail((ctx), OJAS_B200_E_CUDA, "launch %s: %s", what, cudaGetErrorString(e__)); \
-        (ctx)->launches++;                                                                            \
+        ojas_count_launch((ctx), what);                                                               \
     } while (0)
 
 // ---------------------------------------------------------------------------- layouts

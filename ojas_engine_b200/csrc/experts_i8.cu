@@ -524,6 +524,6 @@ int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, fl
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     e = cudaLaunchKernelEx(&cfg, experts_i8_kernel, tw[0], tw[1], tq, tm, a);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch experts_i8: %s", cudaGetErrorString(e));
-    ctx->launches++;
+    ojas_count_launch(ctx, "experts_i8");
     return 0;
 }

@@ -810,7 +810,7 @@ static int launch_gemv(ojas_b200_ctx *ctx, KernelT kernel, const GemvArgs &args,
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch %s: %s", name, cudaGetErrorString(e));
-    ctx->launches++;
+    ojas_count_launch(ctx, name);
     return 0;
 }
 
@@ -939,7 +939,7 @@ static int batch_launch(ojas_b200_ctx *ctx, BatchArgs a, int nt_want) {
             cfg.numAttrs = ctx->pdl ? 1 : 0;
             cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
             if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemv_q4k_batch: %s", cudaGetErrorString(e));
-            ctx->launches++;
+            ojas_count_launch(ctx, "gemv_q4k_batch");
             return 0;
         };
         if (NT == 32) return go(gemv_q4k_batch_kernel<4>);
@@ -989,7 +989,7 @@ int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *
             cfg.numAttrs = ctx->pdl ? 1 : 0;
             e = cudaLaunchKernelEx(&cfg, kernel, a);
             if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch moe_q4k_experts: %s", cudaGetErrorString(e));
-            ctx->launches++;
+            ojas_count_launch(ctx, "moe_q4k_experts");
             return 0;
         };
         if (nt == 4) return go(moe_q4k_experts_kernel<4>);
@@ -1029,7 +1029,7 @@ static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvA
     const long long n_sb = (long long)(values / 256);
     quant_q8k_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(args.x, q, scales, bsums, n_sb);
     if (cudaGetLastError() != cudaSuccess) return false;
-    ctx->launches++;
+    ojas_count_launch(ctx, "quant_q8k");
     args.x = nullptr;
     args.q = q;
     args.scales = scales;

@@ -121,7 +121,7 @@ int ojas_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, const float *u, int8_t
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, silu_mul_q8k_kernel, g, u, q, scales, bsums, n_sb);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch silu_mul_q8k: %s", cudaGetErrorString(e));
-    ctx->launches++;
+    ojas_count_launch(ctx, "silu_mul_q8k");
     return 0;
 }
 
@@ -161,6 +161,6 @@ extern "C" int ojas_b200_rmsnorm_q8k(ojas_b200_ctx *ctx, const float *x, const f
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, rmsnorm_q8k_kernel, x, w, eps, xn, q, scales, bsums, (int)K);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch rmsnorm_q8k: %s", cudaGetErrorString(e));
-    ctx->launches++;
+    ojas_count_launch(ctx, "rmsnorm_q8k");
     return 0;
 }

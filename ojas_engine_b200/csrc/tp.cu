@@ -284,7 +284,7 @@ static int tp_join_launch(ojas_b200_tp *tp, int mode, float *y, size_t n_total, 
     cfg.numAttrs = tp->ctx->pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, tp_join_kernel, a);
     if (e != cudaSuccess) return ojas_fail(tp->ctx, OJAS_B200_E_CUDA, "launch tp_join: %s", cudaGetErrorString(e));
-    tp->ctx->launches++;
+    ojas_count_launch(tp->ctx, "tp_join");
     return 0;
 }
 

@@ -23,6 +23,8 @@ SIGNATURES = {
     "ojas_b200_set_option": (_i, [_vp, C.c_char_p, _i]),
     "ojas_b200_last_error": (C.c_char_p, [_vp]),
     "ojas_b200_sm_count": (_i, [_vp]),
+    "ojas_b200_profile_report": (_sz, [_vp, C.c_char_p, _sz]),
+    "ojas_b200_profile_reset": (_i, [_vp]),
     "ojas_b200_launch_count": (_u64, [_vp]),
     "ojas_b200_version": (C.c_char_p, []),
     "ojas_b200_alloc": (_i, [_vp, _sz, C.POINTER(_vp)]),

@@ -148,6 +148,20 @@ class B200Gpu:
     def sync(self) -> None:
         self._ck(self._l.ojas_b200_sync(self._ctx))
 
+    def profile_report(self) -> list[tuple[str, int, float]]:
+        """Per-kernel (name, launches, total ms) of the per-launch profiler (option ``profile``), largest total first."""
+        n = self._l.ojas_b200_profile_report(self._ctx, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        self._l.ojas_b200_profile_report(self._ctx, buf, n + 1)
+        rows = []
+        for line in buf.value.decode().splitlines():
+            name, launches, ms, _ = line.split()
+            rows.append((name, int(launches), float(ms)))
+        return rows
+
+    def profile_reset(self) -> None:
+        self._ck(self._l.ojas_b200_profile_reset(self._ctx))
+
     # ------------------------------------------------------------------ upload layout
     def load_weight(self, raw: np.ndarray, ggml_type: int, n: int, k: int) -> Lin:
         """``Lin::load_as``: GGUF blocks (host bytes) -> repacked planes on the device."""

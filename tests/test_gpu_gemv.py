@@ -320,3 +320,47 @@ def test_graph_capture_and_replay(gpu):
     gpu.graph_destroy(g)
     for b in (w.buf, xb, y):
         gpu.free(b)
+
+
+def test_profiler_and_environment_options(gpu):
+    """The per-launch event profiler (option "profile") names and counts the launches it saw; a second context created
+    with OJAS_B200_* variables in the environment starts with those options (an unknown value is ignored)."""
+    import os
+    n, k = 512, 1024
+    w = gpu.load_weight(synth_weights(Q4_K, n, k), Q4_K, n, k)
+    x, y = gpu.upload(activations(1, k, seed=3)), gpu.alloc(n)
+    gpu.set_option("profile", 1)
+    try:
+        for _ in range(5):
+            gpu.gemv(w, x, y)
+        q, s, b = gpu.alloc_bytes(k), gpu.alloc(k // 256), gpu.alloc_bytes(k // 32 * 4)
+        gpu.quant_q8k(x, 1, k, q, s, b)
+        rows = {name: (launches, ms) for name, launches, ms in gpu.profile_report()}
+        assert rows["gemv_q4k"][0] == 5 and rows["quant_q8k"][0] == 1
+        assert all(ms >= 0.0 for _, ms in rows.values()) and rows["gemv_q4k"][1] > 0.0
+        gpu.profile_reset()
+        gpu.gemv(w, x, y)
+        assert [(name, launches) for name, launches, _ in gpu.profile_report()] == [("gemv_q4k", 1)]
+    finally:
+        gpu.set_option("profile", 0)
+    assert gpu.profile_report() == []
+    want = gpu.read(y, np.float32, n)
+    old = {key: os.environ.get(key) for key in ("OJAS_B200_GEMV_WARPS", "OJAS_B200_PROFILE", "OJAS_B200_GEMM_KSPLIT")}
+    os.environ.update(OJAS_B200_GEMV_WARPS="4", OJAS_B200_PROFILE="1", OJAS_B200_GEMM_KSPLIT="9999")   # the last one is out of range
+    try:
+        other = ob.B200Gpu(0)
+        w2 = other.load_weight(synth_weights(Q4_K, n, k), Q4_K, n, k)
+        x2, y2 = other.upload(activations(1, k, seed=3)), other.alloc(n)
+        other.gemv(w2, x2, y2)
+        assert np.array_equal(other.read(y2, np.float32, n), want)          # four warps per CTA: same sums in the same order
+        assert ("gemv_q4k", 1) in [(name, launches) for name, launches, _ in other.profile_report()]
+        other.set_option("profile", 0)
+        other.close()
+    finally:
+        for key, val in old.items():
+            if val is None:
+                os.environ.pop(key, None)
+            else:
+                os.environ[key] = val
+    for buf in (w.buf, x, y, q, s, b):
+        gpu.free(buf)
