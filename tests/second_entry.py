@@ -167,7 +167,8 @@ def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
 def silu_mul(g: np.ndarray, u: np.ndarray) -> np.ndarray:
     """cpu_math.rs:486 and cpu_glm.rs:556: act = (g / (1 + exp(-g))) * u."""
     g, u = np.asarray(g, F), np.asarray(u, F)
-    return ((g / (F(1) + np.exp(-g, dtype=F))).astype(F) * u).astype(F)
+    with np.errstate(over="ignore"):                  # exp(-g) of a large negative g is inf: g / inf = -0, as in Rust
+        return ((g / (F(1) + np.exp(-g, dtype=F))).astype(F) * u).astype(F)
 
 
 def moe_topk(logits: np.ndarray, ksel: int):
