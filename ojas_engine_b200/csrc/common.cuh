@@ -128,7 +128,7 @@ size_t ojas_experts_i8_meta_bytes(size_t positions, size_t K);
 int ojas_experts_i8_pack(ojas_b200_ctx *ctx, const int8_t *q, const float *scales, const int32_t *bsums, const int *row_index, size_t positions,
                          size_t K, int8_t *q_out, void *meta);
 int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const void *meta,
-                    size_t positions, const int *counts, const int *offsets, size_t E, size_t K, size_t N, int kparts, size_t part_stride);
+                    size_t positions, const int *counts, const int *offsets, size_t E, size_t K, size_t N, int kparts, size_t part_stride, int tok);
 int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
                           const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
                           size_t rows_hint);

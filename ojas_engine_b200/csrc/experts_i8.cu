@@ -29,31 +29,40 @@
 
 namespace {
 
-constexpr int XI_ROWS = 128, XI_TOK = 32;
+constexpr int XI_ROWS = 128;
 constexpr int XI_UNIT_BYTES = 1152;                          // one 8-row Q4_K tile
 constexpr int XI_RAW_BYTES = (XI_ROWS / 8) * XI_UNIT_BYTES;  // 18432
-constexpr int XI_RAW_STAGES = 3;
 constexpr int XI_PREFETCH_STEPS = 8;                         // raw tiles asked into L2 this many steps ahead of their copy
 constexpr int XI_A_HALF = XI_ROWS * 128;                     // 128 k of 128 rows
 constexpr int XI_A_PART = 2 * XI_A_HALF;                     // one scale part of a super-block: 32 KB
 constexpr int XI_AM_BYTES = XI_ROWS * 16;                    // the mins bytes: first K chunk of a K = 32 tile
 constexpr int XI_A_BYTES = 2 * XI_A_PART + XI_AM_BYTES;      // 67584
 constexpr int XI_A_STAGES = 2;
-constexpr int XI_BQ_HALF = XI_TOK * 128;
-constexpr int XI_BM_BYTES = XI_TOK * 16;                     // lo (and scale) records / hi records of 32 positions
-constexpr int XI_B_BYTES = 2 * XI_BQ_HALF + 2 * XI_BM_BYTES; // 9216
-constexpr int XI_B_STAGES = 3;
-constexpr int XI_ACC_BUFS = 4, XI_ACC_COLS = 4 * XI_TOK;     // D_lo, D_hi, M_lo, M_hi
-constexpr int XI_ZERO_BYTES = XI_AM_BYTES + XI_BM_BYTES;     // second K chunks of the mins tiles
+constexpr int XI_RAW_STAGES = 3;
 constexpr int XI_BAR_BYTES = 512;
-constexpr int XI_SMEM = 1024 + XI_A_STAGES * XI_A_BYTES + XI_B_STAGES * XI_B_BYTES + XI_RAW_STAGES * XI_RAW_BYTES + XI_ZERO_BYTES + XI_BAR_BYTES;
 constexpr int XI_EPI_WARPS = 8, XI_EXP_WARPS = 8;
 constexpr int XI_WARP_EXP0 = XI_EPI_WARPS, XI_WARP_TMA_W = XI_WARP_EXP0 + XI_EXP_WARPS, XI_WARP_TMA_B = XI_WARP_TMA_W + 1,
               XI_WARP_MMA = XI_WARP_TMA_B + 1;
 constexpr int XI_THREADS = (XI_WARP_MMA + 1) * 32;           // 608
 constexpr int XI_MAX_E = 64;
-static_assert(XI_A_BYTES % 1024 == 0 && XI_B_BYTES % 1024 == 0 && XI_RAW_BYTES % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
-static_assert(XI_SMEM <= 232448, "shared memory");
+
+// Sizes that follow from the token tile: TOK = 32 tokens per pass (decode-sized batches: four accumulator buffers, three
+// token stages) or 64 (prefill-sized batches: half the passes over an expert's weights; two buffers, two stages).
+template <int TOK>
+struct XiCfg {
+    static constexpr int BQ_HALF = TOK * 128;                // the tokens' integers of 128 k
+    static constexpr int BM_BYTES = TOK * 16;                // lo (and scale) records / hi records of TOK positions
+    static constexpr int B_BYTES = 2 * BQ_HALF + 2 * BM_BYTES;
+    static constexpr int B_STAGES = TOK == 32 ? 3 : 2;
+    static constexpr int ACC_COLS = 4 * TOK;                 // D_lo, D_hi, M_lo, M_hi
+    static constexpr int ACC_BUFS = 512 / ACC_COLS;
+    static constexpr int ZERO_BYTES = XI_AM_BYTES + BM_BYTES; // second K chunks of the mins tiles
+    static constexpr int SMEM = 1024 + XI_A_STAGES * XI_A_BYTES + B_STAGES * B_BYTES + XI_RAW_STAGES * XI_RAW_BYTES + ZERO_BYTES + XI_BAR_BYTES;
+    // kind::i8: D s32, A and B signed 8-bit, both K-major, M = 128, N = TOK
+    static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TOK >> 3) << 17) | ((uint32_t)(XI_ROWS >> 4) << 24);
+    static_assert(B_BYTES % 1024 == 0 && SMEM <= 232448 - 512, "stage alignment and shared memory");
+};
+static_assert(XI_A_BYTES % 1024 == 0 && XI_RAW_BYTES % 1024 == 0, "stages keep the 1024-byte alignment of swizzled tiles");
 
 struct XiArgs {
     const uint8_t *w[2];         // stacked experts (tile layout), gate and up or down alone
@@ -71,7 +80,7 @@ struct XiPiece { int e, wsel, n0, off, mb, m_here, sb0, sb1, kp; };
 // The CTA's items [it, it_end) in expert-major order; every role walks them with its own copy.
 struct XiSched {
     unsigned it, it_end;
-    int mb, tiles, nw, kparts, nsb;
+    int mb, tiles, nw, kparts, nsb, tok;
     const int *act_e, *counts, *offsets;
     __device__ bool next(XiPiece &p) {
         for (;;) {
@@ -88,10 +97,10 @@ struct XiSched {
             p.kp = (int)(r2 % (unsigned)kparts);
             p.off = __ldg(offsets + e);
             p.mb = mb;
-            p.m_here = count - mb < XI_TOK ? count - mb : XI_TOK;
+            p.m_here = count - mb < tok ? count - mb : tok;
             p.sb0 = (int)((long long)nsb * p.kp / kparts);
             p.sb1 = (int)((long long)nsb * (p.kp + 1) / kparts);
-            mb += XI_TOK;
+            mb += tok;
             return true;
         }
     }
@@ -102,8 +111,6 @@ __device__ __forceinline__ void umma_i8_ss(uint32_t tmem_d, uint64_t adesc, uint
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// kind::i8: D s32, A and B signed 8-bit, both K-major, M = 128, N = 32.
-constexpr uint32_t XI_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(XI_TOK >> 3) << 17) | ((uint32_t)(XI_ROWS >> 4) << 24);
 
 // K-major operand without a swizzle: core matrices of 8 rows x 16 bytes (128 contiguous bytes); `lbo` = distance between
 // the core matrices of consecutive K chunks, `sbo` = distance between consecutive 8-row groups.
@@ -125,17 +132,19 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *t
                  ::"r"(smem_u32(smem_dst)), "l"((uint64_t)tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 
+template <int TOK>
 __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_constant__ CUtensorMap tmap_w0,
                                                                    const __grid_constant__ CUtensorMap tmap_w1,
                                                                    const __grid_constant__ CUtensorMap tmap_q,
                                                                    const __grid_constant__ CUtensorMap tmap_m, const XiArgs a) {
+    using C = XiCfg<TOK>;
     extern __shared__ unsigned char xi_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(((uintptr_t)xi_smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *smem_a = smem;
     unsigned char *smem_b = smem_a + XI_A_STAGES * XI_A_BYTES;
-    unsigned char *smem_raw = smem_b + XI_B_STAGES * XI_B_BYTES;
+    unsigned char *smem_raw = smem_b + C::B_STAGES * C::B_BYTES;
     unsigned char *zero_a = smem_raw + XI_RAW_STAGES * XI_RAW_BYTES, *zero_b = zero_a + XI_AM_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(zero_a + XI_ZERO_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(zero_a + C::ZERO_BYTES);
     uint64_t *raw_full = bars, *raw_empty = bars + 4, *a_full = bars + 8, *a_empty = bars + 12, *b_full = bars + 16, *b_empty = bars + 20;
     uint64_t *acc_full = bars + 24, *acc_empty = bars + 28;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 32);
@@ -160,7 +169,7 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < XI_ZERO_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4 *>(zero_a)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = threadIdx.x; i < C::ZERO_BYTES / 16; i += blockDim.x) reinterpret_cast<uint4 *>(zero_a)[i] = make_uint4(0u, 0u, 0u, 0u);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (warp == XI_WARP_TMA_W && lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&tmap_w0) : "memory");
@@ -183,8 +192,8 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
         for (int e = 0; e < a.E; e++) {
             const int cnt = __ldg(a.counts + e);
             if (cnt <= 0) continue;
-            const unsigned full = (unsigned)(cnt / XI_TOK), rest = (unsigned)(cnt % XI_TOK);
-            ecost[n] = full * (3u + XI_TOK / 8) + (rest ? 3u + ((rest + 7u) >> 3) : 0u);
+            const unsigned full = (unsigned)(cnt / TOK), rest = (unsigned)(cnt % TOK);
+            ecost[n] = full * (3u + TOK / 8) + (rest ? 3u + ((rest + 7u) >> 3) : 0u);
             total += (unsigned long long)ecost[n] * per_e;
             act_e[n++] = e;
         }
@@ -209,7 +218,7 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
     const uint32_t tmem_base = *tmem_slot;
 
     XiSched sched;
-    sched.it = share[0]; sched.it_end = share[1]; sched.mb = 0; sched.tiles = tiles; sched.nw = a.nw; sched.kparts = a.kparts; sched.nsb = nsb;
+    sched.it = share[0]; sched.it_end = share[1]; sched.mb = 0; sched.tiles = tiles; sched.nw = a.nw; sched.kparts = a.kparts; sched.nsb = nsb; sched.tok = TOK;
     sched.act_e = act_e; sched.counts = a.counts; sched.offsets = a.offsets;
     XiPiece pc;
     uint32_t step = 0;                                       // super-block steps done by this CTA: every role counts the same
@@ -226,29 +235,32 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
             // f16 d and dmin of this row's block: first word of the header piece of its tile
             const uint8_t *hdr = a.w[pc.wsel] + (size_t)pc.e * a.expert_bytes + (size_t)(lrow >> 3) * nsb * XI_UNIT_BYTES + 8 * 128 + (lrow & 7) * 16;
             const int ntg = (pc.m_here + 7) >> 3;
-            float yacc[2][8];
+            constexpr int NH = TOK / 16;                 // token groups of eight per epilogue thread
+            float yacc[NH][8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) yacc[0][i] = yacc[1][i] = 0.0f;
+            for (int h = 0; h < NH; h++)
+#pragma unroll
+                for (int i = 0; i < 8; i++) yacc[h][i] = 0.0f;
             uint32_t dn = __ldg(reinterpret_cast<const uint32_t *>(hdr + (size_t)pc.sb0 * XI_UNIT_BYTES));
             for (int sb = pc.sb0; sb < pc.sb1; sb++, step++) {
                 const uint32_t dd = dn;
                 if (sb + 1 < pc.sb1) dn = __ldg(reinterpret_cast<const uint32_t *>(hdr + (size_t)(sb + 1) * XI_UNIT_BYTES));
-                const int ab = (int)(step % XI_ACC_BUFS), bs = (int)(step % XI_B_STAGES), as = (int)(step % XI_A_STAGES);
-                if (!mbar_wait_warp(&acc_full[ab], (step / XI_ACC_BUFS) & 1u, abort_flag, a.status, 0x100000u)) { ok = false; break; }
+                const int ab = (int)(step % C::ACC_BUFS), bs = (int)(step % C::B_STAGES), as = (int)(step % XI_A_STAGES);
+                if (!mbar_wait_warp(&acc_full[ab], (step / C::ACC_BUFS) & 1u, abort_flag, a.status, 0x100000u)) { ok = false; break; }
                 tc_fence_after();
                 if (warp == 0 && lane == 0) mbar_arrive(&a_empty[as]);      // the step's MMAs are done: its weight tiles are free
                 const float d = f16_bits_to_f32(dd), dmin = f16_bits_to_f32(dd >> 16);
-                const unsigned char *recs = smem_b + bs * XI_B_BYTES + 2 * XI_BQ_HALF;     // [token][lo bytes | scale | 0]
-                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * XI_ACC_COLS);
+                const unsigned char *recs = smem_b + bs * C::B_BYTES + 2 * C::BQ_HALF;     // [token][lo bytes | scale | 0]
+                const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(ab * C::ACC_COLS);
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
+                for (int h = 0; h < NH; h++) {
                     const int tg = th + 2 * h;
                     if (tg < ntg) {
                         int dlo[8], dhi[8], mlo[8], mhi[8];
-                        tmem_ld8(taddr + 0 * XI_TOK + tg * 8, dlo);
-                        tmem_ld8(taddr + 1 * XI_TOK + tg * 8, dhi);
-                        tmem_ld8(taddr + 2 * XI_TOK + tg * 8, mlo);
-                        tmem_ld8(taddr + 3 * XI_TOK + tg * 8, mhi);
+                        tmem_ld8(taddr + 0 * TOK + tg * 8, dlo);
+                        tmem_ld8(taddr + 1 * TOK + tg * 8, dhi);
+                        tmem_ld8(taddr + 2 * TOK + tg * 8, mlo);
+                        tmem_ld8(taddr + 3 * TOK + tg * 8, mhi);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                         for (int t = 0; t < 8; t++) {
@@ -268,7 +280,7 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
             if (!ok) break;
             float *yout = a.y[pc.wsel] + (size_t)pc.kp * a.part_stride + (size_t)(pc.off + pc.mb) * a.N + n;
 #pragma unroll
-            for (int h = 0; h < 2; h++)
+            for (int h = 0; h < NH; h++)
 #pragma unroll
                 for (int t = 0; t < 8; t++) {
                     const int tok = (th + 2 * h) * 8 + t;
@@ -366,14 +378,14 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
             bool ok = true;
             while (ok && sched.next(pc)) {
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, step++) {
-                    const int bs = (int)(step % XI_B_STAGES);
-                    if (!mbar_wait_spin(&b_empty[bs], ((step / XI_B_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x2000000u)) { ok = false; break; }
-                    unsigned char *dst = smem_b + bs * XI_B_BYTES;
-                    mbar_arrive_expect_tx(&b_full[bs], (uint32_t)XI_B_BYTES);
+                    const int bs = (int)(step % C::B_STAGES);
+                    if (!mbar_wait_spin(&b_empty[bs], ((step / C::B_STAGES) & 1u) ^ 1u, abort_flag, a.status, 0x2000000u)) { ok = false; break; }
+                    unsigned char *dst = smem_b + bs * C::B_BYTES;
+                    mbar_arrive_expect_tx(&b_full[bs], (uint32_t)C::B_BYTES);
                     tma_load_2d(dst, &tmap_q, sb * 256, pc.off + pc.mb, &b_full[bs]);
-                    tma_load_2d(dst + XI_BQ_HALF, &tmap_q, sb * 256 + 128, pc.off + pc.mb, &b_full[bs]);
-                    tma_load_3d(dst + 2 * XI_BQ_HALF, &tmap_m, 0, pc.off + pc.mb, sb, &b_full[bs]);
-                    tma_load_3d(dst + 2 * XI_BQ_HALF + XI_BM_BYTES, &tmap_m, 0, pc.off + pc.mb, nsb + sb, &b_full[bs]);
+                    tma_load_2d(dst + C::BQ_HALF, &tmap_q, sb * 256 + 128, pc.off + pc.mb, &b_full[bs]);
+                    tma_load_3d(dst + 2 * C::BQ_HALF, &tmap_m, 0, pc.off + pc.mb, sb, &b_full[bs]);
+                    tma_load_3d(dst + 2 * C::BQ_HALF + C::BM_BYTES, &tmap_m, 0, pc.off + pc.mb, nsb + sb, &b_full[bs]);
                 }
             }
         }
@@ -386,28 +398,28 @@ __global__ void __launch_bounds__(XI_THREADS, 1) experts_i8_kernel(const __grid_
             const uint32_t a0 = smem_u32(smem_a), b0 = smem_u32(smem_b);
             const uint64_t ad0 = umma_desc(a0), bd0 = umma_desc(b0);
             const uint64_t am0 = umma_desc_plain(a0 + 2 * XI_A_PART, smem_u32(zero_a) - (a0 + 2 * XI_A_PART), 128u);
-            const uint64_t bm0 = umma_desc_plain(b0 + 2 * XI_BQ_HALF, smem_u32(zero_b) - (b0 + 2 * XI_BQ_HALF), 128u);
-            constexpr uint64_t A_STEP = XI_A_BYTES >> 4, B_STEP = XI_B_BYTES >> 4, BM_STEP = XI_BM_BYTES >> 4;
+            const uint64_t bm0 = umma_desc_plain(b0 + 2 * C::BQ_HALF, smem_u32(zero_b) - (b0 + 2 * C::BQ_HALF), 128u);
+            constexpr uint64_t A_STEP = XI_A_BYTES >> 4, B_STEP = C::B_BYTES >> 4, BM_STEP = C::BM_BYTES >> 4;
             bool ok = true;
             while (ok && sched.next(pc)) {
                 for (int sb = pc.sb0; sb < pc.sb1; sb++, step++) {
-                    const int ab = (int)(step % XI_ACC_BUFS), as = (int)(step % XI_A_STAGES), bs = (int)(step % XI_B_STAGES);
-                    if (!mbar_wait_spin(&acc_empty[ab], ((step / XI_ACC_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000000u)) { ok = false; break; }
+                    const int ab = (int)(step % C::ACC_BUFS), as = (int)(step % XI_A_STAGES), bs = (int)(step % C::B_STAGES);
+                    if (!mbar_wait_spin(&acc_empty[ab], ((step / C::ACC_BUFS) & 1u) ^ 1u, abort_flag, a.status, 0x4000000u)) { ok = false; break; }
                     if (!mbar_wait_spin(&a_full[as], (step / XI_A_STAGES) & 1u, abort_flag, a.status, 0x8000000u)) { ok = false; break; }
-                    if (!mbar_wait_spin(&b_full[bs], (step / XI_B_STAGES) & 1u, abort_flag, a.status, 0x10000000u)) { ok = false; break; }
+                    if (!mbar_wait_spin(&b_full[bs], (step / C::B_STAGES) & 1u, abort_flag, a.status, 0x10000000u)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t acc = tmem_base + (uint32_t)(ab * XI_ACC_COLS);
+                    const uint32_t acc = tmem_base + (uint32_t)(ab * C::ACC_COLS);
                     const uint64_t ad_lo = ad0 + (uint64_t)as * A_STEP, ad_hi = ad_lo + (XI_A_PART >> 4), bd = bd0 + (uint64_t)bs * B_STEP;
                     const uint64_t am = am0 + (uint64_t)as * A_STEP - (((uint64_t)as * A_STEP) << 16);
                     const uint64_t bm_lo = bm0 + (uint64_t)bs * B_STEP - (((uint64_t)bs * B_STEP) << 16), bm_hi = bm_lo + BM_STEP - (BM_STEP << 16);
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
-                        const uint64_t koff = (uint64_t)((j >> 2) * (XI_A_HALF >> 4) + (j & 3) * 2), boff = (uint64_t)((j >> 2) * (XI_BQ_HALF >> 4) + (j & 3) * 2);
-                        umma_i8_ss(acc, ad_lo + koff, bd + boff, XI_IDESC, j > 0 ? 1u : 0u);
-                        umma_i8_ss(acc + XI_TOK, ad_hi + koff, bd + boff, XI_IDESC, j > 0 ? 1u : 0u);
+                        const uint64_t koff = (uint64_t)((j >> 2) * (XI_A_HALF >> 4) + (j & 3) * 2), boff = (uint64_t)((j >> 2) * (C::BQ_HALF >> 4) + (j & 3) * 2);
+                        umma_i8_ss(acc, ad_lo + koff, bd + boff, C::IDESC, j > 0 ? 1u : 0u);
+                        umma_i8_ss(acc + TOK, ad_hi + koff, bd + boff, C::IDESC, j > 0 ? 1u : 0u);
                     }
-                    umma_i8_ss(acc + 2 * XI_TOK, am, bm_lo, XI_IDESC, 0u);
-                    umma_i8_ss(acc + 3 * XI_TOK, am, bm_hi, XI_IDESC, 0u);
+                    umma_i8_ss(acc + 2 * TOK, am, bm_lo, C::IDESC, 0u);
+                    umma_i8_ss(acc + 3 * TOK, am, bm_hi, C::IDESC, 0u);
                     umma_commit(&acc_full[ab]);
                 }
             }
@@ -469,9 +481,10 @@ int ojas_experts_i8_pack(ojas_b200_ctx *ctx, const int8_t *q, const float *scale
 // gate and up (w1 != null) or down (w1 == null) of every expert over the positions' Q8_K integers q [positions][K]
 // (expert order) and their records.  Returns 1 if the shape is not one this kernel takes, < 0 on an error.
 int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const void *meta,
-                    size_t positions, const int *counts, const int *offsets, size_t E, size_t K, size_t N, int kparts, size_t part_stride) {
+                    size_t positions, const int *counts, const int *offsets, size_t E, size_t K, size_t N, int kparts, size_t part_stride, int tok) {
     if (N % OJAS_TILE_ROWS != 0 || E > (size_t)XI_MAX_E || K % 256 != 0 || positions == 0) return 1;
     if (((uintptr_t)q & 15) || ((uintptr_t)meta & 15) || ((uintptr_t)w0 & 127) || ((uintptr_t)w1 & 127)) return 1;
+    if (tok != 32 && tok != 64) return 1;
     EncodeTiledFn encode = encode_tiled_fn();
     if (!encode) return 1;
     const size_t nsb = K / 256, units = E * (N / OJAS_TILE_ROWS);
@@ -491,7 +504,7 @@ int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, fl
     {
         const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)positions};
         const cuuint64_t strides[1] = {(cuuint64_t)K};
-        const cuuint32_t box[2] = {128, (cuuint32_t)XI_TOK};
+        const cuuint32_t box[2] = {128, (cuuint32_t)tok};
         CUresult cr = encode(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)q, dims, strides, box, estr4, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "experts_i8: cuTensorMapEncodeTiled (activations) failed (%d)", (int)cr);
@@ -499,7 +512,7 @@ int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, fl
     {   // the records: [2 planes x nsb][positions][16 bytes]; a box = 32 positions of one (plane, super-block)
         const cuuint64_t dims[3] = {16, (cuuint64_t)positions, (cuuint64_t)(2 * nsb)};
         const cuuint64_t strides[2] = {16, (cuuint64_t)positions * 16};
-        const cuuint32_t box[3] = {16, (cuuint32_t)XI_TOK, 1};
+        const cuuint32_t box[3] = {16, (cuuint32_t)tok, 1};
         CUresult cr = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)meta, dims, strides, box, estr4, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return ojas_fail(ctx, OJAS_B200_E_CUDA, "experts_i8: cuTensorMapEncodeTiled (records) failed (%d)", (int)cr);
@@ -510,20 +523,25 @@ int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, fl
     a.expert_bytes = (N / OJAS_TILE_ROWS) * nsb * (size_t)XI_UNIT_BYTES;
     a.counts = counts; a.offsets = offsets; a.status = ctx->dev_status;
     a.E = (int)E; a.K = (int)K; a.N = (int)N; a.nsb = (int)nsb;
-    cudaError_t e = cudaFuncSetAttribute(experts_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, XI_SMEM);
-    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "experts_i8: shared memory %d: %s", XI_SMEM, cudaGetErrorString(e));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ctx->sm_count);
-    cfg.blockDim = dim3(XI_THREADS);
-    cfg.dynamicSmemBytes = XI_SMEM;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = ctx->pdl ? 1 : 0;
-    e = cudaLaunchKernelEx(&cfg, experts_i8_kernel, tw[0], tw[1], tq, tm, a);
-    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch experts_i8: %s", cudaGetErrorString(e));
+    auto go = [&](auto kernel, int smem) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "experts_i8: shared memory %d: %s", smem, cudaGetErrorString(e));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)ctx->sm_count);
+        cfg.blockDim = dim3(XI_THREADS);
+        cfg.dynamicSmemBytes = (size_t)smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ctx->pdl ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, kernel, tw[0], tw[1], tq, tm, a);
+        if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch experts_i8: %s", cudaGetErrorString(e));
+        return 0;
+    };
+    const int rc = tok == 64 ? go(experts_i8_kernel<64>, XiCfg<64>::SMEM) : go(experts_i8_kernel<32>, XiCfg<32>::SMEM);
+    if (rc) return rc;
     ojas_count_launch(ctx, "experts_i8");
     return 0;
 }

@@ -258,7 +258,8 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     if (i8_fits && (prefill || (ctx->moe_i8 && type_d == OJAS_B200_Q4_K))) {
         rc = ojas_experts_i8_pack(ctx, w.xq, w.xs, w.xb, w.tok, A, d, w.qg, w.meta_gu);
         if (rc) return rc;
-        rc = ojas_experts_i8(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.qg, w.meta_gu, A, w.counts, w.offsets, E, d, ffn, 1, 0);
+        rc = ojas_experts_i8(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.qg, w.meta_gu, A, w.counts, w.offsets, E, d, ffn, 1, 0,
+                             prefill ? 64 : 32);          // prefill-sized groups: 64 tokens per pass over an expert's weights
         if (rc < 0) return rc;
         gu_i8 = rc == 0;
     }
@@ -310,7 +311,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
             if (parts > ffn / 1024) parts = ffn / 1024 ? ffn / 1024 : 1;
         }
         float *ydst = A <= MOE_I8_SPLIT_ROWS ? w.ydp : w.yd;
-        rc = ojas_experts_i8(ctx, (const uint8_t *)wd, nullptr, ydst, nullptr, w.aq, w.meta_d, A, w.counts, w.offsets, E, ffn, d, (int)parts, A * d);
+        rc = ojas_experts_i8(ctx, (const uint8_t *)wd, nullptr, ydst, nullptr, w.aq, w.meta_d, A, w.counts, w.offsets, E, ffn, d, (int)parts, A * d, 32);
         if (rc) return rc < 0 ? rc : ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "moe_ffn: the down projection does not fit the int8 kernel");
         moe_combine_kernel<<<grid, 256, 0, ctx->stream>>>(ydst, w.pos, wgt, out, (int)KSEL, (int)d, accum ? 1 : 0, (int)parts, A * d);
         OJAS_LAUNCH_CHECK(ctx, "moe_combine");
