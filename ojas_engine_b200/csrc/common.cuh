@@ -74,6 +74,10 @@ void ojas_count_launch(ojas_b200_ctx *ctx, const char *name);
 //   pieces 0..7 : qs[16p .. 16p+15] in GGUF order: low nibbles = weights 64(p/2) + 16(p%2) + i, high nibbles the
 //                 same + 32 (crates/ojas-formats/src/gguf.rs:1049-1056)
 //   piece  8    : the block's first 16 bytes as they are: d, dmin, sc[12]
+// Q5_K  (GGUF: 176 B per 256: f16 d, f16 dmin, u8 sc[12], u8 qh[32], u8 qs[128])      tile = 1408 B
+//   pieces 0..8 : as Q4_K (qs, then the first 16 bytes of the block)
+//   pieces 9, 10: qh[0..15], qh[16..31]: bit j of qh[l] is the fifth bit of weight l of sub-block j
+//                 (crates/ojas-formats/src/gguf.rs:1060-1085)
 // Q6_K  (GGUF: 210 B per 256: u8 ql[128], u8 qh[64], i8 sc[16], f16 d)                 tile = 1680 B
 //   pieces 0..7 : low nibbles, piece h*4 + c, byte i: low nibble = weight 64c + 16h + i, high nibble = weight
 //                 64c + 32 + 16h + i   (c = 64-weight chunk, h = 0, 1)
@@ -85,7 +89,7 @@ void ojas_count_launch(ojas_b200_ctx *ctx, const char *name);
 //   piece  16   : the eight f16 block scales
 constexpr int OJAS_TILE_ROWS = 8;
 __host__ __device__ constexpr int tile_bytes(uint32_t type) {
-    return type == OJAS_B200_Q4_K ? 1152 : type == OJAS_B200_Q6_K ? 1680 : 2176;
+    return type == OJAS_B200_Q4_K ? 1152 : type == OJAS_B200_Q5_K ? 1408 : type == OJAS_B200_Q6_K ? 1680 : 2176;
 }
 // Bytes of the leading pieces that hold quants only (what the GEMM stages per tile; scales come after them).
 __host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
@@ -93,7 +97,7 @@ __host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
 }
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
-static inline bool type_supported(uint32_t type) { return type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K || type == OJAS_B200_Q8_0; }
+static inline bool type_supported(uint32_t type) { return type == OJAS_B200_Q4_K || type == OJAS_B200_Q5_K || type == OJAS_B200_Q6_K || type == OJAS_B200_Q8_0; }
 static inline size_t tile_units(size_t N) { return (N + OJAS_TILE_ROWS - 1) / OJAS_TILE_ROWS; }
 static inline size_t repacked_size(uint32_t type, size_t N, size_t K) { return align256(tile_units(N) * (K / 256) * (size_t)tile_bytes(type)); }
 

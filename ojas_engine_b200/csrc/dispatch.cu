@@ -14,6 +14,7 @@ struct NameEntry {
 
 static uint32_t tag_type(const char *tag) {
     if (!strcmp(tag, "q4k")) return OJAS_B200_Q4_K;
+    if (!strcmp(tag, "q5k")) return OJAS_B200_Q5_K;
     if (!strcmp(tag, "q6k")) return OJAS_B200_Q6_K;
     return OJAS_B200_Q8_0;
 }
@@ -46,6 +47,7 @@ static uint32_t tag_type(const char *tag) {
     }
 
 GEMV_ENTRIES(q4k)
+GEMV_ENTRIES(q5k)
 GEMV_ENTRIES(q6k)
 GEMV_ENTRIES(q80)
 
@@ -155,7 +157,7 @@ static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, c
     {"moe_gu_" #tag "_slots", 6, 2, moe_gu_##tag##_slots}, {"moe_down_" #tag "_slots", 5, 3, moe_down_##tag##_slots}
 
 static const NameEntry kTable[] = {
-    GEMV_TABLE(q4k), GEMV_TABLE(q6k), GEMV_TABLE(q80),
+    GEMV_TABLE(q4k), GEMV_TABLE(q5k), GEMV_TABLE(q6k), GEMV_TABLE(q80),
     {"quant_q8k", 4, 2, d_quant_q8k},
     {"moe_topk", 3, 2, d_moe_topk}, {"moe_topk_m", 3, 3, d_moe_topk_m},
     {"gemm_mm_q4k", 3, 4, gemm_q4k}, {"gemm_mm_q6k", 3, 4, gemm_q6k}, {"gemm_mm_q8_0", 3, 4, gemm_q8_0}, {"gemm_mm_q4l", 5, 4, gemm_q4l},

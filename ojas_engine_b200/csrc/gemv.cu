@@ -123,7 +123,7 @@ __device__ __forceinline__ void gv_bar_wait(uint64_t *bar, unsigned parity, unsi
 // lo = s & 63 (0..63) and hi = s >> 6 (a signed byte), s = lo + 64 * hi.  Q4_K: eight sums per 32 values -> 16 bytes
 // (lo[8], hi[8]); Q6_K: sixteen sums per 16 values -> 32 bytes (lo[16], hi[16]).  Then the f32 scales.
 template <int TYPE> struct ActLayout {
-    static constexpr int BS_BYTES = TYPE == OJAS_B200_Q4_K ? 16 : 32;
+    static constexpr int BS_BYTES = TYPE == OJAS_B200_Q6_K ? 32 : 16;       // (Q5_K shares Q4_K's sub-blocks of 32)
     // bytes of one activation row, a multiple of 16 so that every row's values stay 16-byte aligned
     __host__ __device__ static size_t row_bytes(int nsb) { return ((size_t)nsb * (256 + BS_BYTES + 4) + 15) & ~(size_t)15; }
 };
@@ -191,7 +191,7 @@ __device__ __forceinline__ void stage_quant_vals(const Q8kLane &ql, int sb, int 
     reinterpret_cast<uint2 *>(xq + sb * 256)[lane] = ql.packed;
     int s = ql.sum8;
     s += __shfl_xor_sync(0xffffffffu, s, 1);                       // sum of 16 values (lanes 2j, 2j+1)
-    if (TYPE == OJAS_B200_Q4_K) {
+    if (TYPE != OJAS_B200_Q6_K) {
         s += __shfl_xor_sync(0xffffffffu, s, 2);                   // sum of 32 values (lanes 4j .. 4j+3)
         if ((lane & 3) == 0) {
             bs[sb * 16 + (lane >> 2)] = (uint8_t)(s & 63);
@@ -263,7 +263,7 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
                 }
             }
             for (int sb = threadIdx.x; sb < nsb; sb += blockDim.x) sx[sb] = __ldg(a.scales + (size_t)srow * nsb + sb);
-            if (TYPE == OJAS_B200_Q4_K) {
+            if (TYPE != OJAS_B200_Q6_K) {
                 for (int i = threadIdx.x; i < nsb * 8; i += blockDim.x) {
                     const int t = __ldg(a.bsums + (size_t)srow * nsb * 8 + i);
                     bs[(i >> 3) * 16 + (i & 7)] = (uint8_t)(t & 63);
@@ -347,11 +347,18 @@ __device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int n
 
 // Q4_K (dot_q4k, crates/ojas-cpu/src/cpu_math.rs:609-635): eight exact int32 sub-block dots, integer
 // sum_j s_j * idot_j and sum_j m_j * bsum_j, then sx * (d * isum - dmin * msum).
-template <int MT, bool DUMP>
+// FIVE: Q5_K (dot_q5k, :637-671): the same with a fifth bit per weight, bit j of qh[l] for weight l of sub-block j.
+template <int MT, bool DUMP, bool FIVE = false>
 __device__ __forceinline__ void step_q4k(const uint8_t *wl, const uint8_t *act, int nsb, int sb, float (&acc)[MT], int32_t *dump) {
     using L = ActLayout<OJAS_B200_Q4_K>;
     const size_t rb = L::row_bytes(nsb);
     const uint4 H = *reinterpret_cast<const uint4 *>(wl + 8 * 128);
+    uint32_t qh[2][4] = {{0u, 0u, 0u, 0u}, {0u, 0u, 0u, 0u}};
+    if (FIVE) {
+        const uint4 Q0 = *reinterpret_cast<const uint4 *>(wl + 9 * 128), Q1 = *reinterpret_cast<const uint4 *>(wl + 10 * 128);
+        qh[0][0] = Q0.x; qh[0][1] = Q0.y; qh[0][2] = Q0.z; qh[0][3] = Q0.w;
+        qh[1][0] = Q1.x; qh[1][1] = Q1.y; qh[1][2] = Q1.z; qh[1][3] = Q1.w;
+    }
     // the sixteen 6-bit scales / mins as bytes (get_scale_min_k4, crates/ojas-formats/src/gguf.rs:1132-1140)
     const uint32_t s_lo = H.y & 0x3f3f3f3fu, m_lo = H.z & 0x3f3f3f3fu;
     const uint32_t s_hi = (H.w & 0x0f0f0f0fu) | ((H.y >> 2) & 0x30303030u);
@@ -367,8 +374,15 @@ __device__ __forceinline__ void step_q4k(const uint8_t *wl, const uint8_t *act, 
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const uint4 W = *reinterpret_cast<const uint4 *>(wl + (2 * c + h) * 128);
-            const uint32_t lo[4] = {W.x & 0x0f0f0f0fu, W.y & 0x0f0f0f0fu, W.z & 0x0f0f0f0fu, W.w & 0x0f0f0f0fu};
-            const uint32_t hi[4] = {W.x & 0xf0f0f0f0u, W.y & 0xf0f0f0f0u, W.z & 0xf0f0f0f0u, W.w & 0xf0f0f0f0u};
+            uint32_t lo[4] = {W.x & 0x0f0f0f0fu, W.y & 0x0f0f0f0fu, W.z & 0x0f0f0f0fu, W.w & 0x0f0f0f0fu};
+            uint32_t hi[4] = {W.x & 0xf0f0f0f0u, W.y & 0xf0f0f0f0u, W.z & 0xf0f0f0f0u, W.w & 0xf0f0f0f0u};
+            if (FIVE) {                                   // five-bit values 0..31; the high nibbles come down (no room for x16)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    lo[i] |= ((qh[h][i] >> (2 * c)) & 0x01010101u) << 4;
+                    hi[i] = (hi[i] >> 4) | (((qh[h][i] >> (2 * c + 1)) & 0x01010101u) << 4);
+                }
+            }
 #pragma unroll
             for (int m = 0; m < MT; m++) {
                 const uint4 *xs = reinterpret_cast<const uint4 *>(act + m * rb + sb * 256);
@@ -383,7 +397,7 @@ __device__ __forceinline__ void step_q4k(const uint8_t *wl, const uint8_t *act, 
         const int sA = (int)__byte_perm(sw, 0, 0x4440 + 2 * (c & 1)), sB = (int)__byte_perm(sw, 0, 0x4441 + 2 * (c & 1));
 #pragma unroll
         for (int m = 0; m < MT; m++) {
-            const int b = pB[m] >> 4;                  // the high nibbles were left in place: every product carried x16
+            const int b = FIVE ? pB[m] : pB[m] >> 4;   // (Q4_K: the high nibbles were left in place: every product carried x16)
             if (DUMP && m == 0) { dump[2 * c] = pA[0]; dump[2 * c + 1] = b; }
             isum[m] += sA * pA[m] + sB * b;
         }
@@ -620,6 +634,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         } else if (4 * g + unit < nu) {
             const int row = (ub + 4 * g + unit) * 8 + r;
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
+            else if (TYPE == OJAS_B200_Q5_K) step_q4k<MT, DUMP, true>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q6_K) step_q6k<MT, DUMP>(wl + stg * STEP, r, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 16 : nullptr);
             else step_q80<MT>(wl + stg * STEP, act, a.K, sb, acc);
         }
@@ -738,7 +753,7 @@ struct GemvPlan {
 static size_t gemv_act_bytes(uint32_t type, int MT, size_t K) {
     const size_t nsb = K / 256;
     if (type == OJAS_B200_Q8_0) return (size_t)MT * q80_act_row_bytes(K);
-    return (size_t)MT * (type == OJAS_B200_Q4_K ? ActLayout<OJAS_B200_Q4_K>::row_bytes((int)nsb) : ActLayout<OJAS_B200_Q6_K>::row_bytes((int)nsb));
+    return (size_t)MT * (type == OJAS_B200_Q6_K ? ActLayout<OJAS_B200_Q6_K>::row_bytes((int)nsb) : ActLayout<OJAS_B200_Q4_K>::row_bytes((int)nsb));
 }
 
 static int ilog2(size_t v) { int l = 0; while (((size_t)1 << (l + 1)) <= v) l++; return l; }
@@ -856,10 +871,12 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     }
         if (args.norm_w) {
             if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 1, "gemv_q4k_rmsnorm") }
+            if (type == OJAS_B200_Q5_K) { GEMV_PRO_CASE(OJAS_B200_Q5_K, 1, "gemv_q5k_rmsnorm") }
             if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 1, "gemv_q6k_rmsnorm") }
             GEMV_PRO_CASE(OJAS_B200_Q8_0, 1, "gemv_q80_rmsnorm")
         }
         if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 2, "gemv_q4k_silu_mul") }
+        if (type == OJAS_B200_Q5_K) { GEMV_PRO_CASE(OJAS_B200_Q5_K, 2, "gemv_q5k_silu_mul") }
         if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 2, "gemv_q6k_silu_mul") }
         GEMV_PRO_CASE(OJAS_B200_Q8_0, 2, "gemv_q80_silu_mul")
 #undef GEMV_PRO_CASE
@@ -868,6 +885,11 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
         if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q4_K, 1, false, true, 1>, args, p, "gemv_q4k_idots");
         if (preq) { GEMV_CASE(OJAS_B200_Q4_K, true, "gemv_q4k_q8k") }
         GEMV_CASE(OJAS_B200_Q4_K, false, "gemv_q4k")
+    }
+    if (type == OJAS_B200_Q5_K) {
+        if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q5_K, 1, false, true, 1>, args, p, "gemv_q5k_idots");
+        if (preq) { GEMV_CASE(OJAS_B200_Q5_K, true, "gemv_q5k_q8k") }
+        GEMV_CASE(OJAS_B200_Q5_K, false, "gemv_q5k")
     }
     if (type == OJAS_B200_Q6_K) {
         if (dump) return launch_gemv(ctx, gemv_kernel<OJAS_B200_Q6_K, 1, false, true, 1>, args, p, "gemv_q6k_idots");

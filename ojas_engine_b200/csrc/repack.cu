@@ -15,6 +15,15 @@ __host__ __device__ static inline void repack_q4k_block(const uint8_t *src, uint
     for (int i = 0; i < 16; i++) tile_piece(tile, 8, r)[i] = src[i];
 }
 
+// Q5_K: Q4_K's pieces (the nibbles start 48 bytes into the block), then the 32 bytes of fifth bits as two pieces.
+__host__ __device__ static inline void repack_q5k_block(const uint8_t *src, uint8_t *tile, int r) {
+    for (int p = 0; p < 8; p++)
+        for (int i = 0; i < 16; i++) tile_piece(tile, p, r)[i] = src[48 + p * 16 + i];
+    for (int i = 0; i < 16; i++) tile_piece(tile, 8, r)[i] = src[i];
+    for (int p = 0; p < 2; p++)
+        for (int i = 0; i < 16; i++) tile_piece(tile, 9 + p, r)[i] = src[16 + p * 16 + i];
+}
+
 // Six-bit value of weight w (0..255) of a Q6_K block, as the reference decodes it
 // (crates/ojas-formats/src/gguf.rs:1086-1108): half = w/128, quarter = (w%128)/32, l = w%32.
 __host__ __device__ static inline unsigned q6k_value(const uint8_t *src, int w) {
@@ -57,7 +66,9 @@ __host__ __device__ static inline void repack_q80_block(const uint8_t *src, uint
     }
 }
 
-__host__ __device__ static inline size_t raw_sb_bytes(uint32_t type) { return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q6_K ? 210 : 272; }
+__host__ __device__ static inline size_t raw_sb_bytes(uint32_t type) {
+    return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : 272;
+}
 
 // Block `blk` = (row n, super-block s) in row-major order of the GGUF tensor.
 __host__ __device__ static inline void repack_one(uint32_t type, const uint8_t *raw, size_t blk, size_t nsb, uint8_t *out) {
@@ -66,6 +77,7 @@ __host__ __device__ static inline void repack_one(uint32_t type, const uint8_t *
     uint8_t *tile = out + ((n / OJAS_TILE_ROWS) * nsb + s) * (size_t)tile_bytes(type);
     const int r = (int)(n % OJAS_TILE_ROWS);
     if (type == OJAS_B200_Q4_K) repack_q4k_block(src, tile, r);
+    else if (type == OJAS_B200_Q5_K) repack_q5k_block(src, tile, r);
     else if (type == OJAS_B200_Q6_K) repack_q6k_block(src, tile, r);
     else repack_q80_block(src, tile, r);
 }

@@ -13,7 +13,7 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-Q8_0, Q4_K, Q6_K = 8, 12, 14
+Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
 
 
 def _cpu_tag() -> str:
@@ -60,6 +60,7 @@ def _load(native: bool = False) -> C.CDLL:
         "orc_digest_f16": (C.c_uint64, [u16p, C.c_size_t]),
         "orc_quant_q8k": (None, [f32p, C.c_size_t, f32p, i8p, i32p]),
         "orc_dot_q4k": (C.c_float, [u8p, C.c_size_t, f32p, i8p, i32p, i32p]),
+        "orc_dot_q5k": (C.c_float, [u8p, C.c_size_t, f32p, i8p, i32p, i32p]),
         "orc_dot_q6k": (C.c_float, [u8p, C.c_size_t, f32p, i8p, i32p]),
         "orc_dot_q80": (C.c_float, [u8p, f32p, C.c_size_t]),
         "orc_row_bytes": (C.c_size_t, [C.c_uint32, C.c_size_t]),
@@ -97,7 +98,7 @@ def _u8(a) -> np.ndarray:
 
 
 def block_shape(t: int) -> tuple[int, int]:
-    return {Q8_0: (34, 32), Q4_K: (144, 256), Q6_K: (210, 256)}[t]
+    return {Q8_0: (34, 32), Q4_K: (144, 256), Q5_K: (176, 256), Q6_K: (210, 256)}[t]
 
 
 def row_bytes(t: int, k: int) -> int:
@@ -148,6 +149,16 @@ def dot_q4k(row, act, want_idots: bool = False):
     nsb = scales.size
     idots = np.empty(nsb * 8, np.int32) if want_idots else None
     v = lib().orc_dot_q4k(_p(row, C.c_uint8), nsb, _p(scales, C.c_float), _p(q, C.c_int8), _p(bsums, C.c_int32),
+                          _p(idots, C.c_int32) if want_idots else None)
+    return (float(v), idots) if want_idots else float(v)
+
+
+def dot_q5k(row, act, want_idots: bool = False):
+    row = _u8(row)
+    scales, q, bsums = act
+    nsb = scales.size
+    idots = np.empty(nsb * 8, np.int32) if want_idots else None
+    v = lib().orc_dot_q5k(_p(row, C.c_uint8), nsb, _p(scales, C.c_float), _p(q, C.c_int8), _p(bsums, C.c_int32),
                           _p(idots, C.c_int32) if want_idots else None)
     return (float(v), idots) if want_idots else float(v)
 

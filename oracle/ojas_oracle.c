@@ -91,11 +91,12 @@ static inline float rdh(const uint8_t *b, size_t i) {
 }
 
 /* ---------------------------------------------------------------- block shapes
- * crates/ojas-formats/src/synth.rs:12-21 (only the three formats on the path). */
+ * crates/ojas-formats/src/synth.rs:12-21 (the formats on the path: Q8_0, Q4_K, Q5_K, Q6_K). */
 ORC_API int orc_block_shape(uint32_t type, uint32_t *block_bytes, uint32_t *block_weights) {
     switch (type) {
     case 8:  *block_bytes = 34;  *block_weights = 32;  return 0;
     case 12: *block_bytes = 144; *block_weights = 256; return 0;
+    case 13: *block_bytes = 176; *block_weights = 256; return 0;
     case 14: *block_bytes = 210; *block_weights = 256; return 0;
     default: return -1;
     }
@@ -117,7 +118,7 @@ ORC_API int orc_synth_blocks(uint32_t type, size_t nb, uint8_t *out) {
         uint16_t d = orc_f32_to_f16(0.05f + (float)(i % 7) * 0.01f);
         size_t at = (type == 14) ? 208 : 0;
         blk[at] = (uint8_t)(d & 0xff); blk[at + 1] = (uint8_t)(d >> 8);
-        if (type == 12) { blk[2] = (uint8_t)(dmin & 0xff); blk[3] = (uint8_t)(dmin >> 8); }
+        if (type == 12 || type == 13) { blk[2] = (uint8_t)(dmin & 0xff); blk[3] = (uint8_t)(dmin >> 8); }
     }
     return 0;
 }
@@ -160,6 +161,23 @@ ORC_API int orc_dequant_f32(const uint8_t *b, uint32_t type, size_t n, float *ou
                 const uint8_t *q = qs + chunk * 32;
                 for (int l = 0; l < 32; l++) out[o++] = dl1 * (float)(q[l] & 0xF) - ml1;
                 for (int l = 0; l < 32; l++) out[o++] = dl2 * (float)(q[l] >> 4) - ml2;
+            }
+        }
+    } else if (type == 13) {   /* Q5_K, crates/ojas-formats/src/gguf.rs:1060-1085 */
+        for (size_t blk = 0; blk < n / 256; blk++) {
+            const uint8_t *p = b + blk * 176;
+            float d = rdh(p, 0), dmin = rdh(p, 2);
+            const uint8_t *sc = p + 4, *qh = p + 16, *qs = p + 48;
+            uint8_t u1 = 1, u2 = 2;
+            for (int chunk = 0; chunk < 4; chunk++) {
+                float d1, m1, d2, m2;
+                scale_min_k4(chunk * 2, sc, &d1, &m1);
+                scale_min_k4(chunk * 2 + 1, sc, &d2, &m2);
+                float dl1 = d * d1, ml1 = dmin * m1, dl2 = d * d2, ml2 = dmin * m2;
+                const uint8_t *q = qs + chunk * 32;
+                for (int l = 0; l < 32; l++) out[o++] = dl1 * ((float)(q[l] & 0xF) + ((qh[l] & u1) ? 16.0f : 0.0f)) - ml1;
+                for (int l = 0; l < 32; l++) out[o++] = dl2 * ((float)(q[l] >> 4) + ((qh[l] & u2) ? 16.0f : 0.0f)) - ml2;
+                u1 = (uint8_t)(u1 << 2); u2 = (uint8_t)(u2 << 2);
             }
         }
     } else if (type == 14) {
@@ -285,6 +303,43 @@ ORC_API float orc_dot_q4k(const uint8_t *row, size_t nsb, const float *scales, c
     return total;
 }
 
+/* dot_q5k, crates/ojas-cpu/src/cpu_math.rs:637-671: Q4_K's arithmetic on five-bit values (the fifth bit of weight l
+ * of sub-block j is bit j of qh[l]).  idots as for Q4_K. */
+ORC_API float orc_dot_q5k(const uint8_t *row, size_t nsb, const float *scales, const int8_t *q,
+                          const int32_t *bsums, int32_t *idots) {
+    float total = 0.0f;
+    uint8_t lo[32], hi[32];
+    for (size_t sb = 0; sb < nsb; sb++) {
+        const uint8_t *blk = row + sb * 176;
+        float d = rdh(blk, 0), dmin = rdh(blk, 2);
+        const uint8_t *sc = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        float sx = scales[sb];
+        const int8_t *xq = q + sb * 256;
+        const int32_t *bs = bsums + sb * 8;
+        float sumd = 0.0f, summ = 0.0f;
+        uint8_t u1 = 1, u2 = 2;
+        for (int c = 0; c < 4; c++) {
+            const uint8_t *qq = qs + c * 32;
+            for (int l = 0; l < 32; l++) {
+                lo[l] = (uint8_t)((qq[l] & 0xF) | ((qh[l] & u1) ? 16 : 0));
+                hi[l] = (uint8_t)((qq[l] >> 4) | ((qh[l] & u2) ? 16 : 0));
+            }
+            float s1, m1, s2, m2;
+            scale_min_k4(c * 2, sc, &s1, &m1);
+            scale_min_k4(c * 2 + 1, sc, &s2, &m2);
+            int32_t i1 = idot32(lo, xq + c * 64);
+            int32_t i2 = idot32(hi, xq + c * 64 + 32);
+            if (idots) { idots[sb * 8 + c * 2] = i1; idots[sb * 8 + c * 2 + 1] = i2; }
+            sumd += s1 * (float)i1;
+            sumd += s2 * (float)i2;
+            summ += m1 * (float)bs[c * 2] + m2 * (float)bs[c * 2 + 1];
+            u1 = (uint8_t)(u1 << 2); u2 = (uint8_t)(u2 << 2);
+        }
+        total += sx * (d * sumd - dmin * summ);
+    }
+    return total;
+}
+
 /* dot_q6k, crates/ojas-cpu/src/cpu_math.rs:674-722.  idots (optional): 16 int32
  * per super-block, the per-16 dots of the unsigned 0..63 values in weight order. */
 ORC_API float orc_dot_q6k(const uint8_t *row, size_t nsb, const float *scales, const int8_t *q,
@@ -353,6 +408,7 @@ ORC_API float orc_dot_q80(const uint8_t *row, const float *x, size_t k) {
 ORC_API size_t orc_row_bytes(uint32_t type, size_t k) {
     switch (type) {
     case 12: return k / 256 * 144;
+    case 13: return k / 256 * 176;
     case 14: return k / 256 * 210;
     case 8:  return k / 256 * 272;
     default: return 0;
@@ -375,6 +431,7 @@ static void *mv_worker(void *arg) {
             const uint8_t *rb = j->raw + row * j->row_bytes;
             float v;
             if (j->type == 12) v = orc_dot_q4k(rb, j->k / 256, j->scales, j->q, j->bsums, NULL);
+            else if (j->type == 13) v = orc_dot_q5k(rb, j->k / 256, j->scales, j->q, j->bsums, NULL);
             else if (j->type == 8) v = orc_dot_q80(rb, j->x, j->k);
             else v = orc_dot_q6k(rb, j->k / 256, j->scales, j->q, NULL);
             j->out[row] = v;

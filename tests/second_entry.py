@@ -87,6 +87,34 @@ def dot_q4k(row: np.ndarray, act):
     return total, np.array(idots, np.int32)
 
 
+def dot_q5k(row: np.ndarray, act):
+    """cpu_math.rs:637-671: as dot_q4k on five-bit values; bit j of qh[l] is the fifth bit of weight l of sub-block j."""
+    scales, q, bsums = act
+    total = F(0)
+    idots = []
+    for sb in range(scales.size):
+        blk = row[sb * 176:(sb + 1) * 176]
+        d, dmin = _f16(blk, 0), _f16(blk, 2)
+        sc, qh, qs = blk[4:16], blk[16:48], blk[48:176]
+        xq = q[sb * 256:(sb + 1) * 256].astype(np.int64)
+        bs = bsums[sb * 8:(sb + 1) * 8]
+        sumd, summ = F(0), F(0)
+        for c in range(4):
+            qq = qs[c * 32:(c + 1) * 32]
+            lo = (qq & 0xF).astype(np.int64) + 16 * ((qh >> (2 * c)) & 1).astype(np.int64)
+            hi = (qq >> 4).astype(np.int64) + 16 * ((qh >> (2 * c + 1)) & 1).astype(np.int64)
+            s1, m1 = _scale_min_k4(2 * c, sc)
+            s2, m2 = _scale_min_k4(2 * c + 1, sc)
+            i1 = int((lo * xq[c * 64:c * 64 + 32]).sum())
+            i2 = int((hi * xq[c * 64 + 32:c * 64 + 64]).sum())
+            idots += [i1, i2]
+            sumd = F(sumd + F(s1 * F(i1)))
+            sumd = F(sumd + F(s2 * F(i2)))
+            summ = F(summ + F(F(m1 * F(int(bs[2 * c]))) + F(m2 * F(int(bs[2 * c + 1])))))
+        total = F(total + F(scales[sb] * F(F(d * sumd) - F(dmin * summ))))
+    return total, np.asarray(idots, np.int32)
+
+
 def dot_q6k(row: np.ndarray, act):
     """cpu_math.rs:674-722.  Returns (value, the sixteen integer dots of 16 weights per super-block, in weight order)."""
     scales, q, _ = act
@@ -140,7 +168,7 @@ def dot_q80(row: np.ndarray, x: np.ndarray) -> np.float32:
 
 def matvec_kq(raw: np.ndarray, t: int, n: int, k: int, x: np.ndarray) -> np.ndarray:
     """cpu_math.rs:1145-1189: activations quantized once (K-quants), one block dot per row."""
-    rb = {12: 144 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32)}[t]
+    rb = {12: 144 * (k // 256), 13: 176 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32)}[t]
     rows = np.asarray(raw, np.uint8).reshape(n, rb)
     out = np.empty(n, F)
     if t == 8:
@@ -149,7 +177,7 @@ def matvec_kq(raw: np.ndarray, t: int, n: int, k: int, x: np.ndarray) -> np.ndar
         return out
     act = quant_q8k(x)
     for r in range(n):
-        out[r] = (dot_q4k if t == 12 else dot_q6k)(rows[r], act)[0]
+        out[r] = {12: dot_q4k, 13: dot_q5k, 14: dot_q6k}[t](rows[r], act)[0]
     return out
 
 

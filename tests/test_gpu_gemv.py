@@ -288,7 +288,7 @@ def test_errors_are_reported_not_fatal(gpu):
     with pytest.raises(ob.OjasB200Error, match="bias"):
         gpu.gemv(w, x, y, form=BIAS)
     with pytest.raises(ob.OjasB200Error, match="unsupported"):
-        gpu.gemv(ob.Lin(w.buf, 13, 4, 256), x, y)
+        gpu.gemv(ob.Lin(w.buf, 10, 4, 256), x, y)                     # Q2_K: not a format of this path
     with pytest.raises(ob.OjasB200Error, match="no kernel named"):
         gpu.dispatch(gpu.begin(), "gemv_nat_q2k", [(x, 0), (w.buf, 0), (y, 0)], [256, 4])
     with pytest.raises(ob.OjasB200Error, match="expected 3 buffers"):

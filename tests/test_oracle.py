@@ -237,3 +237,24 @@ def test_router_and_expert_ffn_second_entry():
     a = oracle.moe_ffn(wg, wu, wd, Q4_K, Q6_K, h, idx, wgt, d, ffn, threads=1)
     b = second_entry.moe_ffn(wg, wu, wd, Q4_K, Q6_K, h, idx, wgt, d, ffn)
     assert rel_l2(a, b) < 1e-6                              # (the exponential's last bit may flip a Q8_K rounding)
+
+
+def test_q5k_second_entry_and_identity():
+    """Q5_K (type 13) in the oracle: the dot against the transcription of the Rust source bit for bit (integer
+    sub-block dots included), matvec_kq likewise, and the identity dot(row, q8k(x)) == sum dequant(row)[i] * (sx * q[i])."""
+    import second_entry
+    from oracle import Q5_K
+    k, n = 768, 6
+    raw = oracle.synth_blocks(Q5_K, n * k // 256).reshape(n, -1)
+    x = np.random.default_rng(21).standard_normal(k).astype(np.float32)
+    act = oracle.quant_q8k(x)
+    w = oracle.dequant_f32(raw.reshape(-1), Q5_K, n * k).reshape(n, k).astype(np.float64)
+    xd = (np.repeat(act[0], 256).astype(np.float64) * act[1].astype(np.float64))
+    for r in range(n):
+        got, idots = oracle.dot_q5k(raw[r], act, want_idots=True)
+        want, widots = second_entry.dot_q5k(raw[r], act)
+        assert np.array_equal(idots, widots)
+        assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
+        assert abs(got - float(w[r] @ xd)) <= 1e-5 * float(np.abs(w[r]) @ np.abs(xd))
+    a, b = oracle.matvec_kq(raw, Q5_K, n, k, x, threads=1), second_entry.matvec_kq(raw, Q5_K, n, k, x)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))

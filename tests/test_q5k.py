@@ -1,0 +1,127 @@
+"""Q5_K (GGUF type 13) on the repack + GEMV part of the path: layout, integer block dots, outputs, entry names.  The
+CPU side of the format (decoder, dot_q5k against an independent transcription) is in tests/test_oracle.py."""
+import numpy as np
+import pytest
+
+import oracle
+import ojas_engine_b200 as ob
+from ojas_engine_b200 import ACCUM, BIAS, PLAIN, Q5_K
+
+from conftest import rel_l2
+from helpers import activations
+
+
+def _raw(n, k, roll=0):
+    base = oracle.synth_blocks(Q5_K, n * k // 256).reshape(n, -1)
+    return np.ascontiguousarray(np.roll(base, roll, axis=0))
+
+
+def test_q5k_tile_layout_keeps_every_bit():
+    """Host repack: piece p of row r of tile (u, s) at byte (p * 8 + r) * 16; pieces 0-7 = qs, 8 = the first sixteen bytes
+    of the block, 9-10 = qh; rows past N are zero blocks."""
+    n, k = 21, 768
+    raw = _raw(n, k)
+    packed = ob.repack_host(Q5_K, raw, n, k)
+    nsb, units = k // 256, (n + 7) // 8
+    assert packed.size >= units * nsb * 1408
+    tiles = packed[:units * nsb * 1408].reshape(units, nsb, 11, 8, 16)
+    for r in range(units * 8):
+        for s in range(nsb):
+            got = tiles[r // 8, s, :, r % 8, :]
+            if r >= n:
+                assert not got.any()
+                continue
+            blk = raw[r, s * 176:(s + 1) * 176]
+            assert np.array_equal(got[0:8].reshape(-1), blk[48:176])
+            assert np.array_equal(got[8], blk[0:16])
+            assert np.array_equal(got[9:11].reshape(-1), blk[16:48])
+
+
+@pytest.mark.gpu
+def test_q5k_device_repack_equals_host_repack(gpu):
+    n, k = 77, 1024
+    raw = _raw(n, k)
+    w = gpu.load_weight(raw, Q5_K, n, k)
+    want = ob.repack_host(Q5_K, raw, n, k)
+    assert np.array_equal(gpu.read(w.buf, np.uint8, want.size), want)
+    gpu.free(w.buf)
+
+
+@pytest.mark.gpu
+def test_q5k_integer_block_dots_bit_exact(gpu):
+    n, k = 40, 1024
+    raw = _raw(n, k)
+    x = activations(1, k, seed=5)
+    w = gpu.load_weight(raw, Q5_K, n, k)
+    xb, out = gpu.upload(x), gpu.alloc_bytes(n * (k // 256) * 8 * 4)
+    gpu.gemv_idots(w, xb, out)
+    got = gpu.read(out, np.int32, n * (k // 256) * 8).reshape(n, -1)
+    act = oracle.quant_q8k(x[0])
+    for r in range(n):
+        _, want = oracle.dot_q5k(raw[r], act, want_idots=True)
+        assert np.array_equal(got[r], want)
+    for b in (w.buf, xb, out):
+        gpu.free(b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,k,m", [(512, 4096, 1), (1000, 768, 1), (4096, 4096, 1), (330, 1024, 2), (64, 2048, 3), (520, 512, 5), (256, 4096, 8)])
+def test_q5k_gemv_matches_the_oracle(gpu, n, k, m):
+    raw = _raw(n, k, roll=3)
+    x = activations(m, k, seed=7 + m)
+    w = gpu.load_weight(raw, Q5_K, n, k)
+    guard = 64
+    xb = gpu.upload(x)
+    y = gpu.upload(np.full(m * n + 2 * guard, 7.25, np.float32))
+    yv = ob.Buf(y.ptr + guard * 4, m * n * 4)
+    gpu.gemv(w, xb, yv, m)
+    full = gpu.read(y, np.float32, m * n + 2 * guard)
+    assert np.all(full[:guard] == 7.25) and np.all(full[-guard:] == 7.25)          # nothing written outside [M, N]
+    got = full[guard:-guard].reshape(m, n)
+    want = oracle.matmul_kq(raw, Q5_K, n, k, x)
+    assert rel_l2(got, want) < 1e-5
+    for b in (w.buf, xb, y):
+        gpu.free(b)
+
+
+@pytest.mark.gpu
+def test_q5k_store_forms_prequantized_rows_and_entry_names(gpu):
+    n, k = 384, 1024
+    raw = _raw(n, k, roll=1)
+    x = activations(1, k, seed=9)
+    w = gpu.load_weight(raw, Q5_K, n, k)
+    want = oracle.matvec_kq(raw, Q5_K, n, k, x[0])
+    xb = gpu.upload(x)
+    y0 = activations(1, n, seed=10)[0]
+    bias = activations(1, n, seed=11)[0]
+    y, bb = gpu.upload(y0), gpu.upload(bias)
+    gpu.gemv(w, xb, y, 1, ACCUM)
+    assert rel_l2(gpu.read(y, np.float32, n), want + y0) < 1e-5
+    gpu.gemv(w, xb, y, 1, BIAS, bb)
+    assert rel_l2(gpu.read(y, np.float32, n), want + bias) < 1e-5
+    q, s, b = gpu.alloc_bytes(k), gpu.alloc(k // 256), gpu.alloc_bytes(k // 32 * 4)
+    gpu.quant_q8k(xb, 1, k, q, s, b)
+    gpu.gemv(w, xb, y, 1, PLAIN)
+    plain = gpu.read(y, np.float32, n)
+    gpu.gemv_q8k(w, q, s, b, y, 1)
+    assert np.array_equal(gpu.read(y, np.float32, n), plain)                       # the same kernel minus the prologue
+    assert all(gpu.has_kernel(name) for name in ("gemv_nat_q5k", "gemv_nat_q5k_accum", "gemv_nat_q5k_bias", "gemv_nat_q5k_m"))
+    gpu.memset(y, 0)
+    enc = gpu.begin()
+    gpu.dispatch(enc, "gemv_nat_q5k", [(xb, 0), (w.buf, 0), (y, 0)], [k, n])
+    gpu.submit(enc)
+    assert np.array_equal(gpu.read(y, np.float32, n), plain)
+    for buf in (w.buf, xb, y, bb, q, s, b):
+        gpu.free(buf)
+
+
+@pytest.mark.gpu
+def test_q5k_is_refused_where_it_is_not_built(gpu):
+    n, k = 256, 512
+    w = gpu.load_weight(_raw(n, k), Q5_K, n, k)
+    x, y = gpu.alloc(16 * k), gpu.alloc(16 * n)
+    with pytest.raises(ob.OjasB200Error):
+        gpu.gemm(w, x, y, 16)
+    gpu.sync()
+    for b in (w.buf, x, y):
+        gpu.free(b)
