@@ -231,7 +231,7 @@ def test_router_and_expert_ffn_second_entry():
         i2, w2 = second_entry.moe_topk(lg[t], ksel)
         assert np.array_equal(idx[t], i2) and np.allclose(wgt[t], w2, rtol=2e-6, atol=0)
     wg = oracle.synth_blocks(Q4_K, e * ffn * d // 256)
-    wu = oracle.synth_blocks(Q4_K, e * ffn * d // 256)[::-1].copy()
+    wu = np.roll(oracle.synth_blocks(Q4_K, e * ffn * d // 256).reshape(-1, 144), 5, axis=0).reshape(-1).copy()
     wd = oracle.synth_blocks(Q6_K, e * d * ffn // 256)
     h = rng.standard_normal((m, d)).astype(np.float32)
     a = oracle.moe_ffn(wg, wu, wd, Q4_K, Q6_K, h, idx, wgt, d, ffn, threads=1)
