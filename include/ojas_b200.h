@@ -259,6 +259,13 @@ OJAS_B200_API size_t ojas_b200_weight_cache_count(const ojas_b200_weight_cache *
 OJAS_B200_API int ojas_b200_weight_cache_entry(const ojas_b200_weight_cache *cache, size_t index, const char **name, uint32_t *ggml_type,
                                                uint64_t *N, uint64_t *K, const void **data, uint64_t *bytes);
 
+/* ---- token-table gather: x[m, :] = dequantized row ids[m] of a table kept as RAW GGUF blocks [rows, d] on the device
+ * (read in place; not the repacked layout).  Replaces q35_embed_q4k (crates/ojas-cuda/src/kernels/qwen35.rs:51-69) for
+ * Q4_K, Q5_K, Q6_K and Q8_0 tables; the values equal the CPU decoder's bit for bit.  An id >= rows reads the last row.
+ * The entry name "q35_embed_q4k" (emb, ids, x)(d, M) is served by ojas_b200_dispatch. */
+OJAS_B200_API int ojas_b200_embed_rows(ojas_b200_ctx *ctx, uint32_t ggml_type, const void *table, size_t rows, const uint32_t *ids, size_t M,
+                                       size_t d, float *x);
+
 /* ---- expert residency: replaces ExpertCache (crates/ojas-cuda/src/expert_cache.rs:34-160).  A bounded arena of
  * expert-sized slots in device memory with least-recently-used eviction; misses are streamed from the host through
  * pinned staging memory and re-laid into tiles on the device.  gather() returns byte offsets into the arena: what the

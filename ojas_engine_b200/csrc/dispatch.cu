@@ -146,6 +146,11 @@ static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, c
     return ojas_b200_moe_topk(ctx, (const float *)b[0], (uint32_t *)b[1], (float *)b[2], c[2], c[0], c[1]);
 }
 
+// q35_embed_q4k: (emb, ids, x) (d, M) -- crates/ojas-cuda/src/kernels/qwen35.rs:53; the table is raw GGUF Q4_K
+static int d_embed_q4k(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {
+    return ojas_b200_embed_rows(ctx, OJAS_B200_Q4_K, b[0], 0xffffffffu, (const uint32_t *)b[1], c[1], c[0], (float *)b[2]);
+}
+
 #define GEMV_TABLE(tag)                                      \
     {"gemv_nat_" #tag, 3, 2, gemv_##tag##_plain},            \
     {"gemv_nat_" #tag "_accum", 3, 2, gemv_##tag##_accum},   \
@@ -159,6 +164,7 @@ static int d_moe_topk_m(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, c
 static const NameEntry kTable[] = {
     GEMV_TABLE(q4k), GEMV_TABLE(q5k), GEMV_TABLE(q6k), GEMV_TABLE(q80),
     {"quant_q8k", 4, 2, d_quant_q8k},
+    {"q35_embed_q4k", 3, 2, d_embed_q4k},
     {"moe_topk", 3, 2, d_moe_topk}, {"moe_topk_m", 3, 3, d_moe_topk_m},
     {"gemm_mm_q4k", 3, 4, gemm_q4k}, {"gemm_mm_q6k", 3, 4, gemm_q6k}, {"gemm_mm_q8_0", 3, 4, gemm_q8_0}, {"gemm_mm_q4l", 5, 4, gemm_q4l},
     {"gemm_mm_q4k_sk", 3, 4, gemm_q4k_sk}, {"gemm_mm_q6k_sk", 3, 4, gemm_q6k_sk}, {"gemm_mm_q8_0_sk", 3, 4, gemm_q8_0_sk},

@@ -65,6 +65,7 @@ SIGNATURES = {
     "ojas_b200_moe_topk": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "ojas_b200_moe_workspace_bytes": (_sz, [_sz, _sz, _sz, _sz, _sz]),
     "ojas_b200_moe_ffn": (_i, [_vp, _u32, _u32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _i, _vp, _sz]),
+    "ojas_b200_embed_rows": (_i, [_vp, _u32, _vp, _sz, _vp, _sz, _sz, _vp]),
     "ojas_b200_gguf_open": (_i, [C.c_char_p, C.POINTER(_vp), C.c_char_p, _sz]),
     "ojas_b200_gguf_close": (None, [_vp]),
     "ojas_b200_gguf_tensor_count": (_sz, [_vp]),

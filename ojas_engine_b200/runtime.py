@@ -270,6 +270,10 @@ class B200Gpu:
         self._ck(self._l.ojas_b200_gemm_static(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(y.ptr),
                                                w.k, w.n, m, 1 if accum else 0))
 
+    def embed_rows(self, table: Buf, ggml_type: int, rows: int, ids: Buf, m: int, d: int, x: Buf) -> None:
+        """``x[m, :]`` = the dequantized row ``ids[m]`` of a token table kept as raw GGUF blocks (``q35_embed_q4k``)."""
+        self._ck(self._l.ojas_b200_embed_rows(self._ctx, ggml_type, C.c_void_p(table.ptr), rows, C.c_void_p(ids.ptr), m, d, C.c_void_p(x.ptr)))
+
     def gemv_idots(self, w: Lin, x: Buf, idots: Buf) -> None:
         self._ck(self._l.ojas_b200_gemv_idots(self._ctx, w.ggml_type, C.c_void_p(x.ptr), C.c_void_p(w.buf.ptr), C.c_void_p(idots.ptr), w.k, w.n))
 

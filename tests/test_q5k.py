@@ -125,3 +125,26 @@ def test_q5k_is_refused_where_it_is_not_built(gpu):
     gpu.sync()
     for b in (w.buf, x, y):
         gpu.free(b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("t", [ob.Q4_K, Q5_K, ob.Q6_K, ob.Q8_0])
+def test_token_table_gather_equals_the_cpu_decode(gpu, t):
+    """x[m, :] = row ids[m] of a raw GGUF table, bit for bit the oracle's decoder (which the reference's own golden
+    digests pin for Q4_K and Q6_K); repeated and out-of-order ids; by name for Q4_K."""
+    rows, d = 37, 1024
+    raw = oracle.synth_blocks(t, rows * d // (32 if t == ob.Q8_0 else 256))
+    table = oracle.dequant_f32(raw, t, rows * d).reshape(rows, d)
+    ids = np.array([5, 0, 36, 5, 17, 1, 36], np.uint32)
+    tb, ib, x = gpu.upload(raw), gpu.upload(ids), gpu.alloc(ids.size * d)
+    gpu.embed_rows(tb, t, rows, ib, ids.size, d, x)
+    got = gpu.read(x, np.float32, ids.size * d).reshape(ids.size, d)
+    assert np.array_equal(got.view(np.uint32), table[ids].view(np.uint32))
+    if t == ob.Q4_K:
+        gpu.memset(x, 0)
+        enc = gpu.begin()
+        gpu.dispatch(enc, "q35_embed_q4k", [(tb, 0), (ib, 0), (x, 0)], [d, ids.size])
+        gpu.submit(enc)
+        assert np.array_equal(gpu.read(x, np.float32, ids.size * d).reshape(ids.size, d).view(np.uint32), table[ids].view(np.uint32))
+    for b in (tb, ib, x):
+        gpu.free(b)
