@@ -560,6 +560,8 @@ def run_case(args) -> None:
         gpu.set_option("gemv_warps", args.warps)
     if args.stages:
         gpu.set_option("gemv_stages", args.stages)
+    for kv in args.opt:
+        gpu.set_option(kv.split("=")[0], int(kv.split("=")[1]))
     gguf = ob.raw_bytes(t, n, k)
     ring = args.ring or max(2, int(300e6 // gguf) + 1)
     base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
@@ -834,7 +836,7 @@ def main() -> None:
     ap.add_argument("--ksplit", type=int, default=0, help="--case gemm: force the K split (0 = automatic)")
     ap.add_argument("--warps", type=int, default=0, help="--case: the gemv_warps option (warps per CTA; 0 = chosen per shape)")
     ap.add_argument("--stages", type=int, default=0, help="--case: the gemv_stages option (ring stages per warp; 0 = chosen per shape)")
-    ap.add_argument("--opt", action="append", default=[], help="--case moe: a library option as key=value (repeatable)")
+    ap.add_argument("--opt", action="append", default=[], help="--case: a library option as key=value (repeatable)")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch (default: with)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -172,7 +172,7 @@ extern "C" int ojas_b200_create(int device, void *stream, ojas_b200_ctx **out) {
     // (crates/ojas-core/src/config.rs:1-22, crates/ojas-cuda/src/device.rs:87-118): OJAS_B200_<OPTION>=<integer> for every
     // key of ojas_b200_set_option, e.g. OJAS_B200_PDL=0, OJAS_B200_GEMM_KSPLIT=4, OJAS_B200_PROFILE=1.  A value that the
     // option refuses is ignored.
-    static const char *const keys[] = {"pdl", "gemv_mma", "gemv_warps", "gemv_stages", "gemm_ksplit", "moe_gemm_rows", "moe_i8", "profile"};
+    static const char *const keys[] = {"pdl", "gemv_mma", "gemv_warps", "gemv_stages", "gemv_kseg", "gemm_ksplit", "moe_gemm_rows", "moe_i8", "profile"};
     for (const char *key : keys) {
         char name[64] = "OJAS_B200_";
         size_t n = strlen(name);
@@ -249,6 +249,11 @@ extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int val
     if (!strcmp(key, "gemv_warps")) {
         if (value < 0 || value > 16 || (value & (value - 1)) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_warps must be 0 (automatic), 1, 2, 4, 8 or 16");
         ctx->gemv_warps = value;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_kseg")) {
+        if (value < 0 || value > 64) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_kseg must be 0 (automatic), 1 (never) or a segment count up to 64");
+        ctx->gemv_kseg = value;
         return 0;
     }
     if (!strcmp(key, "gemv_stages")) {

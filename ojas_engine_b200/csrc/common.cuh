@@ -21,6 +21,7 @@ struct ojas_b200_ctx {
     struct OjasProfile *prof = nullptr;  // per-launch event profiler (OJAS_B200_PROFILE=1 or option "profile"), null when off
     int gemv_mma = 1;            // Q4_K batches of 3..8 rows and expert groups on the tensor-core batch kernel (0: per-lane kernels only)
     int gemv_warps = 0;          // GEMV: warps per CTA (0: chosen per shape; otherwise 1..16)
+    int gemv_kseg = 0;           // Q8_0 batches of 3..8 rows: K segments per launch (0: only when the whole K does not fit; 1: never; n: n when it divides K / 256)
     int gemv_stages = 0;         // GEMV: ring stages per warp (0: chosen per shape; otherwise 1..4)
     int moe_gemm_rows = 0;       // expert FFN: grouped tensor-core GEMMs from this many rows per expert on average (0: never)
     int gemm_ksplit = 0;         // 0: choose the K split per shape; >0: force it
@@ -133,9 +134,12 @@ int ojas_experts_i8_pack(ojas_b200_ctx *ctx, const int8_t *q, const float *scale
                          size_t K, int8_t *q_out, void *meta);
 int ojas_experts_i8(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const void *meta,
                     size_t positions, const int *counts, const int *offsets, size_t E, size_t K, size_t N, int kparts, size_t part_stride, int tok);
-int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
-                          const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
-                          size_t rows_hint);
+int ojas_gemv_experts_batch(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q,
+                            const float *scales, const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E,
+                            size_t K, size_t N, size_t rows_hint);
+int ojas_gemv_experts_kq(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q,
+                         const float *scales, const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K,
+                         size_t N, size_t rows_hint);
 int ojas_gemv_grouped(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w, const int8_t *q, const float *scales,
                       const int32_t *bsums, const int *row_index, const int *grp_count, const int *grp_offset, float *y,
                       size_t K, size_t N);

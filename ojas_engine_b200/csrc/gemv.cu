@@ -47,6 +47,9 @@ struct GemvArgs {
     int T_log;               // teams per CTA = 1 << T_log (warps per CTA = teams * warps per team)
     int P;                   // partial sums per row and group = min(warps per team, nsb)
     int own_x;               // 1: warp w consumes exactly super-block w, so it quantizes that one for itself
+    // K walked in segments (gemv_q80_kseg_kernel): a pass sees K = the segment's length, while activation rows are
+    // x_stride values apart and the tiles of consecutive 8-row units w_nsb super-blocks apart (0 = K and nsb)
+    int x_stride, w_nsb;
     // decode-time expert selection (the engine's moe_gu_* / moe_down_* and their _slots forms,
     // crates/ojas-cuda/src/kernels/moe.rs:75-178): the weight rows start `*sel * sel_stride` bytes (sel_stride != 0)
     // or `*sel` bytes (an offset table entry) behind w, read on the device; alpha (may be null): the result is
@@ -289,7 +292,7 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
 __host__ __device__ inline size_t q80_act_row_bytes(size_t K) { return 3 * K + K / 8 + 16; }
 
 template <int MT, int PRO>
-__device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int nsb, int warps) {
+__device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int nsb, int warps, int sb0 = 0) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t rb = q80_act_row_bytes((size_t)a.K);
     float inv[MT];
@@ -299,7 +302,7 @@ __device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int n
         uint8_t *row = act + m * rb;
         float *sc = reinterpret_cast<float *>(row + 3 * (size_t)a.K);
         if (m < a.M) {
-            const float *xr = a.x + (size_t)src_row(a, m) * a.K;
+            const float *xr = a.x + (size_t)src_row(a, m) * (PRO == 0 && a.x_stride ? a.x_stride : a.K) + (size_t)sb0 * 256;
             for (int sb = warp; sb < nsb; sb += warps) {
                 float v[8];
                 if (PRO == 1) {
@@ -553,7 +556,7 @@ __device__ __forceinline__ void step_q80_mma(const uint8_t *stage, const uint8_t
 // `ring_uses` counts the steps this warp has put through its ring since the kernel began (the grouped kernel calls
 // the body once per pass and the barriers' phases carry over).
 template <int TYPE, int MT, bool PREQ, bool DUMP, int PRO = 0>
-__device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem, unsigned &ring_uses, bool first_pass) {
+__device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem, unsigned &ring_uses, bool first_pass, int sb0 = 0) {
     constexpr int TB = tile_bytes(TYPE), STEP = 4 * TB;
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nsb = a.nsb, P = a.P;
@@ -580,7 +583,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         }
         __syncwarp();
     }
-    const uint8_t *wbase = a.w;
+    const uint8_t *wbase = a.w + (TYPE == OJAS_B200_Q8_0 ? (size_t)sb0 * TB : (size_t)0);   // sb0: first super-block of a K segment (Q8_0 only)
+    const int wnsb = (TYPE == OJAS_B200_Q8_0 && a.w_nsb) ? a.w_nsb : nsb;   // super-blocks between the tiles of consecutive units
     if (a.sel) {                                                  // the pick comes from the router kernel before this one
         grid_dependency_wait();
         const size_t s = (size_t)__ldg(a.sel);
@@ -594,10 +598,10 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     auto issue = [&]() {
         const int g = team + ik * T;
         const int cnt = (nu - 4 * g) < 4 ? (nu - 4 * g) : 4;
-        const uint8_t *src = wbase + ((size_t)(ub + 4 * g) * nsb + isb) * TB;
+        const uint8_t *src = wbase + ((size_t)(ub + 4 * g) * wnsb + isb) * TB;
         const unsigned stg = issued & (unsigned)(nst - 1);
         gv_bar_expect(bar + stg, (unsigned)(cnt * TB));
-        for (int t = 0; t < cnt; t++) gv_bulk_load(ring + stg * STEP + t * TB, src + (size_t)t * nsb * TB, TB, bar + stg);
+        for (int t = 0; t < cnt; t++) gv_bulk_load(ring + stg * STEP + t * TB, src + (size_t)t * wnsb * TB, TB, bar + stg);
         issued++;
         isb += S;
         while (isb >= nsb) { isb -= nsb; ik++; }
@@ -607,7 +611,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         for (int i = 0; i < nst && i < nsteps; i++) issue();
     }
     if (first_pass) grid_dependency_wait();                       // activations (and y for the accumulate form) come from the kernel before
-    if (TYPE == OJAS_B200_Q8_0) stage_q80<MT, PRO>(a, act, nsb, warps);
+    if (TYPE == OJAS_B200_Q8_0) stage_q80<MT, PRO>(a, act, nsb, warps, sb0);
     else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ, PRO>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
     const float alpha = a.alpha ? __ldg(a.alpha) : 1.0f;
@@ -683,7 +687,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
                 const uint2 pair = make_uint2(__float_as_uint(v), tp_stamp);
                 for (int i = 0; i < a.tp.n; i++) a.tp.dst[i][tp_half + (size_t)m * a.N + row] = pair;     // every rank's receive window
             } else {
-                store_form(a.y + (size_t)m * a.N + row, v, a.form, a.bias, row);
+                store_form(a.y + (size_t)m * a.N + row, v, (TYPE == OJAS_B200_Q8_0 && sb0) ? (int)OJAS_B200_ACCUM : a.form, a.bias, row);
             }
         }
     }
@@ -723,6 +727,19 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_grouped_kernel(co
         else { b.q = a.q + (size_t)(off + mb) * a.K; b.scales = a.scales + (size_t)(off + mb) * (a.K >> 8); b.bsums = a.bsums + (size_t)(off + mb) * (a.K >> 5); }
         b.y = a.y + (size_t)(off + mb) * a.N;
         gemv_body<TYPE, MT, true, false>(b, gemv_smem, ring_uses, mb == 0);
+        __syncthreads();
+    }
+}
+
+// Q8_0 batches whose activations (3.1 bytes per value and row) do not fit in shared memory for the whole K: the same
+// body over equal K segments, every pass staging its segment of the rows and adding onto what the passes before stored
+// (the same thread stores the same y element in every pass, so program order is enough).
+template <int MT>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_q80_kseg_kernel(const GemvArgs a, const int seg_nsb) {
+    extern __shared__ __align__(128) unsigned char gemv_smem[];
+    unsigned ring_uses = 0;
+    for (int sb0 = 0; sb0 < a.w_nsb; sb0 += seg_nsb) {
+        gemv_body<OJAS_B200_Q8_0, MT, false, false>(a, gemv_smem, ring_uses, sb0 == 0, sb0);
         __syncthreads();
     }
 }
@@ -901,12 +918,12 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
 }
 
 // ---- the tensor-core batch kernel (gemv_mma.cuh): plan and launch
-static bool batch_plan(ojas_b200_ctx *ctx, int NT, size_t K, size_t N, GemvPlan &p) {
+static bool batch_plan(ojas_b200_ctx *ctx, uint32_t type, int NT, size_t K, size_t N, GemvPlan &p) {
     const size_t nsb = K / 256, units = tile_units(N), groups = (units + 3) / 4;
-    const size_t step = 4 * (size_t)tile_bytes(OJAS_B200_Q4_K), limit = (size_t)ctx->smem_optin;
+    const size_t step = 4 * (size_t)tile_bytes(type), limit = (size_t)ctx->smem_optin;
     p.grid = (int)(groups < (size_t)ctx->sm_count ? groups : (size_t)ctx->sm_count);
     const size_t units_max = (units + p.grid - 1) / p.grid, ng = (units_max + 3) / 4;
-    const size_t fixed = ((batch_act_bytes(NT, K) + 15) & ~(size_t)15) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
+    const size_t fixed = ((batch_act_bytes(type, NT, K) + 15) & ~(size_t)15) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
     const int w_hi = ctx->gemv_warps ? ctx->gemv_warps : GEMV_MAX_WARPS, n_hi = ctx->gemv_stages ? ctx->gemv_stages : 2;
     size_t best_bytes = 0;
     bool found = false;
@@ -934,10 +951,11 @@ static bool batch_plan(ojas_b200_ctx *ctx, int NT, size_t K, size_t N, GemvPlan 
 
 // Launches the batch kernel over `E` expert groups (E = 1, counts = null: a plain batch of M rows).  NT (8, 16 or 32)
 // is the largest pass that fits; returns 1 when nothing fits.
-static int batch_launch(ojas_b200_ctx *ctx, BatchArgs a, int nt_want) {
+static int batch_launch(ojas_b200_ctx *ctx, uint32_t type, BatchArgs a, int nt_want) {
+    const char *name = type == OJAS_B200_Q6_K ? "gemv_q6k_batch" : "gemv_q4k_batch";
     for (int NT = nt_want; NT >= 8; NT >>= 1) {
         GemvPlan p;
-        if (!batch_plan(ctx, NT, (size_t)a.K, (size_t)a.N, p)) continue;
+        if (!batch_plan(ctx, type, NT, (size_t)a.K, (size_t)a.N, p)) continue;
         const size_t units = tile_units((size_t)a.N);
         a.nsb = a.K / 256;
         a.units_base = (int)(units / p.grid);
@@ -947,7 +965,7 @@ static int batch_launch(ojas_b200_ctx *ctx, BatchArgs a, int nt_want) {
         auto go = [&](auto kernel) -> int {
             if (p.smem > 48 * 1024) {
                 cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);
-                if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemv_q4k_batch: shared memory %zu: %s", p.smem, cudaGetErrorString(e));
+                if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "%s: shared memory %zu: %s", name, p.smem, cudaGetErrorString(e));
             }
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)p.grid);
@@ -960,27 +978,50 @@ static int batch_launch(ojas_b200_ctx *ctx, BatchArgs a, int nt_want) {
             cfg.attrs = attr;
             cfg.numAttrs = ctx->pdl ? 1 : 0;
             cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
-            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemv_q4k_batch: %s", cudaGetErrorString(e));
-            ojas_count_launch(ctx, "gemv_q4k_batch");
+            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch %s: %s", name, cudaGetErrorString(e));
+            ojas_count_launch(ctx, name);
             return 0;
         };
-        if (NT == 32) return go(gemv_q4k_batch_kernel<4>);
-        if (NT == 16) return go(gemv_q4k_batch_kernel<2>);
-        return go(gemv_q4k_batch_kernel<1>);
+        if (type == OJAS_B200_Q6_K) {
+            if (NT == 16) return go(gemv_kq_batch_kernel<OJAS_B200_Q6_K, 2>);
+            if (NT == 8) return go(gemv_kq_batch_kernel<OJAS_B200_Q6_K, 1>);
+            continue;
+        }
+        if (NT == 32) return go(gemv_kq_batch_kernel<OJAS_B200_Q4_K, 4>);
+        if (NT == 16) return go(gemv_kq_batch_kernel<OJAS_B200_Q4_K, 2>);
+        return go(gemv_kq_batch_kernel<OJAS_B200_Q4_K, 1>);
     }
     return 1;
+}
+
+// The expert FFN's matmuls on the batch kernel, every expert (and both of gate / up) in one launch: each CTA owns the
+// same slice of rows of every expert and walks the experts with rows.  Used for Q6_K experts (Q4_K has the experts
+// kernel below).  Returns 1 when the shape does not fit.
+int ojas_gemv_experts_batch(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q,
+                            const float *scales, const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E,
+                            size_t K, size_t N, size_t rows_hint) {
+    if ((type != OJAS_B200_Q4_K && type != OJAS_B200_Q6_K) || N % OJAS_TILE_ROWS != 0) return 1;
+    BatchArgs b{};
+    b.w[0] = w0; b.w[1] = w1; b.y[0] = y0; b.y[1] = y1; b.nw = w1 ? 2 : 1;
+    b.expert_bytes = (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type);
+    b.q = q; b.scales = scales; b.bsums = bsums; b.row_index = row_index; b.counts = counts; b.offsets = offsets;
+    b.form = OJAS_B200_PLAIN;
+    b.E = (int)E; b.M = 0; b.K = (int)K; b.N = (int)N;
+    return batch_launch(ctx, type, b, rows_hint + rows_hint / 2 > 8 ? 16 : 8);
 }
 
 // The expert FFN's matmuls on the experts kernel (gemv_mma.cuh): `nw` weight tensors (gate and up share the
 // activations) of E stacked experts [E * N, K], rows grouped by expert (counts / offsets on the device).  Returns 1
 // when the shape does not fit (the caller falls back to one grouped launch per expert).
-int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q, const float *scales,
-                          const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K, size_t N,
-                          size_t rows_hint) {
+int ojas_gemv_experts_kq(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q,
+                         const float *scales, const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K,
+                         size_t N, size_t rows_hint) {
+    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q6_K) return 1;
     if (N % OJAS_TILE_ROWS != 0 || E > (size_t)EXPERT_MAX_E) return 1;       // experts must start on a tile boundary
+    const char *name = type == OJAS_B200_Q6_K ? "moe_q6k_experts" : "moe_q4k_experts";
     ExpertArgs a{};
     a.w[0] = w0; a.w[1] = w1; a.y[0] = y0; a.y[1] = y1; a.nw = w1 ? 2 : 1;
-    a.expert_bytes = (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(OJAS_B200_Q4_K);
+    a.expert_bytes = (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type);
     a.q = q; a.scales = scales; a.bsums = bsums; a.row_index = row_index; a.counts = counts; a.offsets = offsets;
     a.E = (int)E; a.K = (int)K; a.N = (int)N; a.nsb = (int)(K / 256);
     a.status = ctx->dev_status;
@@ -988,9 +1029,9 @@ int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *
     const size_t want = rows_hint + rows_hint / 2;
     const int ntile = want > 24 ? 4 : want > 16 ? 3 : want > 8 ? 2 : 1;
     const int warps = ctx->gemv_warps ? ctx->gemv_warps : GEMV_MAX_WARPS;
-    const size_t step = 2 * (size_t)tile_bytes(OJAS_B200_Q4_K), limit = (size_t)ctx->smem_optin;
+    const size_t step = 2 * (size_t)tile_bytes(type), limit = (size_t)ctx->smem_optin;
     for (int nt = ntile; nt >= 1; nt--) {
-        const size_t fixed = ((expert_act_bytes(8 * nt, K) + 15) & ~(size_t)15) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
+        const size_t fixed = ((expert_act_bytes(type, 8 * nt, K) + 15) & ~(size_t)15) + GEMV_MAX_WARPS * GEMV_MAX_STAGES * 8 + 128;
         int nst = ctx->gemv_stages ? ctx->gemv_stages : GEMV_MAX_STAGES;
         while (nst >= 2 && fixed + (size_t)warps * nst * step > limit) nst--;
         if (nst < 2) continue;
@@ -998,7 +1039,7 @@ int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *
         const size_t smem = fixed + (size_t)warps * nst * step;
         auto go = [&](auto kernel) -> int {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "moe_q4k_experts: shared memory %zu: %s", smem, cudaGetErrorString(e));
+            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "%s: shared memory %zu: %s", name, smem, cudaGetErrorString(e));
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)ctx->sm_count);
             cfg.blockDim = dim3((unsigned)warps * 32);
@@ -1010,14 +1051,20 @@ int ojas_gemv_experts_q4k(ojas_b200_ctx *ctx, const uint8_t *w0, const uint8_t *
             cfg.attrs = attr;
             cfg.numAttrs = ctx->pdl ? 1 : 0;
             e = cudaLaunchKernelEx(&cfg, kernel, a);
-            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch moe_q4k_experts: %s", cudaGetErrorString(e));
-            ojas_count_launch(ctx, "moe_q4k_experts");
+            if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch %s: %s", name, cudaGetErrorString(e));
+            ojas_count_launch(ctx, name);
             return 0;
         };
-        if (nt == 4) return go(moe_q4k_experts_kernel<4>);
-        if (nt == 3) return go(moe_q4k_experts_kernel<3>);
-        if (nt == 2) return go(moe_q4k_experts_kernel<2>);
-        return go(moe_q4k_experts_kernel<1>);
+        if (type == OJAS_B200_Q6_K) {
+            if (nt == 4) return go(moe_kq_experts_kernel<OJAS_B200_Q6_K, 4>);
+            if (nt == 3) return go(moe_kq_experts_kernel<OJAS_B200_Q6_K, 3>);
+            if (nt == 2) return go(moe_kq_experts_kernel<OJAS_B200_Q6_K, 2>);
+            return go(moe_kq_experts_kernel<OJAS_B200_Q6_K, 1>);
+        }
+        if (nt == 4) return go(moe_kq_experts_kernel<OJAS_B200_Q4_K, 4>);
+        if (nt == 3) return go(moe_kq_experts_kernel<OJAS_B200_Q4_K, 3>);
+        if (nt == 2) return go(moe_kq_experts_kernel<OJAS_B200_Q4_K, 2>);
+        return go(moe_kq_experts_kernel<OJAS_B200_Q4_K, 1>);
     }
     return 1;
 }
@@ -1044,7 +1091,7 @@ static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvA
     if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch || args.norm_w || args.x2) return false;   // (a fused producer runs in the kernel's prologue)
     const size_t values = M * (size_t)args.K;
     if (values > OJAS_ACT_SCRATCH_VALUES) return false;
-    if (values < 16384 && !(type == OJAS_B200_Q4_K && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
+    if (values < 16384 && !((type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
     int8_t *q = (int8_t *)ctx->act_scratch;
     float *scales = (float *)(q + OJAS_ACT_SCRATCH_VALUES);
     int32_t *bsums = (int32_t *)(scales + OJAS_ACT_SCRATCH_VALUES / 256);
@@ -1059,18 +1106,68 @@ static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvA
     return true;
 }
 
+// Q8_0 rows 3..8 with a K too long for one pass: the largest equal segmentation of K (a divisor of its super-block
+// count) among those that keep the most weight bytes in flight.  Returns 1 when the whole K fits (no segments
+// needed) or no segmentation does.
+static int gemv_q80_kseg(ojas_b200_ctx *ctx, GemvArgs args, size_t nsb) {
+    GemvPlan whole;
+    if (ctx->gemv_kseg == 0 && gemv_plan(ctx, OJAS_B200_Q8_0, 8, (size_t)args.K, (size_t)args.N, whole)) return 1;
+    GemvPlan best{};
+    size_t best_seg = 0, best_bytes = 0;
+    for (size_t seg = nsb - 1; seg >= 1; seg--) {
+        if (nsb % seg) continue;
+        if (ctx->gemv_kseg > 0 && nsb / seg != (size_t)ctx->gemv_kseg) continue;
+        GemvPlan p;
+        if (!gemv_plan(ctx, OJAS_B200_Q8_0, 8, seg * 256, (size_t)args.N, p)) continue;
+        const size_t bytes = (size_t)p.warps * ((size_t)1 << p.nst_log);
+        if (bytes > best_bytes) { best_bytes = bytes; best_seg = seg; best = p; }
+    }
+    if (!best_seg) return 1;
+    const int K = args.K;
+    args.K = (int)(best_seg * 256);
+    gemv_fill(args, ctx, best);
+    args.own_x = 0;
+    args.x_stride = K;
+    args.w_nsb = (int)nsb;
+    void (*kernel)(const GemvArgs, const int) = gemv_q80_kseg_kernel<8>;
+    if (best.smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)best.smem);
+        if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "gemv_q80_kseg: shared memory %zu: %s", best.smem, cudaGetErrorString(e));
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)best.grid);
+    cfg.blockDim = dim3((unsigned)best.warps * 32);
+    cfg.dynamicSmemBytes = best.smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (ctx->pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const GemvArgs)args, (const int)best_seg);
+    if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemv_q80_kseg: %s", cudaGetErrorString(e));
+    ojas_count_launch(ctx, "gemv_q80_kseg");
+    return 0;
+}
+
 static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args, size_t M) {
     if (gemv_prequantize(ctx, type, preq, args, M)) preq = true;
-    if (type == OJAS_B200_Q4_K && preq && M >= 3 && ctx->gemv_mma != 0 && !args.tp.step) {   // tensor-core batch kernel
+    if ((type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) && preq && M >= 3 && ctx->gemv_mma != 0 && !args.tp.step) {   // tensor-core batch kernel
         BatchArgs b{};
         b.w[0] = args.w; b.y[0] = args.y; b.nw = 1;
         b.q = args.q; b.scales = args.scales; b.bsums = args.bsums;
         b.bias = args.bias; b.form = args.form;
         b.E = 1; b.M = (int)M; b.K = args.K; b.N = args.N;
-        const int rc = batch_launch(ctx, b, 8);
+        const int rc = batch_launch(ctx, type, b, 8);
         if (rc != 1) return rc;
     }
     const size_t nsb = (size_t)args.K / 256;
+    if (type == OJAS_B200_Q8_0 && M >= 3 && M <= 8 && !args.tp.step && !args.norm_w && !args.x2 && !args.row_index) {
+        const int rc = gemv_q80_kseg(ctx, args, nsb);
+        if (rc != 1) return rc;
+    }
     // the whole batch in one launch when its activations fit beside the ring, else in halves
     for (size_t cap = M; cap >= 1; cap = cap / 2) {
         GemvPlan p;

@@ -1,4 +1,5 @@
-// Small batches of activation rows against Q4_K weights on the integer tensor-core path (included by gemv.cu):
+// Small batches of activation rows against Q4_K (and, in the batch kernel, Q6_K) weights on the integer tensor-core path
+// (included by gemv.cu):
 // 3..8 rows of a decode batch, and the expert groups of the mixture-of-experts FFN (up to 32 rows per pass, every
 // expert and both of gate / up in ONE launch).  Same tiles, same ring of bulk-copied stages and same work split as
 // the single-row kernel; what changes is the inside of a step.
@@ -71,24 +72,127 @@ __device__ __forceinline__ bool batch_job_next(const BatchArgs &a, BatchJob &j) 
     return false;
 }
 
-// Shared-memory bytes of the activations of one pass: NT rows of K + 32 int8 (the pad spreads the eight tokens of a
-// load over the banks), then per row and super-block 16 bytes of block sums (low bytes, high bytes) and the scale.
-__host__ __device__ inline size_t batch_act_bytes(int NT, size_t K) { return (size_t)NT * (K + 32) + (size_t)NT * (K / 256) * 20; }
+// Shared-memory bytes of the activations of one pass: NT rows of K + pad int8 (the pad spreads the eight tokens of a
+// load over the banks: 32 bytes for the 8-byte loads of Q4_K, 16 for the 4-byte loads of Q6_K), then per row and
+// super-block the block sums as bytes (Q4_K: eight sums of 32, low bytes then high bytes; Q6_K: sixteen sums of 16,
+// low six bits then the rest) and the scale.
+__host__ __device__ constexpr int batch_pad(uint32_t type) { return type == OJAS_B200_Q6_K ? 16 : 32; }
+__host__ __device__ constexpr int batch_bs_bytes(uint32_t type) { return type == OJAS_B200_Q6_K ? 32 : 16; }
+__host__ __device__ inline size_t batch_act_bytes(uint32_t type, int NT, size_t K) {
+    return (size_t)NT * (K + batch_pad(type)) + (size_t)NT * (K / 256) * (batch_bs_bytes(type) + 4);
+}
 
+// Q6_K step of the batch kernel (dot_q6k, crates/ojas-cpu/src/cpu_math.rs:674-722): a sub-block is 16 weights, so the
+// MMA is m16n8k16 (A = 16 rows x 16 six-bit values as bytes, B = 16 int8 x 8 tokens) and every accumulator is the
+// exact int32 dot of one sub-block for 16 rows x 8 tokens; its int8 scale is applied by an integer multiply-add.  Lane
+// (g, q) supplies weights 4q .. 4q+3 of the sub-block: the low or high nibbles of FOUR CONTIGUOUS bytes of row g's
+// chunk piece, OR-ed with two bits of the same four bytes of the chunk's top-bit piece.  The -32 of every weight is
+// sum_j sc_j * (-32 * xsum_j): two more MMAs per super-block (A = the sixteen scales, B = the tokens' sums of 16,
+// low six bits and the rest).
+__device__ __forceinline__ void mma_k16_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b), "r"(0));
+}
+__device__ __forceinline__ void mma_k16_s8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b), "r"(0));
+}
+__device__ __forceinline__ int sext_byte(uint32_t w, int i) {   // byte i (a compile-time constant after unrolling) as a signed int
+    return (int)(signed char)(w >> (8 * i));
+}
+
+// One 16-row tile (u0 / u1: its two 8-row weight tiles in the stage) x one super-block x up to NTILE token tiles.
 template <int NTILE>
-__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_q4k_batch_kernel(const BatchArgs a) {
-    constexpr int NT = 8 * NTILE, TB = tile_bytes(OJAS_B200_Q4_K), STEP = 4 * TB;
+__device__ __forceinline__ void q6k_tile_step(const uint8_t *u0, const uint8_t *u1, bool second, const uint8_t *xq, int xstride, const uint8_t *bsb,
+                                              const float *sx, int nsbseg, int sbl, int g8, int q4, int ntile, float (&acc)[NTILE][4]) {
+    const uint8_t *t0 = u0 + g8 * 16 + 4 * q4, *t1 = u1 + g8 * 16 + 4 * q4;   // this lane's four bytes of every piece
+    const uint4 S0 = *reinterpret_cast<const uint4 *>(u0 + 12 * 128 + g8 * 16), S1 = *reinterpret_cast<const uint4 *>(u1 + 12 * 128 + g8 * 16);
+    const uint32_t sw0[4] = {S0.x, S0.y, S0.z, S0.w}, sw1[4] = {S1.x, S1.y, S1.z, S1.w};
+    int isum[NTILE][4];
+#pragma unroll
+    for (int t = 0; t < NTILE; t++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) isum[t][i] = 0;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint32_t la0 = *reinterpret_cast<const uint32_t *>(t0 + c * 128), lb0 = *reinterpret_cast<const uint32_t *>(t0 + (4 + c) * 128);
+        const uint32_t h0 = *reinterpret_cast<const uint32_t *>(t0 + (8 + c) * 128);
+        uint32_t la1 = *reinterpret_cast<const uint32_t *>(t1 + c * 128), lb1 = *reinterpret_cast<const uint32_t *>(t1 + (4 + c) * 128);
+        uint32_t h1 = *reinterpret_cast<const uint32_t *>(t1 + (8 + c) * 128);
+        if (!second) { la1 = 0u; lb1 = 0u; h1 = 0u; }
+        // sub-block 4c + f: f = 0 low nibbles of piece c, 1 low nibbles of piece 4 + c, 2 / 3 their high nibbles; top bits = field f
+        const uint32_t A0[4] = {(la0 & 0x0f0f0f0fu) | ((h0 << 4) & 0x30303030u), (lb0 & 0x0f0f0f0fu) | ((h0 << 2) & 0x30303030u),
+                                ((la0 >> 4) & 0x0f0f0f0fu) | (h0 & 0x30303030u), ((lb0 >> 4) & 0x0f0f0f0fu) | ((h0 >> 2) & 0x30303030u)};
+        const uint32_t A1[4] = {(la1 & 0x0f0f0f0fu) | ((h1 << 4) & 0x30303030u), (lb1 & 0x0f0f0f0fu) | ((h1 << 2) & 0x30303030u),
+                                ((la1 >> 4) & 0x0f0f0f0fu) | (h1 & 0x30303030u), ((lb1 >> 4) & 0x0f0f0f0fu) | ((h1 >> 2) & 0x30303030u)};
+#pragma unroll
+        for (int f = 0; f < 4; f++) {
+            const int s0 = sext_byte(sw0[c], f), s1 = sext_byte(sw1[c], f);
+#pragma unroll
+            for (int t = 0; t < NTILE; t++) {
+                if (t < ntile) {
+                    const uint32_t b = *reinterpret_cast<const uint32_t *>(xq + (size_t)(t * 8 + g8) * xstride + sbl * 256 + 64 * c + 16 * f + 4 * q4);
+                    int d[4];
+                    mma_k16_u8s8(d, A0[f], A1[f], b);
+                    isum[t][0] += s0 * d[0];
+                    isum[t][1] += s0 * d[1];
+                    isum[t][2] += s1 * d[2];
+                    isum[t][3] += s1 * d[3];
+                }
+            }
+        }
+    }
+    // the -32 term: scales of the two rows (lane q holds scales 4q .. 4q+3) against the tokens' sums of 16
+    const uint32_t as0 = *reinterpret_cast<const uint32_t *>(u0 + 12 * 128 + g8 * 16 + 4 * q4);
+    const uint32_t as1 = second ? *reinterpret_cast<const uint32_t *>(u1 + 12 * 128 + g8 * 16 + 4 * q4) : 0u;
+    const float d0 = f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(u0 + 13 * 128 + 2 * g8));
+    const float d1 = second ? f16_bits_to_f32(*reinterpret_cast<const unsigned short *>(u1 + 13 * 128 + 2 * g8)) : 0.0f;
+#pragma unroll
+    for (int t = 0; t < NTILE; t++) {
+        if (t < ntile) {
+            const uint8_t *bp = bsb + ((size_t)(t * 8 + g8) * nsbseg + sbl) * 32 + 4 * q4;
+            int ml[4], mh[4];
+            mma_k16_s8s8(ml, as0, as1, *reinterpret_cast<const uint32_t *>(bp));
+            mma_k16_s8s8(mh, as0, as1, *reinterpret_cast<const uint32_t *>(bp + 16));
+            const float sx0 = sx[(t * 8 + 2 * q4) * nsbseg + sbl], sx1 = sx[(t * 8 + 2 * q4 + 1) * nsbseg + sbl];
+            acc[t][0] += (sx0 * d0) * (float)(isum[t][0] - 32 * (ml[0] + 64 * mh[0]));
+            acc[t][1] += (sx1 * d0) * (float)(isum[t][1] - 32 * (ml[1] + 64 * mh[1]));
+            acc[t][2] += (sx0 * d1) * (float)(isum[t][2] - 32 * (ml[2] + 64 * mh[2]));
+            acc[t][3] += (sx1 * d1) * (float)(isum[t][3] - 32 * (ml[3] + 64 * mh[3]));
+        }
+    }
+}
+
+// The batch kernel's step: the stage's 32 rows as two 16-row tiles.
+template <int NTILE>
+__device__ __forceinline__ void batch_step_q6k(const uint8_t *st, int g, int nu, const uint8_t *xq, int Kpad, const uint8_t *bsb, const float *sx,
+                                               int nsb, int sb, int g8, int q4, float (&acc)[2][NTILE][4]) {
+    constexpr int TB = tile_bytes(OJAS_B200_Q6_K);
+#pragma unroll
+    for (int rt = 0; rt < 2; rt++) {
+        if (4 * g + 2 * rt >= nu) continue;                         // no unit under this row tile
+        const bool second = 4 * g + 2 * rt + 1 < nu;                // the tile's rows 8..15 exist
+        const uint8_t *u0 = st + (2 * rt) * TB;
+        q6k_tile_step<NTILE>(u0, second ? u0 + TB : u0, second, xq, Kpad, bsb, sx, nsb, sb, g8, q4, NTILE, acc[rt]);
+    }
+}
+
+template <int TYPE, int NTILE>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kq_batch_kernel(const BatchArgs a) {
+    constexpr int NT = 8 * NTILE, TB = tile_bytes(TYPE), STEP = 4 * TB, BSB = batch_bs_bytes(TYPE);
     extern __shared__ __align__(128) unsigned char smem[];
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g8 = lane >> 2, q4 = lane & 3;
-    const int nsb = a.nsb, P = a.P, K = a.K, Kpad = K + 32;
+    const int nsb = a.nsb, P = a.P, K = a.K, Kpad = K + batch_pad(TYPE);
     const int nst = 1 << a.nst_log, S = 1 << a.S_log, T = 1 << a.T_log;
     uint8_t *ring = smem + (size_t)warp * nst * STEP;
     uint8_t *xq = smem + (size_t)warps * nst * STEP;               // [NT][Kpad]
-    uint8_t *bsb = xq + (size_t)NT * Kpad;                         // [NT][nsb][16]
-    float *sx = reinterpret_cast<float *>(bsb + (size_t)NT * nsb * 16);   // [NT][nsb]
-    uint64_t *bar = reinterpret_cast<uint64_t *>(xq + ((batch_act_bytes(NT, (size_t)K) + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
-    float *part = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(xq + ((batch_act_bytes(NT, (size_t)K) + 15) & ~(size_t)15)) +
+    uint8_t *bsb = xq + (size_t)NT * Kpad;                         // [NT][nsb][BSB]
+    float *sx = reinterpret_cast<float *>(bsb + (size_t)NT * nsb * BSB);  // [NT][nsb]
+    uint64_t *bar = reinterpret_cast<uint64_t *>(xq + ((batch_act_bytes(TYPE, NT, (size_t)K) + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
+    float *part = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(xq + ((batch_act_bytes(TYPE, NT, (size_t)K) + 15) & ~(size_t)15)) +
                                             GEMV_MAX_WARPS * GEMV_MAX_STAGES);
 
     const int b = blockIdx.x;
@@ -152,17 +256,31 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_q4k_batch_kernel(
                     const int pos = jc.off + jc.mb + m;
                     const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
                     const uint4 *qsrc = reinterpret_cast<const uint4 *>(a.q + (size_t)srow * K);
-                    for (int un = threadIdx.x; un < units; un += blockDim.x) dst[un] = __ldg(qsrc + un);
-                    for (int i = threadIdx.x; i < nsb * 8; i += blockDim.x) {
-                        const int t = __ldg(a.bsums + (size_t)srow * nsb * 8 + i);
-                        uint8_t *o = bsb + ((size_t)m * nsb + (i >> 3)) * 16;
-                        o[i & 7] = (uint8_t)(t & 63);
-                        o[8 + (i & 7)] = (uint8_t)((t >> 6) & 0xff);
+                    for (int un = threadIdx.x; un < units; un += blockDim.x) {
+                        const uint4 v = __ldg(qsrc + un);
+                        dst[un] = v;
+                        if (TYPE == OJAS_B200_Q6_K) {               // the sum of this unit's sixteen values
+                            int t = __dp4a((int)v.x, 0x01010101, 0);
+                            t = __dp4a((int)v.y, 0x01010101, t);
+                            t = __dp4a((int)v.z, 0x01010101, t);
+                            t = __dp4a((int)v.w, 0x01010101, t);
+                            uint8_t *o = bsb + ((size_t)m * nsb + (un >> 4)) * 32;
+                            o[un & 15] = (uint8_t)(t & 63);
+                            o[16 + (un & 15)] = (uint8_t)((t >> 6) & 0xff);
+                        }
+                    }
+                    if (TYPE != OJAS_B200_Q6_K) {
+                        for (int i = threadIdx.x; i < nsb * 8; i += blockDim.x) {
+                            const int t = __ldg(a.bsums + (size_t)srow * nsb * 8 + i);
+                            uint8_t *o = bsb + ((size_t)m * nsb + (i >> 3)) * 16;
+                            o[i & 7] = (uint8_t)(t & 63);
+                            o[8 + (i & 7)] = (uint8_t)((t >> 6) & 0xff);
+                        }
                     }
                     for (int sb = threadIdx.x; sb < nsb; sb += blockDim.x) sx[m * nsb + sb] = __ldg(a.scales + (size_t)srow * nsb + sb);
                 } else {
                     for (int un = threadIdx.x; un < units; un += blockDim.x) dst[un] = make_uint4(0u, 0u, 0u, 0u);
-                    for (int i = threadIdx.x; i < nsb * 4; i += blockDim.x) reinterpret_cast<uint32_t *>(bsb + (size_t)m * nsb * 16)[i] = 0u;
+                    for (int i = threadIdx.x; i < nsb * (BSB / 4); i += blockDim.x) reinterpret_cast<uint32_t *>(bsb + (size_t)m * nsb * BSB)[i] = 0u;
                     for (int sb = threadIdx.x; sb < nsb; sb += blockDim.x) sx[m * nsb + sb] = 0.0f;
                 }
             }
@@ -184,6 +302,8 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_q4k_batch_kernel(
             const int g = team + k * T;
             gv_bar_wait(bar + stg, (uses >> a.nst_log) & 1u, a.status, dead);
             const uint8_t *st = ring + stg * STEP;
+            if (TYPE == OJAS_B200_Q6_K) batch_step_q6k<NTILE>(st, g, nu, xq, Kpad, bsb, sx, nsb, sb, g8, q4, acc);
+            else
 #pragma unroll
             for (int rt = 0; rt < 2; rt++) {
                 if (4 * g + 2 * rt >= nu) continue;                 // no unit under this row tile (rows past the CTA's range)
@@ -315,9 +435,8 @@ struct ExpertArgs {
     int E, K, N, nsb, nst;
 };
 
-__host__ __device__ inline size_t expert_act_bytes(int NT, size_t K) {
-    const size_t kseg = K < (size_t)EXPERT_KSEG ? K : (size_t)EXPERT_KSEG;
-    return (size_t)NT * (kseg + 32) + (size_t)NT * (kseg / 256) * 20;
+__host__ __device__ inline size_t expert_act_bytes(uint32_t type, int NT, size_t K) {
+    return batch_act_bytes(type, NT, K < (size_t)EXPERT_KSEG ? K : (size_t)EXPERT_KSEG);
 }
 
 // One 16-row tile x one super-block x up to NTILE token tiles.  t0 / t1: this lane's row (g8) in the tile's two
@@ -380,22 +499,22 @@ __device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *
     }
 }
 
-template <int NTILE>
-__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_q4k_experts_kernel(const ExpertArgs a) {
-    constexpr int NT = 8 * NTILE, TB = tile_bytes(OJAS_B200_Q4_K), STEP = 2 * TB;
+template <int TYPE, int NTILE>
+__global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_kq_experts_kernel(const ExpertArgs a) {
+    constexpr int NT = 8 * NTILE, TB = tile_bytes(TYPE), STEP = 2 * TB, BSB = batch_bs_bytes(TYPE);
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int act_e[EXPERT_MAX_E], act_n;                    // experts that have rows, in order
     __shared__ unsigned share[2];                                 // this CTA's range of the tile list
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g8 = lane >> 2, q4 = lane & 3;
     const int nsb = a.nsb, K = a.K, nst = a.nst;
-    const int kseg = K < EXPERT_KSEG ? K : EXPERT_KSEG, nsbseg = kseg >> 8, xstride = kseg + 32;
+    const int kseg = K < EXPERT_KSEG ? K : EXPERT_KSEG, nsbseg = kseg >> 8, xstride = kseg + batch_pad(TYPE);
     const int nseg = (K + kseg - 1) / kseg;
     uint8_t *ring = smem + (size_t)warp * nst * STEP;
     uint8_t *xq = smem + (size_t)warps * nst * STEP;
     uint8_t *bsb = xq + (size_t)NT * xstride;
-    float *sx = reinterpret_cast<float *>(bsb + (size_t)NT * nsbseg * 16);
-    uint64_t *bar = reinterpret_cast<uint64_t *>(xq + ((expert_act_bytes(NT, (size_t)K) + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
+    float *sx = reinterpret_cast<float *>(bsb + (size_t)NT * nsbseg * BSB);
+    uint64_t *bar = reinterpret_cast<uint64_t *>(xq + ((expert_act_bytes(TYPE, NT, (size_t)K) + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
 
     if (lane == 0) {
         for (int i = 0; i < nst; i++) gv_bar_init(bar + i);
@@ -518,8 +637,17 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_q4k_experts_kernel
                                 v = __ldg(reinterpret_cast<const uint4 *>(a.q + (size_t)srow * K + (size_t)sb0 * 256) + un);
                             }
                             reinterpret_cast<uint4 *>(xq + (size_t)m * xstride)[un] = v;
+                            if (TYPE == OJAS_B200_Q6_K) {           // the sum of this unit's sixteen values, as two bytes
+                                int t = __dp4a((int)v.x, 0x01010101, 0);
+                                t = __dp4a((int)v.y, 0x01010101, t);
+                                t = __dp4a((int)v.z, 0x01010101, t);
+                                t = __dp4a((int)v.w, 0x01010101, t);
+                                uint8_t *o = bsb + ((size_t)m * nsbseg + (un >> 4)) * 32;
+                                o[un & 15] = (uint8_t)(t & 63);
+                                o[16 + (un & 15)] = (uint8_t)((t >> 6) & 0xff);
+                            }
                         }
-                        for (int idx = threadIdx.x; idx < NT * nsb_here * 8; idx += blockDim.x) {
+                        for (int idx = threadIdx.x; TYPE != OJAS_B200_Q6_K && idx < NT * nsb_here * 8; idx += blockDim.x) {
                             const int m = idx / (nsb_here * 8), i = idx - m * (nsb_here * 8);
                             int t = 0;
                             if (m < m_here) {
@@ -546,8 +674,13 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_q4k_experts_kernel
                     if (mine) {
                         for (int sbl = 0; sbl < nsb_here; sbl++) {
                             gv_bar_wait(bar + cstg, cphase, a.status, dead);
-                            const uint8_t *t0 = ring + cstg * STEP + g8 * 16, *t1 = second ? t0 + TB : t0;
-                            mma_tile_step<NTILE>(t0, t1, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
+                            if (TYPE == OJAS_B200_Q6_K) {
+                                const uint8_t *u0 = ring + cstg * STEP;
+                                q6k_tile_step<NTILE>(u0, second ? u0 + TB : u0, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
+                            } else {
+                                const uint8_t *t0 = ring + cstg * STEP + g8 * 16, *t1 = second ? t0 + TB : t0;
+                                mma_tile_step<NTILE>(t0, t1, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
+                            }
                             __syncwarp();
                             if (lane == 0) {
                                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

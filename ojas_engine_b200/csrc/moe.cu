@@ -267,9 +267,13 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         // one launch of the mma.sync experts kernel over every expert and both tensors (Q4_K); otherwise one grouped
         // launch per expert and tensor
         rc = 1;
-        if (type_gu == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
-            rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts, w.offsets, E, d, ffn,
-                                       (A + E - 1) / E);
+        if ((type_gu == OJAS_B200_Q4_K || type_gu == OJAS_B200_Q6_K) && ctx->gemv_mma != 0) {
+            rc = ojas_gemv_experts_kq(ctx, type_gu, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts, w.offsets, E, d,
+                                      ffn, (A + E - 1) / E);
+            if (rc == 1)
+                rc = ojas_gemv_experts_batch(ctx, type_gu, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts,
+                                             w.offsets, E, d, ffn, (A + E - 1) / E);
+        }
         if (rc < 0) return rc;
         for (size_t e = 0; rc == 1 && e < E; e++) {   // gate and up of expert e over its tokens (gathered rows of h)
             int r2 = ojas_gemv_grouped(ctx, type_gu, weight_rows_at(type_gu, wg, d, e * ffn), w.xq, w.xs, w.xb, w.tok,
@@ -318,9 +322,13 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         return 0;
     }
     rc = 1;
-    if (type_d == OJAS_B200_Q4_K && ctx->gemv_mma != 0)
-        rc = ojas_gemv_experts_q4k(ctx, (const uint8_t *)wd, nullptr, w.yd, nullptr, w.aq, w.as, w.ab, nullptr, w.counts, w.offsets, E, ffn, d,
-                                   (A + E - 1) / E);
+    if ((type_d == OJAS_B200_Q4_K || type_d == OJAS_B200_Q6_K) && ctx->gemv_mma != 0) {
+        rc = ojas_gemv_experts_kq(ctx, type_d, (const uint8_t *)wd, nullptr, w.yd, nullptr, w.aq, w.as, w.ab, nullptr, w.counts, w.offsets, E, ffn, d,
+                                  (A + E - 1) / E);
+        if (rc == 1)
+            rc = ojas_gemv_experts_batch(ctx, type_d, (const uint8_t *)wd, nullptr, w.yd, nullptr, w.aq, w.as, w.ab, nullptr, w.counts, w.offsets, E,
+                                         ffn, d, (A + E - 1) / E);
+    }
     if (rc < 0) return rc;
     for (size_t e = 0; rc == 1 && e < E; e++) {   // down of expert e over its (contiguous, sorted) rows
         const int r2 = ojas_gemv_grouped(ctx, type_d, weight_rows_at(type_d, wd, ffn, e * d), w.aq, w.as, w.ab, nullptr,

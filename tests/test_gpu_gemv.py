@@ -139,6 +139,21 @@ def test_store_forms(gpu, tag, form):
     _gemv_case(gpu, tag, 130, 512, 4, form=form)
 
 
+@pytest.mark.parametrize("segments", [0, 2, 4, 7])
+def test_q80_batches_over_k_segments(gpu, segments):
+    """Q8_0 batches of 3..8 rows walk a long K in equal segments inside one launch (their activations do not fit in
+    shared memory whole): automatic on K = 14336, forced on shorter rows; every store form; a segment count that
+    does not divide K / 256 falls back to the other path."""
+    gpu.set_option("gemv_kseg", segments)
+    try:
+        for n, k, m, form in [(150, 14336, 8, PLAIN), (1000, 14336, 3, BIAS), (37, 14336, 5, ACCUM), (300, 3584, 8, PLAIN),
+                              (4096, 7168, 6, ACCUM), (33, 1024, 4, BIAS)]:
+            err = _gemv_case(gpu, "q80", n, k, m, form=form, seed=m + segments)
+            assert err < 1e-5
+    finally:
+        gpu.set_option("gemv_kseg", 0)
+
+
 @pytest.mark.parametrize("tag", ["q4k", "q6k"])
 def test_prequantized_activations_match(gpu, tag):
     """gemv_q8k over quant_q8k's output gives bit-identical results to the fused call."""
