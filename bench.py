@@ -479,7 +479,7 @@ def run_ours(args) -> None:
                                           (ob.Q6_K, 14336, 4096, 1, "q6k"), (ob.Q6_K, 4096, 14336, 1, "q6k"),
                                           (ob.Q8_0, 14336, 4096, 1, "q80"), (ob.Q8_0, 4096, 14336, 1, "q80"),
                                           (ob.Q4_K, 4096, 4096, 8, "q4k"), (ob.Q6_K, 14336, 4096, 8, "q6k"),
-                                          (ob.Q8_0, 14336, 4096, 8, "q80")]:
+                                          (ob.Q8_0, 14336, 4096, 8, "q80"), (ob.Q8_0, 4096, 14336, 8, "q80")]:
                     try:
                         extras.append(extra_gemv(gpu, ob, t, n, k, m, hbm_peak, tag))
                     except Exception as exc:  # an extra must not take the headline down
@@ -497,9 +497,10 @@ def run_ours(args) -> None:
                     extras.append(decode_layer_case(gpu, ob, hbm_peak))
                 except Exception as exc:
                     extras.append({"workload": "decode_layer", "error": str(exc)})
-                for tokens, rows in ((64, 0), (2048, 32)):      # config 3 as stated; a prefill-sized batch in the prefill form
+                # config 4 as stated; the same with Q6_K experts; a prefill-sized batch in the prefill form
+                for tokens, rows, t_exp in ((64, 0, ob.Q4_K), (64, 0, ob.Q6_K), (2048, 32, ob.Q4_K)):
                     try:
-                        extras.append(moe_case(gpu, ob, 5, 2, hbm_peak, tc_peak, tokens, rows))
+                        extras.append(moe_case(gpu, ob, 20, 3, hbm_peak, tc_peak, tokens, rows, t_exp))
                     except Exception as exc:
                         extras.append({"workload": f"moe_m{tokens}", "error": str(exc)})
         traffic = profile_traffic()
@@ -544,9 +545,9 @@ def run_case(args) -> None:
         gpu = ob.B200Gpu(0)
         for kv in args.opt:
             gpu.set_option(kv.split("=")[0], int(kv.split("=")[1]))
-        parts = args.case.split(":")          # moe[:TOKENS[:GEMM_ROWS]]
+        parts = args.case.split(":")          # moe[:TOKENS[:GEMM_ROWS[:q4k|q6k]]]
         print(json.dumps(moe_case(gpu, ob, args.steps, args.warmup, hbm_peak, tc_peak, int(parts[1]) if len(parts) > 1 else 64,
-                                  int(parts[2]) if len(parts) > 2 else 0)))
+                                  int(parts[2]) if len(parts) > 2 else 0, ob.Q6_K if len(parts) > 3 and parts[3] == "q6k" else ob.Q4_K)))
         gpu.close()
         return
     tag, n, k, m = args.case.split(":")
@@ -630,16 +631,17 @@ def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int
             "frac_of_peak": round(tf / tc_peak, 4), "ksplit": ksplit or "auto"}
 
 
-def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, tokens: int = 64, gemm_rows: int = 0) -> dict:
-    """Mixtral-like expert FFN: 8 experts (gate/up 14336 x 4096, down 4096 x 14336, Q4_K), `tokens` tokens, top-2.
-    gemm_rows > 0 turns on the grouped tensor-core GEMM form from that many rows per expert (option moe_gemm_rows)."""
+def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, tokens: int = 64, gemm_rows: int = 0, t_exp: int = 12) -> dict:
+    """Mixtral-like expert FFN: 8 experts (gate/up 14336 x 4096, down 4096 x 14336; Q4_K, or Q6_K with t_exp = 14),
+    `tokens` tokens, top-2.  gemm_rows > 0 turns on the grouped tensor-core GEMM form from that many rows per expert
+    (option moe_gemm_rows)."""
     import oracle
     e, d, ffn, m, ksel = 8, 4096, 14336, tokens, 2
     gpu.set_option("moe_gemm_rows", gemm_rows)
     rng = np.random.default_rng(0)
-    mk = lambda n, k: oracle.synth_blocks(ob.Q4_K, e * n * k // 256)
-    wg, wu, wd = (gpu.load_weight(mk(ffn, d), ob.Q4_K, e * ffn, d), gpu.load_weight(mk(ffn, d), ob.Q4_K, e * ffn, d),
-                  gpu.load_weight(mk(d, ffn), ob.Q4_K, e * d, ffn))
+    mk = lambda n, k: oracle.synth_blocks(t_exp, e * n * k // 256)
+    wg, wu, wd = (gpu.load_weight(mk(ffn, d), t_exp, e * ffn, d), gpu.load_weight(mk(ffn, d), t_exp, e * ffn, d),
+                  gpu.load_weight(mk(d, ffn), t_exp, e * d, ffn))
     h = gpu.upload(rng.standard_normal((m, d), dtype=np.float32) * np.float32(1e-3))
     lg = gpu.upload(rng.standard_normal((m, e), dtype=np.float32))
     idx, wgt, out = gpu.alloc_bytes(m * ksel * 4), gpu.alloc(m * ksel), gpu.alloc(m * d)
@@ -659,12 +661,13 @@ def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, 
     gpu.record(e1)
     gpu.sync()
     us = gpu.elapsed_ms(e0, e1) * 1e3 / steps
-    gguf = 3 * ob.raw_bytes(ob.Q4_K, e * ffn, d)
+    gguf = 3 * ob.raw_bytes(t_exp, e * ffn, d)
     flops = 2.0 * m * ksel * 3 * ffn * d
+    tag = {ob.Q4_K: "q4k", ob.Q6_K: "q6k"}.get(t_exp, str(t_exp))
     for b in (wg.buf, wu.buf, wd.buf, h, lg, idx, wgt, out, work):
         gpu.free(b)
     gpu.set_option("moe_gemm_rows", 0)
-    return {"workload": f"moe_q4k_e8_top2_m{m}_d4096_ffn14336" + ("_prefill_form" if gemm_rows else ""), "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
+    return {"workload": f"moe_{tag}_e8_top2_m{m}_d4096_ffn14336" + ("_prefill_form" if gemm_rows else ""), "us_per_call": round(us, 1), "GB/s": round(gguf / us / 1e3, 1),
             "frac_of_hbm_peak": round(gguf / us / 1e3 / hbm_peak, 4), "TFLOP/s": round(flops / us / 1e6, 2),
             "frac_of_tensor_peak": round(flops / us / 1e6 / tc_peak, 5), "expert_bytes": gguf}
 
