@@ -599,8 +599,9 @@ def run_case(args) -> None:
     gpu.close()
 
 
-def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int, tc_peak: float, ksplit: int = 0) -> dict:
-    """Times the tensor-core prefill GEMM (activation preparation + MMA kernel per call)."""
+def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int, tc_peak: float, ksplit: int = 0, graph: bool = True) -> dict:
+    """Times the tensor-core prefill GEMM (activation preparation + MMA kernel per call), by default as replays of a
+    CUDA graph over a ring of weights (graph = False: eager launches, for captures under a profiler)."""
     import oracle
     t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
     base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
@@ -615,12 +616,30 @@ def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int
         gpu.gemm(ws[i % ring], x, y, m, workspace=work)
     gpu.sync()
     e0, e1 = gpu.event(), gpu.event()
-    gpu.record(e0)
-    for i in range(steps):
-        gpu.gemm(ws[i % ring], x, y, m, workspace=work)
-    gpu.record(e1)
-    gpu.sync()
-    us = gpu.elapsed_ms(e0, e1) * 1e3 / steps
+    if graph:
+        # one CUDA graph over the ring of weights, replayed: the device time of a call, not the host's launch path
+        per = min(ring, 8)
+        gpu.graph_begin()
+        for i in range(per):
+            gpu.gemm(ws[i % ring], x, y, m, workspace=work)
+        g = gpu.graph_end()
+        reps = max(1, (steps + per - 1) // per)
+        gpu.graph_launch(g)
+        gpu.sync()
+        gpu.record(e0)
+        for _ in range(reps):
+            gpu.graph_launch(g)
+        gpu.record(e1)
+        gpu.sync()
+        us = gpu.elapsed_ms(e0, e1) * 1e3 / (reps * per)
+        gpu.graph_destroy(g)
+    else:
+        gpu.record(e0)
+        for i in range(steps):
+            gpu.gemm(ws[i % ring], x, y, m, workspace=work)
+        gpu.record(e1)
+        gpu.sync()
+        us = gpu.elapsed_ms(e0, e1) * 1e3 / steps
     gpu.set_option("gemm_ksplit", 0)
     for w in ws:
         gpu.free(w.buf)
@@ -628,7 +647,7 @@ def gemm_case(gpu, ob, tag: str, m: int, n: int, k: int, steps: int, warmup: int
         gpu.free(b)
     tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
     return {"workload": f"{tag}_gemm_m{m}_n{n}_k{k}", "us_per_call": round(us, 2), "TFLOP/s": round(tf, 1),
-            "frac_of_peak": round(tf / tc_peak, 4), "ksplit": ksplit or "auto"}
+            "frac_of_peak": round(tf / tc_peak, 4), "ksplit": ksplit or "auto", "launch": "CUDA graph replay" if graph else "eager"}
 
 
 def moe_case(gpu, ob, steps: int, warmup: int, hbm_peak: float, tc_peak: float, tokens: int = 64, gemm_rows: int = 0, t_exp: int = 12) -> dict:
@@ -798,7 +817,7 @@ def run_gemm_case(args) -> None:
     _, tag, m, n, k = args.case.split(":")
     _, tc_peak, peak_kind = measured_peaks()
     gpu = ob.B200Gpu(0)
-    out = gemm_case(gpu, ob, tag, int(m), int(n), int(k), args.steps, args.warmup, tc_peak, args.ksplit)
+    out = gemm_case(gpu, ob, tag, int(m), int(n), int(k), args.steps, args.warmup, tc_peak, args.ksplit, graph=not args.no_graph)
     out["peak_kind"] = peak_kind
     print(json.dumps(out))
     gpu.close()

@@ -45,6 +45,13 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], const uint32_t (&a)[4], ui
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator input (no registers to clear before the MMA).
+__device__ __forceinline__ void mma_u8s8_z(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+}
+
 struct BatchJob {
     int e, mb, wsel;              // expert, first row of the pass inside the expert's group, weight tensor
     int count, off;               // rows of the expert and position of its first row
@@ -334,9 +341,9 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kq_batch_kernel(c
                     for (int t = 0; t < NTILE; t++) {
                         const uint8_t *xr = xq + (size_t)(t * 8 + g8) * Kpad + sb * 256 + 64 * c + 8 * q4;
                         const uint2 xa = *reinterpret_cast<const uint2 *>(xr), xb = *reinterpret_cast<const uint2 *>(xr + 32);
-                        int dlo[4] = {0, 0, 0, 0}, dhi[4] = {0, 0, 0, 0};
-                        mma_u8s8(dlo, alo, xa.x, xa.y);
-                        mma_u8s8(dhi, ahi, xb.x, xb.y);
+                        int dlo[4], dhi[4];
+                        mma_u8s8_z(dlo, alo, xa.x, xa.y);
+                        mma_u8s8_z(dhi, ahi, xb.x, xb.y);
                         isum[t][0] += sA0 * dlo[0] + sB0 * (dhi[0] >> 4);
                         isum[t][1] += sA0 * dlo[1] + sB0 * (dhi[1] >> 4);
                         isum[t][2] += sA1 * dlo[2] + sB1 * (dhi[2] >> 4);
@@ -353,9 +360,9 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kq_batch_kernel(c
                     const uint8_t *bp = bsb + ((size_t)(t * 8 + g8) * nsb + sb) * 16;
                     const uint32_t blo = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 4 * q4) : 0u;
                     const uint32_t bhi = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 8 + 4 * q4) : 0u;
-                    int ml[4] = {0, 0, 0, 0}, mh[4] = {0, 0, 0, 0};
-                    mma_u8s8(ml, am, blo, 0u);
-                    mma_u8s8(mh, am, bhi, 0u);
+                    int ml[4], mh[4];
+                    mma_u8s8_z(ml, am, blo, 0u);
+                    mma_u8s8_z(mh, am, bhi, 0u);
                     const float sx0 = sx[(t * 8 + 2 * q4) * nsb + sb], sx1 = sx[(t * 8 + 2 * q4 + 1) * nsb + sb];
                     acc[rt][t][0] += sx0 * (d0 * (float)isum[t][0] - dm0 * (float)(ml[0] + 64 * mh[0]));
                     acc[rt][t][1] += sx1 * (d0 * (float)isum[t][1] - dm0 * (float)(ml[1] + 64 * mh[1]));
@@ -468,9 +475,9 @@ __device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *
             if (t < ntile) {
                 const uint8_t *xr = xq + (size_t)(t * 8 + g8) * xstride + sbl * 256 + 64 * c + 8 * q4;
                 const uint2 xa = *reinterpret_cast<const uint2 *>(xr), xb = *reinterpret_cast<const uint2 *>(xr + 32);
-                int dlo[4] = {0, 0, 0, 0}, dhi[4] = {0, 0, 0, 0};
-                mma_u8s8(dlo, alo, xa.x, xa.y);
-                mma_u8s8(dhi, ahi, xb.x, xb.y);
+                int dlo[4], dhi[4];
+                mma_u8s8_z(dlo, alo, xa.x, xa.y);
+                mma_u8s8_z(dhi, ahi, xb.x, xb.y);
                 isum[t][0] += sA0 * dlo[0] + sB0 * (dhi[0] >> 4);
                 isum[t][1] += sA0 * dlo[1] + sB0 * (dhi[1] >> 4);
                 isum[t][2] += sA1 * dlo[2] + sB1 * (dhi[2] >> 4);
@@ -487,9 +494,9 @@ __device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *
             const uint8_t *bp = bsb + ((size_t)(t * 8 + g8) * nsbseg + sbl) * 16;
             const uint32_t blo = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 4 * q4) : 0u;
             const uint32_t bhi = q4 < 2 ? *reinterpret_cast<const uint32_t *>(bp + 8 + 4 * q4) : 0u;
-            int ml[4] = {0, 0, 0, 0}, mh[4] = {0, 0, 0, 0};
-            mma_u8s8(ml, am, blo, 0u);
-            mma_u8s8(mh, am, bhi, 0u);
+            int ml[4], mh[4];
+            mma_u8s8_z(ml, am, blo, 0u);
+            mma_u8s8_z(mh, am, bhi, 0u);
             const float sx0 = sx[(t * 8 + 2 * q4) * nsbseg + sbl], sx1 = sx[(t * 8 + 2 * q4 + 1) * nsbseg + sbl];
             acc[t][0] += sx0 * (d0 * (float)isum[t][0] - dm0 * (float)(ml[0] + 64 * mh[0]));
             acc[t][1] += sx1 * (d0 * (float)isum[t][1] - dm0 * (float)(ml[1] + 64 * mh[1]));
