@@ -507,6 +507,59 @@ __device__ __forceinline__ void step_q80(const uint8_t *wl, const uint8_t *act, 
     }
 }
 
+// IQ4_XS (dot_iq4xs, crates/ojas-cpu/src/cpu_math.rs:943-967): the CPU takes f32 activations, so they enter as three int8
+// terms like Q8_0's; a weight is a 4-bit index into the sixteen int8 codebook values.  Four index bytes (eight weights)
+// are looked up with byte permutes: the two halves of the codebook are selected by the low three bits of every nibble
+// (__byte_perm ignores the fourth), a third permute picks between them by that fourth bit, and two more separate the
+// low nibbles (weights j .. j+3 of the group) from the high ones (weights j+16 .. j+19).  Per group of 32: three exact
+// integer dots, then d * (ls - 32) * s * (D1 + D2 / 254 + D3 / 254^2).
+__device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t &lo, uint32_t &hi) {
+    constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;   // the codebook, four values per word
+    const uint32_t a0 = __byte_perm(T0, T1, q), b0 = __byte_perm(T2, T3, q);
+    const uint32_t v0 = __byte_perm(a0, b0, 0x3210u + ((q & 0x8888u) >> 1));          // values of nibbles 0..3
+    const uint32_t qh = q >> 16;
+    const uint32_t a1 = __byte_perm(T0, T1, qh), b1 = __byte_perm(T2, T3, qh);
+    const uint32_t v1 = __byte_perm(a1, b1, 0x3210u + ((qh & 0x8888u) >> 1));         // values of nibbles 4..7
+    lo = __byte_perm(v0, v1, 0x6420u);
+    hi = __byte_perm(v0, v1, 0x7531u);
+}
+
+template <int MT>
+__device__ __forceinline__ void step_iq4xs(const uint8_t *wl, int r, const uint8_t *act, int K, int sb, float (&acc)[MT]) {
+    const uint2 H = *reinterpret_cast<const uint2 *>(wl - r * 16 + 8 * 128 + r * 8);      // d, scales_h | scales_l
+    const float d = f16_bits_to_f32(H.x);
+    const uint32_t sh = H.x >> 16, sl = H.y;
+    const size_t rb = q80_act_row_bytes((size_t)K);
+    constexpr float C1 = 1.0f / 254.0f;
+#pragma unroll
+    for (int g = 0; g < 8; g++) {
+        const uint4 Q = *reinterpret_cast<const uint4 *>(wl + g * 128);
+        uint32_t wv[8];                                          // weights 0..15 of the group, then 16..31
+        iq4_lookup8(Q.x, wv[0], wv[4]);
+        iq4_lookup8(Q.y, wv[1], wv[5]);
+        iq4_lookup8(Q.z, wv[2], wv[6]);
+        iq4_lookup8(Q.w, wv[3], wv[7]);
+        const int ls = (int)(((sl >> (4 * g)) & 0xFu) | (((sh >> (2 * g)) & 3u) << 4)) - 32;
+        const float dl = __fmul_rn(d, (float)ls);
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            const uint8_t *row = act + m * rb + (size_t)sb * 256 + g * 32;
+            int dot[3];
+#pragma unroll
+            for (int t = 0; t < 3; t++) {
+                const uint4 x0 = *reinterpret_cast<const uint4 *>(row + (size_t)t * K), x1 = *reinterpret_cast<const uint4 *>(row + (size_t)t * K + 16);
+                int v = __dp4a((int)wv[0], (int)x0.x, 0);
+                v = __dp4a((int)wv[1], (int)x0.y, v); v = __dp4a((int)wv[2], (int)x0.z, v); v = __dp4a((int)wv[3], (int)x0.w, v);
+                v = __dp4a((int)wv[4], (int)x1.x, v); v = __dp4a((int)wv[5], (int)x1.y, v); v = __dp4a((int)wv[6], (int)x1.z, v); v = __dp4a((int)wv[7], (int)x1.w, v);
+                dot[t] = v;
+            }
+            const float s = reinterpret_cast<const float *>(act + m * rb + 3 * (size_t)K)[sb * 8 + g];
+            const float f = fmaf(fmaf((float)dot[2], C1, (float)dot[1]), C1, (float)dot[0]);
+            acc[m] = fmaf(__fmul_rn(dl, s), f, acc[m]);
+        }
+    }
+}
+
 // Q8_0, eight activation rows: the same three integer dots per block on the tensor cores.  One warp step = 32 weight
 // rows = two 16-row MMA tiles; per block of 32 weights A = 16 rows x 32 int8 (rows g, g + 8 = row g of two 8-row
 // units), B = 8 activation rows x 32 int8 of one term: mma.sync.m16n8k32.s8.s8, exact int32.  acc[4 t + i] belongs to
@@ -563,7 +616,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
     const int nst = 1 << a.nst_log, S = 1 << a.S_log, T = 1 << a.T_log;   // powers of two: no divisions below
     uint8_t *ring = smem + (size_t)warp * nst * STEP;
     uint8_t *act = smem + (size_t)warps * nst * STEP;
-    const size_t act_bytes = TYPE == OJAS_B200_Q8_0 ? (size_t)MT * q80_act_row_bytes((size_t)a.K) : (size_t)MT * ActLayout<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE>::row_bytes(nsb);
+    const size_t act_bytes = f32_act_type(TYPE) ? (size_t)MT * q80_act_row_bytes((size_t)a.K) : (size_t)MT * ActLayout<f32_act_type(TYPE) ? OJAS_B200_Q4_K : TYPE>::row_bytes(nsb);
     uint64_t *bar = reinterpret_cast<uint64_t *>(act + ((act_bytes + 15) & ~(size_t)15)) + warp * GEMV_MAX_STAGES;
     float *part = reinterpret_cast<float *>(reinterpret_cast<uint64_t *>(act + ((act_bytes + 15) & ~(size_t)15)) + GEMV_MAX_WARPS * GEMV_MAX_STAGES);
 
@@ -611,8 +664,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
         for (int i = 0; i < nst && i < nsteps; i++) issue();
     }
     if (first_pass) grid_dependency_wait();                       // activations (and y for the accumulate form) come from the kernel before
-    if (TYPE == OJAS_B200_Q8_0) stage_q80<MT, PRO>(a, act, nsb, warps, sb0);
-    else stage_kquant<TYPE == OJAS_B200_Q8_0 ? OJAS_B200_Q4_K : TYPE, MT, PREQ, PRO>(a, act, nsb, warps);
+    if (f32_act_type(TYPE)) stage_q80<MT, PRO>(a, act, nsb, warps, TYPE == OJAS_B200_Q8_0 ? sb0 : 0);
+    else stage_kquant<f32_act_type(TYPE) ? OJAS_B200_Q4_K : TYPE, MT, PREQ, PRO>(a, act, nsb, warps);
     if (first_pass) grid_launch_dependents();
     const float alpha = a.alpha ? __ldg(a.alpha) : 1.0f;
     // tensor-parallel launches: the step in flight is the stamp and picks the half of the windows
@@ -640,6 +693,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q5_K) step_q4k<MT, DUMP, true>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q6_K) step_q6k<MT, DUMP>(wl + stg * STEP, r, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 16 : nullptr);
+            else if (TYPE == OJAS_B200_IQ4_XS) step_iq4xs<MT>(wl + stg * STEP, r, act, a.K, sb, acc);
             else step_q80<MT>(wl + stg * STEP, act, a.K, sb, acc);
         }
         __syncwarp();                                             // every lane has read the stage
@@ -769,7 +823,7 @@ struct GemvPlan {
 
 static size_t gemv_act_bytes(uint32_t type, int MT, size_t K) {
     const size_t nsb = K / 256;
-    if (type == OJAS_B200_Q8_0) return (size_t)MT * q80_act_row_bytes(K);
+    if (f32_act_type(type)) return (size_t)MT * q80_act_row_bytes(K);
     return (size_t)MT * (type == OJAS_B200_Q6_K ? ActLayout<OJAS_B200_Q6_K>::row_bytes((int)nsb) : ActLayout<OJAS_B200_Q4_K>::row_bytes((int)nsb));
 }
 
@@ -869,7 +923,7 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
     if (preq || dump) args.own_x = dump ? args.own_x : 0;
     // two CTAs per SM fit.  (Not for Q8_0 and not for pre-quantized rows: their bodies do not fit in 64 registers, and a
     // spilled value costs a cold round trip to memory in every launch: measured, 12 bytes of spills added 1 us.)
-    const bool two = p.smem <= (size_t)ctx->smem_optin / 2 - 1024 && type != OJAS_B200_Q8_0 && !(preq && type == OJAS_B200_Q4_K);
+    const bool two = p.smem <= (size_t)ctx->smem_optin / 2 - 1024 && !f32_act_type(type) && !(preq && type == OJAS_B200_Q4_K);
 #define GEMV_CASE(T, PQ, NAME)                                                                 \
     switch (MT) {                                                                              \
     case 1: return two ? launch_gemv(ctx, gemv_kernel<T, 1, PQ, false, 2>, args, p, NAME)      \
@@ -890,11 +944,13 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
             if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 1, "gemv_q4k_rmsnorm") }
             if (type == OJAS_B200_Q5_K) { GEMV_PRO_CASE(OJAS_B200_Q5_K, 1, "gemv_q5k_rmsnorm") }
             if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 1, "gemv_q6k_rmsnorm") }
+            if (type == OJAS_B200_IQ4_XS) { GEMV_PRO_CASE(OJAS_B200_IQ4_XS, 1, "gemv_iq4xs_rmsnorm") }
             GEMV_PRO_CASE(OJAS_B200_Q8_0, 1, "gemv_q80_rmsnorm")
         }
         if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 2, "gemv_q4k_silu_mul") }
         if (type == OJAS_B200_Q5_K) { GEMV_PRO_CASE(OJAS_B200_Q5_K, 2, "gemv_q5k_silu_mul") }
         if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 2, "gemv_q6k_silu_mul") }
+        if (type == OJAS_B200_IQ4_XS) { GEMV_PRO_CASE(OJAS_B200_IQ4_XS, 2, "gemv_iq4xs_silu_mul") }
         GEMV_PRO_CASE(OJAS_B200_Q8_0, 2, "gemv_q80_silu_mul")
 #undef GEMV_PRO_CASE
     }
@@ -913,6 +969,7 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
         if (preq) { GEMV_CASE(OJAS_B200_Q6_K, true, "gemv_q6k_q8k") }
         GEMV_CASE(OJAS_B200_Q6_K, false, "gemv_q6k")
     }
+    if (type == OJAS_B200_IQ4_XS) { GEMV_CASE(OJAS_B200_IQ4_XS, false, "gemv_iq4xs") }
     GEMV_CASE(OJAS_B200_Q8_0, false, "gemv_q80")
 #undef GEMV_CASE
 }
@@ -1088,7 +1145,7 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
 // itself (M * K / 256 warp tasks each).  From a few dozen tasks per warp on that prologue outweighs the
 // matrix, so the batch is quantized once into the context's scratch and the GEMV copies the result.
 static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs &args, size_t M) {
-    if (preq || type == OJAS_B200_Q8_0 || M < 2 || !ctx->act_scratch || args.norm_w || args.x2) return false;   // (a fused producer runs in the kernel's prologue)
+    if (preq || f32_act_type(type) || M < 2 || !ctx->act_scratch || args.norm_w || args.x2) return false;   // (a fused producer runs in the kernel's prologue)
     const size_t values = M * (size_t)args.K;
     if (values > OJAS_ACT_SCRATCH_VALUES) return false;
     if (values < 16384 && !((type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
@@ -1292,8 +1349,8 @@ extern "C" int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t type, int form, c
                                   size_t M) {
     int rc = gemv_check(ctx, type, form, w, y, bias, K, N, M);
     if (rc) return rc;
-    if (type == OJAS_B200_Q8_0)
-        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_q8k: Q8_0 rows meet f32 activations, not Q8_K blocks");
+    if (f32_act_type(type))
+        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_q8k: Q8_0 and IQ4_XS rows meet f32 activations, not Q8_K blocks");
     if (!q || !scales || !bsums) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_q8k: null activation pointer");
     if (((uintptr_t)q & 15) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_q8k: q must be 16-byte aligned");
     GemvArgs a{};
@@ -1307,7 +1364,7 @@ extern "C" int ojas_b200_gemv_idots(ojas_b200_ctx *ctx, uint32_t type, const flo
     float dummy;
     int rc = gemv_check(ctx, type, OJAS_B200_PLAIN, w, &dummy, nullptr, K, N, 1);
     if (rc) return rc;
-    if (type == OJAS_B200_Q8_0) return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_idots: Q8_0 has no integer block dots");
+    if (f32_act_type(type)) return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_idots: Q8_0 and IQ4_XS have no integer block dots");
     if (!x || !idots) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_idots: null pointer");
     GemvArgs a{};
     a.x = x; a.w = (const uint8_t *)w; a.idots = idots;

@@ -66,8 +66,15 @@ __host__ __device__ static inline void repack_q80_block(const uint8_t *src, uint
     }
 }
 
+// IQ4_XS: the 128 index bytes as eight pieces (piece g = sub-block g), then the block's eight header bytes per row.
+__host__ __device__ static inline void repack_iq4xs_block(const uint8_t *src, uint8_t *tile, int r) {
+    for (int p = 0; p < 8; p++)
+        for (int i = 0; i < 16; i++) tile_piece(tile, p, r)[i] = src[8 + p * 16 + i];
+    for (int i = 0; i < 8; i++) tile[8 * 128 + 8 * r + i] = src[i];
+}
+
 __host__ __device__ static inline size_t raw_sb_bytes(uint32_t type) {
-    return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : 272;
+    return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : type == OJAS_B200_IQ4_XS ? 136 : 272;
 }
 
 // Block `blk` = (row n, super-block s) in row-major order of the GGUF tensor.
@@ -79,6 +86,7 @@ __host__ __device__ static inline void repack_one(uint32_t type, const uint8_t *
     if (type == OJAS_B200_Q4_K) repack_q4k_block(src, tile, r);
     else if (type == OJAS_B200_Q5_K) repack_q5k_block(src, tile, r);
     else if (type == OJAS_B200_Q6_K) repack_q6k_block(src, tile, r);
+    else if (type == OJAS_B200_IQ4_XS) repack_iq4xs_block(src, tile, r);
     else repack_q80_block(src, tile, r);
 }
 

@@ -91,13 +91,14 @@ static inline float rdh(const uint8_t *b, size_t i) {
 }
 
 /* ---------------------------------------------------------------- block shapes
- * crates/ojas-formats/src/synth.rs:12-21 (the formats on the path: Q8_0, Q4_K, Q5_K, Q6_K). */
+ * crates/ojas-formats/src/synth.rs:12-21 (the formats on the path: Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS). */
 ORC_API int orc_block_shape(uint32_t type, uint32_t *block_bytes, uint32_t *block_weights) {
     switch (type) {
     case 8:  *block_bytes = 34;  *block_weights = 32;  return 0;
     case 12: *block_bytes = 144; *block_weights = 256; return 0;
     case 13: *block_bytes = 176; *block_weights = 256; return 0;
     case 14: *block_bytes = 210; *block_weights = 256; return 0;
+    case 23: *block_bytes = 136; *block_weights = 256; return 0;
     default: return -1;
     }
 }
@@ -136,6 +137,12 @@ static inline void scale_min_k4(int j, const uint8_t *s, float *sc, float *mn) {
         *mn = (float)m;
     }
 }
+
+/* The 16-entry non-linear codebook of IQ4_NL / IQ4_XS.  The reference reads it as crate::iq_tables::KVALUES_IQ4NL
+ * (crates/ojas-formats/src/gguf.rs:832, crates/ojas-cpu/src/cpu_math.rs:859); the file that defines it is not part of
+ * the reference tree, so the values are ggml's published kvalues_iq4nl.  They are pinned by the reference's own decode
+ * digest of synthetic IQ4_XS blocks (crates/ojas-formats/tests/quant_formats.rs:48): a wrong entry changes the digest. */
+static const int8_t orc_kvalues_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
 /* Decode `n` weights of GGUF `type` to f32 (before the f16 rounding of
  * dequant_to_f16).  Same arithmetic order as crates/ojas-formats/src/gguf.rs:
@@ -200,6 +207,20 @@ ORC_API int orc_dequant_f32(const uint8_t *b, uint32_t type, size_t n, float *ou
                     y[l + 96] = d * (float)sc[is + 6] * (float)q4;
                 }
                 for (int i = 0; i < 128; i++) out[o++] = y[i];
+            }
+        }
+    } else if (type == 23) {   /* IQ4_XS, crates/ojas-formats/src/gguf.rs:814-840 */
+        for (size_t blk = 0; blk < n / 256; blk++) {
+            const uint8_t *p = b + blk * 136;
+            float d = rdh(p, 0);
+            unsigned sh = (unsigned)(p[2] | (p[3] << 8));
+            const uint8_t *sl = p + 4, *qs = p + 8;
+            for (int ib = 0; ib < 8; ib++) {
+                int ls = (int)(((sl[ib / 2] >> (4 * (ib % 2))) & 0xF) | (((sh >> (2 * ib)) & 3u) << 4));
+                float dl = d * (float)(ls - 32);
+                const uint8_t *q = qs + ib * 16;
+                for (int j = 0; j < 16; j++) out[o++] = dl * (float)orc_kvalues_iq4nl[q[j] & 0xF];
+                for (int j = 0; j < 16; j++) out[o++] = dl * (float)orc_kvalues_iq4nl[q[j] >> 4];
             }
         }
     } else {
@@ -401,16 +422,44 @@ ORC_API float orc_dot_q80(const uint8_t *row, const float *x, size_t k) {
     return sum;
 }
 
+/* dot_iq4xs, crates/ojas-cpu/src/cpu_math.rs:943-967: f32 activations; per group of 32 the codebook values times x
+ * (low nibble j, then high nibble j + 16, alternating), the group's sum times (ls - 32), the block's sum times d. */
+ORC_API float orc_dot_iq4xs(const uint8_t *row, const float *x, size_t k) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < k / 256; b++) {
+        const uint8_t *blk = row + b * 136;
+        const float *xb = x + b * 256;
+        float d = rdh(blk, 0);
+        unsigned sh = (unsigned)(blk[2] | (blk[3] << 8));
+        const uint8_t *sl = blk + 4, *qs = blk + 8;
+        float bsum = 0.0f;
+        for (int g = 0; g < 8; g++) {
+            int ls = (int)(((sl[g / 2] >> (4 * (g % 2))) & 0xF) | (((sh >> (2 * g)) & 3u) << 4));
+            const float *xg = xb + g * 32;
+            float gsum = 0.0f;
+            for (int j = 0; j < 16; j++) {
+                uint8_t q = qs[16 * g + j];
+                gsum += (float)orc_kvalues_iq4nl[q & 0xF] * xg[j];
+                gsum += (float)orc_kvalues_iq4nl[q >> 4] * xg[j + 16];
+            }
+            bsum += (float)(ls - 32) * gsum;
+        }
+        sum += d * bsum;
+    }
+    return sum;
+}
+
 /* ---------------------------------------------------------------- matvec_kq
  * crates/ojas-cpu/src/cpu_math.rs:1145-1189: quantize x once, then `threads`
  * workers steal 8-row chunks from a shared counter.  Row stride follows the
- * reference's table (:1148-1160): k/256 * {144, 210, 272}. */
+ * reference's table (:1148-1160): k/256 * {144, 176, 210, 272, 136}. */
 ORC_API size_t orc_row_bytes(uint32_t type, size_t k) {
     switch (type) {
     case 12: return k / 256 * 144;
     case 13: return k / 256 * 176;
     case 14: return k / 256 * 210;
     case 8:  return k / 256 * 272;
+    case 23: return k / 256 * 136;
     default: return 0;
     }
 }
@@ -433,6 +482,7 @@ static void *mv_worker(void *arg) {
             if (j->type == 12) v = orc_dot_q4k(rb, j->k / 256, j->scales, j->q, j->bsums, NULL);
             else if (j->type == 13) v = orc_dot_q5k(rb, j->k / 256, j->scales, j->q, j->bsums, NULL);
             else if (j->type == 8) v = orc_dot_q80(rb, j->x, j->k);
+            else if (j->type == 23) v = orc_dot_iq4xs(rb, j->x, j->k);
             else v = orc_dot_q6k(rb, j->k / 256, j->scales, j->q, NULL);
             j->out[row] = v;
         }

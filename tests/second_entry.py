@@ -166,14 +166,40 @@ def dot_q80(row: np.ndarray, x: np.ndarray) -> np.float32:
     return s
 
 
+KVALUES_IQ4NL = (-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113)   # ggml's kvalues_iq4nl
+
+
+def dot_iq4xs(row: np.ndarray, x: np.ndarray) -> np.float32:
+    """cpu_math.rs:943-967: per group of 32 the codebook values times x (low nibble j, high nibble j + 16, alternating),
+    times (ls - 32); the block's sum times d."""
+    x = np.asarray(x, F)
+    s = F(0)
+    for b in range(x.size // 256):
+        blk = row[b * 136:(b + 1) * 136]
+        d = _f16(blk, 0)
+        sh = int(blk[2]) | (int(blk[3]) << 8)
+        sl, qs = blk[4:8], blk[8:136]
+        bsum = F(0)
+        for g in range(8):
+            ls = ((int(sl[g // 2]) >> (4 * (g % 2))) & 0xF) | (((sh >> (2 * g)) & 3) << 4)
+            gsum = F(0)
+            for j in range(16):
+                qb = int(qs[16 * g + j])
+                gsum = F(gsum + F(F(KVALUES_IQ4NL[qb & 0xF]) * x[b * 256 + g * 32 + j]))
+                gsum = F(gsum + F(F(KVALUES_IQ4NL[qb >> 4]) * x[b * 256 + g * 32 + j + 16]))
+            bsum = F(bsum + F(F(ls - 32) * gsum))
+        s = F(s + F(d * bsum))
+    return s
+
+
 def matvec_kq(raw: np.ndarray, t: int, n: int, k: int, x: np.ndarray) -> np.ndarray:
     """cpu_math.rs:1145-1189: activations quantized once (K-quants), one block dot per row."""
-    rb = {12: 144 * (k // 256), 13: 176 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32)}[t]
+    rb = {12: 144 * (k // 256), 13: 176 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32), 23: 136 * (k // 256)}[t]
     rows = np.asarray(raw, np.uint8).reshape(n, rb)
     out = np.empty(n, F)
-    if t == 8:
+    if t in (8, 23):
         for r in range(n):
-            out[r] = dot_q80(rows[r], x)
+            out[r] = (dot_q80 if t == 8 else dot_iq4xs)(rows[r], x)
         return out
     act = quant_q8k(x)
     for r in range(n):

@@ -9,7 +9,8 @@ from conftest import rel_l2
 
 
 # crates/ojas-formats/tests/quant_formats.rs:33-50: (type, value count, FNV-1a digest)
-@pytest.mark.parametrize("t,n,want", [(Q4_K, 10240, 0x6536b83e8b2292b4), (Q6_K, 10240, 0x38ecabe858257db6)])
+@pytest.mark.parametrize("t,n,want", [(Q4_K, 10240, 0x6536b83e8b2292b4), (Q6_K, 10240, 0x38ecabe858257db6),
+                                      (oracle.Q5_K, 10240, 0x361cbd8f84e79ade), (oracle.IQ4_XS, 10240, 0x1429cafb4df9af64)])
 def test_synth_block_digests(t, n, want):
     raw = oracle.synth_blocks(t, 40)
     vals = oracle.dequant_f16(raw, t, n)
@@ -257,4 +258,21 @@ def test_q5k_second_entry_and_identity():
         assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
         assert abs(got - float(w[r] @ xd)) <= 1e-5 * float(np.abs(w[r]) @ np.abs(xd))
     a, b = oracle.matvec_kq(raw, Q5_K, n, k, x, threads=1), second_entry.matvec_kq(raw, Q5_K, n, k, x)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_iq4xs_second_entry_and_identity():
+    """IQ4_XS (type 23) in the oracle: the f32 dot against the transcription of the Rust source bit for bit, matvec_kq
+    likewise, and the identity dot(row, x) == sum dequant(row)[i] * x[i] (the decode is pinned by the reference's digest)."""
+    import second_entry
+    from oracle import IQ4_XS
+    k, n = 768, 6
+    raw = oracle.synth_blocks(IQ4_XS, n * k // 256).reshape(n, -1)
+    x = np.random.default_rng(23).standard_normal(k).astype(np.float32)
+    w = oracle.dequant_f32(raw.reshape(-1), IQ4_XS, n * k).reshape(n, k).astype(np.float64)
+    for r in range(n):
+        got, want = oracle.dot_iq4xs(raw[r], x), second_entry.dot_iq4xs(raw[r], x)
+        assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
+        assert abs(got - float(w[r] @ x.astype(np.float64))) <= 1e-5 * float(np.abs(w[r]) @ np.abs(x).astype(np.float64))
+    a, b = oracle.matvec_kq(raw, IQ4_XS, n, k, x, threads=1), second_entry.matvec_kq(raw, IQ4_XS, n, k, x)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
