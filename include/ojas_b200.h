@@ -263,7 +263,7 @@ OJAS_B200_API int ojas_b200_weight_cache_entry(const ojas_b200_weight_cache *cac
 
 /* ---- token-table gather: x[m, :] = dequantized row ids[m] of a table kept as RAW GGUF blocks [rows, d] on the device
  * (read in place; not the repacked layout).  Replaces q35_embed_q4k (crates/ojas-cuda/src/kernels/qwen35.rs:51-69) for
- * Q4_K, Q5_K, Q6_K and Q8_0 tables; the values equal the CPU decoder's bit for bit.  An id >= rows reads the last row.
+ * Q4_K, Q5_K, Q6_K, Q8_0 and IQ4_XS tables; the values equal the CPU decoder's bit for bit.  An id >= rows reads the last row.
  * The entry name "q35_embed_q4k" (emb, ids, x)(d, M) is served by ojas_b200_dispatch. */
 OJAS_B200_API int ojas_b200_embed_rows(ojas_b200_ctx *ctx, uint32_t ggml_type, const void *table, size_t rows, const uint32_t *ids, size_t M,
                                        size_t d, float *x);

@@ -1,7 +1,7 @@
 // Token-table gather: x[m, :] = the dequantized row ids[m] of a table kept as raw GGUF blocks (read in place, no
 // re-layout: a table row is touched once per token, there is nothing to stream).  Counterpart of q35_embed_q4k
 // (crates/ojas-cuda/src/kernels/qwen35.rs:51-69), for the formats of this path; the arithmetic and its order are the
-// decoder's (crates/ojas-formats/src/gguf.rs:704-708, 1042-1058, 1060-1085, 1086-1108), so the rows equal the CPU decode
+// decoder's (crates/ojas-formats/src/gguf.rs:704-708, 814-840, 1042-1058, 1060-1085, 1086-1108), so the rows equal the CPU decode
 // bit for bit.  One warp per (token, 256 values): the lane owns values 8 lane .. 8 lane + 7 and writes 32 contiguous bytes.
 #include "common.cuh"
 
@@ -16,6 +16,9 @@ __device__ __forceinline__ void scale_min(int j, const uint8_t *sc, float &s, fl
         m = (float)((sc[j + 4] >> 4) | ((sc[j] >> 6) << 4));
     }
 }
+
+// The codebook of IQ4_NL / IQ4_XS (ggml's kvalues_iq4nl; the decoder reads it as iq_tables::KVALUES_IQ4NL, gguf.rs:832).
+__constant__ int8_t kIq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
 template <int TYPE>
 __global__ void __launch_bounds__(256) embed_kernel(const uint8_t *table, const uint32_t *ids, float *x, unsigned d, unsigned M, unsigned rows) {
@@ -32,6 +35,15 @@ __global__ void __launch_bounds__(256) embed_kernel(const uint8_t *table, const 
         const float dd = f16_bits_to_f32((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = __fmul_rn(dd, (float)(int8_t)blk[2 + (e0 & 31) + i]);
+    } else if (TYPE == OJAS_B200_IQ4_XS) {
+        const uint8_t *blk = table + ((size_t)id * nsb + sb) * 136;
+        const float dd = f16_bits_to_f32((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
+        const unsigned sh = (unsigned)blk[2] | ((unsigned)blk[3] << 8), g = e0 >> 5, o = e0 & 31;
+        const int ls = (int)(((blk[4 + g / 2] >> (4 * (g % 2))) & 0xF) | (((sh >> (2 * g)) & 3u) << 4)) - 32;
+        const float dl = __fmul_rn(dd, (float)ls);
+        const uint8_t *q = blk + 8 + g * 16 + (o & 15);           // values 0..15 of the group are low nibbles, 16..31 high
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __fmul_rn(dl, (float)kIq4nl[(o & 16) ? (q[i] >> 4) : (q[i] & 0xF)]);
     } else if (TYPE == OJAS_B200_Q6_K) {
         const uint8_t *blk = table + ((size_t)id * nsb + sb) * 210;
         const float dd = f16_bits_to_f32((uint32_t)blk[208] | ((uint32_t)blk[209] << 8));
@@ -85,6 +97,7 @@ extern "C" int ojas_b200_embed_rows(ojas_b200_ctx *ctx, uint32_t type, const voi
     if (type == OJAS_B200_Q4_K) embed_kernel<OJAS_B200_Q4_K><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else if (type == OJAS_B200_Q5_K) embed_kernel<OJAS_B200_Q5_K><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else if (type == OJAS_B200_Q6_K) embed_kernel<OJAS_B200_Q6_K><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
+    else if (type == OJAS_B200_IQ4_XS) embed_kernel<OJAS_B200_IQ4_XS><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else embed_kernel<OJAS_B200_Q8_0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     OJAS_LAUNCH_CHECK(ctx, "embed_rows");
     return 0;

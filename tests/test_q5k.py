@@ -128,7 +128,7 @@ def test_q5k_is_refused_where_it_is_not_built(gpu):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t", [ob.Q4_K, Q5_K, ob.Q6_K, ob.Q8_0])
+@pytest.mark.parametrize("t", [ob.Q4_K, Q5_K, ob.Q6_K, ob.Q8_0, ob.IQ4_XS])
 def test_token_table_gather_equals_the_cpu_decode(gpu, t):
     """x[m, :] = row ids[m] of a raw GGUF table, bit for bit the oracle's decoder (which the reference's own golden
     digests pin for Q4_K and Q6_K); repeated and out-of-order ids; by name for Q4_K."""
