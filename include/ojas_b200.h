@@ -32,10 +32,10 @@ extern "C" {
 
 typedef struct ojas_b200_ctx ojas_b200_ctx;
 
-/* GGUF tensor type codes on this path (crates/ojas-formats/src/synth.rs:12-21).  Q5_K and IQ4_XS: repack and the GEMV
- * family only (the prefill GEMM takes Q4_K, Q6_K and Q8_0; the expert FFN Q4_K and Q6_K).  IQ4_XS rows meet f32
- * activations, as Q8_0 rows do (dot_iq4xs, crates/ojas-cpu/src/cpu_math.rs:943-967). */
-enum { OJAS_B200_Q8_0 = 8, OJAS_B200_Q4_K = 12, OJAS_B200_Q5_K = 13, OJAS_B200_Q6_K = 14, OJAS_B200_IQ4_XS = 23 };
+/* GGUF tensor type codes on this path (crates/ojas-formats/src/synth.rs:12-21).  Q5_K, IQ4_NL and IQ4_XS: repack and the GEMV
+ * family only (the prefill GEMM takes Q4_K, Q6_K and Q8_0; the expert FFN Q4_K and Q6_K).  IQ4_NL and IQ4_XS rows meet f32
+ * activations, as Q8_0 rows do (dot_iq4nl / dot_iq4xs, crates/ojas-cpu/src/cpu_math.rs:993-1010, 943-967). */
+enum { OJAS_B200_Q8_0 = 8, OJAS_B200_Q4_K = 12, OJAS_B200_Q5_K = 13, OJAS_B200_Q6_K = 14, OJAS_B200_IQ4_NL = 20, OJAS_B200_IQ4_XS = 23 };
 
 /* Store forms of the native GEMV family: y = acc, y += acc, y = acc + bias
  * (crates/ojas-cuda/src/kernels/nat.rs:69-91). */
@@ -263,7 +263,7 @@ OJAS_B200_API int ojas_b200_weight_cache_entry(const ojas_b200_weight_cache *cac
 
 /* ---- token-table gather: x[m, :] = dequantized row ids[m] of a table kept as RAW GGUF blocks [rows, d] on the device
  * (read in place; not the repacked layout).  Replaces q35_embed_q4k (crates/ojas-cuda/src/kernels/qwen35.rs:51-69) for
- * Q4_K, Q5_K, Q6_K, Q8_0 and IQ4_XS tables; the values equal the CPU decoder's bit for bit.  An id >= rows reads the last row.
+ * Q4_K, Q5_K, Q6_K, Q8_0, IQ4_NL and IQ4_XS tables; the values equal the CPU decoder's bit for bit.  An id >= rows reads the last row.
  * The entry name "q35_embed_q4k" (emb, ids, x)(d, M) is served by ojas_b200_dispatch. */
 OJAS_B200_API int ojas_b200_embed_rows(ojas_b200_ctx *ctx, uint32_t ggml_type, const void *table, size_t rows, const uint32_t *ids, size_t M,
                                        size_t d, float *x);

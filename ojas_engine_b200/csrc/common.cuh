@@ -88,16 +88,21 @@ void ojas_count_launch(ojas_b200_ctx *ctx, const char *name);
 // Q8_0  (GGUF: 34 B per 32: f16 d, i8 q[32]; eight blocks per 256 weights)             tile = 2176 B
 //   pieces 0..15: q[16p .. 16p+15] of the 256 weights, natural order
 //   piece  16   : the eight f16 block scales
+// IQ4_NL (GGUF: 18 B per 32: f16 d, u8 qs[16]; eight blocks per 256 weights)          tile = 1152 B
+//   pieces 0..7 : qs of block p: low nibbles = codebook indices of weights 32p + i, high nibbles of 32p + 16 + i
+//                 (crates/ojas-formats/src/gguf.rs:796-812)
+//   piece  8    : the eight f16 block scales
 // IQ4_XS (GGUF: 136 B per 256: f16 d, u16 scales_h, u8 scales_l[4], u8 qs[128])       tile = 1088 B
 //   pieces 0..7 : qs[16p .. 16p+15] = sub-block p: low nibbles = codebook indices of weights 32p + i, high nibbles
 //                 of weights 32p + 16 + i (crates/ojas-formats/src/gguf.rs:814-840)
 //   then 8 x 8 bytes, one per row, at byte 8 * 128 + 8r: the block's first eight bytes (d, scales_h, scales_l)
 constexpr int OJAS_TILE_ROWS = 8;
 __host__ __device__ constexpr int tile_bytes(uint32_t type) {
-    return type == OJAS_B200_Q4_K ? 1152 : type == OJAS_B200_Q5_K ? 1408 : type == OJAS_B200_Q6_K ? 1680 : type == OJAS_B200_IQ4_XS ? 1088 : 2176;
+    return type == OJAS_B200_Q4_K ? 1152 : type == OJAS_B200_Q5_K ? 1408 : type == OJAS_B200_Q6_K ? 1680 : type == OJAS_B200_IQ4_XS ? 1088 : type == OJAS_B200_IQ4_NL ? 1152 : 2176;
 }
-// The formats whose CPU dot takes f32 activations (Q8_0: dot_q80, IQ4_XS: dot_iq4xs): the GEMV stages them as three int8 terms.
-__host__ __device__ constexpr bool f32_act_type(uint32_t type) { return type == OJAS_B200_Q8_0 || type == OJAS_B200_IQ4_XS; }
+// The formats whose CPU dot takes f32 activations (Q8_0: dot_q80, IQ4_NL: dot_iq4nl, IQ4_XS: dot_iq4xs): the GEMV stages them
+// as three int8 terms.
+__host__ __device__ constexpr bool f32_act_type(uint32_t type) { return type == OJAS_B200_Q8_0 || type == OJAS_B200_IQ4_XS || type == OJAS_B200_IQ4_NL; }
 // Bytes of the leading pieces that hold quants only (what the GEMM stages per tile; scales come after them).
 __host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
     return type == OJAS_B200_Q4_K ? 1024 : type == OJAS_B200_Q6_K ? 1536 : 2048;
@@ -105,7 +110,8 @@ __host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 static inline bool type_supported(uint32_t type) {
-    return type == OJAS_B200_Q4_K || type == OJAS_B200_Q5_K || type == OJAS_B200_Q6_K || type == OJAS_B200_Q8_0 || type == OJAS_B200_IQ4_XS;
+    return type == OJAS_B200_Q4_K || type == OJAS_B200_Q5_K || type == OJAS_B200_Q6_K || type == OJAS_B200_Q8_0 || type == OJAS_B200_IQ4_XS ||
+           type == OJAS_B200_IQ4_NL;
 }
 static inline size_t tile_units(size_t N) { return (N + OJAS_TILE_ROWS - 1) / OJAS_TILE_ROWS; }
 static inline size_t repacked_size(uint32_t type, size_t N, size_t K) { return align256(tile_units(N) * (K / 256) * (size_t)tile_bytes(type)); }

@@ -17,6 +17,7 @@ static uint32_t tag_type(const char *tag) {
     if (!strcmp(tag, "q5k")) return OJAS_B200_Q5_K;
     if (!strcmp(tag, "q6k")) return OJAS_B200_Q6_K;
     if (!strcmp(tag, "iq4xs")) return OJAS_B200_IQ4_XS;
+    if (!strcmp(tag, "iq4nl")) return OJAS_B200_IQ4_NL;
     return OJAS_B200_Q8_0;
 }
 
@@ -51,7 +52,8 @@ GEMV_ENTRIES(q4k)
 GEMV_ENTRIES(q5k)
 GEMV_ENTRIES(q6k)
 GEMV_ENTRIES(q80)
-GEMV_ENTRIES(iq4xs)   // gemv_nat_iq4xs: crates/ojas-core/src/quant_src.rs:85-110
+GEMV_ENTRIES(iq4xs)   // gemv_nat_iq4xs, gemv_nat_iq4nl: crates/ojas-core/src/quant_src.rs:85-110
+GEMV_ENTRIES(iq4nl)
 
 // quant_q8k: (x, q, scales, bsums) (K, M) — the activation step that precedes the K-quant
 // dots (crates/ojas-cpu/src/cpu_math.rs:545-563); no CUDA entry of this name exists upstream.
@@ -140,6 +142,7 @@ MOE_ENTRIES(q4k)
 MOE_ENTRIES(q6k)
 MOE_ENTRIES(q80)
 MOE_ENTRIES(iq4xs)   // moe_gu_iq4xs: crates/ojas-cuda/src/kernels/moe_iq.rs:64-84 (the other three forms by analogy)
+MOE_ENTRIES(iq4nl)   // moe_down_iq4nl: crates/ojas-cuda/src/kernels/moe_iq.rs:87-108 (the other three forms by analogy)
 
 // moe_topk: (lg, idx, wgt) (E, KSEL) — crates/ojas-cuda/src/kernels/moe.rs:45; moe_topk_m adds M.
 static int d_moe_topk(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) {
@@ -165,14 +168,14 @@ static int d_embed_q4k(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, co
     {"moe_gu_" #tag "_slots", 6, 2, moe_gu_##tag##_slots}, {"moe_down_" #tag "_slots", 5, 3, moe_down_##tag##_slots}
 
 static const NameEntry kTable[] = {
-    GEMV_TABLE(q4k), GEMV_TABLE(q5k), GEMV_TABLE(q6k), GEMV_TABLE(q80), GEMV_TABLE(iq4xs),
+    GEMV_TABLE(q4k), GEMV_TABLE(q5k), GEMV_TABLE(q6k), GEMV_TABLE(q80), GEMV_TABLE(iq4xs), GEMV_TABLE(iq4nl),
     {"quant_q8k", 4, 2, d_quant_q8k},
     {"q35_embed_q4k", 3, 2, d_embed_q4k},
     {"moe_topk", 3, 2, d_moe_topk}, {"moe_topk_m", 3, 3, d_moe_topk_m},
     {"gemm_mm_q4k", 3, 4, gemm_q4k}, {"gemm_mm_q6k", 3, 4, gemm_q6k}, {"gemm_mm_q8_0", 3, 4, gemm_q8_0}, {"gemm_mm_q4l", 5, 4, gemm_q4l},
     {"gemm_mm_q4k_sk", 3, 4, gemm_q4k_sk}, {"gemm_mm_q6k_sk", 3, 4, gemm_q6k_sk}, {"gemm_mm_q8_0_sk", 3, 4, gemm_q8_0_sk},
     {"gemm_mm_q4l_sk", 5, 4, gemm_q4l_sk},
-    MOE_TABLE(q4k), MOE_TABLE(q6k), MOE_TABLE(q80), MOE_TABLE(iq4xs),
+    MOE_TABLE(q4k), MOE_TABLE(q6k), MOE_TABLE(q80), MOE_TABLE(iq4xs), MOE_TABLE(iq4nl),
 };
 static const int kTableLen = (int)(sizeof kTable / sizeof kTable[0]);
 

@@ -1,7 +1,7 @@
 // Token-table gather: x[m, :] = the dequantized row ids[m] of a table kept as raw GGUF blocks (read in place, no
 // re-layout: a table row is touched once per token, there is nothing to stream).  Counterpart of q35_embed_q4k
 // (crates/ojas-cuda/src/kernels/qwen35.rs:51-69), for the formats of this path; the arithmetic and its order are the
-// decoder's (crates/ojas-formats/src/gguf.rs:704-708, 814-840, 1042-1058, 1060-1085, 1086-1108), so the rows equal the CPU decode
+// decoder's (crates/ojas-formats/src/gguf.rs:704-708, 796-840, 1042-1058, 1060-1085, 1086-1108), so the rows equal the CPU decode
 // bit for bit.  One warp per (token, 256 values): the lane owns values 8 lane .. 8 lane + 7 and writes 32 contiguous bytes.
 #include "common.cuh"
 
@@ -44,6 +44,13 @@ __global__ void __launch_bounds__(256) embed_kernel(const uint8_t *table, const 
         const uint8_t *q = blk + 8 + g * 16 + (o & 15);           // values 0..15 of the group are low nibbles, 16..31 high
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = __fmul_rn(dl, (float)kIq4nl[(o & 16) ? (q[i] >> 4) : (q[i] & 0xF)]);
+    } else if (TYPE == OJAS_B200_IQ4_NL) {
+        const uint8_t *blk = table + ((size_t)id * nsb + sb) * 144 + (e0 >> 5) * 18;
+        const float dd = f16_bits_to_f32((uint32_t)blk[0] | ((uint32_t)blk[1] << 8));
+        const unsigned o = e0 & 31;
+        const uint8_t *q = blk + 2 + (o & 15);
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __fmul_rn(dd, (float)kIq4nl[(o & 16) ? (q[i] >> 4) : (q[i] & 0xF)]);
     } else if (TYPE == OJAS_B200_Q6_K) {
         const uint8_t *blk = table + ((size_t)id * nsb + sb) * 210;
         const float dd = f16_bits_to_f32((uint32_t)blk[208] | ((uint32_t)blk[209] << 8));
@@ -97,6 +104,7 @@ extern "C" int ojas_b200_embed_rows(ojas_b200_ctx *ctx, uint32_t type, const voi
     if (type == OJAS_B200_Q4_K) embed_kernel<OJAS_B200_Q4_K><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else if (type == OJAS_B200_Q5_K) embed_kernel<OJAS_B200_Q5_K><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else if (type == OJAS_B200_Q6_K) embed_kernel<OJAS_B200_Q6_K><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
+    else if (type == OJAS_B200_IQ4_NL) embed_kernel<OJAS_B200_IQ4_NL><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else if (type == OJAS_B200_IQ4_XS) embed_kernel<OJAS_B200_IQ4_XS><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     else embed_kernel<OJAS_B200_Q8_0><<<(unsigned)blocks, 256, 0, ctx->stream>>>(t, ids, x, (unsigned)d, (unsigned)M, (unsigned)rows);
     OJAS_LAUNCH_CHECK(ctx, "embed_rows");

@@ -524,9 +524,12 @@ __device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t &lo, uint32_t &
     hi = __byte_perm(v0, v1, 0x7531u);
 }
 
-template <int MT>
+// NL: IQ4_NL (dot_iq4nl, :993-1010): the same codebook in plain blocks of 32, each with its own f16 scale and no sub-scale.
+template <int MT, bool NL>
 __device__ __forceinline__ void step_iq4xs(const uint8_t *wl, int r, const uint8_t *act, int K, int sb, float (&acc)[MT]) {
-    const uint2 H = *reinterpret_cast<const uint2 *>(wl - r * 16 + 8 * 128 + r * 8);      // d, scales_h | scales_l
+    const uint2 H = NL ? make_uint2(0u, 0u) : *reinterpret_cast<const uint2 *>(wl - r * 16 + 8 * 128 + r * 8);   // d, scales_h | scales_l
+    const uint4 D = NL ? *reinterpret_cast<const uint4 *>(wl + 8 * 128) : make_uint4(0u, 0u, 0u, 0u);            // eight block scales
+    const uint32_t dw[4] = {D.x, D.y, D.z, D.w};
     const float d = f16_bits_to_f32(H.x);
     const uint32_t sh = H.x >> 16, sl = H.y;
     const size_t rb = q80_act_row_bytes((size_t)K);
@@ -540,7 +543,7 @@ __device__ __forceinline__ void step_iq4xs(const uint8_t *wl, int r, const uint8
         iq4_lookup8(Q.z, wv[2], wv[6]);
         iq4_lookup8(Q.w, wv[3], wv[7]);
         const int ls = (int)(((sl >> (4 * g)) & 0xFu) | (((sh >> (2 * g)) & 3u) << 4)) - 32;
-        const float dl = __fmul_rn(d, (float)ls);
+        const float dl = NL ? f16_bits_to_f32(dw[g >> 1] >> (16 * (g & 1))) : __fmul_rn(d, (float)ls);
 #pragma unroll
         for (int m = 0; m < MT; m++) {
             const uint8_t *row = act + m * rb + (size_t)sb * 256 + g * 32;
@@ -693,7 +696,8 @@ __device__ __forceinline__ void gemv_body(const GemvArgs &a, unsigned char *smem
             if (TYPE == OJAS_B200_Q4_K) step_q4k<MT, DUMP>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q5_K) step_q4k<MT, DUMP, true>(wl + stg * STEP, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 8 : nullptr);
             else if (TYPE == OJAS_B200_Q6_K) step_q6k<MT, DUMP>(wl + stg * STEP, r, act, nsb, sb, acc, DUMP ? a.idots + ((size_t)row * nsb + sb) * 16 : nullptr);
-            else if (TYPE == OJAS_B200_IQ4_XS) step_iq4xs<MT>(wl + stg * STEP, r, act, a.K, sb, acc);
+            else if (TYPE == OJAS_B200_IQ4_XS) step_iq4xs<MT, false>(wl + stg * STEP, r, act, a.K, sb, acc);
+            else if (TYPE == OJAS_B200_IQ4_NL) step_iq4xs<MT, true>(wl + stg * STEP, r, act, a.K, sb, acc);
             else step_q80<MT>(wl + stg * STEP, act, a.K, sb, acc);
         }
         __syncwarp();                                             // every lane has read the stage
@@ -945,12 +949,14 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
             if (type == OJAS_B200_Q5_K) { GEMV_PRO_CASE(OJAS_B200_Q5_K, 1, "gemv_q5k_rmsnorm") }
             if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 1, "gemv_q6k_rmsnorm") }
             if (type == OJAS_B200_IQ4_XS) { GEMV_PRO_CASE(OJAS_B200_IQ4_XS, 1, "gemv_iq4xs_rmsnorm") }
+            if (type == OJAS_B200_IQ4_NL) { GEMV_PRO_CASE(OJAS_B200_IQ4_NL, 1, "gemv_iq4nl_rmsnorm") }
             GEMV_PRO_CASE(OJAS_B200_Q8_0, 1, "gemv_q80_rmsnorm")
         }
         if (type == OJAS_B200_Q4_K) { GEMV_PRO_CASE(OJAS_B200_Q4_K, 2, "gemv_q4k_silu_mul") }
         if (type == OJAS_B200_Q5_K) { GEMV_PRO_CASE(OJAS_B200_Q5_K, 2, "gemv_q5k_silu_mul") }
         if (type == OJAS_B200_Q6_K) { GEMV_PRO_CASE(OJAS_B200_Q6_K, 2, "gemv_q6k_silu_mul") }
         if (type == OJAS_B200_IQ4_XS) { GEMV_PRO_CASE(OJAS_B200_IQ4_XS, 2, "gemv_iq4xs_silu_mul") }
+        if (type == OJAS_B200_IQ4_NL) { GEMV_PRO_CASE(OJAS_B200_IQ4_NL, 2, "gemv_iq4nl_silu_mul") }
         GEMV_PRO_CASE(OJAS_B200_Q8_0, 2, "gemv_q80_silu_mul")
 #undef GEMV_PRO_CASE
     }
@@ -970,6 +976,7 @@ static int gemv_launch_batch(ojas_b200_ctx *ctx, uint32_t type, bool preq, bool 
         GEMV_CASE(OJAS_B200_Q6_K, false, "gemv_q6k")
     }
     if (type == OJAS_B200_IQ4_XS) { GEMV_CASE(OJAS_B200_IQ4_XS, false, "gemv_iq4xs") }
+    if (type == OJAS_B200_IQ4_NL) { GEMV_CASE(OJAS_B200_IQ4_NL, false, "gemv_iq4nl") }
     GEMV_CASE(OJAS_B200_Q8_0, false, "gemv_q80")
 #undef GEMV_CASE
 }
@@ -1350,7 +1357,7 @@ extern "C" int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t type, int form, c
     int rc = gemv_check(ctx, type, form, w, y, bias, K, N, M);
     if (rc) return rc;
     if (f32_act_type(type))
-        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_q8k: Q8_0 and IQ4_XS rows meet f32 activations, not Q8_K blocks");
+        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_q8k: Q8_0, IQ4_NL and IQ4_XS rows meet f32 activations, not Q8_K blocks");
     if (!q || !scales || !bsums) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_q8k: null activation pointer");
     if (((uintptr_t)q & 15) != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_q8k: q must be 16-byte aligned");
     GemvArgs a{};
@@ -1364,7 +1371,7 @@ extern "C" int ojas_b200_gemv_idots(ojas_b200_ctx *ctx, uint32_t type, const flo
     float dummy;
     int rc = gemv_check(ctx, type, OJAS_B200_PLAIN, w, &dummy, nullptr, K, N, 1);
     if (rc) return rc;
-    if (f32_act_type(type)) return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_idots: Q8_0 and IQ4_XS have no integer block dots");
+    if (f32_act_type(type)) return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "gemv_idots: Q8_0, IQ4_NL and IQ4_XS have no integer block dots");
     if (!x || !idots) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemv_idots: null pointer");
     GemvArgs a{};
     a.x = x; a.w = (const uint8_t *)w; a.idots = idots;

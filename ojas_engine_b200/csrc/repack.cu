@@ -73,8 +73,18 @@ __host__ __device__ static inline void repack_iq4xs_block(const uint8_t *src, ui
     for (int i = 0; i < 8; i++) tile[8 * 128 + 8 * r + i] = src[i];
 }
 
+// IQ4_NL: eight GGUF blocks (18 bytes each) = 256 weights: the index bytes of block b as piece b, then the eight scales.
+__host__ __device__ static inline void repack_iq4nl_block(const uint8_t *src, uint8_t *tile, int r) {
+    for (int b = 0; b < 8; b++) {
+        const uint8_t *blk = src + b * 18;
+        for (int i = 0; i < 16; i++) tile_piece(tile, b, r)[i] = blk[2 + i];
+        tile_piece(tile, 8, r)[2 * b] = blk[0];
+        tile_piece(tile, 8, r)[2 * b + 1] = blk[1];
+    }
+}
+
 __host__ __device__ static inline size_t raw_sb_bytes(uint32_t type) {
-    return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : type == OJAS_B200_IQ4_XS ? 136 : 272;
+    return type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : type == OJAS_B200_IQ4_XS ? 136 : type == OJAS_B200_IQ4_NL ? 144 : 272;
 }
 
 // Block `blk` = (row n, super-block s) in row-major order of the GGUF tensor.
@@ -87,6 +97,7 @@ __host__ __device__ static inline void repack_one(uint32_t type, const uint8_t *
     else if (type == OJAS_B200_Q5_K) repack_q5k_block(src, tile, r);
     else if (type == OJAS_B200_Q6_K) repack_q6k_block(src, tile, r);
     else if (type == OJAS_B200_IQ4_XS) repack_iq4xs_block(src, tile, r);
+    else if (type == OJAS_B200_IQ4_NL) repack_iq4nl_block(src, tile, r);
     else repack_q80_block(src, tile, r);
 }
 

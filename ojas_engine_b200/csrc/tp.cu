@@ -32,7 +32,7 @@ extern "C" int ojas_b200_tp_shard_k(size_t K, int world, int rank, size_t *k0, s
 // Copies the K range [k0, k0 + klen) of every row of raw GGUF blocks [N, K] into out [N, klen].
 extern "C" int ojas_b200_tp_slice_k_host(uint32_t type, const void *raw, size_t N, size_t K, size_t k0, size_t klen, void *out) {
     if (!raw || !out || K % 256 != 0 || k0 % 256 != 0 || klen % 256 != 0 || k0 + klen > K) return OJAS_B200_E_ARG;
-    const size_t per256 = type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : type == OJAS_B200_Q8_0 ? 272 : type == OJAS_B200_IQ4_XS ? 136 : 0;
+    const size_t per256 = type == OJAS_B200_Q4_K ? 144 : type == OJAS_B200_Q5_K ? 176 : type == OJAS_B200_Q6_K ? 210 : type == OJAS_B200_Q8_0 ? 272 : type == OJAS_B200_IQ4_XS ? 136 : type == OJAS_B200_IQ4_NL ? 144 : 0;
     if (!per256) return OJAS_B200_E_ARG;
     const size_t row_in = K / 256 * per256, row_out = klen / 256 * per256, skip = k0 / 256 * per256;
     for (size_t r = 0; r < N; r++) memcpy((uint8_t *)out + r * row_out, (const uint8_t *)raw + r * row_in + skip, row_out);

@@ -17,10 +17,10 @@ import numpy as np
 
 from . import lib as _lib
 
-Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS = 8, 12, 13, 14, 23
+Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 8, 12, 13, 14, 20, 23
 PLAIN, ACCUM, BIAS = 0, 1, 2
 GEMV_MAX_M = 8
-_TAGS = {Q4_K: "q4k", Q5_K: "q5k", Q6_K: "q6k", Q8_0: "q80", IQ4_XS: "iq4xs"}
+_TAGS = {Q4_K: "q4k", Q5_K: "q5k", Q6_K: "q6k", Q8_0: "q80", IQ4_NL: "iq4nl", IQ4_XS: "iq4xs"}
 
 
 class OjasB200Error(RuntimeError):

@@ -13,7 +13,7 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS = 8, 12, 13, 14, 23
+Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS = 8, 12, 13, 14, 20, 23
 
 
 def _cpu_tag() -> str:
@@ -64,6 +64,7 @@ def _load(native: bool = False) -> C.CDLL:
         "orc_dot_q6k": (C.c_float, [u8p, C.c_size_t, f32p, i8p, i32p]),
         "orc_dot_q80": (C.c_float, [u8p, f32p, C.c_size_t]),
         "orc_dot_iq4xs": (C.c_float, [u8p, f32p, C.c_size_t]),
+        "orc_dot_iq4nl": (C.c_float, [u8p, f32p, C.c_size_t]),
         "orc_row_bytes": (C.c_size_t, [C.c_uint32, C.c_size_t]),
         "orc_matvec_kq": (C.c_int, [u8p, C.c_uint32, C.c_size_t, C.c_size_t, f32p, C.c_int, f32p]),
         "orc_matmul_kq": (C.c_int, [u8p, C.c_uint32, C.c_size_t, C.c_size_t, f32p, C.c_size_t, C.c_int, f32p]),
@@ -99,7 +100,7 @@ def _u8(a) -> np.ndarray:
 
 
 def block_shape(t: int) -> tuple[int, int]:
-    return {Q8_0: (34, 32), Q4_K: (144, 256), Q5_K: (176, 256), Q6_K: (210, 256), IQ4_XS: (136, 256)}[t]
+    return {Q8_0: (34, 32), Q4_K: (144, 256), Q5_K: (176, 256), Q6_K: (210, 256), IQ4_NL: (18, 32), IQ4_XS: (136, 256)}[t]
 
 
 def row_bytes(t: int, k: int) -> int:
@@ -178,6 +179,12 @@ def dot_q80(row, x) -> float:
     row = _u8(row)
     x = np.ascontiguousarray(x, np.float32).reshape(-1)
     return float(lib().orc_dot_q80(_p(row, C.c_uint8), _p(x, C.c_float), x.size))
+
+
+def dot_iq4nl(row, x) -> float:
+    row = _u8(row)
+    x = np.ascontiguousarray(x, np.float32).reshape(-1)
+    return float(lib().orc_dot_iq4nl(_p(row, C.c_uint8), _p(x, C.c_float), x.size))
 
 
 def dot_iq4xs(row, x) -> float:

@@ -91,13 +91,14 @@ static inline float rdh(const uint8_t *b, size_t i) {
 }
 
 /* ---------------------------------------------------------------- block shapes
- * crates/ojas-formats/src/synth.rs:12-21 (the formats on the path: Q8_0, Q4_K, Q5_K, Q6_K, IQ4_XS). */
+ * crates/ojas-formats/src/synth.rs:12-21 (the formats on the path: Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL, IQ4_XS). */
 ORC_API int orc_block_shape(uint32_t type, uint32_t *block_bytes, uint32_t *block_weights) {
     switch (type) {
     case 8:  *block_bytes = 34;  *block_weights = 32;  return 0;
     case 12: *block_bytes = 144; *block_weights = 256; return 0;
     case 13: *block_bytes = 176; *block_weights = 256; return 0;
     case 14: *block_bytes = 210; *block_weights = 256; return 0;
+    case 20: *block_bytes = 18;  *block_weights = 32;  return 0;
     case 23: *block_bytes = 136; *block_weights = 256; return 0;
     default: return -1;
     }
@@ -208,6 +209,13 @@ ORC_API int orc_dequant_f32(const uint8_t *b, uint32_t type, size_t n, float *ou
                 }
                 for (int i = 0; i < 128; i++) out[o++] = y[i];
             }
+        }
+    } else if (type == 20) {   /* IQ4_NL, crates/ojas-formats/src/gguf.rs:796-812 */
+        for (size_t blk = 0; blk < n / 32; blk++) {
+            const uint8_t *p = b + blk * 18;
+            float d = rdh(p, 0);
+            for (int j = 0; j < 16; j++) out[o++] = d * (float)orc_kvalues_iq4nl[p[2 + j] & 0xF];
+            for (int j = 0; j < 16; j++) out[o++] = d * (float)orc_kvalues_iq4nl[p[2 + j] >> 4];
         }
     } else if (type == 23) {   /* IQ4_XS, crates/ojas-formats/src/gguf.rs:814-840 */
         for (size_t blk = 0; blk < n / 256; blk++) {
@@ -449,16 +457,35 @@ ORC_API float orc_dot_iq4xs(const uint8_t *row, const float *x, size_t k) {
     return sum;
 }
 
+/* dot_iq4nl, crates/ojas-cpu/src/cpu_math.rs:993-1010: blocks of 32 (f16 d, sixteen index bytes), f32 activations. */
+ORC_API float orc_dot_iq4nl(const uint8_t *row, const float *x, size_t k) {
+    float sum = 0.0f;
+    for (size_t b = 0; b < k / 32; b++) {
+        const uint8_t *blk = row + b * 18;
+        const float *xb = x + b * 32;
+        float d = rdh(blk, 0);
+        float bsum = 0.0f;
+        for (int j = 0; j < 16; j++) {
+            uint8_t q = blk[2 + j];
+            bsum += (float)orc_kvalues_iq4nl[q & 0xF] * xb[j];
+            bsum += (float)orc_kvalues_iq4nl[q >> 4] * xb[j + 16];
+        }
+        sum += d * bsum;
+    }
+    return sum;
+}
+
 /* ---------------------------------------------------------------- matvec_kq
  * crates/ojas-cpu/src/cpu_math.rs:1145-1189: quantize x once, then `threads`
  * workers steal 8-row chunks from a shared counter.  Row stride follows the
- * reference's table (:1148-1160): k/256 * {144, 176, 210, 272, 136}. */
+ * reference's table (:1148-1160): k/256 * {144, 176, 210, 272, 144, 136}. */
 ORC_API size_t orc_row_bytes(uint32_t type, size_t k) {
     switch (type) {
     case 12: return k / 256 * 144;
     case 13: return k / 256 * 176;
     case 14: return k / 256 * 210;
     case 8:  return k / 256 * 272;
+    case 20: return k / 256 * 144;
     case 23: return k / 256 * 136;
     default: return 0;
     }
@@ -482,6 +509,7 @@ static void *mv_worker(void *arg) {
             if (j->type == 12) v = orc_dot_q4k(rb, j->k / 256, j->scales, j->q, j->bsums, NULL);
             else if (j->type == 13) v = orc_dot_q5k(rb, j->k / 256, j->scales, j->q, j->bsums, NULL);
             else if (j->type == 8) v = orc_dot_q80(rb, j->x, j->k);
+            else if (j->type == 20) v = orc_dot_iq4nl(rb, j->x, j->k);
             else if (j->type == 23) v = orc_dot_iq4xs(rb, j->x, j->k);
             else v = orc_dot_q6k(rb, j->k / 256, j->scales, j->q, NULL);
             j->out[row] = v;

@@ -169,6 +169,22 @@ def dot_q80(row: np.ndarray, x: np.ndarray) -> np.float32:
 KVALUES_IQ4NL = (-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113)   # ggml's kvalues_iq4nl
 
 
+def dot_iq4nl(row: np.ndarray, x: np.ndarray) -> np.float32:
+    """cpu_math.rs:993-1010."""
+    x = np.asarray(x, F)
+    s = F(0)
+    for b in range(x.size // 32):
+        blk = row[b * 18:(b + 1) * 18]
+        d = _f16(blk, 0)
+        bsum = F(0)
+        for j in range(16):
+            qb = int(blk[2 + j])
+            bsum = F(bsum + F(F(KVALUES_IQ4NL[qb & 0xF]) * x[b * 32 + j]))
+            bsum = F(bsum + F(F(KVALUES_IQ4NL[qb >> 4]) * x[b * 32 + j + 16]))
+        s = F(s + F(d * bsum))
+    return s
+
+
 def dot_iq4xs(row: np.ndarray, x: np.ndarray) -> np.float32:
     """cpu_math.rs:943-967: per group of 32 the codebook values times x (low nibble j, high nibble j + 16, alternating),
     times (ls - 32); the block's sum times d."""
@@ -194,12 +210,12 @@ def dot_iq4xs(row: np.ndarray, x: np.ndarray) -> np.float32:
 
 def matvec_kq(raw: np.ndarray, t: int, n: int, k: int, x: np.ndarray) -> np.ndarray:
     """cpu_math.rs:1145-1189: activations quantized once (K-quants), one block dot per row."""
-    rb = {12: 144 * (k // 256), 13: 176 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32), 23: 136 * (k // 256)}[t]
+    rb = {12: 144 * (k // 256), 13: 176 * (k // 256), 14: 210 * (k // 256), 8: 34 * (k // 32), 20: 18 * (k // 32), 23: 136 * (k // 256)}[t]
     rows = np.asarray(raw, np.uint8).reshape(n, rb)
     out = np.empty(n, F)
-    if t in (8, 23):
+    if t in (8, 20, 23):
         for r in range(n):
-            out[r] = (dot_q80 if t == 8 else dot_iq4xs)(rows[r], x)
+            out[r] = {8: dot_q80, 20: dot_iq4nl, 23: dot_iq4xs}[t](rows[r], x)
         return out
     act = quant_q8k(x)
     for r in range(n):

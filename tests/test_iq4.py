@@ -1,19 +1,24 @@
-"""IQ4_XS (GGUF type 23) on the repack + GEMV part of the path: layout, outputs against the oracle's f32 dot, store
-forms, fused producers, decode-time expert selection by name.  The CPU side of the format (decoder pinned by the
-reference's digest, dot_iq4xs against an independent transcription) is in tests/test_oracle.py."""
+"""IQ4_XS (GGUF type 23) and IQ4_NL (type 20) on the repack + GEMV part of the path: layout, outputs against the
+oracle's f32 dots, store forms, fused producers, decode-time expert selection by name.  The CPU side of the formats
+(decoders pinned by the reference's digests, dot_iq4xs / dot_iq4nl against an independent transcription and the
+reference's known answers) is in tests/test_oracle.py."""
 import numpy as np
 import pytest
 
 import oracle
 import ojas_engine_b200 as ob
-from ojas_engine_b200 import ACCUM, BIAS, IQ4_XS
+from ojas_engine_b200 import ACCUM, BIAS, IQ4_NL, IQ4_XS
 
 from conftest import rel_l2
 from helpers import activations
 
 
-def _raw(n, k, roll=0):
-    base = oracle.synth_blocks(IQ4_XS, n * k // 256).reshape(n, -1)
+BOTH = pytest.mark.parametrize("t", [IQ4_XS, IQ4_NL], ids=["iq4xs", "iq4nl"])
+TAG = {IQ4_XS: "iq4xs", IQ4_NL: "iq4nl"}
+
+
+def _raw(n, k, roll=0, t=IQ4_XS):
+    base = oracle.synth_blocks(t, n * k // oracle.block_shape(t)[1]).reshape(n, -1)
     return np.ascontiguousarray(np.roll(base, roll, axis=0))
 
 
@@ -38,23 +43,43 @@ def test_iq4xs_tile_layout_keeps_every_bit():
             assert np.array_equal(qs, blk[8:136]) and np.array_equal(head, blk[0:8])
 
 
+def test_iq4nl_tile_layout_keeps_every_bit():
+    """Host repack: piece b of row r = the sixteen index bytes of the row's block b of the super-block; piece 8 = the
+    eight f16 block scales."""
+    n, k = 13, 512
+    raw = _raw(n, k, t=IQ4_NL)
+    packed = ob.repack_host(IQ4_NL, raw, n, k)
+    nsb, units = k // 256, (n + 7) // 8
+    tiles = packed[:units * nsb * 1152].reshape(units, nsb, 9, 8, 16)
+    for r in range(units * 8):
+        for s in range(nsb):
+            got = tiles[r // 8, s, :, r % 8, :]
+            if r >= n:
+                assert not got.any()
+                continue
+            blocks = raw[r, s * 144:(s + 1) * 144].reshape(8, 18)
+            assert np.array_equal(got[0:8], blocks[:, 2:]) and np.array_equal(got[8], blocks[:, :2].reshape(-1))
+
+
 @pytest.mark.gpu
-def test_iq4xs_device_repack_equals_host_repack(gpu):
+@BOTH
+def test_iq4_device_repack_equals_host_repack(gpu, t):
     n, k = 77, 1024
-    raw = _raw(n, k)
-    w = gpu.load_weight(raw, IQ4_XS, n, k)
-    want = ob.repack_host(IQ4_XS, raw, n, k)
+    raw = _raw(n, k, t=t)
+    w = gpu.load_weight(raw, t, n, k)
+    want = ob.repack_host(t, raw, n, k)
     assert np.array_equal(gpu.read(w.buf, np.uint8, want.size), want)
     gpu.free(w.buf)
 
 
 @pytest.mark.gpu
+@BOTH
 @pytest.mark.parametrize("n,k,m", [(512, 4096, 1), (1000, 768, 1), (4096, 4096, 1), (14336, 4096, 1), (330, 1024, 2), (64, 2048, 3),
                                    (520, 512, 5), (256, 4096, 8), (17, 256, 1)])
-def test_iq4xs_gemv_matches_the_oracle(gpu, n, k, m):
-    raw = _raw(n, k, roll=3)
+def test_iq4_gemv_matches_the_oracle(gpu, t, n, k, m):
+    raw = _raw(n, k, roll=3, t=t)
     x = activations(m, k, seed=7 + m)
-    w = gpu.load_weight(raw, IQ4_XS, n, k)
+    w = gpu.load_weight(raw, t, n, k)
     guard = 64
     xb = gpu.upload(x)
     y = gpu.upload(np.full(m * n + 2 * guard, 7.25, np.float32))
@@ -63,7 +88,7 @@ def test_iq4xs_gemv_matches_the_oracle(gpu, n, k, m):
     full = gpu.read(y, np.float32, m * n + 2 * guard)
     assert np.all(full[:guard] == 7.25) and np.all(full[-guard:] == 7.25)          # nothing written outside [M, N]
     got = full[guard:-guard].reshape(m, n)
-    want = oracle.matmul_kq(raw, IQ4_XS, n, k, x)
+    want = oracle.matmul_kq(raw, t, n, k, x)
     assert rel_l2(got, want) < 2e-3          # the bar of the path
     assert rel_l2(got, want) < 1e-5          # three int8 terms per activation: fp32-level
     for b in (w.buf, xb, y):
@@ -71,12 +96,13 @@ def test_iq4xs_gemv_matches_the_oracle(gpu, n, k, m):
 
 
 @pytest.mark.gpu
-def test_iq4xs_store_forms_fused_producers_and_entry_names(gpu):
+@BOTH
+def test_iq4_store_forms_fused_producers_and_entry_names(gpu, t):
     n, k = 384, 1024
-    raw = _raw(n, k, roll=1)
+    raw = _raw(n, k, roll=1, t=t)
     x = activations(1, k, seed=9)
-    w = gpu.load_weight(raw, IQ4_XS, n, k)
-    want = oracle.matvec_kq(raw, IQ4_XS, n, k, x[0])
+    w = gpu.load_weight(raw, t, n, k)
+    want = oracle.matvec_kq(raw, t, n, k, x[0])
     xb = gpu.upload(x)
     y0 = activations(1, n, seed=10)[0]
     bias = activations(1, n, seed=11)[0]
@@ -89,12 +115,13 @@ def test_iq4xs_store_forms_fused_producers_and_entry_names(gpu):
     nw = activations(1, k, seed=12)[0]
     nb = gpu.upload(nw)
     gpu.gemv_rmsnorm(w, xb, nb, 1e-5, y, 1)
-    assert rel_l2(gpu.read(y, np.float32, n), oracle.matvec_kq(raw, IQ4_XS, n, k, oracle.rmsnorm(x[0], nw, 1e-5))) < 1e-5
-    names = ("gemv_nat_iq4xs", "gemv_nat_iq4xs_accum", "gemv_nat_iq4xs_bias", "gemv_nat_iq4xs_m", "moe_gu_iq4xs")
+    assert rel_l2(gpu.read(y, np.float32, n), oracle.matvec_kq(raw, t, n, k, oracle.rmsnorm(x[0], nw, 1e-5))) < 1e-5
+    tag = TAG[t]
+    names = (f"gemv_nat_{tag}", f"gemv_nat_{tag}_accum", f"gemv_nat_{tag}_bias", f"gemv_nat_{tag}_m", f"moe_gu_{tag}", f"moe_down_{tag}")
     assert all(gpu.has_kernel(name) for name in names)
     gpu.memset(y, 0)
     enc = gpu.begin()
-    gpu.dispatch(enc, "gemv_nat_iq4xs", [(xb, 0), (w.buf, 0), (y, 0)], [k, n])
+    gpu.dispatch(enc, f"gemv_nat_{tag}", [(xb, 0), (w.buf, 0), (y, 0)], [k, n])
     gpu.submit(enc)
     assert rel_l2(gpu.read(y, np.float32, n), want) < 1e-5
     for buf in (w.buf, xb, y, bb, nb):
@@ -102,8 +129,10 @@ def test_iq4xs_store_forms_fused_producers_and_entry_names(gpu):
 
 
 @pytest.mark.gpu
-def test_iq4xs_expert_gate_up_by_name(gpu):
-    """moe_gu_iq4xs (x, wg, wu, act, idx)(K, N), grid.y = picks: act[j] = silu(gate_e x) * (up_e x) for the picked experts."""
+def test_iq4_experts_by_name(gpu):
+    """The two IQ expert entries of the engine: moe_gu_iq4xs (x, wg, wu, act, idx)(K, N), grid.y = picks:
+    act[j] = silu(gate_e x) * (up_e x) for the picked experts; then moe_down_iq4nl (act, wd, x, idx, wgt)(K, N, KSEL):
+    x += sum_j wgt[j] * down_e act[j]."""
     e, n, k = 4, 256, 512
     raw_g, raw_u = _raw(e * n, k, roll=2), _raw(e * n, k, roll=5)
     x = activations(1, k, seed=13)
@@ -118,14 +147,28 @@ def test_iq4xs_expert_gate_up_by_name(gpu):
         g = oracle.matvec_kq(raw_g[ex * n:(ex + 1) * n], IQ4_XS, n, k, x[0])
         u = oracle.matvec_kq(raw_u[ex * n:(ex + 1) * n], IQ4_XS, n, k, x[0])
         assert rel_l2(got[j], oracle.silu_mul(g, u)) < 1e-5
-    for buf in (wg.buf, wu.buf, xb, ib, act):
+    # down: experts [e, k, n] stored IQ4_NL, rows of width n
+    raw_d = _raw(e * k, n, roll=7, t=IQ4_NL)
+    wd = gpu.load_weight(raw_d, IQ4_NL, e * k, n)
+    wgt = np.array([0.75, 0.25], np.float32)
+    h0 = activations(1, k, seed=14)[0]
+    hb, wb = gpu.upload(h0), gpu.upload(wgt)
+    enc = gpu.begin()
+    gpu.dispatch(enc, "moe_down_iq4nl", [(act, 0), (wd.buf, 0), (hb, 0), (ib, 0), (wb, 0)], [n, k, picks.size])
+    gpu.submit(enc)
+    want = h0.copy()
+    for j, ex in enumerate(picks):
+        want = want + wgt[j] * oracle.matvec_kq(raw_d[ex * k:(ex + 1) * k], IQ4_NL, k, n, got[j])
+    assert rel_l2(gpu.read(hb, np.float32, k), want) < 1e-5
+    for buf in (wg.buf, wu.buf, wd.buf, xb, ib, act, hb, wb):
         gpu.free(buf)
 
 
 @pytest.mark.gpu
-def test_iq4xs_is_refused_where_it_is_not_built(gpu):
+@BOTH
+def test_iq4_is_refused_where_it_is_not_built(gpu, t):
     n, k = 256, 512
-    w = gpu.load_weight(_raw(n, k), IQ4_XS, n, k)
+    w = gpu.load_weight(_raw(n, k, t=t), t, n, k)
     x, y = gpu.alloc(16 * k), gpu.alloc(16 * n)
     with pytest.raises(ob.OjasB200Error):
         gpu.gemm(w, x, y, 16)

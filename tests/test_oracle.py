@@ -10,7 +10,8 @@ from conftest import rel_l2
 
 # crates/ojas-formats/tests/quant_formats.rs:33-50: (type, value count, FNV-1a digest)
 @pytest.mark.parametrize("t,n,want", [(Q4_K, 10240, 0x6536b83e8b2292b4), (Q6_K, 10240, 0x38ecabe858257db6),
-                                      (oracle.Q5_K, 10240, 0x361cbd8f84e79ade), (oracle.IQ4_XS, 10240, 0x1429cafb4df9af64)])
+                                      (oracle.Q5_K, 10240, 0x361cbd8f84e79ade), (oracle.IQ4_XS, 10240, 0x1429cafb4df9af64),
+                                      (oracle.IQ4_NL, 1280, 0xa5d4cf4e5db3a1bf)])
 def test_synth_block_digests(t, n, want):
     raw = oracle.synth_blocks(t, 40)
     vals = oracle.dequant_f16(raw, t, n)
@@ -275,4 +276,31 @@ def test_iq4xs_second_entry_and_identity():
         assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
         assert abs(got - float(w[r] @ x.astype(np.float64))) <= 1e-5 * float(np.abs(w[r]) @ np.abs(x).astype(np.float64))
     a, b = oracle.matvec_kq(raw, IQ4_XS, n, k, x, threads=1), second_entry.matvec_kq(raw, IQ4_XS, n, k, x)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_iq4nl_known_answers_second_entry_and_identity():
+    """IQ4_NL (type 20).  The reference's own unit test (crates/ojas-cpu/src/cpu_math.rs:1203-1223): d = 1.0, qs[0] = 0x93;
+    a one-hot x at 0 selects the low nibble (codebook entry 3), at 16 the high nibble (entry 9).  Then the dot against the
+    transcription of the Rust source bit for bit, matvec_kq likewise, and dot(row, x) == sum dequant(row)[i] * x[i]."""
+    import second_entry
+    from oracle import IQ4_NL
+    row = np.zeros(18, np.uint8)
+    row[0:2] = np.frombuffer(np.float16(1.0).tobytes(), np.uint8)
+    row[2] = 0x93
+    x = np.zeros(32, np.float32)
+    x[0] = 1.0
+    assert oracle.dot_iq4nl(row, x) == float(second_entry.KVALUES_IQ4NL[3]) == -65.0
+    x[:] = 0
+    x[16] = 1.0
+    assert oracle.dot_iq4nl(row, x) == float(second_entry.KVALUES_IQ4NL[9]) == 13.0
+    k, n = 768, 6
+    raw = oracle.synth_blocks(IQ4_NL, n * k // 32).reshape(n, -1)
+    x = np.random.default_rng(29).standard_normal(k).astype(np.float32)
+    w = oracle.dequant_f32(raw.reshape(-1), IQ4_NL, n * k).reshape(n, k).astype(np.float64)
+    for r in range(n):
+        got, want = oracle.dot_iq4nl(raw[r], x), second_entry.dot_iq4nl(raw[r], x)
+        assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
+        assert abs(got - float(w[r] @ x.astype(np.float64))) <= 1e-5 * float(np.abs(w[r]) @ np.abs(x).astype(np.float64))
+    a, b = oracle.matvec_kq(raw, IQ4_NL, n, k, x, threads=1), second_entry.matvec_kq(raw, IQ4_NL, n, k, x)
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))

@@ -128,12 +128,12 @@ def test_q5k_is_refused_where_it_is_not_built(gpu):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("t", [ob.Q4_K, Q5_K, ob.Q6_K, ob.Q8_0, ob.IQ4_XS])
+@pytest.mark.parametrize("t", [ob.Q4_K, Q5_K, ob.Q6_K, ob.Q8_0, ob.IQ4_XS, ob.IQ4_NL])
 def test_token_table_gather_equals_the_cpu_decode(gpu, t):
     """x[m, :] = row ids[m] of a raw GGUF table, bit for bit the oracle's decoder (which the reference's own golden
     digests pin for Q4_K and Q6_K); repeated and out-of-order ids; by name for Q4_K."""
     rows, d = 37, 1024
-    raw = oracle.synth_blocks(t, rows * d // (32 if t == ob.Q8_0 else 256))
+    raw = oracle.synth_blocks(t, rows * d // oracle.block_shape(t)[1])
     table = oracle.dequant_f32(raw, t, rows * d).reshape(rows, d)
     ids = np.array([5, 0, 36, 5, 17, 1, 36], np.uint32)
     tb, ib, x = gpu.upload(raw), gpu.upload(ids), gpu.alloc(ids.size * d)
