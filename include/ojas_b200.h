@@ -62,8 +62,8 @@ OJAS_B200_API void *ojas_b200_stream(ojas_b200_ctx *ctx);
  * engine reads its OJAS_* switches, crates/ojas-core/src/config.rs:1-22): GEMVs and the GEMM are launched
  * with programmatic dependent launch, so a kernel's weight prefetch and set-up overlap the tail of the
  * kernel before it in the stream (activations and y are only touched after the wait on that kernel).
- * "gemv_mma" (0, 1 = default): Q4_K and Q6_K batches of three or more rows and expert groups on the integer
- * tensor-core kernels never / always.  "gemv_kseg": Q8_0 batches of 3..8 rows walk K in this many equal segments
+ * "gemv_mma": Q4_K and Q6_K batches and expert groups on the integer tensor-core kernels: 0 = never, 1 = default (batches
+ * from five rows; up to four the per-lane kernel is faster), n = 2..8: batches from n rows.  "gemv_kseg": Q8_0 batches of 3..8 rows walk K in this many equal segments
  * inside one launch (0 = only when the whole K does not fit in shared memory, 1 = never, n = n when it divides K / 256).  "gemv_warps", "gemv_stages" (0 = chosen per shape): upper bounds on the warps per CTA (a power of
  * two, at most 16) and on the depth of a warp's weight ring (1, 2 or 4) of the GEMV kernel; a bound the shape does
  * not fit under falls back to the next smaller choice.  "gemm_ksplit": 0 = K ranges balanced across the SMs,

@@ -242,7 +242,7 @@ extern "C" int ojas_b200_set_option(ojas_b200_ctx *ctx, const char *key, int val
     if (!strcmp(key, "pdl")) { ctx->pdl = value != 0; return 0; }
     if (!strcmp(key, "profile")) return profile_set(ctx, value != 0);
     if (!strcmp(key, "gemv_mma")) {
-        if (value < 0 || value > 1) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_mma must be 0 or 1");
+        if (value < 0 || value > 8) return ojas_fail(ctx, OJAS_B200_E_ARG, "set_option: gemv_mma must be 0 (never), 1 (default) or the batch size 2..8 from which the tensor-core kernel is used");
         ctx->gemv_mma = value;
         return 0;
     }

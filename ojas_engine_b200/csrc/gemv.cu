@@ -1148,6 +1148,11 @@ static int gemv_check(ojas_b200_ctx *ctx, uint32_t type, int form, const void *w
     return 0;
 }
 
+// Up to this many values a batch of f32 rows is quantized by the batch kernel itself (every CTA repeats it: a few warp
+// tasks) instead of by a launch in front of it, which costs more than it saves on small matrices.
+constexpr size_t GEMV_BATCH_QUANT_INSIDE = 32768;
+constexpr size_t GEMV_BATCH_MIN_ROWS = 5;            // the tensor-core batch kernel takes batches from this many rows (measured: up to four the per-lane kernel is faster on every shape)
+
 // A batch of K-quant rows from fp32 activations: every CTA of the GEMV would quantize the whole batch for
 // itself (M * K / 256 warp tasks each).  From a few dozen tasks per warp on that prologue outweighs the
 // matrix, so the batch is quantized once into the context's scratch and the GEMV copies the result.
@@ -1155,7 +1160,7 @@ static bool gemv_prequantize(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvA
     if (preq || f32_act_type(type) || M < 2 || !ctx->act_scratch || args.norm_w || args.x2) return false;   // (a fused producer runs in the kernel's prologue)
     const size_t values = M * (size_t)args.K;
     if (values > OJAS_ACT_SCRATCH_VALUES) return false;
-    if (values < 16384 && !((type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) && M >= 3 && ctx->gemv_mma != 0)) return false;   // (the batch kernel takes quantized rows only)
+    if (values <= GEMV_BATCH_QUANT_INSIDE) return false;             // few enough for every CTA to quantize them for itself
     int8_t *q = (int8_t *)ctx->act_scratch;
     float *scales = (float *)(q + OJAS_ACT_SCRATCH_VALUES);
     int32_t *bsums = (int32_t *)(scales + OJAS_ACT_SCRATCH_VALUES / 256);
@@ -1217,10 +1222,14 @@ static int gemv_q80_kseg(ojas_b200_ctx *ctx, GemvArgs args, size_t nsb) {
 }
 
 static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args, size_t M) {
-    if (gemv_prequantize(ctx, type, preq, args, M)) preq = true;
-    if ((type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) && preq && M >= 3 && ctx->gemv_mma != 0 && !args.tp.step) {   // tensor-core batch kernel
+    const size_t batch_from = ctx->gemv_mma == 1 ? GEMV_BATCH_MIN_ROWS : (size_t)ctx->gemv_mma;      // option gemv_mma: 0 never, 1 default, n: from n rows
+    const bool batch_kernel = (type == OJAS_B200_Q4_K || type == OJAS_B200_Q6_K) && ctx->gemv_mma != 0 && M >= batch_from && !args.tp.step && !args.row_index;
+    const bool inside = batch_kernel && !preq && args.x && !args.norm_w && !args.x2 && M * (size_t)args.K <= GEMV_BATCH_QUANT_INSIDE;
+    if (!inside && gemv_prequantize(ctx, type, preq, args, M)) preq = true;
+    if (batch_kernel && (preq || inside)) {                                // tensor-core batch kernel
         BatchArgs b{};
         b.w[0] = args.w; b.y[0] = args.y; b.nw = 1;
+        b.x = inside ? args.x : nullptr;
         b.q = args.q; b.scales = args.scales; b.bsums = args.bsums;
         b.bias = args.bias; b.form = args.form;
         b.E = 1; b.M = (int)M; b.K = args.K; b.N = args.N;

@@ -26,6 +26,7 @@ struct BatchArgs {
     float *y[2];                  // outputs [positions, N], one per weight tensor
     int nw;
     size_t expert_bytes;          // distance between consecutive experts in a weight tensor
+    const float *x;               // f32 activation rows [rows, K]: quantized by the kernel itself (small batches); null: q / scales / bsums
     const int8_t *q;              // quantized activation rows [rows, K] (ojas_b200_quant_q8k form)
     const float *scales;          // [rows, K/256]
     const int32_t *bsums;         // [rows, K/32]
@@ -259,7 +260,13 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) gemv_kq_batch_kernel(c
             const int units = K >> 4;
             for (int m = 0; m < NT; m++) {
                 uint4 *dst = reinterpret_cast<uint4 *>(xq + (size_t)m * Kpad);
-                if (m < m_here) {
+                if (m < m_here && a.x) {
+                    // fresh f32 rows: every warp quantizes super-blocks of the row (bit-exact quant_q8k), as the single-row kernel does
+                    const int pos = jc.off + jc.mb + m;
+                    const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
+                    for (int sb = warp; sb < nsb; sb += warps)
+                        stage_quant_sb<TYPE>(a.x + (size_t)srow * K, sb, lane, xq + (size_t)m * Kpad, bsb + (size_t)m * nsb * BSB, sx + m * nsb);
+                } else if (m < m_here) {
                     const int pos = jc.off + jc.mb + m;
                     const int srow = a.row_index ? __ldg(a.row_index + pos) : pos;
                     const uint4 *qsrc = reinterpret_cast<const uint4 *>(a.q + (size_t)srow * K);

@@ -139,6 +139,22 @@ def test_store_forms(gpu, tag, form):
     _gemv_case(gpu, tag, 130, 512, 4, form=form)
 
 
+@pytest.mark.parametrize("tag", ["q4k", "q6k"])
+@pytest.mark.parametrize("rows_from", [0, 2, 3, 5])
+def test_tensor_core_batch_kernel_from_any_batch_size(gpu, tag, rows_from):
+    """Option gemv_mma: 0 = per-lane kernels only, n = the tensor-core batch kernel from n rows (the default takes it from
+    five).  Small batches are quantized inside the batch kernel, larger ones (more than 32768 values) by a launch in
+    front of it; both against the oracle, ragged shapes and every store form included."""
+    gpu.set_option("gemv_mma", rows_from)
+    try:
+        for n, k, m, form in [(300, 2304, 2, PLAIN), (4096, 4096, 3, PLAIN), (1000, 4352, 4, BIAS), (17, 256, 5, ACCUM), (520, 14336, 3, PLAIN),
+                              (14336, 4096, 8, PLAIN), (77, 14336, 8, ACCUM)]:
+            err = _gemv_case(gpu, tag, n, k, m, form=form, seed=m + rows_from)
+            assert err < 1e-5
+    finally:
+        gpu.set_option("gemv_mma", 1)
+
+
 @pytest.mark.parametrize("segments", [0, 2, 4, 7])
 def test_q80_batches_over_k_segments(gpu, segments):
     """Q8_0 batches of 3..8 rows walk a long K in equal segments inside one launch (their activations do not fit in
