@@ -41,7 +41,10 @@ constexpr size_t OJAS_GEMM_FLAG_WORDS = 65536;
 // Activation scratch of a context: up to this many int8 values (8 rows of K = 32768), then one f32 scale per 256
 // and one i32 sum per 32 of them.
 constexpr size_t OJAS_ACT_SCRATCH_VALUES = 262144;
-constexpr size_t OJAS_ACT_SCRATCH_BYTES = OJAS_ACT_SCRATCH_VALUES + OJAS_ACT_SCRATCH_VALUES / 256 * 4 + OJAS_ACT_SCRATCH_VALUES / 32 * 4;
+// (Q8_K rows of OJAS_ACT_SCRATCH_VALUES values need 292 KB; the three-term int8 rows of a Q8_0 batch, 3.125 bytes per
+// value, up to 8 x 32768 values: 1 MiB covers both)
+constexpr size_t OJAS_ACT_SCRATCH_BYTES = (size_t)1 << 20;
+static_assert(OJAS_ACT_SCRATCH_VALUES + OJAS_ACT_SCRATCH_VALUES / 256 * 4 + OJAS_ACT_SCRATCH_VALUES / 32 * 4 <= OJAS_ACT_SCRATCH_BYTES, "Q8_K scratch");
 
 int ojas_fail(ojas_b200_ctx *ctx, int code, const char *fmt, ...);
 

@@ -50,6 +50,9 @@ struct GemvArgs {
     // K walked in segments (gemv_q80_kseg_kernel): a pass sees K = the segment's length, while activation rows are
     // x_stride values apart and the tiles of consecutive 8-row units w_nsb super-blocks apart (0 = K and nsb)
     int x_stride, w_nsb;
+    // Q8_0 batches converted to their three int8 terms once per call (quant_q80_terms_kernel): rows in the layout stage_q80
+    // keeps in shared memory, q80_act_row_bytes(x_stride ? x_stride : K) apart; null: every CTA converts x for itself
+    const uint8_t *q80;
     // decode-time expert selection (the engine's moe_gu_* / moe_down_* and their _slots forms,
     // crates/ojas-cuda/src/kernels/moe.rs:75-178): the weight rows start `*sel * sel_stride` bytes (sel_stride != 0)
     // or `*sel` bytes (an offset table entry) behind w, read on the device; alpha (may be null): the result is
@@ -291,6 +294,50 @@ __device__ __forceinline__ void stage_kquant(const GemvArgs &a, uint8_t *act, in
 // the batch reads at once)
 __host__ __device__ inline size_t q80_act_row_bytes(size_t K) { return 3 * K + K / 8 + 16; }
 
+// One warp converts super-block `sb` of a row (this lane's eight values v) into the three int8 planes and the eight
+// block scales of `row` (planes K bytes apart, scales behind them).
+__device__ __forceinline__ void q80_terms_sb(const float (&v)[8], int lane, uint8_t *row, size_t K, int sb) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));      // a block of 32 = four lanes
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float s = __fdiv_rn(amax, 127.0f), is = amax > 0.0f ? __fdiv_rn(1.0f, s) : 0.0f;
+    uint32_t w1[2] = {0u, 0u}, w2[2] = {0u, 0u}, w3[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float t = __fmul_rn(v[i], is);
+        const float q1 = fminf(fmaxf(rintf(t), -127.0f), 127.0f);
+        const float t2 = __fmul_rn(__fsub_rn(t, q1), 254.0f);
+        const float q2 = fminf(fmaxf(rintf(t2), -127.0f), 127.0f);
+        const float q3 = fminf(fmaxf(rintf(__fmul_rn(__fsub_rn(t2, q2), 254.0f)), -127.0f), 127.0f);
+        w1[i >> 2] |= ((uint32_t)(int)q1 & 0xffu) << (8 * (i & 3));
+        w2[i >> 2] |= ((uint32_t)(int)q2 & 0xffu) << (8 * (i & 3));
+        w3[i >> 2] |= ((uint32_t)(int)q3 & 0xffu) << (8 * (i & 3));
+    }
+    const size_t at = (size_t)sb * 256 + lane * 8;
+    *reinterpret_cast<uint2 *>(row + at) = make_uint2(w1[0], w1[1]);
+    *reinterpret_cast<uint2 *>(row + K + at) = make_uint2(w2[0], w2[1]);
+    *reinterpret_cast<uint2 *>(row + 2 * K + at) = make_uint2(w3[0], w3[1]);
+    if ((lane & 3) == 0) reinterpret_cast<float *>(row + 3 * K)[sb * 8 + (lane >> 2)] = s;
+}
+
+// The conversion once per call, for batches whose every CTA would otherwise repeat it: one warp per (row, super-block),
+// rows q80_act_row_bytes(K) apart.
+__global__ void __launch_bounds__(256) quant_q80_terms_kernel(const float *x, uint8_t *out, int K, long long n_sb) {
+    const int lane = threadIdx.x & 31;
+    const long long task = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    grid_launch_dependents();
+    if (task >= n_sb) return;
+    const int nsb = K >> 8;
+    const long long m = task / nsb;
+    const int sb = (int)(task - m * nsb);
+    const float *seg = x + (size_t)m * K + (size_t)sb * 256;
+    const float4 p = __ldg(reinterpret_cast<const float4 *>(seg) + lane * 2), q = __ldg(reinterpret_cast<const float4 *>(seg) + lane * 2 + 1);
+    const float v[8] = {p.x, p.y, p.z, p.w, q.x, q.y, q.z, q.w};
+    q80_terms_sb(v, lane, out + (size_t)m * q80_act_row_bytes((size_t)K), (size_t)K, sb);
+}
+
 template <int MT, int PRO>
 __device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int nsb, int warps, int sb0 = 0) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -300,8 +347,18 @@ __device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int n
 #pragma unroll
     for (int m = 0; m < MT; m++) {
         uint8_t *row = act + m * rb;
-        float *sc = reinterpret_cast<float *>(row + 3 * (size_t)a.K);
-        if (m < a.M) {
+        if (PRO == 0 && m < a.M && a.q80) {
+            // converted once per call: copy this pass's segment of the three planes and its block scales
+            const size_t Kt = a.x_stride ? (size_t)a.x_stride : (size_t)a.K;
+            const uint8_t *src = a.q80 + (size_t)m * q80_act_row_bytes(Kt);
+            const int pu = a.K >> 4;                              // 16-byte units per plane of the segment
+            for (int u = threadIdx.x; u < 3 * pu; u += blockDim.x) {
+                const int t = u / pu, i = u - t * pu;
+                reinterpret_cast<uint4 *>(row + (size_t)t * a.K)[i] = __ldg(reinterpret_cast<const uint4 *>(src + (size_t)t * Kt + (size_t)sb0 * 256) + i);
+            }
+            for (int u = threadIdx.x; u < nsb * 2; u += blockDim.x)   // eight f32 scales per super-block = two units
+                reinterpret_cast<uint4 *>(row + 3 * (size_t)a.K)[u] = __ldg(reinterpret_cast<const uint4 *>(src + 3 * Kt + (size_t)sb0 * 32) + u);
+        } else if (m < a.M) {
             const float *xr = a.x + (size_t)src_row(a, m) * (PRO == 0 && a.x_stride ? a.x_stride : a.K) + (size_t)sb0 * 256;
             for (int sb = warp; sb < nsb; sb += warps) {
                 float v[8];
@@ -313,29 +370,7 @@ __device__ __forceinline__ void stage_q80(const GemvArgs &a, uint8_t *act, int n
                     const float4 p = __ldg(reinterpret_cast<const float4 *>(xr + sb * 256) + lane * 2), q = __ldg(reinterpret_cast<const float4 *>(xr + sb * 256) + lane * 2 + 1);
                     v[0] = p.x; v[1] = p.y; v[2] = p.z; v[3] = p.w; v[4] = q.x; v[5] = q.y; v[6] = q.z; v[7] = q.w;
                 }
-                float amax = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));      // a block of 32 = four lanes
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                const float s = __fdiv_rn(amax, 127.0f), is = amax > 0.0f ? __fdiv_rn(1.0f, s) : 0.0f;
-                uint32_t w1[2] = {0u, 0u}, w2[2] = {0u, 0u}, w3[2] = {0u, 0u};
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const float t = __fmul_rn(v[i], is);
-                    const float q1 = fminf(fmaxf(rintf(t), -127.0f), 127.0f);
-                    const float t2 = __fmul_rn(__fsub_rn(t, q1), 254.0f);
-                    const float q2 = fminf(fmaxf(rintf(t2), -127.0f), 127.0f);
-                    const float q3 = fminf(fmaxf(rintf(__fmul_rn(__fsub_rn(t2, q2), 254.0f)), -127.0f), 127.0f);
-                    w1[i >> 2] |= ((uint32_t)(int)q1 & 0xffu) << (8 * (i & 3));
-                    w2[i >> 2] |= ((uint32_t)(int)q2 & 0xffu) << (8 * (i & 3));
-                    w3[i >> 2] |= ((uint32_t)(int)q3 & 0xffu) << (8 * (i & 3));
-                }
-                const size_t at = (size_t)sb * 256 + lane * 8;
-                *reinterpret_cast<uint2 *>(row + at) = make_uint2(w1[0], w1[1]);
-                *reinterpret_cast<uint2 *>(row + (size_t)a.K + at) = make_uint2(w2[0], w2[1]);
-                *reinterpret_cast<uint2 *>(row + 2 * (size_t)a.K + at) = make_uint2(w3[0], w3[1]);
-                if ((lane & 3) == 0) sc[sb * 8 + (lane >> 2)] = s;
+                q80_terms_sb(v, lane, row, (size_t)a.K, sb);
             }
         } else {
             for (size_t i = threadIdx.x; i < rb / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(row)[i] = 0u;
@@ -1237,6 +1272,17 @@ static int gemv_run(ojas_b200_ctx *ctx, uint32_t type, bool preq, GemvArgs args,
         if (rc != 1) return rc;
     }
     const size_t nsb = (size_t)args.K / 256;
+    // batches of f32 activations (Q8_0, IQ4_NL, IQ4_XS rows) too large for every CTA to convert for itself: the three int8
+    // terms once, into the context's scratch
+    if (f32_act_type(type) && M >= 2 && args.x && !args.tp.step && !args.norm_w && !args.x2 && !args.row_index && ctx->act_scratch &&
+        M * (size_t)args.K > GEMV_BATCH_QUANT_INSIDE && M * q80_act_row_bytes((size_t)args.K) <= OJAS_ACT_SCRATCH_BYTES) {
+        const long long n_sb = (long long)(M * nsb);
+        quant_q80_terms_kernel<<<(unsigned)((n_sb + 7) / 8), 256, 0, ctx->stream>>>(args.x, (uint8_t *)ctx->act_scratch, args.K, n_sb);
+        if (cudaGetLastError() == cudaSuccess) {
+            ojas_count_launch(ctx, "quant_q80_terms");
+            args.q80 = (const uint8_t *)ctx->act_scratch;
+        }
+    }
     if (type == OJAS_B200_Q8_0 && M >= 3 && M <= 8 && !args.tp.step && !args.norm_w && !args.x2 && !args.row_index) {
         const int rc = gemv_q80_kseg(ctx, args, nsb);
         if (rc != 1) return rc;
