@@ -86,5 +86,5 @@ def test_a_rank_that_never_arrives_is_an_error_not_a_hang(mode, tmp_path):
     for p in procs:
         p.wait(timeout=120)
     with open(outs[0]) as fh:
-        verdict = fh.read()
-    assert verdict.startswith("error"), verdict
+        outcome = fh.read()
+    assert outcome.startswith("error"), outcome
