@@ -108,7 +108,7 @@ __host__ __device__ constexpr int tile_bytes(uint32_t type) {
 __host__ __device__ constexpr bool f32_act_type(uint32_t type) { return type == OJAS_B200_Q8_0 || type == OJAS_B200_IQ4_XS || type == OJAS_B200_IQ4_NL; }
 // Bytes of the leading pieces that hold quants only (what the GEMM stages per tile; scales come after them).
 __host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
-    return type == OJAS_B200_Q4_K ? 1024 : type == OJAS_B200_Q6_K ? 1536 : 2048;
+    return type == OJAS_B200_Q4_K ? 1024 : type == OJAS_B200_Q5_K ? 1408 : type == OJAS_B200_Q6_K ? 1536 : 2048;   // (Q5_K: the whole tile, its fifth bits lie behind the header)
 }
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }

@@ -33,7 +33,7 @@ constexpr int WQ_BUFS_MAX = 3;
 // t * tile_quant_bytes + (p * 8 + r) * 16, so a warp's 32 consecutive rows read a piece without bank conflicts.
 __host__ __device__ constexpr int wq_bytes(int type) { return (BM / OJAS_TILE_ROWS) * tile_quant_bytes((uint32_t)type); }
 // raw tiles in flight: three, or two of the large Q8_0 tiles (so that four activation stages still fit)
-__host__ __device__ constexpr int wq_bufs(int type) { return type == OJAS_B200_Q8_0 ? 2 : 3; }
+__host__ __device__ constexpr int wq_bufs(int type) { return type == OJAS_B200_Q8_0 || type == OJAS_B200_Q5_K ? 2 : 3; }
 
 struct GemmArgs {
     const uint8_t *w;    // first tile of the weight rows (layout: common.cuh)
@@ -111,6 +111,36 @@ __device__ __forceinline__ void dequant_q4k_half(const uint4 &A, const uint4 &B,
     for (int i = 0; i < 8; i++) {
         const __half2 t0 = u32_as_h2((w[i] & 0x000f000fu) | 0x64006400u);          // weights (4i, 4i+2)
         const __half2 t1 = u32_as_h2(((w[i] >> 8) & 0x000f000fu) | 0x64006400u);   // weights (4i+1, 4i+3)
+        o[2 * i] = h2_as_u32(__hfma2(__hsub2(t0, k1024), ds, nm));
+        o[2 * i + 1] = h2_as_u32(__hfma2(__hsub2(t1, k1024), ds, nm));
+    }
+}
+
+// Q5_K (crates/ojas-formats/src/gguf.rs:1060-1085): Q4_K with a fifth bit per weight, bit j = 2c + half of qh[l] for weight l
+// of the sub-block; Qa, Qb = qh[0..15], qh[16..31].  The bit lands on value 16 of the mantissa before the subtraction.
+__device__ __forceinline__ void dequant_q5k_half(const uint4 &A, const uint4 &B, const uint4 &Qa, const uint4 &Qb, const uint4 &H, int c, int half,
+                                                 uint32_t (&o)[16]) {
+    const int j = 2 * c + half;
+    uint32_t sv, mv;
+    if (j < 4) {
+        sv = (H.y >> (8 * j)) & 63u;
+        mv = (H.z >> (8 * j)) & 63u;
+    } else {
+        const uint32_t t = H.w >> (8 * (j - 4));
+        sv = (t & 0xFu) | (((H.y >> (8 * (j - 4) + 6)) & 3u) << 4);
+        mv = ((t >> 4) & 0xFu) | (((H.z >> (8 * (j - 4) + 6)) & 3u) << 4);
+    }
+    const float d = f16_bits_to_f32(H.x), dmin = f16_bits_to_f32(H.x >> 16);
+    const __half2 ds = __float2half2_rn(d * (float)sv);
+    const __half2 nm = __float2half2_rn(-(dmin * (float)mv));
+    const __half2 k1024 = u32_as_h2(0x64006400u);
+    const int nsh = 4 * half;
+    const uint32_t w[8] = {A.x >> nsh, A.y >> nsh, A.z >> nsh, A.w >> nsh, B.x >> nsh, B.y >> nsh, B.z >> nsh, B.w >> nsh};
+    const uint32_t qh[8] = {Qa.x >> j, Qa.y >> j, Qa.z >> j, Qa.w >> j, Qb.x >> j, Qb.y >> j, Qb.z >> j, Qb.w >> j};   // bit 0 of every byte = this sub-block's
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const __half2 t0 = u32_as_h2((w[i] & 0x000f000fu) | ((qh[i] & 0x00010001u) << 4) | 0x64006400u);                 // weights (4i, 4i+2)
+        const __half2 t1 = u32_as_h2(((w[i] >> 8) & 0x000f000fu) | (((qh[i] >> 8) & 0x00010001u) << 4) | 0x64006400u);    // weights (4i+1, 4i+3)
         o[2 * i] = h2_as_u32(__hfma2(__hsub2(t0, k1024), ds, nm));
         o[2 * i + 1] = h2_as_u32(__hfma2(__hsub2(t1, k1024), ds, nm));
     }
@@ -306,7 +336,7 @@ extern "C" int ojas_b200_gemm_f16(ojas_b200_ctx *ctx, uint32_t type, const void 
 static int gemm_entry(ojas_b200_ctx *ctx, uint32_t type, const void *x, bool x_is_f16, const void *w, float *y, size_t K, size_t N, size_t M,
                       int accum, void *workspace, size_t workspace_bytes) {
     if (!ctx) return OJAS_B200_E_ARG;
-    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q6_K && type != OJAS_B200_Q8_0)
+    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q5_K && type != OJAS_B200_Q6_K && type != OJAS_B200_Q8_0)
         return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: unsupported GGUF type %u", type);
     if (!x || !w || !y || !workspace) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: null pointer");
     if (K == 0 || K % 256 != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: K=%zu must be a positive multiple of 256", K);
@@ -419,6 +449,7 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
         const dim3 grid_ts((unsigned)ctas);
         if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
         if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_Q5_K) return launch_gemm_ts_type<OJAS_B200_Q5_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
         return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
     }
 }
@@ -482,7 +513,7 @@ static void *gemm_static_scratch_ptr(ojas_b200_ctx *ctx, int *rc_out) {
         cudaFuncAttributes fa;
 #define OJAS_TOUCH(K) cudaFuncGetAttributes(&fa, K)
 #define OJAS_TOUCH_TYPE(T) OJAS_TOUCH((gemm_ts_kernel<32, T>)); OJAS_TOUCH((gemm_ts_kernel<64, T>)); OJAS_TOUCH((gemm_ts_kernel<128, T>)); OJAS_TOUCH((gemm_ts_kernel<256, T>))
-        OJAS_TOUCH_TYPE(OJAS_B200_Q4_K); OJAS_TOUCH_TYPE(OJAS_B200_Q6_K); OJAS_TOUCH_TYPE(OJAS_B200_Q8_0);
+        OJAS_TOUCH_TYPE(OJAS_B200_Q4_K); OJAS_TOUCH_TYPE(OJAS_B200_Q5_K); OJAS_TOUCH_TYPE(OJAS_B200_Q6_K); OJAS_TOUCH_TYPE(OJAS_B200_Q8_0);
         OJAS_TOUCH((gemm_prep_kernel<true, float>)); OJAS_TOUCH((gemm_prep_kernel<false, float>));
         OJAS_TOUCH((gemm_prep_kernel<true, __half>)); OJAS_TOUCH((gemm_prep_kernel<false, __half>));
 #undef OJAS_TOUCH_TYPE

@@ -357,7 +357,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
             uint4 hdr_next = make_uint4(0u, 0u, 0u, 0u);
             auto small_items = [&](int sb) {
                 const uint8_t *t = grow_tiles + (size_t)sb * TB;
-                if (TYPE == OJAS_B200_Q4_K) {
+                if (TYPE == OJAS_B200_Q4_K || TYPE == OJAS_B200_Q5_K) {
                     hdr_next = __ldg(reinterpret_cast<const uint4 *>(t + 8 * 128));
                 } else if (TYPE == OJAS_B200_Q6_K) {
                     hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(t + 12 * 128) + c);
@@ -384,9 +384,13 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         cC = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 2) * 128);
                         cD = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 3) * 128);
                         ce0 = H.x;
-                    } else if (TYPE == OJAS_B200_Q4_K) {
+                    } else if (TYPE == OJAS_B200_Q4_K || TYPE == OJAS_B200_Q5_K) {
                         cA = *reinterpret_cast<const uint4 *>(wrow + (2 * c) * 128);          // qs[32c .. 32c + 15]
                         cB = *reinterpret_cast<const uint4 *>(wrow + (2 * c + 1) * 128);      // qs[32c + 16 .. 32c + 31]
+                        if (TYPE == OJAS_B200_Q5_K) {                                         // the fifth bits of the whole super-block
+                            cC = *reinterpret_cast<const uint4 *>(wrow + 9 * 128);
+                            cD = *reinterpret_cast<const uint4 *>(wrow + 10 * 128);
+                        }
                     } else {
                         cA = *reinterpret_cast<const uint4 *>(wrow + c * 128);                // low nibbles, h = 0
                         cB = *reinterpret_cast<const uint4 *>(wrow + (4 + c) * 128);          // low nibbles, h = 1
@@ -402,6 +406,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         for (int q = 0; q < 16; q++) out[q] = 0u;
                     } else if (TYPE == OJAS_B200_Q4_K) {
                         dequant_q4k_half(cA, cB, H, c, half, out);
+                    } else if (TYPE == OJAS_B200_Q5_K) {
+                        dequant_q5k_half(cA, cB, cC, cD, H, c, half, out);
                     } else if (TYPE == OJAS_B200_Q6_K) {
                         dequant_q6k_half(cA, cB, cC, ce0, ce1, half, out);
                     } else if (half == 0) {

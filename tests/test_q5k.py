@@ -116,14 +116,42 @@ def test_q5k_store_forms_prequantized_rows_and_entry_names(gpu):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("m,n,k,accum,ksplit", [(32, 128, 256, False, 0), (17, 1000, 768, False, 0), (300, 515, 2304, True, 0), (513, 384, 1280, False, 3),
+                                                (512, 4096, 4096, False, 0), (2048, 1024, 4096, True, 0)])
+def test_q5k_prefill_gemm_matches_the_oracle(gpu, m, n, k, accum, ksplit):
+    """The tcgen05 GEMM with Q5_K weights (f16 weight tiles, f16(sx * q) activations) at the bar of the path, 2e-3; sampled
+    token rows for the large shapes; a sentinel row behind y."""
+    raw = _raw(n, k, roll=2)
+    x = activations(m, k, seed=20 + m)
+    rows = list(range(m)) if m <= 64 else sorted({0, 1, m // 3, m // 2, m - 2, m - 1})
+    want = oracle.matmul_kq(raw, Q5_K, n, k, x[rows])
+    w = gpu.load_weight(raw, Q5_K, n, k)
+    y0 = activations(m, n, seed=21) if accum else np.zeros((m, n), np.float32)
+    xb, yb = gpu.upload(x), gpu.upload(np.concatenate([y0, np.full((1, n), -77.0, np.float32)]))
+    gpu.set_option("gemm_ksplit", ksplit)
+    try:
+        gpu.gemm(w, xb, yb, m, accum)
+        got = gpu.read(yb, np.float32, (m + 1) * n).reshape(m + 1, n)
+    finally:
+        gpu.set_option("gemm_ksplit", 0)
+    assert np.all(got[m] == -77.0), "wrote past row M"
+    assert rel_l2(got[rows], want + y0[rows] if accum else want) < 2e-3
+    for b in (w.buf, xb, yb):
+        gpu.free(b)
+
+
+@pytest.mark.gpu
 def test_q5k_is_refused_where_it_is_not_built(gpu):
-    n, k = 256, 512
-    w = gpu.load_weight(_raw(n, k), Q5_K, n, k)
-    x, y = gpu.alloc(16 * k), gpu.alloc(16 * n)
-    with pytest.raises(ob.OjasB200Error):
-        gpu.gemm(w, x, y, 16)
+    """The expert FFN takes Q4_K and Q6_K experts only."""
+    e, d, ffn, m = 2, 256, 512, 4
+    mk = lambda n, k: gpu.load_weight(_raw(e * n, k), Q5_K, e * n, k)
+    wg, wu, wd = mk(ffn, d), mk(ffn, d), mk(d, ffn)
+    h, idx, wgt, out = gpu.alloc(m * d), gpu.alloc_bytes(m * 4), gpu.alloc(m), gpu.alloc(m * d)
+    gpu.memset(idx, 0)
+    with pytest.raises(ob.OjasB200Error, match="Q4_K or Q6_K"):
+        gpu.moe_ffn(wg, wu, wd, h, idx, wgt, out, m, e, 1)
     gpu.sync()
-    for b in (w.buf, x, y):
+    for b in (wg.buf, wu.buf, wd.buf, h, idx, wgt, out):
         gpu.free(b)
 
 
