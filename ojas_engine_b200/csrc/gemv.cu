@@ -1115,9 +1115,9 @@ int ojas_gemv_experts_batch(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0
 int ojas_gemv_experts_kq(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0, const uint8_t *w1, float *y0, float *y1, const int8_t *q,
                          const float *scales, const int32_t *bsums, const int *row_index, const int *counts, const int *offsets, size_t E, size_t K,
                          size_t N, size_t rows_hint) {
-    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q6_K) return 1;
+    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q5_K && type != OJAS_B200_Q6_K) return 1;
     if (N % OJAS_TILE_ROWS != 0 || E > (size_t)EXPERT_MAX_E) return 1;       // experts must start on a tile boundary
-    const char *name = type == OJAS_B200_Q6_K ? "moe_q6k_experts" : "moe_q4k_experts";
+    const char *name = type == OJAS_B200_Q6_K ? "moe_q6k_experts" : type == OJAS_B200_Q5_K ? "moe_q5k_experts" : "moe_q4k_experts";
     ExpertArgs a{};
     a.w[0] = w0; a.w[1] = w1; a.y[0] = y0; a.y[1] = y1; a.nw = w1 ? 2 : 1;
     a.expert_bytes = (N / OJAS_TILE_ROWS) * (K / 256) * (size_t)tile_bytes(type);
@@ -1154,6 +1154,12 @@ int ojas_gemv_experts_kq(ojas_b200_ctx *ctx, uint32_t type, const uint8_t *w0, c
             ojas_count_launch(ctx, name);
             return 0;
         };
+        if (type == OJAS_B200_Q5_K) {
+            if (nt == 4) return go(moe_kq_experts_kernel<OJAS_B200_Q5_K, 4>);
+            if (nt == 3) return go(moe_kq_experts_kernel<OJAS_B200_Q5_K, 3>);
+            if (nt == 2) return go(moe_kq_experts_kernel<OJAS_B200_Q5_K, 2>);
+            return go(moe_kq_experts_kernel<OJAS_B200_Q5_K, 1>);
+        }
         if (type == OJAS_B200_Q6_K) {
             if (nt == 4) return go(moe_kq_experts_kernel<OJAS_B200_Q6_K, 4>);
             if (nt == 3) return go(moe_kq_experts_kernel<OJAS_B200_Q6_K, 3>);

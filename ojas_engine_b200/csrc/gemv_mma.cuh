@@ -455,10 +455,18 @@ __host__ __device__ inline size_t expert_act_bytes(uint32_t type, int NT, size_t
 
 // One 16-row tile x one super-block x up to NTILE token tiles.  t0 / t1: this lane's row (g8) in the tile's two
 // 8-row weight tiles; xq, bsb, sx: the staged activations of the segment, `sbl` the super-block inside the segment.
-template <int NTILE>
+// FIVE: Q5_K (dot_q5k, crates/ojas-cpu/src/cpu_math.rs:637-671).  Weight l of sub-block j has its fifth bit in bit j of qh[l]
+// (pieces 9, 10 of the tile); the lane's eight weights 8q .. 8q+7 are the same l in every sub-block, so it loads its eight
+// qh bytes once per step.  Five-bit values do not leave room to keep high nibbles in place, so they are shifted down.
+template <int NTILE, bool FIVE = false>
 __device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *t1, bool second, const uint8_t *xq, int xstride, const uint8_t *bsb,
                                               const float *sx, int nsbseg, int sbl, int g8, int q4, int ntile, float (&acc)[NTILE][4]) {
     const uint4 H0 = *reinterpret_cast<const uint4 *>(t0 + 8 * 128), H1 = *reinterpret_cast<const uint4 *>(t1 + 8 * 128);
+    uint2 q50 = make_uint2(0u, 0u), q51 = q50;
+    if (FIVE) {
+        q50 = *reinterpret_cast<const uint2 *>(t0 + (9 + (q4 >> 1)) * 128 + (q4 & 1) * 8);
+        q51 = second ? *reinterpret_cast<const uint2 *>(t1 + (9 + (q4 >> 1)) * 128 + (q4 & 1) * 8) : make_uint2(0u, 0u);
+    }
     const uint32_t s0[2] = {H0.y & 0x3f3f3f3fu, (H0.w & 0x0f0f0f0fu) | ((H0.y >> 2) & 0x30303030u)};
     const uint32_t s1[2] = {H1.y & 0x3f3f3f3fu, (H1.w & 0x0f0f0f0fu) | ((H1.y >> 2) & 0x30303030u)};
     const uint32_t m0[2] = {H0.z & 0x3f3f3f3fu, ((H0.w >> 4) & 0x0f0f0f0fu) | ((H0.z >> 2) & 0x30303030u)};
@@ -473,8 +481,16 @@ __device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *
         const uint2 w0 = *reinterpret_cast<const uint2 *>(t0 + (2 * c + (q4 >> 1)) * 128 + (q4 & 1) * 8);
         uint2 w1 = *reinterpret_cast<const uint2 *>(t1 + (2 * c + (q4 >> 1)) * 128 + (q4 & 1) * 8);
         if (!second) w1 = make_uint2(0u, 0u);
-        const uint32_t alo[4] = {w0.x & 0x0f0f0f0fu, w1.x & 0x0f0f0f0fu, w0.y & 0x0f0f0f0fu, w1.y & 0x0f0f0f0fu};
-        const uint32_t ahi[4] = {w0.x & 0xf0f0f0f0u, w1.x & 0xf0f0f0f0u, w0.y & 0xf0f0f0f0u, w1.y & 0xf0f0f0f0u};
+        uint32_t alo[4] = {w0.x & 0x0f0f0f0fu, w1.x & 0x0f0f0f0fu, w0.y & 0x0f0f0f0fu, w1.y & 0x0f0f0f0fu};
+        uint32_t ahi[4] = {w0.x & 0xf0f0f0f0u, w1.x & 0xf0f0f0f0u, w0.y & 0xf0f0f0f0u, w1.y & 0xf0f0f0f0u};
+        if (FIVE) {                                                // sub-block 2c takes bit 2c of the qh bytes, 2c + 1 bit 2c + 1
+            const uint32_t hb[4] = {q50.x >> (2 * c), q51.x >> (2 * c), q50.y >> (2 * c), q51.y >> (2 * c)};
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                alo[k] |= (hb[k] & 0x01010101u) << 4;
+                ahi[k] = (ahi[k] >> 4) | ((hb[k] & 0x02020202u) << 3);
+            }
+        }
         const int sA0 = (int)__byte_perm(s0[c >> 1], 0, 0x4440 + 2 * (c & 1)), sB0 = (int)__byte_perm(s0[c >> 1], 0, 0x4441 + 2 * (c & 1));
         const int sA1 = (int)__byte_perm(s1[c >> 1], 0, 0x4440 + 2 * (c & 1)), sB1 = (int)__byte_perm(s1[c >> 1], 0, 0x4441 + 2 * (c & 1));
 #pragma unroll
@@ -485,10 +501,11 @@ __device__ __forceinline__ void mma_tile_step(const uint8_t *t0, const uint8_t *
                 int dlo[4], dhi[4];
                 mma_u8s8_z(dlo, alo, xa.x, xa.y);
                 mma_u8s8_z(dhi, ahi, xb.x, xb.y);
-                isum[t][0] += sA0 * dlo[0] + sB0 * (dhi[0] >> 4);
-                isum[t][1] += sA0 * dlo[1] + sB0 * (dhi[1] >> 4);
-                isum[t][2] += sA1 * dlo[2] + sB1 * (dhi[2] >> 4);
-                isum[t][3] += sA1 * dlo[3] + sB1 * (dhi[3] >> 4);
+                constexpr int HS = FIVE ? 0 : 4;                   // Q4_K keeps its high nibbles in place (x 16)
+                isum[t][0] += sA0 * dlo[0] + sB0 * (dhi[0] >> HS);
+                isum[t][1] += sA0 * dlo[1] + sB0 * (dhi[1] >> HS);
+                isum[t][2] += sA1 * dlo[2] + sB1 * (dhi[2] >> HS);
+                isum[t][3] += sA1 * dlo[3] + sB1 * (dhi[3] >> HS);
             }
         }
     }
@@ -693,7 +710,7 @@ __global__ void __launch_bounds__(GEMV_MAX_WARPS * 32, 1) moe_kq_experts_kernel(
                                 q6k_tile_step<NTILE>(u0, second ? u0 + TB : u0, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
                             } else {
                                 const uint8_t *t0 = ring + cstg * STEP + g8 * 16, *t1 = second ? t0 + TB : t0;
-                                mma_tile_step<NTILE>(t0, t1, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
+                                mma_tile_step<NTILE, TYPE == OJAS_B200_Q5_K>(t0, t1, second, xq, xstride, bsb, sx, nsbseg, sbl, g8, q4, ntile, acc);
                             }
                             __syncwarp();
                             if (lane == 0) {

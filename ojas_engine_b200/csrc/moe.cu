@@ -231,8 +231,11 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
     if (E == 0 || E > 1024 || KSEL == 0 || KSEL > 32 || KSEL > E) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: E=%zu KSEL=%zu out of range", E, KSEL);
     if (M == 0) return 0;
     if (M * KSEL > 0x3fffffffu) return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: too many assignments");
-    if ((type_gu != OJAS_B200_Q4_K && type_gu != OJAS_B200_Q6_K) || (type_d != OJAS_B200_Q4_K && type_d != OJAS_B200_Q6_K))
-        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "moe_ffn: expert weights must be Q4_K or Q6_K (got %u / %u)", type_gu, type_d);
+    auto expert_type = [](uint32_t t) { return t == OJAS_B200_Q4_K || t == OJAS_B200_Q5_K || t == OJAS_B200_Q6_K; };
+    if (!expert_type(type_gu) || !expert_type(type_d))
+        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "moe_ffn: expert weights must be Q4_K, Q5_K or Q6_K (got %u / %u)", type_gu, type_d);
+    if ((type_gu == OJAS_B200_Q5_K || type_d == OJAS_B200_Q5_K) && ctx->gemv_mma == 0)
+        return ojas_fail(ctx, OJAS_B200_E_UNSUPPORTED, "moe_ffn: Q5_K experts run on the tensor-core experts kernel only (option gemv_mma is 0)");
     if (workspace_bytes < ojas_b200_moe_workspace_bytes(M, E, KSEL, d, ffn))
         return ojas_fail(ctx, OJAS_B200_E_ARG, "moe_ffn: workspace of %zu bytes, %zu needed", workspace_bytes,
                          ojas_b200_moe_workspace_bytes(M, E, KSEL, d, ffn));
@@ -267,7 +270,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         // one launch of the mma.sync experts kernel over every expert and both tensors (Q4_K); otherwise one grouped
         // launch per expert and tensor
         rc = 1;
-        if ((type_gu == OJAS_B200_Q4_K || type_gu == OJAS_B200_Q6_K) && ctx->gemv_mma != 0) {
+        if (ctx->gemv_mma != 0) {
             rc = ojas_gemv_experts_kq(ctx, type_gu, (const uint8_t *)wg, (const uint8_t *)wu, w.g, w.u, w.xq, w.xs, w.xb, w.tok, w.counts, w.offsets, E, d,
                                       ffn, (A + E - 1) / E);
             if (rc == 1)
@@ -322,7 +325,7 @@ extern "C" int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t 
         return 0;
     }
     rc = 1;
-    if ((type_d == OJAS_B200_Q4_K || type_d == OJAS_B200_Q6_K) && ctx->gemv_mma != 0) {
+    if (ctx->gemv_mma != 0) {
         rc = ojas_gemv_experts_kq(ctx, type_d, (const uint8_t *)wd, nullptr, w.yd, nullptr, w.aq, w.as, w.ab, nullptr, w.counts, w.offsets, E, ffn, d,
                                   (A + E - 1) / E);
         if (rc == 1)

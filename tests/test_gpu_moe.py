@@ -76,6 +76,36 @@ def test_expert_ffn_small(gpu, t_gu, t_d):
     _moe_case(gpu, 3, 5, 3, 256, 512, t_gu, t_d, accum=True, seed=3)
 
 
+def test_q5k_experts(gpu):
+    """Q5_K experts (synthetic blocks: the library has no Q5_K encoder) on the tensor-core experts kernel, alone and with a
+    Q6_K down projection; rows past one pass, the accumulate form; refused when the option turns that kernel off."""
+    from ojas_engine_b200 import Q5_K
+
+    def synth(t, n, k, roll, d=None):
+        base = oracle.synth_blocks(t, n * k // 256).reshape(n, -1)
+        out = np.ascontiguousarray(np.roll(base, roll, axis=0)).reshape(-1, 176 if t == Q5_K else 210)
+        if d is not None:                             # smaller super-block scales: the prefill form keeps activations in f16
+            out[:, 0:2] = np.frombuffer(np.float16(d).tobytes(), np.uint8)
+            out[:, 2:4] = np.frombuffer(np.float16(d / 4).tobytes(), np.uint8)
+        return out.reshape(-1)
+
+    for (m, e, ksel, d, ffn, t_d, accum) in [(9, 4, 2, 512, 768, Q5_K, False), (40, 2, 2, 256, 1024, Q6_K, True), (3, 5, 3, 4096, 512, Q5_K, False)]:
+        experts = (synth(Q5_K, e * ffn, d, 1), synth(Q5_K, e * ffn, d, 5), synth(t_d, e * d, ffn, 9))
+        assert _moe_case(gpu, m, e, ksel, d, ffn, Q5_K, t_d, accum=accum, seed=m, experts=experts) < 3e-4
+    gpu.set_option("moe_gemm_rows", 8)                # the prefill form: gate / up stay on the exact kernel, down on the f16 tcgen05 GEMM
+    try:
+        experts = (synth(Q5_K, 2 * 512, 256, 2, 2e-4), synth(Q5_K, 2 * 512, 256, 3, 2e-4), synth(Q5_K, 2 * 256, 512, 4, 2e-4))
+        assert _moe_case(gpu, 64, 2, 2, 256, 512, Q5_K, Q5_K, seed=11, experts=experts) < TOL
+    finally:
+        gpu.set_option("moe_gemm_rows", 0)
+    gpu.set_option("gemv_mma", 0)
+    try:
+        with pytest.raises(ob.OjasB200Error, match="Q5_K experts"):
+            _moe_case(gpu, 2, 2, 1, 256, 256, Q5_K, Q5_K, experts=(synth(Q5_K, 512, 256, 0), synth(Q5_K, 512, 256, 1), synth(Q5_K, 512, 256, 2)))
+    finally:
+        gpu.set_option("gemv_mma", 1)
+
+
 def test_uneven_routing(gpu):
     """All tokens on one expert (more rows than one eight-row pass), experts with no tokens at all."""
     m, e, ksel = 21, 6, 2
@@ -237,7 +267,7 @@ def test_expert_cache_streams_and_serves_offsets(gpu):
 def test_moe_argument_errors(gpu):
     w = gpu.load_weight(gauss_weights(ob.Q8_0, 2 * 256, 256), ob.Q8_0, 2 * 256, 256)
     h, idx, wgt, out = gpu.upload(np.zeros((1, 256), np.float32)), gpu.upload(np.zeros(2, np.uint32)), gpu.upload(np.ones(2, np.float32)), gpu.alloc(256)
-    with pytest.raises(ob.OjasB200Error, match="Q4_K or Q6_K"):
+    with pytest.raises(ob.OjasB200Error, match="Q4_K, Q5_K or Q6_K"):
         gpu.moe_ffn(w, w, w, h, idx, wgt, out, 1, 2, 2)
     lg = gpu.upload(np.zeros((1, 4), np.float32))
     with pytest.raises(ob.OjasB200Error, match="KSEL"):

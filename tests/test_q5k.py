@@ -1,4 +1,4 @@
-"""Q5_K (GGUF type 13) on the repack + GEMV part of the path: layout, integer block dots, outputs, entry names.  The
+"""Q5_K (GGUF type 13): layout, integer block dots, GEMV outputs, entry names, the prefill GEMM (experts: tests/test_gpu_moe.py).  The
 CPU side of the format (decoder, dot_q5k against an independent transcription) is in tests/test_oracle.py."""
 import numpy as np
 import pytest
@@ -137,21 +137,6 @@ def test_q5k_prefill_gemm_matches_the_oracle(gpu, m, n, k, accum, ksplit):
     assert np.all(got[m] == -77.0), "wrote past row M"
     assert rel_l2(got[rows], want + y0[rows] if accum else want) < 2e-3
     for b in (w.buf, xb, yb):
-        gpu.free(b)
-
-
-@pytest.mark.gpu
-def test_q5k_is_refused_where_it_is_not_built(gpu):
-    """The expert FFN takes Q4_K and Q6_K experts only."""
-    e, d, ffn, m = 2, 256, 512, 4
-    mk = lambda n, k: gpu.load_weight(_raw(e * n, k), Q5_K, e * n, k)
-    wg, wu, wd = mk(ffn, d), mk(ffn, d), mk(d, ffn)
-    h, idx, wgt, out = gpu.alloc(m * d), gpu.alloc_bytes(m * 4), gpu.alloc(m), gpu.alloc(m * d)
-    gpu.memset(idx, 0)
-    with pytest.raises(ob.OjasB200Error, match="Q4_K or Q6_K"):
-        gpu.moe_ffn(wg, wu, wd, h, idx, wgt, out, m, e, 1)
-    gpu.sync()
-    for b in (wg.buf, wu.buf, wd.buf, h, idx, wgt, out):
         gpu.free(b)
 
 
