@@ -139,6 +139,7 @@ static int moe_down_named(ojas_b200_ctx *ctx, uint32_t type, void *const *b, con
     static int moe_down_##tag(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) { return moe_down_named(ctx, tag_type(#tag), b, c, false); }       \
     static int moe_down_##tag##_slots(ojas_b200_ctx *ctx, void *const *b, const uint32_t *c, const uint32_t *) { return moe_down_named(ctx, tag_type(#tag), b, c, true); }
 MOE_ENTRIES(q4k)
+MOE_ENTRIES(q5k)
 MOE_ENTRIES(q6k)
 MOE_ENTRIES(q80)
 MOE_ENTRIES(iq4xs)   // moe_gu_iq4xs: crates/ojas-cuda/src/kernels/moe_iq.rs:64-84 (the other three forms by analogy)
@@ -175,7 +176,7 @@ static const NameEntry kTable[] = {
     {"gemm_mm_q4k", 3, 4, gemm_q4k}, {"gemm_mm_q6k", 3, 4, gemm_q6k}, {"gemm_mm_q8_0", 3, 4, gemm_q8_0}, {"gemm_mm_q4l", 5, 4, gemm_q4l},
     {"gemm_mm_q4k_sk", 3, 4, gemm_q4k_sk}, {"gemm_mm_q6k_sk", 3, 4, gemm_q6k_sk}, {"gemm_mm_q8_0_sk", 3, 4, gemm_q8_0_sk},
     {"gemm_mm_q4l_sk", 5, 4, gemm_q4l_sk},
-    MOE_TABLE(q4k), MOE_TABLE(q6k), MOE_TABLE(q80), MOE_TABLE(iq4xs), MOE_TABLE(iq4nl),
+    MOE_TABLE(q4k), MOE_TABLE(q5k), MOE_TABLE(q6k), MOE_TABLE(q80), MOE_TABLE(iq4xs), MOE_TABLE(iq4nl),
 };
 static const int kTableLen = (int)(sizeof kTable / sizeof kTable[0]);
 
