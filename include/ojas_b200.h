@@ -32,8 +32,8 @@ extern "C" {
 
 typedef struct ojas_b200_ctx ojas_b200_ctx;
 
-/* GGUF tensor type codes on this path (crates/ojas-formats/src/synth.rs:12-21).  IQ4_NL and IQ4_XS: repack and the GEMV
- * family only (the prefill GEMM takes Q4_K, Q5_K, Q6_K and Q8_0; the expert FFN Q4_K, Q5_K and Q6_K).  IQ4_NL and IQ4_XS rows meet f32
+/* GGUF tensor type codes on this path (crates/ojas-formats/src/synth.rs:12-21).  Every format has the repack, the GEMV family and the
+ * prefill GEMM; the expert FFN (ojas_b200_moe_ffn) takes Q4_K, Q5_K and Q6_K experts.  IQ4_NL and IQ4_XS rows meet f32
  * activations, as Q8_0 rows do (dot_iq4nl / dot_iq4xs, crates/ojas-cpu/src/cpu_math.rs:993-1010, 943-967). */
 enum { OJAS_B200_Q8_0 = 8, OJAS_B200_Q4_K = 12, OJAS_B200_Q5_K = 13, OJAS_B200_Q6_K = 14, OJAS_B200_IQ4_NL = 20, OJAS_B200_IQ4_XS = 23 };
 

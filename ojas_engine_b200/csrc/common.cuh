@@ -108,8 +108,23 @@ __host__ __device__ constexpr int tile_bytes(uint32_t type) {
 __host__ __device__ constexpr bool f32_act_type(uint32_t type) { return type == OJAS_B200_Q8_0 || type == OJAS_B200_IQ4_XS || type == OJAS_B200_IQ4_NL; }
 // Bytes of the leading pieces that hold quants only (what the GEMM stages per tile; scales come after them).
 __host__ __device__ constexpr int tile_quant_bytes(uint32_t type) {
-    return type == OJAS_B200_Q4_K ? 1024 : type == OJAS_B200_Q5_K ? 1408 : type == OJAS_B200_Q6_K ? 1536 : 2048;   // (Q5_K: the whole tile, its fifth bits lie behind the header)
+    return type == OJAS_B200_Q4_K || type == OJAS_B200_IQ4_XS || type == OJAS_B200_IQ4_NL ? 1024 : type == OJAS_B200_Q5_K ? 1408 : type == OJAS_B200_Q6_K ? 1536 : 2048;   // (Q5_K: the whole tile, its fifth bits lie behind the header)
 }
+
+#ifdef __CUDACC__
+// Four index bytes of IQ4_NL / IQ4_XS (eight 4-bit indices into the sixteen int8 codebook values) looked up with byte
+// permutes: lo = the values of the four low nibbles, hi = of the four high nibbles, as packed int8.
+__device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t &lo, uint32_t &hi) {
+    constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;   // the codebook, four values per word
+    const uint32_t a0 = __byte_perm(T0, T1, q), b0 = __byte_perm(T2, T3, q);
+    const uint32_t v0 = __byte_perm(a0, b0, 0x3210u + ((q & 0x8888u) >> 1));          // values of nibbles 0..3
+    const uint32_t qh = q >> 16;
+    const uint32_t a1 = __byte_perm(T0, T1, qh), b1 = __byte_perm(T2, T3, qh);
+    const uint32_t v1 = __byte_perm(a1, b1, 0x3210u + ((qh & 0x8888u) >> 1));         // values of nibbles 4..7
+    lo = __byte_perm(v0, v1, 0x6420u);
+    hi = __byte_perm(v0, v1, 0x7531u);
+}
+#endif
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 static inline bool type_supported(uint32_t type) {

@@ -189,6 +189,26 @@ __device__ __forceinline__ void dequant_q80_half(const uint4 &q0, const uint4 &q
     }
 }
 
+// IQ4_XS / IQ4_NL: one 32-weight group (sixteen index bytes: low nibbles = weights 0..15, high nibbles = 16..31), scale dl
+// (IQ4_XS: d * (ls - 32) rounded to f16; IQ4_NL: the block's f16 d).  The codebook values come out of the lookup as int8
+// and take the Q8_0 route into f16.  Natural k order.
+__device__ __forceinline__ void dequant_iq4_half(const uint4 &Q, __half dl, uint32_t (&o)[16]) {
+    const __half2 k1152 = u32_as_h2(0x64806480u);   // 1024 + 128
+    const __half2 dd = __half2half2(dl);
+    const uint32_t q[4] = {Q.x, Q.y, Q.z, Q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        uint32_t lo, hi;
+        iq4_lookup8(q[i], lo, hi);
+        lo ^= 0x80808080u;
+        hi ^= 0x80808080u;
+        o[2 * i] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4140)), k1152), dd));
+        o[2 * i + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4342)), k1152), dd));
+        o[8 + 2 * i] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4140)), k1152), dd));
+        o[8 + 2 * i + 1] = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4342)), k1152), dd));
+    }
+}
+
 #include "gemm_ts.cuh"
 
 // ---------------------------------------------------------------- activation preparation
@@ -336,7 +356,7 @@ extern "C" int ojas_b200_gemm_f16(ojas_b200_ctx *ctx, uint32_t type, const void 
 static int gemm_entry(ojas_b200_ctx *ctx, uint32_t type, const void *x, bool x_is_f16, const void *w, float *y, size_t K, size_t N, size_t M,
                       int accum, void *workspace, size_t workspace_bytes) {
     if (!ctx) return OJAS_B200_E_ARG;
-    if (type != OJAS_B200_Q4_K && type != OJAS_B200_Q5_K && type != OJAS_B200_Q6_K && type != OJAS_B200_Q8_0)
+    if (!type_supported(type))
         return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: unsupported GGUF type %u", type);
     if (!x || !w || !y || !workspace) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: null pointer");
     if (K == 0 || K % 256 != 0) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: K=%zu must be a positive multiple of 256", K);
@@ -355,10 +375,10 @@ static int gemm_entry(ojas_b200_ctx *ctx, uint32_t type, const void *x, bool x_i
     if (blocks > 0x7fffffffLL) return ojas_fail(ctx, OJAS_B200_E_ARG, "gemm: activation matrix too large");
     unsigned *serial = ctx->gemm_flags + OJAS_GEMM_FLAG_WORDS;
     if (x_is_f16) {
-        if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false, __half><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __half *)x, xh, n_sb, serial);
+        if (f32_act_type(type)) gemm_prep_kernel<false, __half><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __half *)x, xh, n_sb, serial);
         else gemm_prep_kernel<true, __half><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const __half *)x, xh, n_sb, serial);
     } else {
-        if (type == OJAS_B200_Q8_0) gemm_prep_kernel<false, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float *)x, xh, n_sb, serial);
+        if (f32_act_type(type)) gemm_prep_kernel<false, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float *)x, xh, n_sb, serial);
         else gemm_prep_kernel<true, float><<<(unsigned)blocks, 256, 0, ctx->stream>>>((const float *)x, xh, n_sb, serial);
     }
     OJAS_LAUNCH_CHECK(ctx, "gemm_prep");
@@ -450,6 +470,8 @@ static int gemm_launch(ojas_b200_ctx *ctx, uint32_t type, const __half *xh, size
         if (type == OJAS_B200_Q4_K) return launch_gemm_ts_type<OJAS_B200_Q4_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
         if (type == OJAS_B200_Q6_K) return launch_gemm_ts_type<OJAS_B200_Q6_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
         if (type == OJAS_B200_Q5_K) return launch_gemm_ts_type<OJAS_B200_Q5_K>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_IQ4_XS) return launch_gemm_ts_type<OJAS_B200_IQ4_XS>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
+        if (type == OJAS_B200_IQ4_NL) return launch_gemm_ts_type<OJAS_B200_IQ4_NL>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
         return launch_gemm_ts_type<OJAS_B200_Q8_0>(ctx, bn, tmap, tmap_w, tmap_y, args, grid_ts);
     }
 }
@@ -514,6 +536,7 @@ static void *gemm_static_scratch_ptr(ojas_b200_ctx *ctx, int *rc_out) {
 #define OJAS_TOUCH(K) cudaFuncGetAttributes(&fa, K)
 #define OJAS_TOUCH_TYPE(T) OJAS_TOUCH((gemm_ts_kernel<32, T>)); OJAS_TOUCH((gemm_ts_kernel<64, T>)); OJAS_TOUCH((gemm_ts_kernel<128, T>)); OJAS_TOUCH((gemm_ts_kernel<256, T>))
         OJAS_TOUCH_TYPE(OJAS_B200_Q4_K); OJAS_TOUCH_TYPE(OJAS_B200_Q5_K); OJAS_TOUCH_TYPE(OJAS_B200_Q6_K); OJAS_TOUCH_TYPE(OJAS_B200_Q8_0);
+        OJAS_TOUCH_TYPE(OJAS_B200_IQ4_XS); OJAS_TOUCH_TYPE(OJAS_B200_IQ4_NL);
         OJAS_TOUCH((gemm_prep_kernel<true, float>)); OJAS_TOUCH((gemm_prep_kernel<false, float>));
         OJAS_TOUCH((gemm_prep_kernel<true, __half>)); OJAS_TOUCH((gemm_prep_kernel<false, __half>));
 #undef OJAS_TOUCH_TYPE

@@ -362,6 +362,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                 } else if (TYPE == OJAS_B200_Q6_K) {
                     hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(t + 12 * 128) + c);
                     hdr_next.y = __ldg(reinterpret_cast<const unsigned short *>(t - (lrow & 7) * 16 + 13 * 128) + (lrow & 7));
+                } else if (TYPE == OJAS_B200_IQ4_XS) {    // the block's eight header bytes: d, scales_h | scales_l
+                    const uint2 h8 = __ldg(reinterpret_cast<const uint2 *>(t - (lrow & 7) * 16 + 8 * 128 + (lrow & 7) * 8));
+                    hdr_next.x = h8.x;
+                    hdr_next.y = h8.y;
+                } else if (TYPE == OJAS_B200_IQ4_NL) {    // the chunk's two f16 block scales
+                    hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(t + 8 * 128) + c);
                 } else {                                  // the chunk's two f16 block scales
                     hdr_next.x = __ldg(reinterpret_cast<const uint32_t *>(t + 16 * 128) + c);
                 }
@@ -384,8 +390,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         cC = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 2) * 128);
                         cD = *reinterpret_cast<const uint4 *>(wrow + (4 * c + 3) * 128);
                         ce0 = H.x;
-                    } else if (TYPE == OJAS_B200_Q4_K || TYPE == OJAS_B200_Q5_K) {
-                        cA = *reinterpret_cast<const uint4 *>(wrow + (2 * c) * 128);          // qs[32c .. 32c + 15]
+                    } else if (TYPE == OJAS_B200_Q4_K || TYPE == OJAS_B200_Q5_K || TYPE == OJAS_B200_IQ4_XS || TYPE == OJAS_B200_IQ4_NL) {
+                        cA = *reinterpret_cast<const uint4 *>(wrow + (2 * c) * 128);          // qs[32c .. 32c + 15] (IQ4: the indices of group 2c)
                         cB = *reinterpret_cast<const uint4 *>(wrow + (2 * c + 1) * 128);      // qs[32c + 16 .. 32c + 31]
                         if (TYPE == OJAS_B200_Q5_K) {                                         // the fifth bits of the whole super-block
                             cC = *reinterpret_cast<const uint4 *>(wrow + 9 * 128);
@@ -408,6 +414,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1) gemm_ts_kernel(const __grid_con
                         dequant_q4k_half(cA, cB, H, c, half, out);
                     } else if (TYPE == OJAS_B200_Q5_K) {
                         dequant_q5k_half(cA, cB, cC, cD, H, c, half, out);
+                    } else if (TYPE == OJAS_B200_IQ4_XS) {
+                        const int g = 2 * c + half;
+                        const int ls = (int)(((H.y >> (4 * g)) & 0xFu) | ((((H.x >> 16) >> (2 * g)) & 3u) << 4)) - 32;
+                        dequant_iq4_half(half == 0 ? cA : cB, __float2half_rn(f16_bits_to_f32(H.x) * (float)ls), out);
+                    } else if (TYPE == OJAS_B200_IQ4_NL) {
+                        dequant_iq4_half(half == 0 ? cA : cB, __ushort_as_half((unsigned short)((H.x >> (16 * half)) & 0xffffu)), out);
                     } else if (TYPE == OJAS_B200_Q6_K) {
                         dequant_q6k_half(cA, cB, cC, ce0, ce1, half, out);
                     } else if (half == 0) {

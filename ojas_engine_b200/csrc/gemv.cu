@@ -548,16 +548,6 @@ __device__ __forceinline__ void step_q80(const uint8_t *wl, const uint8_t *act, 
 // (__byte_perm ignores the fourth), a third permute picks between them by that fourth bit, and two more separate the
 // low nibbles (weights j .. j+3 of the group) from the high ones (weights j+16 .. j+19).  Per group of 32: three exact
 // integer dots, then d * (ls - 32) * s * (D1 + D2 / 254 + D3 / 254^2).
-__device__ __forceinline__ void iq4_lookup8(uint32_t q, uint32_t &lo, uint32_t &hi) {
-    constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;   // the codebook, four values per word
-    const uint32_t a0 = __byte_perm(T0, T1, q), b0 = __byte_perm(T2, T3, q);
-    const uint32_t v0 = __byte_perm(a0, b0, 0x3210u + ((q & 0x8888u) >> 1));          // values of nibbles 0..3
-    const uint32_t qh = q >> 16;
-    const uint32_t a1 = __byte_perm(T0, T1, qh), b1 = __byte_perm(T2, T3, qh);
-    const uint32_t v1 = __byte_perm(a1, b1, 0x3210u + ((qh & 0x8888u) >> 1));         // values of nibbles 4..7
-    lo = __byte_perm(v0, v1, 0x6420u);
-    hi = __byte_perm(v0, v1, 0x7531u);
-}
 
 // NL: IQ4_NL (dot_iq4nl, :993-1010): the same codebook in plain blocks of 32, each with its own f16 scale and no sub-scale.
 template <int MT, bool NL>

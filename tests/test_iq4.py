@@ -166,12 +166,36 @@ def test_iq4_experts_by_name(gpu):
 
 @pytest.mark.gpu
 @BOTH
+@pytest.mark.parametrize("m,n,k,accum,ksplit", [(32, 128, 256, False, 0), (17, 1000, 768, False, 0), (300, 515, 2304, True, 0), (513, 384, 1280, False, 3),
+                                                (512, 4096, 4096, False, 0)])
+def test_iq4_prefill_gemm_matches_the_oracle(gpu, t, m, n, k, accum, ksplit):
+    """The tcgen05 GEMM with IQ4 weights (codebook values looked up and widened to f16, f16(x) activations as for Q8_0) at
+    the bar of the path, 2e-3; sampled token rows for the large shape; a sentinel row behind y."""
+    raw = _raw(n, k, roll=2, t=t)
+    x = activations(m, k, seed=20 + m)
+    rows = list(range(m)) if m <= 64 else sorted({0, 1, m // 3, m // 2, m - 2, m - 1})
+    want = oracle.matmul_kq(raw, t, n, k, x[rows])
+    w = gpu.load_weight(raw, t, n, k)
+    y0 = activations(m, n, seed=21) if accum else np.zeros((m, n), np.float32)
+    xb, yb = gpu.upload(x), gpu.upload(np.concatenate([y0, np.full((1, n), -77.0, np.float32)]))
+    gpu.set_option("gemm_ksplit", ksplit)
+    try:
+        gpu.gemm(w, xb, yb, m, accum)
+        got = gpu.read(yb, np.float32, (m + 1) * n).reshape(m + 1, n)
+    finally:
+        gpu.set_option("gemm_ksplit", 0)
+    assert np.all(got[m] == -77.0), "wrote past row M"
+    assert rel_l2(got[rows], want + y0[rows] if accum else want) < 2e-3
+    for b in (w.buf, xb, yb):
+        gpu.free(b)
+
+
+@pytest.mark.gpu
+@BOTH
 def test_iq4_is_refused_where_it_is_not_built(gpu, t):
     n, k = 256, 512
     w = gpu.load_weight(_raw(n, k, t=t), t, n, k)
     x, y = gpu.alloc(16 * k), gpu.alloc(16 * n)
-    with pytest.raises(ob.OjasB200Error):
-        gpu.gemm(w, x, y, 16)
     q, s, b = gpu.alloc_bytes(k), gpu.alloc(k // 256), gpu.alloc_bytes(k // 32 * 4)
     with pytest.raises(ob.OjasB200Error, match="f32 activations"):
         gpu.gemv_q8k(w, q, s, b, y, 1)
