@@ -7,6 +7,7 @@ import struct
 import numpy as np
 import pytest
 
+import oracle
 import ojas_engine_b200 as ob
 from ojas_engine_b200 import Q4_K, Q6_K, Q8_0
 from ojas_engine_b200.loader import GgufFile, LoaderError, WeightCache
@@ -55,6 +56,9 @@ def model(tmp_path):
         ("output.weight", Q8_0, (256, 40), gauss_weights(Q8_0, 40, 256, 4).tobytes()),
         ("blk.0.ffn_gate_exps.weight", Q4_K, (256, 8, 3), gauss_weights(Q4_K, 24, 256, 5).tobytes()),  # 3 experts of 8 rows
         ("blk.0.attn_norm.weight", F32, (64,), rng.standard_normal(64).astype(np.float32).tobytes()),
+        ("blk.0.attn_v.weight", ob.Q5_K, (512, 16), oracle.synth_blocks(ob.Q5_K, 16 * 2).tobytes()),
+        ("blk.0.ffn_up_exps.weight", ob.IQ4_XS, (256, 8, 2), oracle.synth_blocks(ob.IQ4_XS, 16).tobytes()),
+        ("blk.0.ffn_down_exps.weight", ob.IQ4_NL, (256, 8, 2), oracle.synth_blocks(ob.IQ4_NL, 16 * 8).tobytes()),
     ]
     path = tmp_path / "tiny.gguf"
     write_gguf(path, tensors)
@@ -132,9 +136,9 @@ def test_weight_cache_holds_the_repacked_matrices_and_follows_its_source(model, 
     with pytest.raises(LoaderError, match="rebuild"):
         WeightCache(cache_path, path)
     with WeightCache(cache_path) as c:                           # without a source to compare with it still opens
-        assert len(c) == 5
+        assert len(c) == 8
     with WeightCache.for_gguf(path, cache_path) as c:            # stale: rebuilt
-        assert len(c) == 5 and os.stat(cache_path).st_mtime_ns != built
+        assert len(c) == 8 and os.stat(cache_path).st_mtime_ns != built
 
 
 def test_corrupt_cache_is_rejected(model, tmp_path):
