@@ -152,8 +152,8 @@ OJAS_B200_API int ojas_b200_silu_mul_q8k(ojas_b200_ctx *ctx, const float *g, con
 /* ---- decode GEMV: replaces gemv_nat_{q4k,q6k,q80}{,_accum,_bias,_m}
  * (crates/ojas-cuda/src/kernels/nat.rs:69-91; bodies crates/ojas-core/src/quant_src.rs:779-867,
  * 1028-1057, 1154-1180) with the arithmetic of matvec_kq (crates/ojas-cpu/src/cpu_math.rs:
- * 1145-1189): Q4_K / Q6_K rows meet int8 Q8_K activations in exact integer block dots, Q8_0
- * rows meet f32 activations.  w is the repacked weight.  M <= OJAS_B200_GEMV_MAX_M. */
+ * 1145-1189): Q4_K / Q5_K / Q6_K rows meet int8 Q8_K activations in exact integer block dots, Q8_0,
+ * IQ4_NL and IQ4_XS rows meet f32 activations.  w is the repacked weight.  M <= OJAS_B200_GEMV_MAX_M. */
 #define OJAS_B200_GEMV_MAX_M 8
 OJAS_B200_API int ojas_b200_gemv(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *x, const void *w, float *y,
                    const float *bias, size_t K, size_t N, size_t M);
@@ -168,7 +168,7 @@ OJAS_B200_API int ojas_b200_gemv_rmsnorm(ojas_b200_ctx *ctx, uint32_t ggml_type,
  * ojas_b200_silu_mul_q8k: the two forms agree bit for bit. */
 OJAS_B200_API int ojas_b200_gemv_silu_mul(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const float *g, const float *u, const void *w,
                                           float *y, const float *bias, size_t K, size_t N, size_t M);
-/* Same, with activations already quantized by ojas_b200_quant_q8k (Q4_K / Q6_K only):
+/* Same, with activations already quantized by ojas_b200_quant_q8k (Q4_K / Q5_K / Q6_K only):
  * one quantization can feed several projections (gate and up read the same row). */
 OJAS_B200_API int ojas_b200_gemv_q8k(ojas_b200_ctx *ctx, uint32_t ggml_type, int form, const int8_t *q, const float *scales,
                        const int32_t *bsums, const void *w, float *y, const float *bias, size_t K, size_t N,
@@ -208,7 +208,7 @@ OJAS_B200_API size_t ojas_b200_reserved_bytes(ojas_b200_ctx *ctx);
  * that loads the library holds it until the process exits), so M * K <= 4 194 304
  * (ojas_b200_gemm_static_capacity() bytes / 2); larger shapes are refused with OJAS_B200_E_LIMIT.
  * Calls nothing that allocates.  The first call on a device looks up the array's device address and loads the code of
- * every kernel the entry can launch (all tile widths, all three formats); make that call at set-up, from one thread,
+ * every kernel the entry can launch (all tile widths, every format); make that call at set-up, from one thread,
  * before any stream capture: after it no call on that device allocates, whatever its shape or type.  The array is shared by every call and keeps the last call's
  * contents (each call overwrites the part it uses); two calls whose kernels overlap on the GPU (other
  * streams, other contexts on the same device) race on it. */
@@ -228,7 +228,7 @@ OJAS_B200_API int ojas_b200_moe_topk(ojas_b200_ctx *ctx, const float *logits, ui
  * h [M,d] f32; wg, wu: repacked stacked experts [E*ffn, d]; wd: [E*d, ffn]; idx, wgt as produced by
  * ojas_b200_moe_topk; out [M,d] f32 = sum_j wgt_j * down_e(silu(gate_e h) * up_e h)  (accum != 0: +=).
  * Assignments are grouped by expert so each expert's weights are read once.  `workspace`: caller-owned
- * scratch of ojas_b200_moe_workspace_bytes(...) bytes, 256-byte aligned.  Expert types: Q4_K, Q6_K. */
+ * scratch of ojas_b200_moe_workspace_bytes(...) bytes, 256-byte aligned.  Expert types: Q4_K, Q5_K, Q6_K. */
 OJAS_B200_API size_t ojas_b200_moe_workspace_bytes(size_t M, size_t E, size_t KSEL, size_t d, size_t ffn);
 OJAS_B200_API int ojas_b200_moe_ffn(ojas_b200_ctx *ctx, uint32_t type_gu, uint32_t type_d, const float *h, const void *wg,
                                     const void *wu, const void *wd, const uint32_t *idx, const float *wgt, size_t M, size_t E,
@@ -250,7 +250,7 @@ OJAS_B200_API int ojas_b200_gguf_tensor_info(const ojas_b200_gguf *g, size_t ind
                                              uint64_t dims[4], uint64_t *file_offset, uint64_t *bytes);
 OJAS_B200_API long long ojas_b200_gguf_find(const ojas_b200_gguf *g, const char *name);
 OJAS_B200_API int ojas_b200_gguf_read_raw(const ojas_b200_gguf *g, size_t index, void *dst, size_t bytes);
-/* build: every Q4_K / Q6_K / Q8_0 matrix of the GGUF re-laid on the host and written to cache_path (atomically).
+/* build: every matrix of the GGUF in a format of this path re-laid on the host and written to cache_path (atomically).
  * open: maps the file; with gguf_path given it must be the file the cache was built from, else OJAS_B200_E_UNSUPPORTED
  * (rebuild).  entry: name, type, [N, K] and a pointer to the repacked bytes inside the mapping. */
 OJAS_B200_API int ojas_b200_weight_cache_build(const char *gguf_path, const char *cache_path, char *err, size_t errlen);
