@@ -112,6 +112,35 @@ def _gemv_case(gpu, tag, n, k, m, source="gauss", form=PLAIN, seed=0):
     return err
 
 
+def test_committed_golden_vectors(gpu):
+    """tests/golden/oracle_vectors.npz: the committed activation row against the synthetic blocks of every format of the
+    path; the GEMV reproduces the committed outputs (fp32 summation order is all that differs), and quant_q8k and the
+    router reproduce theirs bit for bit."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_vectors.npz"))
+    x = g["x"].reshape(1, -1)
+    k, n = x.shape[1], 12
+    xb = gpu.upload(x)
+    for tag, t in [("q80", Q8_0), ("q4k", Q4_K), ("q5k", ob.Q5_K), ("q6k", Q6_K), ("iq4nl", ob.IQ4_NL), ("iq4xs", ob.IQ4_XS)]:
+        raw = oracle.synth_blocks(t, n * k // oracle.block_shape(t)[1])
+        w, y = gpu.load_weight(raw, t, n, k), gpu.alloc(n)
+        gpu.gemv(w, xb, y, 1)
+        assert rel_l2(gpu.read(y, np.float32, n), g[f"y_{tag}"]) < 1e-5, tag
+        gpu.free(w.buf)
+        gpu.free(y)
+    q, s, b = gpu.alloc_bytes(k), gpu.alloc(k // 256), gpu.alloc_bytes(k // 32 * 4)
+    gpu.quant_q8k(xb, 1, k, q, s, b)
+    assert np.array_equal(gpu.read(q, np.int8, k), g["q8k_q"]) and np.array_equal(gpu.read(b, np.int32, k // 32), g["q8k_bsums"])
+    assert np.array_equal(gpu.read(s, np.float32, k // 256).view(np.uint32), g["q8k_scales"].view(np.uint32))
+    lg = g["topk_logits"]
+    lb, ib, wb = gpu.upload(lg), gpu.alloc_bytes(lg.shape[0] * 2 * 4), gpu.alloc(lg.shape[0] * 2)
+    gpu.moe_topk(lb, ib, wb, lg.shape[0], lg.shape[1], 2)
+    assert np.array_equal(gpu.read(ib, np.uint32, lg.shape[0] * 2).reshape(-1, 2), g["topk_idx"])
+    assert np.allclose(gpu.read(wb, np.float32, lg.shape[0] * 2).reshape(-1, 2), g["topk_wgt"], rtol=1e-5, atol=1e-7)
+    for buf in (xb, q, s, b, lb, ib, wb):
+        gpu.free(buf)
+
+
 def test_config1_q4k_gemv(gpu):
     """Q4_K x f32, N = K = 4096, batch 1, seed 0: the operation ojas-cpu runs today."""
     err = _gemv_case(gpu, "q4k", 4096, 4096, 1)

@@ -1,4 +1,8 @@
 """The CPU oracle against the reference's own golden values (no GPU)."""
+import json
+import os
+import sys
+
 import numpy as np
 import pytest
 
@@ -8,15 +12,33 @@ from oracle import Q4_K, Q6_K, Q8_0
 from conftest import rel_l2
 
 
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+with open(os.path.join(GOLDEN, "reference_digests.json")) as _fh:
+    REFERENCE_DIGESTS = json.load(_fh)["cases"]
+
+
 # crates/ojas-formats/tests/quant_formats.rs:33-50: (type, value count, FNV-1a digest)
-@pytest.mark.parametrize("t,n,want", [(Q4_K, 10240, 0x6536b83e8b2292b4), (Q6_K, 10240, 0x38ecabe858257db6),
-                                      (oracle.Q5_K, 10240, 0x361cbd8f84e79ade), (oracle.IQ4_XS, 10240, 0x1429cafb4df9af64),
-                                      (oracle.IQ4_NL, 1280, 0xa5d4cf4e5db3a1bf)])
-def test_synth_block_digests(t, n, want):
+@pytest.mark.parametrize("case", REFERENCE_DIGESTS, ids=[c["name"] for c in REFERENCE_DIGESTS])
+def test_synth_block_digests(case):
+    t, n = case["type"], case["values"]
     raw = oracle.synth_blocks(t, 40)
     vals = oracle.dequant_f16(raw, t, n)
     assert vals.size == n
-    assert oracle.digest_f16(vals) == want
+    assert oracle.digest_f16(vals) == int(case["digest"], 16)
+
+
+def test_oracle_outputs_are_frozen():
+    """tests/golden/oracle_vectors.npz (written by tests/golden/make_oracle_vectors.py): the oracle reproduces its own
+    committed outputs bit for bit."""
+    sys.path.insert(0, GOLDEN)
+    import make_oracle_vectors
+    want = np.load(os.path.join(GOLDEN, "oracle_vectors.npz"))
+    got = make_oracle_vectors.compute()
+    assert sorted(got) == sorted(want.files)
+    for key in want.files:
+        a, b = np.asarray(got[key]), want[key]
+        assert a.dtype == b.dtype and a.shape == b.shape, key
+        assert a.tobytes() == b.tobytes(), key
 
 
 def test_q80_rows_fixture():
