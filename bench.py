@@ -552,7 +552,7 @@ def run_case(args) -> None:
         return
     tag, n, k, m = args.case.split(":")
     n, k, m = int(n), int(k), int(m)
-    t = {"q4k": ob.Q4_K, "q6k": ob.Q6_K, "q80": ob.Q8_0}[tag]
+    t = {"q4k": ob.Q4_K, "q5k": ob.Q5_K, "q6k": ob.Q6_K, "q80": ob.Q8_0, "iq4nl": ob.IQ4_NL, "iq4xs": ob.IQ4_XS}[tag]
     hbm_peak, _, peak_kind = measured_peaks()
     gpu = ob.B200Gpu(0)
     if args.no_pdl:
@@ -565,7 +565,7 @@ def run_case(args) -> None:
         gpu.set_option(kv.split("=")[0], int(kv.split("=")[1]))
     gguf = ob.raw_bytes(t, n, k)
     ring = args.ring or max(2, int(300e6 // gguf) + 1)
-    base = oracle.synth_blocks(t, n * k // (32 if t == ob.Q8_0 else 256)).reshape(n, -1)
+    base = oracle.synth_blocks(t, n * k // oracle.block_shape(t)[1]).reshape(n, -1)
     ws = [gpu.load_weight(np.ascontiguousarray(np.roll(base, 13 * i, axis=0)), t, n, k) for i in range(ring)]
     x = gpu.upload(np.random.default_rng(7).standard_normal((m, k), dtype=np.float32))
     y = gpu.alloc(m * n)
