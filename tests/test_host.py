@@ -26,17 +26,20 @@ def test_kernel_name_table():
     names = [l.ojas_b200_kernel_name(i).decode() for i in range(l.ojas_b200_kernel_count())]
     assert len(names) == len(set(names))
     # every native GEMV format carries its four forms (crates/ojas-cuda/tests/conformance.rs:85-202)
-    for tag in ("q4k", "q6k", "q80"):
+    for tag in ("q4k", "q5k", "q6k", "q80", "iq4xs", "iq4nl"):
         for suffix in ("", "_accum", "_bias", "_m"):
             assert f"gemv_nat_{tag}{suffix}" in names
             assert l.ojas_b200_has_kernel(f"gemv_nat_{tag}{suffix}".encode())
+    # the engine's IQ expert entries (crates/ojas-cuda/src/kernels/moe_iq.rs:64-108) and the token-table gather (qwen35.rs:53)
+    for name in ("moe_gu_iq4xs", "moe_down_iq4nl", "moe_gu_q80", "moe_down_q80_slots", "q35_embed_q4k", "moe_topk", "quant_q8k"):
+        assert name in names
     assert not l.ojas_b200_has_kernel(b"gemv_nat_q2k")
 
 
-@pytest.mark.parametrize("tag", ["q4k", "q6k", "q80"])
+@pytest.mark.parametrize("tag", ["q4k", "q5k", "q6k", "q80", "iq4xs", "iq4nl"])
 def test_sizes(tag):
-    t = TYPES[tag]
-    per256 = {"q4k": 144, "q6k": 210, "q80": 272}[tag]
+    t = {**TYPES, "q5k": ob.Q5_K, "iq4xs": ob.IQ4_XS, "iq4nl": ob.IQ4_NL}[tag]
+    per256 = {"q4k": 144, "q5k": 176, "q6k": 210, "q80": 272, "iq4xs": 136, "iq4nl": 144}[tag]
     assert ob.raw_bytes(t, 4096, 4096) == 4096 * 16 * per256
     assert ob.raw_bytes(t, 3, 256) == oracle.row_bytes(t, 256) * 3
     rp = ob.repacked_bytes(t, 4096, 4096)
