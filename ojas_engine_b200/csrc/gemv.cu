@@ -1043,7 +1043,7 @@ static bool batch_plan(ojas_b200_ctx *ctx, uint32_t type, int NT, size_t K, size
 static int batch_launch(ojas_b200_ctx *ctx, uint32_t type, BatchArgs a, int nt_want) {
     const char *name = type == OJAS_B200_Q6_K ? "gemv_q6k_batch" : "gemv_q4k_batch";
     for (int NT = nt_want; NT >= 8; NT >>= 1) {
-        GemvPlan p;
+        GemvPlan p{};
         if (!batch_plan(ctx, type, NT, (size_t)a.K, (size_t)a.N, p)) continue;
         const size_t units = tile_units((size_t)a.N);
         a.nsb = a.K / 256;
@@ -1246,7 +1246,7 @@ static int gemv_q80_kseg(ojas_b200_ctx *ctx, GemvArgs args, size_t nsb) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const GemvArgs)args, (const int)best_seg);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, args, (int)best_seg);
     if (e != cudaSuccess) return ojas_fail(ctx, OJAS_B200_E_CUDA, "launch gemv_q80_kseg: %s", cudaGetErrorString(e));
     ojas_count_launch(ctx, "gemv_q80_kseg");
     return 0;
